@@ -1,0 +1,287 @@
+"""Numerics of every CUDA kernel against a plain PyTorch fp32 formulation of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K():
+    from torchturbo_b200 import kernels
+
+    assert kernels.available(), "sm_100a library not built"
+    return kernels
+
+
+def _rand(*shape, scale=1.0, dtype=torch.bfloat16):
+    return (torch.randn(*shape, device="cuda", dtype=torch.float32) * scale).to(dtype)
+
+
+def _close(a, b, rtol=2e-2, atol=2e-2):
+    a, b = a.float(), b.float()
+    err = (a - b).abs().max().item()
+    ref = b.abs().max().item()
+    assert torch.allclose(a, b, rtol=rtol, atol=atol * max(ref, 1e-6)), f"max err {err} (ref max {ref})"
+
+
+@pytest.mark.parametrize("M,N,K_", [(128, 128, 64), (256, 512, 256), (300, 200, 136), (4096, 1536, 2048), (77, 8, 64)])
+def test_gemm_nt(K, M, N, K_):
+    a, b = _rand(M, K_), _rand(N, K_)
+    c = K.gemm(a, b)
+    torch.cuda.synchronize()
+    assert K.status() == (0, 0)
+    _close(c, a.float() @ b.float().t())
+
+
+@pytest.mark.parametrize("M,N,K_", [(256, 256, 128), (304, 264, 200), (2048, 2048, 768)])
+def test_gemm_nn_and_tn(K, M, N, K_):
+    a, b = _rand(M, K_), _rand(K_, N)
+    _close(K.gemm(a, b, b_mn=True), a.float() @ b.float())
+    at = _rand(K_, M)
+    _close(K.gemm(at, b, a_mn=True, b_mn=True), at.float().t() @ b.float())
+    bk = _rand(N, K_)
+    _close(K.gemm(at, bk, a_mn=True, b_mn=False), at.float().t() @ bk.float().t())
+    assert K.status() == (0, 0)
+
+
+def test_gemm_fp32_accumulate_and_residual(K):
+    a, b = _rand(512, 256), _rand(384, 256)
+    out = torch.ones(512, 384, device="cuda", dtype=torch.float32)
+    K.gemm(a, b, out=out, accumulate=True)
+    _close(out, a.float() @ b.float().t() + 1.0)
+    res = _rand(512, 384)
+    c = K.gemm(a, b, residual=res)
+    _close(c, a.float() @ b.float().t() + res.float())
+
+
+def test_gemm_swiglu_epilogue(K):
+    M, H, F = 384, 256, 320
+    x, w = _rand(M, H), _rand(2 * F, H, scale=0.1)
+    scale = torch.rand(M, device="cuda")
+    pre = torch.empty(M, 2 * F, device="cuda", dtype=torch.bfloat16)
+    y = K.gemm(x, w, swiglu=True, row_scale=scale, preact=pre)
+    ref_pre = (x.float() @ w.float().t())
+    _close(pre, ref_pre)
+    g, u = pre.float()[:, :F], pre.float()[:, F:]
+    _close(y, torch.nn.functional.silu(g) * u * scale[:, None])
+    # MN-major weights ([H, 2F], the expert layout)
+    wt = w.t().contiguous()
+    y2 = K.gemm(x, wt, b_mn=True, swiglu=True, row_scale=scale)
+    _close(y2, torch.nn.functional.silu(g) * u * scale[:, None])
+
+
+def test_grouped_gemm(K):
+    torch.manual_seed(0)
+    E, H, F, T, k = 8, 256, 192, 300, 2
+    idx = torch.randint(0, E, (T, k), device="cuda", dtype=torch.int32)
+    x = _rand(T, H)
+    pm = K.perm_index(idx, E)
+    xp, _ = K.perm_scatter(x, pm["row_of"], k, pm["capacity_rows"], counts=pm["counts"], seg_start=pm["seg_start"])
+    torch.cuda.synchronize()
+    assert int(pm["status"].item()) == 0
+    w = _rand(E, H, F, scale=0.1)  # [E, in, out]
+    y = K.gemm(xp, w, b_mn=True, tile_group=pm["tile_group"])
+    seg = pm["seg_start"].cpu().tolist()
+    cnt = pm["counts"].cpu().tolist()
+    for e in range(E):
+        rows = slice(seg[e], seg[e] + cnt[e])
+        _close(y[rows], xp[rows].float() @ w[e].float())
+    # dX: grouped with K-major B (w[e] is [H, F] = [N, K] for dX = dY @ w[e]^T)
+    dy = _rand(pm["capacity_rows"], F)
+    dx = K.gemm(dy, w, b_mn=False, tile_group=pm["tile_group"])
+    for e in range(E):
+        rows = slice(seg[e], seg[e] + cnt[e])
+        _close(dx[rows], dy[rows].float() @ w[e].float().t())
+    # dW: grouped-K; pad rows of xp are zero so they add nothing
+    dw = K.gemm(xp, dy, a_mn=True, b_mn=True, group_rows=pm["seg_start"], out_dtype=torch.float32)
+    for e in range(E):
+        rows = slice(seg[e], seg[e + 1])
+        _close(dw[e], xp[rows].float().t() @ dy[rows].float())
+    assert K.status() == (0, 0)
+
+
+def test_perm_roundtrip(K):
+    torch.manual_seed(1)
+    E, H, T, k = 16, 128, 257, 4
+    idx = torch.stack([torch.randperm(E, device="cuda")[:k] for _ in range(T)]).to(torch.int32)
+    prob = torch.rand(T, k, device="cuda")
+    x = _rand(T, H)
+    pm = K.perm_index(idx, E)
+    xp, rv = K.perm_scatter(x, pm["row_of"], k, pm["capacity_rows"], counts=pm["counts"], seg_start=pm["seg_start"],
+                            val=prob.reshape(-1))
+    row_of = pm["row_of"].long()
+    # (expert, token) order: rows of one expert are in token order
+    flat_e = idx.reshape(-1).long()
+    order = torch.argsort(flat_e * (T * k) + torch.arange(T * k, device="cuda"))
+    seg = pm["seg_start"].long()
+    cnt = torch.bincount(flat_e, minlength=E)
+    assert torch.equal(cnt.int(), pm["counts"])
+    rank = torch.empty_like(order)
+    start_unpadded = torch.cumsum(cnt, 0) - cnt
+    rank[order] = torch.arange(T * k, device="cuda") - start_unpadded[flat_e[order]]
+    assert torch.equal(row_of, seg[flat_e] + rank)
+    assert torch.equal(xp[row_of], x.repeat_interleave(k, 0))
+    assert torch.equal(rv[row_of], prob.reshape(-1))
+    out = K.perm_combine(xp, pm["row_of"], T, k, weights=prob)
+    _close(out, (x.float()[:, None, :] * prob[:, :, None]).sum(1))
+
+
+def test_rmsnorm(K):
+    T, H = 300, 2048
+    x, r, w = _rand(T, H), _rand(T, H), _rand(H)
+    y, rstd, xs = K.rmsnorm_fwd(x, w, 1e-6, residual=r)
+    s = (x.float() + r.float()).bfloat16().float()
+    ref = (s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + 1e-6)).bfloat16().float() * w.float()
+    _close(xs, s, atol=1e-2)
+    _close(y, ref)
+    dy, dres = _rand(T, H), _rand(T, H)
+    dx, dw = K.rmsnorm_bwd(dy, xs, w, rstd, dres=dres)
+    s_ = s.clone().requires_grad_(True)
+    w_ = w.float().clone().requires_grad_(True)
+    yy = s_ * torch.rsqrt(s_.pow(2).mean(-1, keepdim=True) + 1e-6) * w_
+    yy.backward(dy.float())
+    _close(dx, s_.grad + dres.float())
+    _close(dw, w_.grad)
+    # wide rows
+    x2, w2 = _rand(5, 5120), _rand(5120)
+    y2, _, _ = K.rmsnorm_fwd(x2, w2, 1e-6)
+    _close(y2, (x2.float() * torch.rsqrt(x2.float().pow(2).mean(-1, keepdim=True) + 1e-6)).bfloat16().float() * w2.float())
+
+
+def test_qknorm_rope(K):
+    T, nq, nkv, D = 130, 8, 2, 128
+    qkv = _rand(T, (nq + 2 * nkv) * D)
+    wq, wk = _rand(D), _rand(D)
+    pos = torch.arange(T, device="cuda").float()
+    inv = 1.0 / (1e6 ** (torch.arange(0, D, 2, device="cuda").float() / D))
+    ang = pos[:, None] * inv[None]
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+
+    def ref(qkv_f, wq_f, wk_f):
+        q = qkv_f[:, : nq * D].reshape(T, nq, D)
+        k = qkv_f[:, nq * D: (nq + nkv) * D].reshape(T, nkv, D)
+
+        def nr(x, w):
+            x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6) * w
+            x1, x2 = x[..., : D // 2], x[..., D // 2:]
+            c, s = cos[:, None], sin[:, None]
+            return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], -1)
+
+        return nr(q, wq_f), nr(k, wk_f)
+
+    q, k, rstd = K.qknorm_rope_fwd(qkv, nq, nkv, D, wq, wk, cos, sin, 1e-6)
+    a = qkv.float().requires_grad_(True)
+    b, c = wq.float().requires_grad_(True), wk.float().requires_grad_(True)
+    qr, kr = ref(a, b, c)
+    _close(q, qr)
+    _close(k, kr)
+    dq, dk = _rand(T, nq, D), _rand(T, nkv, D)
+    (qr * dq.float()).sum().add((kr * dk.float()).sum()).backward()
+    dqkv = torch.zeros_like(qkv)
+    dwq, dwk = K.qknorm_rope_bwd(dq, dk, qkv, nq, nkv, D, wq, wk, cos, sin, rstd, dqkv)
+    _close(dqkv[:, : (nq + nkv) * D], a.grad[:, : (nq + nkv) * D])
+    _close(dwq, b.grad)
+    _close(dwk, c.grad)
+
+
+def test_swiglu(K):
+    R, F = 200, 768
+    x = _rand(R, 2 * F)
+    sc = torch.rand(R, device="cuda")
+    y = K.swiglu_fwd(x, sc)
+    xf = x.float().requires_grad_(True)
+    s_ = sc.clone().requires_grad_(True)
+    ref = torch.nn.functional.silu(xf[:, :F]) * xf[:, F:] * s_[:, None]
+    _close(y, ref)
+    dy = _rand(R, F)
+    ref.backward(dy.float())
+    dx, ds = K.swiglu_bwd(dy, x, sc, want_dscale=True)
+    _close(dx, xf.grad)
+    _close(ds, s_.grad)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_cross_entropy(K, dtype):
+    R, V = 64, 5000
+    logits = _rand(R, V, scale=3.0, dtype=dtype)
+    labels = torch.randint(0, V, (R,), device="cuda")
+    labels[::7] = -100
+    grad = torch.empty(R, V, device="cuda", dtype=torch.bfloat16)
+    gs = torch.tensor([0.5], device="cuda")
+    loss = K.cross_entropy(logits, labels, grad_out=grad, grad_scale=gs)
+    lf = logits.float().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(lf, labels, reduction="none", ignore_index=-100)
+    _close(loss, ref, rtol=1e-3, atol=1e-3)
+    (ref.sum() * 0.5).backward()
+    _close(grad, lf.grad, atol=1e-2)
+
+
+def test_adamw_and_clip(K):
+    torch.manual_seed(0)
+    shapes = [(1000,), (70000,), (256, 300)]
+    ps = [torch.randn(*s, device="cuda") for s in shapes]
+    gs = [torch.randn(*s, device="cuda").bfloat16() if i == 1 else torch.randn(*s, device="cuda") for i, s in enumerate(shapes)]
+    ref_p = [p.clone().requires_grad_(True) for p in ps]
+    opt = torch.optim.AdamW(ref_p, lr=1e-2, weight_decay=0.1, betas=(0.9, 0.95), eps=1e-8)
+    m = [torch.zeros_like(p) for p in ps]
+    v = [torch.zeros_like(p) for p in ps]
+    sh = [torch.empty_like(p, dtype=torch.bfloat16) for p in ps]
+    plan = K.MultiTensorPlan(ps, m, v, sh)
+    for step in (1, 2):
+        plan.refresh_grads(gs)
+        part = K.grad_sqnorm_partials(plan)
+        clip = K.clip_coef(part, 1.0)
+        total = math.sqrt(sum(g.float().pow(2).sum().item() for g in gs))
+        assert abs(clip[1].item() - total) / total < 1e-4
+        K.adamw_step(plan, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step, clip=clip[2:3])
+        for rp, g in zip(ref_p, gs):
+            rp.grad = g.float() * min(1.0, 1.0 / (total + 1e-6))
+        opt.step()
+    for p, rp, s in zip(ps, ref_p, sh):
+        _close(p, rp.detach(), rtol=1e-4, atol=1e-5)
+        _close(s, rp.detach(), atol=1e-2)
+
+
+@pytest.mark.parametrize("score_fn", ["softmax_post", "softmax_pre", "sigmoid"])
+def test_router(K, score_fn):
+    torch.manual_seed(0)
+    T, E, k = 333, 128, 8
+    logits = torch.randn(T, E, device="cuda")
+    valid = torch.ones(T, dtype=torch.bool, device="cuda")
+    valid[-5:] = False
+    out = K.router_fwd(logits, k, score_fn, valid_mask=valid, want_stats=True, scaling=2.0)
+
+    def ref(lg):
+        if score_fn == "softmax_post":
+            tv, ti = torch.topk(lg, k, dim=-1)
+            p = torch.softmax(tv, -1)
+            sc = torch.softmax(lg, -1)
+        elif score_fn == "softmax_pre":
+            sc = torch.softmax(lg, -1)
+            p, ti = torch.topk(sc, k, dim=-1)
+        else:
+            s = torch.sigmoid(lg)
+            tv, ti = torch.topk(s, k, dim=-1)
+            p = tv / (tv.sum(-1, keepdim=True) + 1e-20)
+            sc = s / (s.sum(-1, keepdim=True) + 1e-20)
+        return p * 2.0, ti, sc
+
+    lg = logits.clone().requires_grad_(True)
+    p, ti, sc = ref(lg)
+    assert torch.equal(out["topk_idx"].long(), ti)
+    _close(out["topk_prob"], p, rtol=1e-4, atol=1e-5)
+    _close(out["lse"], torch.logsumexp(logits, -1), rtol=1e-4, atol=1e-5)
+    _close(out["score_sum"], (sc * valid[:, None]).sum(0), rtol=1e-3, atol=1e-4)
+    cnt = torch.bincount(ti[valid].reshape(-1), minlength=E)
+    assert torch.equal(out["aux_counts"].long(), cnt)
+    assert torch.equal(out["counts"].long(), torch.bincount(ti.reshape(-1), minlength=E))
+    dprob = torch.randn(T, k, device="cuda")
+    aux_g = torch.randn(E, device="cuda")
+    zc = torch.tensor([0.01], device="cuda")
+    loss = (p * dprob).sum() + ((sc * valid[:, None]) * aux_g).sum() + 0.01 * (torch.logsumexp(lg, -1)[valid] ** 2).sum()
+    loss.backward()
+    dl = K.router_bwd(logits, out["topk_idx"], out["topk_prob"], k, score_fn, dprob=dprob, aux_grad=aux_g,
+                      lse=out["lse"], valid_mask=valid, z_coef=zc, scaling=2.0)
+    _close(dl, lg.grad, rtol=1e-3, atol=1e-3)

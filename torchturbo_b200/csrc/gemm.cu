@@ -1,0 +1,514 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a: TMA -> shared (128B swizzle)
+// -> tcgen05.mma (cta_group::1, M=128) -> TMEM (double-buffered accumulator)
+// -> tcgen05.ld epilogue.  One kernel body covers
+//   * dense  C[M,N] = A . B          with A / B each K-major or MN-major in memory,
+//   * grouped-M (MoE forward / dX): rows are grouped by expert in 128-row aligned
+//     segments, `tile_group[m_tile]` names the expert whose B[g] the tile uses
+//     (-1 skips the tile).  Offsets live on the device; the host never syncs.
+//   * grouped-K (MoE dW): C[g] = A[rows_g]^T . B[rows_g] with row ranges from a
+//     device array (64-aligned, pad rows are zero).
+// Epilogues: plain store (bf16 or fp32, optional accumulate / residual add) and
+// SwiGLU (gate and up column panels are loaded side by side into one 256-wide
+// accumulator; out = silu(g) * u * row_scale, pre-activations optionally kept).
+//
+// Replaces cuBLAS `F.linear`, `grouped_gemm.ops.gmm` and the torch.compile'd
+// SwiGLU of the reference (ops/providers/cuda/grouped_matmul.py:19-36,
+// ops/providers/cuda/swiglu.py:26-36, models/modules/moe/experts.py:181-254).
+#include "common.cuh"
+
+namespace ttb {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr unsigned KID_GEMM = 1;
+
+enum Epi : int { EPI_STORE = 0, EPI_SWIGLU = 1 };
+
+struct GemmParams {
+  int M, N, K;   // per-problem extents (N = output columns; for SwiGLU N = F)
+  int m_tiles, n_tiles, groups_k;  // groups_k > 0 => grouped-K problem count
+  void* C;
+  long long ldc;         // elements
+  long long c_group_stride;  // elements between C[g] (grouped-K)
+  int c_fp32;            // 1: fp32 output, 0: bf16
+  int accumulate;        // C += result (read-modify-write)
+  const __nv_bfloat16* residual;  // optional [M, ldr] added before store (bf16 out)
+  long long ldr;
+  const int* tile_group;  // grouped-M: [m_tiles]
+  const int* group_rows;  // grouped-K: [groups_k + 1], multiples of BK
+  // SwiGLU
+  int F;                  // gate columns [0,F), up columns [F,2F)
+  const float* row_scale; // optional [M]
+  __nv_bfloat16* preact;  // optional [M, ld_preact] receives gate|up
+  long long ld_preact;
+};
+
+template <int BN, bool A_MN, bool B_MN>
+struct SmemLayout {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+template <int BN, bool A_MN, bool B_MN, int EPI>
+__global__ void __launch_bounds__(192, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  using L = SmemLayout<BN, A_MN, B_MN>;
+  constexpr int STAGES = L::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * L::STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* tfull = bars + 2 * STAGES;
+  uint64_t* tempty = bars + 2 * STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 4);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int groups = p.groups_k > 0 ? p.groups_k : 1;
+  const long long tiles_per_group = static_cast<long long>(p.m_tiles) * p.n_tiles;
+  const long long total_tiles = tiles_per_group * groups;
+
+  // Decode tile -> (g, m_tile, n_tile); m fastest so concurrently running CTAs share a B panel.
+  auto decode = [&](long long t, int& g, int& mt, int& nt) {
+    g = static_cast<int>(t / tiles_per_group);
+    long long r = t - static_cast<long long>(g) * tiles_per_group;
+    nt = static_cast<int>(r / p.m_tiles);
+    mt = static_cast<int>(r - static_cast<long long>(nt) * p.m_tiles);
+  };
+  // k-range of a tile: dense -> [0, K); grouped-K -> rows of group g.
+  auto krange = [&](int g, int& k0, int& nkb) {
+    if (p.groups_k > 0) {
+      int r0 = p.group_rows[g], r1 = p.group_rows[g + 1];
+      k0 = r0;
+      nkb = (r1 - r0) / BK;
+    } else {
+      k0 = 0;
+      nkb = (p.K + BK - 1) / BK;
+    }
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int g, mt, nt, k0, nkb;
+        decode(t, g, mt, nt);
+        int bgroup = 0;
+        if (p.tile_group) {
+          bgroup = p.tile_group[mt];
+          if (bgroup < 0) continue;
+        }
+        krange(g, k0, nkb);
+        const int m0 = mt * BM;
+        const int n0 = nt * (EPI == EPI_SWIGLU ? BN / 2 : BN);
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, KID_GEMM, 1)) { ok = false; break; }
+          uint8_t* sa = smem + stage * L::STAGE_BYTES;
+          uint8_t* sb = sa + L::A_BYTES;
+          mbar_expect_tx(&full[stage], L::STAGE_BYTES);
+          const int kc = k0 + kb * BK;
+          if (!A_MN) {
+            tma_load_2d(sa, &tmA, &full[stage], kc, m0);
+          } else {
+            tma_load_2d(sa, &tmA, &full[stage], m0, kc);
+            tma_load_2d(sa + 8192, &tmA, &full[stage], m0 + 64, kc);
+          }
+          if (!B_MN) {
+            if (EPI == EPI_SWIGLU) {
+              tma_load_3d(sb, &tmB, &full[stage], kc, n0, bgroup);
+              tma_load_3d(sb + (BN / 2) * 128, &tmB, &full[stage], kc, p.F + n0, bgroup);
+            } else {
+              tma_load_3d(sb, &tmB, &full[stage], kc, n0, bgroup);
+            }
+          } else {
+            constexpr int PANELS = BN / 64;
+#pragma unroll
+            for (int q = 0; q < PANELS; ++q) {
+              int nc;
+              if (EPI == EPI_SWIGLU) {
+                nc = (q < PANELS / 2) ? (n0 + q * 64) : (p.F + n0 + (q - PANELS / 2) * 64);
+              } else {
+                nc = n0 + q * 64;
+              }
+              tma_load_3d(sb + q * 8192, &tmB, &full[stage], nc, kc, bgroup);
+            }
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int g, mt, nt, k0, nkb;
+        decode(t, g, mt, nt);
+        if (p.tile_group && p.tile_group[mt] < 0) continue;
+        krange(g, k0, nkb);
+        if (!mbar_wait(&tempty[acc], acc_phase ^ 1, KID_GEMM, 2)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(&full[stage], phase, KID_GEMM, 3)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * L::STAGE_BYTES);
+          const uint32_t sb = sa + L::A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            const uint64_t da = A_MN ? make_smem_desc(sa + kk * 2048, 8192, 1024)
+                                     : make_smem_desc(sa + kk * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc(sb + kk * 2048, 8192, 1024)
+                                     : make_smem_desc(sb + kk * 32, 16, 1024);
+            umma_ss(d_tmem, da, db, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&tfull[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int lane_group = warp & 3;  // TMEM lanes [32*lane_group, +32) are the ones this warp may touch
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      int g, mt, nt, k0, nkb;
+      decode(t, g, mt, nt);
+      if (p.tile_group && p.tile_group[mt] < 0) continue;
+      krange(g, k0, nkb);
+      if (!mbar_wait(&tfull[acc], acc_phase, KID_GEMM, 4)) { ok = false; break; }
+      tc_fence_after();
+      const int row = mt * BM + lane_group * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(lane_group * 32) << 16);
+
+      if (EPI == EPI_STORE) {
+        const int n0 = nt * BN;
+        uint8_t* cbase = reinterpret_cast<uint8_t*>(p.C);
+        const long long coff = static_cast<long long>(g) * p.c_group_stride + static_cast<long long>(row) * p.ldc;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col0 = n0 + c * 32;
+          if (col0 >= p.N) break;  // uniform across the warp
+          uint32_t v[32];
+          if (nkb > 0) {
+            tmem_ld_32x32b_x32(t_row + c * 32, v);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0u;
+          }
+          if (!row_ok) continue;
+          const bool full_chunk = (col0 + 32 <= p.N);
+          if (p.c_fp32) {
+            float* dst = reinterpret_cast<float*>(cbase) + coff + col0;
+            if (full_chunk) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) {
+                float4 o = make_float4(__uint_as_float(v[i]), __uint_as_float(v[i + 1]), __uint_as_float(v[i + 2]),
+                                       __uint_as_float(v[i + 3]));
+                if (p.accumulate) {
+                  float4 old = *reinterpret_cast<float4*>(dst + i);
+                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                *reinterpret_cast<float4*>(dst + i) = o;
+              }
+            } else {
+              for (int i = 0; i < 32 && col0 + i < p.N; ++i) {
+                float o = __uint_as_float(v[i]);
+                if (p.accumulate) o += dst[i];
+                dst[i] = o;
+              }
+            }
+          } else {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(cbase) + coff + col0;
+            const __nv_bfloat16* res = p.residual ? p.residual + static_cast<long long>(row) * p.ldr + col0 : nullptr;
+            if (full_chunk) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                float f[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[i + j]);
+                if (res) {
+                  uint4 r = *reinterpret_cast<const uint4*>(res + i);
+                  float2 a = unpack_bf16(r.x), b = unpack_bf16(r.y), c2 = unpack_bf16(r.z), d = unpack_bf16(r.w);
+                  f[0] += a.x; f[1] += a.y; f[2] += b.x; f[3] += b.y;
+                  f[4] += c2.x; f[5] += c2.y; f[6] += d.x; f[7] += d.y;
+                }
+                if (p.accumulate) {
+                  uint4 r = *reinterpret_cast<const uint4*>(dst + i);
+                  float2 a = unpack_bf16(r.x), b = unpack_bf16(r.y), c2 = unpack_bf16(r.z), d = unpack_bf16(r.w);
+                  f[0] += a.x; f[1] += a.y; f[2] += b.x; f[3] += b.y;
+                  f[4] += c2.x; f[5] += c2.y; f[6] += d.x; f[7] += d.y;
+                }
+                uint4 o;
+                o.x = pack_bf16(f[0], f[1]); o.y = pack_bf16(f[2], f[3]);
+                o.z = pack_bf16(f[4], f[5]); o.w = pack_bf16(f[6], f[7]);
+                *reinterpret_cast<uint4*>(dst + i) = o;
+              }
+            } else {
+              for (int i = 0; i < 32 && col0 + i < p.N; ++i) {
+                float o = __uint_as_float(v[i]);
+                if (res) o += __bfloat162float(res[i]);
+                if (p.accumulate) o += __bfloat162float(dst[i]);
+                dst[i] = __float2bfloat16(o);
+              }
+            }
+          }
+        }
+      } else {
+        // SwiGLU: accumulator columns [0,BN/2) = gate, [BN/2,BN) = up, for output columns n0..n0+BN/2.
+        constexpr int HALF = BN / 2;
+        const int n0 = nt * HALF;
+        const float scale = (p.row_scale && row_ok) ? p.row_scale[row] : 1.0f;
+        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc;
+        __nv_bfloat16* pre = p.preact ? p.preact + static_cast<long long>(row) * p.ld_preact : nullptr;
+#pragma unroll 1
+        for (int c = 0; c < HALF / 32; ++c) {
+          const int col0 = n0 + c * 32;
+          if (col0 >= p.N) break;
+          uint32_t gv[32], uv[32];
+          tmem_ld_32x32b_x32(t_row + c * 32, gv);
+          tmem_ld_32x32b_x32(t_row + HALF + c * 32, uv);
+          tmem_ld_wait();
+          if (!row_ok) continue;
+          const int lim = min(32, p.N - col0);
+          if (lim == 32) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint32_t o[4], pg[4], pu[4];
+#pragma unroll
+              for (int j = 0; j < 8; j += 2) {
+                // pre-activations are rounded to bf16 first so forward and backward see the same values
+                float g0 = __bfloat162float(__float2bfloat16(__uint_as_float(gv[i + j])));
+                float g1 = __bfloat162float(__float2bfloat16(__uint_as_float(gv[i + j + 1])));
+                float u0 = __bfloat162float(__float2bfloat16(__uint_as_float(uv[i + j])));
+                float u1 = __bfloat162float(__float2bfloat16(__uint_as_float(uv[i + j + 1])));
+                float a0 = g0 / (1.0f + __expf(-g0)) * u0 * scale;
+                float a1 = g1 / (1.0f + __expf(-g1)) * u1 * scale;
+                o[j / 2] = pack_bf16(a0, a1);
+                pg[j / 2] = pack_bf16(g0, g1);
+                pu[j / 2] = pack_bf16(u0, u1);
+              }
+              *reinterpret_cast<uint4*>(out + col0 + i) = make_uint4(o[0], o[1], o[2], o[3]);
+              if (pre) {
+                *reinterpret_cast<uint4*>(pre + col0 + i) = make_uint4(pg[0], pg[1], pg[2], pg[3]);
+                *reinterpret_cast<uint4*>(pre + p.F + col0 + i) = make_uint4(pu[0], pu[1], pu[2], pu[3]);
+              }
+            }
+          } else {
+            for (int i = 0; i < lim; ++i) {
+              float g0 = __bfloat162float(__float2bfloat16(__uint_as_float(gv[i])));
+              float u0 = __bfloat162float(__float2bfloat16(__uint_as_float(uv[i])));
+              out[col0 + i] = __float2bfloat16(g0 / (1.0f + __expf(-g0)) * u0 * scale);
+              if (pre) {
+                pre[col0 + i] = __float2bfloat16(g0);
+                pre[p.F + col0 + i] = __float2bfloat16(u0);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+// ----------------------------------------------------------------------------
+// Host launcher
+// ----------------------------------------------------------------------------
+struct GemmArgs {
+  const void* A;      // bf16
+  long long lda;      // elements: row stride of A's memory matrix
+  const void* B;      // bf16
+  long long ldb;      // elements: row stride of B's memory matrix
+  long long b_group_stride;  // elements between B[g] (grouped-M), 0 otherwise
+  int b_groups;       // number of B groups (>=1)
+  void* C;
+  long long ldc;
+  long long c_group_stride;
+  int M, N, K;        // grouped-K: K ignored, M = rows of A^T ( = columns of A memory ), N = cols of B memory
+  int a_mn, b_mn;     // memory orientation: 0 = K contiguous, 1 = M/N contiguous
+  int c_fp32, accumulate;
+  const void* residual;
+  long long ldr;
+  const int* tile_group;
+  int m_tiles_cap;    // grouped-M: number of m tiles to schedule (capacity)
+  const int* group_rows;
+  int groups_k;
+  long long total_rows;  // grouped-K: total rows of A/B memory matrices
+  int epi;            // 0 store, 1 swiglu
+  int F;
+  const float* row_scale;
+  void* preact;
+  long long ld_preact;
+  int num_sms;
+};
+
+template <int BN, bool A_MN, bool B_MN, int EPI>
+static int launch(const GemmArgs& a, cudaStream_t stream) {
+  using L = SmemLayout<BN, A_MN, B_MN>;
+  CUtensorMap tmA, tmB;
+  // ---- A map (2D)
+  {
+    uint64_t dims[2];
+    uint64_t str[1] = {static_cast<uint64_t>(a.lda) * 2};
+    uint32_t box[2];
+    if (!A_MN) {
+      // memory [M rows][K contiguous]
+      dims[0] = static_cast<uint64_t>(a.K);
+      dims[1] = static_cast<uint64_t>(a.M);
+      box[0] = BK;
+      box[1] = BM;
+    } else {
+      // memory [K rows][M contiguous]
+      dims[0] = static_cast<uint64_t>(a.M);
+      dims[1] = static_cast<uint64_t>(a.groups_k > 0 ? a.total_rows : a.K);
+      box[0] = 64;
+      box[1] = BK;
+    }
+    int r = make_tmap_bf16(&tmA, a.A, 2, dims, str, box);
+    if (r) return 100 + r;
+  }
+  // ---- B map (3D, last dim = group)
+  const int n_mem = (EPI == EPI_SWIGLU) ? 2 * a.F : a.N;
+  {
+    uint64_t dims[3];
+    uint64_t str[2];
+    uint32_t box[3];
+    str[0] = static_cast<uint64_t>(a.ldb) * 2;
+    const uint64_t rows_b = !B_MN ? static_cast<uint64_t>(n_mem)
+                                  : static_cast<uint64_t>(a.groups_k > 0 ? a.total_rows : a.K);
+    str[1] = a.b_groups > 1 ? static_cast<uint64_t>(a.b_group_stride) * 2 : rows_b * str[0];
+    dims[2] = static_cast<uint64_t>(a.b_groups > 1 ? a.b_groups : 1);
+    if (!B_MN) {
+      // memory [N rows][K contiguous]
+      dims[0] = static_cast<uint64_t>(a.K);
+      dims[1] = rows_b;
+      box[0] = BK;
+      box[1] = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+    } else {
+      // memory [K rows][N contiguous]
+      dims[0] = static_cast<uint64_t>(n_mem);
+      dims[1] = rows_b;
+      box[0] = 64;
+      box[1] = BK;
+    }
+    box[2] = 1;
+    int r = make_tmap_bf16(&tmB, a.B, 3, dims, str, box);
+    if (r) return 200 + r;
+  }
+  GemmParams p;
+  p.M = a.M; p.N = a.N; p.K = a.K;
+  constexpr int TN = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+  p.m_tiles = a.tile_group ? a.m_tiles_cap : (a.M + BM - 1) / BM;
+  p.n_tiles = (a.N + TN - 1) / TN;
+  p.groups_k = a.groups_k;
+  p.C = a.C; p.ldc = a.ldc; p.c_group_stride = a.c_group_stride;
+  p.c_fp32 = a.c_fp32; p.accumulate = a.accumulate;
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(a.residual); p.ldr = a.ldr;
+  p.tile_group = a.tile_group; p.group_rows = a.group_rows;
+  p.F = a.F; p.row_scale = a.row_scale;
+  p.preact = reinterpret_cast<__nv_bfloat16*>(a.preact); p.ld_preact = a.ld_preact;
+
+  auto kfn = gemm_kernel<BN, A_MN, B_MN, EPI>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) return 300 + static_cast<int>(e);
+    attr_set = true;
+  }
+  long long total = static_cast<long long>(p.m_tiles) * p.n_tiles * (p.groups_k > 0 ? p.groups_k : 1);
+  if (total <= 0) return 0;
+  int grid = static_cast<int>(total < a.num_sms ? total : a.num_sms);
+  kfn<<<grid, 192, L::TOTAL, stream>>>(tmA, tmB, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + static_cast<int>(e);
+}
+
+}  // namespace ttb
+
+// Returns 0 on success; non-zero codes: 1xx/2xx tensor-map encode failure, 3xx attribute, 4xx launch, 9xx bad args.
+TTB_EXPORT int ttb_gemm_bf16(const ttb::GemmArgs* args, void* stream_ptr) {
+  using namespace ttb;
+  const GemmArgs& a = *args;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_ptr);
+  if ((a.lda % 8) || (a.ldb % 8)) return 901;
+  if ((reinterpret_cast<uintptr_t>(a.A) | reinterpret_cast<uintptr_t>(a.B)) & 15) return 902;
+  // vectorised epilogue stores: 16-byte aligned rows
+  if (a.c_fp32 ? (a.ldc % 4) : (a.ldc % 8)) return 903;
+  if (reinterpret_cast<uintptr_t>(a.C) & 15) return 903;
+  if (a.residual && ((a.ldr % 8) || (reinterpret_cast<uintptr_t>(a.residual) & 15))) return 904;
+  if (a.epi == EPI_SWIGLU && ((a.F % 8) || a.c_fp32 || (a.preact && (a.ld_preact % 8)))) return 905;
+  const bool wide = (a.epi == EPI_SWIGLU) ? true : (a.N > 128);
+#define TTB_DISPATCH(AMN, BMN)                                                             \
+  if (a.epi == EPI_SWIGLU) return launch<256, AMN, BMN, EPI_SWIGLU>(a, stream);            \
+  if (wide) return launch<256, AMN, BMN, EPI_STORE>(a, stream);                            \
+  return launch<128, AMN, BMN, EPI_STORE>(a, stream);
+  if (!a.a_mn && !a.b_mn) { TTB_DISPATCH(false, false) }
+  if (!a.a_mn && a.b_mn) { TTB_DISPATCH(false, true) }
+  if (a.a_mn && a.b_mn) { TTB_DISPATCH(true, true) }
+  if (a.a_mn && !a.b_mn) { TTB_DISPATCH(true, false) }
+#undef TTB_DISPATCH
+  return 999;
+}
+
+TTB_EXPORT int ttb_gemm_status(unsigned int* out4, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(out4, ttb::g_status_word, sizeof(unsigned int) * 4);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (reset) {
+    unsigned int z[4] = {0, 0, 0, 0};
+    e = cudaMemcpyToSymbol(ttb::g_status_word, z, sizeof(z));
+  }
+  return static_cast<int>(e);
+}

@@ -1,0 +1,449 @@
+"""ctypes bindings for the sm_100a CUDA library (`_lib/libttb200.so`).
+
+Every function here launches hand-written kernels on the *current* CUDA stream
+and takes/returns torch tensors.  Nothing falls back to PyTorch: if the library
+is missing on a machine with a GPU, `lib()` raises so that a silent eager path
+can never pass for the native one.  CPU-only processes never touch this module
+(the op dispatcher selects the torch providers there).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from functools import lru_cache
+from pathlib import Path
+
+import torch
+
+_LIB_PATH = Path(__file__).resolve().parent / "_lib" / "libttb200.so"
+_lib = None
+
+SEG_ALIGN = 128  # rows; every expert segment of a permuted buffer is padded to this
+SCORE_FN = {"softmax_pre": 0, "softmax_post": 1, "sigmoid": 2}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+class _GemmArgs(C.Structure):
+    _fields_ = [
+        ("A", C.c_void_p), ("lda", C.c_longlong),
+        ("B", C.c_void_p), ("ldb", C.c_longlong),
+        ("b_group_stride", C.c_longlong), ("b_groups", C.c_int),
+        ("C", C.c_void_p), ("ldc", C.c_longlong), ("c_group_stride", C.c_longlong),
+        ("M", C.c_int), ("N", C.c_int), ("K", C.c_int),
+        ("a_mn", C.c_int), ("b_mn", C.c_int),
+        ("c_fp32", C.c_int), ("accumulate", C.c_int),
+        ("residual", C.c_void_p), ("ldr", C.c_longlong),
+        ("tile_group", C.c_void_p), ("m_tiles_cap", C.c_int),
+        ("group_rows", C.c_void_p), ("groups_k", C.c_int),
+        ("total_rows", C.c_longlong),
+        ("epi", C.c_int), ("F", C.c_int),
+        ("row_scale", C.c_void_p), ("preact", C.c_void_p), ("ld_preact", C.c_longlong),
+        ("num_sms", C.c_int),
+    ]
+
+
+def lib_path() -> Path:
+    return _LIB_PATH
+
+
+def is_built() -> bool:
+    return _LIB_PATH.exists()
+
+
+def available() -> bool:
+    """True when the CUDA library can be used in this process."""
+    return torch.cuda.is_available() and is_built()
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            raise KernelError(
+                f"{_LIB_PATH} is missing: run `python -m torchturbo_b200.csrc.build` "
+                "(or __graft_entry__.build()) before using the CUDA ops"
+            )
+        _lib = C.CDLL(str(_LIB_PATH))
+        _lib.ttb_gemm_bf16.argtypes = [C.POINTER(_GemmArgs), C.c_void_p]
+        _lib.ttb_gemm_bf16.restype = C.c_int
+    return _lib
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what} failed with code {code}")
+
+
+def _stream() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t: torch.Tensor | None) -> C.c_void_p:
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+@lru_cache(maxsize=None)
+def num_sms(device_index: int | None = None) -> int:
+    return torch.cuda.get_device_properties(device_index if device_index is not None else torch.cuda.current_device()).multi_processor_count
+
+
+def status(reset: bool = False) -> tuple[int, int]:
+    """(first error code, number of errors) recorded by bounded in-kernel waits of the GEMM unit."""
+    buf = (C.c_uint * 4)()
+    _check(lib().ttb_gemm_status(buf, C.c_int(1 if reset else 0)), "ttb_gemm_status")
+    return int(buf[0]), int(buf[1])
+
+
+# --------------------------------------------------------------------------------------
+# GEMM
+# --------------------------------------------------------------------------------------
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    *,
+    a_mn: bool = False,
+    b_mn: bool = False,
+    out: torch.Tensor | None = None,
+    out_dtype: torch.dtype = torch.bfloat16,
+    accumulate: bool = False,
+    residual: torch.Tensor | None = None,
+    tile_group: torch.Tensor | None = None,
+    group_rows: torch.Tensor | None = None,
+    swiglu: bool = False,
+    row_scale: torch.Tensor | None = None,
+    preact: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """tcgen05 GEMM ``C = op(A) @ op(B)`` on bf16 operands with fp32 accumulation.
+
+    Memory orientation (row-major tensors):
+      * ``a_mn=False``: ``a`` is ``[M, K]``;  ``a_mn=True``: ``a`` is ``[K, M]`` (used as its transpose).
+      * ``b_mn=False``: ``b`` is ``[N, K]`` (``nn.Linear`` weight); ``b_mn=True``: ``b`` is ``[K, N]``.
+      * grouped-M (``tile_group`` given): ``b`` is ``[G, N, K]`` / ``[G, K, N]`` and 128-row tile ``i`` of
+        ``a`` multiplies ``b[tile_group[i]]`` (negative = skip the tile).
+      * grouped-K (``group_rows`` given, both operands MN-major): ``C[g] = a[r_g:r_{g+1}].T @ b[r_g:r_{g+1}]``
+        with ``group_rows`` an int32 ``[G+1]`` device tensor of 64-aligned row offsets.
+      * ``swiglu=True``: ``b`` holds ``[gate | up]`` output columns (``2F``); the result is
+        ``silu(gate) * up * row_scale`` of width ``F``; ``preact`` (``[M, 2F]``) optionally keeps gate|up.
+    """
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert a.stride(-1) == 1 and b.stride(-1) == 1
+    args = _GemmArgs()
+    groups_k = 0
+    if group_rows is not None:
+        assert a_mn and b_mn and a.dim() == 2 and b.dim() == 2
+        groups_k = group_rows.numel() - 1
+        M, N, K = a.shape[1], b.shape[1], 0
+        args.total_rows = a.shape[0]
+        assert b.shape[0] == a.shape[0]
+    else:
+        if a_mn:
+            K, M = a.shape
+        else:
+            M, K = a.shape
+        bm = b if b.dim() == 2 else b[0]
+        if b_mn:
+            Kb, Nmem = bm.shape
+        else:
+            Nmem, Kb = bm.shape
+        assert Kb == K, (a.shape, b.shape, a_mn, b_mn)
+        N = Nmem // 2 if swiglu else Nmem
+    args.A, args.lda = a.data_ptr(), a.stride(0)
+    args.B = b.data_ptr()
+    args.ldb = b.stride(-2)
+    if b.dim() == 3:
+        args.b_groups, args.b_group_stride = b.shape[0], b.stride(0)
+        assert tile_group is not None
+    else:
+        args.b_groups, args.b_group_stride = 1, 0
+    if out is None:
+        shape = (groups_k, M, N) if groups_k else (M, N)
+        out = torch.empty(shape, dtype=out_dtype, device=a.device)
+        assert not accumulate
+    assert out.stride(-1) == 1 and out.dtype in (torch.bfloat16, torch.float32)
+    args.C, args.ldc = out.data_ptr(), out.stride(-2)
+    args.c_group_stride = out.stride(0) if groups_k else 0
+    args.M, args.N, args.K = M, N, K
+    args.a_mn, args.b_mn = int(a_mn), int(b_mn)
+    args.c_fp32, args.accumulate = int(out.dtype == torch.float32), int(accumulate)
+    if residual is not None:
+        assert residual.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+        args.residual, args.ldr = residual.data_ptr(), residual.stride(0)
+    if tile_group is not None:
+        assert tile_group.dtype == torch.int32
+        args.tile_group, args.m_tiles_cap = tile_group.data_ptr(), tile_group.numel()
+        assert M <= tile_group.numel() * 128
+    if group_rows is not None:
+        assert group_rows.dtype == torch.int32
+        args.group_rows, args.groups_k = group_rows.data_ptr(), groups_k
+    args.epi = 1 if swiglu else 0
+    args.F = N if swiglu else 0
+    if row_scale is not None:
+        assert row_scale.dtype == torch.float32
+        args.row_scale = row_scale.data_ptr()
+    if preact is not None:
+        assert preact.dtype == torch.bfloat16
+        args.preact, args.ld_preact = preact.data_ptr(), preact.stride(0)
+    args.num_sms = num_sms(a.device.index)
+    _check(lib().ttb_gemm_bf16(C.byref(args), _stream()), "ttb_gemm_bf16")
+    return out
+
+
+# --------------------------------------------------------------------------------------
+# RMSNorm
+# --------------------------------------------------------------------------------------
+def rmsnorm_fwd(x, weight, eps, residual=None, one_plus_w=False):
+    """Returns (y, rstd, x_sum) where x_sum is ``x + residual`` (or ``x`` itself without residual)."""
+    H = x.shape[-1]
+    x2 = x.reshape(-1, H)
+    T = x2.shape[0]
+    y = torch.empty_like(x2)
+    rstd = torch.empty(T, dtype=torch.float32, device=x.device)
+    if residual is not None:
+        r2 = residual.reshape(-1, H)
+        xsum = torch.empty_like(x2)
+    else:
+        r2, xsum = None, None
+    _check(lib().ttb_rmsnorm_fwd(_p(x2), _p(r2), _p(weight), _p(y), _p(xsum), _p(rstd), C.c_longlong(T), C.c_int(H),
+                                 C.c_float(eps), C.c_int(int(one_plus_w)), _stream()), "ttb_rmsnorm_fwd")
+    return y.view(x.shape), rstd, (xsum.view(x.shape) if xsum is not None else x)
+
+
+def rmsnorm_bwd(dy, x_sum, weight, rstd, dres=None, one_plus_w=False):
+    """Returns (dx, dw_fp32); ``dres`` (gradient arriving on the residual stream) is added into dx."""
+    H = x_sum.shape[-1]
+    x2, dy2 = x_sum.reshape(-1, H), dy.reshape(-1, H)
+    T = x2.shape[0]
+    grid = max(1, min(T, 2 * num_sms(x_sum.device.index)))
+    dx = torch.empty_like(x2)
+    partial = torch.empty(grid, H, dtype=torch.float32, device=x_sum.device)
+    dw = torch.empty(H, dtype=torch.float32, device=x_sum.device)
+    d2 = dres.reshape(-1, H) if dres is not None else None
+    _check(lib().ttb_rmsnorm_bwd(_p(dy2), _p(x2), _p(weight), _p(rstd), _p(d2), _p(dx), _p(partial), _p(dw),
+                                 C.c_longlong(T), C.c_int(H), C.c_int(int(one_plus_w)), C.c_int(grid), _stream()),
+           "ttb_rmsnorm_bwd")
+    return dx.view(x_sum.shape), dw
+
+
+# --------------------------------------------------------------------------------------
+# QK-norm + RoPE
+# --------------------------------------------------------------------------------------
+def qknorm_rope_fwd(qkv, n_q, n_kv, head_dim, wq, wk, cos, sin, eps, use_norm=True):
+    """qkv: [T, (n_q + 2 n_kv) * D] -> (q [T, n_q, D], k [T, n_kv, D], rstd [T * (n_q + n_kv)])."""
+    T = qkv.shape[0]
+    q = torch.empty(T, n_q, head_dim, dtype=qkv.dtype, device=qkv.device)
+    k = torch.empty(T, n_kv, head_dim, dtype=qkv.dtype, device=qkv.device)
+    rstd = torch.empty(T * (n_q + n_kv), dtype=torch.float32, device=qkv.device)
+    _check(lib().ttb_qknorm_rope_fwd(_p(qkv), C.c_longlong(qkv.stride(0)), C.c_int(n_q), C.c_int(n_kv),
+                                     C.c_int(head_dim), _p(wq), _p(wk), _p(cos), _p(sin), _p(q), _p(k), _p(rstd),
+                                     C.c_longlong(T), C.c_float(eps), C.c_int(int(use_norm)), _stream()),
+           "ttb_qknorm_rope_fwd")
+    return q, k, rstd
+
+
+def qknorm_rope_bwd(dq, dk, qkv, n_q, n_kv, head_dim, wq, wk, cos, sin, rstd, dqkv, use_norm=True):
+    """Writes the q and k column blocks of ``dqkv`` ([T, ld]) and returns (dwq, dwk) in fp32."""
+    T = qkv.shape[0]
+    dwq = torch.zeros(head_dim, dtype=torch.float32, device=qkv.device)
+    dwk = torch.zeros(head_dim, dtype=torch.float32, device=qkv.device)
+    grid = max(1, min((T * (n_q + n_kv) + 7) // 8, 4 * num_sms(qkv.device.index)))
+    _check(lib().ttb_qknorm_rope_bwd(_p(dq), _p(dk), _p(qkv), C.c_longlong(qkv.stride(0)), C.c_int(n_q), C.c_int(n_kv),
+                                     C.c_int(head_dim), _p(wq), _p(wk), _p(cos), _p(sin), _p(rstd), _p(dqkv),
+                                     C.c_longlong(dqkv.stride(0)), _p(dwq), _p(dwk), C.c_longlong(T),
+                                     C.c_int(int(use_norm)), C.c_int(grid), _stream()), "ttb_qknorm_rope_bwd")
+    return dwq, dwk
+
+
+# --------------------------------------------------------------------------------------
+# SwiGLU
+# --------------------------------------------------------------------------------------
+def swiglu_fwd(x, row_scale=None):
+    R, F2 = x.shape
+    F = F2 // 2
+    y = torch.empty(R, F, dtype=x.dtype, device=x.device)
+    _check(lib().ttb_swiglu_fwd(_p(x), C.c_longlong(x.stride(0)), _p(y), C.c_longlong(y.stride(0)), _p(row_scale),
+                                C.c_longlong(R), C.c_int(F), _stream()), "ttb_swiglu_fwd")
+    return y
+
+
+def swiglu_bwd(dy, x, row_scale=None, want_dscale=False):
+    R, F2 = x.shape
+    F = F2 // 2
+    dx = torch.empty_like(x)
+    dscale = torch.empty(R, dtype=torch.float32, device=x.device) if want_dscale else None
+    _check(lib().ttb_swiglu_bwd(_p(dy), C.c_longlong(dy.stride(0)), _p(x), C.c_longlong(x.stride(0)), _p(row_scale),
+                                _p(dx), C.c_longlong(dx.stride(0)), _p(dscale), C.c_longlong(R), C.c_int(F),
+                                _stream()), "ttb_swiglu_bwd")
+    return dx, dscale
+
+
+# --------------------------------------------------------------------------------------
+# Cross entropy
+# --------------------------------------------------------------------------------------
+def cross_entropy(logits, labels, *, grad_out=None, grad_scale=None, grad_scale_host=1.0, want_lse=False):
+    """Per-row CE (fp32, 0 for ignored rows).  With ``grad_out`` (bf16 [R, V]; may alias bf16 logits) also writes
+    ``(softmax - onehot) * grad_scale[0] * grad_scale_host``."""
+    R, V = logits.shape
+    assert labels.dtype == torch.int64 and labels.numel() == R
+    loss = torch.empty(R, dtype=torch.float32, device=logits.device)
+    lse = torch.empty(R, dtype=torch.float32, device=logits.device) if want_lse else None
+    _check(lib().ttb_cross_entropy(_p(logits), C.c_int(int(logits.dtype == torch.float32)),
+                                   C.c_longlong(logits.stride(0)), _p(labels), _p(loss), _p(lse), _p(grad_out),
+                                   C.c_longlong(grad_out.stride(0) if grad_out is not None else 0), _p(grad_scale),
+                                   C.c_float(grad_scale_host), C.c_longlong(R), C.c_int(V), _stream()),
+           "ttb_cross_entropy")
+    return (loss, lse) if want_lse else loss
+
+
+# --------------------------------------------------------------------------------------
+# Multi-tensor AdamW / grad norm
+# --------------------------------------------------------------------------------------
+ADAM_CHUNK = 65536
+
+
+class MultiTensorPlan:
+    """Device tables for the multi-tensor AdamW / squared-norm kernels.
+
+    ``meta`` rows are ``(p, g, m, v, shadow, numel, g_is_bf16)`` as int64; the chunk table maps each CUDA block to
+    ``(tensor index, chunk index)``.  Gradient pointers are refreshed every step (autograd reallocates them).
+    """
+
+    def __init__(self, params, exp_avg, exp_avg_sq, shadows=None):
+        self.params = list(params)
+        self.device = self.params[0].device
+        n = len(self.params)
+        self.host_meta = torch.zeros(n, 7, dtype=torch.int64).pin_memory()
+        chunks = []
+        for i, p in enumerate(self.params):
+            assert p.dtype == torch.float32 and p.is_contiguous()
+            self.host_meta[i, 0] = p.data_ptr()
+            self.host_meta[i, 2] = exp_avg[i].data_ptr()
+            self.host_meta[i, 3] = exp_avg_sq[i].data_ptr()
+            self.host_meta[i, 4] = shadows[i].data_ptr() if shadows is not None and shadows[i] is not None else 0
+            self.host_meta[i, 5] = p.numel()
+            for c in range((p.numel() + ADAM_CHUNK - 1) // ADAM_CHUNK):
+                chunks.append((i, c))
+        self.n_chunks = len(chunks)
+        self.chunks = torch.tensor(chunks, dtype=torch.int32, device=self.device).reshape(-1, 2)
+        self.meta = torch.empty(n, 7, dtype=torch.int64, device=self.device)
+        self.partial = torch.empty(max(self.n_chunks, 1), dtype=torch.float32, device=self.device)
+
+    def refresh_grads(self, grads):
+        for i, g in enumerate(grads):
+            assert g.is_contiguous() and g.numel() == self.host_meta[i, 5]
+            self.host_meta[i, 1] = g.data_ptr()
+            self.host_meta[i, 6] = int(g.dtype == torch.bfloat16)
+        self.meta.copy_(self.host_meta, non_blocking=True)
+
+
+def grad_sqnorm_partials(plan: MultiTensorPlan, prescale: float = 1.0) -> torch.Tensor:
+    _check(lib().ttb_grad_sqnorm(_p(plan.meta), _p(plan.chunks), C.c_int(plan.n_chunks), _p(plan.partial),
+                                 C.c_float(prescale), _stream()), "ttb_grad_sqnorm")
+    return plan.partial[: plan.n_chunks]
+
+
+def clip_coef(partials: torch.Tensor, max_norm: float, extra_sq: torch.Tensor | None = None) -> torch.Tensor:
+    """Returns a device tensor ``[sum_sq, norm, coef]`` with ``coef = min(1, max_norm / (norm + 1e-6))``."""
+    out = torch.empty(3, dtype=torch.float32, device=partials.device)
+    _check(lib().ttb_clip_coef(_p(partials), C.c_int(partials.numel()), _p(extra_sq), C.c_float(max_norm), _p(out),
+                               _stream()), "ttb_clip_coef")
+    return out
+
+
+def adamw_step(plan: MultiTensorPlan, *, lr, beta1, beta2, eps, weight_decay, step, clip=None, grad_prescale=1.0):
+    bc1 = 1.0 - beta1 ** step
+    bc2_sqrt = (1.0 - beta2 ** step) ** 0.5
+    _check(lib().ttb_adamw(_p(plan.meta), _p(plan.chunks), C.c_int(plan.n_chunks), C.c_float(lr), C.c_float(beta1),
+                           C.c_float(beta2), C.c_float(eps), C.c_float(weight_decay), C.c_float(bc1),
+                           C.c_float(bc2_sqrt), _p(clip), C.c_float(grad_prescale), _stream()), "ttb_adamw")
+
+
+# --------------------------------------------------------------------------------------
+# MoE router / permutation
+# --------------------------------------------------------------------------------------
+def router_fwd(logits, k, score_fn, *, expert_bias=None, valid_mask=None, scaling=1.0, want_stats=False,
+               want_lse=False):
+    """logits fp32 [T, E] -> dict(topk_idx int32 [T,k], topk_prob fp32 [T,k], counts int32 [E],
+    aux_counts int32 [E], score_sum fp32 [E], lse fp32 [T])."""
+    T, E = logits.shape
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    dev = logits.device
+    idx = torch.empty(T, k, dtype=torch.int32, device=dev)
+    prob = torch.empty(T, k, dtype=torch.float32, device=dev)
+    counts = torch.zeros(E, dtype=torch.int32, device=dev)
+    grid = max(1, min((T + 7) // 8, 2 * num_sms(dev.index)))
+    lse = torch.empty(T, dtype=torch.float32, device=dev) if (want_lse or want_stats) else None
+    if want_stats:
+        partial = torch.empty(grid, E, dtype=torch.float32, device=dev)
+        score_sum = torch.empty(E, dtype=torch.float32, device=dev)
+        aux_counts = torch.zeros(E, dtype=torch.int32, device=dev)
+    else:
+        partial = score_sum = aux_counts = None
+    vm = valid_mask.to(torch.uint8).contiguous() if valid_mask is not None else None
+    _check(lib().ttb_router_fwd(_p(logits), _p(expert_bias), _p(vm), _p(idx), _p(prob), _p(lse), _p(partial),
+                                _p(score_sum), _p(aux_counts), _p(counts), C.c_longlong(T), C.c_int(E), C.c_int(k),
+                                C.c_int(SCORE_FN[score_fn]), C.c_float(scaling), C.c_int(grid), _stream()),
+           "ttb_router_fwd")
+    return dict(topk_idx=idx, topk_prob=prob, counts=counts, aux_counts=aux_counts, score_sum=score_sum, lse=lse)
+
+
+def router_bwd(logits, topk_idx, topk_prob, k, score_fn, *, dprob=None, aux_grad=None, lse=None, valid_mask=None,
+               z_coef=None, scaling=1.0):
+    T, E = logits.shape
+    dlogits = torch.empty_like(logits)
+    vm = valid_mask.to(torch.uint8).contiguous() if valid_mask is not None else None
+    _check(lib().ttb_router_bwd(_p(logits), _p(topk_idx), _p(topk_prob), _p(dprob), _p(aux_grad), _p(lse), _p(vm),
+                                _p(z_coef), _p(dlogits), C.c_longlong(T), C.c_int(E), C.c_int(k),
+                                C.c_int(SCORE_FN[score_fn]), C.c_float(scaling), _stream()), "ttb_router_bwd")
+    return dlogits
+
+
+def perm_index(topk_idx: torch.Tensor, num_experts: int, m_tiles_cap: int | None = None):
+    """Padded (expert, token) permutation of the [T, k] expert ids.
+
+    Returns dict(counts [E], seg_start [E+1], tile_group [m_tiles_cap], row_of [T*k], status [1], capacity_rows).
+    All int32 device tensors; nothing is synchronised with the host.
+    """
+    idx = topk_idx.reshape(-1)
+    assert idx.dtype == torch.int32 and idx.is_contiguous()
+    N = idx.numel()
+    dev = idx.device
+    if m_tiles_cap is None:
+        m_tiles_cap = (N + SEG_ALIGN - 1) // SEG_ALIGN + num_experts
+    counts = torch.empty(num_experts, dtype=torch.int32, device=dev)
+    seg_start = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
+    tile_group = torch.empty(m_tiles_cap, dtype=torch.int32, device=dev)
+    row_of = torch.empty(N, dtype=torch.int32, device=dev)
+    st = torch.zeros(1, dtype=torch.int32, device=dev)
+    _check(lib().ttb_perm_index(_p(idx), C.c_longlong(N), C.c_int(num_experts), _p(counts), _p(seg_start),
+                                _p(tile_group), C.c_int(m_tiles_cap), _p(row_of), _p(st), _stream()),
+           "ttb_perm_index")
+    return dict(counts=counts, seg_start=seg_start, tile_group=tile_group, row_of=row_of, status=st,
+                capacity_rows=m_tiles_cap * SEG_ALIGN)
+
+
+def perm_scatter(src, row_of, k, capacity_rows, *, counts=None, seg_start=None, val=None, out=None):
+    """dst[row_of[n]] = src[n // k]; pad rows of every expert segment are zeroed.  Returns (dst, row_val)."""
+    T, H = src.shape
+    N = row_of.numel()
+    if out is None:
+        out = torch.empty(capacity_rows, H, dtype=src.dtype, device=src.device)
+    row_val = torch.empty(capacity_rows, dtype=torch.float32, device=src.device) if val is not None else None
+    E = counts.numel() if counts is not None else 0
+    _check(lib().ttb_perm_scatter(_p(src), C.c_longlong(src.stride(0)), _p(out), C.c_longlong(out.stride(0)),
+                                  _p(row_of), _p(val), _p(row_val), C.c_void_p(0), _p(counts), _p(seg_start),
+                                  C.c_int(E), C.c_longlong(N), C.c_int(k), C.c_int(H), _stream()), "ttb_perm_scatter")
+    return out, row_val
+
+
+def perm_combine(src, row_of, T, k, *, weights=None, residual=None):
+    """out[t] = sum_j weights[t, j] * src[row_of[t*k+j]] (+ residual[t])."""
+    H = src.shape[1]
+    out = torch.empty(T, H, dtype=src.dtype, device=src.device)
+    _check(lib().ttb_perm_combine(_p(src), C.c_longlong(src.stride(0)), _p(row_of), _p(weights), _p(residual),
+                                  C.c_longlong(residual.stride(0) if residual is not None else 0), _p(out),
+                                  C.c_longlong(out.stride(0)), C.c_longlong(T), C.c_int(k), C.c_int(H), _stream()),
+           "ttb_perm_combine")
+    return out
