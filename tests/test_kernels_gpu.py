@@ -279,9 +279,9 @@ def test_router(K, score_fn):
     assert torch.equal(out["counts"].long(), torch.bincount(ti.reshape(-1), minlength=E))
     dprob = torch.randn(T, k, device="cuda")
     aux_g = torch.randn(E, device="cuda")
-    zc = torch.tensor([0.01], device="cuda")
+    dlse = (0.02 * out["lse"] * valid).contiguous()
     loss = (p * dprob).sum() + ((sc * valid[:, None]) * aux_g).sum() + 0.01 * (torch.logsumexp(lg, -1)[valid] ** 2).sum()
     loss.backward()
     dl = K.router_bwd(logits, out["topk_idx"], out["topk_prob"], k, score_fn, dprob=dprob, aux_grad=aux_g,
-                      lse=out["lse"], valid_mask=valid, z_coef=zc, scaling=2.0)
+                      lse=out["lse"], valid_mask=valid, dlse=dlse, scaling=2.0)
     _close(dl, lg.grad, rtol=1e-3, atol=1e-3)

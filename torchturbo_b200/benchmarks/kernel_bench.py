@@ -1,0 +1,156 @@
+"""Device-timed microbenchmarks of the sm_100a kernels with roofline fractions.
+
+    python -m torchturbo_b200.benchmarks.kernel_bench [gemm] [grouped] [elementwise] [attention]
+
+Timing rules: 3+ warm-up launches, CUDA events on the launching stream, an L2 flush (write of a
+256 MiB buffer) between timed launches, best and median of the timed launches reported.  The
+denominators come from MEASURED_PEAKS.json at the repository root when present (cuBLAS bf16
+throughput and copy bandwidth measured on the same pool), else from the documented fallback.
+"""
+from __future__ import annotations
+
+import json
+import sys
+from pathlib import Path
+
+import torch
+
+from .. import kernels as K
+
+
+def peaks() -> dict:
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"tflops": d["bf16_tflops"], "gbs": d["hbm_gbs"], "src": "measured"}
+    return {"tflops": 1590.0, "gbs": 6650.0, "src": "fallback"}
+
+
+_flush = None
+
+
+def time_fn(fn, iters=10, warmup=3, flush=True):
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush:
+            _flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+    ts.sort()
+    return ts[0], ts[len(ts) // 2]
+
+
+def bench_gemm():
+    pk = peaks()
+    rows = []
+    shapes = [
+        (8192, 8192, 8192), (4096, 5120, 2048), (4096, 2048, 4096), (8192, 6144, 4096), (8192, 4096, 4096),
+        (8192, 24576, 4096), (8192, 4096, 12288), (4096, 151936, 2048),
+    ]
+    for M, N, Kd in shapes:
+        a = torch.randn(M, Kd, device="cuda").bfloat16()
+        b = torch.randn(N, Kd, device="cuda").bfloat16()
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        fl = 2.0 * M * N * Kd
+        t_ours, m_ours = time_fn(lambda: K.gemm(a, b, out=out))
+        t_ref, m_ref = time_fn(lambda: torch.matmul(a, b.t(), out=out))
+        rows.append(dict(op="gemm_nt", M=M, N=N, K=Kd, ours_ms=t_ours, ours_med_ms=m_ours, cublas_ms=t_ref,
+                         ours_tflops=fl / t_ours / 1e9, cublas_tflops=fl / t_ref / 1e9,
+                         frac_of_peak=fl / t_ours / 1e9 / pk["tflops"], peak_src=pk["src"]))
+        print(json.dumps(rows[-1]), flush=True)
+    # backward orientations on one shape
+    M, N, Kd = 8192, 4096, 4096
+    a = torch.randn(M, Kd, device="cuda").bfloat16()
+    bkn = torch.randn(Kd, N, device="cuda").bfloat16()
+    akm = torch.randn(Kd, M, device="cuda").bfloat16()
+    fl = 2.0 * M * N * Kd
+    for name, fn, ref in [
+        ("gemm_nn", lambda: K.gemm(a, bkn, b_mn=True), lambda: a @ bkn),
+        ("gemm_tn", lambda: K.gemm(akm, bkn, a_mn=True, b_mn=True), lambda: akm.t() @ bkn),
+    ]:
+        t_ours, _ = time_fn(fn)
+        t_ref, _ = time_fn(ref)
+        rows.append(dict(op=name, M=M, N=N, K=Kd, ours_ms=t_ours, cublas_ms=t_ref, ours_tflops=fl / t_ours / 1e9,
+                         cublas_tflops=fl / t_ref / 1e9, frac_of_peak=fl / t_ours / 1e9 / pk["tflops"]))
+        print(json.dumps(rows[-1]), flush=True)
+    return rows
+
+
+def bench_grouped():
+    pk = peaks()
+    rows = []
+    for E, T, k, H, F in [(16, 32768, 1, 2048, 768), (128, 4096, 8, 2048, 768)]:
+        idx = torch.stack([torch.randperm(E, device="cuda")[:k] for _ in range(T)]).to(torch.int32) if k > 1 else \
+            torch.randint(0, E, (T, 1), device="cuda", dtype=torch.int32)
+        x = torch.randn(T, H, device="cuda").bfloat16()
+        pm = K.perm_index(idx, E)
+        xp, rv = K.perm_scatter(x, pm["row_of"], k, pm["capacity_rows"], counts=pm["counts"],
+                                seg_start=pm["seg_start"], val=torch.rand(T * k, device="cuda"))
+        w1 = (torch.randn(E, H, 2 * F, device="cuda") * 0.02).bfloat16()
+        w2 = (torch.randn(E, F, H, device="cuda") * 0.02).bfloat16()
+        R = T * k
+        pre = torch.empty(pm["capacity_rows"], 2 * F, device="cuda", dtype=torch.bfloat16)
+        t1, _ = time_fn(lambda: K.gemm(xp, w1, b_mn=True, tile_group=pm["tile_group"], swiglu=True, row_scale=rv, preact=pre))
+        act = K.gemm(xp, w1, b_mn=True, tile_group=pm["tile_group"], swiglu=True, row_scale=rv)
+        t2, _ = time_fn(lambda: K.gemm(act, w2, b_mn=True, tile_group=pm["tile_group"]))
+        dy = torch.randn(pm["capacity_rows"], 2 * F, device="cuda").bfloat16()
+        t3, _ = time_fn(lambda: K.gemm(xp, dy, a_mn=True, b_mn=True, group_rows=pm["seg_start"], out_dtype=torch.float32))
+        t4, _ = time_fn(lambda: K.gemm(dy, w1, b_mn=False, tile_group=pm["tile_group"]))
+        for name, t, fl in [("fc1_swiglu", t1, 2.0 * R * H * 2 * F), ("fc2", t2, 2.0 * R * F * H),
+                            ("dW1", t3, 2.0 * R * H * 2 * F), ("dX1", t4, 2.0 * R * H * 2 * F)]:
+            rows.append(dict(op=f"grouped_{name}", E=E, rows=R, H=H, F=F, ms=t, tflops=fl / t / 1e9,
+                             frac_of_peak=fl / t / 1e9 / pk["tflops"], peak_src=pk["src"]))
+            print(json.dumps(rows[-1]), flush=True)
+    return rows
+
+
+def bench_elementwise():
+    pk = peaks()
+    rows = []
+    T, H = 32768, 4096
+    x = torch.randn(T, H, device="cuda").bfloat16()
+    w = torch.randn(H, device="cuda").bfloat16()
+    t, _ = time_fn(lambda: K.rmsnorm_fwd(x, w, 1e-6))
+    rows.append(dict(op="rmsnorm_fwd", T=T, H=H, ms=t, gbs=2 * x.numel() * 2 / t / 1e6, frac=2 * x.numel() * 2 / t / 1e6 / pk["gbs"]))
+    print(json.dumps(rows[-1]), flush=True)
+    R, V = 4096, 151936
+    lg = torch.randn(R, V, device="cuda").bfloat16()
+    lab = torch.randint(0, V, (R,), device="cuda")
+    t, _ = time_fn(lambda: K.cross_entropy(lg, lab, grad_out=lg))
+    rows.append(dict(op="cross_entropy_fwd_bwd", R=R, V=V, ms=t, gbs=2 * lg.numel() * 2 / t / 1e6, frac=2 * lg.numel() * 2 / t / 1e6 / pk["gbs"]))
+    print(json.dumps(rows[-1]), flush=True)
+    xx = torch.randn(32768, 1536, device="cuda").bfloat16()
+    t, _ = time_fn(lambda: K.swiglu_fwd(xx))
+    rows.append(dict(op="swiglu_fwd", ms=t, gbs=xx.numel() * 3 / t / 1e6, frac=xx.numel() * 3 / t / 1e6 / pk["gbs"]))
+    print(json.dumps(rows[-1]), flush=True)
+    return rows
+
+
+def main(argv):
+    which = set(argv) or {"gemm", "grouped", "elementwise"}
+    out = {}
+    if "gemm" in which:
+        out["gemm"] = bench_gemm()
+    if "grouped" in which:
+        out["grouped"] = bench_grouped()
+    if "elementwise" in which:
+        out["elementwise"] = bench_elementwise()
+    if "attention" in which:
+        from .attention_bench import bench_attention
+
+        out["attention"] = bench_attention()
+    return out
+
+
+if __name__ == "__main__":
+    main(sys.argv[1:])

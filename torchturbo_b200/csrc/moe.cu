@@ -197,9 +197,9 @@ struct RouterBwdParams {
   const float* topk_prob;  // [T, k] forward output (after scaling)
   const float* dprob;      // [T, k] or null
   const float* aux_grad;   // [E] or null: d(loss)/d(aux score of expert e), applied to valid tokens
-  const float* lse;        // [T] (needed when z_coef != 0)
+  const float* lse;        // unused (kept for ABI symmetry with the forward)
   const unsigned char* valid_mask;
-  const float* z_coef;     // device scalar or null: d(loss)/d(lse_t^2) for valid tokens
+  const float* dlse;       // [T] or null: d(loss)/d(lse_t)
   float* dlogits;          // [T, E] fp32
   long long T;
   int E, k, score_fn;
@@ -319,9 +319,9 @@ __global__ void router_bwd_kernel(const RouterBwdParams p) {
 #pragma unroll
       for (int j = 0; j < MAX_E_PER_LANE; ++j) dl[j] += sc[j] * (ds[j] - dot);
     }
-    // ---- z-loss: d(lse^2)/dl = 2 lse softmax(l)
-    if (p.z_coef && valid) {
-      const float zc = p.z_coef[0] * 2.f * lse;
+    // ---- logsumexp gradient (z-loss): d(lse)/dl = softmax(l)
+    if (p.dlse) {
+      const float zc = p.dlse[t];
 #pragma unroll
       for (int j = 0; j < MAX_E_PER_LANE; ++j)
         if (lg[j] != -INFINITY) dl[j] += zc * __expf(lg[j] - lse);
@@ -509,11 +509,11 @@ TTB_EXPORT int ttb_router_fwd(const float* logits, const float* expert_bias, con
 
 TTB_EXPORT int ttb_router_bwd(const float* logits, const int* topk_idx, const float* topk_prob, const float* dprob,
                               const float* aux_grad, const float* lse, const unsigned char* valid_mask,
-                              const float* z_coef, float* dlogits, long long T, int E, int k, int score_fn,
+                              const float* dlse, float* dlogits, long long T, int E, int k, int score_fn,
                               float scaling, void* stream) {
   if (E > 32 * MAX_E_PER_LANE || k > MAX_K || k > 32) return 901;
   if (T == 0) return 0;
-  RouterBwdParams p{logits, topk_idx, topk_prob, dprob, aux_grad, lse, valid_mask, z_coef, dlogits, T, E, k, score_fn,
+  RouterBwdParams p{logits, topk_idx, topk_prob, dprob, aux_grad, lse, valid_mask, dlse, dlogits, T, E, k, score_fn,
                     scaling};
   long long grid = (T + 7) / 8;
   if (grid > 4096) grid = 4096;

@@ -390,12 +390,14 @@ def router_fwd(logits, k, score_fn, *, expert_bias=None, valid_mask=None, scalin
 
 
 def router_bwd(logits, topk_idx, topk_prob, k, score_fn, *, dprob=None, aux_grad=None, lse=None, valid_mask=None,
-               z_coef=None, scaling=1.0):
+               dlse=None, scaling=1.0):
+    """d(logits) from the gradients of the routing weights (`dprob` [T,k]), of the per-expert score sums
+    (`aux_grad` [E], applied to valid tokens) and of the per-token logsumexp (`dlse` [T])."""
     T, E = logits.shape
     dlogits = torch.empty_like(logits)
     vm = valid_mask.to(torch.uint8).contiguous() if valid_mask is not None else None
     _check(lib().ttb_router_bwd(_p(logits), _p(topk_idx), _p(topk_prob), _p(dprob), _p(aux_grad), _p(lse), _p(vm),
-                                _p(z_coef), _p(dlogits), C.c_longlong(T), C.c_int(E), C.c_int(k),
+                                _p(dlse), _p(dlogits), C.c_longlong(T), C.c_int(E), C.c_int(k),
                                 C.c_int(SCORE_FN[score_fn]), C.c_float(scaling), _stream()), "ttb_router_bwd")
     return dlogits
 

@@ -1,0 +1,73 @@
+"""Minimal model configuration objects compatible with Hugging Face `config.json` files.
+
+The engine does not depend on `transformers`: a config is a plain attribute bag with the familiar key
+names, `from_pretrained` reads `config.json`, and a `transformers.PretrainedConfig` is accepted anywhere
+because only attribute access is used.
+"""
+from __future__ import annotations
+
+import copy
+import json
+import os
+from typing import Any
+
+
+class ModelConfig:
+    model_type: str = ""
+    _defaults: dict[str, Any] = {}
+
+    def __init__(self, **kwargs: Any) -> None:
+        merged = {}
+        for klass in reversed(type(self).__mro__):
+            merged.update(getattr(klass, "_defaults", {}) or {})
+        merged.update(kwargs)
+        merged.pop("model_type", None)
+        for k, v in merged.items():
+            setattr(self, k, v)
+        if getattr(self, "head_dim", None) is None and hasattr(self, "hidden_size") and hasattr(self, "num_attention_heads"):
+            self.head_dim = self.hidden_size // self.num_attention_heads
+
+    # -- io ---------------------------------------------------------------------------------------
+    @classmethod
+    def from_dict(cls, d: dict[str, Any]) -> "ModelConfig":
+        return cls(**d)
+
+    @classmethod
+    def from_pretrained(cls, path: str) -> "ModelConfig":
+        with open(os.path.join(path, "config.json")) as f:
+            return cls.from_dict(json.load(f))
+
+    def to_dict(self) -> dict[str, Any]:
+        out = {"model_type": self.model_type}
+        for k, v in vars(self).items():
+            if k.startswith("_"):
+                continue
+            if isinstance(v, ModelConfig):
+                v = v.to_dict()
+            elif hasattr(v, "is_floating_point") or str(type(v)).startswith("<class 'torch."):
+                v = str(v).replace("torch.", "")
+            out[k] = copy.deepcopy(v)
+        return out
+
+    def save_pretrained(self, path: str) -> None:
+        os.makedirs(path, exist_ok=True)
+        with open(os.path.join(path, "config.json"), "w") as f:
+            json.dump(self.to_dict(), f, indent=2, sort_keys=True)
+
+    def __repr__(self) -> str:
+        return f"{type(self).__name__}({self.to_dict()})"
+
+
+def load_config(path_or_dict) -> ModelConfig:
+    """Build the registered config class for a checkpoint directory, a dict, or pass an object through."""
+    from .registry import get_model
+
+    if isinstance(path_or_dict, (str, os.PathLike)):
+        with open(os.path.join(path_or_dict, "config.json")) as f:
+            d = json.load(f)
+    elif isinstance(path_or_dict, dict):
+        d = dict(path_or_dict)
+    else:
+        return path_or_dict
+    cls = get_model(d["model_type"])
+    return cls.config_class.from_dict(d)
