@@ -1,0 +1,230 @@
+"""Headline benchmark: SFT tokens/s of a Qwen3-30B-A3B-shaped MoE (FSDP2 + EP) on N B200 GPUs of one node.
+
+    python bench.py --gpus 1 --steps 8 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29500 \
+        bench.py --gpus 8 --steps 8 --warmup 3
+    python bench.py --impl reference ...      # same metric through the unmodified reference (baseline/_ref)
+
+Prints ONE JSON line on rank 0.  `value` is the device-timed aggregate tokens/s over K steps (CUDA events, barrier
+and synchronize on both sides, max over ranks); `e2e` repeats the measurement through the public engine API with the
+per-step host-to-device copy of the batch from pinned memory and the device-to-host read of the loss inside the timed
+region.  Synthetic data (seeded random token ids, documents of 256..4096 tokens packed to 4096 per rank), random-init
+weights, bf16 compute with fp32 master weights and optimizer state, AdamW, global-norm clipping, aux loss 1e-3.
+
+Depth: the named model has 48 layers; its fp32 master + AdamW state (16 bytes per parameter) only fits when the
+experts are spread over 4 or more GPUs, so `layers = min(48, 12 * N)`; the depth used is reported in `config`.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+METRIC = "SFT tokens/s, Qwen3-30B-A3B FSDP2+EP, aggregate over N B200 (device-timed, max over ranks)"
+
+
+def parse():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=8)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--layers", type=int, default=0, help="0 = min(48, 12 * gpus)")
+    p.add_argument("--seq-len", type=int, default=4096)
+    p.add_argument("--model", default="qwen3_moe_30b_a3b", choices=["qwen3_moe_30b_a3b", "qwen3_8b", "tiny_moe"])
+    p.add_argument("--no-e2e", action="store_true")
+    return p.parse_args()
+
+
+def model_config(name: str, layers: int) -> dict:
+    if name == "qwen3_moe_30b_a3b":
+        return dict(model_type="qwen3_moe", vocab_size=151936, hidden_size=2048, intermediate_size=6144,
+                    num_hidden_layers=layers, num_attention_heads=32, num_key_value_heads=4, head_dim=128,
+                    num_experts=128, num_experts_per_tok=8, moe_intermediate_size=768, norm_topk_prob=True,
+                    rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False, router_aux_loss_coef=1e-3)
+    if name == "qwen3_8b":
+        return dict(model_type="qwen3", vocab_size=151936, hidden_size=4096, intermediate_size=12288,
+                    num_hidden_layers=layers, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                    rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False)
+    return dict(model_type="qwen3_moe", vocab_size=32000, hidden_size=512, intermediate_size=1024,
+                num_hidden_layers=layers, num_attention_heads=8, num_key_value_heads=2, head_dim=128, num_experts=16,
+                num_experts_per_tok=4, moe_intermediate_size=256, norm_topk_prob=True)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of this rank's GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.path = index, None, f"/tmp/ttb_clocks_{os.getpid()}.csv"
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                parts = [x.strip() for x in line.split(",")]
+                if len(parts) < 7:
+                    continue
+                try:
+                    sm.append(float(parts[0]))
+                    mx = float(parts[1])
+                except ValueError:
+                    continue
+                for n, v in zip(names, parts[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def run_ours(args) -> dict:
+    import torch
+    import torch.distributed as dist
+
+    from torchturbo_b200 import kernels
+    from torchturbo_b200.data import PackedCollator, SyntheticPackedDataset
+    from torchturbo_b200.engine import EngineConfig, TorchTurboEngine
+    from torchturbo_b200.engine.optimizers import OptimizerClassPlan
+    from torchturbo_b200.loops import train_step
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    layers = args.layers or min(48, 12 * world)
+    is_moe = args.model != "qwen3_8b"
+    cfg = EngineConfig.from_dict({
+        "mixed_precision": "bf16",
+        "parallel_plan": {"sp_size": 1, "ep_size": world if is_moe else 1},
+        "moe": {"aux_loss_coeff": 1e-3},
+        "activation_checkpointing": {"enabled": not is_moe},
+    })
+    engine = TorchTurboEngine(cfg)
+    mc = model_config(args.model, layers)
+    model = engine.build_model(None, load_weights=False, init_kwargs={"config": mc, "seed": 0})
+    optim = engine.prepare_optimizer(model, OptimizerClassPlan(torch.optim.AdamW, lr=1e-5, weight_decay=0.01,
+                                                               betas=(0.9, 0.95)))
+    n_batches = args.warmup + 2 * args.steps
+    ds = SyntheticPackedDataset(n_batches * world, args.seq_len, mc["vocab_size"], min_doc=256, max_doc=args.seq_len,
+                                seed=1234)
+    coll = PackedCollator(pin=True)
+    host = [coll([ds[rank * n_batches + i]]) for i in range(n_batches)]
+    dev = torch.device("cuda", local_rank)
+
+    def to_device(b):
+        return {k: (v.to(dev, non_blocking=True) if isinstance(v, torch.Tensor) and not k.startswith("cu_seq") else v)
+                for k, v in b.items()}
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    model.train()
+    # ---- warm-up
+    for i in range(args.warmup):
+        train_step(engine, model, optim, [to_device(host[i])], check_finite=False)
+    # ---- device-timed region: inputs staged on the device beforehand
+    staged = [to_device(host[args.warmup + i]) for i in range(args.steps)]
+    sampler = ClockSampler(local_rank)
+    sync()
+    sampler.start()
+    launches0 = kernels.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    last = None
+    for b in staged:
+        last, _ = train_step(engine, model, optim, [b], check_finite=False)
+    e1.record()
+    sync()
+    launches = kernels.launch_count() - launches0
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1)
+    t = torch.tensor([ms], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_dev = float(t.item())
+    tokens_per_step = args.seq_len * world
+    value = tokens_per_step * args.steps / (ms_dev / 1e3)
+    # ---- end-to-end region: public API, H2D of every batch from pinned memory, D2H of every loss
+    e2e = None
+    if not args.no_e2e:
+        h2d = sum(v.numel() * v.element_size() for k, v in host[0].items()
+                  if isinstance(v, torch.Tensor) and not k.startswith("cu_seq"))
+        losses = []
+        sync()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        for i in range(args.steps):
+            b = to_device(host[args.warmup + args.steps + i])
+            loss, _ = train_step(engine, model, optim, [b], check_finite=False)
+            losses.append(float(loss.cpu()))        # device -> host read of the step's result
+        f1.record()
+        sync()
+        t2 = torch.tensor([f0.elapsed_time(f1)], device=dev)
+        if world > 1:
+            dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+        e2e = {"value": tokens_per_step * args.steps / (float(t2.item()) / 1e3), "unit": "tokens/s",
+               "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4, "ms_per_step": float(t2.item()) / args.steps,
+               "final_loss": losses[-1]}
+    st = kernels.status()
+    out = {
+        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (seeded random token ids, random-init weights)", "impl": "ours",
+        "config": {"model": "Qwen3-30B-A3B" if args.model == "qwen3_moe_30b_a3b" else args.model, "layers": layers,
+                   "layers_named": 48, "global_batch": world, "seq_len": args.seq_len,
+                   "parallelism": f"fsdp2 dp{world} + ep{world if is_moe else 1}", "optimizer": "AdamW fp32 master",
+                   "l2": "per-step working set (weights, optimizer state, activations: tens of GB) is far larger than the 126 MB L2"},
+        "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "loss": float(last),
+        "kernel_status": list(st), "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30,
+    }
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return out if rank == 0 else {}
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        from baseline.run_reference import run_reference
+
+        out = run_reference(args)
+    else:
+        out = run_ours(args)
+    if out:
+        print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()

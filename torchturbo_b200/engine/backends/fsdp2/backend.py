@@ -1,0 +1,579 @@
+"""FSDP2 backend: data-parallel sharding (ZeRO-3 style) + expert-parallel mesh + Ulysses SP groups.
+
+What it does, in the order `prepare_model` runs (phases as in engine/backends/fsdp2/backend.py:438-540 of
+the reference):
+  1. meshes and groups: 1-D world mesh `("dp",)`, 2-D mesh `(W/ep, ep)` named `("edp", "ep")`, SP groups of
+     consecutive ranks and DP groups of strided ranks;
+  2. module replacement from the plan (`replace_module`), PEFT, SP input-slicing patch;
+  3. activation checkpointing per planned module;
+  4. sharding: explicit plan units, every `ModuleList` child, the input-embedding unit, a resident tail unit
+     (final norm + output embedding) and the root.
+
+B200-first difference: a unit whose mesh has a single rank (everything on one GPU; experts when `ep` equals
+the world size) is *not* wrapped by `fully_shard`.  Such a unit keeps bf16 parameters whose fp32 master copy
+lives in the optimizer (the fused AdamW kernel writes both), which removes the per-step all-gather /
+cast / reduce-scatter copies that a one-rank FSDP unit would still perform.  Units with more than one rank
+use `torch.distributed.fsdp.fully_shard` with bf16 parameters, fp32 reduction and fp32 sharded masters.
+"""
+from __future__ import annotations
+
+import contextlib
+import functools
+from typing import Any
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ....logging import get_logger
+from ....models.modules.attention.ulysses import patch_forward_for_sp_input_slicing, ulysses_pad_inputs
+from ....models.modules.loss import chunk_loss, logits_loss, prepare_loss_labels
+from ....models.modules.moe import BaseMoELayer, MoEAuxLossAutoScaler
+from ....parallel import FSDPParallelPlan, FSDPPlanSpec
+from ....utils.fqn import match_fqn
+from ...backend_registry import register_backend
+from ...config import CPUOffloadMode, EngineConfig, MixedPrecisionPolicy
+from ...distributed import assert_finite, init_process_group_if_needed
+from ..base import BaseBackend
+
+logger = get_logger(__name__)
+
+_RECOMPUTE = {"active": False}
+
+
+def in_recompute() -> bool:
+    """True while activation checkpointing replays a forward pass (statistics must not be counted twice)."""
+    return _RECOMPUTE["active"]
+
+
+@contextlib.contextmanager
+def _recompute_ctx():
+    prev = _RECOMPUTE["active"]
+    _RECOMPUTE["active"] = True
+    try:
+        yield
+    finally:
+        _RECOMPUTE["active"] = prev
+
+
+@register_backend("fsdp2")
+class FSDP2Backend(BaseBackend):
+    def __init__(self, config: EngineConfig, runtime) -> None:
+        super().__init__(config, runtime)
+        self.fsdp_config = config.backend_config
+        offload = self.fsdp_config.cpu_offload
+        init_process_group_if_needed(runtime, with_cpu_backend=bool(offload.enabled))
+        self.rank, self.world_size = dist.get_rank(), dist.get_world_size()
+        self.device = runtime.device
+        self.world_mesh = None
+        self.ep_mesh = None
+        self.sp_size = self.ep_size = 1
+        self.sp_group = self.dp_group = self.ep_group = self.edp_group = None
+        self.sp_rank = 0
+        self.dp_rank, self.dp_size = self.rank, self.world_size
+        self.gradient_scaling_factor = 1.0
+        self.local_units: list[nn.Module] = []
+        self.fsdp_units: list[nn.Module] = []
+        self.no_shard_params: list[nn.Parameter] = []
+        self.expert_param_ids: set[int] = set()
+        self._plan: FSDPParallelPlan | None = None
+
+    # ------------------------------------------------------------------------------------------
+    # meshes and groups
+    # ------------------------------------------------------------------------------------------
+    def _init_mesh(self, plan: FSDPParallelPlan) -> None:
+        from torch.distributed.device_mesh import init_device_mesh
+
+        W = self.world_size
+        self.sp_size, self.ep_size = int(plan.sp_size or 1), int(plan.ep_size or 1)
+        if W % self.sp_size or W % self.ep_size:
+            raise ValueError(f"world size {W} must be divisible by sp_size={self.sp_size} and ep_size={self.ep_size}")
+        dev = self.runtime.turbo_device.value
+        self.world_mesh = init_device_mesh(dev, (W,), mesh_dim_names=("dp",))
+        self.ep_mesh = init_device_mesh(dev, (W // self.ep_size, self.ep_size), mesh_dim_names=("edp", "ep"))
+        self.ep_group = self.ep_mesh.get_group("ep")
+        self.edp_group = self.ep_mesh.get_group("edp")
+        self.ep_rank = dist.get_rank(self.ep_group)
+        self._create_sp_group()
+        self._create_dp_group()
+
+    def _create_sp_group(self) -> None:
+        """SP groups are runs of `sp_size` consecutive ranks."""
+        self.sp_group, self.sp_rank = None, 0
+        if self.sp_size <= 1:
+            return
+        for start in range(0, self.world_size, self.sp_size):
+            ranks = list(range(start, start + self.sp_size))
+            g = dist.new_group(ranks)
+            if self.rank in ranks:
+                self.sp_group, self.sp_rank = g, self.rank - start
+
+    def _create_dp_group(self) -> None:
+        """DP groups take every `sp_size`-th rank: ranks with the same position inside their SP group."""
+        self.dp_size = self.world_size // self.sp_size
+        self.dp_rank = self.rank // self.sp_size
+        self.dp_group = None
+        if self.sp_size <= 1:
+            self.dp_group = dist.group.WORLD
+            return
+        for off in range(self.sp_size):
+            ranks = list(range(off, self.world_size, self.sp_size))
+            g = dist.new_group(ranks)
+            if self.rank in ranks:
+                self.dp_group = g
+
+    def get_dp_info(self) -> dict[str, Any]:
+        return {"dp_group": self.dp_group, "dp_size": self.dp_size, "dp_rank": self.dp_rank}
+
+    def get_ep_info(self) -> dict[str, Any]:
+        return {"ep_group": self.ep_group, "ep_size": self.ep_size, "ep_rank": getattr(self, "ep_rank", 0),
+                "edp_group": self.edp_group, "ep_mesh": self.ep_mesh}
+
+    def get_sp_info(self) -> dict[str, Any]:
+        return {"sp_group": self.sp_group, "sp_size": self.sp_size, "sp_rank": self.sp_rank}
+
+    # ------------------------------------------------------------------------------------------
+    # prepare_model
+    # ------------------------------------------------------------------------------------------
+    def prepare_model(self, model: nn.Module, parallel_plan: FSDPParallelPlan, peft_config: Any = None) -> nn.Module:
+        self._plan = parallel_plan
+        self._init_mesh(parallel_plan)
+        self._replace_modules(model, parallel_plan)
+        if peft_config is not None:
+            from ...peft import apply_peft
+
+            model = apply_peft(model, peft_config)
+        if hasattr(model, "get_sequence_parallel_input_slicing_spec"):
+            patch_forward_for_sp_input_slicing(model.get_sequence_parallel_input_slicing_spec(), self.sp_group,
+                                               self.sp_size, self.sp_rank)
+        compiled = self._compile_parallel_plan(model, parallel_plan)
+        self._apply_activation_checkpointing(model, compiled)
+        self._shard_model(model, compiled)
+        self._setup_prefetch(model)
+        self._register_vision_balance(model, compiled)
+        self.gradient_scaling_factor = 1.0 / self.ep_size
+        return model
+
+    def _replace_modules(self, model: nn.Module, plan: FSDPParallelPlan) -> None:
+        """`spec.replace_module(original, hf_config=..., sp_info=..., ep_info=..., engine_config=..., **kwargs)`
+        for every module whose FQN matches a plan entry carrying a replacement."""
+        targets = []
+        for fqn, mod in model.named_modules():
+            for pattern, spec in plan.plan.items():
+                if spec.replace_module is not None and match_fqn(pattern, fqn):
+                    targets.append((fqn, mod, spec))
+                    break
+        for fqn, mod, spec in targets:
+            parent_name, _, child = fqn.rpartition(".")
+            parent = model.get_submodule(parent_name) if parent_name else model
+            dev = next((p.device for p in mod.parameters()), torch.device("cpu"))
+            with torch.device(dev):
+                new = spec.replace_module(mod, hf_config=model.config, sp_info=self.get_sp_info(),
+                                          ep_info=self.get_ep_info(), engine_config=self.config,
+                                          **(spec.module_kwargs or {}))
+            setattr(parent, child, new)
+
+    def _compile_parallel_plan(self, model: nn.Module, plan: FSDPParallelPlan) -> dict[str, FSDPPlanSpec]:
+        """module FQN -> first matching spec (patterns are written against the model's own names)."""
+        compiled: dict[str, FSDPPlanSpec] = {}
+        for fqn, _ in model.named_modules():
+            spec = plan.match(fqn)
+            if spec is not None:
+                compiled[fqn] = spec
+        return compiled
+
+    # ------------------------------------------------------------------------------------------
+    # activation checkpointing
+    # ------------------------------------------------------------------------------------------
+    def _apply_activation_checkpointing(self, model: nn.Module, compiled: dict[str, FSDPPlanSpec]) -> None:
+        ac = self.config.activation_checkpointing
+        if not ac.enabled:
+            return
+        from torch.utils.checkpoint import checkpoint
+
+        n = 0
+        for fqn, spec in compiled.items():
+            if not spec.activation_checkpoint:
+                continue
+            mod = model.get_submodule(fqn)
+            if getattr(mod, "_tt_ac_wrapped", False):
+                continue
+            orig = mod.forward
+
+            def ac_forward(*args, __orig=orig, **kwargs):
+                if not torch.is_grad_enabled():
+                    return __orig(*args, **kwargs)
+                if ac.use_reentrant:
+                    return checkpoint(__orig, *args, use_reentrant=True, **kwargs)
+                return checkpoint(__orig, *args, use_reentrant=False,
+                                  context_fn=lambda: (contextlib.nullcontext(), _recompute_ctx()), **kwargs)
+
+            mod.forward = ac_forward
+            mod._tt_ac_wrapped = True
+            n += 1
+        logger.info_rank0("activation checkpointing on %d module(s)", n)
+
+    # ------------------------------------------------------------------------------------------
+    # sharding
+    # ------------------------------------------------------------------------------------------
+    def _mesh_for(self, spec: FSDPPlanSpec | None):
+        if spec is not None and spec.placement is not None and spec.placement.mesh_dim in ("edp", 0):
+            return self.ep_mesh["edp"], True
+        return self.world_mesh, False
+
+    def _fsdp_kwargs(self, mesh, *, is_expert: bool, reshard: bool | None = None) -> dict[str, Any]:
+        from torch.distributed.fsdp import CPUOffloadPolicy, MixedPrecisionPolicy as MP
+
+        kw: dict[str, Any] = {"mesh": mesh}
+        if self.config.mixed_precision is MixedPrecisionPolicy.BF16:
+            kw["mp_policy"] = MP(param_dtype=torch.bfloat16, reduce_dtype=torch.float32,
+                                 cast_forward_inputs=not is_expert)
+        kw["reshard_after_forward"] = self.fsdp_config.reshard_after_forward if reshard is None else reshard
+        off = self.fsdp_config.cpu_offload
+        if off.enabled and off.mode is CPUOffloadMode.FULL:
+            kw["offload_policy"] = CPUOffloadPolicy(pin_memory=True)
+        return kw
+
+    def _make_unit(self, module: nn.Module, spec: FSDPPlanSpec | None, *, reshard: bool | None = None) -> None:
+        if getattr(module, "_tt_unit", None) is not None:
+            return
+        mesh, is_expert = self._mesh_for(spec)
+        own = [p for p in module.parameters()]
+        if is_expert:
+            self.expert_param_ids.update(id(p) for p in own)
+        if mesh.size() > 1:
+            from torch.distributed.fsdp import fully_shard
+
+            skip = {id(q) for q in self.no_shard_params}
+            for sub in module.modules():
+                if sub is not module and getattr(sub, "_tt_unit", None) == "local":
+                    skip.update(id(q) for q in sub.parameters())
+            ignored = {p for p in own if id(p) in skip}
+            kw = self._fsdp_kwargs(mesh, is_expert=is_expert, reshard=reshard)
+            if ignored:
+                kw["ignored_params"] = ignored
+            fully_shard(module, **kw)
+            module._tt_unit = "fsdp"
+            self.fsdp_units.append(module)
+        else:
+            module._tt_unit = "local"
+            self.local_units.append(module)
+
+    def _collect_no_shard(self, model: nn.Module, compiled: dict[str, FSDPPlanSpec]) -> None:
+        """`no_shard` entries may name modules or single parameters; their parameters stay replicated and
+        get a world-average all-reduce on the gradient."""
+        ids: set[int] = set()
+        plan = self._plan
+        for fqn, spec in compiled.items():
+            if spec.no_shard:
+                for p in model.get_submodule(fqn).parameters():
+                    ids.add(id(p))
+        for name, p in model.named_parameters():
+            spec = plan.match(name) if plan is not None else None
+            if spec is not None and spec.no_shard:
+                ids.add(id(p))
+        self.no_shard_params = [p for p in model.parameters() if id(p) in ids]
+
+    def _shard_model(self, model: nn.Module, compiled: dict[str, FSDPPlanSpec]) -> None:
+        self._collect_no_shard(model, compiled)
+        # 1. explicit units, deepest first so children are wrapped before their parents
+        explicit = [(fqn, spec) for fqn, spec in compiled.items()
+                    if spec.placement is not None or spec.standalone_world_shard]
+        for fqn, spec in sorted(explicit, key=lambda kv: -kv[0].count(".")):
+            self._make_unit(model.get_submodule(fqn), spec)
+        # 2. every ModuleList child is a unit
+        for _, mod in list(model.named_modules()):
+            if isinstance(mod, nn.ModuleList):
+                for child in mod:
+                    if any(True for _ in child.parameters()):
+                        self._make_unit(child, None)
+        # 3. input embeddings, resident tail (final norm + output embedding), root
+        emb = model.get_input_embeddings() if hasattr(model, "get_input_embeddings") else None
+        head = model.get_output_embeddings() if hasattr(model, "get_output_embeddings") else None
+        tied = emb is not None and head is not None and getattr(head, "weight", None) is getattr(emb, "weight", object())
+        if emb is not None and not tied:
+            self._make_unit(emb, None)
+        if head is not None and not tied:
+            self._make_unit(head, None, reshard=False)
+        self._make_unit(model, None, reshard=False)
+        n_fsdp, n_local = len(self.fsdp_units), len(self.local_units)
+        logger.info_rank0("sharding: %d FSDP unit(s), %d single-rank unit(s), %d replicated parameter(s)", n_fsdp,
+                          n_local, len(self.no_shard_params))
+
+    def _setup_prefetch(self, model: nn.Module) -> None:
+        if not self.fsdp_units:
+            return
+        from .prefetch import FSDPPrefetchManager
+
+        self.prefetch_manager = FSDPPrefetchManager(self.fsdp_config)
+        self.prefetch_manager.setup(model)
+
+    def _register_vision_balance(self, model: nn.Module, compiled: dict[str, FSDPPlanSpec]) -> None:
+        for fqn, spec in compiled.items():
+            vb = spec.vision_balance
+            if vb is not None and vb.mode is not None:
+                from ....models.modules.vision import register_vision_balance
+
+                register_vision_balance(model.get_submodule(fqn), vb, sp_group=self.sp_group, sp_size=self.sp_size,
+                                        sp_rank=self.sp_rank, world_group=dist.group.WORLD)
+
+    # ------------------------------------------------------------------------------------------
+    # materialisation
+    # ------------------------------------------------------------------------------------------
+    def _unit_owned_params(self, model: nn.Module) -> dict[int, str]:
+        """param id -> kind ('fsdp' | 'local') of the deepest unit that contains it."""
+        owner: dict[int, str] = {}
+
+        def walk(mod: nn.Module, kind: str | None):
+            kind = getattr(mod, "_tt_unit", None) or kind
+            for p in mod.parameters(recurse=False):
+                if kind is not None:
+                    owner[id(p)] = kind
+            for c in mod.children():
+                walk(c, kind)
+
+        walk(model, None)
+        for p in self.no_shard_params:
+            owner[id(p)] = "replicated"
+        return owner
+
+    def materialize(self, model: nn.Module, *, init_weights: bool = True) -> None:
+        """Allocate real storage for a meta-device model on this rank's device and (optionally) initialise it
+        with the model's own initialiser, seeded identically on every rank and then sharded."""
+        has_meta = any(p.is_meta for p in model.parameters()) or any(b.is_meta for b in model.buffers())
+        if has_meta:
+            model.to_empty(device=self.device)
+        elif next(model.parameters()).device != self.device:
+            model.to(self.device)
+        if init_weights and has_meta:
+            self._init_parameters(model)
+
+    def _init_parameters(self, model: nn.Module) -> None:
+        std = float(getattr(getattr(model, "config", None), "initializer_range", 0.02))
+        with torch.no_grad():
+            for name, p in model.named_parameters():
+                lp = p._local_tensor if hasattr(p, "_local_tensor") else p
+                if lp.ndim <= 1:
+                    if name.endswith("bias") or "expert_bias" in name:
+                        lp.zero_()
+                    else:
+                        lp.fill_(1.0)
+                else:
+                    lp.normal_(0.0, std)
+            for name, b in model.named_buffers():
+                if b.dtype.is_floating_point and "inv_freq" not in name:
+                    b.zero_()
+
+    def finalize_model_load(self, model: nn.Module) -> None:
+        """After weights are in place: single-rank units switch to bf16 parameters (their fp32 values become
+        the optimizer's master copy), replicated parameters get their gradient all-reduce hook."""
+        if self.config.mixed_precision is MixedPrecisionPolicy.BF16:
+            owner = self._unit_owned_params(model)
+            with torch.no_grad():
+                for name, p in model.named_parameters():
+                    if owner.get(id(p)) in ("local", "replicated") and p.dtype == torch.float32:
+                        master = p.data
+                        p.data = master.to(torch.bfloat16)
+                        if p.requires_grad:
+                            p._master_init = master
+        self._register_no_shard_grad_sync()
+
+    def _register_no_shard_grad_sync(self) -> None:
+        if self.world_size == 1:
+            return
+        W = self.world_size
+
+        def hook(p):
+            if p.grad is not None:
+                dist.all_reduce(p.grad, op=dist.ReduceOp.SUM)
+                p.grad.div_(W)
+
+        for p in self.no_shard_params:
+            if p.requires_grad and not getattr(p, "_tt_sync_hook", False):
+                p.register_post_accumulate_grad_hook(hook)
+                p._tt_sync_hook = True
+
+    def create_checkpoint_manager(self):
+        from .checkpoint import FSDP2CheckpointManager
+
+        return FSDP2CheckpointManager(self)
+
+    # ------------------------------------------------------------------------------------------
+    # optimizer
+    # ------------------------------------------------------------------------------------------
+    def _topology_of(self, p: torch.Tensor) -> str:
+        if id(p) in self.expert_param_ids:
+            return "moe"
+        if hasattr(p, "_local_tensor"):
+            return "dense"
+        return "local"
+
+    def prepare_optimizer(self, model: nn.Module, optimizer_plan) -> torch.optim.Optimizer:
+        """Build one optimizer per (class, sharding topology): fused/foreach optimizers cannot mix DTensor
+        meshes, and the expert group needs its own gradient scale when clipping."""
+        from ...optimizers import FusedAdamW, OptimizersContainer
+        from ...optimizers.plan import OptimizerClassPlan, OptimizerPlan
+
+        if isinstance(optimizer_plan, OptimizerClassPlan):
+            optimizer_plan = optimizer_plan.resolve(model.named_parameters())
+        assert isinstance(optimizer_plan, OptimizerPlan)
+        optimizer_plan.validate(model)
+        buckets: dict[tuple, list[dict]] = {}
+        for g in optimizer_plan.groups:
+            by_topo: dict[str, list] = {}
+            for p in g.params:
+                by_topo.setdefault(self._topology_of(p), []).append(p)
+            for topo, ps in by_topo.items():
+                buckets.setdefault((g.optimizer_cls, topo), []).append({"params": ps, **g.hyperparameters})
+        opts, names = [], []
+        for (cls, topo), groups in buckets.items():
+            if cls in (torch.optim.AdamW, "adamw") and self.runtime.turbo_device.value == "cuda":
+                cls = FusedAdamW
+            elif cls == "adamw":
+                cls = FusedAdamW
+            opt = cls(groups)
+            opt._tt_topology = topo
+            opts.append(opt)
+            names.append(f"{getattr(cls, '__name__', str(cls)).lower()}_{topo}")
+        for o in opts:
+            for grp in o.param_groups:
+                for p in grp["params"]:
+                    init = getattr(p, "_master_init", None)
+                    if init is not None and isinstance(o, FusedAdamW):
+                        st = o._init_state(p)
+                        st["master"] = init
+                        del p._master_init
+        return opts[0] if len(opts) == 1 else OptimizersContainer(opts, names)
+
+    # ------------------------------------------------------------------------------------------
+    # gradient clipping
+    # ------------------------------------------------------------------------------------------
+    def _scale_moe_gradient(self, model: nn.Module) -> None:
+        """Expert gradients are sums over the tokens of all `ep` ranks; dividing by `ep` puts them on the same
+        per-rank-average footing as the FSDP-averaged dense gradients."""
+        if self.ep_size == 1:
+            return
+        with torch.no_grad():
+            for p in model.parameters():
+                if id(p) in self.expert_param_ids and p.grad is not None and not getattr(p, "_tt_grad_scaled", False):
+                    p.grad.mul_(self.gradient_scaling_factor)
+                    p._tt_grad_scaled = True
+
+    @torch.no_grad()
+    def clip_grad_norm_(self, model: nn.Module, max_norm: float, optimizer=None) -> torch.Tensor:
+        """Global L2 norm over dense (world-sharded), expert (edp-sharded, unique per EP rank) and replicated /
+        single-rank parameters; every gradient is then scaled by `min(1, max_norm / (norm + 1e-6))`.
+        With the fused AdamW the coefficient is handed to the optimizer as a device scalar and applied inside
+        the update kernel instead of in a separate pass."""
+        self._scale_moe_gradient(model)
+        sq = {"dense": [], "moe": [], "local": []}
+        for p in model.parameters():
+            g = getattr(p, "main_grad", None)
+            g = g if g is not None else p.grad
+            if g is None:
+                continue
+            lg = g._local_tensor if hasattr(g, "_local_tensor") else g
+            sq[self._topology_of(p)].append(lg)
+        dev = self.device
+
+        def sumsq(ts):
+            if not ts:
+                return torch.zeros((), dtype=torch.float32, device=dev)
+            norms = torch._foreach_norm(ts, 2.0)
+            return torch.stack([n.float() for n in norms]).pow(2).sum()
+
+        dense, moe, local = sumsq(sq["dense"]), sumsq(sq["moe"]), sumsq(sq["local"])
+        sharded = dense + moe
+        if self.world_size > 1:
+            # FSDP shards and EP-local experts are disjoint across the world; replicated ones are not summed
+            dist.all_reduce(sharded)
+        total = (sharded + local).sqrt()
+        coef = (max_norm / (total + 1e-6)).clamp(max=1.0) if max_norm and max_norm > 0 else torch.ones_like(total)
+        from ...optimizers import FusedAdamW, OptimizersContainer
+
+        opts = list(optimizer) if isinstance(optimizer, OptimizersContainer) else ([optimizer] if optimizer is not None else [])
+        fused_ids: set[int] = set()
+        for o in opts:
+            if isinstance(o, FusedAdamW):
+                o.set_clip_coef(coef.reshape(1))
+                fused_ids.update(id(p) for grp in o.param_groups for p in grp["params"])
+        rest = []
+        for p in model.parameters():
+            if id(p) not in fused_ids and p.grad is not None:
+                rest.append(p.grad._local_tensor if hasattr(p.grad, "_local_tensor") else p.grad)
+        if rest:
+            torch._foreach_mul_(rest, coef)
+        for p in model.parameters():
+            if getattr(p, "_tt_grad_scaled", False):
+                p._tt_grad_scaled = False
+        return total
+
+    # ------------------------------------------------------------------------------------------
+    # inputs and loss
+    # ------------------------------------------------------------------------------------------
+    def prepare_inputs(self, model: nn.Module, inputs: dict[str, Any]) -> dict[str, Any]:
+        """Right-pad the declared batch fields to a multiple of `sp_size` and move tensors to the device
+        (packed boundaries stay on the host: kernels that need them receive a device copy once per step)."""
+        if self.sp_size > 1:
+            inputs = ulysses_pad_inputs(inputs, model.get_sequence_parallel_input_slicing_spec(), self.sp_size)
+        out = {}
+        for k, v in inputs.items():
+            if isinstance(v, torch.Tensor) and k not in ("cu_seq_lens_q", "cu_seq_lens_k") and v.device != self.device:
+                v = v.to(self.device, non_blocking=True)
+            out[k] = v
+        return out
+
+    def _prepare_moe_runtime(self, model: nn.Module, inputs: dict[str, Any], aux_loss_scale: float) -> None:
+        layers = [m for m in model.modules() if isinstance(m, BaseMoELayer)]
+        if not layers:
+            return
+        rt = model.get_moe_runtime_inputs(inputs, self.get_parallel_context())
+        rt.aux_loss_scale = aux_loss_scale
+        for m in layers:
+            m.set_runtime_inputs(rt)
+
+    def compute_loss(self, model: nn.Module, inputs: dict[str, Any], *, num_items_in_batch=None,
+                     aux_loss_scale: float = 1.0, return_outputs: bool = False):
+        """Forward + language-model loss for one packed micro-batch.  Labels are shifted inside the engine
+        (the batch carries unshifted labels); under SP every rank computes the loss of its shard with a global
+        normaliser and the shards are summed with an autograd-aware all-reduce."""
+        from ....models.modules.comm import all_reduce_sum_autograd
+
+        inputs = dict(inputs)
+        labels = inputs.pop("labels")
+        cu = inputs["cu_seq_lens_q"]
+        if inputs.get("position_ids") is None:
+            T = inputs["input_ids"].shape[-1]
+            inputs["position_ids"] = torch.arange(T, device=inputs["input_ids"].device).unsqueeze(0)
+        self._prepare_moe_runtime(model, inputs, aux_loss_scale)
+        use_chunk = self.config.loss_chunk.enabled or self.runtime.turbo_device.value == "cuda"
+        head = model.get_lm_head() if hasattr(model, "get_lm_head") else None
+        use_chunk = use_chunk and head is not None
+        out = model(**inputs, skip_lm_head=use_chunk)
+        n_streams = 1 + (len(out.get("mtp_hidden_states") or ()) if self.config.mtp.enabled else 0)
+        scales = [1.0] + [self.config.mtp.loss_scaling_factor] * (n_streams - 1)
+        streams = prepare_loss_labels(labels.to(self.device), cu, num_streams=n_streams, stream_scales=scales,
+                                      num_items_in_batch=num_items_in_batch, sp_size=self.sp_size, sp_rank=self.sp_rank,
+                                      world_size=self.world_size)
+        if use_chunk:
+            hs = [out["hidden_states"]] + list(out.get("mtp_hidden_states") or ())[: n_streams - 1]
+            weight = head.weight
+            total, comps = chunk_loss(hs, weight, streams, self._loss_chunk_size(hs[0]))
+        else:
+            lgs = [out["logits"]] + list(out.get("mtp_logits") or ())[: n_streams - 1]
+            total, comps = logits_loss(lgs, streams)
+        if self.sp_size > 1:
+            total = all_reduce_sum_autograd(total, self.sp_group)
+            for k in comps:
+                dist.all_reduce(comps[k], group=self.sp_group)
+        out["loss"] = total
+        out["main_loss"] = comps.get("main")
+        for k, v in comps.items():
+            if k != "main":
+                out[f"{k}_loss"] = v
+        return (total, out) if return_outputs else total
+
+    def _loss_chunk_size(self, hidden: torch.Tensor) -> int:
+        if self.config.loss_chunk.enabled:
+            return self.config.loss_chunk.chunk_size
+        return 4096  # on B200 the fused path is always used; 4096 rows keep the bf16 logits chunk near 1.2 GB

@@ -1,0 +1,340 @@
+"""Checkpoint I/O for the FSDP2 backend.
+
+Hugging Face safetensors  <->  sharded parameters:
+  * load: every engine tensor has a `LoadRecipe` (source tensors + assembly); a rank reads the sources it needs
+    through memory-mapped safetensors, assembles the full local tensor and keeps its own shard
+    (`Shard(0)` rows for DTensors, everything for replicated / single-rank tensors, only its experts under EP).
+  * save: each parameter is gathered (`full_tensor()`), converted back to Hugging Face names and written by a
+    deterministic owner rank into per-rank shard files of at most 5 GiB; expert tensors are written by the EP rank
+    that owns them; the index is published last so a partial export is never mistaken for a complete one.
+Native sharded state uses `torch.distributed.checkpoint`: model state includes frozen parameters, tensors that
+differ per EP rank are stamped `::ep<rank>` so their keys are unique, loading ignores extra saved entries but
+requires every current one (engine/backends/fsdp2/checkpoint/{dcp,weight_loader,weight_saver}.py of the reference).
+"""
+from __future__ import annotations
+
+import json
+import os
+import shutil
+from pathlib import Path
+from typing import Any
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ....logging import get_logger
+from ...checkpoint.layout import DCP_COMMIT, HF_INDEX, dcp_status, fsync_dir, save_json
+from ..base import BaseCheckpointManager
+
+logger = get_logger(__name__)
+
+MAX_SHARD_BYTES = int(os.environ.get("TORCHTURBO_HF_SHARD_BYTES", 5 * 1024 ** 3))
+
+
+def _is_dtensor(t) -> bool:
+    return hasattr(t, "_local_tensor")
+
+
+def _rank() -> int:
+    return dist.get_rank() if dist.is_initialized() else 0
+
+
+def _world() -> int:
+    return dist.get_world_size() if dist.is_initialized() else 1
+
+
+class _SafetensorsReader:
+    def __init__(self, root: str, tensor_files: dict[str, str]):
+        self.root, self.tensor_files = Path(root), tensor_files
+        self._open: dict[str, Any] = {}
+
+    def get(self, name: str) -> torch.Tensor:
+        from safetensors import safe_open
+
+        fn = self.tensor_files.get(name)
+        if fn is None:
+            raise KeyError(f"tensor {name!r} is not in the checkpoint")
+        if fn not in self._open:
+            self._open[fn] = safe_open(str(self.root / fn), framework="pt", device="cpu")
+        return self._open[fn].get_tensor(name)
+
+    def close(self) -> None:
+        self._open.clear()
+
+
+class FSDP2CheckpointManager(BaseCheckpointManager):
+    def __init__(self, backend) -> None:
+        self.backend = backend
+
+    # ------------------------------------------------------------------------------------------
+    # Hugging Face load
+    # ------------------------------------------------------------------------------------------
+    def _named_state(self, model: nn.Module):
+        seen: set[int] = set()
+        for name, p in model.named_parameters(remove_duplicate=False):
+            yield name, p, id(p) in seen
+            seen.add(id(p))
+        persistent = set(model.state_dict().keys())
+        for name, b in model.named_buffers():
+            if name in persistent:
+                yield name, b, False
+
+    @torch.no_grad()
+    def load_hf(self, model: nn.Module, path: str) -> None:
+        conv = model.get_weight_converter(self.backend.get_parallel_context(), path)
+        reader = _SafetensorsReader(path, conv.checkpoint_info.tensor_files)
+        missing: list[str] = []
+        for name, t, dup in self._named_state(model):
+            if dup:
+                continue
+            recipe = conv.load_recipe(name)
+            if recipe is None:
+                continue  # tied alias omitted by the checkpoint
+            try:
+                full = recipe.assemble([reader.get(s) for s in recipe.sources])
+            except KeyError as e:
+                missing.append(f"{name} <- {e}")
+                continue
+            self._assign(t, full, name)
+        reader.close()
+        if missing:
+            raise KeyError(f"checkpoint {path} lacks tensors for: {missing[:8]}{'...' if len(missing) > 8 else ''}")
+        if hasattr(model, "tie_weights"):
+            model.tie_weights()
+
+    def _assign(self, target: torch.Tensor, full: torch.Tensor, name: str) -> None:
+        if _is_dtensor(target):
+            from torch.distributed.tensor import Shard
+
+            local = target._local_tensor
+            piece = full
+            for mesh_dim, pl in enumerate(target.placements):
+                if isinstance(pl, Shard):
+                    n = target.device_mesh.size(mesh_dim)
+                    r = target.device_mesh.get_local_rank(mesh_dim)
+                    chunks = torch.chunk(piece, n, dim=pl.dim)
+                    piece = chunks[r] if r < len(chunks) else piece.narrow(pl.dim, 0, 0)
+            if tuple(piece.shape) != tuple(local.shape):
+                # uneven sharding: FSDP pads the last shard; copy what exists
+                sl = tuple(slice(0, s) for s in piece.shape)
+                local.zero_()
+                local[sl].copy_(piece.to(local.dtype))
+            else:
+                local.copy_(piece.to(local.dtype))
+        else:
+            if tuple(full.shape) != tuple(target.shape):
+                raise ValueError(f"{name}: checkpoint shape {tuple(full.shape)} != parameter shape {tuple(target.shape)}")
+            target.copy_(full.to(target.dtype))
+
+    # ------------------------------------------------------------------------------------------
+    # Hugging Face save
+    # ------------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def save_hf(self, model: nn.Module, path: str, *, source_path: str | None = None, dtype=torch.bfloat16) -> None:
+        from safetensors.torch import save_file
+
+        ctx = self.backend.get_parallel_context()
+        conv = model.get_weight_converter(ctx, None)
+        rank, world = _rank(), _world()
+        ep_size, ep_rank = ctx["ep"]["ep_size"], ctx["ep"]["ep_rank"]
+        if rank == 0:
+            os.makedirs(path, exist_ok=True)
+        if world > 1:
+            dist.barrier()
+        lora = getattr(model, "merged_lora_delta", None)
+        shard_idx, cur, cur_bytes = 0, {}, 0
+        weight_map: dict[str, str] = {}
+
+        def flush():
+            nonlocal shard_idx, cur, cur_bytes
+            if not cur:
+                return
+            fn = f"model-rank{rank:05d}-{shard_idx:05d}.safetensors"
+            save_file({k: v.contiguous() for k, v in cur.items()}, os.path.join(path, fn), metadata={"format": "pt"})
+            with open(os.path.join(path, fn), "rb") as f:
+                os.fsync(f.fileno())
+            for k in cur:
+                weight_map[k] = fn
+            shard_idx, cur, cur_bytes = shard_idx + 1, {}, 0
+
+        owner_rr = 0
+        for name, t, dup in self._named_state(model):
+            if dup:
+                continue
+            is_expert = conv.is_expert_param(name)
+            full = t.full_tensor() if _is_dtensor(t) else t
+            master = getattr(t, "_tt_master", None)
+            if master is not None:
+                full = master
+            if is_expert and ep_size > 1:
+                # unique per EP rank: written by the member of each EP position with the lowest world rank
+                writer = (rank == min(r for r in range(world) if r % ep_size == ep_rank))
+            else:
+                writer = (rank == owner_rr % world)
+                owner_rr += 1
+            if not writer:
+                continue
+            if lora is not None and name in lora:
+                full = full.float() + lora[name].to(full.device).float()
+            for hf_name, ht in conv.to_hf_tensors(name, full.detach()).items():
+                ht = ht.to(dtype if ht.dtype.is_floating_point else ht.dtype).cpu()
+                nbytes = ht.numel() * ht.element_size()
+                if cur and cur_bytes + nbytes > MAX_SHARD_BYTES:
+                    flush()
+                cur[hf_name] = ht
+                cur_bytes += nbytes
+        flush()
+        maps: list[dict] = [weight_map]
+        if world > 1:
+            maps = [None] * world
+            dist.all_gather_object(maps, weight_map)
+        if rank == 0:
+            merged: dict[str, str] = {}
+            for m in maps:
+                merged.update(m)
+            merged = self._merge_virtual_ep_keys(path, merged)
+            if source_path and os.path.isdir(source_path):
+                for fn in os.listdir(source_path):
+                    src = os.path.join(source_path, fn)
+                    if os.path.isfile(src) and not fn.endswith(".safetensors") and fn != HF_INDEX:
+                        shutil.copy2(src, os.path.join(path, fn))
+            cfg = getattr(model, "config", None)
+            if cfg is not None and hasattr(cfg, "save_pretrained") and not os.path.exists(os.path.join(path, "config.json")):
+                cfg.save_pretrained(path)
+            fsync_dir(path)
+            save_json(os.path.join(path, HF_INDEX), {"metadata": {"format": "pt"}, "weight_map": dict(sorted(merged.items()))})
+        if world > 1:
+            dist.barrier()
+
+    def _merge_virtual_ep_keys(self, path: str, weight_map: dict[str, str]) -> dict[str, str]:
+        """Fused-expert checkpoints write one `<name>__ep<r>` piece per EP rank; concatenate them (rank order)
+        into the real tensor."""
+        from safetensors import safe_open
+        from safetensors.torch import save_file
+
+        groups: dict[str, list[tuple[int, str]]] = {}
+        for k in weight_map:
+            if "__ep" in k:
+                base, _, r = k.rpartition("__ep")
+                groups.setdefault(base, []).append((int(r), k))
+        if not groups:
+            return weight_map
+        out = {k: v for k, v in weight_map.items() if "__ep" not in k}
+        merged_tensors = {}
+        for base, parts in groups.items():
+            pieces = []
+            for _, k in sorted(parts):
+                with safe_open(os.path.join(path, weight_map[k]), framework="pt", device="cpu") as f:
+                    pieces.append(f.get_tensor(k))
+            merged_tensors[base] = torch.cat(pieces, dim=0)
+        fn = "model-fused-experts.safetensors"
+        save_file(merged_tensors, os.path.join(path, fn), metadata={"format": "pt"})
+        for base in merged_tensors:
+            out[base] = fn
+        return out
+
+    # ------------------------------------------------------------------------------------------
+    # native sharded state (torch.distributed.checkpoint)
+    # ------------------------------------------------------------------------------------------
+    def _ep_suffix(self) -> str:
+        ep = self.backend.get_ep_info()
+        return f"::ep{ep['ep_rank']}" if ep["ep_size"] > 1 else ""
+
+    def _model_state(self, model: nn.Module) -> dict[str, torch.Tensor]:
+        """FQN -> tensor (DTensor or plain), frozen parameters included, EP-unique tensors stamped."""
+        suf = self._ep_suffix()
+        state = {}
+        for name, t, dup in self._named_state(model):
+            if dup:
+                continue
+            key = name + suf if (suf and id(t) in self.backend.expert_param_ids and not _is_dtensor(t)) else name
+            if suf and id(t) in self.backend.expert_param_ids and _is_dtensor(t):
+                key = name + suf
+            state[key] = t.data if isinstance(t, nn.Parameter) else t
+        return state
+
+    def save_native_model(self, model: nn.Module, path: str) -> None:
+        import torch.distributed.checkpoint as dcp
+
+        dcp.save(self._model_state(model), checkpoint_id=path)
+
+    def load_native_model(self, model: nn.Module, path: str) -> None:
+        import torch.distributed.checkpoint as dcp
+
+        if dcp_status(path) != "complete":
+            raise RuntimeError(f"{path} is not a complete native checkpoint")
+        state = self._model_state(model)
+        self._check_ep_keys(path, state)
+        dcp.load(state, checkpoint_id=path)  # in-place into the model's tensors; extra saved keys are ignored
+        if hasattr(model, "tie_weights"):
+            model.tie_weights()
+
+    def _check_ep_keys(self, path: str, state: dict[str, Any]) -> None:
+        from torch.distributed.checkpoint import FileSystemReader
+
+        saved = set(FileSystemReader(path).read_metadata().state_dict_metadata.keys())
+        missing = [k for k in state if k not in saved]
+        if missing:
+            saved_ep = sorted({k.rpartition("::ep")[2] for k in saved if "::ep" in k})
+            hint = f" (checkpoint EP ranks: {saved_ep}; current suffix {self._ep_suffix() or 'none'})" if saved_ep or self._ep_suffix() else ""
+            raise KeyError(f"native checkpoint lacks {len(missing)} required entries, e.g. {missing[:4]}{hint}")
+
+    # -- optimizer -------------------------------------------------------------------------------------
+    def _flatten_optimizer(self, model: nn.Module, optimizer) -> tuple[dict[str, torch.Tensor], dict[str, Any]]:
+        from ...optimizers import OptimizersContainer
+
+        names = {id(p): n for n, p in model.named_parameters()}
+        suf = self._ep_suffix()
+        opts = list(optimizer) if isinstance(optimizer, OptimizersContainer) else [optimizer]
+        onames = optimizer.names if isinstance(optimizer, OptimizersContainer) else ["opt0"]
+        tensors: dict[str, torch.Tensor] = {}
+        groups: dict[str, Any] = {}
+        for oname, opt in zip(onames, opts):
+            groups[oname] = [{k: v for k, v in g.items() if k != "params"} | {"params": [names[id(p)] for p in g["params"]]}
+                             for g in opt.param_groups]
+            for g in opt.param_groups:
+                for p in g["params"]:
+                    if hasattr(opt, "_init_state"):
+                        opt._init_state(p)
+                    st = opt.state.get(p, {})
+                    stamp = suf if (suf and id(p) in self.backend.expert_param_ids) else ""
+                    for k, v in st.items():
+                        if isinstance(v, torch.Tensor):
+                            tensors[f"{oname}/{names[id(p)]}{stamp}/{k}"] = v
+        return tensors, groups
+
+    def save_native_optimizer(self, model: nn.Module, optimizer, path: str) -> None:
+        import torch.distributed.checkpoint as dcp
+
+        tensors, groups = self._flatten_optimizer(model, optimizer)
+        dcp.save({"state": tensors, "param_groups": groups}, checkpoint_id=path)
+
+    def load_native_optimizer(self, model: nn.Module, optimizer, path: str) -> None:
+        import torch.distributed.checkpoint as dcp
+
+        tensors, groups = self._flatten_optimizer(model, optimizer)
+        holder = {"state": tensors, "param_groups": groups}
+        dcp.load(holder, checkpoint_id=path)
+        from ...optimizers import OptimizersContainer
+
+        opts = list(optimizer) if isinstance(optimizer, OptimizersContainer) else [optimizer]
+        onames = optimizer.names if isinstance(optimizer, OptimizersContainer) else ["opt0"]
+        for oname, opt in zip(onames, opts):
+            for g, saved in zip(opt.param_groups, holder["param_groups"].get(oname, [])):
+                for k, v in saved.items():
+                    if k != "params":
+                        g[k] = v
+            # bf16 parameters follow their restored fp32 master
+            for g in opt.param_groups:
+                for p in g["params"]:
+                    m = opt.state.get(p, {}).get("master")
+                    if m is not None:
+                        lp = p._local_tensor if _is_dtensor(p) else p
+                        lp.data.copy_(m.to(lp.dtype))
+
+    def native_model_status(self, path: str) -> str:
+        return dcp_status(path)
+
+    def native_optimizer_status(self, path: str) -> str:
+        return dcp_status(path)

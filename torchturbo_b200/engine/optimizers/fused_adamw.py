@@ -1,0 +1,125 @@
+"""AdamW on fp32 master state with one multi-tensor CUDA launch per parameter group.
+
+Two storage schemes are handled by the same optimizer:
+  * fp32 parameters (FSDP2 shards: DTensor locals): updated in place;
+  * bf16 parameters (units that are not sharded, e.g. experts when the expert-data-parallel mesh has one
+    rank): the optimizer owns an fp32 master copy and the kernel writes the bf16 parameter as a shadow
+    in the same pass, so there is no per-step cast traffic.
+The gradient-clipping coefficient is a device scalar applied inside the update kernel (no separate
+"scale all gradients" pass and no host synchronisation); a non-finite norm skips the update.
+On CPU (tests, oracle) the same arithmetic runs in PyTorch.  Math follows torch's fused AdamW, which the
+reference calls on the shards (engine/backends/fsdp2/optimizers/adamw.py:226-251).
+"""
+from __future__ import annotations
+
+from typing import Any
+
+import torch
+
+from ... import kernels as K
+
+
+def _local(t: torch.Tensor) -> torch.Tensor:
+    return t._local_tensor if hasattr(t, "_local_tensor") else t
+
+
+class FusedAdamW(torch.optim.Optimizer):
+    def __init__(self, params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01,
+                 **_ignored: Any):
+        defaults = dict(lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay)
+        super().__init__(params, defaults)
+        self._clip_coef: torch.Tensor | None = None
+        self._plans: dict[int, tuple[tuple, Any]] = {}
+
+    # -- clipping ------------------------------------------------------------------------------------
+    def set_clip_coef(self, coef: torch.Tensor | None) -> None:
+        """Device scalar multiplied into every gradient by the next `step()` (then cleared)."""
+        self._clip_coef = coef
+
+    # -- state ---------------------------------------------------------------------------------------
+    def _init_state(self, p: torch.Tensor) -> dict:
+        st = self.state[p]
+        if "exp_avg" not in st:
+            lp = _local(p)
+            st["step"] = torch.zeros((), dtype=torch.float32)
+            st["exp_avg"] = torch.zeros_like(p, dtype=torch.float32)
+            st["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
+            if lp.dtype != torch.float32:
+                st["master"] = _local(p).detach().float().clone()
+        return st
+
+    def grad_of(self, p: torch.Tensor) -> torch.Tensor | None:
+        g = getattr(p, "main_grad", None)
+        return g if g is not None else p.grad
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        clip, self._clip_coef = self._clip_coef, None
+        for gi, group in enumerate(self.param_groups):
+            ps = [p for p in group["params"] if self.grad_of(p) is not None]
+            if not ps:
+                continue
+            states = [self._init_state(p) for p in ps]
+            for st in states:
+                st["step"] += 1
+            step = int(states[0]["step"].item())
+            b1, b2 = group["betas"]
+            lp0 = _local(ps[0])
+            if lp0.is_cuda and K.available():
+                self._step_cuda(gi, group, ps, states, step, clip)
+            else:
+                self._step_torch(group, ps, states, step, clip)
+        return loss
+
+    def _step_cuda(self, gi, group, ps, states, step, clip):
+        key = tuple(id(p) for p in ps)
+        cached = self._plans.get(gi)
+        if cached is None or cached[0] != key:
+            masters, shadows = [], []
+            for p, st in zip(ps, states):
+                lp = _local(p)
+                if "master" in st:
+                    masters.append(st["master"]); shadows.append(lp)
+                else:
+                    masters.append(lp); shadows.append(None)
+            plan = K.MultiTensorPlan(masters, [_local(s["exp_avg"]) for s in states],
+                                     [_local(s["exp_avg_sq"]) for s in states], shadows)
+            self._plans[gi] = cached = (key, plan)
+        plan = cached[1]
+        grads = []
+        for p in ps:
+            g = _local(self.grad_of(p))
+            grads.append(g if g.is_contiguous() else g.contiguous())
+        plan.refresh_grads(grads)
+        b1, b2 = group["betas"]
+        K.adamw_step(plan, lr=group["lr"], beta1=b1, beta2=b2, eps=group["eps"], weight_decay=group["weight_decay"],
+                     step=step, clip=clip)
+
+    def _step_torch(self, group, ps, states, step, clip):
+        b1, b2 = group["betas"]
+        lr, eps, wd = group["lr"], group["eps"], group["weight_decay"]
+        bc1, bc2 = 1 - b1 ** step, 1 - b2 ** step
+        coef = float(clip) if clip is not None else 1.0
+        if coef != coef or coef in (float("inf"), float("-inf")):
+            return
+        for p, st in zip(ps, states):
+            lp = _local(p)
+            g = _local(self.grad_of(p)).float() * coef
+            w = st.get("master", lp)
+            m, v = _local(st["exp_avg"]), _local(st["exp_avg_sq"])
+            w.mul_(1 - lr * wd)
+            m.lerp_(g, 1 - b1)
+            v.mul_(b2).addcmul_(g, g, value=1 - b2)
+            denom = (v.sqrt() / (bc2 ** 0.5)).add_(eps)
+            w.addcdiv_(m, denom, value=-lr / bc1)
+            if w is not lp:
+                lp.copy_(w)
+
+    def zero_grad(self, set_to_none: bool = True):
+        super().zero_grad(set_to_none=set_to_none)
+        for group in self.param_groups:
+            for p in group["params"]:
+                mg = getattr(p, "main_grad", None)
+                if mg is not None:
+                    mg.zero_()

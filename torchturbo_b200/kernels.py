@@ -72,9 +72,22 @@ def lib():
     return _lib
 
 
+# kernels launched per C entry point (used to report how many of this library's kernels ran in a region)
+_LAUNCHES_PER_CALL = {"ttb_rmsnorm_bwd": 2, "ttb_router_fwd": 2, "ttb_perm_index": 3, "ttb_perm_scatter": 2,
+                      "ttb_gemm_status": 0}
+LAUNCH_COUNT = 0
+
+
+def launch_count() -> int:
+    """Number of CUDA kernels of this library launched so far in this process."""
+    return LAUNCH_COUNT
+
+
 def _check(code: int, what: str) -> None:
+    global LAUNCH_COUNT
     if code != 0:
         raise KernelError(f"{what} failed with code {code}")
+    LAUNCH_COUNT += _LAUNCHES_PER_CALL.get(what, 1)
 
 
 def _stream() -> C.c_void_p:
