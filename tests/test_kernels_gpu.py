@@ -285,3 +285,30 @@ def test_router(K, score_fn):
     dl = K.router_bwd(logits, out["topk_idx"], out["topk_prob"], k, score_fn, dprob=dprob, aux_grad=aux_g,
                       lse=out["lse"], valid_mask=valid, dlse=dlse, scaling=2.0)
     _close(dl, lg.grad, rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_attention_fwd(K, causal):
+    from torchturbo_b200.ops.providers.native import attention_ref
+
+    torch.manual_seed(0)
+    T, Hq, Hk, D = 1000, 8, 2, 128
+    cu = torch.tensor([0, 130, 131, 600, 900], dtype=torch.int32)  # tokens 900..999 are padding
+    qkv = _rand(T, (Hq + 2 * Hk) * D)
+    q = qkv[:, : Hq * D].reshape(T, Hq, D).contiguous()
+    k = qkv[:, Hq * D: (Hq + Hk) * D].reshape(T, Hk, D).contiguous()
+    v = qkv[:, (Hq + Hk) * D:].view(T, Hk, D)  # strided view, as produced by the fused QKV projection
+    tiles = K.build_q_tiles(cu).cuda()
+    out, lse, ml = K.attn_fwd(q, k, v, tiles, scale=D ** -0.5, causal=causal, want_max_logit=True)
+    torch.cuda.synchronize()
+    assert K.attn_status() == (0, 0)
+    ref, ref_ml = attention_ref(q, k, v, cu, causal=causal, scale=D ** -0.5, want_max_logits=True)
+    _close(out, ref, atol=2e-2)
+    _close(ml, ref_ml, rtol=1e-2, atol=1e-2)
+    assert float(out[900:].abs().max()) == 0.0
+    # lse against a direct computation on one document / head
+    a, b = 131, 600
+    s = (q[a:b, 3].float() @ k[a:b, 0].float().t()) * D ** -0.5
+    if causal:
+        s = s.masked_fill(~torch.ones(b - a, b - a, dtype=torch.bool, device="cuda").tril(), float("-inf"))
+    _close(lse[3, a:b], torch.logsumexp(s, -1), rtol=1e-2, atol=1e-2)

@@ -1,0 +1,368 @@
+// Variable-length (packed) flash attention forward for sm_100a, head_dim 128, GQA, causal or full.
+//
+// One CTA handles one 128-row query tile of one document for one query head.  Warp roles:
+//   warp 0      TMA producer   : Q once, then K_j / V_j tiles (2 stages each)
+//   warp 1      MMA issuer     : S_j = Q K_j^T  (tcgen05, fp32 in TMEM, 2 buffers)
+//                                O_j = P_j V_j  (V consumed MN-major straight from its [kv, d] tile, 2 buffers)
+//   warps 2-5   softmax        : one thread per query row: mask, running max, exp2, row sum,
+//                                P_j -> shared memory (bf16, 128B-swizzled K-major A operand)
+//   warps 6-9   accumulate     : one thread per query row keeps the 128 output values in registers,
+//                                O = O * alpha_j + O_j (O_j read from TMEM), final 1/l scaling and store
+// Every wait is bounded (mbar_wait): on timeout the role stops, all roles meet at the final barrier,
+// TMEM is released and the status word records kernel/site.
+//
+// Replaces flash-attn 2 `flash_attn_varlen_func` used by the reference (models/modules/attention/interface.py:114-158)
+// and produces the optional per-head maximum logit of its TE / FlexAttention providers
+// (ops/providers/cuda/attention.py:34-331).
+#include "common.cuh"
+
+namespace ttb {
+
+constexpr unsigned KID_ATTN_FWD = 2;
+constexpr int AT_BM = 128;   // query rows per CTA
+constexpr int AT_BN = 128;   // kv rows per block
+constexpr int AT_D = 128;    // head dim
+constexpr int TILE_BYTES = 128 * 128 * 2;  // one [128 x 128] bf16 tile = two 16 KB swizzle panels
+
+struct AttnFwdParams {
+  const int* q_tiles;   // [n_tiles, 3]: first query row, document start, document end (token indices)
+  __nv_bfloat16* out;   // [T, Hq, D]
+  float* lse;           // [Hq, T] natural-log logsumexp of the scaled logits (or null)
+  float* max_logit;     // [Hq] per-head maximum scaled logit (atomic max; or null)
+  int Hq, Hk;
+  long long T;
+  float scale;          // softmax scale (1/sqrt(D))
+  int causal;
+};
+
+struct AttnSmem {
+  // tiles (each 32 KB, 1024-byte aligned)
+  static constexpr int Q = 0;
+  static constexpr int K0 = Q + TILE_BYTES;
+  static constexpr int V0 = K0 + 2 * TILE_BYTES;
+  static constexpr int P = V0 + 2 * TILE_BYTES;
+  static constexpr int ALPHA = P + TILE_BYTES;            // float [4][128]
+  static constexpr int ROWSUM = ALPHA + 4 * 128 * 4;      // float [128]
+  static constexpr int BARS = ROWSUM + 128 * 4;
+  static constexpr int TOTAL = BARS + 256 + 1024;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ void atomic_max_float(float* addr, float v) {
+  // valid for any sign mix: compare as ordered ints
+  if (v >= 0.f) atomicMax(reinterpret_cast<int*>(addr), __float_as_int(v));
+  else atomicMin(reinterpret_cast<unsigned int*>(addr), __float_as_uint(v));
+}
+
+__global__ void __launch_bounds__(320, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const AttnFwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AttnSmem::BARS);
+  uint64_t* q_full = bars + 0;
+  uint64_t* k_full = bars + 1;    // [2]
+  uint64_t* k_empty = bars + 3;   // [2]
+  uint64_t* v_full = bars + 5;    // [2]
+  uint64_t* v_empty = bars + 7;   // [2]
+  uint64_t* s_full = bars + 9;    // [2]
+  uint64_t* s_empty = bars + 11;  // [2]
+  uint64_t* p_full = bars + 13;
+  uint64_t* p_empty = bars + 14;
+  uint64_t* o_full = bars + 15;   // [2]
+  uint64_t* o_empty = bars + 17;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
+  float* s_alpha = reinterpret_cast<float*>(smem + AttnSmem::ALPHA);
+  float* s_rowsum = reinterpret_cast<float*>(smem + AttnSmem::ROWSUM);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x, h = blockIdx.y;
+  const int hk = h / (p.Hq / p.Hk);
+  const int q0 = p.q_tiles[tile * 3 + 0];
+  const int ds = p.q_tiles[tile * 3 + 1];
+  const int de = p.q_tiles[tile * 3 + 2];
+  const int kv_end = p.causal ? min(de, q0 + AT_BM) : de;
+  const int nblk = (kv_end - ds + AT_BN - 1) / AT_BN;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
+      mbar_init(&o_full[i], 1); mbar_init(&o_empty[i], 4);
+    }
+    mbar_init(p_full, 4);
+    mbar_init(p_empty, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tm_S = tmem_base;        // 2 x 128 columns
+  const uint32_t tm_O = tmem_base + 256;  // 2 x 128 columns
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (elect_one()) {
+      tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+      mbar_expect_tx(q_full, TILE_BYTES);
+      tma_load_2d(smem + AttnSmem::Q, &tmQ, q_full, h * AT_D, q0);
+      tma_load_2d(smem + AttnSmem::Q + 16384, &tmQ, q_full, h * AT_D + 64, q0);
+      bool ok = true;
+      for (int j = 0; j < nblk && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        const int kv0 = ds + j * AT_BN;
+        if (!mbar_wait(&k_empty[st], ph ^ 1, KID_ATTN_FWD, 1)) { ok = false; break; }
+        mbar_expect_tx(&k_full[st], TILE_BYTES);
+        tma_load_2d(smem + AttnSmem::K0 + st * TILE_BYTES, &tmK, &k_full[st], hk * AT_D, kv0);
+        tma_load_2d(smem + AttnSmem::K0 + st * TILE_BYTES + 16384, &tmK, &k_full[st], hk * AT_D + 64, kv0);
+        if (!mbar_wait(&v_empty[st], ph ^ 1, KID_ATTN_FWD, 2)) { ok = false; break; }
+        mbar_expect_tx(&v_full[st], TILE_BYTES);
+        tma_load_2d(smem + AttnSmem::V0 + st * TILE_BYTES, &tmV, &v_full[st], hk * AT_D, kv0);
+        tma_load_2d(smem + AttnSmem::V0 + st * TILE_BYTES + 16384, &tmV, &v_full[st], hk * AT_D + 64, kv0);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);  // Q (K-major) x K (K-major)
+      constexpr uint32_t idesc_o = make_idesc_bf16(128, 128, false, true);   // P (K-major) x V (MN-major)
+      const uint32_t sQ = smem_u32(smem + AttnSmem::Q);
+      const uint32_t sP = smem_u32(smem + AttnSmem::P);
+      bool ok = mbar_wait(q_full, 0, KID_ATTN_FWD, 3);
+      auto issue_s = [&](int j) -> bool {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&k_full[st], ph, KID_ATTN_FWD, 4)) return false;
+        if (!mbar_wait(&s_empty[st], ph ^ 1, KID_ATTN_FWD, 5)) return false;
+        tc_fence_after();
+        const uint32_t sK = smem_u32(smem + AttnSmem::K0 + st * TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_ss(tm_S + st * 128, make_smem_desc(sQ + off, 16, 1024), make_smem_desc(sK + off, 16, 1024), idesc_s,
+                  kk != 0);
+        }
+        umma_commit(&s_full[st]);
+        umma_commit(&k_empty[st]);
+        return true;
+      };
+      if (ok && nblk > 0) ok = issue_s(0);
+      for (int j = 0; j < nblk && ok; ++j) {
+        if (j + 1 < nblk) {
+          if (!issue_s(j + 1)) { ok = false; break; }
+        }
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&v_full[st], ph, KID_ATTN_FWD, 6)) { ok = false; break; }
+        if (!mbar_wait(p_full, j & 1, KID_ATTN_FWD, 7)) { ok = false; break; }
+        if (!mbar_wait(&o_empty[st], ph ^ 1, KID_ATTN_FWD, 8)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sV = smem_u32(smem + AttnSmem::V0 + st * TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          // A = P: K-major, k-step of 16 kv columns = 32 bytes inside a panel, second panel after 64 columns
+          const uint32_t offp = (kk >> 2) * 16384 + (kk & 3) * 32;
+          // B = V: MN-major [kv rows][d], k-step of 16 kv rows = 2048 bytes, d panels 16 KB apart
+          umma_ss(tm_O + st * 128, make_smem_desc(sP + offp, 16, 1024), make_smem_desc(sV + kk * 2048, 16384, 1024),
+                  idesc_o, kk != 0);
+        }
+        umma_commit(&o_full[st]);
+        umma_commit(&v_empty[st]);
+        umma_commit(p_empty);
+      }
+    }
+  } else if (warp < 6) {
+    // ---------------------------------------------------------------- softmax (thread = query row)
+    const int lg = warp & 3;
+    const int row = lg * 32 + lane;
+    const int qrow = q0 + row;
+    const bool row_ok = qrow < de;
+    const float c = p.scale * 1.4426950408889634f;
+    float m_run = -INFINITY, l_run = 0.f, mx_logit = -INFINITY;
+    uint8_t* sP = smem + AttnSmem::P;
+    bool ok = true;
+    for (int j = 0; j < nblk && ok; ++j) {
+      const int st = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      if (!mbar_wait(&s_full[st], ph, KID_ATTN_FWD, 9)) { ok = false; break; }
+      tc_fence_after();
+      const int kv0 = ds + j * AT_BN;
+      const bool need_mask = (kv0 + AT_BN > de) || (p.causal && kv0 + AT_BN - 1 > q0);
+      float s[128];
+      const uint32_t t_row = tm_S + st * 128 + (static_cast<uint32_t>(lg * 32) << 16);
+#pragma unroll
+      for (int cb = 0; cb < 4; ++cb) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(t_row + cb * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s[cb * 32 + i] = __uint_as_float(v[i]);
+      }
+      // S buffer can be refilled as soon as every warp has its copy
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[st]);
+      float m_blk = -INFINITY;
+      if (need_mask) {
+        const int lim = p.causal ? min(de - 1, qrow) : de - 1;  // last visible kv index
+#pragma unroll
+        for (int i = 0; i < 128; ++i) {
+          const bool vis = row_ok && (kv0 + i <= lim);
+          s[i] = vis ? s[i] : -INFINITY;
+          m_blk = fmaxf(m_blk, s[i]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 128; ++i) m_blk = fmaxf(m_blk, s[i]);
+      }
+      mx_logit = fmaxf(mx_logit, m_blk);
+      const float m_new = fmaxf(m_run, m_blk);
+      const float alpha = (m_run == -INFINITY) ? 0.f : fast_exp2((m_run - m_new) * c);
+      const float mc = (m_new == -INFINITY) ? 0.f : m_new * c;
+      float l_blk = 0.f;
+      // P may only be overwritten once the previous P.V has retired
+      if (j > 0) {
+        if (!mbar_wait(p_empty, (j - 1) & 1, KID_ATTN_FWD, 10)) { ok = false; break; }
+      }
+      s_alpha[(j & 3) * 128 + row] = alpha;
+#pragma unroll
+      for (int ch = 0; ch < 16; ++ch) {  // 16 chunks of 8 columns (16 bytes of bf16)
+        uint32_t w[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float e0 = fast_exp2(s[ch * 8 + 2 * q] * c - mc);
+          const float e1 = fast_exp2(s[ch * 8 + 2 * q + 1] * c - mc);
+          w[q] = pack_bf16(e0, e1);
+          // accumulate what the tensor core will actually see (bf16-rounded probabilities)
+          float2 r = unpack_bf16(w[q]);
+          l_blk += r.x + r.y;
+        }
+        const int panel = ch >> 3, cc = ch & 7;
+        uint8_t* dst = sP + panel * 16384 + row * 128 + ((cc ^ (row & 7)) * 16);
+        *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      l_run = l_run * alpha + l_blk;
+      m_run = m_new;
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    s_rowsum[row] = l_run;
+    if (ok && row_ok) {
+      if (p.lse) p.lse[static_cast<long long>(h) * p.T + qrow] = (l_run > 0.f) ? m_run * p.scale + logf(l_run) : -INFINITY;
+    }
+    if (p.max_logit) {
+      float wm = warp_max(row_ok ? mx_logit * p.scale : -INFINITY);
+      if (lane == 0 && wm > -INFINITY) atomic_max_float(&p.max_logit[h], wm);
+    }
+    // hand the row sums to the accumulate warps: named barrier over the 256 threads of warps 2..9
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+  } else {
+    // ---------------------------------------------------------------- accumulate (thread = query row)
+    const int lg = warp & 3;
+    const int row = lg * 32 + lane;
+    const int qrow = q0 + row;
+    float o[128];
+#pragma unroll
+    for (int i = 0; i < 128; ++i) o[i] = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nblk && ok; ++j) {
+      const int st = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      if (!mbar_wait(&o_full[st], ph, KID_ATTN_FWD, 11)) { ok = false; break; }
+      tc_fence_after();
+      const float alpha = s_alpha[(j & 3) * 128 + row];
+      const uint32_t t_row = tm_O + st * 128 + (static_cast<uint32_t>(lg * 32) << 16);
+#pragma unroll
+      for (int cb = 0; cb < 4; ++cb) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(t_row + cb * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[cb * 32 + i] = o[cb * 32 + i] * alpha + __uint_as_float(v[i]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&o_empty[st]);
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (ok && qrow < de) {
+      const float l = s_rowsum[row];
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* dst = p.out + (static_cast<long long>(qrow) * p.Hq + h) * AT_D;
+#pragma unroll
+      for (int i = 0; i < 128; i += 8) {
+        uint4 w;
+        w.x = pack_bf16(o[i] * inv, o[i + 1] * inv); w.y = pack_bf16(o[i + 2] * inv, o[i + 3] * inv);
+        w.z = pack_bf16(o[i + 4] * inv, o[i + 5] * inv); w.w = pack_bf16(o[i + 6] * inv, o[i + 7] * inv);
+        *reinterpret_cast<uint4*>(dst + i) = w;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+static int make_rows_map(CUtensorMap* m, const void* base, long long rows, long long row_stride_elems, int cols) {
+  uint64_t dims[2] = {static_cast<uint64_t>(cols), static_cast<uint64_t>(rows)};
+  uint64_t str[1] = {static_cast<uint64_t>(row_stride_elems) * 2};
+  uint32_t box[2] = {64, 128};
+  return make_tmap_bf16(m, base, 2, dims, str, box);
+}
+
+}  // namespace ttb
+
+using namespace ttb;
+
+// q: [T, Hq*128] (row stride ldq), k: [T, Hk*128] (ldk), v: [T, Hk*128] (ldv; may be a strided view)
+TTB_EXPORT int ttb_attn_fwd(const void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv,
+                            void* out, float* lse, float* max_logit, const int* q_tiles, int n_tiles, long long T,
+                            int Hq, int Hk, int D, float scale, int causal, void* stream) {
+  if (D != 128 || Hq % Hk) return 901;
+  if ((ldq % 8) || (ldk % 8) || (ldv % 8)) return 902;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) return 903;
+  if (n_tiles == 0) return 0;
+  CUtensorMap tq, tk, tv;
+  if (make_rows_map(&tq, q, T, ldq, Hq * D)) return 101;
+  if (make_rows_map(&tk, k, T, ldk, Hk * D)) return 102;
+  if (make_rows_map(&tv, v, T, ldv, Hk * D)) return 103;
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem::TOTAL);
+    if (e != cudaSuccess) return 300 + (int)e;
+    attr = true;
+  }
+  AttnFwdParams p{q_tiles, (__nv_bfloat16*)out, lse, max_logit, Hq, Hk, T, scale, causal};
+  dim3 grid(n_tiles, Hq);
+  attn_fwd_kernel<<<grid, 320, AttnSmem::TOTAL, reinterpret_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+TTB_EXPORT int ttb_attn_status(unsigned int* out4, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(out4, ttb::g_status_word, sizeof(unsigned int) * 4);
+  if (e != cudaSuccess) return (int)e;
+  if (reset) {
+    unsigned int z[4] = {0, 0, 0, 0};
+    e = cudaMemcpyToSymbol(ttb::g_status_word, z, sizeof(z));
+  }
+  return (int)e;
+}

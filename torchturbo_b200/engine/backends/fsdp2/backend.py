@@ -74,9 +74,23 @@ class FSDP2Backend(BaseBackend):
         self.gradient_scaling_factor = 1.0
         self.local_units: list[nn.Module] = []
         self.fsdp_units: list[nn.Module] = []
-        self.no_shard_params: list[nn.Parameter] = []
-        self.expert_param_ids: set[int] = set()
+        self.expert_modules: list[nn.Module] = []
+        self.no_shard_names: list[str] = []
+        self._model_ref = None
         self._plan: FSDPParallelPlan | None = None
+
+    @property
+    def no_shard_params(self) -> list[nn.Parameter]:
+        if self._model_ref is None or not self.no_shard_names:
+            return []
+        table = dict(self._model_ref.named_parameters())
+        return [table[n] for n in self.no_shard_names if n in table]
+
+    @property
+    def expert_param_ids(self) -> set[int]:
+        """ids of the parameters owned by expert units.  Recomputed from the modules because materialisation
+        (`to_empty`) and dtype changes replace parameter objects."""
+        return {id(p) for m in self.expert_modules for p in m.parameters()}
 
     # ------------------------------------------------------------------------------------------
     # meshes and groups
@@ -239,8 +253,8 @@ class FSDP2Backend(BaseBackend):
             return
         mesh, is_expert = self._mesh_for(spec)
         own = [p for p in module.parameters()]
-        if is_expert:
-            self.expert_param_ids.update(id(p) for p in own)
+        if is_expert and module not in self.expert_modules:
+            self.expert_modules.append(module)
         if mesh.size() > 1:
             from torch.distributed.fsdp import fully_shard
 
@@ -272,15 +286,22 @@ class FSDP2Backend(BaseBackend):
             spec = plan.match(name) if plan is not None else None
             if spec is not None and spec.no_shard:
                 ids.add(id(p))
-        self.no_shard_params = [p for p in model.parameters() if id(p) in ids]
+        self.no_shard_names = [n for n, p in model.named_parameters() if id(p) in ids]
+        self._model_ref = model
 
     def _shard_model(self, model: nn.Module, compiled: dict[str, FSDPPlanSpec]) -> None:
         self._collect_no_shard(model, compiled)
         # 1. explicit units, deepest first so children are wrapped before their parents
         explicit = [(fqn, spec) for fqn, spec in compiled.items()
                     if spec.placement is not None or spec.standalone_world_shard]
+        emb = model.get_input_embeddings() if hasattr(model, "get_input_embeddings") else None
+        head = model.get_output_embeddings() if hasattr(model, "get_output_embeddings") else None
+        tied = emb is not None and head is not None and getattr(head, "weight", None) is getattr(emb, "weight", object())
         for fqn, spec in sorted(explicit, key=lambda kv: -kv[0].count(".")):
-            self._make_unit(model.get_submodule(fqn), spec)
+            mod = model.get_submodule(fqn)
+            if tied and (mod is emb or mod is head):
+                continue  # tied input/output embeddings must live in one unit: the root
+            self._make_unit(mod, spec)
         # 2. every ModuleList child is a unit
         for _, mod in list(model.named_modules()):
             if isinstance(mod, nn.ModuleList):
@@ -288,9 +309,6 @@ class FSDP2Backend(BaseBackend):
                     if any(True for _ in child.parameters()):
                         self._make_unit(child, None)
         # 3. input embeddings, resident tail (final norm + output embedding), root
-        emb = model.get_input_embeddings() if hasattr(model, "get_input_embeddings") else None
-        head = model.get_output_embeddings() if hasattr(model, "get_output_embeddings") else None
-        tied = emb is not None and head is not None and getattr(head, "weight", None) is getattr(emb, "weight", object())
         if emb is not None and not tied:
             self._make_unit(emb, None)
         if head is not None and not tied:
@@ -348,18 +366,48 @@ class FSDP2Backend(BaseBackend):
         if init_weights and has_meta:
             self._init_parameters(model)
 
-    def _init_parameters(self, model: nn.Module) -> None:
+    def _init_parameters(self, model: nn.Module, seed: int = 0) -> None:
+        """normal(0, initializer_range) for matrices, ones for norm weights, zeros for biases.  Every parameter is
+        drawn from its own generator (seed + CRC of its name) at its *global* shape and then cut down to this
+        rank's shard / experts, so the initial model does not depend on the world size or the EP / FSDP layout."""
+        import zlib
+
         std = float(getattr(getattr(model, "config", None), "initializer_range", 0.02))
+        seed = int(getattr(self, "_init_seed", seed))
+        expert_ids_cache = self.expert_param_ids
         with torch.no_grad():
             for name, p in model.named_parameters():
                 lp = p._local_tensor if hasattr(p, "_local_tensor") else p
-                if lp.ndim <= 1:
+                if p.ndim <= 1:
                     if name.endswith("bias") or "expert_bias" in name:
                         lp.zero_()
                     else:
                         lp.fill_(1.0)
+                    continue
+                gen = torch.Generator(device=lp.device)
+                expert_ids = expert_ids_cache
+                gen.manual_seed(seed * 1000003 + zlib.crc32(name.encode()))
+                shape = list(p.shape)
+                is_expert = id(p) in expert_ids
+                if is_expert and self.ep_size > 1:
+                    shape[0] *= self.ep_size
+                full = torch.empty(shape, dtype=torch.float32, device=lp.device).normal_(0.0, std, generator=gen)
+                if is_expert and self.ep_size > 1:
+                    rows = p.shape[0]
+                    full = full[self.ep_rank * rows:(self.ep_rank + 1) * rows]
+                if hasattr(p, "_local_tensor"):
+                    from torch.distributed.tensor import Shard
+
+                    for mesh_dim, pl in enumerate(p.placements):
+                        if isinstance(pl, Shard):
+                            n, r = p.device_mesh.size(mesh_dim), p.device_mesh.get_local_rank(mesh_dim)
+                            chunks = torch.chunk(full, n, dim=pl.dim)
+                            full = chunks[r] if r < len(chunks) else full.narrow(pl.dim, 0, 0)
+                    lp.zero_()
+                    lp[tuple(slice(0, s_) for s_ in full.shape)].copy_(full)
                 else:
-                    lp.normal_(0.0, std)
+                    lp.copy_(full)
+                del full
             for name, b in model.named_buffers():
                 if b.dtype.is_floating_point and "inv_freq" not in name:
                     b.zero_()
@@ -401,8 +449,8 @@ class FSDP2Backend(BaseBackend):
     # ------------------------------------------------------------------------------------------
     # optimizer
     # ------------------------------------------------------------------------------------------
-    def _topology_of(self, p: torch.Tensor) -> str:
-        if id(p) in self.expert_param_ids:
+    def _topology_of(self, p: torch.Tensor, expert_ids: set[int] | None = None) -> str:
+        if id(p) in (self.expert_param_ids if expert_ids is None else expert_ids):
             return "moe"
         if hasattr(p, "_local_tensor"):
             return "dense"
@@ -421,8 +469,9 @@ class FSDP2Backend(BaseBackend):
         buckets: dict[tuple, list[dict]] = {}
         for g in optimizer_plan.groups:
             by_topo: dict[str, list] = {}
+            eids = self.expert_param_ids
             for p in g.params:
-                by_topo.setdefault(self._topology_of(p), []).append(p)
+                by_topo.setdefault(self._topology_of(p, eids), []).append(p)
             for topo, ps in by_topo.items():
                 buckets.setdefault((g.optimizer_cls, topo), []).append({"params": ps, **g.hyperparameters})
         opts, names = [], []
@@ -453,9 +502,10 @@ class FSDP2Backend(BaseBackend):
         per-rank-average footing as the FSDP-averaged dense gradients."""
         if self.ep_size == 1:
             return
+        eids = self.expert_param_ids
         with torch.no_grad():
             for p in model.parameters():
-                if id(p) in self.expert_param_ids and p.grad is not None and not getattr(p, "_tt_grad_scaled", False):
+                if id(p) in eids and p.grad is not None and not getattr(p, "_tt_grad_scaled", False):
                     p.grad.mul_(self.gradient_scaling_factor)
                     p._tt_grad_scaled = True
 
@@ -467,13 +517,14 @@ class FSDP2Backend(BaseBackend):
         the update kernel instead of in a separate pass."""
         self._scale_moe_gradient(model)
         sq = {"dense": [], "moe": [], "local": []}
+        eids = self.expert_param_ids
         for p in model.parameters():
             g = getattr(p, "main_grad", None)
             g = g if g is not None else p.grad
             if g is None:
                 continue
             lg = g._local_tensor if hasattr(g, "_local_tensor") else g
-            sq[self._topology_of(p)].append(lg)
+            sq[self._topology_of(p, eids)].append(lg)
         dev = self.device
 
         def sumsq(ts):
@@ -546,7 +597,7 @@ class FSDP2Backend(BaseBackend):
             T = inputs["input_ids"].shape[-1]
             inputs["position_ids"] = torch.arange(T, device=inputs["input_ids"].device).unsqueeze(0)
         self._prepare_moe_runtime(model, inputs, aux_loss_scale)
-        use_chunk = self.config.loss_chunk.enabled or self.runtime.turbo_device.value == "cuda"
+        use_chunk = self.config.loss_chunk.enabled or self.runtime.turbo_device.value == "cuda" or self.world_size > 1
         head = model.get_lm_head() if hasattr(model, "get_lm_head") else None
         use_chunk = use_chunk and head is not None
         out = model(**inputs, skip_lm_head=use_chunk)
@@ -557,8 +608,7 @@ class FSDP2Backend(BaseBackend):
                                       world_size=self.world_size)
         if use_chunk:
             hs = [out["hidden_states"]] + list(out.get("mtp_hidden_states") or ())[: n_streams - 1]
-            weight = head.weight
-            total, comps = chunk_loss(hs, weight, streams, self._loss_chunk_size(hs[0]))
+            total, comps = chunk_loss(hs, head, streams, self._loss_chunk_size(hs[0]))
         else:
             lgs = [out["logits"]] + list(out.get("mtp_logits") or ())[: n_streams - 1]
             total, comps = logits_loss(lgs, streams)

@@ -244,13 +244,12 @@ class FSDP2CheckpointManager(BaseCheckpointManager):
     def _model_state(self, model: nn.Module) -> dict[str, torch.Tensor]:
         """FQN -> tensor (DTensor or plain), frozen parameters included, EP-unique tensors stamped."""
         suf = self._ep_suffix()
+        eids = self.backend.expert_param_ids
         state = {}
         for name, t, dup in self._named_state(model):
             if dup:
                 continue
-            key = name + suf if (suf and id(t) in self.backend.expert_param_ids and not _is_dtensor(t)) else name
-            if suf and id(t) in self.backend.expert_param_ids and _is_dtensor(t):
-                key = name + suf
+            key = name + suf if (suf and id(t) in eids) else name
             state[key] = t.data if isinstance(t, nn.Parameter) else t
         return state
 
@@ -290,6 +289,7 @@ class FSDP2CheckpointManager(BaseCheckpointManager):
         onames = optimizer.names if isinstance(optimizer, OptimizersContainer) else ["opt0"]
         tensors: dict[str, torch.Tensor] = {}
         groups: dict[str, Any] = {}
+        eids = self.backend.expert_param_ids
         for oname, opt in zip(onames, opts):
             groups[oname] = [{k: v for k, v in g.items() if k != "params"} | {"params": [names[id(p)] for p in g["params"]]}
                              for g in opt.param_groups]
@@ -298,7 +298,7 @@ class FSDP2CheckpointManager(BaseCheckpointManager):
                     if hasattr(opt, "_init_state"):
                         opt._init_state(p)
                     st = opt.state.get(p, {})
-                    stamp = suf if (suf and id(p) in self.backend.expert_param_ids) else ""
+                    stamp = suf if (suf and id(p) in eids) else ""
                     for k, v in st.items():
                         if isinstance(v, torch.Tensor):
                             tensors[f"{oname}/{names[id(p)]}{stamp}/{k}"] = v

@@ -164,6 +164,7 @@ class TorchTurboEngine:
         else:
             seed = int(init_kwargs.get("seed", 0))
             self.runtime.manual_seed_all(seed)
+            self.backend._init_seed = seed
             self.backend.materialize(model, init_weights=True)
         self.backend.finalize_model_load(model)
         model.on_materialized()

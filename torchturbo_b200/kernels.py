@@ -462,3 +462,41 @@ def perm_combine(src, row_of, T, k, *, weights=None, residual=None):
                                   C.c_longlong(out.stride(0)), C.c_longlong(T), C.c_int(k), C.c_int(H), _stream()),
            "ttb_perm_combine")
     return out
+
+
+# --------------------------------------------------------------------------------------
+# Flash attention (varlen, head_dim 128)
+# --------------------------------------------------------------------------------------
+def attn_status(reset: bool = False) -> tuple[int, int]:
+    buf = (C.c_uint * 4)()
+    _check(lib().ttb_attn_status(buf, C.c_int(1 if reset else 0)), "ttb_gemm_status")
+    return int(buf[0]), int(buf[1])
+
+
+def build_q_tiles(cu_seqlens, block: int = 128) -> torch.Tensor:
+    """Host-side table of 128-row query tiles `[n, 3] = (first row, document start, document end)` from packed
+    boundaries (a CPU tensor or list); no device synchronisation is involved."""
+    offs = cu_seqlens.tolist() if isinstance(cu_seqlens, torch.Tensor) else list(cu_seqlens)
+    rows = []
+    for a, b in zip(offs[:-1], offs[1:]):
+        # longest-first inside a document does not matter; later tiles of causal documents do more work, so
+        # emit them first to shorten the tail of the launch
+        for q0 in range(a + ((b - a - 1) // block) * block, a - 1, -block) if b > a else ():
+            rows.append((q0, a, b))
+    return torch.tensor(rows, dtype=torch.int32).reshape(-1, 3)
+
+
+def attn_fwd(q, k, v, q_tiles_dev, *, scale: float, causal: bool = True, want_lse: bool = True,
+             want_max_logit: bool = False):
+    """q: [T, Hq, 128]; k, v: [T, Hk, 128] (v may be a row-strided view).  Returns (out, lse [Hq, T], max_logit [Hq])."""
+    T, Hq, D = q.shape
+    Hk = k.shape[1]
+    assert q.stride(2) == 1 and q.stride(1) == D and k.stride(1) == D and v.stride(1) == D and v.stride(2) == 1
+    out = torch.zeros_like(q) if True else None
+    lse = torch.full((Hq, T), float("-inf"), dtype=torch.float32, device=q.device) if want_lse else None
+    ml = torch.full((Hq,), float("-inf"), dtype=torch.float32, device=q.device) if want_max_logit else None
+    _check(lib().ttb_attn_fwd(_p(q), C.c_longlong(q.stride(0)), _p(k), C.c_longlong(k.stride(0)), _p(v),
+                              C.c_longlong(v.stride(0)), _p(out), _p(lse), _p(ml), _p(q_tiles_dev),
+                              C.c_int(q_tiles_dev.shape[0]), C.c_longlong(T), C.c_int(Hq), C.c_int(Hk), C.c_int(D),
+                              C.c_float(scale), C.c_int(int(causal)), _stream()), "ttb_attn_fwd")
+    return out, lse, ml

@@ -91,11 +91,17 @@ def logits_loss(logits: Sequence[torch.Tensor] | torch.Tensor, streams: Sequence
     return _finish(sums, streams)
 
 
-def chunk_loss(hidden: Sequence[torch.Tensor] | torch.Tensor, lm_head_weight: torch.Tensor, streams: Sequence[LossStream],
+def chunk_loss(hidden: Sequence[torch.Tensor] | torch.Tensor, lm_head, streams: Sequence[LossStream],
                chunk_size: int = 1024):
-    """`hidden[i]`: [1, T_local, H] for stream i; all streams share `lm_head_weight` ([V, H])."""
+    """`hidden[i]`: [1, T_local, H] for stream i; all streams share the output projection.  `lm_head` is either
+    the head module (called with `labels=` so FSDP hooks run) or a plain `[V, H]` weight tensor."""
     if isinstance(hidden, torch.Tensor):
         hidden = [hidden]
-    sums = [ops.linear_cross_entropy(h.reshape(-1, h.shape[-1]), lm_head_weight, st.labels.reshape(-1), chunk_size=chunk_size)
-            for h, st in zip(hidden, streams)]
+    sums = []
+    for h, st in zip(hidden, streams):
+        if isinstance(lm_head, torch.nn.Module):
+            sums.append(lm_head(h, labels=st.labels, chunk_size=chunk_size))
+        else:
+            sums.append(ops.linear_cross_entropy(h.reshape(-1, h.shape[-1]), lm_head, st.labels.reshape(-1),
+                                                 chunk_size=chunk_size))
     return _finish(sums, streams)

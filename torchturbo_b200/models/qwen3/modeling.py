@@ -59,6 +59,17 @@ class Qwen3Model(nn.Module):
         return h.unsqueeze(0)
 
 
+class LMHead(nn.Linear):
+    """Output projection.  Called as a module (never through `.weight`) so that FSDP's forward hooks gather
+    the sharded weight; with `labels` it runs the fused projection + cross entropy and returns the loss sum."""
+
+    def forward(self, hidden, labels=None, chunk_size: int = 1024):
+        if labels is None:
+            return ops.linear(hidden, self.weight)
+        return ops.linear_cross_entropy(hidden.reshape(-1, hidden.shape[-1]), self.weight, labels.reshape(-1),
+                                        chunk_size=chunk_size)
+
+
 class Qwen3ForCausalLMBase(nn.Module):
     """Causal LM head on top of a decoder; shared by the dense and MoE model classes."""
 
@@ -71,7 +82,7 @@ class Qwen3ForCausalLMBase(nn.Module):
         if isinstance(dtype, str):
             dtype = getattr(torch, dtype.replace("torch.", ""))
         self.model = self.model_cls(config, dtype)
-        self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False, dtype=dtype)
+        self.lm_head = LMHead(config.hidden_size, config.vocab_size, bias=False, dtype=dtype)
         self.init_weights()
         self.tie_weights()
 
@@ -93,5 +104,5 @@ class Qwen3ForCausalLMBase(nn.Module):
                             cu_seq_lens_q=cu_seq_lens_q, max_length_q=max_length_q, **kwargs)
         out = CausalLMOutput(hidden_states=hidden)
         if not skip_lm_head:
-            out["logits"] = ops.linear(hidden, self.lm_head.weight)
+            out["logits"] = self.lm_head(hidden)
         return out

@@ -1,0 +1,81 @@
+"""tcgen05 variable-length flash attention as the `attention` / `attention_with_max_logits` operators."""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ... import kernels as K
+from ...runtime import TurboDevice
+from ...utils.functools import cache
+from ..base import OpImplKind
+from ..registry import register_op
+from . import native as N
+from .b200 import BF16, _B200Op, _ok
+
+
+@cache
+def _tiles_for(cu_seqlens, device):
+    t = K.build_q_tiles(cu_seqlens)
+    return t.to(device, non_blocking=True), int(cu_seqlens[-1])
+
+
+class FlashAttnFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, cu_seqlens, max_seqlen, causal, scale, want_ml):
+        tiles, n_valid = _tiles_for(cu_seqlens, q.device)
+        out, lse, ml = K.attn_fwd(q, k, v, tiles, scale=scale, causal=causal, want_max_logit=want_ml)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.meta = (cu_seqlens, max_seqlen, causal, scale, n_valid)
+        if want_ml:
+            ctx.mark_non_differentiable(ml)
+            return out, ml
+        return out
+
+    @staticmethod
+    def backward(ctx, dout, *_):
+        q, k, v, out, lse = ctx.saved_tensors
+        cu_seqlens, max_seqlen, causal, scale, n = ctx.meta
+        if hasattr(K.lib(), "ttb_attn_bwd"):
+            dq, dk, dv = K.attn_bwd(dout.contiguous(), q, k, v, out, lse, cu_seqlens, scale=scale, causal=causal)
+            return dq, dk, dv, None, None, None, None, None
+        # until the tcgen05 backward lands, the library backward consumes this kernel's out / lse
+        from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
+
+        cu = cu_seqlens.to(device=q.device, dtype=torch.int32)
+        if max_seqlen is None:
+            max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max())
+        dq, dk, dv = torch.zeros_like(q), torch.zeros_like(k), torch.zeros(k.shape, dtype=k.dtype, device=k.device)
+        _flash_attn_varlen_backward(dout.contiguous()[:n], q[:n], k[:n], v[:n].contiguous(), out[:n], lse[:, :n].contiguous(),
+                                    dq[:n], dk[:n], dv[:n], cu, cu, max_seqlen, max_seqlen, 0.0, scale, causal,
+                                    -1, -1, 0.0, None, False)
+        return dq, dk, dv, None, None, None, None, None
+
+
+def _usable(q, k, v):
+    return _ok(q, k, v) and q.shape[-1] == 128 and q.dim() == 3 and q.shape[1] % k.shape[1] == 0 and v.stride(2) == 1 \
+        and v.stride(1) == 128
+
+
+@register_op(op_name="attention", impl_name="tcgen05_varlen_attention", kind=OpImplKind.CUSTOM, priority=100,
+             devices=(TurboDevice.CUDA,))
+class B200Attention(_B200Op):
+    def __call__(self, q, k, v, cu_seqlens, max_seqlen=None, *, causal=True, scale=None):
+        if not _usable(q, k, v):
+            return N.attention_ref(q, k, v, cu_seqlens, causal, scale)
+        scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+        cu = cu_seqlens if isinstance(cu_seqlens, torch.Tensor) else torch.tensor(cu_seqlens, dtype=torch.int32)
+        return FlashAttnFn.apply(q.contiguous(), k.contiguous(), v, cu.cpu() if cu.is_cuda else cu, max_seqlen, causal,
+                                 float(scale), False)
+
+
+@register_op(op_name="attention_with_max_logits", impl_name="tcgen05_varlen_attention_max_logits",
+             kind=OpImplKind.CUSTOM, priority=100, devices=(TurboDevice.CUDA,))
+class B200AttentionWithMaxLogits(_B200Op):
+    def __call__(self, q, k, v, cu_seqlens, max_seqlen=None, *, causal=True, scale=None):
+        if not _usable(q, k, v):
+            return N.attention_ref(q, k, v, cu_seqlens, causal, scale, want_max_logits=True)
+        scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+        cu = cu_seqlens if isinstance(cu_seqlens, torch.Tensor) else torch.tensor(cu_seqlens, dtype=torch.int32)
+        return FlashAttnFn.apply(q.contiguous(), k.contiguous(), v, cu.cpu() if cu.is_cuda else cu, max_seqlen, causal,
+                                 float(scale), True)
