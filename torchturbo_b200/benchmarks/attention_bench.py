@@ -1,0 +1,39 @@
+"""Device-timed comparison of the tcgen05 varlen attention with flash-attn 2 (library baseline)."""
+from __future__ import annotations
+
+import json
+
+import torch
+
+from .. import kernels as K
+from .kernel_bench import peaks, time_fn
+
+
+def bench_attention():
+    pk = peaks()
+    rows = []
+    for T, Hq, Hk, docs in [(4096, 32, 4, [4096]), (8192, 32, 8, [8192]), (8192, 32, 8, [1000, 3000, 4192]),
+                            (65536, 5, 1, [65536])]:
+        D = 128
+        q = torch.randn(T, Hq, D, device="cuda").bfloat16()
+        k = torch.randn(T, Hk, D, device="cuda").bfloat16()
+        v = torch.randn(T, Hk, D, device="cuda").bfloat16()
+        cu = torch.tensor([0] + list(torch.tensor(docs).cumsum(0)), dtype=torch.int32)
+        tiles = K.build_q_tiles(cu).cuda()
+        fl = sum(4.0 * L * L * Hq * D / 2 for L in docs)
+        t, _ = time_fn(lambda: K.attn_fwd(q, k, v, tiles, scale=D ** -0.5, causal=True))
+        row = dict(op="attn_fwd_causal", T=T, Hq=Hq, Hk=Hk, docs=docs, ms=t, tflops=fl / t / 1e9,
+                   frac_of_peak=fl / t / 1e9 / pk["tflops"], peak_src=pk["src"])
+        try:
+            from flash_attn import flash_attn_varlen_func
+
+            cud = cu.cuda()
+            mx = max(docs)
+            t2, _ = time_fn(lambda: flash_attn_varlen_func(q, k, v, cud, cud, mx, mx, causal=True))
+            row["flash_attn2_ms"] = t2
+            row["flash_attn2_tflops"] = fl / t2 / 1e9
+        except Exception as e:  # noqa: BLE001
+            row["flash_attn2_error"] = str(e)[:80]
+        rows.append(row)
+        print(json.dumps(row), flush=True)
+    return rows

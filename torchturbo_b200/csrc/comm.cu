@@ -1,0 +1,339 @@
+// In-kernel NVLink communication for expert parallelism (and other all-to-all shaped exchanges).
+//
+// Every rank owns one symmetric buffer (peer-mapped through CUDA IPC / VMM by the host runtime) and holds a
+// table with the base address of every peer's buffer.  Kernels here move data with plain peer stores / loads
+// (no NCCL, no multicast loads) and synchronise with per-(kind, source rank) epoch flags:
+//   writer : data stores -> __threadfence_system() -> st.release.sys flag = epoch
+//   reader : ld.acquire.sys flag until it equals epoch (bounded by a time budget) -> data loads
+// A wait that exceeds its budget records {kernel, site, peer} in the status word and returns; the kernel then
+// stops touching remote memory and exits, so a missing peer can never hang the GPU.
+//
+//   ep_exchange : per-expert token counts -> every peer; then each rank derives, from the full [W, E] matrix,
+//                 (a) for its own experts: 128-row aligned segment starts, tile->expert map, rows per expert,
+//                 (b) for every global expert: the first row *this* rank may write on the owning rank.
+//   ep_scatter  : token rows (and routing probabilities) written straight into the owner's expert-major buffer.
+//   ep_gather   : k-way sum of expert output rows pulled from the owners (+ residual), token order.
+//   flag_signal / flag_wait : stream-ordered hand-offs between the kernels above and the grouped GEMMs.
+//
+// Together they replace counts all-gather + host read of split sizes + two all-to-all-v + chunk sort + unpermute of
+// the reference dispatcher (models/modules/moe/token_dispatcher.py:125-259).
+#include "common.cuh"
+
+namespace ttb {
+
+constexpr unsigned KID_COMM = 3;
+constexpr int MAX_RANKS = 16;
+constexpr int EP_ALIGN = 128;
+
+struct PeerTable {
+  unsigned long long base[MAX_RANKS];  // device-visible base address of every rank's symmetric buffer
+};
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Wait until *flag >= epoch (epochs of one channel only grow).  Returns false after `budget_ns`.
+__device__ __forceinline__ bool wait_flag(const int* flag, int epoch, unsigned long long budget_ns, unsigned site,
+                                          unsigned peer, int* status) {
+  if (ld_acquire_sys(flag) >= epoch) return true;
+  const uint64_t t0 = globaltimer_ns();
+  while (ld_acquire_sys(flag) < epoch) {
+    if (globaltimer_ns() - t0 > budget_ns) {
+      set_status(KID_COMM, site, peer);
+      if (status) atomicExch(status, static_cast<int>((site << 8) | peer | 0x10000));
+      return false;
+    }
+    __nanosleep(64);
+  }
+  return true;
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// counts exchange + layout tables.  One CTA.
+//   symmetric layout (per rank): counts_all int32 [W][E] at byte offset off_counts; flags int32 [W] at off_flags
+// ------------------------------------------------------------------------------------------------------------
+struct EpExchangeParams {
+  PeerTable peers;
+  long long off_counts, off_flags;
+  const int* counts;   // [E] local routing counts
+  int rank, W, E, epoch;
+  unsigned long long budget_ns;
+  int m_tiles_cap;
+  int* seg_start;      // [El + 1]
+  int* recv_counts;    // [El]
+  int* tile_group;     // [m_tiles_cap]
+  int* dest_base;      // [E]
+  int* status;         // [1] 0 ok, else error code (timeout or capacity overflow)
+};
+
+__global__ void ep_exchange_kernel(const EpExchangeParams p) {
+  extern __shared__ int sh[];  // [W*E] counts matrix, then [W * (El+1)] per-owner segment starts
+  const int W = p.W, E = p.E, El = E / W;
+  int* s_counts = sh;
+  int* s_seg = sh + W * E;  // s_seg[o * (El + 1) + e_l]
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  // 1. publish my counts to every peer
+  for (int i = threadIdx.x; i < W * E; i += blockDim.x) {
+    const int peer = i / E, e = i - peer * E;
+    int* dst = reinterpret_cast<int*>(p.peers.base[peer] + p.off_counts) + p.rank * E + e;
+    *dst = p.counts[e];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < W) {
+    int* f = reinterpret_cast<int*>(p.peers.base[threadIdx.x] + p.off_flags) + p.rank;
+    st_release_sys(f, p.epoch);
+  }
+  // 2. wait for every peer's counts
+  if (threadIdx.x < W) {
+    const int* f = reinterpret_cast<const int*>(p.peers.base[p.rank] + p.off_flags) + threadIdx.x;
+    if (!wait_flag(f, p.epoch, p.budget_ns, 1, threadIdx.x, p.status)) s_ok = 0;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const int* mine = reinterpret_cast<const int*>(p.peers.base[p.rank] + p.off_counts);
+  for (int i = threadIdx.x; i < W * E; i += blockDim.x) s_counts[i] = mine[i];
+  __syncthreads();
+  // 3. per-owner aligned segment starts (thread o scans owner o's local experts)
+  if (threadIdx.x < W) {
+    const int o = threadIdx.x;
+    int acc = 0;
+    for (int el = 0; el < El; ++el) {
+      s_seg[o * (El + 1) + el] = acc;
+      int tot = 0;
+      for (int s = 0; s < W; ++s) tot += s_counts[s * E + o * El + el];
+      acc += ((tot + EP_ALIGN - 1) / EP_ALIGN) * EP_ALIGN;
+    }
+    s_seg[o * (El + 1) + El] = acc;
+    if (o == p.rank && acc > p.m_tiles_cap * EP_ALIGN) atomicExch(p.status, 2);  // receive capacity exceeded
+  }
+  __syncthreads();
+  // 4. tables
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int o = e / El, el = e - o * El;
+    int before = 0;
+    for (int s = 0; s < p.rank; ++s) before += s_counts[s * E + e];
+    p.dest_base[e] = s_seg[o * (El + 1) + el] + before;
+  }
+  const int* my_seg = s_seg + p.rank * (El + 1);
+  for (int el = threadIdx.x; el <= El; el += blockDim.x) {
+    p.seg_start[el] = my_seg[el];
+    if (el < El) {
+      int tot = 0;
+      for (int s = 0; s < W; ++s) tot += s_counts[s * E + p.rank * El + el];
+      p.recv_counts[el] = tot;
+    }
+  }
+  for (int m = threadIdx.x; m < p.m_tiles_cap; m += blockDim.x) {
+    const int row = m * EP_ALIGN;
+    int g = -1;
+    if (row < my_seg[El]) {
+      int lo = 0, hi = El;
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (my_seg[mid] <= row) lo = mid; else hi = mid;
+      }
+      g = lo;
+    }
+    p.tile_group[m] = g;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// scatter: dst_rank = expert / El, dst_row = dest_row[n].  One warp per (token, slot) entry.
+// The last block to finish publishes flag[kind][rank] = epoch on every peer.
+// ------------------------------------------------------------------------------------------------------------
+struct EpScatterParams {
+  PeerTable peers;
+  long long off_rows, off_vals, off_flags;  // byte offsets inside the symmetric buffer
+  const __nv_bfloat16* src;  // [T, lds]
+  long long lds;
+  const int* expert;         // [N] global expert id
+  const int* dest_row;       // [N]
+  const float* val;          // [N] or null
+  long long N;
+  int k, H, El, rank, W, epoch;
+  long long cap_rows;
+  unsigned int* done_counter;  // local, zeroed by the launcher
+  int* status;
+};
+
+__global__ void ep_scatter_kernel(const EpScatterParams p) {
+  const int lane = threadIdx.x & 31;
+  const long long warps_per_grid = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long n = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; n < p.N; n += warps_per_grid) {
+    const int e = p.expert[n];
+    const int o = e / p.El;
+    const long long r = p.dest_row[n];
+    if (r < 0 || r >= p.cap_rows || o < 0 || o >= p.W) {  // never write outside the peer's buffer
+      if (lane == 0) atomicExch(p.status, 3);
+      continue;
+    }
+    const uint4* s = reinterpret_cast<const uint4*>(p.src + (n / p.k) * p.lds);
+    uint4* d = reinterpret_cast<uint4*>(p.peers.base[o] + p.off_rows) + r * (p.H / 8);
+    for (int c = lane; c < p.H / 8; c += 32) d[c] = s[c];
+    if (p.val && lane == 0) reinterpret_cast<float*>(p.peers.base[o] + p.off_vals)[r] = p.val[n];
+  }
+  __threadfence_system();
+  __syncthreads();
+  __shared__ bool last;
+  if (threadIdx.x == 0) last = (atomicAdd(p.done_counter, 1u) == gridDim.x - 1);
+  __syncthreads();
+  if (last) {
+    __threadfence_system();
+    if (threadIdx.x < p.W) {
+      int* f = reinterpret_cast<int*>(p.peers.base[threadIdx.x] + p.off_flags) + p.rank;
+      st_release_sys(f, p.epoch);
+    }
+    if (threadIdx.x == 0) *p.done_counter = 0;
+  }
+}
+
+// flag[kind][rank] = epoch on every peer (stream-ordered "my buffer is ready" hand-off)
+__global__ void flag_signal_kernel(PeerTable peers, long long off_flags, int rank, int W, int epoch) {
+  __threadfence_system();
+  if (threadIdx.x < W) st_release_sys(reinterpret_cast<int*>(peers.base[threadIdx.x] + off_flags) + rank, epoch);
+}
+
+// wait until my flag[kind][s] == epoch for every s
+__global__ void flag_wait_kernel(PeerTable peers, long long off_flags, int rank, int W, int epoch,
+                                 unsigned long long budget_ns, int* status) {
+  if (threadIdx.x < W)
+    wait_flag(reinterpret_cast<const int*>(peers.base[rank] + off_flags) + threadIdx.x, epoch, budget_ns, 2, threadIdx.x,
+              status);
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// gather: out[t] = sum_j w[t,j] * rows_of(owner(n))[dest_row[n]]  (+ residual[t]).  One block per token.
+// ------------------------------------------------------------------------------------------------------------
+struct EpGatherParams {
+  PeerTable peers;
+  long long off_rows;
+  const int* expert;    // [T*k]
+  const int* dest_row;  // [T*k]
+  const float* w;       // [T*k] or null
+  const __nv_bfloat16* residual;
+  long long ldr;
+  __nv_bfloat16* out;
+  long long ldo;
+  int k, H, El, W;
+  long long cap_rows;
+  const int* status;    // skip remote reads when a wait already failed
+};
+
+__global__ void ep_gather_kernel(const EpGatherParams p) {
+  const long long t = blockIdx.x;
+  const bool healthy = (p.status == nullptr) || (*p.status == 0);
+  for (int c = threadIdx.x * 8; c < p.H; c += blockDim.x * 8) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (healthy) {
+      for (int j = 0; j < p.k; ++j) {
+        const long long n = t * p.k + j;
+        const int o = p.expert[n] / p.El;
+        const long long r = p.dest_row[n];
+        if (r < 0 || r >= p.cap_rows || o < 0 || o >= p.W) continue;
+        const float wt = p.w ? p.w[n] : 1.f;
+        const uint4 u = *reinterpret_cast<const uint4*>(
+            reinterpret_cast<const __nv_bfloat16*>(p.peers.base[o] + p.off_rows) + r * p.H + c);
+        float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), cc = unpack_bf16(u.z), d = unpack_bf16(u.w);
+        acc[0] += wt * a.x; acc[1] += wt * a.y; acc[2] += wt * b.x; acc[3] += wt * b.y;
+        acc[4] += wt * cc.x; acc[5] += wt * cc.y; acc[6] += wt * d.x; acc[7] += wt * d.y;
+      }
+    }
+    if (p.residual) {
+      const uint4 u = *reinterpret_cast<const uint4*>(p.residual + t * p.ldr + c);
+      float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), cc = unpack_bf16(u.z), d = unpack_bf16(u.w);
+      acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += cc.x; acc[5] += cc.y; acc[6] += d.x; acc[7] += d.y;
+    }
+    uint4 o4;
+    o4.x = pack_bf16(acc[0], acc[1]); o4.y = pack_bf16(acc[2], acc[3]);
+    o4.z = pack_bf16(acc[4], acc[5]); o4.w = pack_bf16(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(p.out + t * p.ldo + c) = o4;
+  }
+}
+
+}  // namespace ttb
+
+using namespace ttb;
+#define STREAM(s) reinterpret_cast<cudaStream_t>(s)
+#define LAUNCH_RET() do { cudaError_t e__ = cudaGetLastError(); return e__ == cudaSuccess ? 0 : 400 + (int)e__; } while (0)
+
+static PeerTable make_peers(const unsigned long long* ptrs, int W) {
+  PeerTable t;
+  for (int i = 0; i < MAX_RANKS; ++i) t.base[i] = i < W ? ptrs[i] : 0ull;
+  return t;
+}
+
+TTB_EXPORT int ttb_ep_exchange(const unsigned long long* peer_ptrs, long long off_counts, long long off_flags,
+                               const int* counts, int rank, int W, int E, int epoch, long long budget_ms,
+                               int m_tiles_cap, int* seg_start, int* recv_counts, int* tile_group, int* dest_base,
+                               int* status, void* stream) {
+  if (W > MAX_RANKS || E % W || W < 1) return 901;
+  const int El = E / W;
+  const size_t sh = static_cast<size_t>(W) * E * 4 + static_cast<size_t>(W) * (El + 1) * 4;
+  if (sh > 48 * 1024) return 902;
+  EpExchangeParams p{make_peers(peer_ptrs, W), off_counts, off_flags, counts, rank, W, E, epoch,
+                     static_cast<unsigned long long>(budget_ms) * 1000000ull, m_tiles_cap, seg_start, recv_counts,
+                     tile_group, dest_base, status};
+  ep_exchange_kernel<<<1, 256, sh, STREAM(stream)>>>(p);
+  LAUNCH_RET();
+}
+
+TTB_EXPORT int ttb_ep_scatter(const unsigned long long* peer_ptrs, long long off_rows, long long off_vals,
+                              long long off_flags, const void* src, long long lds, const int* expert,
+                              const int* dest_row, const float* val, long long N, int k, int H, int El, int rank,
+                              int W, int epoch, long long cap_rows, unsigned int* done_counter, int* status, int grid,
+                              void* stream) {
+  if (W > MAX_RANKS || H % 8 || lds % 8) return 901;
+  EpScatterParams p{make_peers(peer_ptrs, W), off_rows, off_vals, off_flags, (const __nv_bfloat16*)src, lds, expert,
+                    dest_row, val, N, k, H, El, rank, W, epoch, cap_rows, done_counter, status};
+  if (grid < 1) grid = 1;
+  ep_scatter_kernel<<<grid, 256, 0, STREAM(stream)>>>(p);
+  LAUNCH_RET();
+}
+
+TTB_EXPORT int ttb_flag_signal(const unsigned long long* peer_ptrs, long long off_flags, int rank, int W, int epoch,
+                               void* stream) {
+  if (W > MAX_RANKS) return 901;
+  flag_signal_kernel<<<1, 32, 0, STREAM(stream)>>>(make_peers(peer_ptrs, W), off_flags, rank, W, epoch);
+  LAUNCH_RET();
+}
+
+TTB_EXPORT int ttb_flag_wait(const unsigned long long* peer_ptrs, long long off_flags, int rank, int W, int epoch,
+                             long long budget_ms, int* status, void* stream) {
+  if (W > MAX_RANKS) return 901;
+  flag_wait_kernel<<<1, 32, 0, STREAM(stream)>>>(make_peers(peer_ptrs, W), off_flags, rank, W, epoch,
+                                                 static_cast<unsigned long long>(budget_ms) * 1000000ull, status);
+  LAUNCH_RET();
+}
+
+TTB_EXPORT int ttb_ep_gather(const unsigned long long* peer_ptrs, long long off_rows, const int* expert,
+                             const int* dest_row, const float* w, const void* residual, long long ldr, void* out,
+                             long long ldo, long long T, int k, int H, int El, int W, long long cap_rows,
+                             const int* status, void* stream) {
+  if (W > MAX_RANKS || H % 8 || ldo % 8) return 901;
+  if (T == 0) return 0;
+  EpGatherParams p{make_peers(peer_ptrs, W), off_rows, expert, dest_row, w, (const __nv_bfloat16*)residual, ldr,
+                   (__nv_bfloat16*)out, ldo, k, H, El, W, cap_rows, status};
+  int threads = H / 8;
+  threads = threads > 256 ? 256 : ((threads + 31) / 32) * 32;
+  ep_gather_kernel<<<(unsigned)T, threads, 0, STREAM(stream)>>>(p);
+  LAUNCH_RET();
+}
+
+TTB_EXPORT int ttb_comm_status(unsigned int* out4, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(out4, ttb::g_status_word, sizeof(unsigned int) * 4);
+  if (e != cudaSuccess) return (int)e;
+  if (reset) {
+    unsigned int z[4] = {0, 0, 0, 0};
+    e = cudaMemcpyToSymbol(ttb::g_status_word, z, sizeof(z));
+  }
+  return (int)e;
+}
