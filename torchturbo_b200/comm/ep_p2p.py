@@ -1,0 +1,189 @@
+"""Expert-parallel token dispatch / combine over peer memory (NVLink), without NCCL and without host reads.
+
+Forward of one MoE layer on every rank (all stream-ordered, nothing waits on the host):
+    counts exchange kernel      : my per-expert counts -> every peer; tables for my experts and my send offsets
+    rank kernel                 : destination row of each of my (token, slot) entries on its owner
+    scatter kernel              : token rows + routing probabilities written into the owners' expert-major buffers,
+                                  then "rows landed" flags
+    wait kernel                 : all sources have delivered
+    grouped GEMMs               : fc1 (SwiGLU x prob epilogue), fc2 -> symmetric output buffer, then "output ready" flags
+    wait + gather kernel        : every source pulls its rows from the owners and sums its k expert outputs
+Backward mirrors this: d(out) rows are scattered to the owners, d(x) rows and d(prob) scalars are pulled back.
+
+Buffers are shared by all MoE layers of a model.  Reuse is safe because every rank waits on every other rank once
+per layer in each direction: a rank that starts writing layer L+1 data has observed the owners' layer-L
+"output ready" flags, which they raise after they stopped reading their receive buffers.
+
+Receive capacity is `capacity_factor` x the balanced share (rows are never dropped silently: an overflow sets the
+workspace status, which `check()` turns into an exception).
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+import torch.distributed as dist
+
+from .. import kernels as K
+from ..ops import MoEPermutation, ops
+from .symm import SymmetricBuffer
+
+_WORKSPACES: dict[tuple, "EPWorkspace"] = {}
+
+
+class EPWorkspace:
+    def __init__(self, group, hidden: int, num_experts: int, tokens: int, topk: int, capacity_factor: float):
+        self.group = group
+        self.W, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.E, self.El, self.H = num_experts, num_experts // self.W, hidden
+        rows = int(tokens * topk * capacity_factor)
+        self.m_tiles_cap = (rows + K.SEG_ALIGN - 1) // K.SEG_ALIGN + self.El
+        self.cap = self.m_tiles_cap * K.SEG_ALIGN
+        nbytes = 4 * self.W * self.E + 2 * self.cap * hidden * 2 + 2 * self.cap * 4 + 8 * 4 * self.W + 16 * 256
+        self.buf = SymmetricBuffer(nbytes, group)
+        self.off_counts, self.counts_all = self.buf.carve(4 * self.W * self.E, torch.int32)
+        self.off_recv, self.recv_rows = self.buf.carve(self.cap * hidden * 2, torch.bfloat16, (self.cap, hidden))
+        self.off_recv_vals, self.recv_vals = self.buf.carve(self.cap * 4, torch.float32)
+        self.off_y, self.y_rows = self.buf.carve(self.cap * hidden * 2, torch.bfloat16, (self.cap, hidden))
+        self.off_y_vals, self.y_vals = self.buf.carve(self.cap * 4, torch.float32)
+        self.ch_counts, self.ch_rows, self.ch_ready = self.buf.channel(), self.buf.channel(), self.buf.channel()
+        dev = self.buf.local.device
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.done = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.budget_ms = int(os.environ.get("TORCHTURBO_P2P_WAIT_MS", "20000"))
+        self.ptrs = self.buf.peer_ptrs
+
+    # -- primitives ---------------------------------------------------------------------------------
+    def exchange(self, counts):
+        return K.ep_exchange(self.ptrs, self.off_counts, self.ch_counts.offset, counts, self.rank, self.W, self.E,
+                             self.ch_counts.next(), self.budget_ms, self.m_tiles_cap, self.status)
+
+    def scatter_rows(self, src, expert, dest_row, vals, k):
+        """Rows (and optional scalars) -> owners' receive buffers; returns after every source's rows have landed here."""
+        epoch = self.ch_rows.next()
+        K.ep_scatter(self.ptrs, self.off_recv, self.off_recv_vals, self.ch_rows.offset, src, expert, dest_row, vals, k,
+                     self.El, self.rank, self.W, epoch, self.cap, self.done, self.status)
+        K.flag_wait(self.ptrs, self.ch_rows.offset, self.rank, self.W, epoch, self.budget_ms, self.status)
+
+    def publish_and_wait_ready(self):
+        epoch = self.ch_ready.next()
+        K.flag_signal(self.ptrs, self.ch_ready.offset, self.rank, self.W, epoch)
+        K.flag_wait(self.ptrs, self.ch_ready.offset, self.rank, self.W, epoch, self.budget_ms, self.status)
+
+    def gather_rows(self, expert, dest_row, T, k, residual=None):
+        return K.ep_gather(self.ptrs, self.off_y, expert, dest_row, T, k, self.H, self.El, self.W, self.cap, self.status,
+                           residual=residual)
+
+    def gather_vals(self, expert, dest_row):
+        return K.ep_gather_vals(self.ptrs, self.off_y_vals, expert, dest_row, self.El, self.W, self.cap, self.status)
+
+    def check(self) -> None:
+        code = int(self.status.item())
+        if code:
+            what = "receive capacity exceeded (raise capacity_factor)" if code == 2 else \
+                "row index outside the receive buffer" if code == 3 else f"peer wait timed out (code {code:#x})"
+            raise RuntimeError(f"expert-parallel exchange failed on rank {self.rank}: {what}")
+
+
+def get_workspace(group, hidden, num_experts, tokens, topk, capacity_factor=2.0) -> EPWorkspace:
+    key = (id(group), hidden, num_experts, topk)
+    ws = _WORKSPACES.get(key)
+    need = int(tokens * topk * capacity_factor)
+    if ws is None or ws.cap < need:
+        ws = EPWorkspace(group, hidden, num_experts, tokens, topk, capacity_factor)
+        _WORKSPACES[key] = ws
+    return ws
+
+
+class _Dispatch(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, prob, idx, counts, ws: EPWorkspace):
+        T, k = idx.shape
+        seg_start, recv_counts, tile_group, dest_base = ws.exchange(counts)
+        expert = idx.reshape(-1).contiguous()
+        dest_row = K.perm_rank(expert, ws.E, dest_base)
+        K.perm_zero_pad(ws.recv_rows, recv_counts, seg_start, ws.recv_vals)
+        ws.scatter_rows(x, expert, dest_row, prob.reshape(-1).contiguous(), k)
+        xp, rp = ws.recv_rows.clone(), ws.recv_vals.clone()
+        ctx.ws, ctx.dims = ws, (T, k)
+        ctx.save_for_backward(expert, dest_row)
+        for t in (seg_start, recv_counts, tile_group, dest_row, expert):
+            ctx.mark_non_differentiable(t)
+        return xp, rp, seg_start, recv_counts, tile_group, dest_row, expert
+
+    @staticmethod
+    def backward(ctx, dxp, drp, *_):
+        ws, (T, k) = ctx.ws, ctx.dims
+        expert, dest_row = ctx.saved_tensors
+        ws.y_rows.copy_(dxp)
+        if drp is not None:
+            ws.y_vals.copy_(drp)
+        else:
+            ws.y_vals.zero_()
+        ws.publish_and_wait_ready()
+        dx = ws.gather_rows(expert, dest_row, T, k)
+        dprob = ws.gather_vals(expert, dest_row).view(T, k)
+        return dx, dprob, None, None, None
+
+
+class _Combine(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y, expert, dest_row, seg_start, recv_counts, ws: EPWorkspace, T, k, residual):
+        ws.y_rows.copy_(y)
+        ws.publish_and_wait_ready()
+        out = ws.gather_rows(expert, dest_row, T, k, residual=residual)
+        ctx.ws, ctx.dims = ws, (T, k, residual is not None)
+        ctx.save_for_backward(expert, dest_row, seg_start, recv_counts)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        ws, (T, k, has_res) = ctx.ws, ctx.dims
+        expert, dest_row, seg_start, recv_counts = ctx.saved_tensors
+        dout = dout.contiguous()
+        K.perm_zero_pad(ws.recv_rows, recv_counts, seg_start, None)
+        ws.scatter_rows(dout, expert, dest_row, None, k)
+        dy = ws.recv_rows.clone()
+        return dy, None, None, None, None, None, None, None, (dout if has_res else None)
+
+
+class P2PTokenDispatcher:
+    """Drop-in replacement of the all-to-all dispatcher of `MoELayer` for bf16 CUDA tensors on one NVLink domain."""
+
+    def __init__(self, config, ep_group, num_local_experts: int, capacity_factor: float | None = None):
+        self.config, self.ep_group = config, ep_group
+        self.ep_size = dist.get_world_size(ep_group)
+        self.num_local_experts = num_local_experts
+        self.capacity_factor = capacity_factor or float(os.environ.get("TORCHTURBO_EP_CAPACITY_FACTOR", "2.0"))
+        self._fallback = None
+
+    @staticmethod
+    def usable(ep_group) -> bool:
+        return K.available() and SymmetricBuffer.usable(ep_group) and dist.get_world_size(ep_group) > 1
+
+    def _nccl(self):
+        if self._fallback is None:
+            from ..models.modules.moe.moe import MoEAlltoAllTokenDispatcher
+
+            self._fallback = MoEAlltoAllTokenDispatcher(self.config, self.ep_group, self.num_local_experts)
+        return self._fallback
+
+    def dispatch(self, x, idx, prob):
+        if not (x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0):
+            return self._nccl().dispatch(x, idx, prob)
+        T, k = idx.shape
+        E = self.config.num_moe_experts
+        ws = get_workspace(self.ep_group, x.shape[-1], E, T, k, self.capacity_factor)
+        idx32 = idx.to(torch.int32).contiguous()
+        counts = torch.bincount(idx32.reshape(-1), minlength=E).to(torch.int32)
+        xp, rp, seg_start, recv_counts, tile_group, dest_row, expert = _Dispatch.apply(
+            x.contiguous(), prob.float().contiguous(), idx32, counts, ws)
+        perm = MoEPermutation(tokens=xp, probs=rp, row_indices=dest_row.view(T, k), expert_indices=idx.long(),
+                              counts=recv_counts, seg_start=seg_start, tile_group=tile_group)
+        return perm, recv_counts, ("p2p", ws, expert, dest_row, seg_start, recv_counts, T, k)
+
+    def combine(self, y, state, residual=None):
+        if state[0] != "p2p":
+            return self._nccl().combine(y, state)
+        _, ws, expert, dest_row, seg_start, recv_counts, T, k = state
+        return _Combine.apply(y, expert, dest_row, seg_start, recv_counts, ws, T, k, residual)

@@ -337,3 +337,31 @@ TTB_EXPORT int ttb_comm_status(unsigned int* out4, int reset) {
   }
   return (int)e;
 }
+
+namespace ttb {
+// out[n] = vals_of(owner(n))[dest_row[n]] : scalar pull used for the routing-probability gradient
+__global__ void ep_gather_vals_kernel(PeerTable peers, long long off_vals, const int* __restrict__ expert,
+                                      const int* __restrict__ dest_row, float* __restrict__ out, long long N, int El,
+                                      int W, long long cap_rows, const int* status) {
+  const long long n = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  float v = 0.f;
+  if (status == nullptr || *status == 0) {
+    const int o = expert[n] / El;
+    const long long r = dest_row[n];
+    if (r >= 0 && r < cap_rows && o >= 0 && o < W) v = reinterpret_cast<const float*>(peers.base[o] + off_vals)[r];
+  }
+  out[n] = v;
+}
+}  // namespace ttb
+
+TTB_EXPORT int ttb_ep_gather_vals(const unsigned long long* peer_ptrs, long long off_vals, const int* expert,
+                                  const int* dest_row, float* out, long long N, int El, int W, long long cap_rows,
+                                  const int* status, void* stream) {
+  if (W > MAX_RANKS) return 901;
+  if (N == 0) return 0;
+  ttb::ep_gather_vals_kernel<<<(unsigned)((N + 255) / 256), 256, 0, STREAM(stream)>>>(make_peers(peer_ptrs, W), off_vals,
+                                                                                     expert, dest_row, out, N, El, W,
+                                                                                     cap_rows, status);
+  LAUNCH_RET();
+}

@@ -424,9 +424,18 @@ struct AdamMeta {
 };
 constexpr int ADAM_CHUNK = 65536;
 
-__global__ void adamw_kernel(const AdamMeta* __restrict__ meta, const int2* __restrict__ chunks, float lr, float beta1,
-                             float beta2, float eps, float weight_decay, float bc1, float bc2_sqrt,
-                             const float* __restrict__ clip_coef, float grad_prescale) {
+__device__ __forceinline__ void adamw_one(float& p, float g, float& m, float& v, float lr, float beta1, float beta2,
+                                          float eps, float decay, float step_size, float bc2_sqrt) {
+  p *= decay;
+  m = m + (1.f - beta1) * (g - m);
+  v = beta2 * v + (1.f - beta2) * g * g;
+  p -= step_size * m / (sqrtf(v) / bc2_sqrt + eps);
+}
+
+__global__ void __launch_bounds__(256)
+adamw_kernel(const AdamMeta* __restrict__ meta, const int2* __restrict__ chunks, float lr, float beta1, float beta2,
+             float eps, float weight_decay, float bc1, float bc2_sqrt, const float* __restrict__ clip_coef,
+             float grad_prescale) {
   const int2 ch = chunks[blockIdx.x];
   const AdamMeta t = meta[ch.x];
   const long long start = static_cast<long long>(ch.y) * ADAM_CHUNK;
@@ -439,24 +448,52 @@ __global__ void adamw_kernel(const AdamMeta* __restrict__ meta, const int2* __re
     coef *= c;
   }
   const float step_size = lr / bc1;
-  for (long long i = start + threadIdx.x; i < end; i += blockDim.x) {
+  const float decay = 1.f - lr * weight_decay;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(t.p) | reinterpret_cast<uintptr_t>(t.m) |
+                         reinterpret_cast<uintptr_t>(t.v) | reinterpret_cast<uintptr_t>(t.g) |
+                         reinterpret_cast<uintptr_t>(t.shadow)) & 15) == 0;
+  const long long n4 = aligned ? ((end - start) / 4) : 0;
+  for (long long q = threadIdx.x; q < n4; q += blockDim.x) {
+    const long long i = start + q * 4;
+    float4 p = *reinterpret_cast<const float4*>(t.p + i);
+    float4 m = *reinterpret_cast<const float4*>(t.m + i);
+    float4 v = *reinterpret_cast<const float4*>(t.v + i);
+    float g[4];
+    if (t.g_is_bf16) {
+      const uint2 u = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(t.g) + i);
+      const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y);
+      g[0] = a.x; g[1] = a.y; g[2] = b.x; g[3] = b.y;
+    } else {
+      const float4 u = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(t.g) + i);
+      g[0] = u.x; g[1] = u.y; g[2] = u.z; g[3] = u.w;
+    }
+    adamw_one(p.x, g[0] * coef, m.x, v.x, lr, beta1, beta2, eps, decay, step_size, bc2_sqrt);
+    adamw_one(p.y, g[1] * coef, m.y, v.y, lr, beta1, beta2, eps, decay, step_size, bc2_sqrt);
+    adamw_one(p.z, g[2] * coef, m.z, v.z, lr, beta1, beta2, eps, decay, step_size, bc2_sqrt);
+    adamw_one(p.w, g[3] * coef, m.w, v.w, lr, beta1, beta2, eps, decay, step_size, bc2_sqrt);
+    *reinterpret_cast<float4*>(t.p + i) = p;
+    *reinterpret_cast<float4*>(t.m + i) = m;
+    *reinterpret_cast<float4*>(t.v + i) = v;
+    if (t.shadow) {
+      uint2 o;
+      o.x = pack_bf16(p.x, p.y); o.y = pack_bf16(p.z, p.w);
+      *reinterpret_cast<uint2*>(t.shadow + i) = o;
+    }
+  }
+  for (long long i = start + n4 * 4 + threadIdx.x; i < end; i += blockDim.x) {
     float g = t.g_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(t.g)[i])
                           : reinterpret_cast<const float*>(t.g)[i];
-    g *= coef;
-    float p = t.p[i];
-    p *= (1.f - lr * weight_decay);
-    float m = t.m[i] + (1.f - beta1) * (g - t.m[i]);
-    float v = beta2 * t.v[i] + (1.f - beta2) * g * g;
-    float denom = sqrtf(v) / bc2_sqrt + eps;
-    p -= step_size * m / denom;
+    float p = t.p[i], m = t.m[i], v = t.v[i];
+    adamw_one(p, g * coef, m, v, lr, beta1, beta2, eps, decay, step_size, bc2_sqrt);
     t.p[i] = p; t.m[i] = m; t.v[i] = v;
     if (t.shadow) t.shadow[i] = __float2bfloat16(p);
   }
 }
 
 // Squared-norm partials: partial[blockIdx.x] = sum over the chunk of g^2 (fp32).
-__global__ void sqnorm_kernel(const AdamMeta* __restrict__ meta, const int2* __restrict__ chunks,
-                              float* __restrict__ partial, float prescale) {
+__global__ void __launch_bounds__(256)
+sqnorm_kernel(const AdamMeta* __restrict__ meta, const int2* __restrict__ chunks, float* __restrict__ partial,
+              float prescale) {
   __shared__ float red[32];
   const int2 ch = chunks[blockIdx.x];
   const AdamMeta t = meta[ch.x];
@@ -464,13 +501,19 @@ __global__ void sqnorm_kernel(const AdamMeta* __restrict__ meta, const int2* __r
   long long end = start + ADAM_CHUNK;
   if (end > t.numel) end = t.numel;
   float s = 0.f;
-  for (long long i = start + threadIdx.x; i < end; i += blockDim.x) {
+  const bool aligned = (reinterpret_cast<uintptr_t>(t.g) & 15) == 0;
+  const long long n8 = (aligned && t.g_is_bf16) ? ((end - start) / 8) : 0;
+  for (long long q = threadIdx.x; q < n8; q += blockDim.x) {
+    const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(t.g) + start + q * 8);
+    const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+    s += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y + c.x * c.x + c.y * c.y + d.x * d.x + d.y * d.y;
+  }
+  for (long long i = start + n8 * 8 + threadIdx.x; i < end; i += blockDim.x) {
     float g = t.g_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(t.g)[i])
                           : reinterpret_cast<const float*>(t.g)[i];
-    g *= prescale;
     s += g * g;
   }
-  s = block_sum(s, red);
+  s = block_sum(s, red) * prescale * prescale;
   if (threadIdx.x == 0) partial[blockIdx.x] = s;
 }
 

@@ -559,3 +559,17 @@ TTB_EXPORT int ttb_perm_combine(const void* src, long long lds, const int* row_o
 }
 
 TTB_EXPORT int ttb_moe_seg_align() { return SEG_ALIGN; }
+
+// row_of[n] = base[idx[n]] + stable rank of n among the entries of its expert (base need not be a scan of counts)
+TTB_EXPORT int ttb_perm_rank(const int* idx, long long N, int E, const int* base, int* row_of, void* stream) {
+  if (N == 0) return 0;
+  perm_rank_kernel<<<E, 256, 0, STREAM(stream)>>>(idx, N, base, row_of);
+  LAUNCH_RET();
+}
+
+TTB_EXPORT int ttb_perm_zero_pad(void* dst, long long ldd, const int* counts, const int* seg_start, float* row_val,
+                                 int E, int H, void* stream) {
+  if (H % 8 || ldd % 8) return 901;
+  perm_zero_pad_kernel<<<E, 256, 0, STREAM(stream)>>>((__nv_bfloat16*)dst, ldd, counts, seg_start, row_val, H);
+  LAUNCH_RET();
+}

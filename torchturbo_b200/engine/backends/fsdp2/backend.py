@@ -516,16 +516,30 @@ class FSDP2Backend(BaseBackend):
         With the fused AdamW the coefficient is handed to the optimizer as a device scalar and applied inside
         the update kernel instead of in a separate pass."""
         self._scale_moe_gradient(model)
+        from ...optimizers import FusedAdamW, OptimizersContainer
+
+        opts = list(optimizer) if isinstance(optimizer, OptimizersContainer) else ([optimizer] if optimizer is not None else [])
+        dev = self.device
+        sums = {"dense": torch.zeros((), dtype=torch.float32, device=dev), "moe": torch.zeros((), dtype=torch.float32, device=dev),
+                "local": torch.zeros((), dtype=torch.float32, device=dev)}
+        covered: set[int] = set()
+        for o in opts:  # fused path: one multi-tensor launch per parameter group, no per-tensor norms
+            if isinstance(o, FusedAdamW) and getattr(o, "_tt_topology", None) in sums:
+                s_ = o.grad_sq_sum()
+                if s_ is not None:
+                    sums[o._tt_topology] = sums[o._tt_topology] + s_
+                    covered.update(id(p) for grp in o.param_groups for p in grp["params"])
         sq = {"dense": [], "moe": [], "local": []}
         eids = self.expert_param_ids
         for p in model.parameters():
+            if id(p) in covered:
+                continue
             g = getattr(p, "main_grad", None)
             g = g if g is not None else p.grad
             if g is None:
                 continue
             lg = g._local_tensor if hasattr(g, "_local_tensor") else g
             sq[self._topology_of(p, eids)].append(lg)
-        dev = self.device
 
         def sumsq(ts):
             if not ts:
@@ -533,16 +547,14 @@ class FSDP2Backend(BaseBackend):
             norms = torch._foreach_norm(ts, 2.0)
             return torch.stack([n.float() for n in norms]).pow(2).sum()
 
-        dense, moe, local = sumsq(sq["dense"]), sumsq(sq["moe"]), sumsq(sq["local"])
+        dense, moe, local = (sums["dense"] + sumsq(sq["dense"]), sums["moe"] + sumsq(sq["moe"]),
+                             sums["local"] + sumsq(sq["local"]))
         sharded = dense + moe
         if self.world_size > 1:
             # FSDP shards and EP-local experts are disjoint across the world; replicated ones are not summed
             dist.all_reduce(sharded)
         total = (sharded + local).sqrt()
         coef = (max_norm / (total + 1e-6)).clamp(max=1.0) if max_norm and max_norm > 0 else torch.ones_like(total)
-        from ...optimizers import FusedAdamW, OptimizersContainer
-
-        opts = list(optimizer) if isinstance(optimizer, OptimizersContainer) else ([optimizer] if optimizer is not None else [])
         fused_ids: set[int] = set()
         for o in opts:
             if isinstance(o, FusedAdamW):

@@ -72,7 +72,24 @@ class FusedAdamW(torch.optim.Optimizer):
                 self._step_torch(group, ps, states, step, clip)
         return loss
 
-    def _step_cuda(self, gi, group, ps, states, step, clip):
+    @torch.no_grad()
+    def grad_sq_sum(self) -> torch.Tensor | None:
+        """Sum of squared gradients over every parameter of this optimizer as a device scalar, computed by the
+        multi-tensor kernel on the same tables the update uses (CUDA only; `None` elsewhere)."""
+        total = None
+        for gi, group in enumerate(self.param_groups):
+            ps = [p for p in group["params"] if self.grad_of(p) is not None]
+            if not ps:
+                continue
+            if not (_local(ps[0]).is_cuda and K.available()):
+                return None
+            states = [self._init_state(p) for p in ps]
+            plan = self._plan_for(gi, ps, states)
+            s = K.grad_sqnorm_partials(plan).sum()
+            total = s if total is None else total + s
+        return total
+
+    def _plan_for(self, gi, ps, states):
         key = tuple(id(p) for p in ps)
         cached = self._plans.get(gi)
         if cached is None or cached[0] != key:
@@ -91,10 +108,19 @@ class FusedAdamW(torch.optim.Optimizer):
         for p in ps:
             g = _local(self.grad_of(p))
             grads.append(g if g.is_contiguous() else g.contiguous())
-        plan.refresh_grads(grads)
+        gkey = tuple(g.data_ptr() for g in grads)
+        if getattr(plan, "_gkey", None) != gkey:
+            plan.refresh_grads(grads)
+            plan._gkey = gkey
+            plan._grads = grads  # keep contiguous copies alive until the kernels have consumed them
+        return plan
+
+    def _step_cuda(self, gi, group, ps, states, step, clip):
+        plan = self._plan_for(gi, ps, states)
         b1, b2 = group["betas"]
         K.adamw_step(plan, lr=group["lr"], beta1=b1, beta2=b2, eps=group["eps"], weight_decay=group["weight_decay"],
                      step=step, clip=clip)
+        plan._gkey = None
 
     def _step_torch(self, group, ps, states, step, clip):
         b1, b2 = group["betas"]

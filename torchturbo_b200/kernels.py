@@ -500,3 +500,80 @@ def attn_fwd(q, k, v, q_tiles_dev, *, scale: float, causal: bool = True, want_ls
                               C.c_int(q_tiles_dev.shape[0]), C.c_longlong(T), C.c_int(Hq), C.c_int(Hk), C.c_int(D),
                               C.c_float(scale), C.c_int(int(causal)), _stream()), "ttb_attn_fwd")
     return out, lse, ml
+
+
+# --------------------------------------------------------------------------------------
+# Expert-parallel exchange over peer memory (see csrc/comm.cu)
+# --------------------------------------------------------------------------------------
+def comm_status(reset: bool = False) -> tuple[int, int]:
+    buf = (C.c_uint * 4)()
+    _check(lib().ttb_comm_status(buf, C.c_int(1 if reset else 0)), "ttb_gemm_status")
+    return int(buf[0]), int(buf[1])
+
+
+def perm_rank(idx: torch.Tensor, num_experts: int, base: torch.Tensor) -> torch.Tensor:
+    flat = idx.reshape(-1)
+    row_of = torch.empty_like(flat)
+    _check(lib().ttb_perm_rank(_p(flat), C.c_longlong(flat.numel()), C.c_int(num_experts), _p(base), _p(row_of), _stream()),
+           "ttb_perm_rank")
+    return row_of
+
+
+def perm_zero_pad(dst, counts, seg_start, row_val=None):
+    _check(lib().ttb_perm_zero_pad(_p(dst), C.c_longlong(dst.stride(0)), _p(counts), _p(seg_start), _p(row_val),
+                                   C.c_int(counts.numel()), C.c_int(dst.shape[1]), _stream()), "ttb_perm_zero_pad")
+
+
+def ep_exchange(peer_ptrs, off_counts, off_flags, counts, rank, world, num_experts, epoch, budget_ms, m_tiles_cap,
+                status):
+    dev = counts.device
+    El = num_experts // world
+    seg_start = torch.empty(El + 1, dtype=torch.int32, device=dev)
+    recv_counts = torch.empty(El, dtype=torch.int32, device=dev)
+    tile_group = torch.empty(m_tiles_cap, dtype=torch.int32, device=dev)
+    dest_base = torch.empty(num_experts, dtype=torch.int32, device=dev)
+    _check(lib().ttb_ep_exchange(peer_ptrs, C.c_longlong(off_counts), C.c_longlong(off_flags), _p(counts), C.c_int(rank),
+                                 C.c_int(world), C.c_int(num_experts), C.c_int(epoch), C.c_longlong(budget_ms),
+                                 C.c_int(m_tiles_cap), _p(seg_start), _p(recv_counts), _p(tile_group), _p(dest_base),
+                                 _p(status), _stream()), "ttb_ep_exchange")
+    return seg_start, recv_counts, tile_group, dest_base
+
+
+def ep_scatter(peer_ptrs, off_rows, off_vals, off_flags, src, expert, dest_row, val, k, El, rank, world, epoch, cap_rows,
+               done_counter, status):
+    N = expert.numel()
+    grid = max(1, min((N + 7) // 8, 8 * num_sms(src.device.index)))
+    _check(lib().ttb_ep_scatter(peer_ptrs, C.c_longlong(off_rows), C.c_longlong(off_vals), C.c_longlong(off_flags), _p(src),
+                                C.c_longlong(src.stride(0)), _p(expert), _p(dest_row), _p(val), C.c_longlong(N), C.c_int(k),
+                                C.c_int(src.shape[1]), C.c_int(El), C.c_int(rank), C.c_int(world), C.c_int(epoch),
+                                C.c_longlong(cap_rows), _p(done_counter), _p(status), C.c_int(grid), _stream()),
+           "ttb_ep_scatter")
+
+
+def flag_signal(peer_ptrs, off_flags, rank, world, epoch):
+    _check(lib().ttb_flag_signal(peer_ptrs, C.c_longlong(off_flags), C.c_int(rank), C.c_int(world), C.c_int(epoch),
+                                 _stream()), "ttb_flag_signal")
+
+
+def flag_wait(peer_ptrs, off_flags, rank, world, epoch, budget_ms, status):
+    _check(lib().ttb_flag_wait(peer_ptrs, C.c_longlong(off_flags), C.c_int(rank), C.c_int(world), C.c_int(epoch),
+                               C.c_longlong(budget_ms), _p(status), _stream()), "ttb_flag_wait")
+
+
+def ep_gather(peer_ptrs, off_rows, expert, dest_row, T, k, H, El, world, cap_rows, status, *, weights=None, residual=None,
+              dtype=torch.bfloat16):
+    out = torch.empty(T, H, dtype=dtype, device=expert.device)
+    _check(lib().ttb_ep_gather(peer_ptrs, C.c_longlong(off_rows), _p(expert), _p(dest_row), _p(weights), _p(residual),
+                               C.c_longlong(residual.stride(0) if residual is not None else 0), _p(out),
+                               C.c_longlong(out.stride(0)), C.c_longlong(T), C.c_int(k), C.c_int(H), C.c_int(El),
+                               C.c_int(world), C.c_longlong(cap_rows), _p(status), _stream()), "ttb_ep_gather")
+    return out
+
+
+def ep_gather_vals(peer_ptrs, off_vals, expert, dest_row, El, world, cap_rows, status):
+    N = expert.numel()
+    out = torch.empty(N, dtype=torch.float32, device=expert.device)
+    _check(lib().ttb_ep_gather_vals(peer_ptrs, C.c_longlong(off_vals), _p(expert), _p(dest_row), _p(out), C.c_longlong(N),
+                                    C.c_int(El), C.c_int(world), C.c_longlong(cap_rows), _p(status), _stream()),
+           "ttb_ep_gather_vals")
+    return out

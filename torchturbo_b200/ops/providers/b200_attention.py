@@ -16,14 +16,17 @@ from .b200 import BF16, _B200Op, _ok
 
 @cache
 def _tiles_for(cu_seqlens, device):
-    t = K.build_q_tiles(cu_seqlens)
-    return t.to(device, non_blocking=True), int(cu_seqlens[-1])
+    """(query-tile table on the device, number of valid tokens, boundaries on the device) for one batch; built
+    once and shared by every layer (pinned staging keeps the copies asynchronous)."""
+    t = K.build_q_tiles(cu_seqlens).pin_memory()
+    cu = cu_seqlens.to(torch.int32).pin_memory()
+    return t.to(device, non_blocking=True), int(cu_seqlens[-1]), cu.to(device, non_blocking=True)
 
 
 class FlashAttnFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, cu_seqlens, max_seqlen, causal, scale, want_ml):
-        tiles, n_valid = _tiles_for(cu_seqlens, q.device)
+        tiles, n_valid, _ = _tiles_for(cu_seqlens, q.device)
         out, lse, ml = K.attn_fwd(q, k, v, tiles, scale=scale, causal=causal, want_max_logit=want_ml)
         ctx.save_for_backward(q, k, v, out, lse)
         ctx.meta = (cu_seqlens, max_seqlen, causal, scale, n_valid)
@@ -42,7 +45,7 @@ class FlashAttnFn(torch.autograd.Function):
         # until the tcgen05 backward lands, the library backward consumes this kernel's out / lse
         from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
 
-        cu = cu_seqlens.to(device=q.device, dtype=torch.int32)
+        cu = _tiles_for(cu_seqlens, q.device)[2]
         if max_seqlen is None:
             max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max())
         dq, dk, dv = torch.zeros_like(q), torch.zeros_like(k), torch.zeros(k.shape, dtype=k.dtype, device=k.device)
