@@ -312,3 +312,26 @@ def test_attention_fwd(K, causal):
     if causal:
         s = s.masked_fill(~torch.ones(b - a, b - a, dtype=torch.bool, device="cuda").tril(), float("-inf"))
     _close(lse[3, a:b], torch.logsumexp(s, -1), rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_attention_bwd(K, causal):
+    from torchturbo_b200.ops.providers.native import attention_ref
+
+    torch.manual_seed(1)
+    T, Hq, Hk, D = 700, 4, 2, 128
+    cu = torch.tensor([0, 200, 201, 520, 650], dtype=torch.int32)
+    q, k, v = _rand(T, Hq, D), _rand(T, Hk, D), _rand(T, Hk, D)
+    tiles = K.build_q_tiles(cu).cuda()
+    out, lse, _ = K.attn_fwd(q, k, v, tiles, scale=D ** -0.5, causal=causal)
+    dout = _rand(T, Hq, D)
+    dq, dk, dv = K.attn_bwd(dout, q, k, v, out, lse, tiles, scale=D ** -0.5, causal=causal)
+    torch.cuda.synchronize()
+    assert K.attn_status() == (0, 0)
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    ref = attention_ref(qf, kf, vf, cu, causal=causal, scale=D ** -0.5)
+    ref.backward(dout.float())
+    _close(dq, qf.grad, atol=3e-2)
+    _close(dk, kf.grad, atol=3e-2)
+    _close(dv, vf.grad, atol=3e-2)
+    assert float(dk[650:].abs().max()) == 0.0 and float(dq[650:].abs().max()) == 0.0

@@ -1,0 +1,416 @@
+// Variable-length flash attention backward for sm_100a (head_dim 128, GQA, causal or full).
+//
+// One CTA owns one 128-row KV tile of one document for one KV head; K_j and V_j stay resident in shared memory
+// and dK_j / dV_j accumulate in TMEM over every query head of the group and every 64-row query tile that can see
+// the KV tile.  Per (query head, query tile) iteration, all on tcgen05 with M = 128:
+//     S^T  = K_j  Q_i^T          [kv, q]     (K-major  x K-major)
+//     dP^T = V_j  dO_i^T         [kv, q]     (K-major  x K-major)
+//     P^T  = exp2(S^T c - lse_q),  dS^T = P^T (dP^T - Delta_q) scale        (one thread per kv row, bf16 -> smem)
+//     dV  += P^T  dO_i           [kv, d]     (K-major  x MN-major)
+//     dK  += dS^T Q_i            [kv, d]     (K-major  x MN-major)
+//     dQ^T = K_j^T dS^T          [d, q]      (MN-major x MN-major)  -> fp32 atomic add into dQ
+// Warp roles: 0 TMA producer, 1 MMA issuer, 2-5 softmax/dS, 6-9 dQ read-out.  Waits are bounded; on timeout the
+// roles drain to the final barrier, TMEM is freed and the status word records where the wait gave up.
+//
+// Replaces flash-attn 2's backward used through the reference attention interface
+// (models/modules/attention/interface.py:114-158).
+#include "common.cuh"
+
+namespace ttb {
+
+constexpr unsigned KID_ATTN_BWD = 4;
+constexpr int BW_KV = 128;   // kv rows per CTA
+constexpr int BW_Q = 64;     // query rows per iteration
+constexpr int BW_D = 128;
+
+struct AttnBwdParams {
+  const int* kv_tiles;   // [n_tiles, 3]: first kv row, document start, document end
+  const float* lse;      // [Hq, T]
+  const float* delta;    // [Hq, T]  rowsum(dO * O)
+  float* dq_acc;         // [T, Hq, D] fp32, zero-initialised
+  __nv_bfloat16* dk;     // [T, Hk, D]
+  __nv_bfloat16* dv;     // [T, Hk, D]
+  int Hq, Hk;
+  long long T;
+  float scale;
+  int causal;
+};
+
+struct BwdSmem {
+  static constexpr int K = 0;                       // 32 KB
+  static constexpr int V = K + 32768;               // 32 KB
+  static constexpr int Q0 = V + 32768;              // 2 x 16 KB
+  static constexpr int DO0 = Q0 + 2 * 16384;        // 2 x 16 KB
+  static constexpr int PT = DO0 + 2 * 16384;        // 16 KB  P^T  [128 kv][64 q]
+  static constexpr int DST = PT + 16384;            // 16 KB  dS^T [128 kv][64 q]
+  static constexpr int LSE = DST + 16384;           // float [2][64]
+  static constexpr int DELTA = LSE + 2 * 64 * 4;    // float [2][64]
+  static constexpr int BARS = DELTA + 2 * 64 * 4;
+  static constexpr int TOTAL = BARS + 256 + 1024;
+};
+
+__device__ __forceinline__ float bw_exp2(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Warp-collective: 64 consecutive fp32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&out)[64]) {
+#pragma unroll
+  for (int cb = 0; cb < 2; ++cb) {
+    uint32_t v[32];
+    tmem_ld_32x32b_x32(taddr + cb * 32, v);
+    tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 32; ++i) out[cb * 32 + i] = __uint_as_float(v[i]);
+  }
+}
+
+__global__ void __launch_bounds__(320, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
+                const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                const AttnBwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BwdSmem::BARS);
+  uint64_t* kv_full = bars + 0;
+  uint64_t* qdo_full = bars + 1;    // [2]
+  uint64_t* qdo_empty = bars + 3;   // [2]
+  uint64_t* st_full = bars + 5;
+  uint64_t* st_empty = bars + 6;
+  uint64_t* pds_full = bars + 7;
+  uint64_t* pds_empty = bars + 8;
+  uint64_t* dq_full = bars + 9;
+  uint64_t* dq_empty = bars + 10;
+  uint64_t* acc_full = bars + 11;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  float* s_lse = reinterpret_cast<float*>(smem + BwdSmem::LSE);
+  float* s_delta = reinterpret_cast<float*>(smem + BwdSmem::DELTA);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x, hk = blockIdx.y;
+  const int G = p.Hq / p.Hk;
+  const int kv0 = p.kv_tiles[tile * 3 + 0];
+  const int ds = p.kv_tiles[tile * 3 + 1];
+  const int de = p.kv_tiles[tile * 3 + 2];
+  // query tiles (64 rows, aligned to the document start) that can see this kv tile
+  const int q_first = p.causal ? ds + ((kv0 - ds) / BW_Q) * BW_Q : ds;
+  const int n_qt = (de - q_first + BW_Q - 1) / BW_Q;
+  const int n_it = n_qt * G;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
+    mbar_init(st_full, 1); mbar_init(st_empty, 4);
+    mbar_init(pds_full, 4); mbar_init(pds_empty, 1);
+    mbar_init(dq_full, 1); mbar_init(dq_empty, 4);
+    mbar_init(acc_full, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tm_ST = tmem_base;          // 64 cols
+  const uint32_t tm_DPT = tmem_base + 64;    // 64 cols
+  const uint32_t tm_DQT = tmem_base + 128;   // 64 cols
+  const uint32_t tm_DV = tmem_base + 256;    // 128 cols
+  const uint32_t tm_DK = tmem_base + 384;    // 128 cols
+
+  auto it_head = [&](int it) { return hk * G + it / n_qt; };
+  auto it_q0 = [&](int it) { return q_first + (it % n_qt) * BW_Q; };
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (elect_one()) {
+      tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmDO); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+      mbar_expect_tx(kv_full, 65536);
+      tma_load_2d(smem + BwdSmem::K, &tmK, kv_full, hk * BW_D, kv0);
+      tma_load_2d(smem + BwdSmem::K + 16384, &tmK, kv_full, hk * BW_D + 64, kv0);
+      tma_load_2d(smem + BwdSmem::V, &tmV, kv_full, hk * BW_D, kv0);
+      tma_load_2d(smem + BwdSmem::V + 16384, &tmV, kv_full, hk * BW_D + 64, kv0);
+      for (int it = 0; it < n_it; ++it) {
+        const int st = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
+        if (!mbar_wait(&qdo_empty[st], ph ^ 1, KID_ATTN_BWD, 1)) break;
+        const int h = it_head(it), q0 = it_q0(it);
+        mbar_expect_tx(&qdo_full[st], 32768);
+        uint8_t* sq = smem + BwdSmem::Q0 + st * 16384;
+        uint8_t* sd = smem + BwdSmem::DO0 + st * 16384;
+        tma_load_2d(sq, &tmQ, &qdo_full[st], h * BW_D, q0);
+        tma_load_2d(sq + 8192, &tmQ, &qdo_full[st], h * BW_D + 64, q0);
+        tma_load_2d(sd, &tmDO, &qdo_full[st], h * BW_D, q0);
+        tma_load_2d(sd + 8192, &tmDO, &qdo_full[st], h * BW_D + 64, q0);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t id_s = make_idesc_bf16(128, 64, false, false);
+      constexpr uint32_t id_acc = make_idesc_bf16(128, 128, false, true);
+      constexpr uint32_t id_dq = make_idesc_bf16(128, 64, true, true);
+      const uint32_t sK = smem_u32(smem + BwdSmem::K), sV = smem_u32(smem + BwdSmem::V);
+      const uint32_t sPT = smem_u32(smem + BwdSmem::PT), sDST = smem_u32(smem + BwdSmem::DST);
+      bool ok = mbar_wait(kv_full, 0, KID_ATTN_BWD, 2);
+      auto issue_scores = [&](int it) -> bool {
+        const int st = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
+        if (!mbar_wait(&qdo_full[st], ph, KID_ATTN_BWD, 3)) return false;
+        if (!mbar_wait(st_empty, (it & 1) ^ 1, KID_ATTN_BWD, 4)) return false;
+        tc_fence_after();
+        const uint32_t sQ = smem_u32(smem + BwdSmem::Q0 + st * 16384);
+        const uint32_t sDO = smem_u32(smem + BwdSmem::DO0 + st * 16384);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {  // reduction over d = 128
+          const uint32_t offa = (kk >> 2) * 16384 + (kk & 3) * 32;   // K / V tiles: [128 rows][64 d] panels
+          const uint32_t offb = (kk >> 2) * 8192 + (kk & 3) * 32;    // Q / dO tiles: [64 rows][64 d] panels
+          umma_ss(tm_ST, make_smem_desc(sK + offa, 16, 1024), make_smem_desc(sQ + offb, 16, 1024), id_s, kk != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t offa = (kk >> 2) * 16384 + (kk & 3) * 32;
+          const uint32_t offb = (kk >> 2) * 8192 + (kk & 3) * 32;
+          umma_ss(tm_DPT, make_smem_desc(sV + offa, 16, 1024), make_smem_desc(sDO + offb, 16, 1024), id_s, kk != 0);
+        }
+        umma_commit(st_full);
+        return true;
+      };
+      if (ok && n_it > 0) ok = issue_scores(0);
+      for (int it = 0; it < n_it && ok; ++it) {
+        if (it + 1 < n_it) {
+          if (!issue_scores(it + 1)) { ok = false; break; }
+        }
+        const int st = it & 1;
+        if (!mbar_wait(pds_full, it & 1, KID_ATTN_BWD, 5)) { ok = false; break; }
+        if (!mbar_wait(dq_empty, (it & 1) ^ 1, KID_ATTN_BWD, 6)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sQ = smem_u32(smem + BwdSmem::Q0 + st * 16384);
+        const uint32_t sDO = smem_u32(smem + BwdSmem::DO0 + st * 16384);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {  // reduction over q = 64
+          // A: P^T / dS^T K-major single panel; B: dO / Q as [q rows][d] MN-major, d panels 8 KB apart
+          umma_ss(tm_DV, make_smem_desc(sPT + kk * 32, 16, 1024), make_smem_desc(sDO + kk * 2048, 8192, 1024), id_acc,
+                  (it | kk) != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          umma_ss(tm_DK, make_smem_desc(sDST + kk * 32, 16, 1024), make_smem_desc(sQ + kk * 2048, 8192, 1024), id_acc,
+                  (it | kk) != 0);
+        }
+        umma_commit(&qdo_empty[st]);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {  // reduction over kv = 128
+          // A: K^T from the K tile ([kv rows][d], MN-major, d panels 16 KB apart); B: dS^T ([kv rows][q]) MN-major
+          umma_ss(tm_DQT, make_smem_desc(sK + kk * 2048, 16384, 1024), make_smem_desc(sDST + kk * 2048, 8192, 1024),
+                  id_dq, kk != 0);
+        }
+        umma_commit(dq_full);
+        umma_commit(pds_empty);
+      }
+      if (ok) umma_commit(acc_full);
+    }
+  } else if (warp < 6) {
+    // ---------------------------------------------------------------- softmax / dS (thread = kv row)
+    const int lg = warp & 3;
+    const int row = lg * 32 + lane;
+    const int kv = kv0 + row;
+    const bool kv_ok = kv < de;
+    const float c = p.scale * 1.4426950408889634f;
+    const int tid = threadIdx.x - 64;  // 0..127 inside this group
+    uint8_t* sPT = smem + BwdSmem::PT;
+    uint8_t* sDST = smem + BwdSmem::DST;
+    bool ok = true;
+    for (int it = 0; it < n_it && ok; ++it) {
+      const int h = it_head(it), q0 = it_q0(it);
+      // stage lse / delta of the 64 query rows (double-buffered by iteration parity)
+      if (tid < 64) {
+        const int q = q0 + tid;
+        s_lse[(it & 1) * 64 + tid] = (q < de) ? p.lse[static_cast<long long>(h) * p.T + q] * 1.4426950408889634f : INFINITY;
+      } else {
+        const int q = q0 + tid - 64;
+        s_delta[(it & 1) * 64 + tid - 64] = (q < de) ? p.delta[static_cast<long long>(h) * p.T + q] : 0.f;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (!mbar_wait(st_full, it & 1, KID_ATTN_BWD, 7)) { ok = false; break; }
+      tc_fence_after();
+      float s[64], dp[64];
+      const uint32_t lane_off = static_cast<uint32_t>(lg * 32) << 16;
+      tmem_ld64(tm_ST + lane_off, s);
+      tmem_ld64(tm_DPT + lane_off, dp);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(st_empty);
+      const float* lse = s_lse + (it & 1) * 64;
+      const float* dl = s_delta + (it & 1) * 64;
+      const bool need_mask = (q0 + BW_Q > de) || (kv0 + BW_KV > de) || (p.causal && kv0 + BW_KV - 1 > q0);
+      // previous P^T / dS^T must have been consumed
+      if (it > 0) {
+        if (!mbar_wait(pds_empty, (it - 1) & 1, KID_ATTN_BWD, 8)) { ok = false; break; }
+      }
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        uint32_t wp[4], wd[4];
+#pragma unroll
+        for (int qq = 0; qq < 4; ++qq) {
+          float pv[2], dv[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int col = ch * 8 + qq * 2 + e;
+            float pr = bw_exp2(s[col] * c - lse[col]);
+            if (need_mask) {
+              const int q = q0 + col;
+              const bool vis = kv_ok && q < de && (!p.causal || kv <= q);
+              pr = vis ? pr : 0.f;
+            }
+            pv[e] = pr;
+            dv[e] = pr * (dp[col] - dl[col]) * p.scale;
+          }
+          wp[qq] = pack_bf16(pv[0], pv[1]);
+          wd[qq] = pack_bf16(dv[0], dv[1]);
+        }
+        const int off = row * 128 + ((ch ^ (row & 7)) * 16);
+        *reinterpret_cast<uint4*>(sPT + off) = make_uint4(wp[0], wp[1], wp[2], wp[3]);
+        *reinterpret_cast<uint4*>(sDST + off) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pds_full);
+    }
+    // ---- epilogue: dK / dV of this tile
+    if (ok && n_it > 0) ok = mbar_wait(acc_full, 0, KID_ATTN_BWD, 9);
+    if (ok) {
+      tc_fence_after();
+      const uint32_t lane_off = static_cast<uint32_t>(lg * 32) << 16;
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        __nv_bfloat16* dst = (which == 0 ? p.dv : p.dk) + (static_cast<long long>(kv) * p.Hk + hk) * BW_D;
+        const uint32_t tm = (which == 0 ? tm_DV : tm_DK) + lane_off;
+#pragma unroll 1
+        for (int cb = 0; cb < 4; ++cb) {
+          uint32_t v[32];
+          if (n_it > 0) {
+            tmem_ld_32x32b_x32(tm + cb * 32, v);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0u;
+          }
+          if (kv_ok) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 w;
+              w.x = pack_bf16(__uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+              w.y = pack_bf16(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+              w.z = pack_bf16(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+              w.w = pack_bf16(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+              *reinterpret_cast<uint4*>(dst + cb * 32 + i) = w;
+            }
+          }
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- dQ read-out (thread = head-dim index d)
+    const int lg = warp & 3;
+    const int d = lg * 32 + lane;
+    bool ok = true;
+    for (int it = 0; it < n_it && ok; ++it) {
+      const int h = it_head(it), q0 = it_q0(it);
+      if (!mbar_wait(dq_full, it & 1, KID_ATTN_BWD, 10)) { ok = false; break; }
+      tc_fence_after();
+      float v[64];
+      tmem_ld64(tm_DQT + (static_cast<uint32_t>(lg * 32) << 16), v);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_empty);
+      float* base = p.dq_acc + (static_cast<long long>(q0) * p.Hq + h) * BW_D + d;
+      const int nq = min(BW_Q, de - q0);
+#pragma unroll
+      for (int col = 0; col < BW_Q; ++col) {
+        if (col < nq) atomicAdd(base + static_cast<long long>(col) * p.Hq * BW_D, v[col]);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// delta[h, t] = sum_d dO[t,h,d] * O[t,h,d]; also converts nothing else.  One warp per (t, h).
+__global__ void attn_bwd_delta_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ out,
+                                      float* __restrict__ delta, long long T, int Hq) {
+  const long long gw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (gw >= T * Hq) return;
+  const long long t = gw / Hq;
+  const int h = static_cast<int>(gw - t * Hq);
+  const uint2 a = *reinterpret_cast<const uint2*>(dout + gw * BW_D + lane * 4);
+  const uint2 b = *reinterpret_cast<const uint2*>(out + gw * BW_D + lane * 4);
+  const float2 a0 = unpack_bf16(a.x), a1 = unpack_bf16(a.y), b0 = unpack_bf16(b.x), b1 = unpack_bf16(b.y);
+  float s = a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y;
+  s = warp_sum(s);
+  if (lane == 0) delta[static_cast<long long>(h) * T + t] = s;
+}
+
+// dq (bf16) = dq_acc (fp32)
+__global__ void attn_bwd_cast_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long long n) {
+  const long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
+  if (i >= n) return;
+  const float4 a = *reinterpret_cast<const float4*>(acc + i), b = *reinterpret_cast<const float4*>(acc + i + 4);
+  uint4 w;
+  w.x = pack_bf16(a.x, a.y); w.y = pack_bf16(a.z, a.w); w.z = pack_bf16(b.x, b.y); w.w = pack_bf16(b.z, b.w);
+  *reinterpret_cast<uint4*>(dq + i) = w;
+}
+
+static int bw_map(CUtensorMap* m, const void* base, long long rows, long long row_stride, int cols, int box_rows) {
+  uint64_t dims[2] = {static_cast<uint64_t>(cols), static_cast<uint64_t>(rows)};
+  uint64_t str[1] = {static_cast<uint64_t>(row_stride) * 2};
+  uint32_t box[2] = {64, static_cast<uint32_t>(box_rows)};
+  return make_tmap_bf16(m, base, 2, dims, str, box);
+}
+
+}  // namespace ttb
+
+using namespace ttb;
+
+// q, dout, out: [T, Hq*128] contiguous rows; k: [T, Hk*128] (ldk); v: [T, Hk*128] (ldv, may be strided).
+// dq_acc fp32 [T*Hq*128] zero-initialised scratch; delta fp32 [Hq*T] scratch.
+TTB_EXPORT int ttb_attn_bwd(const void* q, const void* k, long long ldk, const void* v, long long ldv, const void* out,
+                            const void* dout, const float* lse, float* delta, float* dq_acc, void* dq, void* dk,
+                            void* dv, const int* kv_tiles, int n_tiles, long long T, int Hq, int Hk, int D, float scale,
+                            int causal, void* stream_ptr) {
+  if (D != 128 || Hq % Hk) return 901;
+  if ((ldk % 8) || (ldv % 8)) return 902;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_ptr);
+  if (T == 0 || n_tiles == 0) return 0;
+  const long long warps = T * Hq;
+  attn_bwd_delta_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, stream>>>((const __nv_bfloat16*)dout,
+                                                                        (const __nv_bfloat16*)out, delta, T, Hq);
+  CUtensorMap tq, tdo, tk, tv;
+  if (bw_map(&tq, q, T, (long long)Hq * D, Hq * D, 64)) return 101;
+  if (bw_map(&tdo, dout, T, (long long)Hq * D, Hq * D, 64)) return 102;
+  if (bw_map(&tk, k, T, ldk, Hk * D, 128)) return 103;
+  if (bw_map(&tv, v, T, ldv, Hk * D, 128)) return 104;
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::TOTAL);
+    if (e != cudaSuccess) return 300 + (int)e;
+    attr = true;
+  }
+  AttnBwdParams p{kv_tiles, lse, delta, dq_acc, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, Hq, Hk, T, scale, causal};
+  dim3 grid(n_tiles, Hk);
+  attn_bwd_kernel<<<grid, 320, BwdSmem::TOTAL, stream>>>(tq, tdo, tk, tv, p);
+  const long long n = T * Hq * D;
+  attn_bwd_cast_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, stream>>>(dq_acc, (__nv_bfloat16*)dq, n);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}

@@ -577,3 +577,24 @@ def ep_gather_vals(peer_ptrs, off_vals, expert, dest_row, El, world, cap_rows, s
                                     C.c_int(El), C.c_int(world), C.c_longlong(cap_rows), _p(status), _stream()),
            "ttb_ep_gather_vals")
     return out
+
+
+def attn_bwd(dout, q, k, v, out, lse, kv_tiles_dev, *, scale: float, causal: bool = True):
+    """Gradients of `attn_fwd`.  Returns (dq [T,Hq,128], dk [T,Hk,128], dv [T,Hk,128]) in bf16; dQ is accumulated in
+    an fp32 scratch buffer with atomic adds (the order of the adds is not deterministic)."""
+    T, Hq, D = q.shape
+    Hk = k.shape[1]
+    assert dout.is_contiguous() and out.is_contiguous() and q.is_contiguous()
+    assert k.stride(1) == D and v.stride(1) == D and v.stride(2) == 1
+    delta = torch.empty(Hq * T, dtype=torch.float32, device=q.device)
+    dq_acc = torch.zeros(T, Hq, D, dtype=torch.float32, device=q.device)
+    dq = torch.empty_like(q)
+    dk = torch.zeros(T, Hk, D, dtype=q.dtype, device=q.device)
+    dv = torch.zeros(T, Hk, D, dtype=q.dtype, device=q.device)
+    global LAUNCH_COUNT
+    _check(lib().ttb_attn_bwd(_p(q), _p(k), C.c_longlong(k.stride(0)), _p(v), C.c_longlong(v.stride(0)), _p(out),
+                              _p(dout), _p(lse), _p(delta), _p(dq_acc), _p(dq), _p(dk), _p(dv), _p(kv_tiles_dev),
+                              C.c_int(kv_tiles_dev.shape[0]), C.c_longlong(T), C.c_int(Hq), C.c_int(Hk), C.c_int(D),
+                              C.c_float(scale), C.c_int(int(causal)), _stream()), "ttb_attn_bwd")
+    LAUNCH_COUNT += 2
+    return dq, dk, dv

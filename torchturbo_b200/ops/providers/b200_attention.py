@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -39,10 +40,11 @@ class FlashAttnFn(torch.autograd.Function):
     def backward(ctx, dout, *_):
         q, k, v, out, lse = ctx.saved_tensors
         cu_seqlens, max_seqlen, causal, scale, n = ctx.meta
-        if hasattr(K.lib(), "ttb_attn_bwd"):
-            dq, dk, dv = K.attn_bwd(dout.contiguous(), q, k, v, out, lse, cu_seqlens, scale=scale, causal=causal)
+        if os.environ.get("TORCHTURBO_ATTN_BWD", "tcgen05") == "tcgen05":
+            tiles = _tiles_for(cu_seqlens, q.device)[0]
+            dq, dk, dv = K.attn_bwd(dout.contiguous(), q, k, v, out, lse, tiles, scale=scale, causal=causal)
             return dq, dk, dv, None, None, None, None, None
-        # until the tcgen05 backward lands, the library backward consumes this kernel's out / lse
+        # library backward on this kernel's out / lse (selected with TORCHTURBO_ATTN_BWD=flash_attn2; used as a baseline)
         from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
 
         cu = _tiles_for(cu_seqlens, q.device)[2]
