@@ -40,6 +40,7 @@ from .config import EngineConfig, FreezePolicy, ParameterGroup
 from .distributed import assert_finite
 from .metrics import MetricTracker, MFUEstimator
 from .plugins import PluginManager
+from .rl import RLMixin
 
 logger = get_logger(__name__)
 
@@ -106,7 +107,7 @@ class EpochDrivenDataLoader(DataLoader):
             bs.sampler.set_epoch(epoch)
 
 
-class TorchTurboEngine:
+class TorchTurboEngine(RLMixin):
     def __init__(self, config: EngineConfig | dict[str, Any] | None = None) -> None:
         if config is None:
             config = EngineConfig()
