@@ -1,0 +1,24 @@
+"""ms-swift launcher: `torchrun scripts/runs/run_swift.py [sft|pt|dpo] --tt_* <swift arguments>`."""
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+
+def main():
+    import torchturbo_b200
+    from torchturbo_b200.engine.args import parse_torchturbo_args, set_torchturbo_args
+
+    stage = sys.argv[1] if len(sys.argv) > 1 and sys.argv[1] in ("sft", "pt", "dpo") else "sft"
+    argv = sys.argv[2:] if len(sys.argv) > 1 and sys.argv[1] == stage else sys.argv[1:]
+    tt_args, rest = parse_torchturbo_args(argv)
+    set_torchturbo_args(tt_args)
+    torchturbo_b200.activate("msswift")
+    import swift.pipelines.train as train
+
+    cls = {"sft": "SwiftSft", "pt": "SwiftPretrain", "dpo": "SwiftRLHF"}[stage]
+    getattr(train, cls)(rest).main()
+
+
+if __name__ == "__main__":
+    main()

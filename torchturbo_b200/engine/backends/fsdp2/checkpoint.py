@@ -293,16 +293,47 @@ class FSDP2CheckpointManager(BaseCheckpointManager):
         for oname, opt in zip(onames, opts):
             groups[oname] = [{k: v for k, v in g.items() if k != "params"} | {"params": [names[id(p)] for p in g["params"]]}
                              for g in opt.param_groups]
+            self._materialize_state(opt)
             for g in opt.param_groups:
                 for p in g["params"]:
-                    if hasattr(opt, "_init_state"):
-                        opt._init_state(p)
                     st = opt.state.get(p, {})
                     stamp = suf if (suf and id(p) in eids) else ""
                     for k, v in st.items():
                         if isinstance(v, torch.Tensor):
                             tensors[f"{oname}/{names[id(p)]}{stamp}/{k}"] = v
         return tensors, groups
+
+    @staticmethod
+    @torch.no_grad()
+    def _materialize_state(opt) -> None:
+        """Make sure every trainable parameter has its state tensors (a freshly built optimizer has none, and
+        loading needs destinations).  Optimizers without an explicit initialiser take one step on zero gradients
+        with their parameters saved and restored around it."""
+        if hasattr(opt, "_init_state"):
+            for g in opt.param_groups:
+                for p in g["params"]:
+                    if p.requires_grad:
+                        opt._init_state(p)
+            return
+        missing = [p for g in opt.param_groups for p in g["params"] if p.requires_grad and len(opt.state.get(p, {})) == 0]
+        if not missing:
+            return
+        saved = [(p, (p._local_tensor if _is_dtensor(p) else p).detach().clone(), p.grad) for p in missing]
+        for p in missing:
+            p.grad = torch.zeros_like(p)
+        others = [(p, p.grad) for g in opt.param_groups for p in g["params"] if p not in set(missing)]
+        for p, _ in others:
+            p.grad = None
+        opt.step()
+        for p, data, grad in saved:
+            (p._local_tensor if _is_dtensor(p) else p).copy_(data)
+            p.grad = grad
+            st = opt.state[p]
+            for k, v in st.items():
+                if isinstance(v, torch.Tensor):
+                    v.zero_()
+        for p, grad in others:
+            p.grad = grad
 
     def save_native_optimizer(self, model: nn.Module, optimizer, path: str) -> None:
         import torch.distributed.checkpoint as dcp
