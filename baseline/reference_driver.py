@@ -75,8 +75,9 @@ def run(args, ref_dir: str) -> dict:
     dev = torch.device("cuda", local_rank) if use_cuda else torch.device("cpu")
 
     def to_device(b):
-        return {k: (v.to(dev, non_blocking=True) if isinstance(v, torch.Tensor) and not k.startswith("cu_seq") else v)
-                for k, v in b.items()}
+        # the reference's trainers hand it batches that HF `Trainer._prepare_inputs` moved to the device as a whole,
+        # packed boundaries included
+        return {k: (v.to(dev, non_blocking=True) if isinstance(v, torch.Tensor) else v) for k, v in b.items()}
 
     def step(b):
         loss = engine.compute_loss(model, b)
