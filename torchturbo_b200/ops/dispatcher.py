@@ -20,7 +20,8 @@ from .registry import REGISTRY
 
 logger = get_logger(__name__)
 
-_PROVIDER_MODULES = ("torchturbo_b200.ops.providers.native", "torchturbo_b200.ops.providers.b200")
+_PROVIDER_MODULES = ("torchturbo_b200.ops.providers.native", "torchturbo_b200.ops.providers.native_linear_attention",
+                     "torchturbo_b200.ops.providers.b200")
 
 
 def load_providers() -> None:
