@@ -1,8 +1,10 @@
 // Variable-length flash attention backward for sm_100a (head_dim 128, GQA, causal or full).
 //
-// One CTA owns one 128-row KV tile of one document for one KV head; K_j and V_j stay resident in shared memory
-// and dK_j / dV_j accumulate in TMEM over every query head of the group and every 64-row query tile that can see
-// the KV tile.  Per (query head, query tile) iteration, all on tcgen05 with M = 128:
+// One CTA owns one 128-row KV tile of one document for one *query* head; K_j and V_j stay resident in shared memory
+// and dK_j / dV_j accumulate in TMEM over every 64-row query tile that can see the KV tile.  With grouped-query
+// attention the CTAs of the query heads that share a KV head add their dK / dV into fp32 accumulators with vector
+// atomics (splitting by query head keeps the longest CTA short: a causal KV tile near the start of a long document
+// is seen by every later query tile).  Per query-tile iteration, all on tcgen05 with M = 128:
 //     S^T  = K_j  Q_i^T          [kv, q]     (K-major  x K-major)
 //     dP^T = V_j  dO_i^T         [kv, q]     (K-major  x K-major)
 //     P^T  = exp2(S^T c - lse_q),  dS^T = P^T (dP^T - Delta_q) scale        (one thread per kv row, bf16 -> smem)
@@ -28,8 +30,10 @@ struct AttnBwdParams {
   const float* lse;      // [Hq, T]
   const float* delta;    // [Hq, T]  rowsum(dO * O)
   float* dq_acc;         // [T, Hq, D] fp32, zero-initialised
-  __nv_bfloat16* dk;     // [T, Hk, D]
+  __nv_bfloat16* dk;     // [T, Hk, D]   written directly when Hq == Hk
   __nv_bfloat16* dv;     // [T, Hk, D]
+  float* dk_acc;         // [T, Hk, D] fp32, zero-initialised (used when Hq > Hk)
+  float* dv_acc;
   int Hq, Hk;
   long long T;
   float scale;
@@ -89,15 +93,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   float* s_delta = reinterpret_cast<float*>(smem + BwdSmem::DELTA);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = blockIdx.x, hk = blockIdx.y;
+  const int tile = blockIdx.x, hq = blockIdx.y;
   const int G = p.Hq / p.Hk;
+  const int hk = hq / G;
   const int kv0 = p.kv_tiles[tile * 3 + 0];
   const int ds = p.kv_tiles[tile * 3 + 1];
   const int de = p.kv_tiles[tile * 3 + 2];
   // query tiles (64 rows, aligned to the document start) that can see this kv tile
   const int q_first = p.causal ? ds + ((kv0 - ds) / BW_Q) * BW_Q : ds;
   const int n_qt = (de - q_first + BW_Q - 1) / BW_Q;
-  const int n_it = n_qt * G;
+  const int n_it = n_qt;
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
@@ -122,8 +127,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t tm_DV = tmem_base + 256;    // 128 cols
   const uint32_t tm_DK = tmem_base + 384;    // 128 cols
 
-  auto it_head = [&](int it) { return hk * G + it / n_qt; };
-  auto it_q0 = [&](int it) { return q_first + (it % n_qt) * BW_Q; };
+  auto it_head = [&](int) { return hq; };
+  auto it_q0 = [&](int it) { return q_first + it * BW_Q; };
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -225,17 +230,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     uint8_t* sPT = smem + BwdSmem::PT;
     uint8_t* sDST = smem + BwdSmem::DST;
     bool ok = true;
-    for (int it = 0; it < n_it && ok; ++it) {
-      const int h = it_head(it), q0 = it_q0(it);
-      // stage lse / delta of the 64 query rows (double-buffered by iteration parity)
+    // lse / delta of the 64 query rows of an iteration are staged one iteration ahead (double-buffered)
+    auto stage = [&](int it) {
+      const int q0s = it_q0(it);
       if (tid < 64) {
-        const int q = q0 + tid;
-        s_lse[(it & 1) * 64 + tid] = (q < de) ? p.lse[static_cast<long long>(h) * p.T + q] * 1.4426950408889634f : INFINITY;
+        const int q = q0s + tid;
+        s_lse[(it & 1) * 64 + tid] = (q < de) ? p.lse[static_cast<long long>(hq) * p.T + q] * 1.4426950408889634f : INFINITY;
       } else {
-        const int q = q0 + tid - 64;
-        s_delta[(it & 1) * 64 + tid - 64] = (q < de) ? p.delta[static_cast<long long>(h) * p.T + q] : 0.f;
+        const int q = q0s + tid - 64;
+        s_delta[(it & 1) * 64 + tid - 64] = (q < de) ? p.delta[static_cast<long long>(hq) * p.T + q] : 0.f;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+    };
+    if (n_it > 0) stage(0);
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    for (int it = 0; it < n_it && ok; ++it) {
+      const int q0 = it_q0(it);
       if (!mbar_wait(st_full, it & 1, KID_ATTN_BWD, 7)) { ok = false; break; }
       tc_fence_after();
       float s[64], dp[64];
@@ -280,6 +289,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_full);
+      if (it + 1 < n_it) stage(it + 1);
+      asm volatile("bar.sync 1, 128;" ::: "memory");
     }
     // ---- epilogue: dK / dV of this tile
     if (ok && n_it > 0) ok = mbar_wait(acc_full, 0, KID_ATTN_BWD, 9);
@@ -288,7 +299,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t lane_off = static_cast<uint32_t>(lg * 32) << 16;
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
-        __nv_bfloat16* dst = (which == 0 ? p.dv : p.dk) + (static_cast<long long>(kv) * p.Hk + hk) * BW_D;
+        const long long off = (static_cast<long long>(kv) * p.Hk + hk) * BW_D;
+        __nv_bfloat16* dst = (which == 0 ? p.dv : p.dk) + off;
+        float* acc = (which == 0 ? p.dv_acc : p.dk_acc) + off;
         const uint32_t tm = (which == 0 ? tm_DV : tm_DK) + lane_off;
 #pragma unroll 1
         for (int cb = 0; cb < 4; ++cb) {
@@ -301,14 +314,23 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             for (int i = 0; i < 32; ++i) v[i] = 0u;
           }
           if (kv_ok) {
+            if (G == 1) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              uint4 w;
-              w.x = pack_bf16(__uint_as_float(v[i]), __uint_as_float(v[i + 1]));
-              w.y = pack_bf16(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
-              w.z = pack_bf16(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
-              w.w = pack_bf16(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
-              *reinterpret_cast<uint4*>(dst + cb * 32 + i) = w;
+              for (int i = 0; i < 32; i += 8) {
+                uint4 w;
+                w.x = pack_bf16(__uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+                w.y = pack_bf16(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+                w.z = pack_bf16(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+                w.w = pack_bf16(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+                *reinterpret_cast<uint4*>(dst + cb * 32 + i) = w;
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) {
+                atomicAdd(reinterpret_cast<float4*>(acc + cb * 32 + i),
+                          make_float4(__uint_as_float(v[i]), __uint_as_float(v[i + 1]), __uint_as_float(v[i + 2]),
+                                      __uint_as_float(v[i + 3])));
+              }
             }
           }
         }
@@ -320,7 +342,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int d = lg * 32 + lane;
     bool ok = true;
     for (int it = 0; it < n_it && ok; ++it) {
-      const int h = it_head(it), q0 = it_q0(it);
+      const int h = hq, q0 = it_q0(it);
       if (!mbar_wait(dq_full, it & 1, KID_ATTN_BWD, 10)) { ok = false; break; }
       tc_fence_after();
       float v[64];
@@ -385,8 +407,8 @@ using namespace ttb;
 // q, dout, out: [T, Hq*128] contiguous rows; k: [T, Hk*128] (ldk); v: [T, Hk*128] (ldv, may be strided).
 // dq_acc fp32 [T*Hq*128] zero-initialised scratch; delta fp32 [Hq*T] scratch.
 TTB_EXPORT int ttb_attn_bwd(const void* q, const void* k, long long ldk, const void* v, long long ldv, const void* out,
-                            const void* dout, const float* lse, float* delta, float* dq_acc, void* dq, void* dk,
-                            void* dv, const int* kv_tiles, int n_tiles, long long T, int Hq, int Hk, int D, float scale,
+                            const void* dout, const float* lse, float* delta, float* dq_acc, float* dk_acc,
+                            float* dv_acc, void* dq, void* dk, void* dv, const int* kv_tiles, int n_tiles, long long T, int Hq, int Hk, int D, float scale,
                             int causal, void* stream_ptr) {
   if (D != 128 || Hq % Hk) return 901;
   if ((ldk % 8) || (ldv % 8)) return 902;
@@ -406,11 +428,17 @@ TTB_EXPORT int ttb_attn_bwd(const void* q, const void* k, long long ldk, const v
     if (e != cudaSuccess) return 300 + (int)e;
     attr = true;
   }
-  AttnBwdParams p{kv_tiles, lse, delta, dq_acc, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, Hq, Hk, T, scale, causal};
-  dim3 grid(n_tiles, Hk);
+  if (Hq != Hk && (dk_acc == nullptr || dv_acc == nullptr)) return 903;
+  AttnBwdParams p{kv_tiles, lse, delta, dq_acc, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, dk_acc, dv_acc, Hq, Hk, T, scale, causal};
+  dim3 grid(n_tiles, Hq);
   attn_bwd_kernel<<<grid, 320, BwdSmem::TOTAL, stream>>>(tq, tdo, tk, tv, p);
   const long long n = T * Hq * D;
   attn_bwd_cast_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, stream>>>(dq_acc, (__nv_bfloat16*)dq, n);
+  if (Hq != Hk) {
+    const long long nk = T * Hk * D;
+    attn_bwd_cast_kernel<<<(unsigned)((nk / 8 + 255) / 256), 256, 0, stream>>>(dk_acc, (__nv_bfloat16*)dk, nk);
+    attn_bwd_cast_kernel<<<(unsigned)((nk / 8 + 255) / 256), 256, 0, stream>>>(dv_acc, (__nv_bfloat16*)dv, nk);
+  }
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }

@@ -367,27 +367,51 @@ __device__ __forceinline__ float ld_logit<__nv_bfloat16>(const __nv_bfloat16* p,
 }
 
 template <typename TL>
-__global__ void cross_entropy_kernel(const TL* __restrict__ logits, long long ldl, const long long* __restrict__ labels,
-                                     float* __restrict__ loss_rows, float* __restrict__ lse_rows,
-                                     __nv_bfloat16* dlogits, long long ldd, const float* __restrict__ grad_scale,
-                                     float grad_scale_host, int V) {
+__global__ void __launch_bounds__(1024)
+cross_entropy_kernel(const TL* __restrict__ logits, long long ldl, const long long* __restrict__ labels,
+                     float* __restrict__ loss_rows, float* __restrict__ lse_rows, __nv_bfloat16* dlogits, long long ldd,
+                     const float* __restrict__ grad_scale, float grad_scale_host, int V) {
   __shared__ float red[32];
   const long long r = blockIdx.x;
   const TL* lr = logits + r * ldl;
   const long long label = labels[r];
   const bool valid = label >= 0 && label < V;
+  constexpr bool kBf16 = sizeof(TL) == 2;
+  // 16-byte vector path for bf16 rows (8 logits per access); everything else goes element by element
+  const bool vec = kBf16 && (V % 8 == 0) && ((reinterpret_cast<uintptr_t>(lr) & 15) == 0) &&
+                   (dlogits == nullptr || (reinterpret_cast<uintptr_t>(dlogits + r * ldd) & 15) == 0);
   if (!valid) {
     if (threadIdx.x == 0) { loss_rows[r] = 0.f; if (lse_rows) lse_rows[r] = 0.f; }
     if (dlogits) {
-      __nv_bfloat16 z = __float2bfloat16(0.f);
-      for (int c = threadIdx.x; c < V; c += blockDim.x) dlogits[r * ldd + c] = z;
+      if (vec) {
+        const uint4 z = make_uint4(0, 0, 0, 0);
+        for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) *reinterpret_cast<uint4*>(dlogits + r * ldd + c) = z;
+      } else {
+        __nv_bfloat16 z = __float2bfloat16(0.f);
+        for (int c = threadIdx.x; c < V; c += blockDim.x) dlogits[r * ldd + c] = z;
+      }
     }
     return;
   }
   float m = -INFINITY, s = 0.f;
-  for (int c = threadIdx.x; c < V; c += blockDim.x) {
-    float v = ld_logit<TL>(lr, c);
-    if (v > m) { s = s * __expf(m - v) + 1.f; m = v; } else { s += __expf(v - m); }
+  if (vec) {
+    const __nv_bfloat16* lb = reinterpret_cast<const __nv_bfloat16*>(lr);
+    for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
+      const uint4 u = *reinterpret_cast<const uint4*>(lb + c);
+      const float2 a = unpack_bf16(u.x), b2 = unpack_bf16(u.y), c2 = unpack_bf16(u.z), d = unpack_bf16(u.w);
+      const float f[8] = {a.x, a.y, b2.x, b2.y, c2.x, c2.y, d.x, d.y};
+      float vm = f[0];
+#pragma unroll
+      for (int j = 1; j < 8; ++j) vm = fmaxf(vm, f[j]);
+      if (vm > m) { s *= __expf(m - vm); m = vm; }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s += __expf(f[j] - m);
+    }
+  } else {
+    for (int c = threadIdx.x; c < V; c += blockDim.x) {
+      float v = ld_logit<TL>(lr, c);
+      if (v > m) { s = s * __expf(m - v) + 1.f; m = v; } else { s += __expf(v - m); }
+    }
   }
   const float gm = block_max(m, red);
   s = (m == -INFINITY) ? 0.f : s * __expf(m - gm);
@@ -399,10 +423,29 @@ __global__ void cross_entropy_kernel(const TL* __restrict__ logits, long long ld
   }
   if (dlogits) {
     const float sc = (grad_scale ? grad_scale[0] : 1.f) * grad_scale_host;
-    for (int c = threadIdx.x; c < V; c += blockDim.x) {
-      float p = __expf(ld_logit<TL>(lr, c) - lse);
-      if (c == label) p -= 1.f;
-      dlogits[r * ldd + c] = __float2bfloat16(p * sc);
+    __syncthreads();  // the label logit has been read before any thread overwrites an aliased buffer
+    if (vec) {
+      const __nv_bfloat16* lb = reinterpret_cast<const __nv_bfloat16*>(lr);
+      for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
+        const uint4 u = *reinterpret_cast<const uint4*>(lb + c);
+        const float2 a = unpack_bf16(u.x), b2 = unpack_bf16(u.y), c2 = unpack_bf16(u.z), d = unpack_bf16(u.w);
+        float f[8] = {a.x, a.y, b2.x, b2.y, c2.x, c2.y, d.x, d.y};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float pr = __expf(f[j] - lse);
+          if (c + j == label) pr -= 1.f;
+          f[j] = pr * sc;
+        }
+        uint4 o;
+        o.x = pack_bf16(f[0], f[1]); o.y = pack_bf16(f[2], f[3]); o.z = pack_bf16(f[4], f[5]); o.w = pack_bf16(f[6], f[7]);
+        *reinterpret_cast<uint4*>(dlogits + r * ldd + c) = o;
+      }
+    } else {
+      for (int c = threadIdx.x; c < V; c += blockDim.x) {
+        float pr = __expf(ld_logit<TL>(lr, c) - lse);
+        if (c == label) pr -= 1.f;
+        dlogits[r * ldd + c] = __float2bfloat16(pr * sc);
+      }
     }
   }
 }

@@ -473,6 +473,15 @@ def attn_status(reset: bool = False) -> tuple[int, int]:
     return int(buf[0]), int(buf[1])
 
 
+def build_kv_tiles(cu_seqlens, block: int = 128) -> torch.Tensor:
+    """Table of 128-row KV tiles for the backward pass, earliest tile of a document first (under a causal mask the
+    earliest KV tiles are seen by the most query tiles, so they carry the most work)."""
+    offs = cu_seqlens.tolist() if isinstance(cu_seqlens, torch.Tensor) else list(cu_seqlens)
+    rows = [(k0, a, b) for a, b in zip(offs[:-1], offs[1:]) for k0 in range(a, b, block)]
+    rows.sort(key=lambda r: -(r[2] - r[0]))
+    return torch.tensor(rows, dtype=torch.int32).reshape(-1, 3)
+
+
 def build_q_tiles(cu_seqlens, block: int = 128) -> torch.Tensor:
     """Host-side table of 128-row query tiles `[n, 3] = (first row, document start, document end)` from packed
     boundaries (a CPU tensor or list); no device synchronisation is involved."""
@@ -589,12 +598,20 @@ def attn_bwd(dout, q, k, v, out, lse, kv_tiles_dev, *, scale: float, causal: boo
     delta = torch.empty(Hq * T, dtype=torch.float32, device=q.device)
     dq_acc = torch.zeros(T, Hq, D, dtype=torch.float32, device=q.device)
     dq = torch.empty_like(q)
-    dk = torch.zeros(T, Hk, D, dtype=q.dtype, device=q.device)
-    dv = torch.zeros(T, Hk, D, dtype=q.dtype, device=q.device)
+    if Hq != Hk:   # query heads of a group add into fp32 accumulators, converted at the end
+        kv_acc = torch.zeros(2, T, Hk, D, dtype=torch.float32, device=q.device)
+        dk_acc, dv_acc = kv_acc[0], kv_acc[1]
+        dk = torch.empty(T, Hk, D, dtype=q.dtype, device=q.device)
+        dv = torch.empty(T, Hk, D, dtype=q.dtype, device=q.device)
+    else:
+        dk_acc = dv_acc = None
+        dk = torch.zeros(T, Hk, D, dtype=q.dtype, device=q.device)
+        dv = torch.zeros(T, Hk, D, dtype=q.dtype, device=q.device)
     global LAUNCH_COUNT
     _check(lib().ttb_attn_bwd(_p(q), _p(k), C.c_longlong(k.stride(0)), _p(v), C.c_longlong(v.stride(0)), _p(out),
-                              _p(dout), _p(lse), _p(delta), _p(dq_acc), _p(dq), _p(dk), _p(dv), _p(kv_tiles_dev),
+                              _p(dout), _p(lse), _p(delta), _p(dq_acc), _p(dk_acc), _p(dv_acc), _p(dq), _p(dk), _p(dv),
+                              _p(kv_tiles_dev),
                               C.c_int(kv_tiles_dev.shape[0]), C.c_longlong(T), C.c_int(Hq), C.c_int(Hk), C.c_int(D),
                               C.c_float(scale), C.c_int(int(causal)), _stream()), "ttb_attn_bwd")
-    LAUNCH_COUNT += 2
+    LAUNCH_COUNT += 2 if Hq == Hk else 4
     return dq, dk, dv

@@ -440,7 +440,8 @@ class LinearCrossEntropyFn(torch.autograd.Function):
         dh = torch.empty_like(h2) if need_h else None
         mg = getattr(weight, "main_grad", None)
         dw = None
-        if need_w:
+        single = T <= chunk_size
+        if need_w and not single:
             dw = mg if mg is not None else torch.zeros(V, h2.shape[1], dtype=torch.float32, device=h2.device)
         total = torch.zeros((), dtype=torch.float32, device=h2.device)
         for s in range(0, T, chunk_size):
@@ -451,7 +452,13 @@ class LinearCrossEntropyFn(torch.autograd.Function):
             if need_h:
                 K.gemm(logits, weight, b_mn=True, out=dh[s:s + chunk_size])
             if need_w:
-                K.gemm(logits, hc, a_mn=True, b_mn=True, out=dw, accumulate=True)
+                if single and mg is None:
+                    # one chunk: the weight gradient is written once, in the weight's dtype, with no accumulator pass
+                    dw = K.gemm(logits, hc, a_mn=True, b_mn=True, out_dtype=weight.dtype)
+                else:
+                    if dw is None:
+                        dw = mg
+                    K.gemm(logits, hc, a_mn=True, b_mn=True, out=dw, accumulate=True)
         ctx.save_for_backward(dh, dw if (need_w and mg is None) else None)
         ctx.meta = (hidden.shape, weight.dtype, mg is not None)
         return total

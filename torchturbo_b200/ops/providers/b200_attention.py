@@ -20,14 +20,16 @@ def _tiles_for(cu_seqlens, device):
     """(query-tile table on the device, number of valid tokens, boundaries on the device) for one batch; built
     once and shared by every layer (pinned staging keeps the copies asynchronous)."""
     t = K.build_q_tiles(cu_seqlens).pin_memory()
+    tk = K.build_kv_tiles(cu_seqlens).pin_memory()
     cu = cu_seqlens.to(torch.int32).pin_memory()
-    return t.to(device, non_blocking=True), int(cu_seqlens[-1]), cu.to(device, non_blocking=True)
+    return (t.to(device, non_blocking=True), int(cu_seqlens[-1]), cu.to(device, non_blocking=True),
+            tk.to(device, non_blocking=True))
 
 
 class FlashAttnFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, cu_seqlens, max_seqlen, causal, scale, want_ml):
-        tiles, n_valid, _ = _tiles_for(cu_seqlens, q.device)
+        tiles, n_valid = _tiles_for(cu_seqlens, q.device)[:2]
         out, lse, ml = K.attn_fwd(q, k, v, tiles, scale=scale, causal=causal, want_max_logit=want_ml)
         ctx.save_for_backward(q, k, v, out, lse)
         ctx.meta = (cu_seqlens, max_seqlen, causal, scale, n_valid)
@@ -41,7 +43,7 @@ class FlashAttnFn(torch.autograd.Function):
         q, k, v, out, lse = ctx.saved_tensors
         cu_seqlens, max_seqlen, causal, scale, n = ctx.meta
         if os.environ.get("TORCHTURBO_ATTN_BWD", "tcgen05") == "tcgen05":
-            tiles = _tiles_for(cu_seqlens, q.device)[0]
+            tiles = _tiles_for(cu_seqlens, q.device)[3]
             dq, dk, dv = K.attn_bwd(dout.contiguous(), q, k, v, out, lse, tiles, scale=scale, causal=causal)
             return dq, dk, dv, None, None, None, None, None
         # library backward on this kernel's out / lse (selected with TORCHTURBO_ATTN_BWD=flash_attn2; used as a baseline)
