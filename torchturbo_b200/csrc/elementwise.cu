@@ -705,3 +705,72 @@ TTB_EXPORT int ttb_clip_coef(const float* partial, int n, const float* extra_sq,
   clip_coef_kernel<<<1, 1024, 0, STREAM(stream)>>>(partial, n, extra_sq, max_norm, out3);
   LAUNCH_RET();
 }
+
+// ----------------------------------------------------------------------------
+// Allocation-free RMSNorm backward (see ttb_noalloc.h for the contract).
+// The scratch that ttb_rmsnorm_bwd receives from its caller lives here in a file-scope device array.  In host code
+// the name `g_noalloc_scratch` is only a handle for the runtime; the address a kernel can use comes from
+// cudaGetSymbolAddress, looked up once per device with that device current.
+// ----------------------------------------------------------------------------
+#include "ttb_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_scratch[TTB_NOALLOC_BLOCKS * TTB_NOALLOC_MAX_H];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+
+// Device address of the scratch array on the current device (cached).  Returns 0 or a TTB_NOALLOC_ERR_SYMBOL code.
+int noalloc_scratch(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) return TTB_NOALLOC_ERR_SYMBOL + static_cast<int>(e);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) return TTB_NOALLOC_ERR_SYMBOL + static_cast<int>(e);
+    g_noalloc_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_noalloc_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+TTB_EXPORT int ttb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd,
+                                       const void* dres_in, void* dx, float* dw_out, long long T, int H,
+                                       int one_plus_w, void* stream) {
+  if (H <= 0 || (H % 8) != 0 || H > TTB_NOALLOC_MAX_H || T < 0) return TTB_NOALLOC_ERR_SIZE;
+  if (T == 0) return TTB_NOALLOC_OK;
+  float* scratch = nullptr;
+  const int rc = noalloc_scratch(&scratch);
+  if (rc != 0) return rc;
+  int threads = H / 8;
+  threads = threads > 256 ? 256 : ((threads + 31) / 32) * 32;
+  const int iters = (H + threads * 8 - 1) / (threads * 8);
+  int grid = TTB_NOALLOC_BLOCKS;
+  if (grid > T) grid = static_cast<int>(T);
+  auto DY = (const __nv_bfloat16*)dy; auto X = (const __nv_bfloat16*)x; auto W = (const __nv_bfloat16*)w;
+  // every block writes its full row of `scratch` (H floats), and the column sum below reads exactly rows [0, grid):
+  // nothing has to be cleared between calls
+  if (iters <= 1)
+    rmsnorm_bwd_kernel<1><<<grid, threads, 0, STREAM(stream)>>>(DY, X, W, rstd, (const __nv_bfloat16*)dres_in,
+                                                               (__nv_bfloat16*)dx, scratch, T, H, one_plus_w);
+  else
+    rmsnorm_bwd_kernel<4><<<grid, threads, 0, STREAM(stream)>>>(DY, X, W, rstd, (const __nv_bfloat16*)dres_in,
+                                                               (__nv_bfloat16*)dx, scratch, T, H, one_plus_w);
+  colsum_kernel<<<(H + 255) / 256, 256, 0, STREAM(stream)>>>(scratch, dw_out, grid, H);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TTB_NOALLOC_OK : TTB_NOALLOC_ERR_LAUNCH + static_cast<int>(e);
+}
+
+TTB_EXPORT const char* ttb_noalloc_strerror(int code) {
+  if (code == TTB_NOALLOC_OK) return "ok";
+  if (code == TTB_NOALLOC_ERR_SIZE)
+    return "ttb_rmsnorm_bwd_noalloc: H must be a positive multiple of 8 and at most 8192 (TTB_NOALLOC_MAX_H), T >= 0";
+  if (code >= TTB_NOALLOC_ERR_SYMBOL && code < TTB_NOALLOC_ERR_SYMBOL + 1000 - 10)
+    return "ttb_rmsnorm_bwd_noalloc: could not resolve the device address of the built-in scratch array "
+           "(cudaGetDevice / cudaGetSymbolAddress failed; code - 910 is the CUDA error)";
+  if (code >= TTB_NOALLOC_ERR_LAUNCH && code < TTB_NOALLOC_ERR_SIZE)
+    return "ttb_rmsnorm_bwd_noalloc: kernel launch failed (code - 400 is the CUDA error)";
+  return "ttb_rmsnorm_bwd_noalloc: unknown error code";
+}
