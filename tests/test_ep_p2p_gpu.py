@@ -17,6 +17,7 @@ def _worker(rank, world, init_file, err_dir):
         import torch.distributed as dist
 
         os.environ["NCCL_NVLS_ENABLE"] = "0"
+        os.environ["LOCAL_RANK"] = str(rank)
         torch.cuda.set_device(rank)
         dist.init_process_group("nccl", init_method=f"file://{init_file}", rank=rank, world_size=world,
                                 timeout=datetime.timedelta(seconds=120), device_id=torch.device("cuda", rank))

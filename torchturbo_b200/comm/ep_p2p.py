@@ -50,7 +50,7 @@ class EPWorkspace:
         dev = self.buf.local.device
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         self.done = torch.zeros(1, dtype=torch.int32, device=dev)
-        self.budget_ms = int(os.environ.get("TORCHTURBO_P2P_WAIT_MS", "20000"))
+        self.budget_ms = int(os.environ.get("TORCHTURBO_P2P_WAIT_MS", "5000"))
         self.ptrs = self.buf.peer_ptrs
 
     # -- primitives ---------------------------------------------------------------------------------
@@ -86,11 +86,17 @@ class EPWorkspace:
 
 
 def get_workspace(group, hidden, num_experts, tokens, topk, capacity_factor=2.0) -> EPWorkspace:
+    """One workspace per (group, hidden, experts, top-k), created at first use.  Every rank must carve identical
+    offsets, so the token count that sizes it is the maximum over the group (one all-reduce, once); it never grows
+    afterwards, because a rank cannot know that a peer wants to: a later batch that does not fit raises the
+    capacity status instead.  `TORCHTURBO_EP_MAX_TOKENS` presets the per-rank token count."""
     key = (id(group), hidden, num_experts, topk)
     ws = _WORKSPACES.get(key)
-    need = int(tokens * topk * capacity_factor)
-    if ws is None or ws.cap < need:
-        ws = EPWorkspace(group, hidden, num_experts, tokens, topk, capacity_factor)
+    if ws is None:
+        preset = int(os.environ.get("TORCHTURBO_EP_MAX_TOKENS", "0"))
+        t = torch.tensor([max(tokens, preset)], dtype=torch.int64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+        ws = EPWorkspace(group, hidden, num_experts, int(t.item()), topk, capacity_factor)
         _WORKSPACES[key] = ws
     return ws
 

@@ -12,6 +12,8 @@ engine/distributed.py, models/modules/comm/comm.py).
 """
 from __future__ import annotations
 
+import importlib
+
 import ctypes as C
 
 import torch
@@ -73,7 +75,7 @@ class SymmetricBuffer:
         if not (torch.cuda.is_available() and dist.is_initialized()):
             return False
         try:
-            import torch.distributed._symmetric_memory  # noqa: F401
+            importlib.import_module("torch.distributed._symmetric_memory")
         except Exception:
             return False
         g = group if group is not None else dist.group.WORLD

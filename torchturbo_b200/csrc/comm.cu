@@ -42,6 +42,8 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
 __device__ __forceinline__ bool wait_flag(const int* flag, int epoch, unsigned long long budget_ns, unsigned site,
                                           unsigned peer, int* status) {
   if (ld_acquire_sys(flag) >= epoch) return true;
+  // once any wait of this workspace has failed, later waits give up at once: the total stall stays within one budget
+  if (status && *reinterpret_cast<volatile int*>(status) != 0) return false;
   const uint64_t t0 = globaltimer_ns();
   while (ld_acquire_sys(flag) < epoch) {
     if (globaltimer_ns() - t0 > budget_ns) {
@@ -97,7 +99,17 @@ __global__ void ep_exchange_kernel(const EpExchangeParams p) {
     if (!wait_flag(f, p.epoch, p.budget_ns, 1, threadIdx.x, p.status)) s_ok = 0;
   }
   __syncthreads();
-  if (!s_ok) return;
+  if (!s_ok) {
+    // a peer never answered: leave tables that make every later kernel of this layer a no-op (no rows, no tiles,
+    // destination rows outside the buffer, which the scatter kernel skips) instead of uninitialised indices
+    for (int e = threadIdx.x; e < E; e += blockDim.x) p.dest_base[e] = -(1 << 30);
+    for (int el = threadIdx.x; el <= El; el += blockDim.x) {
+      p.seg_start[el] = 0;
+      if (el < El) p.recv_counts[el] = 0;
+    }
+    for (int m = threadIdx.x; m < p.m_tiles_cap; m += blockDim.x) p.tile_group[m] = -1;
+    return;
+  }
   const int* mine = reinterpret_cast<const int*>(p.peers.base[p.rank] + p.off_counts);
   for (int i = threadIdx.x; i < W * E; i += blockDim.x) s_counts[i] = mine[i];
   __syncthreads();

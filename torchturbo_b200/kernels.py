@@ -94,6 +94,13 @@ def _stream() -> C.c_void_p:
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+def check_device(t: torch.Tensor) -> None:
+    """Kernels run on the current device's stream: an operand of another GPU would be an illegal address there."""
+    if t.device.index != torch.cuda.current_device():
+        raise KernelError(f"operand lives on {t.device} but the current CUDA device is {torch.cuda.current_device()}; "
+                          "call torch.cuda.set_device() for this process before using the ops")
+
+
 def _p(t: torch.Tensor | None) -> C.c_void_p:
     return C.c_void_p(0 if t is None else t.data_ptr())
 
@@ -143,6 +150,7 @@ def gemm(
     """
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
     assert a.stride(-1) == 1 and b.stride(-1) == 1
+    check_device(a)
     args = _GemmArgs()
     groups_k = 0
     if group_rows is not None:

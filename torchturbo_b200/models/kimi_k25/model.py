@@ -1,0 +1,167 @@
+"""`kimi_k25`: Kimi-K2.5, a DeepSeek-V3 language model (MLA + sigmoid group-limited MoE with shared experts) behind
+a ViT tower whose merged patch features replace the media placeholder tokens.
+
+Module tree as in models/kimi_k25/modeling_kimi_k25.py:901-925 of the reference: `vision_tower`, `mm_projector`
+(folded into the tower's merger here) and `language_model` (`.model`, `.lm_head`).  Plan
+(models/kimi_k25/parallel_plan.py:60-133): experts on the expert-data-parallel mesh, MoE blocks rebuilt EP-aware,
+decoder layers and tower blocks checkpointed, the tower world-sharded with vision balancing; Ulysses attention is
+bound per attention instance.  Muon recipe with MLA QK-clip as for the other MLA families."""
+from __future__ import annotations
+
+from typing import Any
+
+import torch
+import torch.nn as nn
+
+from ...engine.metrics.flops import VLMFlops
+from ...parallel import FSDPPlanSpec, VisionBalanceMode, VisionBalanceSpec
+from ..base import TurboVLMModel
+from ..config import ModelConfig
+from ..modules.deepseek import DeepseekV3Config, DeepseekV3ForCausalLMBase, DeepseekWeightConverter, deepseek_plan
+from ..modules.transformer import CausalLMOutput
+from ..modules.vision import GridVisionBalanceIO
+from ..qwen3_5.modeling import as_dtype, init_hybrid_weights
+from ..qwen3_vl.modeling import Qwen3VLVisionConfig, VisionTower
+from ..registry import register_model
+
+
+class KimiK25Config(ModelConfig):
+    model_type = "kimi_k25"
+    _defaults = dict(media_placeholder_token_id=163605, pad_token_id=0, ignore_index=-100, tie_word_embeddings=False,
+                     initializer_range=0.02)
+
+    def __init__(self, text_config=None, vision_config=None, **kw):
+        super().__init__(**kw)
+        self.text_config = text_config if isinstance(text_config, ModelConfig) else DeepseekV3Config(**(text_config or {}))
+        if not isinstance(vision_config, ModelConfig):
+            vc = dict(vision_config or {})
+            # MoonViT key names -> the tower's
+            for src, dst in (("vt_num_hidden_layers", "depth"), ("vt_hidden_size", "hidden_size"),
+                             ("vt_num_attention_heads", "num_heads"), ("vt_intermediate_size", "intermediate_size")):
+                if src in vc:
+                    vc.setdefault(dst, vc.pop(src))
+            if "merge_kernel_size" in vc:
+                vc.setdefault("spatial_merge_size", int(tuple(vc.pop("merge_kernel_size"))[0]))
+            vc.setdefault("temporal_patch_size", 1)
+            vc.setdefault("out_hidden_size", self.text_config.hidden_size)
+            vision_config = Qwen3VLVisionConfig(**{k: v for k, v in vc.items() if not k.startswith("_")})
+        self.vision_config = vision_config
+        for k in ("hidden_size", "vocab_size", "num_hidden_layers", "num_attention_heads", "n_routed_experts",
+                  "moe_intermediate_size", "num_experts"):
+            setattr(self, k, getattr(self.text_config, k))
+        self.image_token_id = self.media_placeholder_token_id
+
+    @property
+    def dtype(self):
+        return getattr(self.text_config, "dtype", None) or getattr(self.text_config, "torch_dtype", None)
+
+    @dtype.setter
+    def dtype(self, v):
+        self.text_config.torch_dtype = v
+        self.text_config.dtype = v
+
+
+class KimiK25ForConditionalGenerationBase(nn.Module):
+    def __init__(self, config: Any):
+        super().__init__()
+        self.config = config
+        dtype = as_dtype(config.dtype)
+        self.vision_tower = VisionTower(config.vision_config, dtype)
+        self.language_model = DeepseekV3ForCausalLMBase(config.text_config)
+        if not any(p.is_meta for p in self.vision_tower.parameters()):
+            init_hybrid_weights(self.vision_tower, config.initializer_range)
+
+    @property
+    def lm_head(self):
+        return self.language_model.lm_head
+
+    def tie_weights(self) -> None:
+        self.language_model.tie_weights()
+
+    @property
+    def all_tied_weights_keys(self):
+        return {f"language_model.{k}": f"language_model.{v}" for k, v in self.language_model.all_tied_weights_keys.items()}
+
+    def fuse_media(self, input_ids, pixel_values, grid_thw):
+        emb = self.language_model.model.embed_tokens(input_ids)
+        if pixel_values is None:
+            v_in, grid = self.vision_tower.dummy_inputs(emb.device, emb.dtype)
+            return emb + 0.0 * self.vision_tower(v_in, grid_thw=grid).sum()
+        feats = self.vision_tower(pixel_values, grid_thw=grid_thw)
+        mask = input_ids == self.config.media_placeholder_token_id
+        n = int(mask.sum())
+        if n == 0:
+            return emb + 0.0 * feats.sum()
+        if n != feats.shape[0]:
+            raise ValueError(f"{n} media placeholder tokens but {feats.shape[0]} media features")
+        return emb.masked_scatter(mask.unsqueeze(-1), feats.to(emb.dtype))
+
+    def forward(self, input_ids=None, position_ids=None, pixel_values=None, grid_thws=None, image_grid_thw=None,
+                inputs_embeds=None, skip_lm_head=False, **kw):
+        grid = grid_thws if grid_thws is not None else image_grid_thw
+        if inputs_embeds is None:
+            inputs_embeds = self.fuse_media(input_ids, pixel_values, grid)
+        out = self.language_model(input_ids=None, position_ids=position_ids, inputs_embeds=inputs_embeds,
+                                  skip_lm_head=skip_lm_head, global_input_ids=input_ids, **kw)
+        return CausalLMOutput(out)
+
+
+def get_parallel_plan():
+    plan = deepseek_plan("language_model.model")
+    plan.plan.update({
+        "vision_tower.blocks.*": FSDPPlanSpec(activation_checkpoint=True),
+        "vision_tower": FSDPPlanSpec(standalone_world_shard=True, vision_balance=VisionBalanceSpec(
+            mode=VisionBalanceMode.PATCH_SQ, io=GridVisionBalanceIO(2))),
+        "language_model.model.embed_tokens": FSDPPlanSpec(standalone_world_shard=True),
+        "language_model.lm_head": FSDPPlanSpec(standalone_world_shard=True),
+    })
+    return plan
+
+
+@register_model("kimi_k25")
+class TurboKimiK25ForConditionalGeneration(TurboVLMModel, KimiK25ForConditionalGenerationBase):
+    config_class = KimiK25Config
+    multimodal_input_keys = ("pixel_values", "grid_thws", "image_grid_thw")
+
+    @classmethod
+    def get_default_parallel_plan(cls, **kwargs):
+        return get_parallel_plan()
+
+    def get_norm(self):
+        return self.language_model.model.norm
+
+    def get_lm_head(self):
+        return self.language_model.lm_head
+
+    def get_input_embeddings(self):
+        return self.language_model.model.embed_tokens
+
+    def get_language_model(self):
+        return self.language_model.model
+
+    def get_sequence_parallel_input_slicing_spec(self):
+        from ..modules.attention.ulysses import SequenceParallelInputSlicingSpec
+
+        lm = self.language_model
+        return SequenceParallelInputSlicingSpec(lm, type(lm).forward)
+
+    def on_parallelized(self, parallel_context) -> None:
+        sp = parallel_context["sp"]
+        self.language_model.model.set_sequence_parallel(sp["sp_group"], sp["sp_size"], sp["sp_rank"])
+
+    def on_materialized(self) -> None:
+        self.language_model.model.rotary_emb.reset(self.language_model.lm_head.weight.device)
+        self.tie_weights()
+
+    def get_weight_converter(self, parallel_context, model_path=None):
+        return DeepseekWeightConverter(self, parallel_context, model_path)
+
+    def get_flops_class(self):
+        return VLMFlops
+
+    def get_optimizer_recipe(self, optimizer_name: str):
+        from ...engine.optimizers.muon import default_decoder_muon_recipe
+
+        if optimizer_name == "muon":
+            return default_decoder_muon_recipe(self)
+        return super().get_optimizer_recipe(optimizer_name)

@@ -46,6 +46,7 @@ class MoELayerConfig:
     params_dtype: torch.dtype = torch.float32
     init_method_std: float = 0.02
     moe_shared_expert_intermediate_size: Optional[int] = None
+    moe_shared_expert_gate: bool = False          # sigmoid(x @ w) scales the shared expert's output (Qwen MoE)
     moe_aux_loss_coeff: float = 0.0
     moe_z_loss_coeff: float = 0.0
     moe_router_num_groups: Optional[int] = None
@@ -365,7 +366,8 @@ class MoELayer(BaseMoELayer):
         self.experts = GroupedMLP(config, self.num_local_experts)
         self.token_dispatcher = self._build_dispatcher()
         si = config.moe_shared_expert_intermediate_size
-        self.shared_experts = SharedExpertMLP(config.hidden_size, si, config.params_dtype) if si else None
+        self.shared_experts = SharedExpertMLP(config.hidden_size, si, config.params_dtype, config.moe_shared_expert_gate,
+                                              config.init_method_std) if si else None
 
     def _build_dispatcher(self):
         transport = self.config.moe_token_dispatcher_transport

@@ -73,6 +73,9 @@ class LoadRecipe:
 class BaseWeightConverter:
     expert_gate, expert_up, expert_down = "gate_proj", "up_proj", "down_proj"
     hf_router_name, router_name = "gate", "router"
+    hf_shared_expert_name = "shared_expert"          # DeepSeek-style checkpoints call it `shared_experts`
+    # family-specific (engine regex, Hugging Face replacement) pairs applied to every name before the generic rules
+    extra_renames: tuple[tuple[str, str], ...] = ()
 
     def __init__(self, model, parallel_context: dict | None = None, model_path: str | None = None):
         self.model = model
@@ -93,9 +96,12 @@ class BaseWeightConverter:
 
     def to_hf_name(self, name: str) -> str:
         """Engine FQN -> Hugging Face name for tensors that map one-to-one."""
+        for pat, repl in self.extra_renames:
+            name = re.sub(pat, repl, name)
         name = re.sub(r"\.mlp\.router\.weight$", f".mlp.{self.hf_router_name}.weight", name)
         name = re.sub(r"\.mlp\.router\.expert_bias$", f".mlp.{self.hf_router_name}.e_score_correction_bias", name)
-        name = re.sub(r"\.mlp\.shared_experts\.", ".mlp.shared_expert.", name)
+        name = re.sub(r"\.mlp\.shared_experts\.gate\.weight$", f".mlp.{self.hf_shared_expert_name}_gate.weight", name)
+        name = re.sub(r"\.mlp\.shared_experts\.", f".mlp.{self.hf_shared_expert_name}.", name)
         return name
 
     def local_expert_ids(self) -> range:

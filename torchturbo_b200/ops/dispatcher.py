@@ -21,6 +21,7 @@ from .registry import REGISTRY
 logger = get_logger(__name__)
 
 _PROVIDER_MODULES = ("torchturbo_b200.ops.providers.native", "torchturbo_b200.ops.providers.native_linear_attention",
+                     "torchturbo_b200.ops.providers.native_sparse_attention",
                      "torchturbo_b200.ops.providers.b200")
 
 

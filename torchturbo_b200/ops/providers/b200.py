@@ -10,6 +10,7 @@ from __future__ import annotations
 import math
 
 import torch
+import torch.nn.functional as F
 
 from ... import kernels as K
 from ...runtime import TurboDevice
@@ -497,17 +498,26 @@ class FlashAttn2Varlen(_B200Op):
             return False
 
     def __call__(self, q, k, v, cu_seqlens, max_seqlen=None, *, causal=True, scale=None):
-        if not _ok(q, k, v):
+        D, Dv = q.shape[-1], v.shape[-1]
+        if not _ok(q, k, v) or D > 256 or Dv > D:
             return N.attention_ref(q, k, v, cu_seqlens, causal, scale)
         from flash_attn import flash_attn_varlen_func
 
         T = q.shape[0]
+        scale = scale if scale is not None else 1.0 / math.sqrt(D)
+        pad_d = (-D) % 8
+        if pad_d or Dv != D:
+            # the library wants equal, 8-aligned head widths: zero columns change neither the scores nor the output
+            q, k = F.pad(q, (0, pad_d)), F.pad(k, (0, pad_d))
+            v = F.pad(v, (0, D + pad_d - Dv))
         n = int(cu_seqlens[-1])  # boundaries live on the host in the packed-batch contract
         if max_seqlen is None:
             max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max())
         cu = cu_seqlens.to(device=q.device, dtype=torch.int32)
         out = flash_attn_varlen_func(q[:n], k[:n], v[:n], cu, cu, max_seqlen, max_seqlen, softmax_scale=scale,
                                      causal=causal)
+        if out.shape[-1] != Dv:
+            out = out[..., :Dv]
         if n < T:  # tokens after the last boundary are padding: zeros
             out = torch.nn.functional.pad(out, (0, 0, 0, 0, 0, T - n))
         return out

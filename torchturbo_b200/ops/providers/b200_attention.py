@@ -59,8 +59,17 @@ class FlashAttnFn(torch.autograd.Function):
         return dq, dk, dv, None, None, None, None, None
 
 
+def _LIB_FALLBACK(q, k, v, cu_seqlens, max_seqlen, *, causal, scale):
+    from .b200 import FlashAttn2Varlen
+
+    lib = FlashAttn2Varlen()
+    if lib.available():
+        return lib(q, k, v, cu_seqlens, max_seqlen, causal=causal, scale=scale)
+    return N.attention_ref(q, k, v, cu_seqlens, causal, scale)
+
+
 def _usable(q, k, v):
-    return _ok(q, k, v) and q.shape[-1] == 128 and q.dim() == 3 and q.shape[1] % k.shape[1] == 0 and v.stride(2) == 1 \
+    return _ok(q, k, v) and q.shape[-1] == 128 and v.shape[-1] == 128 and q.dim() == 3 and q.shape[1] % k.shape[1] == 0 and v.stride(2) == 1 \
         and v.stride(1) == 128
 
 
@@ -69,7 +78,8 @@ def _usable(q, k, v):
 class B200Attention(_B200Op):
     def __call__(self, q, k, v, cu_seqlens, max_seqlen=None, *, causal=True, scale=None):
         if not _usable(q, k, v):
-            return N.attention_ref(q, k, v, cu_seqlens, causal, scale)
+            # other head widths (ViT 72, MLA 192/128): the library kernel, which pads to what it supports
+            return _LIB_FALLBACK(q, k, v, cu_seqlens, max_seqlen, causal=causal, scale=scale)
         scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
         cu = cu_seqlens if isinstance(cu_seqlens, torch.Tensor) else torch.tensor(cu_seqlens, dtype=torch.int32)
         return FlashAttnFn.apply(q.contiguous(), k.contiguous(), v, cu.cpu() if cu.is_cuda else cu, max_seqlen, causal,

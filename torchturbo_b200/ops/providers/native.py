@@ -311,7 +311,7 @@ def attention_ref(q, k, v, cu_seqlens, causal=True, scale=None, want_max_logits=
     Hk = k.shape[1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     offs = [int(c) for c in (cu_seqlens.tolist() if isinstance(cu_seqlens, torch.Tensor) else cu_seqlens)]
-    out = torch.zeros_like(q)
+    out = q.new_zeros(T, Hq, v.shape[-1])        # value heads may be narrower than q/k heads (MLA)
     max_logits = torch.full((Hq,), -float("inf"), dtype=torch.float32, device=q.device)
     rep = Hq // Hk
     pieces = []

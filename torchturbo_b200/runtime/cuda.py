@@ -69,9 +69,17 @@ class CudaRuntime(DeviceRuntime):
         return torch.cuda.is_available()
 
     def initialize(self) -> None:
-        local = int(os.environ.get("LOCAL_RANK", "0"))
-        if torch.cuda.device_count() > 0:
-            torch.cuda.set_device(local % torch.cuda.device_count())
+        """Bind the process to its GPU.  Under a launcher `LOCAL_RANK` names it.  Without that variable the
+        process keeps whatever device it already selected: the runtime is created lazily (first op dispatch), and
+        switching devices then would launch kernels on one GPU with pointers of another."""
+        local = os.environ.get("LOCAL_RANK")
+        if local is None or torch.cuda.device_count() == 0:
+            return
+        want = int(local) % torch.cuda.device_count()
+        if torch.cuda.is_initialized() and torch.cuda.current_device() != want:
+            # the application chose another device explicitly before the first op; respect it
+            return
+        torch.cuda.set_device(want)
 
     def use_deterministic_algorithms(self) -> None:
         os.environ.setdefault("CUBLAS_WORKSPACE_CONFIG", ":4096:8")
