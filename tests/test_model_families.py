@@ -28,6 +28,11 @@ def _build(model_type):
                                       topk_group=1, moe_intermediate_size=16, moe_shared_expert_intermediate_size=16,
                                       layer_group_size=3, num_nextn_predict_layers=1, pad_token_id=0,
                                       gated_attention_proj_granularity_type="head_wise", **MLA))
+    elif model_type == "bailing_moe_v3_vl":
+        tc = dict(TEXT, num_hidden_layers=5, head_dim=8, num_experts=8, num_experts_per_tok=2, n_group=2, topk_group=1,
+                  moe_intermediate_size=16, moe_shared_expert_intermediate_size=16, layer_group_size=3,
+                  num_nextn_predict_layers=1, pad_token_id=0, **MLA)
+        cfg = cls.config_class(text_config=tc, vision_config=VISION, image_patch_token=5, video_patch_token=4)
     elif model_type == "kimi_k25":
         cfg = cls.config_class(text_config=DSV3, media_placeholder_token_id=5,
                                vision_config=dict(vt_num_hidden_layers=1, vt_hidden_size=16, vt_num_attention_heads=2,
@@ -52,7 +57,7 @@ def _batch(vlm: bool, media_key="image_grid_thw"):
     return b
 
 
-FAMILIES = ["qwen3_5", "qwen3_5_moe", "qwen3_5_moe_text", "bailing_hybrid", "kimi_k25", "glm_moe_dsa"]
+FAMILIES = ["qwen3_5", "qwen3_5_moe", "qwen3_5_moe_text", "bailing_hybrid", "bailing_moe_v3_vl", "kimi_k25", "glm_moe_dsa"]
 
 
 def test_all_families_registered():
@@ -63,7 +68,7 @@ def test_all_families_registered():
 def test_family_forward_backward_and_isolation(model_type):
     cls, m = _build(model_type)
     m.train()
-    vlm = model_type in ("qwen3_5", "qwen3_5_moe", "kimi_k25")
+    vlm = model_type in ("qwen3_5", "qwen3_5_moe", "kimi_k25", "bailing_moe_v3_vl")
     b = _batch(vlm, "grid_thws" if model_type == "kimi_k25" else "image_grid_thw")
     out = m(**b)
     assert out.logits.shape == (1, 24, 128) and torch.isfinite(out.logits).all()

@@ -1,0 +1,60 @@
+"""Where one training step spends its time: CPU issue time per step (host-bound or not) and the torch profiler's
+per-kernel device time of one step of the flagship model at a reduced depth.
+
+    python -m torchturbo_b200.benchmarks.step_profile [--layers 4] [--model qwen3_moe_30b_a3b] [--seq-len 4096] [--rows 40]
+"""
+from __future__ import annotations
+
+import argparse
+import sys
+import time
+from pathlib import Path
+
+import torch
+
+
+def main(argv=None) -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--layers", type=int, default=4)
+    ap.add_argument("--model", default="qwen3_moe_30b_a3b")
+    ap.add_argument("--seq-len", type=int, default=4096)
+    ap.add_argument("--rows", type=int, default=40)
+    args = ap.parse_args(argv)
+    sys.path.insert(0, str(Path(__file__).resolve().parents[2]))
+    from bench import model_config  # the benchmark's model table (repository root)
+
+    from ..data import PackedCollator, SyntheticPackedDataset
+    from ..engine import EngineConfig, TorchTurboEngine
+    from ..engine.optimizers import OptimizerClassPlan
+    from ..loops import train_step
+
+    eng = TorchTurboEngine(EngineConfig.from_dict({"mixed_precision": "bf16", "moe": {"aux_loss_coeff": 1e-3},
+                                                   "activation_checkpointing": {"enabled": False}}))
+    mc = model_config(args.model, args.layers)
+    model = eng.build_model(None, load_weights=False, init_kwargs={"config": mc})
+    opt = eng.prepare_optimizer(model, OptimizerClassPlan(torch.optim.AdamW, lr=1e-5))
+    ds = SyntheticPackedDataset(8, args.seq_len, mc["vocab_size"], min_doc=256, max_doc=args.seq_len, seed=1)
+    batches = []
+    for i in range(6):
+        b = PackedCollator()([ds[i]])
+        batches.append({k: (v.cuda() if isinstance(v, torch.Tensor) and not k.startswith("cu_seq") else v) for k, v in b.items()})
+    for i in range(3):
+        train_step(eng, model, opt, [batches[i]], check_finite=False)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for i in range(3):
+        train_step(eng, model, opt, [batches[3 + i]], check_finite=False)
+    t1 = time.perf_counter()
+    torch.cuda.synchronize()
+    t2 = time.perf_counter()
+    print(f"cpu issue time per step {(t1 - t0) / 3 * 1e3:.1f} ms, total per step {(t2 - t0) / 3 * 1e3:.1f} ms")
+    from torch.profiler import ProfilerActivity, profile
+
+    with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+        train_step(eng, model, opt, [batches[0]], check_finite=False)
+        torch.cuda.synchronize()
+    print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=args.rows, max_name_column_width=70))
+
+
+if __name__ == "__main__":
+    main()
