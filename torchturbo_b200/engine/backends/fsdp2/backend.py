@@ -56,6 +56,18 @@ def _recompute_ctx():
         _RECOMPUTE["active"] = prev
 
 
+def confidence_entropy_sum(logits: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100):
+    """(sum of softmax entropies over rows whose argmax equals the label, number of such rows): both summable, so
+    they can be reduced across ranks before the division."""
+    valid = labels != ignore_index
+    correct = (logits.argmax(-1) == labels) & valid
+    n = correct.sum()
+    lp = torch.log_softmax(logits.float(), dim=-1)
+    ent = -(lp.exp() * lp).sum(-1)
+    return (ent * correct.to(ent.dtype)).sum(), n
+
+
+
 @register_backend("fsdp2")
 class FSDP2Backend(BaseBackend):
     def __init__(self, config: EngineConfig, runtime) -> None:
@@ -634,6 +646,58 @@ class FSDP2Backend(BaseBackend):
             if k != "main":
                 out[f"{k}_loss"] = v
         return (total, out) if return_outputs else total
+
+    def compute_diffusion_loss(self, model: nn.Module, inputs: dict[str, Any], *, ga: int = 1,
+                               return_outputs: bool = False, **_unused):
+        """Block-diffusion loss: unshifted cross entropy over the supervised (masked, noisy-half) positions of a
+        `[noisy | clean]` row, plus `cap_lambda` times the mean prediction entropy over the positions the model
+        already gets right (a confidence term).  Under SP the row is sliced, the block mask stays global; sums and
+        counts are all-reduced over the SP group and divided globally, so the value equals the SP=1 mean.  The
+        result is divided by `ga` (gradient-accumulation steps including the SP factor).  Same contract as
+        engine/backends/fsdp2/backend.py:2005-2090 of the reference."""
+        from ....models.modules.attention.ulysses import slice_input_tensor
+        from ....models.modules.comm import all_reduce_sum_autograd
+
+        if self.config.loss_chunk.enabled:
+            raise NotImplementedError("chunked LM loss does not support diffusion training")
+        inputs = dict(self.prepare_inputs(model, inputs))
+        inputs.pop("bd_structure", None)
+        inputs.pop("attention_mask", None)
+        labels = inputs.pop("labels").to(self.device)
+        self._prepare_moe_runtime_for_row(model, inputs)
+        out = model(**inputs)
+        logits = out["logits"]
+        n_valid = (labels != -100).sum()
+        if self.sp_size > 1:
+            labels = slice_input_tensor(labels, 1, self.sp_group, self.sp_rank)
+        flat, lab = logits.reshape(-1, logits.shape[-1]).float(), labels.reshape(-1)
+        loss_sum = torch.nn.functional.cross_entropy(flat, lab, ignore_index=-100, reduction="sum")
+        cap = float(self.config.diffusion.cap_lambda)
+        ent_sum = n_correct = None
+        if cap > 0:
+            ent_sum, n_correct = confidence_entropy_sum(flat, lab)
+        if self.sp_size > 1:
+            loss_sum = all_reduce_sum_autograd(loss_sum, self.sp_group)
+            if cap > 0:
+                ent_sum = all_reduce_sum_autograd(ent_sum, self.sp_group)
+                n_correct = n_correct.clone()
+                dist.all_reduce(n_correct, group=self.sp_group)
+        loss = loss_sum / n_valid.clamp_min(1).to(loss_sum.dtype)
+        if cap > 0:
+            loss = loss + cap * ent_sum / n_correct.clamp_min(1).to(ent_sum.dtype)
+        loss = loss / ga
+        out["loss"] = loss
+        return (loss, out) if return_outputs else loss
+
+    def _prepare_moe_runtime_for_row(self, model: nn.Module, inputs: dict[str, Any]) -> None:
+        """MoE statistics of a diffusion row: no packed boundaries, nothing is padding."""
+        layers = [m for m in model.modules() if isinstance(m, BaseMoELayer)]
+        if layers:
+            from ....models.modules.moe import MoERuntimeInputs
+
+            rt = MoERuntimeInputs()
+            for m in layers:
+                m.set_runtime_inputs(rt)
 
     def _loss_chunk_size(self, hidden: torch.Tensor) -> int:
         if self.config.loss_chunk.enabled:

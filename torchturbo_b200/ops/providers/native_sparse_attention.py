@@ -121,3 +121,26 @@ class TorchSparseFlashMLA(OpImpl):
             kv = torch.cat((ori_kv, cmp_kv), dim=0)
         kv = kv.unsqueeze(1)
         return sparse_attention_ref(query, kv, kv, idx, softmax_scale, sinks)
+
+
+def masked_attention_ref(q, k, v, allow, scale=None):
+    """Dense attention under an explicit boolean mask.  q: [Tq, H, D]; k, v: [Tk, Hk, D]; allow: [Tq, Tk] (True =
+    may attend).  Rows without any allowed key produce zeros."""
+    Tq, H, D = q.shape
+    Hk = k.shape[1]
+    rep = H // Hk
+    scale = D ** -0.5 if scale is None else scale
+    qh = q.transpose(0, 1).unsqueeze(0)                                        # [1, H, Tq, D]
+    kh = k.transpose(0, 1).repeat_interleave(rep, 0).unsqueeze(0)
+    vh = v.transpose(0, 1).repeat_interleave(rep, 0).unsqueeze(0)
+    live = allow.any(-1)
+    m = allow | ~live[:, None]                                                 # dead rows: attend everywhere, zeroed below
+    o = torch.nn.functional.scaled_dot_product_attention(qh, kh, vh, attn_mask=m[None, None], scale=scale)
+    o = o[0].transpose(0, 1)
+    return o * live[:, None, None].to(o.dtype)
+
+
+@_native("masked_attention", "torch_masked_attention")
+class TorchMaskedAttention(OpImpl):
+    def __call__(self, q, k, v, allow, *, scale=None):
+        return masked_attention_ref(q, k, v, allow, scale)
