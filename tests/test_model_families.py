@@ -37,6 +37,11 @@ def _build(model_type):
         cfg = cls.config_class(text_config=DSV3, media_placeholder_token_id=5,
                                vision_config=dict(vt_num_hidden_layers=1, vt_hidden_size=16, vt_num_attention_heads=2,
                                                   vt_intermediate_size=32, patch_size=2, merge_kernel_size=(2, 2)))
+    elif model_type == "deepseek_v4":
+        cfg = cls.config_class(**dict(TEXT, moe_intermediate_size=16, num_hidden_layers=3, n_routed_experts=8, num_experts_per_tok=2,
+                                      q_lora_rank=16, qk_rope_head_dim=4, qk_nope_head_dim=12, o_groups=2, o_lora_rank=8,
+                                      sliding_window=4, compress_ratios=[1, 4, 2], index_n_heads=2, index_head_dim=8, index_topk=2,
+                                      hc_mult=2, hc_sinkhorn_iters=3, swiglu_limit=7.0, num_hash_layers=1, num_mtp_layers=1))
     elif model_type == "glm_moe_dsa":
         cfg = cls.config_class(**dict(DSV3, num_hidden_layers=4, n_group=1, num_nextn_predict_layers=0, index_topk=6,
                                       index_head_dim=8, index_n_heads=2, index_topk_freq=2, index_skip_topk_offset=1,
@@ -57,11 +62,12 @@ def _batch(vlm: bool, media_key="image_grid_thw"):
     return b
 
 
-FAMILIES = ["qwen3_5", "qwen3_5_moe", "qwen3_5_moe_text", "bailing_hybrid", "bailing_moe_v3_vl", "kimi_k25", "glm_moe_dsa"]
+FAMILIES = ["qwen3_5", "qwen3_5_moe", "qwen3_5_moe_text", "bailing_hybrid", "bailing_moe_v3_vl", "kimi_k25", "glm_moe_dsa",
+            "deepseek_v4"]
 
 
 def test_all_families_registered():
-    assert set(FAMILIES + ["qwen3", "qwen3_moe", "qwen3_vl"]) <= set(list_models())
+    assert set(FAMILIES + ["qwen3", "qwen3_moe", "qwen3_vl", "llada2_moe"]) <= set(list_models())
 
 
 @pytest.mark.parametrize("model_type", FAMILIES)

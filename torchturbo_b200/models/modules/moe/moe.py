@@ -53,7 +53,8 @@ class MoELayerConfig:
     moe_router_group_topk: Optional[int] = None
     moe_router_pre_softmax: bool = False
     moe_router_topk_scaling_factor: Optional[float] = None
-    moe_router_score_function: str = "softmax"   # softmax | sigmoid
+    moe_router_score_function: str = "softmax"   # softmax | sigmoid | sqrtsoftplus
+    moe_swiglu_limit: Optional[float] = None      # clamp gate to <= limit and up to [-limit, limit] (0 / None = off)
     moe_router_dtype: Optional[str] = None        # None | fp32 | fp64
     moe_router_enable_expert_bias: bool = False
     moe_token_dispatcher_type: str = "alltoall"
@@ -72,7 +73,7 @@ class MoELayerConfig:
 
     @property
     def score_fn(self) -> str:
-        if self.moe_router_score_function == "sigmoid":
+        if self.moe_router_score_function in ("sigmoid", "sqrtsoftplus"):
             return "sigmoid"
         return "softmax_pre" if self.moe_router_pre_softmax else "softmax_post"
 
@@ -174,6 +175,8 @@ class TopKRouter(nn.Module):
             idx, prob, stats = self._hash_routing(logits, input_ids, scaling, valid)
         elif cfg.moe_router_num_groups:
             idx, prob, stats = self._group_limited(logits, scaling, valid)
+        elif cfg.moe_router_score_function == "sqrtsoftplus":
+            idx, prob, stats = self._eager_topk(logits, scaling, valid)
         else:
             idx, prob, stats = ops.router_topk(logits, cfg.moe_router_topk, cfg.score_fn, expert_bias=self.expert_bias,
                                                scaling=scaling, valid_mask=valid)
@@ -204,6 +207,31 @@ class TopKRouter(nn.Module):
         return idx, prob, logits
 
     # -- rarely used routing variants stay in torch ---------------------------------------------------
+    def _scores(self, lg: torch.Tensor) -> torch.Tensor:
+        fn = self.config.moe_router_score_function
+        if fn == "sigmoid":
+            return torch.sigmoid(lg)
+        if fn == "sqrtsoftplus":
+            return torch.sqrt(F.softplus(lg))
+        return torch.softmax(lg, -1)
+
+    def _eager_topk(self, logits, scaling, valid):
+        """Score functions the fused router kernel does not cover (`sqrtsoftplus`): scores, bias-corrected selection,
+        weights normalised over the selected experts."""
+        from ....ops.providers.native import router_topk_ref
+
+        cfg = self.config
+        lg = logits.float()
+        scores = self._scores(lg)
+        sel = scores + self.expert_bias if self.expert_bias is not None else scores
+        idx = sel.topk(cfg.moe_router_topk, dim=-1).indices
+        prob = scores.gather(1, idx)
+        if cfg.moe_router_topk > 1:
+            prob = prob / (prob.sum(-1, keepdim=True) + 1e-20)
+        _, _, stats = router_topk_ref(lg, cfg.moe_router_topk, "sigmoid", None, 1.0, valid)
+        stats["counts"] = torch.bincount(idx.reshape(-1), minlength=lg.shape[1])
+        return idx, prob * scaling, stats
+
     def _group_limited(self, logits, scaling, valid):
         """Group-limited top-k: keep the best `group_topk` groups (score of a group = sum of its top
         `k / group_topk` experts), then top-k inside them (models/modules/moe/utils.py:30-77 of the reference)."""
@@ -213,14 +241,14 @@ class TopKRouter(nn.Module):
         lg = logits.float()
         T, E = lg.shape
         G, gk, k = cfg.moe_router_num_groups, cfg.moe_router_group_topk, cfg.moe_router_topk
-        scores = torch.sigmoid(lg) if cfg.moe_router_score_function == "sigmoid" else torch.softmax(lg, -1)
+        scores = self._scores(lg)
         sel = scores + self.expert_bias if self.expert_bias is not None else scores
         group_scores = sel.view(T, G, E // G).topk(max(k // gk, 1), dim=-1).values.sum(-1)
         gmask = torch.zeros_like(group_scores).scatter_(1, group_scores.topk(gk, dim=-1).indices, 1.0)
         emask = gmask[:, :, None].expand(T, G, E // G).reshape(T, E).bool()
         idx = sel.masked_fill(~emask, float("-inf")).topk(k, dim=-1).indices
         prob = scores.gather(1, idx)
-        if cfg.moe_router_score_function == "sigmoid" and k > 1:
+        if cfg.moe_router_score_function != "softmax" and k > 1:
             prob = prob / (prob.sum(-1, keepdim=True) + 1e-20)
         _, _, stats = router_topk_ref(lg, k, cfg.score_fn, None, 1.0, valid)
         stats["counts"] = torch.bincount(idx.reshape(-1), minlength=E)
@@ -232,7 +260,7 @@ class TopKRouter(nn.Module):
         cfg = self.config
         idx = self.tid2eid[input_ids.reshape(-1)].long()
         lg = logits.float()
-        scores = torch.sigmoid(lg) if cfg.moe_router_score_function == "sigmoid" else torch.softmax(lg, -1)
+        scores = self._scores(lg)
         prob = scores.gather(1, idx)
         if cfg.moe_router_topk > 1:
             prob = prob / (prob.sum(-1, keepdim=True) + 1e-20)
@@ -266,7 +294,31 @@ class GroupedMLP(nn.Module):
         if perm.tokens.shape[0] == 0:
             # keep the weights in the autograd graph on ranks that received no tokens
             return perm.tokens.new_zeros(0, w2.shape[-1]) + 0.0 * (w1.sum() + w2.sum())
+        if self.config.moe_swiglu_limit:
+            return self._forward_clamped(perm, w1, w2, float(self.config.moe_swiglu_limit), tokens_per_expert)
         return ops.moe_experts(perm, w1, w2, tokens_per_expert)
+
+    @staticmethod
+    def _forward_clamped(perm: MoEPermutation, w1, w2, limit: float, tokens_per_expert=None) -> torch.Tensor:
+        """Clamped SwiGLU (gate <= limit, |up| <= limit).  The fused expert kernel has no clamp, so this variant runs
+        per expert in torch and reads the segment table on the host."""
+        x = perm.tokens
+        counts = (perm.counts if perm.counts is not None else tokens_per_expert).tolist()
+        starts = perm.seg_start.tolist() if perm.seg_start is not None else None
+        out, pos = [], 0
+        pieces = x.new_zeros(x.shape[0], w2.shape[-1])
+        segs = []
+        for e, n in enumerate(counts):
+            a = starts[e] if starts is not None else pos
+            pos += n
+            if n:
+                h = ops.gated_activation(x[a:a + n] @ w1[e], limit=limit,
+                                         probs=perm.probs[a:a + n] if perm.probs is not None else None)
+                segs.append((a, n, h @ w2[e]))
+        if not segs:
+            return pieces + 0.0 * (w1.sum() + w2.sum())
+        idx = torch.cat([torch.arange(a, a + n, device=x.device) for a, n, _ in segs])
+        return pieces.index_copy(0, idx, torch.cat([y for _, _, y in segs]).to(pieces.dtype))
 
     def get_muon_parameter_specs(self):
         """Each expert matrix is an independent Muon matrix inside the fused storage."""
