@@ -37,7 +37,8 @@ def parse():
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--layers", type=int, default=0, help="0 = min(48, 12 * gpus)")
     p.add_argument("--seq-len", type=int, default=4096)
-    p.add_argument("--model", default="qwen3_moe_30b_a3b", choices=["qwen3_moe_30b_a3b", "qwen3_8b", "tiny_moe"])
+    p.add_argument("--model", default="qwen3_moe_30b_a3b", choices=["qwen3_moe_30b_a3b", "qwen3_8b", "qwen3_14b", "tiny_moe"])
+    p.add_argument("--sp", type=int, default=1, help="Ulysses sequence-parallel size (a sequence of --seq-len tokens per SP group)")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--ep-transport", default="auto", choices=["auto", "nccl", "p2p"],
                    help="expert-parallel token exchange: NVLink peer-memory kernels (p2p) or NCCL all-to-all")
@@ -50,6 +51,10 @@ def model_config(name: str, layers: int) -> dict:
                     num_hidden_layers=layers, num_attention_heads=32, num_key_value_heads=4, head_dim=128,
                     num_experts=128, num_experts_per_tok=8, moe_intermediate_size=768, norm_topk_prob=True,
                     rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False, router_aux_loss_coef=1e-3)
+    if name == "qwen3_14b":
+        return dict(model_type="qwen3", vocab_size=151936, hidden_size=5120, intermediate_size=17408,
+                    num_hidden_layers=layers, num_attention_heads=40, num_key_value_heads=8, head_dim=128,
+                    rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False)
     if name == "qwen3_8b":
         return dict(model_type="qwen3", vocab_size=151936, hidden_size=4096, intermediate_size=12288,
                     num_hidden_layers=layers, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
@@ -123,10 +128,11 @@ def run_ours(args) -> dict:
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
     layers = args.layers or min(48, 12 * world)
-    is_moe = args.model != "qwen3_8b"
+    is_moe = args.model not in ("qwen3_8b", "qwen3_14b")
+    sp = max(args.sp, 1)
     cfg = EngineConfig.from_dict({
         "mixed_precision": "bf16",
-        "parallel_plan": {"sp_size": 1, "ep_size": world if is_moe else 1},
+        "parallel_plan": {"sp_size": sp, "ep_size": world if is_moe else 1},
         "moe": {"aux_loss_coeff": 1e-3},
         "activation_checkpointing": {"enabled": not is_moe},
     })
@@ -141,7 +147,7 @@ def run_ours(args) -> dict:
     ds = SyntheticPackedDataset(n_batches * world, args.seq_len, mc["vocab_size"], min_doc=256, max_doc=args.seq_len,
                                 seed=1234)
     coll = PackedCollator(pin=True)
-    host = [coll([ds[rank * n_batches + i]]) for i in range(n_batches)]
+    host = [coll([ds[(rank // sp) * n_batches + i]]) for i in range(n_batches)]   # an SP group shares its row
     dev = torch.device("cuda", local_rank)
 
     def to_device(b):
@@ -177,7 +183,7 @@ def run_ours(args) -> dict:
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_dev = float(t.item())
-    tokens_per_step = args.seq_len * world
+    tokens_per_step = args.seq_len * (world // sp)
     value = tokens_per_step * args.steps / (ms_dev / 1e3)
     # ---- end-to-end region: public API, H2D of every batch from pinned memory, D2H of every loss
     e2e = None
@@ -208,8 +214,9 @@ def run_ours(args) -> dict:
         "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (seeded random token ids, random-init weights)", "impl": "ours",
         "config": {"model": "Qwen3-30B-A3B" if args.model == "qwen3_moe_30b_a3b" else args.model, "layers": layers,
-                   "layers_named": 48, "global_batch": world, "seq_len": args.seq_len,
-                   "parallelism": f"fsdp2 dp{world} + ep{world if is_moe else 1}", "optimizer": "AdamW fp32 master",
+                   "layers_named": 48, "global_batch": world // sp, "seq_len": args.seq_len,
+                   "parallelism": f"fsdp2 dp{world // sp} + ep{world if is_moe else 1}" + (f" + ulysses sp{sp}" if sp > 1 else ""),
+                   "sp_transport": os.environ.get("TORCHTURBO_ULYSSES_TRANSPORT", "auto") if sp > 1 else "none", "optimizer": "AdamW fp32 master",
                    "ep_transport": ep_transport, "depth_rule": "layers = min(48, 12 * n_gpus): the deepest stack whose "
                    "weights + fp32 AdamW state fit 180 GB per GPU without activation checkpointing; 48 (the named "
                    "model) at 8 GPUs", "tokens_per_s_scaled_to_48_layers": value * layers / 48.0,

@@ -422,11 +422,10 @@ TTB_EXPORT int ttb_attn_bwd(const void* q, const void* k, long long ldk, const v
   if (bw_map(&tdo, dout, T, (long long)Hq * D, Hq * D, 64)) return 102;
   if (bw_map(&tk, k, T, ldk, Hk * D, 128)) return 103;
   if (bw_map(&tv, v, T, ldv, Hk * D, 128)) return 104;
-  static bool attr = false;
-  if (!attr) {
-    cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::TOTAL);
-    if (e != cudaSuccess) return 300 + (int)e;
-    attr = true;
+  static bool smem_done[16] = {};
+  {
+    const cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(attn_bwd_kernel), BwdSmem::TOTAL, smem_done);
+    if (e != cudaSuccess) return 300 + static_cast<int>(e);
   }
   if (Hq != Hk && (dk_acc == nullptr || dv_acc == nullptr)) return 903;
   AttnBwdParams p{kv_tiles, lse, delta, dq_acc, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, dk_acc, dv_acc, Hq, Hk, T, scale, causal};

@@ -344,11 +344,10 @@ TTB_EXPORT int ttb_attn_fwd(const void* q, long long ldq, const void* k, long lo
   if (make_rows_map(&tq, q, T, ldq, Hq * D)) return 101;
   if (make_rows_map(&tk, k, T, ldk, Hk * D)) return 102;
   if (make_rows_map(&tv, v, T, ldv, Hk * D)) return 103;
-  static bool attr = false;
-  if (!attr) {
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem::TOTAL);
-    if (e != cudaSuccess) return 300 + (int)e;
-    attr = true;
+  static bool smem_done[16] = {};
+  {
+    const cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(attn_fwd_kernel), AttnSmem::TOTAL, smem_done);
+    if (e != cudaSuccess) return 300 + static_cast<int>(e);
   }
   AttnFwdParams p{q_tiles, (__nv_bfloat16*)out, lse, max_logit, Hq, Hk, T, scale, causal};
   dim3 grid(n_tiles, Hq);

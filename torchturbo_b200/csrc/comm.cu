@@ -377,3 +377,208 @@ TTB_EXPORT int ttb_ep_gather_vals(const unsigned long long* peer_ptrs, long long
                                                                                      cap_rows, status);
   LAUNCH_RET();
 }
+
+// ============================================================================================================
+// Ulysses sequence parallelism over peer memory.
+//
+// Layouts (bf16, D = 128): a rank holds `Tl` consecutive tokens of the row and all heads; around attention it
+// needs all `T = W * Tl` tokens of `Hl = H / W` heads.  Head h of local token t therefore belongs to rank
+// `h / Hl`, which stores it at row `rank * Tl + t`, head `h % Hl` of its `[T, Hl, D]` buffer.
+// Key / value heads are repeated `rep` times first when there are fewer of them than ranks (repeated head
+// `hk * rep + i`), so a source head may have `rep` destinations; the reverse direction sums the `rep` copies.
+//
+//   ulysses_qkv_scatter : per-head RMSNorm + rotary embedding of q and k (the epilogue of the QKV projection)
+//                         computed in registers and stored straight into the owning ranks' buffers; v heads are
+//                         copied the same way.  The last block publishes "rows landed" flags.
+//   ulysses_scatter     : plain seq -> head push of a `[Tl, H, D]` tensor (gradient of the attention output).
+//   ulysses_gather      : head -> seq pull: `[Tl, H, D]` assembled from the owners' `[T, Hl, D]` buffers, summing
+//                         replicas (attention output forward; dq / dk / dv backward).
+// Replaces the three + one `all_to_all_single` calls and their pack / unpack copies
+// (models/modules/attention/ulysses/ulysses.py:307-327,381-383 of the reference).
+// ============================================================================================================
+namespace ttb {
+struct UlyQkvParams {
+  PeerTable peers;
+  long long off_q, off_k, off_v, off_flags;
+  const __nv_bfloat16* qkv;   // [Tl, ld]: q heads, then k heads, then v heads
+  long long ld;
+  const __nv_bfloat16 *wq, *wk;
+  const float *cos_t, *sin_t; // [Tl, 64]
+  float* rstd_out;            // [Tl * (Hq + Hk)] or null
+  long long Tl;
+  int Hq, Hk, rep, W, rank, epoch, use_norm;
+  float eps;
+  unsigned int* done_counter;
+};
+
+__global__ void ulysses_qkv_scatter_kernel(const UlyQkvParams p) {
+  constexpr int D = 128;
+  const int lane = threadIdx.x & 31;
+  const int heads = p.Hq + 2 * p.Hk;
+  const int Hql = p.Hq / p.W, Hkl = p.Hk * p.rep / p.W;
+  const long long total = p.Tl * heads;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long gw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; gw < total; gw += nwarps) {
+    const long long t = gw / heads;
+    const int h = static_cast<int>(gw - t * heads);
+    const __nv_bfloat16* src = p.qkv + t * p.ld + static_cast<long long>(h) * D;
+    float2 lo = unpack_bf16(*reinterpret_cast<const uint32_t*>(src + 2 * lane));
+    float2 hi = unpack_bf16(*reinterpret_cast<const uint32_t*>(src + 64 + 2 * lane));
+    const bool is_q = h < p.Hq, is_k = !is_q && h < p.Hq + p.Hk;
+    uint32_t o_lo, o_hi;
+    if (is_q || is_k) {
+      float rstd = 1.f;
+      if (p.use_norm) {
+        const __nv_bfloat16* w = is_q ? p.wq : p.wk;
+        float ss = warp_sum(lo.x * lo.x + lo.y * lo.y + hi.x * hi.x + hi.y * hi.y);
+        rstd = rsqrtf(ss / D + p.eps);
+        float2 wl = unpack_bf16(*reinterpret_cast<const uint32_t*>(w + 2 * lane));
+        float2 wh = unpack_bf16(*reinterpret_cast<const uint32_t*>(w + 64 + 2 * lane));
+        lo.x = __bfloat162float(__float2bfloat16(__bfloat162float(__float2bfloat16(lo.x * rstd)) * wl.x));
+        lo.y = __bfloat162float(__float2bfloat16(__bfloat162float(__float2bfloat16(lo.y * rstd)) * wl.y));
+        hi.x = __bfloat162float(__float2bfloat16(__bfloat162float(__float2bfloat16(hi.x * rstd)) * wh.x));
+        hi.y = __bfloat162float(__float2bfloat16(__bfloat162float(__float2bfloat16(hi.y * rstd)) * wh.y));
+      }
+      if (p.rstd_out && lane == 0) p.rstd_out[t * (p.Hq + p.Hk) + h] = rstd;
+      const float2 c = *reinterpret_cast<const float2*>(p.cos_t + t * (D / 2) + 2 * lane);
+      const float2 s = *reinterpret_cast<const float2*>(p.sin_t + t * (D / 2) + 2 * lane);
+      o_lo = pack_bf16(lo.x * c.x - hi.x * s.x, lo.y * c.y - hi.y * s.y);
+      o_hi = pack_bf16(hi.x * c.x + lo.x * s.x, hi.y * c.y + lo.y * s.y);
+    } else {
+      o_lo = pack_bf16(lo.x, lo.y);
+      o_hi = pack_bf16(hi.x, hi.y);
+    }
+    const long long row = static_cast<long long>(p.rank) * p.Tl + t;
+    if (is_q) {
+      const int o = h / Hql, hl = h - o * Hql;
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.peers.base[o] + p.off_q) + (row * Hql + hl) * D;
+      *reinterpret_cast<uint32_t*>(dst + 2 * lane) = o_lo;
+      *reinterpret_cast<uint32_t*>(dst + 64 + 2 * lane) = o_hi;
+    } else {
+      const int hk = is_k ? h - p.Hq : h - p.Hq - p.Hk;
+      const long long off = is_k ? p.off_k : p.off_v;
+      for (int i = 0; i < p.rep; ++i) {
+        const int r = hk * p.rep + i;
+        const int o = r / Hkl, hl = r - o * Hkl;
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.peers.base[o] + off) + (row * Hkl + hl) * D;
+        *reinterpret_cast<uint32_t*>(dst + 2 * lane) = o_lo;
+        *reinterpret_cast<uint32_t*>(dst + 64 + 2 * lane) = o_hi;
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  __shared__ bool last;
+  if (threadIdx.x == 0) last = (atomicAdd(p.done_counter, 1u) == gridDim.x - 1);
+  __syncthreads();
+  if (last) {
+    __threadfence_system();
+    if (threadIdx.x < p.W) st_release_sys(reinterpret_cast<int*>(p.peers.base[threadIdx.x] + p.off_flags) + p.rank, p.epoch);
+    if (threadIdx.x == 0) *p.done_counter = 0;
+  }
+}
+
+struct UlyMoveParams {
+  PeerTable peers;
+  long long off_buf, off_flags;  // off_flags < 0: no flags (gather)
+  __nv_bfloat16* local;          // [Tl, H, D] (source of a scatter, destination of a gather)
+  long long Tl;
+  int H, rep, W, rank, epoch;    // H: heads of `local`; destinations hold H * rep / W heads
+  unsigned int* done_counter;
+  const int* status;
+};
+
+__global__ void ulysses_scatter_kernel(const UlyMoveParams p) {
+  constexpr int D = 128;
+  const int lane = threadIdx.x & 31;
+  const int Hl = p.H * p.rep / p.W;
+  const long long total = p.Tl * p.H;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long gw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; gw < total; gw += nwarps) {
+    const long long t = gw / p.H;
+    const int h = static_cast<int>(gw - t * p.H);
+    const uint2 v = *reinterpret_cast<const uint2*>(p.local + gw * D + 4 * lane);
+    const long long row = static_cast<long long>(p.rank) * p.Tl + t;
+    for (int i = 0; i < p.rep; ++i) {
+      const int r = h * p.rep + i;
+      const int o = r / Hl, hl = r - o * Hl;
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.peers.base[o] + p.off_buf) + (row * Hl + hl) * D;
+      *reinterpret_cast<uint2*>(dst + 4 * lane) = v;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  __shared__ bool last;
+  if (threadIdx.x == 0) last = (atomicAdd(p.done_counter, 1u) == gridDim.x - 1);
+  __syncthreads();
+  if (last) {
+    __threadfence_system();
+    if (threadIdx.x < p.W) st_release_sys(reinterpret_cast<int*>(p.peers.base[threadIdx.x] + p.off_flags) + p.rank, p.epoch);
+    if (threadIdx.x == 0) *p.done_counter = 0;
+  }
+}
+
+__global__ void ulysses_gather_kernel(const UlyMoveParams p) {
+  constexpr int D = 128;
+  const int lane = threadIdx.x & 31;
+  const int Hl = p.H * p.rep / p.W;
+  const long long total = p.Tl * p.H;
+  const bool healthy = (p.status == nullptr) || (*p.status == 0);
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long gw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; gw < total; gw += nwarps) {
+    const long long t = gw / p.H;
+    const int h = static_cast<int>(gw - t * p.H);
+    const long long row = static_cast<long long>(p.rank) * p.Tl + t;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    uint2 single = make_uint2(0u, 0u);
+    if (healthy) {
+      for (int i = 0; i < p.rep; ++i) {
+        const int r = h * p.rep + i;
+        const int o = r / Hl, hl = r - o * Hl;
+        const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.peers.base[o] + p.off_buf) + (row * Hl + hl) * D;
+        const uint2 v = *reinterpret_cast<const uint2*>(src + 4 * lane);
+        if (p.rep == 1) {
+          single = v;
+        } else {
+          const float2 a = unpack_bf16(v.x), b = unpack_bf16(v.y);
+          acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
+        }
+      }
+    }
+    if (p.rep != 1) single = make_uint2(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]));
+    *reinterpret_cast<uint2*>(p.local + gw * D + 4 * lane) = single;
+  }
+}
+
+}  // namespace ttb
+
+TTB_EXPORT int ttb_ulysses_qkv_scatter(const unsigned long long* peer_ptrs, long long off_q, long long off_k,
+                                       long long off_v, long long off_flags, const void* qkv, long long ld,
+                                       const void* wq, const void* wk, const float* cos_t, const float* sin_t,
+                                       float* rstd_out, long long Tl, int Hq, int Hk, int rep, int W, int rank,
+                                       int epoch, int use_norm, float eps, unsigned int* done_counter, int grid,
+                                       void* stream) {
+  using namespace ttb;
+  if (W > MAX_RANKS || W < 1 || ld % 8 || Hq % W || (Hk * rep) % W || rep < 1) return 901;
+  UlyQkvParams p{make_peers(peer_ptrs, W), off_q, off_k, off_v, off_flags, (const __nv_bfloat16*)qkv, ld,
+                 (const __nv_bfloat16*)wq, (const __nv_bfloat16*)wk, cos_t, sin_t, rstd_out, Tl, Hq, Hk, rep, W, rank,
+                 epoch, use_norm, eps, done_counter};
+  if (grid < 1) grid = 1;
+  ulysses_qkv_scatter_kernel<<<grid, 256, 0, STREAM(stream)>>>(p);
+  LAUNCH_RET();
+}
+
+TTB_EXPORT int ttb_ulysses_move(const unsigned long long* peer_ptrs, long long off_buf, long long off_flags, void* local,
+                                long long Tl, int H, int rep, int W, int rank, int epoch, unsigned int* done_counter,
+                                const int* status, int gather, int grid, void* stream) {
+  using namespace ttb;
+  if (W > MAX_RANKS || W < 1 || (H * rep) % W || rep < 1) return 901;
+  UlyMoveParams p{make_peers(peer_ptrs, W), off_buf, off_flags, (__nv_bfloat16*)local, Tl, H, rep, W, rank, epoch,
+                  done_counter, status};
+  if (grid < 1) grid = 1;
+  if (gather)
+    ulysses_gather_kernel<<<grid, 256, 0, STREAM(stream)>>>(p);
+  else
+    ulysses_scatter_kernel<<<grid, 256, 0, STREAM(stream)>>>(p);
+  LAUNCH_RET();
+}

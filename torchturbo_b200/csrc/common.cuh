@@ -7,6 +7,7 @@
 // up and returns false; callers unwind, free TMEM and exit so the context
 // stays usable.
 #pragma once
+#include <cstdio>
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -270,6 +271,39 @@ inline PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
 
 // bf16 tensor map of rank 2 or 3 (dims innermost first), 128-byte swizzle.
 // Returns 0 on success.
+// Opt a kernel into `bytes` of dynamic shared memory on the calling thread's current device, once per device.
+// The attribute belongs to the (function, device) pair, so the "done" flags are per device.  `cudaGetDevice` runs
+// first: it binds this thread of this runtime instance to the context that is current (worker threads created by
+// the framework may reach this code before any other runtime call).  One retry after clearing the thread's error
+// state covers a first call that finds that state not yet set up; a second failure is reported to the caller and
+// printed once with what the runtime knows about the function.
+inline cudaError_t ensure_dynamic_smem(const void* fn, int bytes, bool (&done)[16]) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 16) dev = 0;
+  if (done[dev]) return cudaSuccess;
+  e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    (void)cudaSetDevice(dev);
+    e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) {
+      cudaFuncAttributes fa{};
+      const cudaError_t e2 = cudaFuncGetAttributes(&fa, fn);
+      int optin = -1;
+      (void)cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+      fprintf(stderr, "[ttb] cudaFuncSetAttribute(%d B dynamic smem) failed on device %d: %s; get-attributes: %s, static smem "
+                      "%zu B, current max dynamic %d B, device opt-in limit %d B\n", bytes, dev, cudaGetErrorString(e),
+              cudaGetErrorString(e2), fa.sharedSizeBytes, fa.maxDynamicSharedSizeBytes, optin);
+      (void)cudaGetLastError();
+      return e;
+    }
+  }
+  done[dev] = true;
+  return cudaSuccess;
+}
+
 inline int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
                           const uint64_t* strides_bytes /* rank-1 entries */, const uint32_t* box) {
   auto fn = get_encode_fn();

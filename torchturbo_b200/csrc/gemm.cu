@@ -93,12 +93,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const long long tiles_per_group = static_cast<long long>(p.m_tiles) * p.n_tiles;
   const long long total_tiles = tiles_per_group * groups;
 
-  // Decode tile -> (g, m_tile, n_tile); m fastest so concurrently running CTAs share a B panel.
+  // Decode tile -> (g, m_tile, n_tile).  Tiles are walked in bands of RASTER_M m-tiles: inside a band m runs
+  // fastest, then n, so the ~148 tiles in flight cover a near-square RASTER_M x (148 / RASTER_M) block of C.  Per wave
+  // that needs RASTER_M A panels and ~9 B panels instead of every A panel, and a band's A panels stay in L2 while
+  // its n-tiles are walked (an m-fastest walk over all m-tiles re-read A from DRAM once per n-tile column).
+  constexpr int RASTER_M = 16;
   auto decode = [&](long long t, int& g, int& mt, int& nt) {
     g = static_cast<int>(t / tiles_per_group);
-    long long r = t - static_cast<long long>(g) * tiles_per_group;
-    nt = static_cast<int>(r / p.m_tiles);
-    mt = static_cast<int>(r - static_cast<long long>(nt) * p.m_tiles);
+    const long long r = t - static_cast<long long>(g) * tiles_per_group;
+    const long long per_band = static_cast<long long>(RASTER_M) * p.n_tiles;
+    const int band = static_cast<int>(r / per_band);
+    const int m_base = band * RASTER_M;
+    const int band_rows = (p.m_tiles - m_base) < RASTER_M ? (p.m_tiles - m_base) : RASTER_M;
+    const long long w = r - static_cast<long long>(band) * per_band;
+    nt = static_cast<int>(w / band_rows);
+    mt = m_base + static_cast<int>(w - static_cast<long long>(nt) * band_rows);
   };
   // k-range of a tile: dense -> [0, K); grouped-K -> rows of group g.
   auto krange = [&](int g, int& k0, int& nkb) {
@@ -462,11 +471,10 @@ static int launch(const GemmArgs& a, cudaStream_t stream) {
   p.preact = reinterpret_cast<__nv_bfloat16*>(a.preact); p.ld_preact = a.ld_preact;
 
   auto kfn = gemm_kernel<BN, A_MN, B_MN, EPI>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+  static bool smem_done[16] = {};
+  {
+    const cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kfn), L::TOTAL, smem_done);
     if (e != cudaSuccess) return 300 + static_cast<int>(e);
-    attr_set = true;
   }
   long long total = static_cast<long long>(p.m_tiles) * p.n_tiles * (p.groups_k > 0 ? p.groups_k : 1);
   if (total <= 0) return 0;

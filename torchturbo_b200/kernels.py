@@ -623,3 +623,39 @@ def attn_bwd(dout, q, k, v, out, lse, kv_tiles_dev, *, scale: float, causal: boo
                               C.c_float(scale), C.c_int(int(causal)), _stream()), "ttb_attn_bwd")
     LAUNCH_COUNT += 2 if Hq == Hk else 4
     return dq, dk, dv
+
+
+# --------------------------------------------------------------------------------------
+# Ulysses sequence parallelism over peer memory
+# --------------------------------------------------------------------------------------
+def ulysses_qkv_scatter(peer_ptrs, off_q, off_k, off_v, off_flags, qkv, n_q, n_kv, rep, wq, wk, cos, sin, eps, rank, world,
+                        epoch, done_counter, use_norm=True):
+    """Per-head RMSNorm + RoPE of the q / k columns of `qkv` [Tl, (n_q + 2 n_kv) * 128] and a copy of the v columns,
+    stored straight into the owning ranks' `[T, heads / world, 128]` buffers; publishes this rank's "landed" flag.
+    Returns rstd [Tl * (n_q + n_kv)]."""
+    Tl = qkv.shape[0]
+    check_device(qkv)
+    rstd = torch.empty(Tl * (n_q + n_kv), dtype=torch.float32, device=qkv.device)
+    warps = Tl * (n_q + 2 * n_kv)
+    grid = max(1, min((warps + 7) // 8, 8 * num_sms(qkv.device.index)))
+    _check(lib().ttb_ulysses_qkv_scatter(peer_ptrs, C.c_longlong(off_q), C.c_longlong(off_k), C.c_longlong(off_v),
+                                         C.c_longlong(off_flags), _p(qkv), C.c_longlong(qkv.stride(0)), _p(wq), _p(wk),
+                                         _p(cos), _p(sin), _p(rstd), C.c_longlong(Tl), C.c_int(n_q), C.c_int(n_kv),
+                                         C.c_int(rep), C.c_int(world), C.c_int(rank), C.c_int(epoch),
+                                         C.c_int(int(use_norm)), C.c_float(eps), _p(done_counter), C.c_int(grid),
+                                         _stream()), "ttb_ulysses_qkv_scatter")
+    return rstd
+
+
+def ulysses_move(peer_ptrs, off_buf, off_flags, local, heads, rep, rank, world, epoch, done_counter, status, gather: bool):
+    """`gather=False`: push `local` [Tl, heads, 128] into the owners' buffers and publish the "landed" flag.
+    `gather=True`: fill `local` from the owners' buffers (replicas summed)."""
+    Tl = local.shape[0]
+    check_device(local)
+    assert local.is_contiguous() and local.dtype == torch.bfloat16 and local.shape[-1] == 128
+    grid = max(1, min((Tl * heads + 7) // 8, 8 * num_sms(local.device.index)))
+    _check(lib().ttb_ulysses_move(peer_ptrs, C.c_longlong(off_buf), C.c_longlong(off_flags), _p(local), C.c_longlong(Tl),
+                                  C.c_int(heads), C.c_int(rep), C.c_int(world), C.c_int(rank), C.c_int(epoch),
+                                  _p(done_counter), _p(status), C.c_int(int(gather)), C.c_int(grid), _stream()),
+           "ttb_ulysses_move")
+    return local

@@ -81,17 +81,32 @@ class Attention(nn.Module):
         qkv = ops.linear(x, self.qkv_proj.weight)
         if self.qkv_proj.bias is not None:
             qkv = qkv + self.qkv_proj.bias
-        q, k, v = ops.qk_norm_rope(qkv, self.n_q, self.n_kv, self.head_dim,
-                                   self.q_norm.weight if self.q_norm is not None else None,
-                                   self.k_norm.weight if self.k_norm is not None else None, cos, sin,
-                                   self.q_norm.eps if self.q_norm is not None else 1e-6)
         want_ml = self.qk_clip_state is not None
+        qw = self.q_norm.weight if self.q_norm is not None else None
+        kw = self.k_norm.weight if self.k_norm is not None else None
+        eps = self.q_norm.eps if self.q_norm is not None else 1e-6
+        if self.sp_size > 1 and not want_ml and self._p2p_ok(qkv):
+            # peer-memory path: QK-norm + RoPE are computed by the kernel that scatters heads to their owners
+            from ...comm import ulysses_p2p
+
+            q, k, v, ws = ulysses_p2p.qkv_exchange(qkv.contiguous(), self.n_q, self.n_kv, qw, kw, cos, sin, eps, self.sp_group)
+            o = ops.attention(q, k, v, cu_seqlens, max_seqlen, causal=self.causal, scale=self.scale)
+            out = ulysses_p2p.out_exchange(o, ws)
+            return ops.linear(out.reshape(T, self.n_q * self.head_dim), self.o_proj.weight)
+        q, k, v = ops.qk_norm_rope(qkv, self.n_q, self.n_kv, self.head_dim, qw, kw, cos, sin, eps)
         out = ulysses_attention(q, k, v, cu_seqlens, max_seqlen, sp_group=self.sp_group, sp_size=self.sp_size,
                                 causal=self.causal, scale=self.scale, want_max_logits=want_ml)
         if want_ml:
             out, max_logits = out
             self.qk_clip_state.update(max_logits)
         return ops.linear(out.reshape(T, self.n_q * self.head_dim), self.o_proj.weight)
+
+    def _p2p_ok(self, qkv) -> bool:
+        if not qkv.is_cuda:
+            return False
+        from ...comm import ulysses_p2p
+
+        return ulysses_p2p.usable(self.sp_group, qkv, self.n_q, self.n_kv, self.head_dim)
 
 
 class DenseMLP(nn.Module):
