@@ -42,6 +42,12 @@ def _build(model_type):
                                       q_lora_rank=16, qk_rope_head_dim=4, qk_nope_head_dim=12, o_groups=2, o_lora_rank=8,
                                       sliding_window=4, compress_ratios=[1, 4, 2], index_n_heads=2, index_head_dim=8, index_topk=2,
                                       hc_mult=2, hc_sinkhorn_iters=3, swiglu_limit=7.0, num_hash_layers=1, num_mtp_layers=1))
+    elif model_type == "qwen4_exp":
+        tc = dict(QWEN35, **QMOE, hc_count=2, hc_lowrank=8, ple_layer_ids=[1, 2], ple_embed_dim=16, ple_conv_kernel_size=2,
+                  ngram_size=3, heads_per_ngram=2, ngram_vocab_size_base=50, make_ngram_vocab_size_divisible_by=8,
+                  indexer_n_heads=2, indexer_head_dim=16, indexer_budget=4, indexer_compress_ratio=2, eos_token_id=0)
+        tc.pop("mtp_num_hidden_layers")
+        cfg = cls.config_class(text_config=tc, vision_config=VISION, image_token_id=5)
     elif model_type == "glm_moe_dsa":
         cfg = cls.config_class(**dict(DSV3, num_hidden_layers=4, n_group=1, num_nextn_predict_layers=0, index_topk=6,
                                       index_head_dim=8, index_n_heads=2, index_topk_freq=2, index_skip_topk_offset=1,
@@ -63,7 +69,7 @@ def _batch(vlm: bool, media_key="image_grid_thw"):
 
 
 FAMILIES = ["qwen3_5", "qwen3_5_moe", "qwen3_5_moe_text", "bailing_hybrid", "bailing_moe_v3_vl", "kimi_k25", "glm_moe_dsa",
-            "deepseek_v4"]
+            "deepseek_v4", "qwen4_exp"]
 
 
 def test_all_families_registered():
@@ -74,7 +80,7 @@ def test_all_families_registered():
 def test_family_forward_backward_and_isolation(model_type):
     cls, m = _build(model_type)
     m.train()
-    vlm = model_type in ("qwen3_5", "qwen3_5_moe", "kimi_k25", "bailing_moe_v3_vl")
+    vlm = model_type in ("qwen3_5", "qwen3_5_moe", "kimi_k25", "bailing_moe_v3_vl", "qwen4_exp")
     b = _batch(vlm, "grid_thws" if model_type == "kimi_k25" else "image_grid_thw")
     out = m(**b)
     assert out.logits.shape == (1, 24, 128) and torch.isfinite(out.logits).all()
@@ -82,7 +88,7 @@ def test_family_forward_backward_and_isolation(model_type):
     for h in out.get("mtp_logits") or ():
         loss = loss + h.float().pow(2).mean()
     loss.backward()
-    missing = [n for n, p in m.named_parameters() if p.grad is None and ".indexer." not in n]
+    missing = [n for n, p in m.named_parameters() if p.grad is None and p.requires_grad and ".indexer." not in n]
     assert not missing, missing
     # document isolation: changing the second document leaves the first document's logits untouched
     m.eval()
