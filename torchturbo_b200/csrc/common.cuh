@@ -320,6 +320,15 @@ inline int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const ui
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), gdim, gstr, bdim, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_ERROR_INVALID_CONTEXT || r == CUDA_ERROR_NOT_INITIALIZED) {
+    // The encode call is a driver API and needs a context current on this thread.  A worker thread of the framework
+    // (the autograd thread of device 0, which never has to switch devices) can arrive here before any runtime call
+    // has bound the primary context to it: bind it (cudaFree(0) is the no-op that does) and encode again.
+    (void)cudaFree(nullptr);
+    r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), gdim, gstr, bdim, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 }  // namespace ttb

@@ -427,7 +427,7 @@ static int launch(const GemmArgs& a, cudaStream_t stream) {
       box[1] = BK;
     }
     int r = make_tmap_bf16(&tmA, a.A, 2, dims, str, box);
-    if (r) return 100 + r;
+    if (r) return 10000 + r;
   }
   // ---- B map (3D, last dim = group)
   const int n_mem = (EPI == EPI_SWIGLU) ? 2 * a.F : a.N;
@@ -455,7 +455,7 @@ static int launch(const GemmArgs& a, cudaStream_t stream) {
     }
     box[2] = 1;
     int r = make_tmap_bf16(&tmB, a.B, 3, dims, str, box);
-    if (r) return 200 + r;
+    if (r) return 20000 + r;
   }
   GemmParams p;
   p.M = a.M; p.N = a.N; p.K = a.K;
@@ -486,7 +486,8 @@ static int launch(const GemmArgs& a, cudaStream_t stream) {
 
 }  // namespace ttb
 
-// Returns 0 on success; non-zero codes: 1xx/2xx tensor-map encode failure, 3xx attribute, 4xx launch, 9xx bad args.
+// Returns 0 on success; non-zero codes: 10000+r / 20000+r tensor-map encode failure of A / B (r = CUresult),
+// 300+e shared-memory opt-in, 400+e launch (e = cudaError_t), 9xx bad arguments.
 TTB_EXPORT int ttb_gemm_bf16(const ttb::GemmArgs* args, void* stream_ptr) {
   using namespace ttb;
   const GemmArgs& a = *args;
