@@ -210,7 +210,7 @@ def run_ours(args) -> dict:
     disp = [type(m.token_dispatcher).__name__ for m in model.modules() if hasattr(m, "token_dispatcher")]
     ep_transport = (disp[0] if disp else "none") if world > 1 else "local"
     out = {
-        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "metric": METRIC if args.model == "qwen3_moe_30b_a3b" else METRIC.replace("Qwen3-30B-A3B FSDP2+EP", args.model), "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (seeded random token ids, random-init weights)", "impl": "ours",
         "config": {"model": "Qwen3-30B-A3B" if args.model == "qwen3_moe_30b_a3b" else args.model, "layers": layers,
