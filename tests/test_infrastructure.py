@@ -238,3 +238,52 @@ def test_rl_packed_helpers():
     ref = torch.log_softmax(logits[0].float(), -1)
     assert torch.allclose(lp[0], ref[0, 2]) and float(lp[2]) == 0.0           # ignored targets give 0
     assert torch.allclose(ent[1], -(ref[1].exp() * ref[1]).sum(), atol=1e-5)
+
+
+def test_adamw_swap_matches_torch_adamw_and_keeps_state_on_host():
+    from torchturbo_b200.engine.optimizers import AdamWSwap
+
+    torch.manual_seed(0)
+    a = [nn.Parameter(torch.randn(7, 5)), nn.Parameter(torch.randn(11))]
+    b = [nn.Parameter(p.detach().clone()) for p in a]
+    oa = AdamWSwap(a, lr=1e-2, weight_decay=0.1, betas=(0.9, 0.95))
+    ob = torch.optim.AdamW(b, lr=1e-2, weight_decay=0.1, betas=(0.9, 0.95))
+    for _ in range(4):
+        for pa, pb in zip(a, b):
+            g = torch.randn_like(pa)
+            pa.grad, pb.grad = g.clone(), g.clone()
+        oa.step()
+        ob.step()
+    assert max((pa - pb).abs().max().item() for pa, pb in zip(a, b)) < 1e-6
+    st = oa.state_dict()["state"][0]
+    assert st["exp_avg"].device.type == "cpu" and st["master"].dtype == torch.float32 and st["step"] == 4
+    oa.set_clip_coef(torch.tensor(0.5))
+    a[0].grad = torch.ones_like(a[0])
+    before = oa.state[a[0]]["exp_avg"].clone()
+    oa.step()
+    assert torch.allclose(oa.state[a[0]]["exp_avg"], before * 0.9 + 0.1 * 0.5)        # gradient scaled by the clip coefficient
+
+
+def test_unpad_helpers_and_attention_interface():
+    from torchturbo_b200.models.modules.attention import attention_forward
+    from torchturbo_b200.ops.providers import native as N
+    from torchturbo_b200.utils.flash_attn_utils import cu_seqlens_to_segment_ids, get_unpad_data, pad_input, unpad_input
+
+    m = torch.tensor([[1, 1, 2, 2, 2, 0], [1, 1, 1, 1, 0, 0]])
+    idx, cu, mx = get_unpad_data(m)
+    assert idx.tolist() == [0, 1, 2, 3, 4, 6, 7, 8, 9] and cu.tolist() == [0, 2, 5, 9] and mx == 4
+    x = torch.arange(12.0).view(2, 6, 1)
+    assert torch.equal(pad_input(unpad_input(x, idx), idx, 2, 6), x * (m > 0).unsqueeze(-1))
+    assert cu_seqlens_to_segment_ids(torch.tensor([0, 2, 5]), 7).tolist() == [1, 1, 2, 2, 2, 0, 0]
+    torch.manual_seed(0)
+    q, k, v = torch.randn(2, 4, 6, 8), torch.randn(2, 2, 6, 8), torch.randn(2, 2, 6, 8)
+    out, _ = attention_forward(None, q, k, v, m)
+    assert out.shape == (2, 6, 4, 8) and float(out[0, 5].abs().sum()) == 0.0
+    ref = N.attention_ref(q[0, :, 2:5].transpose(0, 1), k[0, :, 2:5].transpose(0, 1), v[0, :, 2:5].transpose(0, 1), [0, 3])
+    assert torch.allclose(out[0, 2:5], ref, atol=1e-6)
+    state = SimpleNamespace(seen=None, update=lambda ml: setattr(state, "seen", ml))
+    mod = SimpleNamespace(is_causal=True, qk_clip_state=state)
+    out2, _ = attention_forward(mod, q[:1], k[:1], v[:1], None, cu_seq_lens_q=torch.tensor([0, 2, 6], dtype=torch.int32), max_length_q=4)
+    assert out2.shape == (1, 6, 4, 8) and state.seen.shape == (4,)
+    with pytest.raises(ValueError):
+        attention_forward(None, q, k, v, torch.zeros(2, 1, 6, 6))

@@ -335,3 +335,25 @@ def test_attention_bwd(K, causal):
     _close(dk, kf.grad, atol=3e-2)
     _close(dv, vf.grad, atol=3e-2)
     assert float(dk[650:].abs().max()) == 0.0 and float(dq[650:].abs().max()) == 0.0
+
+
+def test_adamw_swap_pipelined_matches_torch(K):
+    """Host-resident AdamW state streamed through a two-slot device workspace (chunks smaller than the parameters)."""
+    from torchturbo_b200.engine.optimizers import AdamWSwap
+
+    torch.manual_seed(0)
+    a = [torch.nn.Parameter(torch.randn(300, 70, device="cuda")), torch.nn.Parameter(torch.randn(5000, device="cuda"))]
+    b = [torch.nn.Parameter(p.detach().clone()) for p in a]
+    oa = AdamWSwap(a, lr=1e-2, weight_decay=0.1, betas=(0.9, 0.95), chunk_elems=4096)
+    ob = torch.optim.AdamW(b, lr=1e-2, weight_decay=0.1, betas=(0.9, 0.95))
+    for _ in range(3):
+        for pa, pb in zip(a, b):
+            g = torch.randn_like(pa)
+            pa.grad, pb.grad = g.clone(), g.clone()
+        oa.step()
+        ob.step()
+    torch.cuda.synchronize()
+    assert max((pa - pb).abs().max().item() for pa, pb in zip(a, b)) < 1e-5
+    st = oa.state[a[0]]
+    assert st["exp_avg"].device.type == "cpu" and st["exp_avg"].is_pinned()
+    assert torch.allclose(st["master"].view_as(a[0]).cuda(), a[0].detach(), atol=0)

@@ -180,6 +180,45 @@ def profile_case(name: str) -> None:
         def fn():
             step[0] += 1
             K.adamw_step(plan, lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.01, step=step[0])
+    elif name in ("ulysses", "ep_dispatch"):
+        # the peer-memory kernels on a 1-rank group: the "peer" is this GPU, so the counters show the kernels' own
+        # memory behaviour (the NVLink leg needs 2+ ranks and cannot run under a profiler)
+        import os
+
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29577")
+        if not dist.is_initialized():
+            dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
+        if name == "ulysses":
+            from ..comm import ulysses_p2p
+
+            Tl, nq, nkv = 16384, 40, 8
+            qkv = rnd(Tl, (nq + 2 * nkv) * 128)
+            w = rnd(128) + 1.0
+            pos = torch.arange(Tl, device=dev).float()
+            inv = 1.0 / (1e6 ** (torch.arange(0, 128, 2, device=dev).float() / 128))
+            cos, sin = (pos[:, None] * inv[None]).cos(), (pos[:, None] * inv[None]).sin()
+
+            def fn():
+                q, k, v, ws = ulysses_p2p.qkv_exchange(qkv, nq, nkv, w, w, cos, sin, 1e-6, dist.group.WORLD)
+                ulysses_p2p.out_exchange(q, ws)
+        else:
+            from ..comm.ep_p2p import P2PTokenDispatcher
+            from ..models.modules.moe import MoELayerConfig
+
+            T, H, E, k = 8192, 2048, 128, 8
+            cfg = MoELayerConfig(hidden_size=H, moe_ffn_hidden_size=768, num_moe_experts=E, moe_router_topk=k,
+                                 params_dtype=torch.bfloat16)
+            disp = P2PTokenDispatcher(cfg, dist.group.WORLD, E)
+            x = rnd(T, H)
+            idx = torch.stack([torch.randperm(E, device=dev)[:k] for _ in range(64)]).repeat(T // 64, 1)
+            prob = torch.rand(T, k, device=dev)
+
+            def fn():
+                perm, tpe, state = disp.dispatch(x, idx, prob)
+                disp.combine(perm.tokens, state)
     elif name == "rmsnorm":
         x, w = rnd(32768, 4096), rnd(4096)
         fn = lambda: K.rmsnorm_fwd(x, w, 1e-6)                          # noqa: E731

@@ -488,6 +488,16 @@ class FSDP2Backend(BaseBackend):
                 buckets.setdefault((g.optimizer_cls, topo), []).append({"params": ps, **g.hyperparameters})
         opts, names = [], []
         for (cls, topo), groups in buckets.items():
+            off = self.fsdp_config.cpu_offload
+            if cls in (torch.optim.AdamW, "adamw") and off.enabled and off.mode is CPUOffloadMode.OPTIMIZER:
+                # optimizer state on the host, streamed through a bounded device workspace
+                from ...optimizers.adamw_swap import AdamWSwap
+
+                opt = AdamWSwap(groups, memory_fraction=off.optimizer_memory_fraction)
+                opt._tt_topology = topo
+                opts.append(opt)
+                names.append(f"adamwswap_{topo}")
+                continue
             if cls in (torch.optim.AdamW, "adamw") and self.runtime.turbo_device.value == "cuda":
                 cls = FusedAdamW
             elif cls == "adamw":
