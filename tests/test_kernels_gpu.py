@@ -357,3 +357,46 @@ def test_adamw_swap_pipelined_matches_torch(K):
     st = oa.state[a[0]]
     assert st["exp_avg"].device.type == "cpu" and st["exp_avg"].is_pinned()
     assert torch.allclose(st["master"].view_as(a[0]).cuda(), a[0].detach(), atol=0)
+
+
+def test_ulysses_peer_kernels_single_rank(K, tmp_path):
+    """The peer-memory Ulysses kernels on a one-rank group (the peer is this GPU): fused QK-norm + RoPE + head scatter
+    against the separate QK-norm + RoPE kernel, and the gather / scatter round trip with gradients."""
+    import torch.distributed as dist
+
+    from torchturbo_b200.comm import ulysses_p2p
+
+    created = False
+    if not dist.is_initialized():
+        dist.init_process_group("nccl", init_method=f"file://{tmp_path}/rdzv", rank=0, world_size=1,
+                                device_id=torch.device("cuda", torch.cuda.current_device()))
+        created = True
+    try:
+        Tl, nq, nkv, D = 200, 8, 2, 128
+        qkv = _rand(Tl, (nq + 2 * nkv) * D).requires_grad_(True)
+        wq, wk = (_rand(D) * 0.1 + 1.0).requires_grad_(True), (_rand(D) * 0.1 + 1.0).requires_grad_(True)
+        pos = torch.arange(Tl, device="cuda").float()
+        inv = 1.0 / (1e6 ** (torch.arange(0, D, 2, device="cuda").float() / D))
+        cos, sin = (pos[:, None] * inv[None]).cos().contiguous(), (pos[:, None] * inv[None]).sin().contiguous()
+        q, k, v, ws = ulysses_p2p.qkv_exchange(qkv, nq, nkv, wq, wk, cos, sin, 1e-6, dist.group.WORLD)
+        q_ref, k_ref, _ = K.qknorm_rope_fwd(qkv.detach(), nq, nkv, D, wq.detach(), wk.detach(), cos, sin, 1e-6, True)
+        assert torch.equal(q, q_ref) and torch.equal(k, k_ref)
+        assert torch.equal(v, qkv.detach()[:, (nq + nkv) * D:].view(Tl, nkv, D))
+        out = ulysses_p2p.out_exchange(q * 1.0, ws)
+        assert torch.equal(out, q)
+        g = _rand(Tl, nq, D)
+        (out.float() * g.float()).sum().backward()
+        torch.cuda.synchronize()
+        ws.check()
+        # reference gradient through the separate kernels
+        dqkv = torch.empty_like(qkv)
+        dqkv[:, (nq + nkv) * D:] = 0
+        rstd = K.qknorm_rope_fwd(qkv.detach(), nq, nkv, D, wq.detach(), wk.detach(), cos, sin, 1e-6, True)[2]
+        dwq, dwk = K.qknorm_rope_bwd(g.contiguous(), torch.zeros(Tl, nkv, D, device="cuda", dtype=torch.bfloat16), qkv.detach(),
+                                     nq, nkv, D, wq.detach(), wk.detach(), cos, sin, rstd, dqkv, True)
+        _close(qkv.grad[:, : nq * D], dqkv[:, : nq * D])
+        _close(wq.grad, dwq)
+        assert float(qkv.grad[:, nq * D:].abs().max()) == 0.0
+    finally:
+        if created:
+            dist.destroy_process_group()

@@ -412,48 +412,56 @@ struct UlyQkvParams {
 };
 
 __global__ void ulysses_qkv_scatter_kernel(const UlyQkvParams p) {
+  // One warp per (token, head).  Lane l owns the four consecutive columns [4l, 4l+4): lanes 0-15 hold the first half of
+  // the head, lanes 16-31 the second, so the rotary partner of a column sits in lane l ^ 16 and one 8-byte access per
+  // lane moves the whole 256-byte head row.
   constexpr int D = 128;
   const int lane = threadIdx.x & 31;
   const int heads = p.Hq + 2 * p.Hk;
   const int Hql = p.Hq / p.W, Hkl = p.Hk * p.rep / p.W;
   const long long total = p.Tl * heads;
   const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const bool low = lane < 16;
+  const int pair = (lane & 15) * 4;                    // rotary pair index of this lane's first column
   for (long long gw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; gw < total; gw += nwarps) {
     const long long t = gw / heads;
     const int h = static_cast<int>(gw - t * heads);
     const __nv_bfloat16* src = p.qkv + t * p.ld + static_cast<long long>(h) * D;
-    float2 lo = unpack_bf16(*reinterpret_cast<const uint32_t*>(src + 2 * lane));
-    float2 hi = unpack_bf16(*reinterpret_cast<const uint32_t*>(src + 64 + 2 * lane));
+    uint2 raw = *reinterpret_cast<const uint2*>(src + 4 * lane);
     const bool is_q = h < p.Hq, is_k = !is_q && h < p.Hq + p.Hk;
-    uint32_t o_lo, o_hi;
     if (is_q || is_k) {
+      float2 a = unpack_bf16(raw.x), b = unpack_bf16(raw.y);
+      float x[4] = {a.x, a.y, b.x, b.y};
       float rstd = 1.f;
       if (p.use_norm) {
         const __nv_bfloat16* w = is_q ? p.wq : p.wk;
-        float ss = warp_sum(lo.x * lo.x + lo.y * lo.y + hi.x * hi.x + hi.y * hi.y);
+        const float ss = warp_sum(x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3]);
         rstd = rsqrtf(ss / D + p.eps);
-        float2 wl = unpack_bf16(*reinterpret_cast<const uint32_t*>(w + 2 * lane));
-        float2 wh = unpack_bf16(*reinterpret_cast<const uint32_t*>(w + 64 + 2 * lane));
-        lo.x = __bfloat162float(__float2bfloat16(__bfloat162float(__float2bfloat16(lo.x * rstd)) * wl.x));
-        lo.y = __bfloat162float(__float2bfloat16(__bfloat162float(__float2bfloat16(lo.y * rstd)) * wl.y));
-        hi.x = __bfloat162float(__float2bfloat16(__bfloat162float(__float2bfloat16(hi.x * rstd)) * wh.x));
-        hi.y = __bfloat162float(__float2bfloat16(__bfloat162float(__float2bfloat16(hi.y * rstd)) * wh.y));
+        const uint2 wr = *reinterpret_cast<const uint2*>(w + 4 * lane);
+        const float2 w0 = unpack_bf16(wr.x), w1 = unpack_bf16(wr.y);
+        const float wv[4] = {w0.x, w0.y, w1.x, w1.y};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          x[i] = __bfloat162float(__float2bfloat16(__bfloat162float(__float2bfloat16(x[i] * rstd)) * wv[i]));
       }
       if (p.rstd_out && lane == 0) p.rstd_out[t * (p.Hq + p.Hk) + h] = rstd;
-      const float2 c = *reinterpret_cast<const float2*>(p.cos_t + t * (D / 2) + 2 * lane);
-      const float2 s = *reinterpret_cast<const float2*>(p.sin_t + t * (D / 2) + 2 * lane);
-      o_lo = pack_bf16(lo.x * c.x - hi.x * s.x, lo.y * c.y - hi.y * s.y);
-      o_hi = pack_bf16(hi.x * c.x + lo.x * s.x, hi.y * c.y + lo.y * s.y);
-    } else {
-      o_lo = pack_bf16(lo.x, lo.y);
-      o_hi = pack_bf16(hi.x, hi.y);
+      const float4 c = *reinterpret_cast<const float4*>(p.cos_t + t * (D / 2) + pair);
+      const float4 s4 = *reinterpret_cast<const float4*>(p.sin_t + t * (D / 2) + pair);
+      const float cv[4] = {c.x, c.y, c.z, c.w}, sv[4] = {s4.x, s4.y, s4.z, s4.w};
+      float o[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float other = __shfl_xor_sync(0xffffffffu, x[i], 16);
+        // first half: x1 * cos - x2 * sin ; second half: x2 * cos + x1 * sin
+        o[i] = low ? (x[i] * cv[i] - other * sv[i]) : (x[i] * cv[i] + other * sv[i]);
+      }
+      raw = make_uint2(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]));
     }
     const long long row = static_cast<long long>(p.rank) * p.Tl + t;
     if (is_q) {
       const int o = h / Hql, hl = h - o * Hql;
       __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.peers.base[o] + p.off_q) + (row * Hql + hl) * D;
-      *reinterpret_cast<uint32_t*>(dst + 2 * lane) = o_lo;
-      *reinterpret_cast<uint32_t*>(dst + 64 + 2 * lane) = o_hi;
+      *reinterpret_cast<uint2*>(dst + 4 * lane) = raw;
     } else {
       const int hk = is_k ? h - p.Hq : h - p.Hq - p.Hk;
       const long long off = is_k ? p.off_k : p.off_v;
@@ -461,8 +469,7 @@ __global__ void ulysses_qkv_scatter_kernel(const UlyQkvParams p) {
         const int r = hk * p.rep + i;
         const int o = r / Hkl, hl = r - o * Hkl;
         __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.peers.base[o] + off) + (row * Hkl + hl) * D;
-        *reinterpret_cast<uint32_t*>(dst + 2 * lane) = o_lo;
-        *reinterpret_cast<uint32_t*>(dst + 64 + 2 * lane) = o_hi;
+        *reinterpret_cast<uint2*>(dst + 4 * lane) = raw;
       }
     }
   }
