@@ -181,7 +181,9 @@ class P2PTokenDispatcher:
         E = self.config.num_moe_experts
         ws = get_workspace(self.ep_group, x.shape[-1], E, T, k, self.capacity_factor)
         idx32 = idx.to(torch.int32).contiguous()
-        counts = torch.bincount(idx32.reshape(-1), minlength=E).to(torch.int32)
+        # histogram without the host sync torch.bincount makes on CUDA (it reads the maximum back)
+        counts = torch.zeros(E, dtype=torch.int32, device=x.device)
+        counts.scatter_add_(0, idx32.reshape(-1).long(), torch.ones(idx32.numel(), dtype=torch.int32, device=x.device))
         xp, rp, seg_start, recv_counts, tile_group, dest_row, expert = _Dispatch.apply(
             x.contiguous(), prob.float().contiguous(), idx32, counts, ws)
         perm = MoEPermutation(tokens=xp, probs=rp, row_indices=dest_row.view(T, k), expert_indices=idx.long(),
