@@ -22,19 +22,43 @@ from ....ops import ops
 IGNORE_INDEX = -100
 
 
+_STAGING: dict[tuple, tuple[torch.Tensor, "torch.cuda.Event | None"]] = {}
+
+
+def _to_device_async(host: torch.Tensor, device: torch.device) -> torch.Tensor:
+    """Host -> device copy that does not block the host: staged through a cached pinned buffer (a copy from pageable
+    memory waits for the stream).  The buffer is reused only after its previous copy has finished."""
+    if device.type != "cuda":
+        return host.to(device)
+    key = (tuple(host.shape), host.dtype, device.index)
+    buf, ev = _STAGING.get(key, (None, None))
+    if buf is None:
+        buf = torch.empty(host.shape, dtype=host.dtype, pin_memory=True)
+    elif ev is not None:
+        ev.synchronize()
+    buf.copy_(host)
+    out = buf.to(device, non_blocking=True)
+    ev = torch.cuda.Event()
+    ev.record(torch.cuda.current_stream(device))
+    _STAGING[key] = (buf, ev)
+    return out
+
+
 def shift_labels_packed(labels: torch.Tensor, cu_seq_lens: torch.Tensor, shift: int = 1) -> torch.Tensor:
     """labels [1, T] -> shifted [1, T]: position t gets `labels[t + shift]` unless that target lies beyond the
-    end of t's document (or t is padding after `cu[-1]`), in which case it gets -100."""
+    end of t's document (or t is padding after `cu[-1]`), in which case it gets -100.  The validity mask depends on
+    the (host) boundaries only; it is built on the host and sent without blocking."""
     T = labels.shape[-1]
     flat = labels.reshape(-1)
     out = torch.full_like(flat, IGNORE_INDEX)
     if shift < T:
         out[: T - shift] = flat[shift:]
-    cu = cu_seq_lens.to(device=labels.device, dtype=torch.long)
-    pos = torch.arange(T, device=labels.device)
+    cu = torch.as_tensor(cu_seq_lens).to(device="cpu", dtype=torch.long)
+    pos = torch.arange(T)
     seg = torch.searchsorted(cu, pos, right=True)              # index of the boundary after pos
     seg_end = torch.where(seg < cu.numel(), cu[seg.clamp(max=cu.numel() - 1)], torch.zeros_like(pos))
-    out = torch.where(pos + shift < seg_end, out, torch.full_like(out, IGNORE_INDEX))
+    keep = _to_device_async(pos + shift < seg_end, labels.device)
+    out = torch.where(keep, out, torch.full_like(out, IGNORE_INDEX))
     return out.view_as(labels)
 
 
