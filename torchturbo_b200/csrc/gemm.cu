@@ -52,8 +52,11 @@ struct SmemLayout {
   static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
+constexpr int EPI_WARPS = 8;                       // two warps per TMEM lane quarter, each takes half of the columns
+constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
+
 template <int BN, bool A_MN, bool B_MN, int EPI>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
   using L = SmemLayout<BN, A_MN, B_MN>;
   constexpr int STAGES = L::STAGES;
@@ -76,7 +79,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull[a], 1);
-      mbar_init(&tempty[a], 4);
+      mbar_init(&tempty[a], EPI_WARPS);
     }
     mbar_fence_init();
   }
@@ -215,8 +218,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2..5)
+    // ------------------------------------------------------------ epilogue (warps 2..9)
     const int lane_group = warp & 3;  // TMEM lanes [32*lane_group, +32) are the ones this warp may touch
+    const int col_half = (warp - 2) >> 2;  // which half of the tile's column chunks this warp stores
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -236,7 +240,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         uint8_t* cbase = reinterpret_cast<uint8_t*>(p.C);
         const long long coff = static_cast<long long>(g) * p.c_group_stride + static_cast<long long>(row) * p.ldc;
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        constexpr int CH = BN / 32 / (EPI_WARPS / 4);
+        for (int c = col_half * CH; c < (col_half + 1) * CH; ++c) {
           const int col0 = n0 + c * 32;
           if (col0 >= p.N) break;  // uniform across the warp
           uint32_t v[32];
@@ -313,7 +318,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc;
         __nv_bfloat16* pre = p.preact ? p.preact + static_cast<long long>(row) * p.ld_preact : nullptr;
 #pragma unroll 1
-        for (int c = 0; c < HALF / 32; ++c) {
+        constexpr int CH = HALF / 32 / (EPI_WARPS / 4);
+        for (int c = col_half * CH; c < (col_half + 1) * CH; ++c) {
           const int col0 = n0 + c * 32;
           if (col0 >= p.N) break;
           uint32_t gv[32], uv[32];
@@ -479,7 +485,7 @@ static int launch(const GemmArgs& a, cudaStream_t stream) {
   long long total = static_cast<long long>(p.m_tiles) * p.n_tiles * (p.groups_k > 0 ? p.groups_k : 1);
   if (total <= 0) return 0;
   int grid = static_cast<int>(total < a.num_sms ? total : a.num_sms);
-  kfn<<<grid, 192, L::TOTAL, stream>>>(tmA, tmB, p);
+  kfn<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(tmA, tmB, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + static_cast<int>(e);
 }
