@@ -12,7 +12,8 @@ than ranks, a model-provided dummy medium for ranks that received nothing (so FS
 aligned), no balancing under `torch.no_grad()`, and gradients materialised for every stream so that all ranks run the
 same backward exchanges in the same order.
 
-Transport: `all_to_all` from `comm` (NCCL / gloo); row exchanges are plain all-to-all-v on dim 0.
+Transport: on an NVLink domain the rows are written straight into the owners' buffers by a peer-memory kernel
+(`comm/rows_p2p.py`); elsewhere `all_to_all` from `comm` (NCCL / gloo).  Row exchanges are all-to-all-v on dim 0.
 """
 from __future__ import annotations
 
@@ -80,6 +81,22 @@ class MediaPool:
 
     def in_group(self, group: int, sp_size: int) -> list[MediaMeta]:
         return [m for m in self.media if m.src // sp_size == group]
+
+    def pixel_matrix(self, world: int) -> list[list[int]]:
+        """`m[s][d]`: pixel rows rank `s` sends to owner `d`."""
+        m = [[0] * world for _ in range(world)]
+        for x in self.media:
+            m[x.src][x.owner] += x.patches
+        return m
+
+    def fanout_matrix(self, stream: str, world: int, sp_size: int) -> list[list[int]]:
+        """`m[o][d]`: output rows of `stream` owner `o` returns to rank `d` (every member of the source group)."""
+        m = [[0] * world for _ in range(world)]
+        for x in self.media:
+            g = x.src // sp_size
+            for d in range(g * sp_size, (g + 1) * sp_size):
+                m[x.owner][d] += x.tokens[stream]
+        return m
 
     def loads(self, world_size: int) -> list[int]:
         out = [0] * world_size
@@ -197,6 +214,17 @@ class VisionBalanceState:
         table = out.view(self.world, max(mx, 1), width).cpu().tolist()
         return [table[r][: counts_l[r]] for r in range(self.world)]
 
+    # -- transport -----------------------------------------------------------------------------------
+    def _exchange(self, send, recv_splits, send_splits, matrix):
+        """Rows to their destinations: peer-memory stores on an NVLink domain (every rank knows the whole split matrix,
+        so destination offsets need no extra exchange), NCCL / gloo all-to-all-v otherwise."""
+        if send.is_cuda and send.dim() == 2:
+            from ....comm import rows_p2p
+
+            if rows_p2p.usable(self.world_group, send):
+                return rows_p2p.p2p_all_to_all_rows(self.world_group, send, matrix)
+        return all_to_all(self.world_group, send, recv_splits, send_splits)
+
     # -- hooks ---------------------------------------------------------------------------------------
     def pre_forward(self, module, args, kwargs):
         self._ctx = None
@@ -222,7 +250,7 @@ class VisionBalanceState:
         else:
             send = batch.pixels[:0]
         with torch.no_grad():
-            recv = all_to_all(self.world_group, send.contiguous(), plan.recv_splits, plan.send_splits)
+            recv = self._exchange(send.contiguous(), plan.recv_splits, plan.send_splits, pool.pixel_matrix(self.world))
         mine = pool.assigned_to(self.rank)
         # received rows are source-major with the sender's (owner, index) order == pooled order per source
         if mine:
@@ -249,7 +277,8 @@ class VisionBalanceState:
             plan = FanoutPlan.build(pool, name, self.rank, self.world, self.sp_size)
             idx = torch.tensor(plan.send_rows, dtype=torch.long, device=x.device)
             send = x.index_select(0, idx) if idx.numel() else x[:0]
-            recv = all_to_all(self.world_group, send.contiguous(), plan.recv_splits, plan.send_splits)
+            recv = self._exchange(send.contiguous(), plan.recv_splits, plan.send_splits,
+                                  pool.fanout_matrix(name, self.world, self.sp_size))
             ridx = torch.tensor(plan.restore, dtype=torch.long, device=x.device)
             restored.append(recv.index_select(0, ridx) if ridx.numel() else recv[:0])
         restored = _MaterializeOutputGradients.apply(*restored)
