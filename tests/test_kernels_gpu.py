@@ -401,3 +401,23 @@ def test_ulysses_peer_kernels_single_rank(K, tmp_path):
     finally:
         if created:
             dist.destroy_process_group()
+
+
+def test_newton_schulz_on_tcgen05_gemm(K):
+    """Muon's orthogonalisation through the library GEMM against the torch bmm formulation."""
+    from torchturbo_b200.engine.optimizers import muon
+
+    torch.manual_seed(0)
+    G = torch.randn(3, 256, 512, device="cuda")
+    coeffs = (3.4445, -4.7750, 2.0315)
+    got = muon.newton_schulz(G, 5, coeffs, 1e-7)
+    X = G.to(torch.bfloat16)
+    X = X / (X.float().norm(dim=(-2, -1), keepdim=True) + 1e-7).to(X.dtype)
+    for _ in range(5):
+        A = X @ X.transpose(-2, -1)
+        B = torch.baddbmm(A, A, A, beta=coeffs[1], alpha=coeffs[2])
+        X = torch.baddbmm(X, B, X, beta=coeffs[0], alpha=1.0)
+    assert got.shape == G.shape
+    _close(got, X, rtol=5e-2, atol=5e-2)
+    s = torch.linalg.svdvals(got[0].float())
+    assert float(s.max()) < 1.3 and float(s.min()) > 0.3          # singular values pulled towards one

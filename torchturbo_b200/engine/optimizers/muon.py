@@ -95,6 +95,32 @@ def default_decoder_muon_recipe(model: nn.Module) -> MuonRecipe:
     return MuonRecipe(rec, exclude=("**.embed_tokens.weight", "lm_head.weight", "**.router.weight", "**.visual.**"))
 
 
+def _ns_tcgen05_ok(X: torch.Tensor) -> bool:
+    if not X.is_cuda or X.shape[-1] % 8 or X.shape[-2] % 8:
+        return False
+    from ... import kernels as K
+
+    return K.available()
+
+
+def _newton_schulz_tcgen05(X: torch.Tensor, steps: int, coeffs) -> torch.Tensor:
+    """The iteration on the library's tcgen05 GEMM, one matrix of the batch at a time: `A = X X^T` and `A A` (A is
+    symmetric, so both are NT products), `X <- a X + B X` with the `a X` term added by the GEMM's residual epilogue."""
+    from ... import kernels as K
+
+    per_step = isinstance(coeffs[0], (tuple, list))
+    out = []
+    for x in X:
+        x = x.contiguous()
+        for i in range(steps):
+            a, b, c = coeffs[i] if per_step else coeffs
+            A = K.gemm(x, x)                                     # [r, r] = x x^T
+            B = K.gemm(A, A, residual=(A * (b / c)).contiguous()) * c if c != 0 else A * b     # b A + c A A
+            x = K.gemm(B.contiguous(), x, b_mn=True, residual=(x * a).contiguous())            # a x + B x
+        out.append(x)
+    return torch.stack(out, 0)
+
+
 def newton_schulz(G: torch.Tensor, steps: int, coeffs, eps: float) -> torch.Tensor:
     """Batched Newton-Schulz orthogonalisation in bf16.  G: [b, r, c] -> same shape."""
     X = G.to(torch.bfloat16)
@@ -102,6 +128,9 @@ def newton_schulz(G: torch.Tensor, steps: int, coeffs, eps: float) -> torch.Tens
     if transposed:
         X = X.transpose(-2, -1)
     X = X / (X.float().norm(dim=(-2, -1), keepdim=True) + eps).to(X.dtype)
+    if X.dim() == 3 and _ns_tcgen05_ok(X):
+        X = _newton_schulz_tcgen05(X, steps, coeffs)
+        return X.transpose(-2, -1) if transposed else X
     per_step = isinstance(coeffs[0], (tuple, list))
     for i in range(steps):
         a, b, c = coeffs[i] if per_step else coeffs
