@@ -2,6 +2,7 @@
 per-kernel device time of one step of the flagship model at a reduced depth.
 
     python -m torchturbo_b200.benchmarks.step_profile [--layers 4] [--model qwen3_moe_30b_a3b] [--seq-len 4096] [--rows 40]
+    torchrun --nproc-per-node N -m torchturbo_b200.benchmarks.step_profile ...     # expert parallel over N ranks, rank 0 prints
 """
 from __future__ import annotations
 
@@ -28,7 +29,13 @@ def main(argv=None) -> None:
     from ..engine.optimizers import OptimizerClassPlan
     from ..loops import train_step
 
+    import os
+
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    is_moe = "moe" in args.model
     eng = TorchTurboEngine(EngineConfig.from_dict({"mixed_precision": "bf16", "moe": {"aux_loss_coeff": 1e-3},
+                                                   "parallel_plan": {"sp_size": 1, "ep_size": world if is_moe else 1},
                                                    "activation_checkpointing": {"enabled": False}}))
     mc = model_config(args.model, args.layers)
     model = eng.build_model(None, load_weights=False, init_kwargs={"config": mc})
@@ -47,13 +54,18 @@ def main(argv=None) -> None:
     t1 = time.perf_counter()
     torch.cuda.synchronize()
     t2 = time.perf_counter()
-    print(f"cpu issue time per step {(t1 - t0) / 3 * 1e3:.1f} ms, total per step {(t2 - t0) / 3 * 1e3:.1f} ms")
+    if rank == 0:
+        print(f"cpu issue time per step {(t1 - t0) / 3 * 1e3:.1f} ms, total per step {(t2 - t0) / 3 * 1e3:.1f} ms")
     from torch.profiler import ProfilerActivity, profile
 
     with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
         train_step(eng, model, opt, [batches[0]], check_finite=False)
         torch.cuda.synchronize()
-    print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=args.rows, max_name_column_width=70))
+    if rank == 0:
+        print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=args.rows, max_name_column_width=70))
+    if world > 1:
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
 
 
 if __name__ == "__main__":
