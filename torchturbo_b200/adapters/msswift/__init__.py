@@ -13,7 +13,8 @@ from typing import Any
 from ...engine.args import get_torchturbo_args
 from ...engine.config import build_from_args
 from ...registry import BaseAdapter, BasePatch, register_adapter
-from ..hf_trainer import normalize_training_features
+from .inputs_bridging import (SwiftInputCollator, bake_loss_scale_into_labels, bridge_packed_inputs,  # noqa: F401
+                              bridge_swift_inputs, bridge_unpacked_inputs)
 
 _FORCED_OFF = {"gradient_checkpointing": False, "sequence_parallel_size": 1, "deepspeed": None, "fsdp": ""}
 
@@ -27,21 +28,6 @@ def build_config_from_swift_args(args: Any, stage: str, tt_args=None):
         if hasattr(args, k):
             setattr(args, k, v)
     return build_from_args(tt_args or get_torchturbo_args(), defaults=defaults)
-
-
-class SwiftInputCollator:
-    """Wraps swift's template collator: whatever it returns (packed with `position_ids` resets, or padded) becomes
-    one packed row; per-token `loss_scale` is baked into the labels (tokens with scale 0 become -100)."""
-
-    def __init__(self, inner):
-        self.inner = inner
-
-    def __call__(self, batch):
-        f = self.inner(batch)
-        ls = f.pop("loss_scale", None)
-        if ls is not None and f.get("labels") is not None:
-            f["labels"] = f["labels"].masked_fill(ls == 0, -100)
-        return normalize_training_features(f)
 
 
 class PipelinePatch(BasePatch):
