@@ -40,6 +40,10 @@ def parse():
     p.add_argument("--model", default="qwen3_moe_30b_a3b", choices=["qwen3_moe_30b_a3b", "qwen3_8b", "qwen3_14b", "tiny_moe"])
     p.add_argument("--sp", type=int, default=1, help="Ulysses sequence-parallel size (a sequence of --seq-len tokens per SP group)")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--fsdp-transport", default="auto", choices=["auto", "nccl", "p2p"],
+                   help="all-gather / reduce-scatter of the FSDP units: peer-memory kernels (auto / p2p) or NCCL")
+    p.add_argument("--fsdp-unit-mb", type=int, default=-1, help="merge decoder layers into FSDP units of at least "
+                   "this many MiB of bf16 parameters (-1: engine default, 0: one unit per layer)")
     p.add_argument("--ep-transport", default="auto", choices=["auto", "nccl", "p2p"],
                    help="expert-parallel token exchange: NVLink peer-memory kernels (p2p) or NCCL all-to-all")
     return p.parse_args()
@@ -135,6 +139,8 @@ def run_ours(args) -> dict:
         "parallel_plan": {"sp_size": sp, "ep_size": world if is_moe else 1},
         "moe": {"aux_loss_coeff": 1e-3},
         "activation_checkpointing": {"enabled": not is_moe},
+        "backend_config": dict({"transport": args.fsdp_transport},
+                               **({"unit_min_bytes": args.fsdp_unit_mb << 20} if args.fsdp_unit_mb >= 0 else {})),
     })
     engine = TorchTurboEngine(cfg)
     mc = model_config(args.model, layers)
@@ -217,7 +223,10 @@ def run_ours(args) -> dict:
                    "layers_named": 48, "global_batch": world // sp, "seq_len": args.seq_len,
                    "parallelism": f"fsdp2 dp{world // sp} + ep{world if is_moe else 1}" + (f" + ulysses sp{sp}" if sp > 1 else ""),
                    "sp_transport": os.environ.get("TORCHTURBO_ULYSSES_TRANSPORT", "auto") if sp > 1 else "none", "optimizer": "AdamW fp32 master",
-                   "ep_transport": ep_transport, "depth_rule": "layers = min(48, 12 * n_gpus): the deepest stack whose "
+                   "ep_transport": ep_transport,
+                   "fsdp_transport": "p2p" if getattr(engine.backend, "peer_arenas", None) else ("nccl" if world > 1 else "local"),
+                   "fsdp_units": len(engine.backend.fsdp_units),
+                   "reshard_after_forward": engine.backend.fsdp_config.reshard_after_forward, "depth_rule": "layers = min(48, 12 * n_gpus): the deepest stack whose "
                    "weights + fp32 AdamW state fit 180 GB per GPU without activation checkpointing; 48 (the named "
                    "model) at 8 GPUs", "tokens_per_s_scaled_to_48_layers": value * layers / 48.0,
                    "l2": "per-step working set (weights, optimizer state, activations: tens of GB) is far larger than the 126 MB L2"},

@@ -104,7 +104,7 @@ def test_four_layer_merge_precedence(tmp_path):
     assert c.plugin_paths == ["a.py", "b.py:cfg"]
     # built-in defaults
     d = build_from_args(TorchTurboArgs(), env={})
-    assert d.mixed_precision is MixedPrecisionPolicy.FP32 and d.backend_config.reshard_after_forward is True
+    assert d.mixed_precision is MixedPrecisionPolicy.FP32 and d.backend_config.reshard_after_forward == "auto"
     assert d.activation_checkpointing.enabled is True and d.checkpoint.hf_export == "every"
 
 

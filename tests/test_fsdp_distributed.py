@@ -92,3 +92,43 @@ def test_ulysses_sp2_matches_sp1():
     a, b = torch.load("/tmp/tt_sp1.pt"), torch.load("/tmp/tt_sp2.pt")
     assert torch.allclose(a[:, 0], b[:, 0], rtol=1e-4, atol=1e-5), (a, b)
     assert torch.allclose(a[:, 1], b[:, 1], rtol=1e-3, atol=1e-4), (a, b)
+
+
+def _w_merged(rank, world, unit_bytes, ac, reshard):
+    from torchturbo_b200.data import PackedCollator, SyntheticPackedDataset
+    from torchturbo_b200.engine import EngineConfig, TorchTurboEngine
+    from torchturbo_b200.engine.optimizers import OptimizerClassPlan
+    from torchturbo_b200.loops import train_step
+
+    mc = dict(MOE, num_hidden_layers=4)
+    eng = TorchTurboEngine(EngineConfig.from_dict({
+        "mixed_precision": "fp32", "parallel_plan": {"sp_size": 1, "ep_size": 1}, "moe": {"aux_loss_coeff": 1e-2},
+        "activation_checkpointing": {"enabled": ac},
+        "backend_config": {"unit_min_bytes": unit_bytes, "reshard_after_forward": reshard}}))
+    model = eng.build_model(None, load_weights=False, init_kwargs={"config": mc, "seed": 0})
+    units = eng.backend.fsdp_units
+    layers = [m for m in units if type(m).__name__.endswith("DecoderLayer")]
+    if unit_bytes:
+        assert len(layers) == 2 and all(len(m._tt_group) == 2 for m in layers), [len(m._tt_group) for m in layers]
+    else:
+        assert len(layers) == 4
+    opt = eng.prepare_optimizer(model, OptimizerClassPlan(torch.optim.AdamW, lr=1e-2, weight_decay=0.0))
+    ds = SyntheticPackedDataset(8, 64, mc["vocab_size"], num_docs=3, seed=5)
+    out = []
+    for i in range(3):
+        loss, gn = train_step(eng, model, opt, [PackedCollator()([ds[i]])])
+        out.append((float(loss), float(gn)))
+    if rank == 0:
+        torch.save(torch.tensor(out), f"/tmp/tt_merged_{unit_bytes}_{int(ac)}_{int(reshard)}.pt")
+
+
+@pytest.mark.parametrize("ac,reshard", [(False, True), (True, True), (True, False)])
+def test_merged_fsdp_units_match_per_layer_units(ac, reshard):
+    """Two decoder layers per FSDP unit (one all-gather / reduce-scatter for both) train exactly like one unit per
+    layer, with and without activation recomputation and with parameters kept gathered until backward."""
+    # one tiny MoE layer without its experts is ~26 KB of bf16-equivalent bytes: 50 KB merges two layers
+    run_distributed(_w_merged, 2, 0, ac, True)
+    run_distributed(_w_merged, 2, 50_000, ac, reshard)
+    a = torch.load(f"/tmp/tt_merged_0_{int(ac)}_1.pt")
+    b = torch.load(f"/tmp/tt_merged_50000_{int(ac)}_{int(reshard)}.pt")
+    assert torch.allclose(a, b, rtol=1e-5, atol=1e-6), (a, b)

@@ -244,6 +244,28 @@ def test_adamw_and_clip(K):
         _close(s, rp.detach(), atol=1e-2)
 
 
+def test_fused_adamw_gradient_prescale(K):
+    """`FusedAdamW.grad_prescale` (the 1/ep scaling of expert gradients) equals scaling the gradients beforehand,
+    in the squared-norm reduction and in the update, and is cleared by `step()`."""
+    from torchturbo_b200.engine.optimizers import FusedAdamW
+
+    torch.manual_seed(1)
+    a = [torch.randn(300, 70, device="cuda").bfloat16().requires_grad_(True) for _ in range(2)]
+    b = [x.detach().clone().requires_grad_(True) for x in a]
+    gs = [torch.randn_like(x) for x in a]
+    oa, ob = FusedAdamW(a, lr=1e-2), FusedAdamW(b, lr=1e-2)
+    for x, y, g in zip(a, b, gs):
+        x.grad, y.grad = g.clone(), (g.float() * 0.25).to(g.dtype)
+    oa.grad_prescale = 0.25
+    sa, sb = oa.grad_sq_sum(), ob.grad_sq_sum()
+    _close(sa, sb, rtol=2e-2, atol=1e-3)          # b's gradients were rounded to bf16 after scaling
+    oa.step(); ob.step()
+    assert oa.grad_prescale == 1.0
+    for x, y in zip(a, b):
+        _close(x.detach(), y.detach(), atol=2e-2)
+        _close(oa.state[x]["master"], ob.state[y]["master"], rtol=2e-2, atol=1e-4)
+
+
 @pytest.mark.parametrize("score_fn", ["softmax_post", "softmax_pre", "sigmoid"])
 def test_router(K, score_fn):
     torch.manual_seed(0)

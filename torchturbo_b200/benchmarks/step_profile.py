@@ -1,7 +1,7 @@
 """Where one training step spends its time: CPU issue time per step (host-bound or not) and the torch profiler's
 per-kernel device time of one step of the flagship model at a reduced depth.
 
-    python -m torchturbo_b200.benchmarks.step_profile [--layers 4] [--model qwen3_moe_30b_a3b] [--seq-len 4096] [--rows 40]
+    python -m torchturbo_b200.benchmarks.step_profile [--layers 4] [--model qwen3_moe_30b_a3b] [--seq-len 4096] [--rows 40] [--sort self_cpu_time_total]
     torchrun --nproc-per-node N -m torchturbo_b200.benchmarks.step_profile ...     # expert parallel over N ranks, rank 0 prints
 """
 from __future__ import annotations
@@ -20,6 +20,7 @@ def main(argv=None) -> None:
     ap.add_argument("--model", default="qwen3_moe_30b_a3b")
     ap.add_argument("--seq-len", type=int, default=4096)
     ap.add_argument("--rows", type=int, default=40)
+    ap.add_argument("--sort", default="cuda_time_total", help="profiler sort key, e.g. self_cpu_time_total")
     args = ap.parse_args(argv)
     sys.path.insert(0, str(Path(__file__).resolve().parents[2]))
     from bench import model_config  # the benchmark's model table (repository root)
@@ -62,7 +63,7 @@ def main(argv=None) -> None:
         train_step(eng, model, opt, [batches[0]], check_finite=False)
         torch.cuda.synchronize()
     if rank == 0:
-        print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=args.rows, max_name_column_width=70))
+        print(prof.key_averages().table(sort_by=args.sort, row_limit=args.rows, max_name_column_width=70))
     if world > 1:
         torch.distributed.barrier()
         torch.distributed.destroy_process_group()

@@ -589,3 +589,152 @@ TTB_EXPORT int ttb_ulysses_move(const unsigned long long* peer_ptrs, long long o
     ulysses_scatter_kernel<<<grid, 256, 0, STREAM(stream)>>>(p);
   LAUNCH_RET();
 }
+
+// ------------------------------------------------------------------------------------------------------------
+// Sharded-data-parallel collectives over peer memory (the all-gather of parameter shards and the reduce-scatter
+// of gradients of one FSDP unit).  Both are PULL kernels on a slot of the symmetric buffer that has the same
+// offset on every rank:
+//   all-gather     : slot = [W][n] pieces; rank r has written piece r; the kernel copies every other piece from
+//                    its owner's slot into the local slot.
+//   reduce-scatter : slot = [W][n] gradient pieces (piece q is what rank q must reduce); the kernel computes
+//                    out[i] = scale * sum_p slot_of(p)[rank][i] in fp32 (bf16 or fp32 pieces) - the cast, the
+//                    averaging scale and the reduction in one pass over NVLink.
+// Flags: `ready[src]` (peer src has filled its slot for this epoch) is waited on before the first remote load;
+// `consumed[src]` is raised on every peer when this rank has finished reading, and the next writer of the slot
+// waits for it (host side, stream-ordered).  Waits are bounded; after a timeout no remote memory is touched.
+// The NCCL ring kernels these replace: torch FSDP2's all_gather_into_tensor / reduce_scatter_tensor calls under
+// the reference's fully_shard units (engine/backends/fsdp2/backend.py:420-470 of the reference).
+// ------------------------------------------------------------------------------------------------------------
+namespace ttb {
+
+struct PeerCollParams {
+  PeerTable peers;
+  long long off_data, off_ready, off_consumed;
+  long long units;   // 16-byte units per piece
+  int rank, W, epoch;
+  unsigned long long budget_ns;
+  float scale;
+  void* out;         // reduce-scatter result (local memory), same element type as the pieces
+  unsigned int* done_counter;
+  int* status;
+};
+
+__device__ __forceinline__ bool coll_wait_ready(const PeerCollParams& p, unsigned site) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (threadIdx.x < p.W && static_cast<int>(threadIdx.x) != p.rank) {
+    const int* f = reinterpret_cast<const int*>(p.peers.base[p.rank] + p.off_ready) + threadIdx.x;
+    if (!wait_flag(f, p.epoch, p.budget_ns, site, threadIdx.x, p.status)) s_ok = 0;
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+
+__device__ __forceinline__ void coll_signal_consumed(const PeerCollParams& p) {
+  __shared__ unsigned s_last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(p.done_counter, 1u) == gridDim.x - 1) ? 1u : 0u;
+  __syncthreads();
+  if (s_last) {
+    if (threadIdx.x < p.W)
+      st_release_sys(reinterpret_cast<int*>(p.peers.base[threadIdx.x] + p.off_consumed) + p.rank, p.epoch);
+    if (threadIdx.x == 0) *p.done_counter = 0;
+  }
+}
+
+__global__ void __launch_bounds__(512) peer_allgather_kernel(const PeerCollParams p) {
+  if (coll_wait_ready(p, 7)) {
+    const long long total = p.units * (p.W - 1);
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    uint4* mine = reinterpret_cast<uint4*>(p.peers.base[p.rank] + p.off_data);
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += 4 * stride) {
+      uint4 v[4];
+      long long at[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const long long ii = i + u * stride;
+        at[u] = -1;
+        if (ii < total) {
+          const int j = static_cast<int>(ii / p.units);
+          const int peer = (p.rank + 1 + j) % p.W;
+          at[u] = static_cast<long long>(peer) * p.units + (ii - j * p.units);
+          v[u] = __ldcg(reinterpret_cast<const uint4*>(p.peers.base[peer] + p.off_data) + at[u]);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (at[u] >= 0) mine[at[u]] = v[u];
+    }
+  }
+  coll_signal_consumed(p);
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(512) peer_reduce_scatter_kernel(const PeerCollParams p) {
+  if (coll_wait_ready(p, 8)) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    const long long piece = static_cast<long long>(p.rank) * p.units;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < p.units; i += stride) {
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int j0 = 0; j0 < p.W; j0 += 4) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (j0 + u < p.W) {
+            const int peer = (p.rank + j0 + u) % p.W;
+            v[u] = __ldcg(reinterpret_cast<const uint4*>(p.peers.base[peer] + p.off_data) + piece + i);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (j0 + u < p.W) {
+            if (BF16) {
+              const float2 a = unpack_bf16(v[u].x), b = unpack_bf16(v[u].y), c = unpack_bf16(v[u].z), d = unpack_bf16(v[u].w);
+              acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
+              acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+            } else {
+              acc[0] += __uint_as_float(v[u].x); acc[1] += __uint_as_float(v[u].y);
+              acc[2] += __uint_as_float(v[u].z); acc[3] += __uint_as_float(v[u].w);
+            }
+          }
+        }
+      }
+      uint4 o;
+      if (BF16) {
+        o.x = pack_bf16(acc[0] * p.scale, acc[1] * p.scale); o.y = pack_bf16(acc[2] * p.scale, acc[3] * p.scale);
+        o.z = pack_bf16(acc[4] * p.scale, acc[5] * p.scale); o.w = pack_bf16(acc[6] * p.scale, acc[7] * p.scale);
+      } else {
+        o.x = __float_as_uint(acc[0] * p.scale); o.y = __float_as_uint(acc[1] * p.scale);
+        o.z = __float_as_uint(acc[2] * p.scale); o.w = __float_as_uint(acc[3] * p.scale);
+      }
+      reinterpret_cast<uint4*>(p.out)[i] = o;
+    }
+  }
+  coll_signal_consumed(p);
+}
+
+}  // namespace ttb
+
+// kind: 0 = all-gather (any element type, `units` 16-byte units per piece), 1 = reduce-scatter of fp32 pieces,
+// 2 = reduce-scatter of bf16 pieces.  The caller has already raised its own `ready` flag (ttb_flag_signal) in
+// stream order after filling the slot.
+TTB_EXPORT int ttb_peer_collective(const unsigned long long* peer_ptrs, long long off_data, long long off_ready,
+                                   long long off_consumed, long long units, int rank, int W, int epoch,
+                                   long long budget_ms, float scale, void* out, unsigned int* done_counter, int* status,
+                                   int kind, int grid, void* stream) {
+  using namespace ttb;
+  if (W > MAX_RANKS || W < 2 || units < 0 || off_data % 16) return 901;
+  if (kind != 0 && (out == nullptr || reinterpret_cast<unsigned long long>(out) % 16)) return 903;
+  PeerCollParams p{make_peers(peer_ptrs, W), off_data, off_ready, off_consumed, units, rank, W, epoch,
+                   static_cast<unsigned long long>(budget_ms) * 1000000ull, scale, out, done_counter, status};
+  if (grid < 1) grid = 1;
+  if (kind == 0)
+    peer_allgather_kernel<<<grid, 512, 0, STREAM(stream)>>>(p);
+  else if (kind == 1)
+    peer_reduce_scatter_kernel<false><<<grid, 512, 0, STREAM(stream)>>>(p);
+  else
+    peer_reduce_scatter_kernel<true><<<grid, 512, 0, STREAM(stream)>>>(p);
+  LAUNCH_RET();
+}

@@ -176,6 +176,7 @@ class FSDP2Backend(BaseBackend):
         self._apply_activation_checkpointing(model, compiled)
         self._shard_model(model, compiled)
         self._setup_prefetch(model)
+        self._install_peer_collectives()
         self._register_vision_balance(model, compiled)
         self.gradient_scaling_factor = 1.0 / self.ep_size
         return model
@@ -260,30 +261,84 @@ class FSDP2Backend(BaseBackend):
             kw["offload_policy"] = CPUOffloadPolicy(pin_memory=True)
         return kw
 
-    def _make_unit(self, module: nn.Module, spec: FSDPPlanSpec | None, *, reshard: bool | None = None) -> None:
-        if getattr(module, "_tt_unit", None) is not None:
+    def _make_unit(self, module: nn.Module | list[nn.Module], spec: FSDPPlanSpec | None, *,
+                   reshard: bool | None = None) -> None:
+        """Make one unit of `module`, or of a list of sibling modules that share one all-gather / reduce-scatter
+        (the first module of the list is the unit's handle; the others are marked as members)."""
+        group = list(module) if isinstance(module, (list, tuple)) else [module]
+        group = [m for m in group if getattr(m, "_tt_unit", None) is None]
+        if not group:
             return
         mesh, is_expert = self._mesh_for(spec)
-        own = [p for p in module.parameters()]
-        if is_expert and module not in self.expert_modules:
-            self.expert_modules.append(module)
+        own = [p for m in group for p in m.parameters()]
+        for m in group:
+            if is_expert and m not in self.expert_modules:
+                self.expert_modules.append(m)
         if mesh.size() > 1:
             from torch.distributed.fsdp import fully_shard
 
             skip = {id(q) for q in self.no_shard_params}
-            for sub in module.modules():
-                if sub is not module and getattr(sub, "_tt_unit", None) == "local":
-                    skip.update(id(q) for q in sub.parameters())
+            for m in group:
+                for sub in m.modules():
+                    if sub is not m and getattr(sub, "_tt_unit", None) == "local":
+                        skip.update(id(q) for q in sub.parameters())
             ignored = {p for p in own if id(p) in skip}
             kw = self._fsdp_kwargs(mesh, is_expert=is_expert, reshard=reshard)
             if ignored:
                 kw["ignored_params"] = ignored
-            fully_shard(module, **kw)
-            module._tt_unit = "fsdp"
-            self.fsdp_units.append(module)
+            fully_shard(group if len(group) > 1 else group[0], **kw)
+            group[0]._tt_unit, group[0]._tt_group, group[0]._tt_mesh = "fsdp", group, mesh
+            for m in group[1:]:
+                m._tt_unit, m._tt_group = "fsdp_member", group
+            self.fsdp_units.append(group[0])
         else:
-            module._tt_unit = "local"
-            self.local_units.append(module)
+            for m in group:
+                m._tt_unit = "local"
+                self.local_units.append(m)
+
+    def _unit_param_bytes(self, module: nn.Module) -> int:
+        """bf16 bytes one all-gather of `module` as a unit of its own would deliver: parameters that are not
+        replicated and not owned by a nested unit."""
+        skip = {id(q) for q in self.no_shard_params}
+        for sub in module.modules():
+            if sub is not module and getattr(sub, "_tt_unit", None) is not None:
+                skip.update(id(q) for q in sub.parameters())
+        return sum(2 * p.numel() for p in module.parameters() if id(p) not in skip)
+
+    def _group_layers(self, layers: list[nn.Module]) -> list[list[nn.Module]]:
+        """Consecutive decoder layers are merged into one FSDP unit until the unit gathers at least
+        `unit_min_bytes`: a 30B-A3B layer without its experts is ~38 MB of bf16, far below the size at which the
+        host cost of a unit's hooks and the latency of its two collectives stop mattering."""
+        want = int(self.fsdp_config.unit_min_bytes)
+        if want <= 0 or self.world_mesh.size() <= 1:
+            return [[m] for m in layers]
+        groups, cur, cur_bytes = [], [], 0
+        for m in layers:
+            cur.append(m)
+            cur_bytes += self._unit_param_bytes(m)
+            if cur_bytes >= want:
+                groups.append(cur)
+                cur, cur_bytes = [], 0
+        if cur:
+            if groups and cur_bytes < want // 2:
+                groups[-1].extend(cur)
+            else:
+                groups.append(cur)
+        return groups
+
+    def _resolve_reshard(self, model: nn.Module, single_rank: list[nn.Module]) -> None:
+        """`reshard_after_forward: auto` keeps gathered bf16 parameters until backward has used them whenever all
+        FSDP-managed parameters together are a small part of the device memory (no second all-gather per unit)."""
+        if self.fsdp_config.reshard_after_forward != "auto":
+            return
+        resident = False
+        if torch.cuda.is_available() and self.world_mesh.size() > 1 and not self.fsdp_config.cpu_offload.enabled:
+            local = {id(p) for m in single_rank for p in m.parameters()} | {id(p) for p in self.no_shard_params}
+            total = sum(2 * p.numel() for p in model.parameters() if id(p) not in local)
+            cap = torch.cuda.get_device_properties(torch.cuda.current_device()).total_memory
+            resident = total <= self.fsdp_config.resident_fraction * cap
+        self.fsdp_config.reshard_after_forward = not resident
+        logger.info_rank0("reshard_after_forward resolved to %s", self.fsdp_config.reshard_after_forward)
 
     def _collect_no_shard(self, model: nn.Module, compiled: dict[str, FSDPPlanSpec]) -> None:
         """`no_shard` entries may name modules or single parameters; their parameters stay replicated and
@@ -309,17 +364,18 @@ class FSDP2Backend(BaseBackend):
         emb = model.get_input_embeddings() if hasattr(model, "get_input_embeddings") else None
         head = model.get_output_embeddings() if hasattr(model, "get_output_embeddings") else None
         tied = emb is not None and head is not None and getattr(head, "weight", None) is getattr(emb, "weight", object())
+        self._resolve_reshard(model, [model.get_submodule(fqn) for fqn, spec in explicit if self._mesh_for(spec)[0].size() <= 1])
         for fqn, spec in sorted(explicit, key=lambda kv: -kv[0].count(".")):
             mod = model.get_submodule(fqn)
             if tied and (mod is emb or mod is head):
                 continue  # tied input/output embeddings must live in one unit: the root
             self._make_unit(mod, spec)
-        # 2. every ModuleList child is a unit
+        # 2. every ModuleList child is a unit (small consecutive children share one)
         for _, mod in list(model.named_modules()):
             if isinstance(mod, nn.ModuleList):
-                for child in mod:
-                    if any(True for _ in child.parameters()):
-                        self._make_unit(child, None)
+                children = [c for c in mod if any(True for _ in c.parameters()) and getattr(c, "_tt_unit", None) is None]
+                for group in self._group_layers(children):
+                    self._make_unit(group, None)
         # 3. input embeddings, resident tail (final norm + output embedding), root
         if emb is not None and not tied:
             self._make_unit(emb, None)
@@ -329,6 +385,37 @@ class FSDP2Backend(BaseBackend):
         n_fsdp, n_local = len(self.fsdp_units), len(self.local_units)
         logger.info_rank0("sharding: %d FSDP unit(s), %d single-rank unit(s), %d replicated parameter(s)", n_fsdp,
                           n_local, len(self.no_shard_params))
+
+    def _install_peer_collectives(self) -> None:
+        """All-gather / reduce-scatter of the FSDP units run as peer-memory NVLink kernels where the group allows
+        it (`backend_config.transport`: auto | p2p | nccl)."""
+        self.peer_arenas = []
+        mode = str(self.fsdp_config.transport).lower()
+        if mode == "nccl" or not self.fsdp_units or not torch.cuda.is_available():
+            return
+        off = self.fsdp_config.cpu_offload
+        if off.enabled and off.mode is CPUOffloadMode.FULL:
+            return  # sharded parameters and gradients live on the host
+        from ....comm import fsdp_p2p
+
+        by_group: dict[int, tuple[Any, list]] = {}
+        for u in self.fsdp_units:
+            mesh = getattr(u, "_tt_mesh", None)
+            if mesh is None or mesh.ndim != 1:
+                continue
+            g = mesh.get_group()
+            by_group.setdefault(id(g), (g, []))[1].append(u)
+        depth = max(self.fsdp_config.forward_prefetch_depth, self.fsdp_config.backward_prefetch_depth)
+        for g, units in by_group.values():
+            if not fsdp_p2p.usable(g):
+                if mode == "p2p":
+                    raise RuntimeError("backend_config.transport=p2p needs one NVLink domain with one GPU per rank")
+                continue
+            arena = fsdp_p2p.install(units, g, prefetch_depth=depth)
+            if arena is not None:
+                self.peer_arenas.append(arena)
+        if self.peer_arenas:
+            logger.info_rank0("FSDP collectives over peer memory: %d group(s)", len(self.peer_arenas))
 
     def _setup_prefetch(self, model: nn.Module) -> None:
         if not self.fsdp_units:
@@ -537,11 +624,20 @@ class FSDP2Backend(BaseBackend):
         single-rank parameters; every gradient is then scaled by `min(1, max_norm / (norm + 1e-6))`.
         With the fused AdamW the coefficient is handed to the optimizer as a device scalar and applied inside
         the update kernel instead of in a separate pass."""
-        self._scale_moe_gradient(model)
         from ...optimizers import FusedAdamW, OptimizersContainer
 
         opts = list(optimizer) if isinstance(optimizer, OptimizersContainer) else ([optimizer] if optimizer is not None else [])
         dev = self.device
+        if self.ep_size > 1:
+            # the fused optimizer of the expert parameters folds the 1/ep scaling into its gradient reads
+            for o in opts:
+                if isinstance(o, FusedAdamW) and getattr(o, "_tt_topology", None) == "moe" and dev.type == "cuda":
+                    ps = [p for grp in o.param_groups for p in grp["params"]]
+                    if ps and not any(getattr(p, "_tt_grad_scaled", False) for p in ps):
+                        o.grad_prescale = self.gradient_scaling_factor
+                        for p in ps:
+                            p._tt_grad_scaled = True
+        self._scale_moe_gradient(model)
         sums = {"dense": torch.zeros((), dtype=torch.float32, device=dev), "moe": torch.zeros((), dtype=torch.float32, device=dev),
                 "local": torch.zeros((), dtype=torch.float32, device=dev)}
         covered: set[int] = set()

@@ -28,6 +28,7 @@ class FSDPPrefetchManager:
         self.config = config
         self.layer_chain: list[nn.Module] = []
         self.expert_chain: list[nn.Module | None] = []
+        self.expert_groups: list[list[nn.Module]] = []
         self._suspended = False
         self._saved: dict[int, list] = {}
 
@@ -41,8 +42,13 @@ class FSDPPrefetchManager:
                     best = units
         self.layer_chain = best
         self.expert_chain = []
+        self.expert_groups: list[list[nn.Module]] = []
         for layer in best:
-            ex = [m for m in layer.modules() if m is not layer and _is_fsdp(m)]
+            # a unit may hold several merged decoder layers: its expert units are those of all its members;
+            # the first one is the handle that carries expert -> expert prefetch lists
+            members = getattr(layer, "_tt_group", None) or [layer]
+            ex = [m for member in members for m in member.modules() if m not in members and _is_fsdp(m)]
+            self.expert_groups.append(ex)
             self.expert_chain.append(ex[0] if ex else None)
 
     def resolved_strategy(self) -> FSDPPrefetchStrategy:
@@ -80,16 +86,16 @@ class FSDPPrefetchManager:
         has = [e is not None for e in self.expert_chain]
         fwd = self.build_targets(n, self.config.forward_prefetch_depth, strategy, has)
         for i, (lt, el, ee) in enumerate(fwd):
-            mods = [self.layer_chain[j] for j in lt] + [self.expert_chain[j] for j in el]
+            mods = [self.layer_chain[j] for j in lt] + [e for j in el for e in self.expert_groups[j]]
             if mods:
                 self.layer_chain[i].set_modules_to_forward_prefetch(mods)
             if ee and self.expert_chain[i] is not None:
                 self.expert_chain[i].set_modules_to_forward_prefetch([self.expert_chain[j] for j in ee])
         if self.config.prefetch_direction is FSDPPrefetchDirection.FORWARD_BACKWARD:
             bwd = self.build_targets(n, self.config.backward_prefetch_depth, strategy, has[::-1])
-            rl, re_ = self.layer_chain[::-1], self.expert_chain[::-1]
+            rl, re_, rg = self.layer_chain[::-1], self.expert_chain[::-1], self.expert_groups[::-1]
             for i, (lt, el, ee) in enumerate(bwd):
-                mods = [rl[j] for j in lt] + [re_[j] for j in el]
+                mods = [rl[j] for j in lt] + [e for j in el for e in rg[j][::-1]]
                 if mods:
                     rl[i].set_modules_to_backward_prefetch(mods)
                 if ee and re_[i] is not None:
@@ -100,7 +106,7 @@ class FSDPPrefetchManager:
         """During activation-checkpoint recomputation of one layer the experts of later layers must not be
         gathered again; the explicit forward lists of expert units are emptied for the duration."""
         touched = []
-        for e in self.expert_chain:
+        for e in [e for g in self.expert_groups for e in g]:
             if e is not None and hasattr(e, "set_modules_to_forward_prefetch"):
                 st = e._get_fsdp_state() if hasattr(e, "_get_fsdp_state") else None
                 prev = list(getattr(st, "_states_to_forward_prefetch", [])) if st is not None else []

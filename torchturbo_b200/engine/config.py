@@ -374,7 +374,16 @@ class CPUOffloadConfig:
 @dataclass
 class FSDPConfig:
     sharding_strategy: ShardingStrategy = ShardingStrategy.FULL_SHARD
-    reshard_after_forward: bool = True
+    # True / False, or "auto": gathered parameters stay resident between forward and backward when all
+    # FSDP-managed parameters are at most `resident_fraction` of the device memory (never on CPU meshes)
+    reshard_after_forward: Any = "auto"
+    resident_fraction: float = 0.10
+    # consecutive decoder layers share one FSDP unit until it gathers this many bf16 bytes; "auto" = 64 MiB on
+    # CUDA meshes and no merging on CPU meshes; 0 = one unit per layer
+    unit_min_bytes: Any = "auto"
+    # all-gather / reduce-scatter of FSDP units: "auto" (peer-memory NVLink kernels when every rank of the group
+    # has its own GPU on one node, else NCCL), "p2p" (required), "nccl"
+    transport: str = "auto"
     cpu_offload: CPUOffloadConfig = field(default_factory=lambda: CPUOffloadConfig(enabled=False))
     prefetch_strategy: FSDPPrefetchStrategy = FSDPPrefetchStrategy.AUTO
     prefetch_direction: FSDPPrefetchDirection = FSDPPrefetchDirection.FORWARD_BACKWARD
@@ -394,7 +403,18 @@ class FSDPConfig:
         self.sharding_strategy = ShardingStrategy(self.sharding_strategy)
         self.prefetch_strategy = FSDPPrefetchStrategy(self.prefetch_strategy)
         self.prefetch_direction = FSDPPrefetchDirection(self.prefetch_direction)
-        self.reshard_after_forward = string_to_bool(self.reshard_after_forward)
+        if not (isinstance(self.reshard_after_forward, str) and self.reshard_after_forward.lower() == "auto"):
+            self.reshard_after_forward = string_to_bool(self.reshard_after_forward)
+        else:
+            self.reshard_after_forward = "auto"
+        if isinstance(self.unit_min_bytes, str) and self.unit_min_bytes.lower() == "auto":
+            import torch
+
+            self.unit_min_bytes = (64 << 20) if torch.cuda.is_available() else 0
+        self.unit_min_bytes = int(self.unit_min_bytes)
+        self.resident_fraction = float(self.resident_fraction)
+        if str(self.transport).lower() not in ("auto", "p2p", "nccl"):
+            raise ValueError("backend_config.transport must be auto, p2p or nccl")
         self.forward_prefetch_depth, self.backward_prefetch_depth = int(self.forward_prefetch_depth), int(self.backward_prefetch_depth)
         if self.forward_prefetch_depth < 1 or self.backward_prefetch_depth < 1:
             raise ValueError("prefetch depth must be >= 1")
@@ -567,7 +587,7 @@ _BUILTIN_DEFAULTS: dict[str, Any] = {
     "backend": "fsdp2",
     "mixed_precision": "fp32",
     "parallel_plan": {"sp_size": 1, "ep_size": 1},
-    "backend_config": {"reshard_after_forward": True},
+    "backend_config": {"reshard_after_forward": "auto"},
 }
 
 

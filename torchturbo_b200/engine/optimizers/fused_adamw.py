@@ -29,6 +29,9 @@ class FusedAdamW(torch.optim.Optimizer):
         defaults = dict(lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay)
         super().__init__(params, defaults)
         self._clip_coef: torch.Tensor | None = None
+        # constant folded into every gradient read by `grad_sq_sum()` and by the next `step()` (then reset to 1):
+        # the backend uses it for the 1/ep scaling of expert gradients instead of a pass of its own over them
+        self.grad_prescale: float = 1.0
         self._plans: dict[int, tuple[tuple, Any]] = {}
 
     # -- clipping ------------------------------------------------------------------------------------
@@ -56,6 +59,7 @@ class FusedAdamW(torch.optim.Optimizer):
     def step(self, closure=None):
         loss = closure() if closure is not None else None
         clip, self._clip_coef = self._clip_coef, None
+        prescale, self.grad_prescale = self.grad_prescale, 1.0
         for gi, group in enumerate(self.param_groups):
             ps = [p for p in group["params"] if self.grad_of(p) is not None]
             if not ps:
@@ -67,9 +71,9 @@ class FusedAdamW(torch.optim.Optimizer):
             b1, b2 = group["betas"]
             lp0 = _local(ps[0])
             if lp0.is_cuda and K.available():
-                self._step_cuda(gi, group, ps, states, step, clip)
+                self._step_cuda(gi, group, ps, states, step, clip, prescale)
             else:
-                self._step_torch(group, ps, states, step, clip)
+                self._step_torch(group, ps, states, step, clip, prescale)
         return loss
 
     @torch.no_grad()
@@ -85,7 +89,7 @@ class FusedAdamW(torch.optim.Optimizer):
                 return None
             states = [self._init_state(p) for p in ps]
             plan = self._plan_for(gi, ps, states)
-            s = K.grad_sqnorm_partials(plan).sum()
+            s = K.grad_sqnorm_partials(plan, self.grad_prescale).sum()
             total = s if total is None else total + s
         return total
 
@@ -115,18 +119,18 @@ class FusedAdamW(torch.optim.Optimizer):
             plan._grads = grads  # keep contiguous copies alive until the kernels have consumed them
         return plan
 
-    def _step_cuda(self, gi, group, ps, states, step, clip):
+    def _step_cuda(self, gi, group, ps, states, step, clip, prescale=1.0):
         plan = self._plan_for(gi, ps, states)
         b1, b2 = group["betas"]
         K.adamw_step(plan, lr=group["lr"], beta1=b1, beta2=b2, eps=group["eps"], weight_decay=group["weight_decay"],
-                     step=step, clip=clip)
+                     step=step, clip=clip, grad_prescale=prescale)
         plan._gkey = None
 
-    def _step_torch(self, group, ps, states, step, clip):
+    def _step_torch(self, group, ps, states, step, clip, prescale=1.0):
         b1, b2 = group["betas"]
         lr, eps, wd = group["lr"], group["eps"], group["weight_decay"]
         bc1, bc2 = 1 - b1 ** step, 1 - b2 ** step
-        coef = float(clip) if clip is not None else 1.0
+        coef = (float(clip) if clip is not None else 1.0) * prescale
         if coef != coef or coef in (float("inf"), float("-inf")):
             return
         for p, st in zip(ps, states):

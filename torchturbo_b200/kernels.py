@@ -659,3 +659,14 @@ def ulysses_move(peer_ptrs, off_buf, off_flags, local, heads, rep, rank, world, 
                                   _p(done_counter), _p(status), C.c_int(int(gather)), C.c_int(grid), _stream()),
            "ttb_ulysses_move")
     return local
+
+
+def peer_collective(peer_ptrs, off_data, off_ready, off_consumed, units, rank, world, epoch, budget_ms, done_counter,
+                    status, *, kind: int, out: torch.Tensor | None = None, scale: float = 1.0, grid: int = 64):
+    """Pull all-gather (kind 0) or pull reduce-scatter of fp32 (kind 1) / bf16 (kind 2) pieces over a slot of the
+    symmetric buffer; `units` is the piece length in 16-byte units."""
+    _check(lib().ttb_peer_collective(peer_ptrs, C.c_longlong(off_data), C.c_longlong(off_ready),
+                                     C.c_longlong(off_consumed), C.c_longlong(units), C.c_int(rank), C.c_int(world),
+                                     C.c_int(epoch), C.c_longlong(budget_ms), C.c_float(scale), _p(out),
+                                     _p(done_counter), _p(status), C.c_int(kind), C.c_int(grid), _stream()),
+           "ttb_peer_collective")
