@@ -12,7 +12,10 @@ Backward mirrors this: d(out) rows are scattered to the owners, d(x) rows and d(
 
 Buffers are shared by all MoE layers of a model.  Reuse is safe because every rank waits on every other rank once
 per layer in each direction: a rank that starts writing layer L+1 data has observed the owners' layer-L
-"output ready" flags, which they raise after they stopped reading their receive buffers.
+"output ready" flags, which they raise after they stopped reading their receive buffers.  The same ordering lets
+the expert MLP write its output (forward) and its input gradient (backward) directly into the peer-visible output
+buffer, and lets its backward read d(y) in place from the receive buffer: only the forward input rows, which
+backward needs again, are copied out of the workspace.
 
 Receive capacity is `capacity_factor` x the balanced share (rows are never dropped silently: an overflow sets the
 workspace status, which `check()` turns into an exception).
@@ -121,7 +124,8 @@ class _Dispatch(torch.autograd.Function):
     def backward(ctx, dxp, drp, *_):
         ws, (T, k) = ctx.ws, ctx.dims
         expert, dest_row = ctx.saved_tensors
-        ws.y_rows.copy_(dxp)
+        if dxp.data_ptr() != ws.y_rows.data_ptr():   # the expert MLP normally writes d(x) straight into the buffer
+            ws.y_rows.copy_(dxp)
         if drp is not None:
             ws.y_vals.copy_(drp)
         else:
@@ -135,7 +139,8 @@ class _Dispatch(torch.autograd.Function):
 class _Combine(torch.autograd.Function):
     @staticmethod
     def forward(ctx, y, expert, dest_row, seg_start, recv_counts, ws: EPWorkspace, T, k, residual):
-        ws.y_rows.copy_(y)
+        if y.data_ptr() != ws.y_rows.data_ptr():     # the expert MLP normally writes y straight into the buffer
+            ws.y_rows.copy_(y)
         ws.publish_and_wait_ready()
         out = ws.gather_rows(expert, dest_row, T, k, residual=residual)
         ctx.ws, ctx.dims = ws, (T, k, residual is not None)
@@ -149,7 +154,9 @@ class _Combine(torch.autograd.Function):
         dout = dout.contiguous()
         K.perm_zero_pad(ws.recv_rows, recv_counts, seg_start, None)
         ws.scatter_rows(dout, expert, dest_row, None, k)
-        dy = ws.recv_rows.clone()
+        # no copy: the expert backward that consumes d(y) runs before this rank raises the next "ready" flag, and no
+        # peer writes these rows again before it has seen that flag (it first gathers its d(x) of this layer)
+        dy = ws.recv_rows.detach()
         return dy, None, None, None, None, None, None, None, (dout if has_res else None)
 
 
@@ -187,7 +194,8 @@ class P2PTokenDispatcher:
         xp, rp, seg_start, recv_counts, tile_group, dest_row, expert = _Dispatch.apply(
             x.contiguous(), prob.float().contiguous(), idx32, counts, ws)
         perm = MoEPermutation(tokens=xp, probs=rp, row_indices=dest_row.view(T, k), expert_indices=idx.long(),
-                              counts=recv_counts, seg_start=seg_start, tile_group=tile_group)
+                              counts=recv_counts, seg_start=seg_start, tile_group=tile_group,
+                              out_buffer=ws.y_rows, grad_buffer=ws.y_rows)
         return perm, recv_counts, ("p2p", ws, expert, dest_row, seg_start, recv_counts, T, k)
 
     def combine(self, y, state, residual=None):

@@ -65,7 +65,7 @@ class PeerCollectiveArena:
         self.done_ag = torch.zeros(1, dtype=torch.int32, device=dev)
         self.done_rs = torch.zeros(1, dtype=torch.int32, device=dev)
         self.budget_ms = int(os.environ.get("TORCHTURBO_P2P_WAIT_MS", "5000"))
-        self.grid = int(os.environ.get("TORCHTURBO_FSDP_P2P_GRID", "48"))
+        self.grid = int(os.environ.get("TORCHTURBO_FSDP_P2P_GRID", "96"))
         self.by_ptr: dict[int, _Slot] = {s.bytes.data_ptr(): s for s in self.ag + self.rs}
         self.calls = {"all_gather": 0, "reduce_scatter": 0, "nccl": 0}
 

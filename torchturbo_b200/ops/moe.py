@@ -24,6 +24,10 @@ class MoEPermutation:
     counts: torch.Tensor | None = None      # int32 [E] tokens per expert
     seg_start: torch.Tensor | None = None   # int32 [E + 1] padded segment starts
     tile_group: torch.Tensor | None = None  # int32 [capacity / 128] expert of each 128-row tile (-1: unused)
+    # optional preallocated [capacity, H] buffers the expert MLP writes its output (forward) and its input gradient
+    # (backward) into, e.g. the peer-visible buffer of an expert-parallel dispatcher (saves a copy each way)
+    out_buffer: torch.Tensor | None = None
+    grad_buffer: torch.Tensor | None = None
 
     @property
     def padded(self) -> bool:

@@ -352,14 +352,18 @@ class B200MoEUnpermutation(_B200Op):
 
 class MoEExpertsFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, xp, row_prob, w1, w2, tile_group, seg_start):
+    def forward(ctx, xp, row_prob, w1, w2, tile_group, seg_start, buffers=(None, None)):
+        # `buffers` = (output buffer, input-gradient buffer) or Nones.  They travel inside a tuple so that autograd
+        # does not treat these long-lived, reused workspaces as inputs; the results are returned as fresh aliases.
+        out_buffer, grad_buffer = buffers
         cap = xp.shape[0]
         F2 = w1.shape[-1]
         pre = torch.empty(cap, F2, dtype=BF16, device=xp.device)
         act = K.gemm(xp, w1, b_mn=True, tile_group=tile_group, swiglu=True, row_scale=row_prob, preact=pre)
-        y = K.gemm(act, w2, b_mn=True, tile_group=tile_group)
+        y = K.gemm(act, w2, b_mn=True, tile_group=tile_group, out=out_buffer)
         ctx.save_for_backward(xp, row_prob, w1, w2, tile_group, seg_start, pre)
-        return y
+        ctx.grad_buffer = grad_buffer
+        return y.detach() if out_buffer is not None else y
 
     @staticmethod
     def backward(ctx, dy):
@@ -368,14 +372,17 @@ class MoEExpertsFn(torch.autograd.Function):
         # d(act) = dY @ W2[e]^T  (W2[e] is [F, H] = [N, K] K-major)
         dact = K.gemm(dy, w2, tile_group=tile_group)
         dpre, dprob = K.swiglu_bwd(dact, pre, row_prob, want_dscale=row_prob is not None)
-        dxp = K.gemm(dpre, w1, tile_group=tile_group) if ctx.needs_input_grad[0] else None
         dw1 = dw2 = None
-        if ctx.needs_input_grad[2]:
-            dw1 = _weight_grad(w1, xp, dpre, group_rows=seg_start)
         if ctx.needs_input_grad[3]:
             act = K.swiglu_fwd(pre, row_prob)
             dw2 = _weight_grad(w2, act, dy, group_rows=seg_start)
-        return dxp, dprob, dw1, dw2, None, None
+        if ctx.needs_input_grad[2]:
+            dw1 = _weight_grad(w1, xp, dpre, group_rows=seg_start)
+        # last, so that `dy` (possibly a receive buffer peers refill once they see this output) is no longer read
+        dxp = K.gemm(dpre, w1, tile_group=tile_group, out=ctx.grad_buffer) if ctx.needs_input_grad[0] else None
+        if dxp is not None and ctx.grad_buffer is not None:
+            dxp = dxp.detach()
+        return dxp, dprob, dw1, dw2, None, None, None
 
 
 @_custom("moe_experts", "tcgen05_grouped_mlp")
@@ -386,7 +393,8 @@ class B200MoEExperts(_B200Op):
     def __call__(self, perm: MoEPermutation, w1, w2, tokens_per_expert=None):
         if not _ok(perm.tokens, w1, w2) or not perm.padded:
             return N.TorchMoEExperts()(perm, w1, w2, tokens_per_expert)
-        return MoEExpertsFn.apply(perm.tokens, perm.probs, w1, w2, perm.tile_group, perm.seg_start)
+        return MoEExpertsFn.apply(perm.tokens, perm.probs, w1, w2, perm.tile_group, perm.seg_start,
+                                  (perm.out_buffer, perm.grad_buffer))
 
 
 @_custom("grouped_matmul", "tcgen05_grouped_matmul")
