@@ -443,3 +443,108 @@ def test_newton_schulz_on_tcgen05_gemm(K):
     _close(got, X, rtol=5e-2, atol=5e-2)
     s = torch.linalg.svdvals(got[0].float())
     assert float(s.max()) < 1.3 and float(s.min()) > 0.3          # singular values pulled towards one
+
+
+def _single_rank_group(tmp_path):
+    import torch.distributed as dist
+
+    if dist.is_initialized():
+        return False
+    dist.init_process_group("nccl", init_method=f"file://{tmp_path}/rdzv", rank=0, world_size=1,
+                            device_id=torch.device("cuda", torch.cuda.current_device()))
+    return True
+
+
+def test_bounded_peer_wait_gives_up_and_reports(K, tmp_path):
+    """A wait on a flag that nothing sets ends after its time budget, records {site, peer} in the status word and
+    leaves the context usable (the failure path of every peer-memory kernel; nothing here traps or spins forever)."""
+    import time
+
+    import torch.distributed as dist
+
+    from torchturbo_b200.comm.symm import SymmetricBuffer
+
+    created = _single_rank_group(tmp_path)
+    try:
+        buf = SymmetricBuffer(4096, dist.group.WORLD)
+        ch = buf.channel()
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        K.comm_status(reset=True)
+        t0 = time.time()
+        K.flag_wait(buf.peer_ptrs, ch.offset, 0, 1, ch.next(), 20, status)      # 20 ms budget, flag stays 0
+        torch.cuda.synchronize()
+        assert time.time() - t0 < 5.0
+        code = int(status.item())
+        assert code & 0x10000 and (code >> 8) & 0xFF == 2 and code & 0xFF == 0, hex(code)   # site 2 (flag_wait), peer 0
+        first, n = K.comm_status(reset=True)
+        assert n >= 1 and first != 0
+        # once a workspace has failed, later waits return at once instead of stalling for another budget
+        t0 = time.time()
+        K.flag_wait(buf.peer_ptrs, ch.offset, 0, 1, ch.next(), 2000, status)
+        torch.cuda.synchronize()
+        assert time.time() - t0 < 1.0
+        K.comm_status(reset=True)
+        # a satisfied wait is silent, and the GPU still computes
+        status.zero_()
+        e = ch.next()
+        K.flag_signal(buf.peer_ptrs, ch.offset, 0, 1, e)
+        K.flag_wait(buf.peer_ptrs, ch.offset, 0, 1, e, 20, status)
+        a, b = _rand(128, 64), _rand(128, 64)
+        _close(K.gemm(a, b), a.float() @ b.float().t())
+        assert int(status.item()) == 0 and K.comm_status() == (0, 0)
+    finally:
+        if created:
+            dist.destroy_process_group()
+
+
+def test_ep_exchange_writes_every_row_once_and_is_deterministic(K, tmp_path):
+    """Expert-parallel dispatch / combine kernels on a one-rank group with poisoned buffers: every routed row lands
+    exactly once in its expert's segment, padding rows are zero, nothing else is touched, and two runs agree bitwise."""
+    import torch.distributed as dist
+
+    from torchturbo_b200.comm import ep_p2p
+
+    created = _single_rank_group(tmp_path)
+    try:
+        T, H, E, k = 300, 64, 8, 2
+        torch.manual_seed(3)
+        x = _rand(T, H)
+        idx = torch.stack([torch.randperm(E, device="cuda")[:k] for _ in range(T)]).to(torch.int32)
+        prob = torch.rand(T, k, device="cuda")
+        ws = ep_p2p.EPWorkspace(dist.group.WORLD, H, E, T, k, 2.0)
+        counts = torch.zeros(E, dtype=torch.int32, device="cuda")
+        counts.scatter_add_(0, idx.reshape(-1).long(), torch.ones(T * k, dtype=torch.int32, device="cuda"))
+        outs = []
+        for _ in range(2):
+            ws.recv_rows.fill_(float("nan"))
+            ws.recv_vals.fill_(float("nan"))
+            xp, rp, seg_start, recv_counts, tile_group, dest_row, expert = ep_p2p._Dispatch.apply(x, prob, idx, counts, ws)
+            torch.cuda.synchronize()
+            ws.check()
+            assert torch.equal(recv_counts, counts)
+            seg = seg_start.tolist()
+            dr = dest_row.view(T, k)
+            assert dr.unique().numel() == T * k                      # no two (token, slot) pairs share a row
+            for e in range(E):
+                n = int(counts[e])
+                rows = xp[seg[e]:seg[e] + n]
+                toks = (idx == e).nonzero()[:, 0]
+                inside = dr[idx == e]
+                assert int(inside.min()) >= seg[e] and int(inside.max()) < seg[e] + n if n else True
+                assert not torch.isnan(rows).any()
+                assert torch.equal(xp[dr[idx == e].long()], x[toks])          # each row is its token, bit for bit
+                pad = xp[seg[e] + n:seg[e + 1]]
+                assert float(pad.abs().max()) == 0.0 if pad.numel() else True # padding zeroed, not poison
+            used = torch.zeros(xp.shape[0], dtype=torch.bool, device="cuda")
+            for e in range(E):
+                used[seg[e]:seg[e + 1]] = True
+            assert torch.isnan(xp[~used]).all()                      # rows outside every segment were never written
+            y = ep_p2p._Combine.apply(xp.clone(), expert, dest_row, seg_start, recv_counts, ws, T, k, None)
+            torch.cuda.synchronize()
+            _close(y, x.float() * k, rtol=1e-2, atol=1e-2)           # identity experts: k copies of the token
+            outs.append((xp.clone(), y.clone(), dest_row.clone()))
+        assert torch.equal(outs[0][1], outs[1][1])                   # run-twice determinism of the combined output
+        assert torch.equal(outs[0][0].nan_to_num(), outs[1][0].nan_to_num()) and torch.equal(outs[0][2], outs[1][2])
+    finally:
+        if created:
+            dist.destroy_process_group()

@@ -365,7 +365,16 @@ class TorchTurboEngine(RLMixin):
     def report_metrics(self, logs: dict, gather: Callable | None = None) -> dict:
         if self._mfu is not None:
             logs.update(self._mfu.pop())
+        self.check_health()
         return self.metrics.report(logs, gather)
+
+    def check_health(self) -> None:
+        """Turn a timeout / overflow recorded by any rank's peer-memory kernels into an exception on every rank.
+        Runs at logging boundaries (one small device read per workspace), never inside a step."""
+        if self.backend.world_size > 1 and self.runtime.turbo_device.value == "cuda":
+            from .health import check_peer_status
+
+            check_peer_status(what="peer-memory exchange since the last report")
 
     def _get_mfu_estimator(self, model: nn.Module | None = None):
         if self._mfu is None and self.config.mfu.enabled and model is not None:
