@@ -1,68 +1,57 @@
 """ms-swift 4.x adapter: SFT, PT and DPO through swift's pipelines.
 
-Activation swaps swift's `SwiftSft` / `SwiftPretrain` / `SwiftRLHF` pipeline classes for subclasses that build the engine
-before the model is loaded, route model loading through `engine.prepare_model` (the DPO reference model through
-`engine.build_model`), force swift's own gradient checkpointing / sequence parallel / FSDP / DeepSpeed switches off
-(the engine owns those), and mix `TurboTrainerMixin` into the trainer.  Import-guarded: swift is not part of this
-environment (adapters/msswift/* of the reference)."""
+Activation swaps `SwiftSft` / `SwiftPretrain` / `SwiftRLHF` in their modules for engine-backed subclasses
+(`pipeline.make_pipeline`).  Such a pipeline builds the engine before the model is loaded, parks it in `session`,
+registers the engine's model types (`turbo_<name>`, loader = engine `get_model` in front of the model's native swift
+loader) and trainers, forces swift's own gradient checkpointing / sequence parallel / FSDP / DeepSpeed switches off,
+bridges the template collator's output to packed rows and mixes the engine trainer in.  Import-guarded: swift is not
+part of this environment (adapters/msswift/* of the reference)."""
 from __future__ import annotations
 
-import importlib.util
+import importlib
 from typing import Any
 
-from ...engine.args import get_torchturbo_args
-from ...engine.config import build_from_args
 from ...registry import BaseAdapter, BasePatch, register_adapter
+from . import session
+from .compat import SUPPORTED, get_swift_version, is_swift_installed, is_swift_supported
+from .data_check import check_row, validate_raw_dataset
 from .inputs_bridging import (SwiftInputCollator, bake_loss_scale_into_labels, bridge_packed_inputs,  # noqa: F401
                               bridge_swift_inputs, bridge_unpacked_inputs)
-
-_FORCED_OFF = {"gradient_checkpointing": False, "sequence_parallel_size": 1, "deepspeed": None, "fsdp": ""}
-
-
-def build_config_from_swift_args(args: Any, stage: str, tt_args=None):
-    defaults: dict[str, Any] = {"mixed_precision": "bf16" if getattr(args, "bf16", True) else "fp32",
-                                "activation_checkpointing": {"enabled": bool(getattr(args, "gradient_checkpointing", True))}}
-    if stage == "dpo" and getattr(args, "router_aux_loss_coef", None):
-        defaults["moe"] = {"aux_loss_coeff": float(args.router_aux_loss_coef)}
-    for k, v in _FORCED_OFF.items():
-        if hasattr(args, k):
-            setattr(args, k, v)
-    return build_from_args(tt_args or get_torchturbo_args(), defaults=defaults)
+from .plugins import DatasetPluginBridge, SwiftPluginHost
+from .stages import SwiftStageSpec, get_stage, iter_stages, register_stage
+from .utils import (FORCED_OFF, build_config_from_swift_args, build_lora_config_from_swift_args, raise_if_unsupported,
+                    take_over_swift_switches)
 
 
 class PipelinePatch(BasePatch):
+    """Swap every registered stage's pipeline class (and keep the module's `*_main` entry points working: they
+    instantiate the class through the module global)."""
+
     name = "pipelines"
-    version_spec = ">=4.0,<5"
+    version_spec = SUPPORTED
+
+    def __init__(self) -> None:
+        super().__init__()
+        self._saved: list[tuple[Any, str, Any]] = []
 
     def _patch(self, engine=None) -> None:
-        import swift.pipelines.train as train_mod
+        from .pipeline import make_pipeline
 
-        self._saved = {}
-        adapter = self.adapter
-        for cls_name, stage in (("SwiftSft", "sft"), ("SwiftPretrain", "pt"), ("SwiftRLHF", "dpo")):
-            orig = getattr(train_mod, cls_name, None)
-            if orig is None:
+        for spec in iter_stages():
+            try:
+                mod = importlib.import_module(spec.pipeline_module)
+            except ImportError:
                 continue
-
-            def make(orig=orig, stage=stage):
-                class TurboPipeline(orig):  # type: ignore[misc,valid-type]
-                    def __init__(self, args=None):
-                        from ...engine import TorchTurboEngine
-
-                        parsed = self._parse_args(args) if hasattr(self, "_parse_args") else args
-                        adapter.engine = TorchTurboEngine(build_config_from_swift_args(parsed, stage))
-                        super().__init__(args)
-
-                return TurboPipeline
-
-            self._saved[cls_name] = orig
-            setattr(train_mod, cls_name, make())
+            if not hasattr(mod, spec.pipeline_attr):
+                continue
+            self._saved.append((mod, spec.pipeline_attr, getattr(mod, spec.pipeline_attr)))
+            setattr(mod, spec.pipeline_attr, make_pipeline(spec.name))
 
     def _revert(self) -> None:
-        import swift.pipelines.train as train_mod
-
-        for k, v in self._saved.items():
-            setattr(train_mod, k, v)
+        for mod, attr, orig in reversed(self._saved):
+            setattr(mod, attr, orig)
+        self._saved.clear()
+        session.clear()
 
 
 @register_adapter("msswift")
@@ -71,16 +60,27 @@ class MSSwiftAdapter(BaseAdapter):
 
     def __init__(self) -> None:
         super().__init__()
-        self.engine = None
-        p = PipelinePatch()
-        p.adapter = self
-        self.add_patch(p)
+        self.add_patch(PipelinePatch())
+
+    @property
+    def engine(self):
+        return session.get_engine_or_none()
+
+    def framework_version(self) -> str | None:
+        return get_swift_version() or super().framework_version()
 
     def detect(self) -> bool:
-        return importlib.util.find_spec("swift") is not None
+        return is_swift_installed()
 
     def activate(self) -> None:
         if not self.detect():
             raise RuntimeError("ms-swift is not installed in this environment")
+        if not is_swift_supported():
+            raise RuntimeError(f"ms-swift {get_swift_version()} is not supported (need {SUPPORTED})")
         self.apply_patches()
         super().activate()
+
+    def main(self, stage: str, args: Any = None):
+        """Run a stage through swift's own entry function (`sft_main`, `pretrain_main`, `rlhf_main`)."""
+        spec = get_stage(stage)
+        return getattr(importlib.import_module(spec.pipeline_module), spec.main_attr)(args)

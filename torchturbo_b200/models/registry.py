@@ -51,3 +51,9 @@ def get_model(model_type: str) -> type:
 def list_models() -> list[str]:
     _register_builtins()
     return sorted(_MODELS)
+
+
+def get_all_models() -> dict[str, type]:
+    """model_type -> class for every registered family."""
+    _register_builtins()
+    return dict(_MODELS)
