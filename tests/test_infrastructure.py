@@ -157,6 +157,35 @@ def test_qk_clip_scales_only_hot_heads():
     assert a.qk_clip_state.max_logits is None                               # consumed
 
 
+def test_qk_clip_mla_splits_nope_and_rope_rows():
+    from torchturbo_b200.engine.optimizers.qk_clip import MLAQKClipSpec, QKClipController
+
+    class MLA(nn.Module):
+        n_heads, d_nope, d_rope, d_v = 2, 2, 1, 3
+
+        def __init__(self):
+            super().__init__()
+            self.q_b_proj = nn.Linear(4, 2 * (2 + 1), bias=False)
+            self.kv_b_proj = nn.Linear(4, 2 * (2 + 3), bias=False)
+            nn.init.ones_(self.q_b_proj.weight); nn.init.ones_(self.kv_b_proj.weight)
+            self.qk_clip_state = None
+
+    m = nn.ModuleDict({"attn": MLA()})
+    ctl = QKClipController(m, threshold=10.0, alpha=0.25)
+    spec = ctl.plan.specs[0]
+    assert isinstance(spec, MLAQKClipSpec) and spec.projection_rows == {"attn.q_b_proj.weight": 6, "attn.kv_b_proj.weight": 10}
+    m["attn"].qk_clip_state.update(torch.tensor([160.0, 3.0]))              # head 0 is hot: gamma = 1/16
+    ctl.apply()
+    q, kv = m["attn"].q_b_proj.weight, m["attn"].kv_b_proj.weight
+    g = 1.0 / 16
+    assert torch.allclose(q[0:2], torch.full((2, 4), g ** 0.25)) and torch.allclose(q[2:3], torch.full((1, 4), g))   # NoPE, RoPE
+    assert torch.allclose(q[3:], torch.ones(3, 4))                                                                   # cool head
+    assert torch.allclose(kv[0:2], torch.full((2, 4), g ** 0.75)) and torch.allclose(kv[2:5], torch.ones(3, 4))      # K NoPE, V
+    assert torch.allclose(kv[5:], torch.ones(5, 4))
+    with pytest.raises(ValueError, match="distinct"):
+        MLAQKClipSpec("a", "w", "w", 1, 1, 1, 1)
+
+
 def test_optimizer_memory_controller_guards():
     from torchturbo_b200.engine.optimizers.memory import OptimizerMemoryController, OptimizerSuspendedError
 
