@@ -359,6 +359,33 @@ def test_attention_bwd(K, causal):
     assert float(dk[650:].abs().max()) == 0.0 and float(dq[650:].abs().max()) == 0.0
 
 
+def test_narrow_heads_run_on_the_tcgen05_kernel_with_zero_padding(K):
+    """ViT-style attention (head width 72, full attention, no GQA) through the operator: zero-padded to 128 columns on
+    the library's own kernel, forward and backward against the fp32 formulation."""
+    from torchturbo_b200.ops.providers import b200_attention as BA
+    from torchturbo_b200.ops.providers.native import attention_ref
+
+    torch.manual_seed(2)
+    T, H, D = 500, 4, 72
+    cu = torch.tensor([0, 196, 452, 500], dtype=torch.int32)
+    q, k, v = (_rand(T, H, D).requires_grad_(True) for _ in range(3))
+    before = K.launch_count()
+    out = BA.B200Attention()(q, k, v, cu, 256, causal=False, scale=D ** -0.5)
+    assert K.launch_count() > before and out.shape == (T, H, D)
+    g = _rand(T, H, D)
+    out.backward(g)
+    torch.cuda.synchronize()
+    assert K.attn_status() == (0, 0)
+    qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    ref = attention_ref(qf, kf, vf, cu, causal=False, scale=D ** -0.5)
+    ref.backward(g.float())
+    _close(out, ref, atol=2e-2)
+    _close(q.grad, qf.grad, atol=3e-2); _close(k.grad, kf.grad, atol=3e-2); _close(v.grad, vf.grad, atol=3e-2)
+    o2, ml = BA.B200AttentionWithMaxLogits()(q.detach(), k.detach(), v.detach(), cu, 256, causal=False, scale=D ** -0.5)
+    _, ref_ml = attention_ref(qf, kf, vf, cu, causal=False, scale=D ** -0.5, want_max_logits=True)
+    _close(ml, ref_ml, rtol=1e-2, atol=1e-2)
+
+
 def test_adamw_swap_pipelined_matches_torch(K):
     """Host-resident AdamW state streamed through a two-slot device workspace (chunks smaller than the parameters)."""
     from torchturbo_b200.engine.optimizers import AdamWSwap

@@ -73,15 +73,36 @@ def _usable(q, k, v):
         and v.stride(1) == 128
 
 
+def _paddable(q, k, v):
+    """Head widths below 128 (ViT: 72, 80) run on the 128-wide kernel with zero columns: padded query / key columns add
+    nothing to the logits and padded value columns only produce output columns that are sliced away."""
+    return _ok(q, k, v) and q.dim() == 3 and q.shape[1] % k.shape[1] == 0 and q.shape[-1] == k.shape[-1] and \
+        q.shape[-1] <= 128 and v.shape[-1] <= 128 and (q.shape[-1] < 128 or v.shape[-1] < 128)
+
+
+def _padded_call(q, k, v, cu, max_seqlen, causal, scale, want_ml):
+    import torch.nn.functional as F
+
+    dqk, dv = q.shape[-1], v.shape[-1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(dqk)
+    qp, kp, vp = F.pad(q, (0, 128 - dqk)), F.pad(k, (0, 128 - dqk)), F.pad(v, (0, 128 - dv))
+    res = FlashAttnFn.apply(qp, kp, vp, cu.cpu() if cu.is_cuda else cu, max_seqlen, causal, float(scale), want_ml)
+    if want_ml:
+        return res[0][..., :dv], res[1]
+    return res[..., :dv]
+
+
 @register_op(op_name="attention", impl_name="tcgen05_varlen_attention", kind=OpImplKind.CUSTOM, priority=100,
              devices=(TurboDevice.CUDA,))
 class B200Attention(_B200Op):
     def __call__(self, q, k, v, cu_seqlens, max_seqlen=None, *, causal=True, scale=None):
+        cu = cu_seqlens if isinstance(cu_seqlens, torch.Tensor) else torch.tensor(cu_seqlens, dtype=torch.int32)
         if not _usable(q, k, v):
-            # other head widths (ViT 72, MLA 192/128): the library kernel, which pads to what it supports
+            if _paddable(q, k, v):
+                return _padded_call(q, k, v, cu, max_seqlen, causal, scale, False)
+            # wider heads (MLA 192 / 128): the library kernel
             return _LIB_FALLBACK(q, k, v, cu_seqlens, max_seqlen, causal=causal, scale=scale)
         scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
-        cu = cu_seqlens if isinstance(cu_seqlens, torch.Tensor) else torch.tensor(cu_seqlens, dtype=torch.int32)
         return FlashAttnFn.apply(q.contiguous(), k.contiguous(), v, cu.cpu() if cu.is_cuda else cu, max_seqlen, causal,
                                  float(scale), False)
 
@@ -90,9 +111,11 @@ class B200Attention(_B200Op):
              kind=OpImplKind.CUSTOM, priority=100, devices=(TurboDevice.CUDA,))
 class B200AttentionWithMaxLogits(_B200Op):
     def __call__(self, q, k, v, cu_seqlens, max_seqlen=None, *, causal=True, scale=None):
+        cu = cu_seqlens if isinstance(cu_seqlens, torch.Tensor) else torch.tensor(cu_seqlens, dtype=torch.int32)
         if not _usable(q, k, v):
+            if _paddable(q, k, v):
+                return _padded_call(q, k, v, cu, max_seqlen, causal, scale, True)
             return N.attention_ref(q, k, v, cu_seqlens, causal, scale, want_max_logits=True)
         scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
-        cu = cu_seqlens if isinstance(cu_seqlens, torch.Tensor) else torch.tensor(cu_seqlens, dtype=torch.int32)
         return FlashAttnFn.apply(q.contiguous(), k.contiguous(), v, cu.cpu() if cu.is_cuda else cu, max_seqlen, causal,
                                  float(scale), True)
