@@ -106,8 +106,10 @@ def bench_grouped():
         dy = torch.randn(pm["capacity_rows"], 2 * F, device="cuda").bfloat16()
         t3, _ = time_fn(lambda: K.gemm(xp, dy, a_mn=True, b_mn=True, group_rows=pm["seg_start"], out_dtype=torch.float32))
         t4, _ = time_fn(lambda: K.gemm(dy, w1, b_mn=False, tile_group=pm["tile_group"]))
+        t5, _ = time_fn(lambda: K.gemm(xp, dy, a_mn=True, b_mn=True, group_rows=pm["seg_start"]))
         for name, t, fl in [("fc1_swiglu", t1, 2.0 * R * H * 2 * F), ("fc2", t2, 2.0 * R * F * H),
-                            ("dW1", t3, 2.0 * R * H * 2 * F), ("dX1", t4, 2.0 * R * H * 2 * F)]:
+                            ("dW1", t3, 2.0 * R * H * 2 * F), ("dX1", t4, 2.0 * R * H * 2 * F),
+                            ("dW1_bf16_out", t5, 2.0 * R * H * 2 * F)]:
             rows.append(dict(op=f"grouped_{name}", E=E, rows=R, H=H, F=F, ms=t, tflops=fl / t / 1e9,
                              frac_of_peak=fl / t / 1e9 / pk["tflops"], peak_src=pk["src"]))
             print(json.dumps(rows[-1]), flush=True)
@@ -139,7 +141,7 @@ def bench_elementwise():
 def profile_case(name: str) -> None:
     """One small, self-ending case per kernel for a profiler capture: inputs larger than L2 (126 MB) but well under
     a GB on the device, one warm-up launch and two more.  `python -m torchturbo_b200.benchmarks.kernel_bench
-    profile:<gemm|grouped|attn_fwd|attn_bwd|adamw|rmsnorm>`."""
+    profile:<gemm|grouped|grouped_dw|attn_fwd|attn_bwd|adamw|rmsnorm>`."""
     dev = "cuda"
     g = torch.Generator(device=dev).manual_seed(0)
 
@@ -156,6 +158,13 @@ def profile_case(name: str) -> None:
         x = rnd(pm["capacity_rows"], H)
         w1 = rnd(E, H, 2 * F_)                                         # engine storage: [E, H, gate|up]
         fn = lambda: K.gemm(x, w1, b_mn=True, tile_group=pm["tile_group"], swiglu=True)   # noqa: E731
+    elif name == "grouped_dw":
+        # expert weight gradient at 1-GPU shapes: 128 experts x ~256 routed rows, dW[e] = x_e^T @ dy_e (bf16 out)
+        E, H, F2, T, k = 128, 2048, 1536, 4096, 8
+        idx = torch.stack([torch.randperm(E, device=dev)[:k] for _ in range(T)]).to(torch.int32)
+        pm = K.perm_index(idx, E)
+        x, dy = rnd(pm["capacity_rows"], H), rnd(pm["capacity_rows"], F2)
+        fn = lambda: K.gemm(x, dy, a_mn=True, b_mn=True, group_rows=pm["seg_start"])     # noqa: E731
     elif name in ("attn_fwd", "attn_bwd"):
         from ..ops.providers.b200_attention import FlashAttnFn
 

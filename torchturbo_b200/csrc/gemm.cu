@@ -49,11 +49,22 @@ struct SmemLayout {
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
-  static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int EPI_STAGE_BYTES = 32 * 32 * 4;   // one 32-row x 32-column fp32 chunk per epilogue warp
+  static constexpr int EPI_BYTES = 8 * EPI_STAGE_BYTES;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 constexpr int EPI_WARPS = 8;                       // two warps per TMEM lane quarter, each takes half of the columns
 constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
+static_assert(EPI_WARPS == 8, "the staging area is sized for eight epilogue warps");
+
+// Epilogue staging.  tcgen05.ld hands every lane 32 consecutive columns of ITS row, so direct stores touch 32 rows per
+// instruction with 16 bytes each.  The chunk is instead parked in shared memory (fp32, 128 bytes per row, 16-byte
+// pieces XOR-swizzled by the row so that neither side has more than the unavoidable 4-way bank split) and written
+// out row-major: one instruction stores whole 64-byte (bf16) or 128-byte (fp32) row segments of 8 or 4 rows.
+__device__ __forceinline__ uint32_t epi_piece_addr(uint32_t base, int row, int piece) {
+  return base + row * 128 + ((piece ^ (row & 7)) << 4);
+}
 
 template <int BN, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -62,7 +73,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   constexpr int STAGES = L::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * L::STAGE_BYTES);
+  uint8_t* epi_stage = smem + STAGES * L::STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * L::STAGE_BYTES + L::EPI_BYTES);
   uint64_t* full = bars;
   uint64_t* empty = bars + STAGES;
   uint64_t* tfull = bars + 2 * STAGES;
@@ -252,8 +264,65 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = 0u;
           }
-          if (!row_ok) continue;
           const bool full_chunk = (col0 + 32 <= p.N);
+          if (full_chunk) {
+            // warp-uniform branch: every lane takes part in the transposition, rows past M are skipped on the way out
+            const uint32_t st = smem_u32(epi_stage + (warp - 2) * L::EPI_STAGE_BYTES);
+            __syncwarp();  // the previous chunk's readers are done with the staging area
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              st_shared_v4(epi_piece_addr(st, lane, i), v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+            __syncwarp();
+            const int row_base = mt * BM + lane_group * 32;
+            const long long gbase = static_cast<long long>(g) * p.c_group_stride;
+            if (p.c_fp32) {
+              const int q = lane & 7;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const int r = (lane >> 3) + 4 * j;
+                if (row_base + r >= p.M) continue;
+                uint32_t w0, w1, w2, w3;
+                ld_shared_v4(epi_piece_addr(st, r, q), w0, w1, w2, w3);
+                float4 o = make_float4(__uint_as_float(w0), __uint_as_float(w1), __uint_as_float(w2), __uint_as_float(w3));
+                float* dst = reinterpret_cast<float*>(cbase) + gbase + static_cast<long long>(row_base + r) * p.ldc + col0 + 4 * q;
+                if (p.accumulate) {
+                  const float4 old = *reinterpret_cast<const float4*>(dst);
+                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                *reinterpret_cast<float4*>(dst) = o;
+              }
+            } else {
+              const int q = lane & 3;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int r = (lane >> 2) + 8 * j;
+                if (row_base + r >= p.M) continue;
+                uint32_t w[8];
+                ld_shared_v4(epi_piece_addr(st, r, 2 * q), w[0], w[1], w[2], w[3]);
+                ld_shared_v4(epi_piece_addr(st, r, 2 * q + 1), w[4], w[5], w[6], w[7]);
+                float f[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(w[e]);
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(cbase) + gbase + static_cast<long long>(row_base + r) * p.ldc + col0 + 8 * q;
+                if (p.residual) {
+                  const uint4 rr = *reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(row_base + r) * p.ldr + col0 + 8 * q);
+                  const float2 a = unpack_bf16(rr.x), b = unpack_bf16(rr.y), c2 = unpack_bf16(rr.z), d = unpack_bf16(rr.w);
+                  f[0] += a.x; f[1] += a.y; f[2] += b.x; f[3] += b.y; f[4] += c2.x; f[5] += c2.y; f[6] += d.x; f[7] += d.y;
+                }
+                if (p.accumulate) {
+                  const uint4 rr = *reinterpret_cast<const uint4*>(dst);
+                  const float2 a = unpack_bf16(rr.x), b = unpack_bf16(rr.y), c2 = unpack_bf16(rr.z), d = unpack_bf16(rr.w);
+                  f[0] += a.x; f[1] += a.y; f[2] += b.x; f[3] += b.y; f[4] += c2.x; f[5] += c2.y; f[6] += d.x; f[7] += d.y;
+                }
+                uint4 o;
+                o.x = pack_bf16(f[0], f[1]); o.y = pack_bf16(f[2], f[3]);
+                o.z = pack_bf16(f[4], f[5]); o.w = pack_bf16(f[6], f[7]);
+                *reinterpret_cast<uint4*>(dst) = o;
+              }
+            }
+            continue;
+          }
+          if (!row_ok) continue;
           if (p.c_fp32) {
             float* dst = reinterpret_cast<float*>(cbase) + coff + col0;
             if (full_chunk) {
@@ -268,10 +337,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 *reinterpret_cast<float4*>(dst + i) = o;
               }
             } else {
-              for (int i = 0; i < 32 && col0 + i < p.N; ++i) {
-                float o = __uint_as_float(v[i]);
-                if (p.accumulate) o += dst[i];
-                dst[i] = o;
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {  // constant indices keep v[] in registers
+                if (col0 + i < p.N) {
+                  float o = __uint_as_float(v[i]);
+                  if (p.accumulate) o += dst[i];
+                  dst[i] = o;
+                }
               }
             }
           } else {
@@ -301,11 +373,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 *reinterpret_cast<uint4*>(dst + i) = o;
               }
             } else {
-              for (int i = 0; i < 32 && col0 + i < p.N; ++i) {
-                float o = __uint_as_float(v[i]);
-                if (res) o += __bfloat162float(res[i]);
-                if (p.accumulate) o += __bfloat162float(dst[i]);
-                dst[i] = __float2bfloat16(o);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                if (col0 + i < p.N) {
+                  float o = __uint_as_float(v[i]);
+                  if (res) o += __bfloat162float(res[i]);
+                  if (p.accumulate) o += __bfloat162float(dst[i]);
+                  dst[i] = __float2bfloat16(o);
+                }
               }
             }
           }
@@ -352,13 +427,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               }
             }
           } else {
-            for (int i = 0; i < lim; ++i) {
-              float g0 = __bfloat162float(__float2bfloat16(__uint_as_float(gv[i])));
-              float u0 = __bfloat162float(__float2bfloat16(__uint_as_float(uv[i])));
-              out[col0 + i] = __float2bfloat16(g0 / (1.0f + __expf(-g0)) * u0 * scale);
-              if (pre) {
-                pre[col0 + i] = __float2bfloat16(g0);
-                pre[p.F + col0 + i] = __float2bfloat16(u0);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              if (i < lim) {
+                float g0 = __bfloat162float(__float2bfloat16(__uint_as_float(gv[i])));
+                float u0 = __bfloat162float(__float2bfloat16(__uint_as_float(uv[i])));
+                out[col0 + i] = __float2bfloat16(g0 / (1.0f + __expf(-g0)) * u0 * scale);
+                if (pre) {
+                  pre[col0 + i] = __float2bfloat16(g0);
+                  pre[p.F + col0 + i] = __float2bfloat16(u0);
+                }
               }
             }
           }
