@@ -235,6 +235,7 @@ def run_ours(args) -> dict:
     }
     if world > 1:
         dist.barrier()
+    if dist.is_initialized():
         dist.destroy_process_group()
     return out if rank == 0 else {}
 

@@ -65,6 +65,10 @@ static_assert(EPI_WARPS == 8, "the staging area is sized for eight epilogue warp
 __device__ __forceinline__ uint32_t epi_piece_addr(uint32_t base, int row, int piece) {
   return base + row * 128 + ((piece ^ (row & 7)) << 4);
 }
+// same for packed bf16 chunks: 64 bytes per row, four 16-byte pieces
+__device__ __forceinline__ uint32_t epi_piece_addr64(uint32_t base, int row, int piece) {
+  return base + row * 64 + ((piece ^ ((row >> 1) & 3)) << 4);
+}
 
 template <int BN, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -401,32 +405,65 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           tmem_ld_32x32b_x32(t_row + c * 32, gv);
           tmem_ld_32x32b_x32(t_row + HALF + c * 32, uv);
           tmem_ld_wait();
-          if (!row_ok) continue;
           const int lim = min(32, p.N - col0);
           if (lim == 32) {
+            // all lanes take part (warp-uniform branch): results are packed to bf16, transposed through the staging
+            // area in two rounds (out + gate, then up) and stored as 64-byte row segments, 8 rows per instruction
+            uint32_t o[16], pg[16], pu[16];
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              uint32_t o[4], pg[4], pu[4];
+            for (int j = 0; j < 32; j += 2) {
+              // pre-activations are rounded to bf16 first so forward and backward see the same values
+              float g0 = __bfloat162float(__float2bfloat16(__uint_as_float(gv[j])));
+              float g1 = __bfloat162float(__float2bfloat16(__uint_as_float(gv[j + 1])));
+              float u0 = __bfloat162float(__float2bfloat16(__uint_as_float(uv[j])));
+              float u1 = __bfloat162float(__float2bfloat16(__uint_as_float(uv[j + 1])));
+              float a0 = g0 / (1.0f + __expf(-g0)) * u0 * scale;
+              float a1 = g1 / (1.0f + __expf(-g1)) * u1 * scale;
+              o[j / 2] = pack_bf16(a0, a1);
+              pg[j / 2] = pack_bf16(g0, g1);
+              pu[j / 2] = pack_bf16(u0, u1);
+            }
+            const uint32_t st = smem_u32(epi_stage + (warp - 2) * L::EPI_STAGE_BYTES);
+            const int row_base = mt * BM + lane_group * 32;
+            const int q = lane & 3;
+            __syncwarp();
 #pragma unroll
-              for (int j = 0; j < 8; j += 2) {
-                // pre-activations are rounded to bf16 first so forward and backward see the same values
-                float g0 = __bfloat162float(__float2bfloat16(__uint_as_float(gv[i + j])));
-                float g1 = __bfloat162float(__float2bfloat16(__uint_as_float(gv[i + j + 1])));
-                float u0 = __bfloat162float(__float2bfloat16(__uint_as_float(uv[i + j])));
-                float u1 = __bfloat162float(__float2bfloat16(__uint_as_float(uv[i + j + 1])));
-                float a0 = g0 / (1.0f + __expf(-g0)) * u0 * scale;
-                float a1 = g1 / (1.0f + __expf(-g1)) * u1 * scale;
-                o[j / 2] = pack_bf16(a0, a1);
-                pg[j / 2] = pack_bf16(g0, g1);
-                pu[j / 2] = pack_bf16(u0, u1);
-              }
-              *reinterpret_cast<uint4*>(out + col0 + i) = make_uint4(o[0], o[1], o[2], o[3]);
+            for (int i = 0; i < 4; ++i) {
+              st_shared_v4(epi_piece_addr64(st, lane, i), o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+              if (pre) st_shared_v4(epi_piece_addr64(st + 2048, lane, i), pg[4 * i], pg[4 * i + 1], pg[4 * i + 2], pg[4 * i + 3]);
+            }
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int r = (lane >> 2) + 8 * j;
+              if (row_base + r >= p.M) continue;
+              uint4 w;
+              ld_shared_v4(epi_piece_addr64(st, r, q), w.x, w.y, w.z, w.w);
+              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row_base + r) * p.ldc + col0 + 8 * q) = w;
               if (pre) {
-                *reinterpret_cast<uint4*>(pre + col0 + i) = make_uint4(pg[0], pg[1], pg[2], pg[3]);
-                *reinterpret_cast<uint4*>(pre + p.F + col0 + i) = make_uint4(pu[0], pu[1], pu[2], pu[3]);
+                ld_shared_v4(epi_piece_addr64(st + 2048, r, q), w.x, w.y, w.z, w.w);
+                *reinterpret_cast<uint4*>(p.preact + static_cast<long long>(row_base + r) * p.ld_preact + col0 + 8 * q) = w;
               }
             }
-          } else {
+            if (pre) {
+              __syncwarp();
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                st_shared_v4(epi_piece_addr64(st, lane, i), pu[4 * i], pu[4 * i + 1], pu[4 * i + 2], pu[4 * i + 3]);
+              __syncwarp();
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int r = (lane >> 2) + 8 * j;
+                if (row_base + r >= p.M) continue;
+                uint4 w;
+                ld_shared_v4(epi_piece_addr64(st, r, q), w.x, w.y, w.z, w.w);
+                *reinterpret_cast<uint4*>(p.preact + static_cast<long long>(row_base + r) * p.ld_preact + p.F + col0 + 8 * q) = w;
+              }
+            }
+            continue;
+          }
+          if (!row_ok) continue;
+          {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               if (i < lim) {
