@@ -174,6 +174,225 @@ __global__ void colsum_kernel(const float* __restrict__ partial, float* __restri
 }
 
 // ============================================================================
+// LayerNorm (weight + bias) for the vision tower: fp32 statistics, bf16 in / out.
+//   y = (x - mean) * rstd * w + b
+//   dx = rstd * (g - mean(g) - xhat * mean(g * xhat)),  g = dy * w ; dw = sum dy * xhat ; db = sum dy
+// Forward: one block per row.  Backward: persistent blocks, per-thread dw / db partials flushed to
+// part[blockIdx.x][2][H] and reduced by colsum_kernel (deterministic order).
+// HF ViT eager `nn.LayerNorm` of the reference's vision blocks (models/qwen3_5/modeling_qwen3_5.py:1035-1207).
+// ============================================================================
+template <int MAX_ITERS>
+__global__ void layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                     const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ y,
+                                     float* __restrict__ mean_out, float* __restrict__ rstd_out, int H, float eps) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  float vals[MAX_ITERS][8];
+  float s = 0.f;
+#pragma unroll
+  for (int it = 0; it < MAX_ITERS; ++it) {
+    const int c = (it * blockDim.x + threadIdx.x) * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) vals[it][j] = 0.f;
+    if (c >= H) continue;
+    const uint4 u = *reinterpret_cast<const uint4*>(x + row * H + c);
+    const float2 a = unpack_bf16(u.x), bb = unpack_bf16(u.y), cc = unpack_bf16(u.z), d = unpack_bf16(u.w);
+    vals[it][0] = a.x; vals[it][1] = a.y; vals[it][2] = bb.x; vals[it][3] = bb.y;
+    vals[it][4] = cc.x; vals[it][5] = cc.y; vals[it][6] = d.x; vals[it][7] = d.y;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += vals[it][j];
+  }
+  const float mean = block_sum(s, red) / static_cast<float>(H);
+  float ss = 0.f;
+#pragma unroll
+  for (int it = 0; it < MAX_ITERS; ++it) {
+    const int c = (it * blockDim.x + threadIdx.x) * 8;
+    if (c >= H) continue;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float d = vals[it][j] - mean;
+      ss += d * d;
+    }
+  }
+  const float rstd = rsqrtf(block_sum(ss, red) / static_cast<float>(H) + eps);
+  if (threadIdx.x == 0) {
+    mean_out[row] = mean;
+    rstd_out[row] = rstd;
+  }
+#pragma unroll
+  for (int it = 0; it < MAX_ITERS; ++it) {
+    const int c = (it * blockDim.x + threadIdx.x) * 8;
+    if (c >= H) continue;
+    const uint4 wu = *reinterpret_cast<const uint4*>(w + c);
+    const uint4 bu = *reinterpret_cast<const uint4*>(b + c);
+    const uint32_t ws[4] = {wu.x, wu.y, wu.z, wu.w}, bs[4] = {bu.x, bu.y, bu.z, bu.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 wf = unpack_bf16(ws[j]), bf = unpack_bf16(bs[j]);
+      o[j] = pack_bf16((vals[it][2 * j] - mean) * rstd * wf.x + bf.x, (vals[it][2 * j + 1] - mean) * rstd * wf.y + bf.y);
+    }
+    *reinterpret_cast<uint4*>(y + row * H + c) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+template <int MAX_ITERS>
+__global__ void layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                     const __nv_bfloat16* __restrict__ w, const float* __restrict__ mean_in,
+                                     const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
+                                     float* __restrict__ part, long long T, int H) {
+  __shared__ float red[32];
+  float dwacc[MAX_ITERS][8], dbacc[MAX_ITERS][8];
+#pragma unroll
+  for (int i = 0; i < MAX_ITERS; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { dwacc[i][j] = 0.f; dbacc[i][j] = 0.f; }
+  for (long long row = blockIdx.x; row < T; row += gridDim.x) {
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    float xh[MAX_ITERS][8], g[MAX_ITERS][8];
+    float sg = 0.f, sgx = 0.f;
+#pragma unroll
+    for (int it = 0; it < MAX_ITERS; ++it) {
+      const int c = (it * blockDim.x + threadIdx.x) * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { xh[it][j] = 0.f; g[it][j] = 0.f; }
+      if (c >= H) continue;
+      const uint4 xu = *reinterpret_cast<const uint4*>(x + row * H + c);
+      const uint4 du = *reinterpret_cast<const uint4*>(dy + row * H + c);
+      const uint4 wu = *reinterpret_cast<const uint4*>(w + c);
+      const uint32_t xs[4] = {xu.x, xu.y, xu.z, xu.w}, ds[4] = {du.x, du.y, du.z, du.w}, ws[4] = {wu.x, wu.y, wu.z, wu.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 xf = unpack_bf16(xs[j]), df = unpack_bf16(ds[j]), wf = unpack_bf16(ws[j]);
+        const float h0 = (xf.x - mean) * rstd, h1 = (xf.y - mean) * rstd;
+        xh[it][2 * j] = h0; xh[it][2 * j + 1] = h1;
+        g[it][2 * j] = df.x * wf.x; g[it][2 * j + 1] = df.y * wf.y;
+        sg += g[it][2 * j] + g[it][2 * j + 1];
+        sgx += g[it][2 * j] * h0 + g[it][2 * j + 1] * h1;
+        dwacc[it][2 * j] += df.x * h0; dwacc[it][2 * j + 1] += df.y * h1;
+        dbacc[it][2 * j] += df.x; dbacc[it][2 * j + 1] += df.y;
+      }
+    }
+    sg = block_sum(sg, red) / static_cast<float>(H);
+    sgx = block_sum(sgx, red) / static_cast<float>(H);
+#pragma unroll
+    for (int it = 0; it < MAX_ITERS; ++it) {
+      const int c = (it * blockDim.x + threadIdx.x) * 8;
+      if (c >= H) continue;
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        o[j] = pack_bf16(rstd * (g[it][2 * j] - sg - xh[it][2 * j] * sgx), rstd * (g[it][2 * j + 1] - sg - xh[it][2 * j + 1] * sgx));
+      *reinterpret_cast<uint4*>(dx + row * H + c) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+#pragma unroll
+  for (int it = 0; it < MAX_ITERS; ++it) {
+    const int c = (it * blockDim.x + threadIdx.x) * 8;
+    if (c >= H) continue;
+    float* dwp = part + static_cast<long long>(blockIdx.x) * 2 * H + c;
+    float* dbp = dwp + H;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { dwp[j] = dwacc[it][j]; dbp[j] = dbacc[it][j]; }
+  }
+}
+
+// ============================================================================
+// y = act(x + bias) (+ residual): the elementwise tail of a biased projection in one pass.
+//   act 0: identity, 1: GELU (tanh approximation), 2: GELU (erf).   x [R, C], bias [C], residual [R, C]; C % 8 == 0
+// Backward: dx = dy * act'(x + bias) ; dbias = column sum of dx (partials per block, reduced by colsum_kernel).
+// ============================================================================
+__device__ __forceinline__ float act_fwd(float v, int act) {
+  if (act == 1) {
+    const float u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
+    return 0.5f * v * (1.f + tanhf(u));
+  }
+  if (act == 2) return 0.5f * v * (1.f + erff(v * 0.7071067811865476f));
+  return v;
+}
+__device__ __forceinline__ float act_grad(float v, int act) {
+  if (act == 1) {
+    const float u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
+    const float t = tanhf(u);
+    return 0.5f * (1.f + t) + 0.5f * v * (1.f - t * t) * 0.7978845608028654f * (1.f + 3.f * 0.044715f * v * v);
+  }
+  if (act == 2) return 0.5f * (1.f + erff(v * 0.7071067811865476f)) + v * 0.3989422804014327f * __expf(-0.5f * v * v);
+  return 1.f;
+}
+
+__global__ void bias_act_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ bias,
+                                    const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ y,
+                                    long long R, int C, int act) {
+  const long long vec_per_row = C / 8;
+  const long long total = R * vec_per_row;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(i % vec_per_row) * 8;
+    const uint4 xu = *(reinterpret_cast<const uint4*>(x) + i);
+    const uint4 bu = *reinterpret_cast<const uint4*>(bias + c);
+    uint4 ru = make_uint4(0u, 0u, 0u, 0u);
+    if (residual) ru = *(reinterpret_cast<const uint4*>(residual) + i);
+    const uint32_t xs[4] = {xu.x, xu.y, xu.z, xu.w}, bs[4] = {bu.x, bu.y, bu.z, bu.w}, rs[4] = {ru.x, ru.y, ru.z, ru.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 xf = unpack_bf16(xs[j]), bf = unpack_bf16(bs[j]), rf = unpack_bf16(rs[j]);
+      o[j] = pack_bf16(act_fwd(xf.x + bf.x, act) + rf.x, act_fwd(xf.y + bf.y, act) + rf.y);
+    }
+    *(reinterpret_cast<uint4*>(y) + i) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+template <int MAX_ITERS>
+__global__ void bias_act_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                    const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ dx,
+                                    float* __restrict__ part, long long R, int C, int act) {
+  float acc[MAX_ITERS][8];
+#pragma unroll
+  for (int i = 0; i < MAX_ITERS; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+  for (long long row = blockIdx.x; row < R; row += gridDim.x) {
+#pragma unroll
+    for (int it = 0; it < MAX_ITERS; ++it) {
+      const int c = (it * blockDim.x + threadIdx.x) * 8;
+      if (c >= C) continue;
+      const uint4 du = *reinterpret_cast<const uint4*>(dy + row * C + c);
+      const uint32_t ds[4] = {du.x, du.y, du.z, du.w};
+      uint32_t o[4];
+      if (act == 0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 df = unpack_bf16(ds[j]);
+          acc[it][2 * j] += df.x; acc[it][2 * j + 1] += df.y;
+          o[j] = ds[j];
+        }
+      } else {
+        const uint4 xu = *reinterpret_cast<const uint4*>(x + row * C + c);
+        const uint4 bu = *reinterpret_cast<const uint4*>(bias + c);
+        const uint32_t xs[4] = {xu.x, xu.y, xu.z, xu.w}, bs[4] = {bu.x, bu.y, bu.z, bu.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 df = unpack_bf16(ds[j]), xf = unpack_bf16(xs[j]), bf = unpack_bf16(bs[j]);
+          const float g0 = df.x * act_grad(xf.x + bf.x, act), g1 = df.y * act_grad(xf.y + bf.y, act);
+          acc[it][2 * j] += g0; acc[it][2 * j + 1] += g1;
+          o[j] = pack_bf16(g0, g1);
+        }
+      }
+      if (dx) *reinterpret_cast<uint4*>(dx + row * C + c) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+#pragma unroll
+  for (int it = 0; it < MAX_ITERS; ++it) {
+    const int c = (it * blockDim.x + threadIdx.x) * 8;
+    if (c >= C) continue;
+    float* dst = part + static_cast<long long>(blockIdx.x) * C + c;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dst[j] = acc[it][j];
+  }
+}
+
+// ============================================================================
 // Fused per-head RMSNorm + rotary embedding (half rotation) for q and k.
 // in : qkv [T, ld] bf16 with q heads at column 0, k heads at column Hq*D
 // out: q_out [T, Hq, D], k_out [T, Hk, D]  (v is consumed in place by attention)
@@ -616,6 +835,67 @@ TTB_EXPORT int ttb_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
   else if (iters <= 4) rmsnorm_bwd_kernel<4><<<grid, threads, 0, STREAM(stream)>>>(DY, X, W, rstd, (const __nv_bfloat16*)dres_in, (__nv_bfloat16*)dx, dw_partial, T, H, one_plus_w);
   else return 902;
   colsum_kernel<<<(H + 255) / 256, 256, 0, STREAM(stream)>>>(dw_partial, dw_out, grid, H);
+  LAUNCH_RET();
+}
+
+TTB_EXPORT int ttb_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
+                                 long long T, int H, float eps, void* stream) {
+  if (H % 8) return 901;
+  if (T == 0) return 0;
+  int threads = H / 8;
+  threads = threads > 256 ? 256 : ((threads + 31) / 32) * 32;
+  const int iters = (H + threads * 8 - 1) / (threads * 8);
+  auto X = (const __nv_bfloat16*)x; auto W = (const __nv_bfloat16*)w; auto B = (const __nv_bfloat16*)b;
+  if (iters <= 1) layernorm_fwd_kernel<1><<<(unsigned)T, threads, 0, STREAM(stream)>>>(X, W, B, (__nv_bfloat16*)y, mean, rstd, H, eps);
+  else if (iters <= 4) layernorm_fwd_kernel<4><<<(unsigned)T, threads, 0, STREAM(stream)>>>(X, W, B, (__nv_bfloat16*)y, mean, rstd, H, eps);
+  else return 902;
+  LAUNCH_RET();
+}
+
+// part must hold grid * 2 * H floats; dwdb_out receives [2][H] (dw then db).
+TTB_EXPORT int ttb_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, void* dx,
+                                 float* part, float* dwdb_out, long long T, int H, int grid, void* stream) {
+  if (H % 8) return 901;
+  if (T == 0) return 0;
+  int threads = H / 8;
+  threads = threads > 256 ? 256 : ((threads + 31) / 32) * 32;
+  const int iters = (H + threads * 8 - 1) / (threads * 8);
+  if (grid > T) grid = (int)T;
+  auto DY = (const __nv_bfloat16*)dy; auto X = (const __nv_bfloat16*)x; auto W = (const __nv_bfloat16*)w;
+  if (iters <= 1) layernorm_bwd_kernel<1><<<grid, threads, 0, STREAM(stream)>>>(DY, X, W, mean, rstd, (__nv_bfloat16*)dx, part, T, H);
+  else if (iters <= 4) layernorm_bwd_kernel<4><<<grid, threads, 0, STREAM(stream)>>>(DY, X, W, mean, rstd, (__nv_bfloat16*)dx, part, T, H);
+  else return 902;
+  colsum_kernel<<<(2 * H + 255) / 256, 256, 0, STREAM(stream)>>>(part, dwdb_out, grid, 2 * H);
+  LAUNCH_RET();
+}
+
+TTB_EXPORT int ttb_bias_act_fwd(const void* x, const void* bias, const void* residual, void* y, long long R, int C, int act,
+                                void* stream) {
+  if (C % 8 || act < 0 || act > 2) return 901;
+  if (R == 0) return 0;
+  const long long total = R * (C / 8);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  bias_act_fwd_kernel<<<(unsigned)blocks, 256, 0, STREAM(stream)>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)bias,
+                                                                    (const __nv_bfloat16*)residual, (__nv_bfloat16*)y, R, C, act);
+  LAUNCH_RET();
+}
+
+// part must hold grid * C floats; dx may be null (identity activation: d(x) is dy itself).
+TTB_EXPORT int ttb_bias_act_bwd(const void* dy, const void* x, const void* bias, void* dx, float* part, float* dbias_out,
+                                long long R, int C, int act, int grid, void* stream) {
+  if (C % 8 || act < 0 || act > 2) return 901;
+  if (R == 0) return 0;
+  int threads = C / 8;
+  threads = threads > 256 ? 256 : ((threads + 31) / 32) * 32;
+  const int iters = (C + threads * 8 - 1) / (threads * 8);
+  if (grid > R) grid = (int)R;
+  auto DY = (const __nv_bfloat16*)dy; auto X = (const __nv_bfloat16*)x; auto B = (const __nv_bfloat16*)bias;
+  if (iters <= 1) bias_act_bwd_kernel<1><<<grid, threads, 0, STREAM(stream)>>>(DY, X, B, (__nv_bfloat16*)dx, part, R, C, act);
+  else if (iters <= 4) bias_act_bwd_kernel<4><<<grid, threads, 0, STREAM(stream)>>>(DY, X, B, (__nv_bfloat16*)dx, part, R, C, act);
+  else if (iters <= 8) bias_act_bwd_kernel<8><<<grid, threads, 0, STREAM(stream)>>>(DY, X, B, (__nv_bfloat16*)dx, part, R, C, act);
+  else return 902;
+  colsum_kernel<<<(C + 255) / 256, 256, 0, STREAM(stream)>>>(part, dbias_out, grid, C);
   LAUNCH_RET();
 }
 

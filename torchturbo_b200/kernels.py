@@ -73,7 +73,7 @@ def lib():
 
 
 # kernels launched per C entry point (used to report how many of this library's kernels ran in a region)
-_LAUNCHES_PER_CALL = {"ttb_rmsnorm_bwd": 2, "ttb_router_fwd": 2, "ttb_perm_index": 3, "ttb_perm_scatter": 2,
+_LAUNCHES_PER_CALL = {"ttb_rmsnorm_bwd": 2, "ttb_layernorm_bwd": 2, "ttb_bias_act_bwd": 2, "ttb_router_fwd": 2, "ttb_perm_index": 3, "ttb_perm_scatter": 2,
                       "ttb_gemm_status": 0}
 LAUNCH_COUNT = 0
 
@@ -246,6 +246,65 @@ def rmsnorm_bwd(dy, x_sum, weight, rstd, dres=None, one_plus_w=False):
                                  C.c_longlong(T), C.c_int(H), C.c_int(int(one_plus_w)), C.c_int(grid), _stream()),
            "ttb_rmsnorm_bwd")
     return dx.view(x_sum.shape), dw
+
+
+# --------------------------------------------------------------------------------------
+# LayerNorm and bias + activation (vision tower)
+# --------------------------------------------------------------------------------------
+ACT = {None: 0, "none": 0, "identity": 0, "gelu_tanh": 1, "gelu_pytorch_tanh": 1, "gelu": 2, "gelu_erf": 2}
+
+
+def layernorm_fwd(x, weight, bias, eps):
+    """Returns (y, mean, rstd); statistics in fp32."""
+    H = x.shape[-1]
+    x2 = x.reshape(-1, H)
+    T = x2.shape[0]
+    y = torch.empty_like(x2)
+    mean = torch.empty(T, dtype=torch.float32, device=x.device)
+    rstd = torch.empty(T, dtype=torch.float32, device=x.device)
+    _check(lib().ttb_layernorm_fwd(_p(x2), _p(weight), _p(bias), _p(y), _p(mean), _p(rstd), C.c_longlong(T), C.c_int(H),
+                                   C.c_float(eps), _stream()), "ttb_layernorm_fwd")
+    return y.view(x.shape), mean, rstd
+
+
+def layernorm_bwd(dy, x, weight, mean, rstd):
+    """Returns (dx, dw_fp32, db_fp32)."""
+    H = x.shape[-1]
+    x2, dy2 = x.reshape(-1, H), dy.reshape(-1, H)
+    T = x2.shape[0]
+    grid = max(1, min(T, 2 * num_sms(x.device.index)))
+    dx = torch.empty_like(x2)
+    part = torch.empty(grid, 2 * H, dtype=torch.float32, device=x.device)
+    dwdb = torch.empty(2, H, dtype=torch.float32, device=x.device)
+    _check(lib().ttb_layernorm_bwd(_p(dy2), _p(x2), _p(weight), _p(mean), _p(rstd), _p(dx), _p(part), _p(dwdb),
+                                   C.c_longlong(T), C.c_int(H), C.c_int(grid), _stream()), "ttb_layernorm_bwd")
+    return dx.view(x.shape), dwdb[0], dwdb[1]
+
+
+def bias_act_fwd(x, bias, act, residual=None):
+    """y = act(x + bias) (+ residual) on bf16 rows."""
+    Cn = x.shape[-1]
+    x2 = x.reshape(-1, Cn)
+    y = torch.empty_like(x2)
+    r2 = residual.reshape(-1, Cn) if residual is not None else None
+    _check(lib().ttb_bias_act_fwd(_p(x2), _p(bias), _p(r2), _p(y), C.c_longlong(x2.shape[0]), C.c_int(Cn), C.c_int(ACT[act]),
+                                  _stream()), "ttb_bias_act_fwd")
+    return y.view(x.shape)
+
+
+def bias_act_bwd(dy, x, bias, act):
+    """Returns (dx, dbias_fp32); with the identity activation dx is dy itself."""
+    Cn = x.shape[-1]
+    x2, dy2 = x.reshape(-1, Cn), dy.reshape(-1, Cn)
+    R = x2.shape[0]
+    code = ACT[act]
+    grid = max(1, min(R, 2 * num_sms(x.device.index)))
+    dx = torch.empty_like(x2) if code else None
+    part = torch.empty(grid, Cn, dtype=torch.float32, device=x.device)
+    db = torch.empty(Cn, dtype=torch.float32, device=x.device)
+    _check(lib().ttb_bias_act_bwd(_p(dy2), _p(x2), _p(bias), _p(dx), _p(part), _p(db), C.c_longlong(R), C.c_int(Cn),
+                                  C.c_int(code), C.c_int(grid), _stream()), "ttb_bias_act_bwd")
+    return (dx.view(x.shape) if dx is not None else dy), db
 
 
 # --------------------------------------------------------------------------------------

@@ -87,17 +87,19 @@ class VisionBlock(nn.Module):
         self.fc2 = nn.Linear(cfg.intermediate_size, H, dtype=dtype)
 
     def forward(self, x, cos, sin, cu, max_len):
+        """Biases, GELU and residual adds ride on `ops.bias_act` (one pass after each GEMM), the norms on
+        `ops.layer_norm`; attention is full (non-causal) over each image's patches."""
         P = x.shape[0]
-        h = self.norm1(x)
-        qkv = (ops.linear(h, self.qkv.weight) + self.qkv.bias).view(P, 3, self.n_heads, self.head_dim)
+        h = ops.layer_norm(x, self.norm1.weight, self.norm1.bias, self.norm1.eps)
+        qkv = ops.bias_act(ops.linear(h, self.qkv.weight), self.qkv.bias).view(P, 3, self.n_heads, self.head_dim)
         q, k, v = qkv[:, 0], qkv[:, 1], qkv[:, 2]
         q, k = ops.rotary_position_embedding(q, cos, sin), ops.rotary_position_embedding(k, cos, sin)
         a = ops.attention(q.contiguous(), k.contiguous(), v.contiguous(), cu, max_len, causal=False,
                           scale=1.0 / math.sqrt(self.head_dim))
-        x = x + ops.linear(a.reshape(P, -1), self.proj.weight) + self.proj.bias
-        h = self.norm2(x)
-        h = F.gelu(ops.linear(h, self.fc1.weight) + self.fc1.bias, approximate="tanh")
-        return x + ops.linear(h, self.fc2.weight) + self.fc2.bias
+        x = ops.bias_act(ops.linear(a.reshape(P, -1), self.proj.weight), self.proj.bias, residual=x)
+        h = ops.layer_norm(x, self.norm2.weight, self.norm2.bias, self.norm2.eps)
+        h = ops.bias_act(ops.linear(h, self.fc1.weight), self.fc1.bias, "gelu_tanh")
+        return ops.bias_act(ops.linear(h, self.fc2.weight), self.fc2.bias, residual=x)
 
 
 class PatchMerger(nn.Module):
@@ -110,8 +112,9 @@ class PatchMerger(nn.Module):
         self.fc2 = nn.Linear(Hm, cfg.out_hidden_size, dtype=dtype)
 
     def forward(self, x):
-        x = self.ln_q(x).view(-1, self.unit * x.shape[-1])
-        return ops.linear(F.gelu(ops.linear(x, self.fc1.weight) + self.fc1.bias), self.fc2.weight) + self.fc2.bias
+        x = ops.layer_norm(x, self.ln_q.weight, self.ln_q.bias, self.ln_q.eps).view(-1, self.unit * x.shape[-1])
+        h = ops.bias_act(ops.linear(x, self.fc1.weight), self.fc1.bias, "gelu")
+        return ops.bias_act(ops.linear(h, self.fc2.weight), self.fc2.bias)
 
 
 class VisionTower(nn.Module):

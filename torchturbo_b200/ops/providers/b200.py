@@ -176,6 +176,60 @@ class B200RMSNorm(_B200Op):
         return RMSNormFn.apply(x, weight, eps, residual, one_plus_weight)
 
 
+class LayerNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, b, eps):
+        x = x.contiguous()
+        y, mean, rstd = K.layernorm_fwd(x, w, b, eps)
+        ctx.save_for_backward(x, w, mean, rstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, mean, rstd = ctx.saved_tensors
+        dx, dw, db = K.layernorm_bwd(dy.contiguous(), x, w, mean, rstd)
+        return dx, dw.to(w.dtype), db.to(w.dtype), None
+
+
+@_custom("layer_norm", "b200_layer_norm")
+class B200LayerNorm(_B200Op):
+    """LayerNorm with weight and bias in one pass each way (vision tower)."""
+
+    def __call__(self, x, weight, bias, eps=1e-6):
+        H = x.shape[-1]
+        if not _ok(x, weight, bias) or H % 8 or H > 8192:
+            return N.layer_norm_ref(x, weight, bias, eps)
+        return LayerNormFn.apply(x, weight, bias, eps)
+
+
+class BiasActFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, bias, act, residual):
+        x = x.contiguous()
+        y = K.bias_act_fwd(x, bias, act, residual.contiguous() if residual is not None else None)
+        ctx.save_for_backward(x, bias)
+        ctx.act, ctx.has_res = act, residual is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, bias = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx, db = K.bias_act_bwd(dy, x, bias, ctx.act)
+        return dx, db.to(bias.dtype), None, (dy if ctx.has_res else None)
+
+
+@_custom("bias_act", "b200_bias_act")
+class B200BiasAct(_B200Op):
+    """`act(x + bias) (+ residual)` and its backward (d(x) and the bias gradient in one pass)."""
+
+    def __call__(self, x, bias, act=None, *, residual=None):
+        Cn = x.shape[-1]
+        if not _ok(x, bias, residual) or Cn % 8 or Cn > 16384 or act not in K.ACT:
+            return N.bias_act_ref(x, bias, act, residual)
+        return BiasActFn.apply(x, bias, act, residual)
+
+
 class SwiGLUFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, probs):

@@ -43,6 +43,39 @@ class TorchRMSNorm(OpImpl):
         return rms_norm_ref(x, weight, eps, residual, one_plus_weight)
 
 
+def layer_norm_ref(x, weight, bias, eps=1e-6):
+    return F.layer_norm(x.float(), (x.shape[-1],), weight.float(), bias.float(), eps).to(x.dtype)
+
+
+@_native("layer_norm")
+class TorchLayerNorm(OpImpl):
+    """fp32 LayerNorm with affine weight and bias, cast back to the input dtype."""
+
+    def __call__(self, x, weight, bias, eps=1e-6):
+        return layer_norm_ref(x, weight, bias, eps)
+
+
+def bias_act_ref(x, bias, act=None, residual=None):
+    v = x.float() + bias.float()
+    if act in ("gelu_tanh", "gelu_pytorch_tanh"):
+        v = F.gelu(v, approximate="tanh")
+    elif act in ("gelu", "gelu_erf"):
+        v = F.gelu(v)
+    elif act not in (None, "none", "identity"):
+        raise ValueError(f"unknown activation {act!r}")
+    if residual is not None:
+        v = v + residual.float()
+    return v.to(x.dtype)
+
+
+@_native("bias_act")
+class TorchBiasAct(OpImpl):
+    """`act(x + bias) (+ residual)`: the elementwise tail of a biased projection."""
+
+    def __call__(self, x, bias, act=None, *, residual=None):
+        return bias_act_ref(x, bias, act, residual)
+
+
 def swiglu_ref(x, probs=None):
     gate, up = x.chunk(2, dim=-1)
     y = F.silu(gate) * up
