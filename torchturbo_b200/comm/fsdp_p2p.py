@@ -19,8 +19,9 @@ finds its slot still referenced locally is served by the NCCL collective instead
 ranks decide alike).  The number of slots bounds how many collectives FSDP may keep alive at once: an all-gather
 result lives from its copy-in to its copy-out (current unit + prefetched units + the one whose buffer release is
 deferred by one unit), a reduce-scatter input until the next reduce-scatter has been issued; FSDP orders a new
-copy-in after the copy-out of the previous unit, so `prefetch depth + 5` all-gather slots and 3 reduce-scatter
-slots are never overwritten while still being read locally.
+copy-in after the copy-out of the previous unit, so `prefetch depth + 4` all-gather slots and 3 reduce-scatter
+slots are never overwritten while still being read locally.  Slots are capped at 1 GiB (all-gather) / 2 GiB
+(reduce-scatter input): larger units, e.g. a 150k-row embedding of a wide model, keep NCCL.
 
 The reference runs these collectives through NCCL inside torch FSDP2 (engine/backends/fsdp2/backend.py:420-470).
 """
@@ -179,10 +180,10 @@ def install(units, group, *, prefetch_depth: int = 1) -> PeerCollectiveArena | N
             continue
         n = sum(fp.padded_sharded_param_size.numel() for fp in pg.fsdp_params)
         biggest = max(biggest, n * W)
-    cap = int(os.environ.get("TORCHTURBO_FSDP_P2P_MAX_SLOT_MB", "2048")) << 20
+    cap = int(os.environ.get("TORCHTURBO_FSDP_P2P_MAX_SLOT_MB", "1024")) << 20
     ag_bytes = min(cap, biggest * 2 + 4096 * W)
     rs_bytes = min(2 * cap, biggest * 4 + 4096 * W)
-    n_ag = int(os.environ.get("TORCHTURBO_FSDP_P2P_SLOTS", str(prefetch_depth + 5)))
+    n_ag = int(os.environ.get("TORCHTURBO_FSDP_P2P_SLOTS", str(prefetch_depth + 4)))
     key = id(group)
     arena = _ARENAS.get(key)
     if arena is None or arena.ag_bytes < ag_bytes or arena.rs_bytes < rs_bytes:

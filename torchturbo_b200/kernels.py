@@ -90,7 +90,13 @@ def _check(code: int, what: str) -> None:
     LAUNCH_COUNT += _LAUNCHES_PER_CALL.get(what, 1)
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> C.c_void_p:
+    """Handle of the current stream of the current device (the raw accessor skips building a `torch.cuda.Stream`)."""
+    if _raw_stream is not None:
+        return C.c_void_p(_raw_stream(torch.cuda.current_device()))
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
