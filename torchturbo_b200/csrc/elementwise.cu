@@ -393,6 +393,136 @@ __global__ void bias_act_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const 
 }
 
 // ============================================================================
+// Causal depthwise short convolution over a packed row (linear-attention mixers: GDN / KDA q, k, v streams).
+//   pre[t, c] = bias[c] + sum_{s < W} w[c, W-1-s] * x[t-s, c]   for t-s inside t's sequence;   y = silu(pre) or pre
+// x, y: [T, D] bf16 (D % 8 == 0), w: [D, W] bf16 (tap W-1 multiplies the current token), seq_start[t] = first token of
+// t's sequence, seq_end[t] = one past its last.  W <= 8.
+// Backward: dpre = dy * act'(pre) (pre is recomputed);  dx[t] = sum_s w[., W-1-s] * dpre[t+s] for t+s in the sequence;
+// dw[c, W-1-s] = sum_t dpre[t, c] * x[t-s, c];  db = sum_t dpre.  Pass 1 writes dpre (bf16) and per-block dw / db
+// partials; pass 2 forms dx.  Torch formulation: ops/providers/native/causal_conv1d.py of the reference (fla Triton
+// kernel on its GPU path).
+// ============================================================================
+constexpr int CONV_MAX_W = 8;   // widest supported filter (kernels are instantiated for <= 4 and <= 8 taps)
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
+  *reinterpret_cast<uint4*>(p) = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+}
+
+// grid: (ceil(D/8 / blockDim.x), row blocks); each thread owns 8 channels and walks rows [r0, r1)
+template <bool BWD, int WMAX>
+__global__ void causal_conv1d_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                     const __nv_bfloat16* __restrict__ bias, const int* __restrict__ seq_start,
+                                     const __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ out,
+                                     float* __restrict__ part, long long T, int D, int W, int silu, int rows_per_block) {
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c >= D) return;
+  float wt[WMAX][8];   // wt[s] = tap for distance s into the past
+#pragma unroll
+  for (int s = 0; s < WMAX; ++s)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) wt[s][j] = (s < W) ? __bfloat162float(w[static_cast<long long>(c + j) * W + (W - 1 - s)]) : 0.f;
+  float bs[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) bs[j] = bias ? __bfloat162float(bias[c + j]) : 0.f;
+  float dwacc[WMAX][8], dbacc[8];
+  if (BWD) {
+#pragma unroll
+    for (int s = 0; s < WMAX; ++s)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dwacc[s][j] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dbacc[j] = 0.f;
+  }
+  const long long r0 = static_cast<long long>(blockIdx.y) * rows_per_block;
+  const long long r1 = (r0 + rows_per_block < T) ? r0 + rows_per_block : T;
+  for (long long t = r0; t < r1; ++t) {
+    const long long first = seq_start[t];
+    float xs[WMAX][8];
+    float pre[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) pre[j] = bs[j];
+#pragma unroll
+    for (int s = 0; s < WMAX; ++s) {
+      if (s < W && t - s >= first) {
+        load8(x + (t - s) * D + c, xs[s]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) pre[j] += wt[s][j] * xs[s][j];
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) xs[s][j] = 0.f;
+      }
+    }
+    float o[8];
+    if (!BWD) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = silu ? pre[j] / (1.f + __expf(-pre[j])) : pre[j];
+    } else {
+      float g[8];
+      load8(dy + t * D + c, g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float d = g[j];
+        if (silu) {
+          const float sg = 1.f / (1.f + __expf(-pre[j]));
+          d *= sg * (1.f + pre[j] * (1.f - sg));
+        }
+        o[j] = d;
+        dbacc[j] += d;
+#pragma unroll
+        for (int s = 0; s < WMAX; ++s) dwacc[s][j] += d * xs[s][j];
+      }
+    }
+    store8(out + t * D + c, o);
+  }
+  if (BWD) {
+    // part[blockIdx.y][(W + 1)][D]: W tap planes (distance s) then the bias plane
+    float* base = part + static_cast<long long>(blockIdx.y) * (W + 1) * D;
+#pragma unroll
+    for (int s = 0; s < WMAX; ++s)
+      if (s < W)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) base[static_cast<long long>(s) * D + c + j] = dwacc[s][j];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) base[static_cast<long long>(W) * D + c + j] = dbacc[j];
+  }
+}
+
+// dx[t] = sum_s w[., W-1-s] * dpre[t+s] for t+s < seq_end[t]
+template <int WMAX>
+__global__ void causal_conv1d_dx_kernel(const __nv_bfloat16* __restrict__ dpre, const __nv_bfloat16* __restrict__ w,
+                                        const int* __restrict__ seq_end, __nv_bfloat16* __restrict__ dx, long long T,
+                                        int D, int W, int rows_per_block) {
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c >= D) return;
+  float wt[WMAX][8];
+#pragma unroll
+  for (int s = 0; s < WMAX; ++s)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) wt[s][j] = (s < W) ? __bfloat162float(w[static_cast<long long>(c + j) * W + (W - 1 - s)]) : 0.f;
+  const long long r0 = static_cast<long long>(blockIdx.y) * rows_per_block;
+  const long long r1 = (r0 + rows_per_block < T) ? r0 + rows_per_block : T;
+  for (long long t = r0; t < r1; ++t) {
+    const long long last = seq_end[t];
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+    for (int s = 0; s < WMAX; ++s) {
+      if (s < W && t + s < last) {
+        float g[8];
+        load8(dpre + (t + s) * D + c, g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += wt[s][j] * g[j];
+      }
+    }
+    store8(dx + t * D + c, acc);
+  }
+}
+
+// ============================================================================
 // Fused per-head RMSNorm + rotary embedding (half rotation) for q and k.
 // in : qkv [T, ld] bf16 with q heads at column 0, k heads at column Hq*D
 // out: q_out [T, Hq, D], k_out [T, Hk, D]  (v is consumed in place by attention)
@@ -896,6 +1026,65 @@ TTB_EXPORT int ttb_bias_act_bwd(const void* dy, const void* x, const void* bias,
   else if (iters <= 8) bias_act_bwd_kernel<8><<<grid, threads, 0, STREAM(stream)>>>(DY, X, B, (__nv_bfloat16*)dx, part, R, C, act);
   else return 902;
   colsum_kernel<<<(C + 255) / 256, 256, 0, STREAM(stream)>>>(part, dbias_out, grid, C);
+  LAUNCH_RET();
+}
+
+static void conv_grid(long long T, int D, int& threads, dim3& grid, int& rows_per_block) {
+  const int vec = D / 8;
+  threads = vec >= 128 ? 128 : ((vec + 31) / 32) * 32;
+  const int gx = (vec + threads - 1) / threads;
+  long long want = (148LL * 8 + gx - 1) / gx;      // about eight blocks per SM in total
+  if (want > T) want = T;
+  if (want < 1) want = 1;
+  rows_per_block = static_cast<int>((T + want - 1) / want);
+  grid = dim3(gx, static_cast<unsigned>((T + rows_per_block - 1) / rows_per_block));
+}
+
+TTB_EXPORT int ttb_causal_conv1d_fwd(const void* x, const void* w, const void* bias, const int* seq_start, void* y,
+                                     long long T, int D, int W, int silu, void* stream) {
+  if (D % 8 || W < 1 || W > CONV_MAX_W) return 901;
+  if (T == 0) return 0;
+  int threads, rpb;
+  dim3 grid;
+  conv_grid(T, D, threads, grid, rpb);
+  if (W <= 4)
+    causal_conv1d_kernel<false, 4><<<grid, threads, 0, STREAM(stream)>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+        (const __nv_bfloat16*)bias, seq_start, nullptr, (__nv_bfloat16*)y, nullptr, T, D, W, silu, rpb);
+  else
+    causal_conv1d_kernel<false, 8><<<grid, threads, 0, STREAM(stream)>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+        (const __nv_bfloat16*)bias, seq_start, nullptr, (__nv_bfloat16*)y, nullptr, T, D, W, silu, rpb);
+  LAUNCH_RET();
+}
+
+// part must hold row_blocks * (W + 1) * D floats (row_blocks from ttb_causal_conv1d_row_blocks); dwdb_out: [(W + 1), D]
+TTB_EXPORT int ttb_causal_conv1d_row_blocks(long long T, int D) {
+  int threads, rpb;
+  dim3 grid;
+  conv_grid(T > 0 ? T : 1, D, threads, grid, rpb);
+  return static_cast<int>(grid.y);
+}
+
+TTB_EXPORT int ttb_causal_conv1d_bwd(const void* dy, const void* x, const void* w, const void* bias, const int* seq_start,
+                                     const int* seq_end, void* dpre, void* dx, float* part, float* dwdb_out, long long T,
+                                     int D, int W, int silu, void* stream) {
+  if (D % 8 || W < 1 || W > CONV_MAX_W) return 901;
+  if (T == 0) return 0;
+  int threads, rpb;
+  dim3 grid;
+  conv_grid(T, D, threads, grid, rpb);
+  if (W <= 4) {
+    causal_conv1d_kernel<true, 4><<<grid, threads, 0, STREAM(stream)>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+        (const __nv_bfloat16*)bias, seq_start, (const __nv_bfloat16*)dy, (__nv_bfloat16*)dpre, part, T, D, W, silu, rpb);
+    causal_conv1d_dx_kernel<4><<<grid, threads, 0, STREAM(stream)>>>((const __nv_bfloat16*)dpre, (const __nv_bfloat16*)w,
+                                                                     seq_end, (__nv_bfloat16*)dx, T, D, W, rpb);
+  } else {
+    causal_conv1d_kernel<true, 8><<<grid, threads, 0, STREAM(stream)>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+        (const __nv_bfloat16*)bias, seq_start, (const __nv_bfloat16*)dy, (__nv_bfloat16*)dpre, part, T, D, W, silu, rpb);
+    causal_conv1d_dx_kernel<8><<<grid, threads, 0, STREAM(stream)>>>((const __nv_bfloat16*)dpre, (const __nv_bfloat16*)w,
+                                                                     seq_end, (__nv_bfloat16*)dx, T, D, W, rpb);
+  }
+  const int cols = (W + 1) * D;
+  colsum_kernel<<<(cols + 255) / 256, 256, 0, STREAM(stream)>>>(part, dwdb_out, static_cast<int>(grid.y), cols);
   LAUNCH_RET();
 }
 

@@ -73,7 +73,8 @@ def lib():
 
 
 # kernels launched per C entry point (used to report how many of this library's kernels ran in a region)
-_LAUNCHES_PER_CALL = {"ttb_rmsnorm_bwd": 2, "ttb_layernorm_bwd": 2, "ttb_bias_act_bwd": 2, "ttb_router_fwd": 2, "ttb_perm_index": 3, "ttb_perm_scatter": 2,
+_LAUNCHES_PER_CALL = {"ttb_rmsnorm_bwd": 2, "ttb_layernorm_bwd": 2, "ttb_bias_act_bwd": 2, "ttb_causal_conv1d_bwd": 3,
+                      "ttb_causal_conv1d_row_blocks": 0, "ttb_router_fwd": 2, "ttb_perm_index": 3, "ttb_perm_scatter": 2,
                       "ttb_gemm_status": 0}
 LAUNCH_COUNT = 0
 
@@ -311,6 +312,34 @@ def bias_act_bwd(dy, x, bias, act):
     _check(lib().ttb_bias_act_bwd(_p(dy2), _p(x2), _p(bias), _p(dx), _p(part), _p(db), C.c_longlong(R), C.c_int(Cn),
                                   C.c_int(code), C.c_int(grid), _stream()), "ttb_bias_act_bwd")
     return (dx.view(x.shape) if dx is not None else dy), db
+
+
+# --------------------------------------------------------------------------------------
+# causal depthwise short convolution (linear-attention mixers)
+# --------------------------------------------------------------------------------------
+def causal_conv1d_fwd(x, weight, bias, seq_start, silu: bool):
+    """x [T, D] bf16, weight [D, W] bf16, seq_start int32 [T] (first token of each token's sequence) -> y [T, D]."""
+    T, D = x.shape
+    y = torch.empty_like(x)
+    _check(lib().ttb_causal_conv1d_fwd(_p(x), _p(weight), _p(bias), _p(seq_start), _p(y), C.c_longlong(T), C.c_int(D),
+                                       C.c_int(weight.shape[1]), C.c_int(int(silu)), _stream()), "ttb_causal_conv1d_fwd")
+    return y
+
+
+def causal_conv1d_bwd(dy, x, weight, bias, seq_start, seq_end, silu: bool):
+    """Returns (dx [T, D] bf16, dw [D, W] fp32, db [D] fp32)."""
+    T, D = x.shape
+    W = weight.shape[1]
+    blocks = int(lib().ttb_causal_conv1d_row_blocks(C.c_longlong(T), C.c_int(D)))
+    dpre, dx = torch.empty_like(x), torch.empty_like(x)
+    part = torch.empty(blocks, (W + 1) * D, dtype=torch.float32, device=x.device)
+    dwdb = torch.empty(W + 1, D, dtype=torch.float32, device=x.device)
+    _check(lib().ttb_causal_conv1d_bwd(_p(dy), _p(x), _p(weight), _p(bias), _p(seq_start), _p(seq_end), _p(dpre), _p(dx),
+                                       _p(part), _p(dwdb), C.c_longlong(T), C.c_int(D), C.c_int(W), C.c_int(int(silu)),
+                                       _stream()), "ttb_causal_conv1d_bwd")
+    # plane s holds the tap at distance s into the past = weight column W-1-s
+    dw = dwdb[:W].flip(0).t().contiguous()
+    return dx, dw, dwdb[W]
 
 
 # --------------------------------------------------------------------------------------

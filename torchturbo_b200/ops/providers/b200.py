@@ -230,6 +230,63 @@ class B200BiasAct(_B200Op):
         return BiasActFn.apply(x, bias, act, residual)
 
 
+# ------------------------------------------------------------------------------------------------
+# causal short convolution (GDN / KDA mixers)
+# ------------------------------------------------------------------------------------------------
+def _seq_bounds(cu_seqlens, T: int, device):
+    """int32 [T] first token and one-past-last token of every token's sequence (tokens past the last boundary form
+    a sequence of their own), built on the host from the packed-row boundaries and copied once."""
+    if cu_seqlens is None:
+        cu = torch.tensor([0, T], dtype=torch.int64)
+    else:
+        cu = (cu_seqlens if isinstance(cu_seqlens, torch.Tensor) else torch.tensor(cu_seqlens)).to("cpu", torch.int64)
+        if int(cu[-1]) < T:
+            cu = torch.cat((cu, torch.tensor([T])))
+    lens = cu[1:] - cu[:-1]
+    start = torch.repeat_interleave(cu[:-1], lens).to(torch.int32)
+    end = torch.repeat_interleave(cu[1:], lens).to(torch.int32)
+    both = torch.stack((start, end)).pin_memory().to(device, non_blocking=True)
+    return both[0], both[1]
+
+
+class CausalConv1dFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, seq_start, seq_end, silu):
+        y = K.causal_conv1d_fwd(x, weight, bias, seq_start, silu)
+        ctx.save_for_backward(x, weight, bias, seq_start, seq_end)
+        ctx.silu = silu
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight, bias, seq_start, seq_end = ctx.saved_tensors
+        dx, dw, db = K.causal_conv1d_bwd(dy.contiguous(), x, weight, bias, seq_start, seq_end, ctx.silu)
+        return dx, dw.to(weight.dtype), (db.to(bias.dtype) if bias is not None else None), None, None, None
+
+
+@_custom("causal_conv1d", "b200_causal_conv1d")
+class B200CausalConv1d(_B200Op):
+    """Packed-row training path of the depthwise short convolution (one row, no carried state); decoding-style calls
+    with `initial_state` / `output_final_state` use the torch formulation."""
+
+    def __call__(self, x, weight, bias=None, *, activation=None, initial_state=None, output_final_state=False,
+                 cu_seqlens=None, packed_params=None):
+        from .native_linear_attention import TorchCausalConv1d
+
+        if packed_params is not None and cu_seqlens is None:
+            cu_seqlens = packed_params.cu_seqlens
+            packed_params = None
+        usable = (_ok(x, weight, bias) and x.dim() == 3 and x.shape[0] == 1 and x.shape[-1] % 8 == 0 and weight.shape[1] <= 8
+                  and initial_state is None and not output_final_state and activation in (None, "silu", "swish"))
+        if not usable:
+            return TorchCausalConv1d()(x, weight, bias, activation=activation, initial_state=initial_state,
+                                       output_final_state=output_final_state, cu_seqlens=cu_seqlens, packed_params=packed_params)
+        T = x.shape[1]
+        start, end = _seq_bounds(cu_seqlens, T, x.device)
+        y = CausalConv1dFn.apply(x[0].contiguous(), weight.contiguous(), bias, start, end, activation is not None)
+        return y.unsqueeze(0), None
+
+
 class SwiGLUFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, probs):
