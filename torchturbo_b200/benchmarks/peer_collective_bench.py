@@ -1,6 +1,6 @@
 """Bandwidth of the peer-memory FSDP collectives against NCCL on the same buffers.
 
-    torchrun --nproc-per-node N -m torchturbo_b200.benchmarks.peer_collective_bench [--mb 64 256 1024] [--grids 16 48 96]
+    torchrun --nproc-per-node N -m torchturbo_b200.benchmarks.peer_collective_bench [--mb 64 256 1024] [--grids 16 48 96] [--ep]
 
 For every size (MiB of the gathered / scattered buffer per rank) rank 0 prints the time (CUDA events, max over ranks,
 mean of `--iters` calls after warm-up) and the bytes this rank moves over NVLink divided by it:
@@ -37,6 +37,7 @@ def main(argv=None) -> None:
     ap.add_argument("--mb", type=int, nargs="+", default=[64, 256, 1024])
     ap.add_argument("--grids", type=int, nargs="+", default=[16, 48, 96])
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--ep", action="store_true", help="also time the expert-parallel row scatter / gather")
     args = ap.parse_args(argv)
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
@@ -80,8 +81,48 @@ def main(argv=None) -> None:
                       f"peer reduce-scatter(fp32) {t_rs:7.3f} ms {moved / t_rs / 1e6:7.1f} GB/s", flush=True)
     torch.cuda.synchronize()
     arena.check()
+    if args.ep:
+        _bench_ep(args, g, rank, world, dev)
     dist.barrier()
     dist.destroy_process_group()
+
+
+def _bench_ep(args, g, rank, world, dev) -> None:
+    """Expert-parallel row exchange at the 30B-A3B layer shape: 4096 tokens x top-8 of 128 experts, hidden 2048.
+    Scatter pushes every routed row into its owner's buffer, gather pulls the k expert outputs of every token back and
+    sums them; the bytes that cross NVLink are the rows whose expert lives on another rank."""
+    from .. import kernels as K
+    from ..comm import ep_p2p
+
+    T, H, E, k = 4096, 2048, 128, 8
+    torch.manual_seed(7 + rank)
+    x = torch.randn(T, H, device=dev).bfloat16()
+    idx = torch.stack([torch.randperm(E, device=dev)[:k] for _ in range(T)]).to(torch.int32)
+    prob = torch.rand(T, k, device=dev)
+    ws = ep_p2p.get_workspace(g, H, E, T, k, 2.0)
+    counts = torch.zeros(E, dtype=torch.int32, device=dev)
+    counts.scatter_add_(0, idx.reshape(-1).long(), torch.ones(T * k, dtype=torch.int32, device=dev))
+    seg_start, recv_counts, tile_group, dest_base = ws.exchange(counts)
+    expert = idx.reshape(-1).contiguous()
+    dest_row = K.perm_rank(expert, E, dest_base)
+    pflat = prob.reshape(-1).contiguous()
+    remote = int(((expert // (E // world)) != rank).sum().item())
+    nbytes = remote * H * 2
+
+    def scatter():
+        ws.scatter_rows(x, expert, dest_row, pflat, k)
+
+    def gather():
+        ws.publish_and_wait_ready()
+        ws.gather_rows(expert, dest_row, T, k)
+
+    t_s, t_g = _time(scatter, args.iters, g), _time(gather, args.iters, g)
+    torch.cuda.synchronize()
+    ws.check()
+    if rank == 0:
+        print(f"EP rows (T={T}, k={k}, E={E}, H={H}, {world} ranks): {remote} of {T * k} rows remote = {nbytes / 1e6:.1f} MB; "
+              f"scatter + landed-wait {t_s:.3f} ms {nbytes / t_s / 1e6:.1f} GB/s | ready-wait + gather-sum {t_g:.3f} ms "
+              f"{nbytes / t_g / 1e6:.1f} GB/s", flush=True)
 
 
 if __name__ == "__main__":
