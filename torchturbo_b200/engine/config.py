@@ -378,7 +378,7 @@ class FSDPConfig:
     # FSDP-managed parameters are at most `resident_fraction` of the device memory (never on CPU meshes)
     reshard_after_forward: Any = "auto"
     resident_fraction: float = 0.10
-    # consecutive decoder layers share one FSDP unit until it gathers this many bf16 bytes; "auto" = 64 MiB on
+    # consecutive decoder layers share one FSDP unit until it gathers this many bf16 bytes; "auto" = 256 MiB on
     # CUDA meshes and no merging on CPU meshes; 0 = one unit per layer
     unit_min_bytes: Any = "auto"
     # all-gather / reduce-scatter of FSDP units: "auto" (peer-memory NVLink kernels when every rank of the group
@@ -410,7 +410,7 @@ class FSDPConfig:
         if isinstance(self.unit_min_bytes, str) and self.unit_min_bytes.lower() == "auto":
             import torch
 
-            self.unit_min_bytes = (64 << 20) if torch.cuda.is_available() else 0
+            self.unit_min_bytes = (256 << 20) if torch.cuda.is_available() else 0
         self.unit_min_bytes = int(self.unit_min_bytes)
         self.resident_fraction = float(self.resident_fraction)
         if str(self.transport).lower() not in ("auto", "p2p", "nccl"):
