@@ -192,3 +192,31 @@ def test_dp_block_sampler():
     s = DPBlockDistributedSampler(list(range(5)), 2, 0, rank_block=2, shuffle=False, drop_last=False)
     assert len(list(s)) == 4 and s.total_size == 8                                # cycled to whole blocks
     s.set_epoch(1)
+
+
+def test_layer_norm_and_bias_act_torch_formulations():
+    """The torch (oracle) implementations of the vision-tower elementwise operators and their dispatch by name."""
+    import torch.nn.functional as F
+
+    from torchturbo_b200.ops import ops
+
+    torch.manual_seed(0)
+    x, w, b = torch.randn(5, 16), torch.randn(16), torch.randn(16)
+    assert torch.allclose(ops.layer_norm(x, w, b, 1e-6), F.layer_norm(x, (16,), w, b, 1e-6), atol=1e-6)
+    r = torch.randn(5, 16)
+    assert torch.allclose(ops.bias_act(x, b), x + b)
+    assert torch.allclose(ops.bias_act(x, b, "gelu_tanh"), F.gelu(x + b, approximate="tanh"), atol=1e-6)
+    assert torch.allclose(ops.bias_act(x, b, "gelu", residual=r), F.gelu(x + b) + r, atol=1e-6)
+    with pytest.raises(ValueError, match="unknown activation"):
+        ops.bias_act(x, b, "relu6")
+    h = ops.bias_act(x.bfloat16(), b.bfloat16(), "gelu_tanh")
+    assert h.dtype == torch.bfloat16
+
+
+def test_sequence_bounds_for_the_packed_convolution():
+    from torchturbo_b200.ops.providers.b200 import _seq_bounds
+
+    s, e = _seq_bounds(torch.tensor([0, 2, 5], dtype=torch.int32), 7, torch.device("cpu"))
+    assert s.tolist() == [0, 0, 2, 2, 2, 5, 5] and e.tolist() == [2, 2, 5, 5, 5, 7, 7]     # the padding tail is its own sequence
+    s, e = _seq_bounds(None, 3, torch.device("cpu"))
+    assert s.tolist() == [0, 0, 0] and e.tolist() == [3, 3, 3]

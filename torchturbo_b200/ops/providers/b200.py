@@ -245,7 +245,9 @@ def _seq_bounds(cu_seqlens, T: int, device):
     lens = cu[1:] - cu[:-1]
     start = torch.repeat_interleave(cu[:-1], lens).to(torch.int32)
     end = torch.repeat_interleave(cu[1:], lens).to(torch.int32)
-    both = torch.stack((start, end)).pin_memory().to(device, non_blocking=True)
+    both = torch.stack((start, end))
+    if torch.device(device).type == "cuda":
+        both = both.pin_memory().to(device, non_blocking=True)
     return both[0], both[1]
 
 
