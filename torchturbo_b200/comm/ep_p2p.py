@@ -181,18 +181,23 @@ class P2PTokenDispatcher:
             self._fallback = MoEAlltoAllTokenDispatcher(self.config, self.ep_group, self.num_local_experts)
         return self._fallback
 
-    def dispatch(self, x, idx, prob):
+    accepts_counts = True
+
+    def dispatch(self, x, idx, prob, counts=None):
+        """`counts` (int32 [E], the histogram of `idx`) is taken from the routing kernel when the caller has it."""
         if not (x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0):
             return self._nccl().dispatch(x, idx, prob)
         T, k = idx.shape
         E = self.config.num_moe_experts
         ws = get_workspace(self.ep_group, x.shape[-1], E, T, k, self.capacity_factor)
-        idx32 = idx.to(torch.int32).contiguous()
-        # histogram without the host sync torch.bincount makes on CUDA (it reads the maximum back)
-        counts = torch.zeros(E, dtype=torch.int32, device=x.device)
-        counts.scatter_add_(0, idx32.reshape(-1).long(), torch.ones(idx32.numel(), dtype=torch.int32, device=x.device))
+        idx32 = idx if idx.dtype == torch.int32 and idx.is_contiguous() else idx.to(torch.int32).contiguous()
+        if counts is None or counts.dtype != torch.int32 or counts.numel() != E:
+            # histogram without the host sync torch.bincount makes on CUDA (it reads the maximum back)
+            counts = torch.zeros(E, dtype=torch.int32, device=x.device)
+            counts.scatter_add_(0, idx32.reshape(-1).long(), torch.ones(idx32.numel(), dtype=torch.int32, device=x.device))
         xp, rp, seg_start, recv_counts, tile_group, dest_row, expert = _Dispatch.apply(
-            x.contiguous(), prob.float().contiguous(), idx32, counts, ws)
+            x.contiguous(), prob if prob.dtype == torch.float32 and prob.is_contiguous() else prob.float().contiguous(), idx32,
+            counts, ws)
         perm = MoEPermutation(tokens=xp, probs=rp, row_indices=dest_row.view(T, k), expert_indices=idx.long(),
                               counts=recv_counts, seg_start=seg_start, tile_group=tile_group,
                               out_buffer=ws.y_rows, grad_buffer=ws.y_rows)

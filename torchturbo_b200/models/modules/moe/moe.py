@@ -204,6 +204,8 @@ class TopKRouter(nn.Module):
         if self.expert_bias is not None and self.training and runtime.accumulate_tokens_per_expert:
             with torch.no_grad():
                 self.local_tokens_per_expert += stats["counts"].float()
+        # histogram of `idx` over the experts, as the routing kernel produced it: dispatchers reuse it
+        self.last_counts = stats.get("counts") if isinstance(stats, dict) else None
         return idx, prob, logits
 
     # -- rarely used routing variants stay in torch ---------------------------------------------------
@@ -442,7 +444,10 @@ class MoELayer(BaseMoELayer):
         if self.config.moe_apply_probs_on_input:
             xin = (x.float() * prob.view(-1, 1)).to(x.dtype)
             prob = torch.ones_like(prob)
-        perm, tpe, state = self.token_dispatcher.dispatch(xin, idx, prob)
+        if getattr(self.token_dispatcher, "accepts_counts", False):
+            perm, tpe, state = self.token_dispatcher.dispatch(xin, idx, prob, counts=getattr(self.router, "last_counts", None))
+        else:
+            perm, tpe, state = self.token_dispatcher.dispatch(xin, idx, prob)
         y = self.experts(perm, tpe)
         out = self.token_dispatcher.combine(y, state).to(x.dtype)
         if self.shared_experts is not None:
