@@ -611,12 +611,12 @@ class FSDP2Backend(BaseBackend):
         per-rank-average footing as the FSDP-averaged dense gradients."""
         if self.ep_size == 1:
             return
-        eids = self.expert_param_ids
         with torch.no_grad():
-            for p in model.parameters():
-                if id(p) in eids and p.grad is not None and not getattr(p, "_tt_grad_scaled", False):
-                    p.grad.mul_(self.gradient_scaling_factor)
-                    p._tt_grad_scaled = True
+            for m in self.expert_modules:
+                for p in m.parameters():
+                    if p.grad is not None and not getattr(p, "_tt_grad_scaled", False):
+                        p.grad.mul_(self.gradient_scaling_factor)
+                        p._tt_grad_scaled = True
 
     @torch.no_grad()
     def clip_grad_norm_(self, model: nn.Module, max_norm: float, optimizer=None) -> torch.Tensor:
@@ -628,6 +628,15 @@ class FSDP2Backend(BaseBackend):
 
         opts = list(optimizer) if isinstance(optimizer, OptimizersContainer) else ([optimizer] if optimizer is not None else [])
         dev = self.device
+        # the module tree is walked once: parameter objects and their optimizer membership do not change between steps
+        ckey = (id(model), tuple(id(o) for o in opts))
+        cache = getattr(self, "_clip_cache", None)
+        if cache is None or cache["key"] != ckey:
+            params = list(model.parameters())
+            fused = {id(p) for o in opts if isinstance(o, FusedAdamW) for grp in o.param_groups for p in grp["params"]}
+            cache = self._clip_cache = {"key": ckey, "params": params, "fused": fused,
+                                        "unfused": [p for p in params if id(p) not in fused]}
+        params = cache["params"]
         if self.ep_size > 1:
             # the fused optimizer of the expert parameters folds the 1/ep scaling into its gradient reads
             for o in opts:
@@ -648,8 +657,10 @@ class FSDP2Backend(BaseBackend):
                     sums[o._tt_topology] = sums[o._tt_topology] + s_
                     covered.update(id(p) for grp in o.param_groups for p in grp["params"])
         sq = {"dense": [], "moe": [], "local": []}
-        eids = self.expert_param_ids
-        for p in model.parameters():
+        eids = cache.get("eids")
+        if eids is None:
+            eids = cache["eids"] = self.expert_param_ids
+        for p in (params if not covered else (cache["unfused"] if covered >= cache["fused"] else params)):
             if id(p) in covered:
                 continue
             g = getattr(p, "main_grad", None)
@@ -673,20 +684,19 @@ class FSDP2Backend(BaseBackend):
             dist.all_reduce(sharded)
         total = (sharded + local).sqrt()
         coef = (max_norm / (total + 1e-6)).clamp(max=1.0) if max_norm and max_norm > 0 else torch.ones_like(total)
-        fused_ids: set[int] = set()
         for o in opts:
             if isinstance(o, FusedAdamW):
                 o.set_clip_coef(coef.reshape(1))
-                fused_ids.update(id(p) for grp in o.param_groups for p in grp["params"])
         rest = []
-        for p in model.parameters():
-            if id(p) not in fused_ids and p.grad is not None:
+        for p in cache["unfused"]:
+            if p.grad is not None:
                 rest.append(p.grad._local_tensor if hasattr(p.grad, "_local_tensor") else p.grad)
         if rest:
             torch._foreach_mul_(rest, coef)
-        for p in model.parameters():
-            if getattr(p, "_tt_grad_scaled", False):
-                p._tt_grad_scaled = False
+        if self.ep_size > 1:
+            for p in params:
+                if getattr(p, "_tt_grad_scaled", False):
+                    p._tt_grad_scaled = False
         return total
 
     # ------------------------------------------------------------------------------------------
