@@ -714,8 +714,16 @@ class FSDP2Backend(BaseBackend):
             out[k] = v
         return out
 
+    def _moe_layers(self, model: nn.Module) -> list:
+        """MoE layers of `model`, found once (the module tree does not change after preparation)."""
+        cached = getattr(model, "_tt_moe_layers", None)
+        if cached is None:
+            cached = [m for m in model.modules() if isinstance(m, BaseMoELayer)]
+            object.__setattr__(model, "_tt_moe_layers", cached)
+        return cached
+
     def _prepare_moe_runtime(self, model: nn.Module, inputs: dict[str, Any], aux_loss_scale: float) -> None:
-        layers = [m for m in model.modules() if isinstance(m, BaseMoELayer)]
+        layers = self._moe_layers(model)
         if not layers:
             return
         rt = model.get_moe_runtime_inputs(inputs, self.get_parallel_context())

@@ -23,11 +23,13 @@ class MetricTracker:
 
     def collect(self, model: torch.nn.Module) -> None:
         per_step: dict[str, list[torch.Tensor]] = defaultdict(list)
-        for m in model.modules():
-            pop = getattr(m, "pop_metrics", None)
-            if callable(pop):
-                for k, v in pop().items():
-                    per_step[k].append(v)
+        producers = getattr(model, "_tt_metric_modules", None)
+        if producers is None:   # the modules that can report metrics are found once per model
+            producers = [m for m in model.modules() if callable(getattr(m, "pop_metrics", None))]
+            object.__setattr__(model, "_tt_metric_modules", producers)
+        for m in producers:
+            for k, v in m.pop_metrics().items():
+                per_step[k].append(v)
         for k, vs in per_step.items():
             self.add(k, torch.stack([v.float() for v in vs]).mean())
 
