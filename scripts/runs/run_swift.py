@@ -13,11 +13,17 @@ def main():
     argv = sys.argv[2:] if len(sys.argv) > 1 and sys.argv[1] == stage else sys.argv[1:]
     tt_args, rest = parse_torchturbo_args(argv)
     set_torchturbo_args(tt_args)
-    torchturbo_b200.activate("msswift")
-    import swift.pipelines.train as train
+    adapter = torchturbo_b200.activate("msswift")
+    if adapter is None:            # TORCH_TURBO_DISABLE: stock swift
+        import importlib
 
-    cls = {"sft": "SwiftSft", "pt": "SwiftPretrain", "dpo": "SwiftRLHF"}[stage]
-    getattr(train, cls)(rest).main()
+        from torchturbo_b200.adapters.msswift import get_stage
+
+        spec = get_stage(stage)
+        return getattr(importlib.import_module(spec.pipeline_module), spec.main_attr)(rest)
+    # swift's own entry function of the stage (`sft_main`, `pretrain_main`, `rlhf_main`) now builds the engine-backed
+    # pipeline, because the adapter swapped the pipeline class in that module
+    return adapter.main(stage, rest)
 
 
 if __name__ == "__main__":
