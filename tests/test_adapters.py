@@ -80,3 +80,53 @@ def test_swift_args_force_engine_ownership():
     assert args.gradient_checkpointing is False and args.sequence_parallel_size == 1 and args.deepspeed is None and args.fsdp == ""
     assert cfg.parallel_plan.sp_size == 2 and cfg.moe.aux_loss_coeff == pytest.approx(0.01)
     assert cfg.activation_checkpointing.enabled is True
+
+
+def test_chat_formats_render_and_register_with_a_fake_llamafactory(monkeypatch):
+    import sys
+    import types
+
+    from torchturbo_b200.adapters import chat_templates as C
+
+    conv = [{"role": "system", "content": "S"}, {"role": "user", "content": "hi"}, {"role": "assistant", "content": "yo"},
+            {"role": "observation", "content": "42"}]
+    assert C.render(C.FORMATS["bailing_v3"], conv) == (
+        "<role>SYSTEM</role>\nS<|role_end|>\n\n<role>HUMAN</role>\nhi<|role_end|>\n\n<role>ASSISTANT</role>yo<|role_end|>\n\n"
+        "<role>OBSERVATION</role>\n\n```result\n42\n```\n<|role_end|>\n\n<role>ASSISTANT</role>")
+    assert C.render(C.FORMATS["deepseek_v4"], conv[1:3], bos="<B>") == "<B><｜User｜>hi<｜Assistant｜>yo<｜end▁of▁sentence｜>"
+    assert C.render(C.FORMATS["kimi_k25"], conv[1:2]).startswith("<|im_system|>system<|im_middle|>You are a helpful assistant<|im_end|>")
+    assert C.render(C.FORMATS["glm5"], conv[1:3]) == "[gMASK]<sop><|user|>\nhi<|assistant|>\nyo"
+    with pytest.raises(ValueError, match="no tool-result turn"):
+        C.render(C.FORMATS["qwen3_5_nothink"], conv)
+    assert set(C.MODEL_FORMATS.values()) <= set(C.FORMATS)
+    assert '"name": "f"' in C.ling_v3_tool_text([{"name": "f", "parameters": {}}]) and "<tools>" in C.ling_v3_tool_text([])
+
+    registered = {}
+
+    def mod(name, **attrs):
+        m = types.ModuleType(name)
+        m.__dict__.update(attrs)
+        m.__path__ = []
+        monkeypatch.setitem(sys.modules, name, m)
+        return m
+
+    class Fmt:
+        def __init__(self, slots=None, tool_format=None):
+            self.slots, self.tool_format = slots, tool_format
+
+    mod("llamafactory")
+    mod("llamafactory.data")
+    mod("llamafactory.data.formatter", EmptyFormatter=Fmt, FunctionFormatter=Fmt, StringFormatter=Fmt, ToolFormatter=Fmt)
+    mod("llamafactory.data.tool_utils", TOOLS={"qwen": object(), "glm4_moe": object()}, QwenToolUtils=object)
+    mod("llamafactory.data.mm_plugin", get_mm_plugin=lambda name, **kw: (name, kw))
+    mod("llamafactory.data.template", TEMPLATES=registered, ReasoningTemplate=type("ReasoningTemplate", (), {}),
+        register_template=lambda **kw: registered.__setitem__(kw["name"], kw))
+    done = C.register_lf_templates()
+    assert set(done) == set(C.FORMATS) and C.register_lf_templates() == []            # idempotent
+    b = registered["bailing_v3"]
+    assert b["format_user"].slots == ["<role>HUMAN</role>\n{{content}}<|role_end|>\n\n<role>ASSISTANT</role>"] and b["efficient_eos"]
+    assert b["format_tools"].tool_format == "ling_v3" and "ling_v3" in sys.modules["llamafactory.data.tool_utils"].TOOLS
+    d = registered["deepseek_v4_thinking"]
+    assert d["format_prefix"].slots == [{"bos_token"}] and d["template_class"].__name__ == "ReasoningTemplate"
+    assert "format_tools" not in d                                                    # its tool format is not known to this LF
+    assert registered["qwen3_5"]["mm_plugin"][0] == "qwen3_vl" and registered["kimi_k25"]["default_system"]

@@ -111,6 +111,12 @@ class RunExpPatch(_AttrPatch):
             if adapter.peft_config is not None:
                 raw = strip_lora_args(raw)
             adapter.stage = finetuning_args.stage
+            try:
+                from ..chat_templates import register_lf_templates
+
+                register_lf_templates()
+            except Exception as e:  # noqa: BLE001 - another template API: the user's --template must exist already
+                logger.warning_rank0("chat templates of the engine's model families were not registered: %s", e)
             adapter.apply_patches(adapter.engine)
             try:
                 return orig(raw, callbacks)
