@@ -679,3 +679,58 @@ def test_causal_conv1d(K, W, silu, with_bias):
     _close(w.grad, wf.grad, rtol=3e-2, atol=3e-2)
     if with_bias:
         _close(b.grad, bf.grad, rtol=3e-2, atol=3e-2)
+
+
+def test_ep_exchange_tables_for_eight_ranks_emulated(K, tmp_path):
+    """The count-exchange kernel as rank r of an 8-rank group on one GPU: the other ranks' counts and flags are put
+    in place by the host (all eight "peer" buffers are this GPU's buffer, so nothing waits), and the tables the kernel
+    derives from the 8 x 128 matrix are compared with a direct computation."""
+    import ctypes as C
+
+    import torch.distributed as dist
+
+    from torchturbo_b200.comm.symm import SymmetricBuffer
+
+    created = _single_rank_group(tmp_path)
+    try:
+        W, E = 8, 128
+        El = E // W
+        g = torch.Generator().manual_seed(5)
+        mat = torch.randint(0, 700, (W, E), generator=g, dtype=torch.int32)
+        mat[3, 17] = 0
+        mat[:, 40] = 0                                              # an expert nobody routes to
+        buf = SymmetricBuffer(4 * W * E + 4 * W + 1024, dist.group.WORLD)
+        off_counts, counts_all = buf.carve(4 * W * E, torch.int32)
+        off_flags, flags = buf.carve(4 * W, torch.int32)
+        ptrs = (C.c_ulonglong * W)(*([buf.peer_ptrs[0]] * W))
+        for rank in (0, 5, 7):
+            counts_all.copy_(mat.reshape(-1))
+            counts_all.view(W, E)[rank].zero_()                     # the kernel itself publishes this rank's row
+            flags.fill_(1)
+            status = torch.zeros(1, dtype=torch.int32, device="cuda")
+            cap_tiles = 4096
+            seg_start, recv_counts, tile_group, dest_base = K.ep_exchange(ptrs, off_counts, off_flags, mat[rank].cuda(), rank, W, E,
+                                                                          1, 50, cap_tiles, status)
+            torch.cuda.synchronize()
+            assert int(status.item()) == 0
+            assert torch.equal(counts_all.view(W, E).cpu(), mat)
+            tot = mat.sum(0)                                        # rows every expert receives
+            aligned = (tot + 127) // 128 * 128
+            for o in range(W):
+                seg_o = torch.cat((torch.zeros(1, dtype=torch.int64), aligned[o * El:(o + 1) * El].cumsum(0)))
+                before = mat[:rank, o * El:(o + 1) * El].sum(0)
+                assert torch.equal(dest_base[o * El:(o + 1) * El].cpu().long(), seg_o[:-1] + before), (rank, o)
+                if o == rank:
+                    assert torch.equal(seg_start.cpu().long(), seg_o)
+                    assert torch.equal(recv_counts.cpu(), tot[o * El:(o + 1) * El].to(torch.int32))
+                    tg = tile_group.cpu()
+                    for m in range(int(seg_o[-1]) // 128 + 2):
+                        row = m * 128
+                        want = -1
+                        if row < int(seg_o[-1]):
+                            want = int((seg_o[1:] > row).nonzero()[0])
+                        assert int(tg[m]) == want, (rank, m)
+        assert K.comm_status() == (0, 0)
+    finally:
+        if created:
+            dist.destroy_process_group()
