@@ -171,11 +171,10 @@ def gemm(
             K, M = a.shape
         else:
             M, K = a.shape
-        bm = b if b.dim() == 2 else b[0]
         if b_mn:
-            Kb, Nmem = bm.shape
+            Kb, Nmem = b.shape[-2], b.shape[-1]
         else:
-            Nmem, Kb = bm.shape
+            Nmem, Kb = b.shape[-2], b.shape[-1]
         assert Kb == K, (a.shape, b.shape, a_mn, b_mn)
         N = Nmem // 2 if swiglu else Nmem
     args.A, args.lda = a.data_ptr(), a.stride(0)
