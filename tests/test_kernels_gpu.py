@@ -734,3 +734,23 @@ def test_ep_exchange_tables_for_eight_ranks_emulated(K, tmp_path):
     finally:
         if created:
             dist.destroy_process_group()
+
+
+def test_fused_aux_loss_matches_the_torch_chain(K):
+    from torchturbo_b200.models.modules.moe.moe import _FusedAuxLoss
+
+    torch.manual_seed(0)
+    E, k, coeff = 128, 8, 1e-3
+    score = torch.rand(E, device="cuda").requires_grad_(True)
+    cnt = torch.randint(0, 400, (E,), device="cuda", dtype=torch.int32)
+    aux, unscaled = _FusedAuxLoss.apply(score, cnt, k, float(E * coeff), coeff)
+    (aux * 3.0).backward()
+    s2 = score.detach().clone().requires_grad_(True)
+    tpe = cnt.float()
+    n = (tpe.sum() / k).clamp(min=1.0)
+    ref = (s2 * tpe).sum() * (E * coeff) / (k * n * n)
+    (ref * 3.0).backward()
+    assert torch.allclose(aux, ref, rtol=1e-5, atol=1e-8) and torch.allclose(unscaled, ref / coeff, rtol=1e-5)
+    assert torch.allclose(score.grad, s2.grad, rtol=1e-5, atol=1e-10)
+    z, _ = _FusedAuxLoss.apply(score.detach(), torch.zeros_like(cnt), k, float(E * coeff), coeff)
+    assert float(z) == 0.0

@@ -484,6 +484,51 @@ __global__ void perm_combine_kernel(const __nv_bfloat16* __restrict__ src, long 
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------------------
+// Load-balance (auxiliary) loss of one router from the statistics the routing kernel already produced:
+//   aux = scale_num * sum_e score_sum[e] * cnt[e] / (k * n^2),   n = max(sum_e cnt[e] / k, 1)
+// out[0] = aux, out[1] = aux / coeff (the unscaled value for logging); coef[e] = d aux / d score_sum[e].
+// One block.  Replaces a chain of a dozen elementwise / reduction launches per MoE layer
+// (models/modules/moe/router.py:164-200 of the reference computes the same quantity with torch ops).
+// ------------------------------------------------------------------------------------------------------------
+__global__ void aux_loss_kernel(const float* __restrict__ score_sum, const int* __restrict__ cnt, int E, int k,
+                                float scale_num, float coeff, float* __restrict__ out, float* __restrict__ coef) {
+  __shared__ float red[32];
+  __shared__ float s_n, s_dot;
+  float c = 0.f, d = 0.f;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const float ce = static_cast<float>(cnt[e]);
+    c += ce;
+    d += score_sum[e] * ce;
+  }
+  c = warp_sum(c);
+  d = warp_sum(d);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (l == 0) red[w] = c;
+  __syncthreads();
+  if (w == 0) {
+    float t = l < nw ? red[l] : 0.f;
+    t = warp_sum(t);
+    if (l == 0) s_n = fmaxf(t / static_cast<float>(k), 1.f);
+  }
+  __syncthreads();
+  if (l == 0) red[w] = d;
+  __syncthreads();
+  if (w == 0) {
+    float t = l < nw ? red[l] : 0.f;
+    t = warp_sum(t);
+    if (l == 0) s_dot = t;
+  }
+  __syncthreads();
+  const float f = scale_num / (static_cast<float>(k) * s_n * s_n);
+  if (threadIdx.x == 0) {
+    out[0] = s_dot * f;
+    out[1] = coeff != 0.f ? s_dot * f / coeff : 0.f;
+  }
+  for (int e = threadIdx.x; e < E; e += blockDim.x) coef[e] = static_cast<float>(cnt[e]) * f;
+}
+
 }  // namespace ttb
 
 using namespace ttb;
@@ -555,6 +600,13 @@ TTB_EXPORT int ttb_perm_combine(const void* src, long long lds, const int* row_o
   perm_combine_kernel<<<(unsigned)T, threads, 0, STREAM(stream)>>>((const __nv_bfloat16*)src, lds, row_of, w,
                                                                   (const __nv_bfloat16*)residual, ldr,
                                                                   (__nv_bfloat16*)out, ldo, k, H);
+  LAUNCH_RET();
+}
+
+TTB_EXPORT int ttb_aux_loss(const float* score_sum, const int* cnt, int E, int k, float scale_num, float coeff, float* out2,
+                            float* coef, void* stream) {
+  if (E < 1 || k < 1) return 901;
+  aux_loss_kernel<<<1, 256, 0, STREAM(stream)>>>(score_sum, cnt, E, k, scale_num, coeff, out2, coef);
   LAUNCH_RET();
 }
 

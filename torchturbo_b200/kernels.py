@@ -516,6 +516,16 @@ def router_bwd(logits, topk_idx, topk_prob, k, score_fn, *, dprob=None, aux_grad
     return dlogits
 
 
+def aux_loss(score_sum: torch.Tensor, counts: torch.Tensor, k: int, scale_num: float, coeff: float):
+    """Load-balance loss from the routing kernel's statistics.  Returns (out [2] = (aux, aux / coeff), d aux / d score_sum [E])."""
+    E = score_sum.numel()
+    out = torch.empty(2, dtype=torch.float32, device=score_sum.device)
+    coef = torch.empty(E, dtype=torch.float32, device=score_sum.device)
+    _check(lib().ttb_aux_loss(_p(score_sum), _p(counts), C.c_int(E), C.c_int(k), C.c_float(scale_num), C.c_float(coeff),
+                              _p(out), _p(coef), _stream()), "ttb_aux_loss")
+    return out, coef
+
+
 def perm_index(topk_idx: torch.Tensor, num_experts: int, m_tiles_cap: int | None = None):
     """Padded (expert, token) permutation of the [T, k] expert ids.
 

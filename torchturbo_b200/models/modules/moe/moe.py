@@ -93,6 +93,31 @@ class MoERuntimeInputs:
 # --------------------------------------------------------------------------------------------------
 # loss helpers
 # --------------------------------------------------------------------------------------------------
+def _fused_aux_usable(stats) -> bool:
+    s, c = stats.get("score_sum"), stats.get("aux_counts")
+    if s is None or c is None or not (s.is_cuda and s.dtype == torch.float32 and c.dtype == torch.int32):
+        return False
+    from .... import kernels as K
+
+    return K.available()
+
+
+class _FusedAuxLoss(torch.autograd.Function):
+    """aux = E * coeff * sum_e score_sum[e] * cnt[e] / (k * n^2) with n = max(sum cnt / k, 1); gradient flows to
+    `score_sum` only (the counts are integers)."""
+
+    @staticmethod
+    def forward(ctx, score_sum, counts, k, scale_num, coeff):
+        from .... import kernels as K
+
+        out, coef = K.aux_loss(score_sum.contiguous(), counts.contiguous(), int(k), scale_num, coeff)
+        ctx.save_for_backward(coef)
+        return out[0], out[1]
+
+    @staticmethod
+    def backward(ctx, g, _g_unscaled):
+        (coef,) = ctx.saved_tensors
+        return coef * g, None, None, None, None
 class MoEAuxLossAutoScaler(torch.autograd.Function):
     """Identity on `output` that makes `aux_loss` part of the graph: backward feeds `loss_scale` into the
     aux loss so it trains the router without changing the reported LM loss."""
@@ -190,7 +215,14 @@ class TopKRouter(nn.Module):
             prob = MoEAuxLossAutoScaler.apply(prob, z * runtime.aux_loss_scale)
             self._record("z_loss", z / cfg.moe_z_loss_coeff)
             self._record("z_loss_scaled", z)
-        if cfg.moe_aux_loss_coeff > 0 and self.training:
+        if cfg.moe_aux_loss_coeff > 0 and self.training and sp == 1 and _fused_aux_usable(stats):
+            # one kernel for the loss and its gradient coefficients instead of a dozen small launches each way
+            aux, aux_unscaled = _FusedAuxLoss.apply(stats["score_sum"], stats["aux_counts"], cfg.moe_router_topk,
+                                                    float(E * cfg.moe_aux_loss_coeff), float(cfg.moe_aux_loss_coeff))
+            prob = MoEAuxLossAutoScaler.apply(prob, aux * runtime.aux_loss_scale)
+            self._record("aux_loss", aux_unscaled)
+            self._record("aux_loss_scaled", aux)
+        elif cfg.moe_aux_loss_coeff > 0 and self.training:
             tokens_per_expert = stats["aux_counts"].float()
             if sp > 1:
                 tokens_per_expert = tokens_per_expert.clone()
