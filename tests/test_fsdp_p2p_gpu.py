@@ -26,6 +26,8 @@ def _train(transport, steps=4):
         "backend_config": {"transport": transport, "unit_min_bytes": 0, "reshard_after_forward": True}}))
     model = eng.build_model(None, load_weights=False, init_kwargs={"config": dict(DENSE), "seed": 0})
     opt = eng.prepare_optimizer(model, OptimizerClassPlan(torch.optim.AdamW, lr=1e-3, weight_decay=0.0))
+    seen = []
+    model.register_forward_pre_hook(lambda m, a, kw: seen.append(kw["cu_seq_lens_q"].device.type), with_kwargs=True)
     ds = SyntheticPackedDataset(2 * steps, 512, DENSE["vocab_size"], num_docs=3, seed=5)
     dp = eng.get_dp_info()
     out = []
@@ -33,6 +35,8 @@ def _train(transport, steps=4):
         b = PackedCollator()([ds[i * dp["dp_size"] + dp["dp_rank"]]])
         loss, gn = train_step(eng, model, opt, [b])
         out.append((float(loss), float(gn)))
+    # the packed-row boundaries reach the model as host tensors: FSDP's input mover did not copy them to the GPU
+    assert seen and set(seen) == {"cpu"}, seen
     return out, eng
 
 

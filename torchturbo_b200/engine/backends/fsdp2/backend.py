@@ -68,6 +68,15 @@ def confidence_entropy_sum(logits: torch.Tensor, labels: torch.Tensor, ignore_in
 
 
 
+class _HostInput:
+    """A host tensor in transit through FSDP's input mover (which only moves what it recognises as a tensor)."""
+
+    __slots__ = ("tensor",)
+
+    def __init__(self, tensor: torch.Tensor):
+        self.tensor = tensor
+
+
 @register_backend("fsdp2")
 class FSDP2Backend(BaseBackend):
     def __init__(self, config: EngineConfig, runtime) -> None:
@@ -296,6 +305,31 @@ class FSDP2Backend(BaseBackend):
                 m._tt_unit = "local"
                 self.local_units.append(m)
 
+    def _keep_host_inputs_on_host(self, model: nn.Module) -> None:
+        """FSDP's root pre-forward hook moves every tensor argument to the GPU with a blocking copy.  The packed-row
+        boundaries (`cu_seq_lens_*`) are host tensors on purpose (tile tables and loop bounds are derived from them
+        on the host); moved to the GPU they cost one blocking copy per forward and then one device-to-host read per
+        attention layer, which serialises host and device.  A hook in front of FSDP's wraps host tensors in a plain
+        object FSDP does not recognise, a hook behind it unwraps them."""
+        if getattr(model, "_tt_unit", None) != "fsdp" or getattr(model, "_tt_host_input_hooks", False):
+            return
+
+        def box(_m, args, kwargs):
+            if not any(isinstance(v, torch.Tensor) and v.device.type == "cpu" for v in list(args) + list(kwargs.values())):
+                return None
+            wrap = lambda v: _HostInput(v) if isinstance(v, torch.Tensor) and v.device.type == "cpu" else v   # noqa: E731
+            return tuple(wrap(a) for a in args), {k: wrap(v) for k, v in kwargs.items()}
+
+        def unbox(_m, args, kwargs):
+            if not any(isinstance(v, _HostInput) for v in list(args) + list(kwargs.values())):
+                return None
+            un = lambda v: v.tensor if isinstance(v, _HostInput) else v   # noqa: E731
+            return tuple(un(a) for a in args), {k: un(v) for k, v in kwargs.items()}
+
+        model.register_forward_pre_hook(unbox, with_kwargs=True)                 # after FSDP's (prepended) hook
+        model.register_forward_pre_hook(box, prepend=True, with_kwargs=True)     # before it
+        model._tt_host_input_hooks = True
+
     def _unit_param_bytes(self, module: nn.Module) -> int:
         """bf16 bytes one all-gather of `module` as a unit of its own would deliver: parameters that are not
         replicated and not owned by a nested unit."""
@@ -382,6 +416,7 @@ class FSDP2Backend(BaseBackend):
         if head is not None and not tied:
             self._make_unit(head, None, reshard=False)
         self._make_unit(model, None, reshard=False)
+        self._keep_host_inputs_on_host(model)
         n_fsdp, n_local = len(self.fsdp_units), len(self.local_units)
         logger.info_rank0("sharding: %d FSDP unit(s), %d single-rank unit(s), %d replicated parameter(s)", n_fsdp,
                           n_local, len(self.no_shard_params))
