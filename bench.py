@@ -131,7 +131,8 @@ def run_ours(args) -> dict:
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
-    layers = args.layers or min(48, 12 * world)
+    named_layers = {"qwen3_moe_30b_a3b": 48, "qwen3_8b": 36, "qwen3_14b": 40}.get(args.model, 4)
+    layers = args.layers or min(named_layers, 12 * world)
     is_moe = args.model not in ("qwen3_8b", "qwen3_14b")
     sp = max(args.sp, 1)
     cfg = EngineConfig.from_dict({
@@ -220,15 +221,15 @@ def run_ours(args) -> dict:
         "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (seeded random token ids, random-init weights)", "impl": "ours",
         "config": {"model": "Qwen3-30B-A3B" if args.model == "qwen3_moe_30b_a3b" else args.model, "layers": layers,
-                   "layers_named": 48, "global_batch": world // sp, "seq_len": args.seq_len,
+                   "layers_named": named_layers, "global_batch": world // sp, "seq_len": args.seq_len,
                    "parallelism": f"fsdp2 dp{world // sp} + ep{world if is_moe else 1}" + (f" + ulysses sp{sp}" if sp > 1 else ""),
                    "sp_transport": os.environ.get("TORCHTURBO_ULYSSES_TRANSPORT", "auto") if sp > 1 else "none", "optimizer": "AdamW fp32 master",
                    "ep_transport": ep_transport,
                    "fsdp_transport": "p2p" if getattr(engine.backend, "peer_arenas", None) else ("nccl" if world > 1 else "local"),
                    "fsdp_units": len(engine.backend.fsdp_units),
-                   "reshard_after_forward": engine.backend.fsdp_config.reshard_after_forward, "depth_rule": "layers = min(48, 12 * n_gpus): the deepest stack whose "
-                   "weights + fp32 AdamW state fit 180 GB per GPU without activation checkpointing; 48 (the named "
-                   "model) at 8 GPUs", "tokens_per_s_scaled_to_48_layers": value * layers / 48.0,
+                   "reshard_after_forward": engine.backend.fsdp_config.reshard_after_forward, "depth_rule": f"layers = min({named_layers}, 12 * n_gpus): the deepest stack whose "
+                   "weights + fp32 AdamW state fit 180 GB per GPU without activation checkpointing; the named "
+                   "depth from 4 GPUs on", "tokens_per_s_scaled_to_named_layers": value * layers / float(named_layers),
                    "l2": "per-step working set (weights, optimizer state, activations: tens of GB) is far larger than the 126 MB L2"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "loss": float(last),
         "kernel_status": list(st), "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30,
