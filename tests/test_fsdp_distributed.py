@@ -94,7 +94,7 @@ def test_ulysses_sp2_matches_sp1():
     assert torch.allclose(a[:, 1], b[:, 1], rtol=1e-3, atol=1e-4), (a, b)
 
 
-def _w_merged(rank, world, unit_bytes, ac, reshard):
+def _w_merged(rank, world, unit_bytes, ac, reshard, ep=1):
     from torchturbo_b200.data import PackedCollator, SyntheticPackedDataset
     from torchturbo_b200.engine import EngineConfig, TorchTurboEngine
     from torchturbo_b200.engine.optimizers import OptimizerClassPlan
@@ -102,7 +102,7 @@ def _w_merged(rank, world, unit_bytes, ac, reshard):
 
     mc = dict(MOE, num_hidden_layers=4)
     eng = TorchTurboEngine(EngineConfig.from_dict({
-        "mixed_precision": "fp32", "parallel_plan": {"sp_size": 1, "ep_size": 1}, "moe": {"aux_loss_coeff": 1e-2},
+        "mixed_precision": "fp32", "parallel_plan": {"sp_size": 1, "ep_size": ep}, "moe": {"aux_loss_coeff": 1e-2},
         "activation_checkpointing": {"enabled": ac},
         "backend_config": {"unit_min_bytes": unit_bytes, "reshard_after_forward": reshard}}))
     model = eng.build_model(None, load_weights=False, init_kwargs={"config": mc, "seed": 0})
@@ -119,7 +119,7 @@ def _w_merged(rank, world, unit_bytes, ac, reshard):
         loss, gn = train_step(eng, model, opt, [PackedCollator()([ds[i]])])
         out.append((float(loss), float(gn)))
     if rank == 0:
-        torch.save(torch.tensor(out), f"/tmp/tt_merged_{unit_bytes}_{int(ac)}_{int(reshard)}.pt")
+        torch.save(torch.tensor(out), f"/tmp/tt_merged_{unit_bytes}_{int(ac)}_{int(reshard)}_ep{ep}_w{world}.pt")
 
 
 @pytest.mark.parametrize("ac,reshard", [(False, True), (True, True), (True, False)])
@@ -129,6 +129,17 @@ def test_merged_fsdp_units_match_per_layer_units(ac, reshard):
     # one tiny MoE layer without its experts is ~26 KB of bf16-equivalent bytes: 50 KB merges two layers
     run_distributed(_w_merged, 2, 0, ac, True)
     run_distributed(_w_merged, 2, 50_000, ac, reshard)
-    a = torch.load(f"/tmp/tt_merged_0_{int(ac)}_1.pt")
-    b = torch.load(f"/tmp/tt_merged_50000_{int(ac)}_{int(reshard)}.pt")
+    a = torch.load(f"/tmp/tt_merged_0_{int(ac)}_1_ep1_w2.pt")
+    b = torch.load(f"/tmp/tt_merged_50000_{int(ac)}_{int(reshard)}_ep1_w2.pt")
+    assert torch.allclose(a, b, rtol=1e-5, atol=1e-6), (a, b)
+
+
+def test_merged_units_with_expert_units_sharded_over_edp():
+    """4 ranks, EP=2: expert containers are FSDP units of their own on the 2-rank `edp` mesh, nested inside decoder
+    layers that are merged pairwise on the world mesh; with recomputation the explicit prefetch lists (layers + the
+    experts of the next merged unit) must still give the per-layer result."""
+    run_distributed(_w_merged, 4, 0, True, True, 2)
+    run_distributed(_w_merged, 4, 50_000, True, True, 2)
+    a = torch.load("/tmp/tt_merged_0_1_1_ep2_w4.pt")
+    b = torch.load("/tmp/tt_merged_50000_1_1_ep2_w4.pt")
     assert torch.allclose(a, b, rtol=1e-5, atol=1e-6), (a, b)
