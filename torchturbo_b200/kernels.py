@@ -612,7 +612,7 @@ def attn_fwd(q, k, v, q_tiles_dev, *, scale: float, causal: bool = True, want_ls
     T, Hq, D = q.shape
     Hk = k.shape[1]
     assert q.stride(2) == 1 and q.stride(1) == D and k.stride(1) == D and v.stride(1) == D and v.stride(2) == 1
-    out = torch.zeros_like(q) if True else None
+    out = torch.zeros_like(q)  # rows past the last sequence boundary are never written by the kernel and must read as zero
     lse = torch.full((Hq, T), float("-inf"), dtype=torch.float32, device=q.device) if want_lse else None
     ml = torch.full((Hq,), float("-inf"), dtype=torch.float32, device=q.device) if want_max_logit else None
     _check(lib().ttb_attn_fwd(_p(q), C.c_longlong(q.stride(0)), _p(k), C.c_longlong(k.stride(0)), _p(v),
