@@ -243,6 +243,15 @@ def run_ours(args) -> dict:
 
 def main():
     args = parse()
+    # stdout carries the one JSON result line: the package's log lines go to stderr
+    import logging
+
+    from torchturbo_b200.logging import logging_configure
+
+    logging_configure()
+    for h in logging.getLogger("torchturbo_b200").handlers:
+        if hasattr(h, "setStream"):
+            h.setStream(sys.stderr)
     if args.impl == "reference":
         from baseline.run_reference import run_reference
 
