@@ -129,4 +129,5 @@ class OpDispatcher:
             return self._dispatch(name, *args, impl=impl, **kwargs)
 
         facade.__name__ = name
+        self.__dict__[name] = facade   # later `ops.<name>` lookups skip __getattr__ (selection still happens per call)
         return facade
