@@ -80,6 +80,23 @@ class EPWorkspace:
     def gather_vals(self, expert, dest_row):
         return K.ep_gather_vals(self.ptrs, self.off_y_vals, expert, dest_row, self.El, self.W, self.cap, self.status)
 
+    # -- one host call per direction (same kernels as the primitives above) ----------------------------
+    def dispatch_all(self, src, expert, vals, k, counts=None, tables=None):
+        """Forward dispatch (`counts` given) or the row scatter of combine's backward (`tables` given)."""
+        return K.ep_dispatch_all(
+            self.ptrs, off_counts=self.off_counts, off_flags_counts=self.ch_counts.offset, off_rows=self.off_recv,
+            off_vals=self.off_recv_vals, off_flags_rows=self.ch_rows.offset, counts=counts, expert=expert, src=src, val=vals,
+            recv_rows_local=self.recv_rows, recv_vals_local=self.recv_vals if vals is not None else None, rank=self.rank,
+            world=self.W, num_experts=self.E, k=k, m_tiles_cap=self.m_tiles_cap, cap_rows=self.cap,
+            epoch_counts=self.ch_counts.next() if tables is None else 0, epoch_rows=self.ch_rows.next(),
+            budget_ms=self.budget_ms, done_counter=self.done, status=self.status, tables=tables)
+
+    def combine_all(self, expert, dest_row, T, k, residual=None, want_vals=False):
+        return K.ep_combine_all(self.ptrs, off_rows=self.off_y, off_vals=self.off_y_vals, off_flags=self.ch_ready.offset,
+                                expert=expert, dest_row=dest_row, T=T, k=k, H=self.H, El=self.El, rank=self.rank, world=self.W,
+                                epoch=self.ch_ready.next(), budget_ms=self.budget_ms, cap_rows=self.cap, status=self.status,
+                                residual=residual, want_vals=want_vals)
+
     def check(self) -> None:
         code = int(self.status.item())
         if code:
@@ -108,11 +125,8 @@ class _Dispatch(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, prob, idx, counts, ws: EPWorkspace):
         T, k = idx.shape
-        seg_start, recv_counts, tile_group, dest_base = ws.exchange(counts)
         expert = idx.reshape(-1).contiguous()
-        dest_row = K.perm_rank(expert, ws.E, dest_base)
-        K.perm_zero_pad(ws.recv_rows, recv_counts, seg_start, ws.recv_vals)
-        ws.scatter_rows(x, expert, dest_row, prob.reshape(-1).contiguous(), k)
+        seg_start, recv_counts, tile_group, dest_row = ws.dispatch_all(x, expert, prob.reshape(-1).contiguous(), k, counts=counts)
         xp, rp = ws.recv_rows.clone(), ws.recv_vals.clone()
         ctx.ws, ctx.dims = ws, (T, k)
         ctx.save_for_backward(expert, dest_row)
@@ -130,10 +144,8 @@ class _Dispatch(torch.autograd.Function):
             ws.y_vals.copy_(drp)
         else:
             ws.y_vals.zero_()
-        ws.publish_and_wait_ready()
-        dx = ws.gather_rows(expert, dest_row, T, k)
-        dprob = ws.gather_vals(expert, dest_row).view(T, k)
-        return dx, dprob, None, None, None
+        dx, dprob = ws.combine_all(expert, dest_row, T, k, want_vals=True)
+        return dx, dprob.view(T, k), None, None, None
 
 
 class _Combine(torch.autograd.Function):
@@ -141,8 +153,7 @@ class _Combine(torch.autograd.Function):
     def forward(ctx, y, expert, dest_row, seg_start, recv_counts, ws: EPWorkspace, T, k, residual):
         if y.data_ptr() != ws.y_rows.data_ptr():     # the expert MLP normally writes y straight into the buffer
             ws.y_rows.copy_(y)
-        ws.publish_and_wait_ready()
-        out = ws.gather_rows(expert, dest_row, T, k, residual=residual)
+        out, _ = ws.combine_all(expert, dest_row, T, k, residual=residual)
         ctx.ws, ctx.dims = ws, (T, k, residual is not None)
         ctx.save_for_backward(expert, dest_row, seg_start, recv_counts)
         return out
@@ -152,8 +163,7 @@ class _Combine(torch.autograd.Function):
         ws, (T, k, has_res) = ctx.ws, ctx.dims
         expert, dest_row, seg_start, recv_counts = ctx.saved_tensors
         dout = dout.contiguous()
-        K.perm_zero_pad(ws.recv_rows, recv_counts, seg_start, None)
-        ws.scatter_rows(dout, expert, dest_row, None, k)
+        ws.dispatch_all(dout, expert, None, k, tables=(seg_start, recv_counts, dest_row))
         # no copy: the expert backward that consumes d(y) runs before this rank raises the next "ready" flag, and no
         # peer writes these rows again before it has seen that flag (it first gathers its d(x) of this layer)
         dy = ws.recv_rows.detach()

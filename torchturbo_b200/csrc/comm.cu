@@ -763,3 +763,68 @@ TTB_EXPORT int ttb_peer_collective(const unsigned long long* peer_ptrs, long lon
     peer_reduce_scatter_kernel<true><<<grid, 512, 0, STREAM(stream)>>>(p);
   LAUNCH_RET();
 }
+
+// ------------------------------------------------------------------------------------------------------------
+// One host call per direction of an expert-parallel layer.  The kernels are the ones above (and the permutation
+// helpers of moe.cu); launching them from one entry point only removes host work: the Python side of a 48-layer step
+// made ~1000 separate calls for these sequences and the step is host-bound from two GPUs on.
+// ------------------------------------------------------------------------------------------------------------
+extern "C" int ttb_perm_rank(const int* idx, long long N, int E, const int* base, int* row_of, void* stream);
+extern "C" int ttb_perm_zero_pad(void* dst, long long ldd, const int* counts, const int* seg_start, float* row_val, int E,
+                                 int H, void* stream);
+
+struct EpDispatchArgs {
+  const unsigned long long* peer_ptrs;
+  long long off_counts, off_flags_counts, off_rows, off_vals, off_flags_rows;
+  const int* counts;       // [E] this rank's routing histogram
+  const int* expert;       // [N] expert of every (token, slot) entry
+  const void* src;         // [T, H] bf16 rows
+  long long lds;
+  const float* val;        // [N] routing weights or null
+  void* recv_rows_local;   // this rank's receive buffer (for zeroing the padding rows)
+  float* recv_vals_local;
+  int* seg_start; int* recv_counts; int* tile_group; int* dest_base; int* dest_row;   // outputs
+  unsigned int* done_counter;
+  int* status;
+  long long N, cap_rows, budget_ms;
+  int rank, W, E, k, H, m_tiles_cap, epoch_counts, epoch_rows, grid, exchange;   // exchange = 0: tables are given
+};
+
+// forward dispatch (exchange = 1): counts exchange -> destination rows -> zero the padding -> scatter -> landed wait.
+// backward of combine (exchange = 0): zero the padding -> scatter -> landed wait, with the forward's tables.
+TTB_EXPORT int ttb_ep_dispatch_all(const EpDispatchArgs* a, void* stream) {
+  int r;
+  const int El = a->E / a->W;
+  if (a->exchange) {
+    r = ttb_ep_exchange(a->peer_ptrs, a->off_counts, a->off_flags_counts, a->counts, a->rank, a->W, a->E, a->epoch_counts,
+                        a->budget_ms, a->m_tiles_cap, a->seg_start, a->recv_counts, a->tile_group, a->dest_base, a->status,
+                        stream);
+    if (r) return r;
+    r = ttb_perm_rank(a->expert, a->N, a->E, a->dest_base, a->dest_row, stream);
+    if (r) return r;
+  }
+  r = ttb_perm_zero_pad(a->recv_rows_local, a->H, a->recv_counts, a->seg_start, a->recv_vals_local, El, a->H, stream);
+  if (r) return r;
+  r = ttb_ep_scatter(a->peer_ptrs, a->off_rows, a->off_vals, a->off_flags_rows, a->src, a->lds, a->expert, a->dest_row, a->val,
+                     a->N, a->k, a->H, El, a->rank, a->W, a->epoch_rows, a->cap_rows, a->done_counter, a->status, a->grid,
+                     stream);
+  if (r) return r;
+  return ttb_flag_wait(a->peer_ptrs, a->off_flags_rows, a->rank, a->W, a->epoch_rows, a->budget_ms, a->status, stream);
+}
+
+// publish "my output rows are ready" -> wait for every owner -> pull and sum the k rows of every token
+// (+ optionally the per-entry scalars, for the routing-weight gradient).
+TTB_EXPORT int ttb_ep_combine_all(const unsigned long long* peer_ptrs, long long off_rows, long long off_vals,
+                                  long long off_flags, const int* expert, const int* dest_row, const void* residual,
+                                  long long ldr, void* out, long long ldo, float* vals_out, long long T, int k, int H,
+                                  int El, int rank, int W, int epoch, long long budget_ms, long long cap_rows, int* status,
+                                  void* stream) {
+  int r = ttb_flag_signal(peer_ptrs, off_flags, rank, W, epoch, stream);
+  if (r) return r;
+  r = ttb_flag_wait(peer_ptrs, off_flags, rank, W, epoch, budget_ms, status, stream);
+  if (r) return r;
+  r = ttb_ep_gather(peer_ptrs, off_rows, expert, dest_row, nullptr, residual, ldr, out, ldo, T, k, H, El, W, cap_rows, status,
+                    stream);
+  if (r || vals_out == nullptr) return r;
+  return ttb_ep_gather_vals(peer_ptrs, off_vals, expert, dest_row, vals_out, T * k, El, W, cap_rows, status, stream);
+}

@@ -74,7 +74,8 @@ def lib():
 
 # kernels launched per C entry point (used to report how many of this library's kernels ran in a region)
 _LAUNCHES_PER_CALL = {"ttb_rmsnorm_bwd": 2, "ttb_layernorm_bwd": 2, "ttb_bias_act_bwd": 2, "ttb_causal_conv1d_bwd": 3,
-                      "ttb_causal_conv1d_row_blocks": 0, "ttb_router_fwd": 2, "ttb_perm_index": 3, "ttb_perm_scatter": 2,
+                      "ttb_causal_conv1d_row_blocks": 0, "ttb_ep_dispatch_all": 5, "ttb_ep_dispatch_rows": 3,
+                      "ttb_ep_combine_all": 3, "ttb_ep_combine_vals": 4, "ttb_router_fwd": 2, "ttb_perm_index": 3, "ttb_perm_scatter": 2,
                       "ttb_gemm_status": 0}
 LAUNCH_COUNT = 0
 
@@ -657,6 +658,76 @@ def ep_exchange(peer_ptrs, off_counts, off_flags, counts, rank, world, num_exper
                                  C.c_int(m_tiles_cap), _p(seg_start), _p(recv_counts), _p(tile_group), _p(dest_base),
                                  _p(status), _stream()), "ttb_ep_exchange")
     return seg_start, recv_counts, tile_group, dest_base
+
+
+class _EpDispatchArgs(C.Structure):
+    _fields_ = [
+        ("peer_ptrs", C.c_void_p),
+        ("off_counts", C.c_longlong), ("off_flags_counts", C.c_longlong), ("off_rows", C.c_longlong),
+        ("off_vals", C.c_longlong), ("off_flags_rows", C.c_longlong),
+        ("counts", C.c_void_p), ("expert", C.c_void_p), ("src", C.c_void_p), ("lds", C.c_longlong), ("val", C.c_void_p),
+        ("recv_rows_local", C.c_void_p), ("recv_vals_local", C.c_void_p),
+        ("seg_start", C.c_void_p), ("recv_counts", C.c_void_p), ("tile_group", C.c_void_p), ("dest_base", C.c_void_p),
+        ("dest_row", C.c_void_p), ("done_counter", C.c_void_p), ("status", C.c_void_p),
+        ("N", C.c_longlong), ("cap_rows", C.c_longlong), ("budget_ms", C.c_longlong),
+        ("rank", C.c_int), ("W", C.c_int), ("E", C.c_int), ("k", C.c_int), ("H", C.c_int), ("m_tiles_cap", C.c_int),
+        ("epoch_counts", C.c_int), ("epoch_rows", C.c_int), ("grid", C.c_int), ("exchange", C.c_int),
+    ]
+
+
+def ep_dispatch_all(peer_ptrs, *, off_counts, off_flags_counts, off_rows, off_vals, off_flags_rows, counts, expert, src, val,
+                    recv_rows_local, recv_vals_local, rank, world, num_experts, k, m_tiles_cap, cap_rows, epoch_counts,
+                    epoch_rows, budget_ms, done_counter, status, tables=None):
+    """Expert-parallel row dispatch in one host call.  With `tables=None`: counts exchange, destination rows, padding
+    zeroed, scatter, landed wait; returns (seg_start, recv_counts, tile_group, dest_row).  With `tables = (seg_start,
+    recv_counts, dest_row)` (backward of combine) only the last three stages run."""
+    dev = src.device
+    N = expert.numel()
+    El = num_experts // world
+    a = _EpDispatchArgs()
+    if tables is None:
+        seg_start = torch.empty(El + 1, dtype=torch.int32, device=dev)
+        recv_counts = torch.empty(El, dtype=torch.int32, device=dev)
+        tile_group = torch.empty(m_tiles_cap, dtype=torch.int32, device=dev)
+        dest_base = torch.empty(num_experts, dtype=torch.int32, device=dev)
+        dest_row = torch.empty_like(expert)
+        a.exchange, a.counts = 1, counts.data_ptr()
+        a.tile_group, a.dest_base = tile_group.data_ptr(), dest_base.data_ptr()
+    else:
+        seg_start, recv_counts, dest_row = tables
+        tile_group = None
+        a.exchange = 0
+    a.peer_ptrs = C.addressof(peer_ptrs)
+    a.off_counts, a.off_flags_counts, a.off_rows = off_counts, off_flags_counts, off_rows
+    a.off_vals, a.off_flags_rows = off_vals, off_flags_rows
+    a.expert, a.src, a.lds = expert.data_ptr(), src.data_ptr(), src.stride(0)
+    a.val = val.data_ptr() if val is not None else None
+    a.recv_rows_local = recv_rows_local.data_ptr()
+    a.recv_vals_local = recv_vals_local.data_ptr() if recv_vals_local is not None else None
+    a.seg_start, a.recv_counts, a.dest_row = seg_start.data_ptr(), recv_counts.data_ptr(), dest_row.data_ptr()
+    a.done_counter, a.status = done_counter.data_ptr(), status.data_ptr()
+    a.N, a.cap_rows, a.budget_ms = N, cap_rows, budget_ms
+    a.rank, a.W, a.E, a.k, a.H, a.m_tiles_cap = rank, world, num_experts, k, src.shape[1], m_tiles_cap
+    a.epoch_counts, a.epoch_rows = epoch_counts, epoch_rows
+    a.grid = max(1, min((N + 7) // 8, 8 * num_sms(dev.index)))
+    _check(lib().ttb_ep_dispatch_all(C.byref(a), _stream()), "ttb_ep_dispatch_all" if tables is None else "ttb_ep_dispatch_rows")
+    return seg_start, recv_counts, tile_group, dest_row
+
+
+def ep_combine_all(peer_ptrs, *, off_rows, off_vals, off_flags, expert, dest_row, T, k, H, El, rank, world, epoch, budget_ms,
+                   cap_rows, status, residual=None, want_vals=False):
+    """Ready signal, ready wait and the k-way gather (optionally also the per-entry scalars) in one host call."""
+    dev = expert.device
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    vals = torch.empty(T * k, dtype=torch.float32, device=dev) if want_vals else None
+    _check(lib().ttb_ep_combine_all(peer_ptrs, C.c_longlong(off_rows), C.c_longlong(off_vals), C.c_longlong(off_flags),
+                                    _p(expert), _p(dest_row), _p(residual),
+                                    C.c_longlong(residual.stride(0) if residual is not None else 0), _p(out),
+                                    C.c_longlong(out.stride(0)), _p(vals), C.c_longlong(T), C.c_int(k), C.c_int(H),
+                                    C.c_int(El), C.c_int(rank), C.c_int(world), C.c_int(epoch), C.c_longlong(budget_ms),
+                                    C.c_longlong(cap_rows), _p(status), _stream()),
+           "ttb_ep_combine_vals" if want_vals else "ttb_ep_combine_all")
+    return out, vals
 
 
 def ep_scatter(peer_ptrs, off_rows, off_vals, off_flags, src, expert, dest_row, val, k, El, rank, world, epoch, cap_rows,
