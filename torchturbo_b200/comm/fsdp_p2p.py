@@ -89,6 +89,9 @@ class PeerCollectiveArena:
         slot.epoch = slot.ready.next()
         slot.consumed.epoch = slot.epoch
         K.flag_signal(self.buf.peer_ptrs, slot.ready.offset, self.rank, self.W, slot.epoch)
+        # the wait for the peers runs as a one-CTA kernel of its own: a peer can be milliseconds behind, and the ~100
+        # CTAs of the copy kernel must not sit on the SMs spinning (and crowding out compute) for that long
+        K.flag_wait(self.buf.peer_ptrs, slot.ready.offset, self.rank, self.W, slot.epoch, self.budget_ms, self.status)
         K.peer_collective(self.buf.peer_ptrs, slot.offset, slot.ready.offset, slot.consumed.offset, units, self.rank,
                           self.W, slot.epoch, self.budget_ms, self.done_ag if kind == 0 else self.done_rs, self.status,
                           kind=kind, out=out, scale=scale, grid=self.grid)
