@@ -130,3 +130,33 @@ def test_chat_formats_render_and_register_with_a_fake_llamafactory(monkeypatch):
     assert d["format_prefix"].slots == [{"bos_token"}] and d["template_class"].__name__ == "ReasoningTemplate"
     assert "format_tools" not in d                                                    # its tool format is not known to this LF
     assert registered["qwen3_5"]["mm_plugin"][0] == "qwen3_vl" and registered["kimi_k25"]["default_system"]
+
+
+def test_chat_formats_register_with_a_fake_swift(monkeypatch):
+    import sys
+    import types
+
+    from torchturbo_b200.adapters import chat_templates as C
+
+    metas = {}
+
+    class TemplateMeta:
+        def __init__(self, template_type, prefix, prompt, chat_sep, suffix=None, system_prefix=None, default_system=None, stop_words=None):
+            self.template_type, self.prefix, self.prompt, self.chat_sep = template_type, prefix, prompt, chat_sep
+            self.suffix, self.system_prefix, self.default_system, self.stop_words = suffix, system_prefix, default_system, stop_words
+
+    for name, attrs in (("swift", {}), ("swift.template", {"register_template": lambda m, exist_ok=False: metas.__setitem__(m.template_type, m)}),
+                        ("swift.template.template_meta", {"TemplateMeta": TemplateMeta})):
+        m = types.ModuleType(name)
+        m.__dict__.update(attrs)
+        m.__path__ = []
+        monkeypatch.setitem(sys.modules, name, m)
+    done = C.register_swift_templates(["bailing_v3", "kimi_k25", "glm5"])
+    assert done == ["turbo_bailing_v3", "turbo_kimi_k25", "turbo_glm5"]
+    b = metas["turbo_bailing_v3"]
+    assert b.prompt == ["<role>HUMAN</role>\n{{QUERY}}<|role_end|>\n\n<role>ASSISTANT</role>"] and b.chat_sep == ["<|role_end|>\n\n"]
+    assert b.system_prefix == ["<role>SYSTEM</role>\n{{SYSTEM}}<|role_end|>\n\n"] and b.suffix == ["<|role_end|>"] and b.stop_words == []
+    k = metas["turbo_kimi_k25"]
+    assert k.default_system == "You are a helpful assistant" and k.stop_words == ["<|im_end|>"]
+    g = metas["turbo_glm5"]
+    assert g.prefix == ["[gMASK]<sop>"] and g.system_prefix[0] == "[gMASK]<sop>" and g.chat_sep == ["\n"]
