@@ -118,7 +118,9 @@ def test_chat_formats_render_and_register_with_a_fake_llamafactory(monkeypatch):
     mod("llamafactory.data")
     mod("llamafactory.data.formatter", EmptyFormatter=Fmt, FunctionFormatter=Fmt, StringFormatter=Fmt, ToolFormatter=Fmt)
     mod("llamafactory.data.tool_utils", TOOLS={"qwen": object(), "glm4_moe": object()}, QwenToolUtils=object)
-    mod("llamafactory.data.mm_plugin", get_mm_plugin=lambda name, **kw: (name, kw))
+    plugins = {}
+    mod("llamafactory.data.mm_plugin", get_mm_plugin=lambda name, **kw: (name, kw), PLUGINS=plugins,
+        BasePlugin=type("BasePlugin", (), {}), register_mm_plugin=plugins.__setitem__)
     mod("llamafactory.data.template", TEMPLATES=registered, ReasoningTemplate=type("ReasoningTemplate", (), {}),
         register_template=lambda **kw: registered.__setitem__(kw["name"], kw))
     done = C.register_lf_templates()
@@ -130,6 +132,8 @@ def test_chat_formats_render_and_register_with_a_fake_llamafactory(monkeypatch):
     assert d["format_prefix"].slots == [{"bos_token"}] and d["template_class"].__name__ == "ReasoningTemplate"
     assert "format_tools" not in d                                                    # its tool format is not known to this LF
     assert registered["qwen3_5"]["mm_plugin"][0] == "qwen3_vl" and registered["kimi_k25"]["default_system"]
+    assert set(plugins) == {"kimi_k25", "bailing_vl"}                                 # plugin classes registered first
+    assert registered["bailing_v3_vl"]["mm_plugin"] == ("bailing_vl", {"image_token": "<|image_pad|>", "video_token": "<|video_pad|>"})
 
 
 def test_chat_formats_register_with_a_fake_swift(monkeypatch):

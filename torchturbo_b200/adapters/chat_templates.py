@@ -13,6 +13,7 @@ from dataclasses import dataclass, field
 from typing import Any
 
 from ..logging import get_logger
+from .mm_tokens import register_lf_mm_plugins
 
 logger = get_logger(__name__)
 
@@ -49,6 +50,9 @@ FORMATS: dict[str, ChatFormat] = {f.name: f for f in (
                system="<role>SYSTEM</role>\n{content}<|role_end|>\n\n",
                observation="<role>OBSERVATION</role>\n\n```result\n{content}\n```\n<|role_end|>\n\n<role>ASSISTANT</role>",
                stop_words=("",), efficient_eos=True, tool_format="ling_v3", swift_suffix=("<|role_end|>",)),
+    ChatFormat("bailing_v3_vl", user="<role>HUMAN</role>{content}<|role_end|><role>ASSISTANT</role>\n", assistant="{content}<|role_end|>",
+               system="<role>SYSTEM</role>{content}<|role_end|>", stop_words=("<|role_end|>",), thought_words=("<think>", "</think>"),
+               mm_plugin=("bailing_vl", {"image_token": "<|image_pad|>", "video_token": "<|video_pad|>"}), swift_suffix=("<|role_end|>",)),
     ChatFormat("kimi_k25", user="<|im_user|>user<|im_middle|>{content}<|im_end|><|im_assistant|>assistant<|im_middle|>",
                assistant="{content}<|im_end|>", system="<|im_system|>system<|im_middle|>{content}<|im_end|>",
                default_system="You are a helpful assistant", stop_words=("<|im_end|>",), replace_eos=True,
@@ -69,7 +73,7 @@ FORMATS: dict[str, ChatFormat] = {f.name: f for f in (
 
 # model_type -> default format
 MODEL_FORMATS = {"qwen3_5": "qwen3_5", "qwen3_5_moe": "qwen3_5", "qwen3_5_moe_text": "qwen3_5", "qwen4_exp": "qwen3_5",
-                 "bailing_hybrid": "bailing_v3", "bailing_moe_v3": "bailing_v3", "bailing_moe_v3_vl": "bailing_v3",
+                 "bailing_hybrid": "bailing_v3", "bailing_moe_v3": "bailing_v3", "bailing_moe_v3_vl": "bailing_v3_vl",
                  "kimi_k25": "kimi_k25", "deepseek_v4": "deepseek_v4", "glm_moe_dsa": "glm5", "llada2_moe": "bailing_v3"}
 
 LING_V3_TOOL_PROMPT = ("# Tools\nYou may call one or more functions to assist with the user query.\n"
@@ -127,6 +131,7 @@ def register_lf_templates(names: list[str] | None = None) -> list[str]:
     from llamafactory.data.formatter import EmptyFormatter, FunctionFormatter, StringFormatter, ToolFormatter
 
     done = []
+    register_lf_mm_plugins()      # the plugin names the formats below refer to
     tools = getattr(__import__("llamafactory.data.tool_utils", fromlist=["TOOLS"]), "TOOLS", None)
     if isinstance(tools, dict) and "ling_v3" not in tools:
         base = getattr(__import__("llamafactory.data.tool_utils", fromlist=["QwenToolUtils"]), "QwenToolUtils", None)
