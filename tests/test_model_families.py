@@ -147,3 +147,45 @@ def test_sparse_attention_ops():
     assert torch.equal(half, top[20:])
     o = ops.sparse_flash_mla(q, k[:, 0], None, None, None, torch.zeros(H), D ** -0.5, 1, 3, cu_seq_lens_q=cu)
     assert o.shape == (T, H, D) and torch.isfinite(o).all()
+
+
+def test_deepseek_v4_indexer_kl_loss_trains_the_indexer():
+    """Off by default: the indexer only selects (no gradient).  With `dsa_indexer_loss_coeff > 0` the KL term between
+    the main attention over the selected compressed rows and the indexer's softmax reaches the indexer's parameters
+    and nothing else changes in the reported loss."""
+    import torch.nn.functional as F
+
+    cls = get_model("deepseek_v4")
+    kw = dict(TEXT, moe_intermediate_size=16, num_hidden_layers=2, n_routed_experts=8, num_experts_per_tok=2, q_lora_rank=16,
+              qk_rope_head_dim=4, qk_nope_head_dim=12, o_groups=2, o_lora_rank=8, sliding_window=4, compress_ratios=[1, 4],
+              index_n_heads=2, index_head_dim=8, index_topk=2, hc_mult=2, hc_sinkhorn_iters=3)
+    b = _batch(False)
+    losses, grads = {}, {}
+    for coeff in (0.0, 0.5):
+        torch.manual_seed(0)
+        m = cls(cls.config_class(**kw, dsa_indexer_loss_coeff=coeff)).float().train()
+        loss = m(**b).logits.float().pow(2).mean()
+        loss.backward()
+        losses[coeff] = loss.item()
+        idx_params = {n: p for n, p in m.named_parameters() if ".indexer." in n}
+        assert idx_params
+        grads[coeff] = {n: (None if p.grad is None else p.grad.abs().sum().item()) for n, p in idx_params.items()}
+        attn = [mod for mod in m.modules() if getattr(mod, "indexer", None) is not None][0]
+        if coeff:
+            assert attn.last_indexer_loss is not None and attn.last_indexer_loss.item() >= 0
+        else:
+            assert attn.last_indexer_loss is None
+    assert losses[0.0] == pytest.approx(losses[0.5], rel=1e-6)          # the reported LM loss is unchanged
+    assert all(g in (None, 0.0) for g in grads[0.0].values())
+    assert any(g for g in grads[0.5].values() if g)
+
+    # the formula, against a direct restatement on small tensors
+    torch.manual_seed(1)
+    t = torch.rand(5, 3)
+    s = torch.randn(5, 3)
+    valid = torch.tensor([[1, 1, 0], [1, 0, 0], [0, 0, 0], [1, 1, 1], [1, 1, 1]], dtype=torch.bool)
+    p = torch.softmax(s.masked_fill(~valid, torch.finfo(torch.float32).min), -1).masked_fill(~valid, 0)
+    tt = F.normalize(t.masked_fill(~valid, 0), p=1, dim=-1)
+    want = F.kl_div((p + 1e-10).log(), tt, reduction="none").sum() / valid.any(-1).sum()
+    got = torch.where(tt > 0, tt * (tt.clamp_min(1e-30).log() - (p + 1e-10).log()), torch.zeros_like(tt)).sum() / valid.any(-1).sum()
+    assert torch.allclose(want, got, atol=1e-6)

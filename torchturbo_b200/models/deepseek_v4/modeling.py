@@ -37,6 +37,7 @@ from ..modules.attention.ulysses import all_gather_sp_with_grad_reduce
 from ..modules.hybrid import roll_left_in_sequences
 from ..modules.mixers import MixerContext
 from ..modules.moe import MoELayer, MoELayerConfig
+from ..modules.moe.moe import MoEAuxLossAutoScaler
 from ..modules.transformer import CausalLMOutput, DenseMLP, RMSNorm
 from ..qwen3.modeling import LMHead
 
@@ -51,7 +52,7 @@ class DeepseekV4Config(ModelConfig):
         compress_ratios=None, rope_theta=10000.0, compress_rope_theta=40000.0, index_n_heads=64, index_head_dim=128,
         index_topk=512, hc_mult=4, hc_sinkhorn_iters=20, hc_eps=1e-6, swiglu_limit=0.0, num_hash_layers=0,
         num_mtp_layers=0, rms_norm_eps=1e-6, tie_word_embeddings=False, initializer_range=0.02, pad_token_id=0,
-        torch_dtype="bfloat16", first_k_dense_replace=0, router_dtype="fp32",
+        torch_dtype="bfloat16", first_k_dense_replace=0, router_dtype="fp32", dsa_indexer_loss_coeff=0.0,
     )
 
     def __init__(self, **kw):
@@ -201,6 +202,13 @@ class Indexer(nn.Module):
         self.weights_proj = nn.Linear(config.hidden_size, self.n_heads, bias=False, dtype=dtype)
         self.compressor = Compressor(config, ratio, self.head_dim, dtype)
 
+    def _queries(self, x_full, qr_local, cos, sin, q_rows):
+        Tl = qr_local.shape[0]
+        q = ops.linear(qr_local, self.wq_b.weight).view(Tl, self.n_heads, self.head_dim)
+        q = rope_tail(q, cos, sin)
+        w = ops.linear(x_full[q_rows], self.weights_proj.weight).float() * (self.head_dim ** -0.5 * self.n_heads ** -0.5)
+        return q, w
+
     @torch.no_grad()
     def forward(self, x_full, qr_local, cos, sin, cu_seqlens, positions_full, q_rows):
         """Selected rows of the compressed stream per local query: [T_local, topk] (-1 padded), or None."""
@@ -208,16 +216,36 @@ class Indexer(nn.Module):
         if comp is None:
             return None
         k, ends, seq_of = comp
-        Tl = qr_local.shape[0]
-        q = ops.linear(qr_local, self.wq_b.weight).view(Tl, self.n_heads, self.head_dim)
-        q = rope_tail(q, cos, sin)
-        w = ops.linear(x_full[q_rows], self.weights_proj.weight).float() * (self.head_dim ** -0.5 * self.n_heads ** -0.5)
+        q, w = self._queries(x_full, qr_local, cos, sin, q_rows)
         sc = (torch.relu(torch.einsum("thd,cd->thc", q.float(), k.float())) * w.unsqueeze(-1)).sum(1)     # [Tl, Tc]
         visible = visible_compressed(q_rows, ends, seq_of, cu_seqlens, x_full.shape[0])
         sc = sc.masked_fill(~visible, float("-inf"))
         kk = min(self.topk, sc.shape[1])
         val, idx = sc.topk(kk, dim=-1)
         return idx.masked_fill(~torch.isfinite(val), -1).to(torch.int32)
+
+    def kl_loss(self, x_full, qr_local, cos, sin, cu_seqlens, positions_full, q_rows, sel, q_main, ckv_main, scale):
+        """Trains the indexer towards the main attention: KL(target || indexer) over the selected rows, where the
+        target is the main attention's softmax over the visible compressed rows summed over heads, taken at the
+        selected rows and normalised to 1, and the indexer side is the softmax of its scores over the same rows.
+        Averaged over the queries that selected anything.  The target carries no gradient; the indexer's inputs are
+        detached by the caller, so only indexer parameters (its compressor included) receive gradient.
+        (DSAIndexerLoss / LiLoss, models/deepseek_v4/modeling_deepseek_v4.py:250-381 in the reference.)"""
+        k, ends, seq_of = self.compressor(x_full, cu_seqlens, positions_full)
+        valid = sel >= 0
+        safe = sel.clamp_min(0).long()
+        q, w = self._queries(x_full, qr_local, cos, sin, q_rows)
+        s = (torch.relu(torch.einsum("thd,tkd->thk", q.float(), k.float()[safe])) * w.unsqueeze(-1)).sum(1)   # [Tl, K]
+        p = torch.softmax(s.masked_fill(~valid, torch.finfo(torch.float32).min), dim=-1).masked_fill(~valid, 0.0)
+        with torch.no_grad():
+            visible = visible_compressed(q_rows, ends, seq_of, cu_seqlens, x_full.shape[0])
+            a = torch.einsum("thd,cd->thc", q_main.float(), ckv_main.float()) * scale
+            a = a.masked_fill(~visible[:, None, :], torch.finfo(torch.float32).min)
+            a = torch.softmax(a, dim=-1).masked_fill(~visible[:, None, :], 0.0).sum(1)                       # [Tl, Tc]
+            t = a.gather(1, safe).masked_fill(~valid, 0.0)
+            t = t / t.sum(-1, keepdim=True).clamp_min(1e-12)
+        kl = torch.where(t > 0, t * (t.clamp_min(1e-30).log() - (p + 1e-10).log()), torch.zeros_like(t)).sum()
+        return kl / valid.any(-1).sum().clamp_min(1)
 
 
 def visible_compressed(q_rows, ends, seq_of, cu_seqlens, T):
@@ -252,6 +280,8 @@ class DeepseekV4Attention(nn.Module):
         self.indexer = Indexer(c, self.ratio, dtype) if self.ratio == 4 else None
         self.theta = c.compress_rope_theta if self.ratio > 1 else c.rope_theta
         self.scale = self.head_dim ** -0.5
+        self.indexer_loss_coeff = float(getattr(c, "dsa_indexer_loss_coeff", 0.0) or 0.0)
+        self.last_indexer_loss: torch.Tensor | None = None
 
     def forward(self, x, ctx: MixerContext):
         """x [T_local, H].  Under sequence parallelism the shared key/value stream and the layer input (for the
@@ -275,12 +305,17 @@ class DeepseekV4Attention(nn.Module):
         T = kv.shape[0]
         idx = window_indices(T, self.window, ctx.cu_seqlens, x.device)[q_rows]
         keys = kv
+        index_loss = None
         if self.compressor is not None:
             comp = self.compressor(x_full, ctx.cu_seqlens, pos_full)
             if comp is not None:
                 ckv, ends, seq_of = comp
                 if self.indexer is not None:
                     sel = self.indexer(x_full.detach(), qr.detach(), cos, sin, ctx.cu_seqlens, pos_full, q_rows)
+                    if sel is not None and self.training and self.indexer_loss_coeff > 0 and torch.is_grad_enabled():
+                        index_loss = self.indexer.kl_loss(x_full.detach(), qr.detach(), cos, sin, ctx.cu_seqlens, pos_full,
+                                                          q_rows, sel, q.detach(), ckv.detach(), self.scale)
+                        self.last_indexer_loss = index_loss.detach()
                 else:
                     vis = visible_compressed(q_rows, ends, seq_of, ctx.cu_seqlens, T)
                     ar = torch.arange(ckv.shape[0], device=x.device, dtype=torch.int32)
@@ -294,7 +329,10 @@ class DeepseekV4Attention(nn.Module):
         o = o.reshape(Tl, self.n_groups, -1)
         wa = self.wo_a.weight.view(self.n_groups, self.o_rank, -1)
         o = torch.einsum("tgd,grd->tgr", o, wa.to(o.dtype))
-        return ops.linear(o.reshape(Tl, -1), self.wo_b.weight)
+        out = ops.linear(o.reshape(Tl, -1), self.wo_b.weight)
+        if index_loss is not None:
+            out = MoEAuxLossAutoScaler.apply(out, index_loss * self.indexer_loss_coeff)
+        return out
 
 
 # --------------------------------------------------------------------------------------------------
