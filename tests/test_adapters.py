@@ -164,3 +164,54 @@ def test_chat_formats_register_with_a_fake_swift(monkeypatch):
     assert k.default_system == "You are a helpful assistant" and k.stop_words == ["<|im_end|>"]
     g = metas["turbo_glm5"]
     assert g.prefix == ["[gMASK]<sop>"] and g.system_prefix[0] == "[gMASK]<sop>" and g.chat_sep == ["\n"]
+
+
+def test_ling_vl_tool_serialisers():
+    from torchturbo_b200.adapters import chat_templates as C
+
+    t = C.ling_vl_tool_call_text([{"name": "get", "arguments": {"city": "Paris", "days": 3}}, '{"name": "f", "arguments": {}}'])
+    assert t == ("<tool_call>get\n<arg_key>city</arg_key>\n<arg_value>Paris</arg_value>\n<arg_key>days</arg_key>\n"
+                 "<arg_value>3</arg_value>\n</tool_call>\n<tool_call>f\n</tool_call>")
+    with pytest.raises(ValueError):
+        C.ling_vl_tool_call_text([{"name": " ", "arguments": {}}])
+    with pytest.raises(ValueError):
+        C.ling_vl_tool_call_text([{"name": "f", "arguments": [1]}])
+    o = C.ling_vl_observation_text(["a", "b"])
+    assert o == "<role>OBSERVATION</role>\n<tool_response>\na\n</tool_response>\n<tool_response>\nb\n</tool_response>"
+    with pytest.raises(ValueError):
+        C.ling_vl_observation_text([])
+
+
+def test_swift_template_wrap_keeps_input_ids_and_merges_mrope(monkeypatch):
+    import sys
+    import types
+
+    from torchturbo_b200.adapters import chat_templates as C
+
+    class Native:
+        def pre_forward_hook(self, model, args, kwargs):
+            kwargs = dict(kwargs)
+            kwargs.pop("input_ids")                      # what swift does once vision is folded into the embeddings
+            kwargs["inputs_embeds"] = "E"
+            return args, kwargs
+
+    K = C.keep_inputs_template(Native)
+    assert C.keep_inputs_template(K) is K
+    ids = torch.arange(6).view(1, 6)
+    pos = torch.arange(18).view(3, 1, 6)
+    _, kw = K().pre_forward_hook(None, (), {"input_ids": ids, "position_ids": pos, "text_position_ids": torch.arange(6).view(1, 6)})
+    assert kw["input_ids"] is ids and kw["inputs_embeds"] == "E" and "text_position_ids" not in kw
+    assert kw["position_ids"].shape == (4, 1, 6) and torch.equal(kw["position_ids"][0, 0], torch.arange(6))
+    plain = {"position_ids": torch.arange(6).view(1, 6)}
+    assert C.merge_mrope_rows(dict(plain))["position_ids"].shape == (1, 6)
+
+    mapping = {"qwen3_5": types.SimpleNamespace(template_cls=Native, template_type="qwen3_5")}
+    reg = types.ModuleType("swift.template.register")
+    reg.TEMPLATE_MAPPING = mapping
+    reg.register_template = lambda meta, exist_ok=False: mapping.__setitem__(meta.template_type, meta)
+    for name, mod in (("swift", types.ModuleType("swift")), ("swift.template", types.ModuleType("swift.template")),
+                      ("swift.template.register", reg)):
+        monkeypatch.setitem(sys.modules, name, mod)
+    assert C.wrap_swift_native_templates(("qwen3_5", "unknown")) == ["qwen3_5"]
+    assert mapping["qwen3_5"].template_cls._tt_keeps_inputs
+    assert C.wrap_swift_native_templates(("qwen3_5",)) == []       # already wrapped

@@ -94,6 +94,35 @@ def ling_v3_tool_text(tools: list[dict[str, Any]]) -> str:
     return LING_V3_TOOL_PROMPT.format(tool_text=lines)
 
 
+def ling_vl_tool_call_text(calls: list[dict[str, Any]]) -> str:
+    """Tool calls the way the Bailing VL checkpoints render them: `<tool_call>name`, one `<arg_key>` / `<arg_value>`
+    pair per argument (non-string values as JSON), `</tool_call>`; calls separated by a newline.  Each call is a
+    dict with `name` and `arguments` (or a JSON string of such a dict).
+    (BailingVLAgentTemplate._format_tool_calls, models/bailing_moe_v3_vl/swift_template.py:60-80 in the reference.)"""
+    out = []
+    for call in calls:
+        if isinstance(call, str):
+            call = json.loads(call)
+        name, args = call.get("name"), call.get("arguments")
+        if isinstance(args, str):
+            args = json.loads(args)
+        if not isinstance(name, str) or not name.strip() or not isinstance(args, dict):
+            raise ValueError("a tool call needs a non-empty name and an arguments object")
+        lines = [f"<tool_call>{name}"]
+        for k, v in args.items():
+            lines += [f"<arg_key>{k}</arg_key>", f"<arg_value>{v if isinstance(v, str) else json.dumps(v, ensure_ascii=False)}</arg_value>"]
+        lines.append("</tool_call>")
+        out.append("\n".join(lines))
+    return "\n".join(out)
+
+
+def ling_vl_observation_text(results: list[str]) -> str:
+    """A group of consecutive tool results as one OBSERVATION turn body (without the closing role marker)."""
+    if not results:
+        raise ValueError("an observation turn needs at least one tool result")
+    return "<role>OBSERVATION</role>" + "".join(f"\n<tool_response>\n{r}\n</tool_response>" for r in results)
+
+
 def render(fmt: ChatFormat, messages: list[dict[str, str]], *, bos: str = "", add_generation_prompt: bool = False) -> str:
     """Plain-text rendering of a conversation (used by tests and by dataset plugins that tokenise offline).  The user
     wrapper opens the assistant turn, so a trailing user message already ends with the generation prompt."""
@@ -191,4 +220,58 @@ def register_swift_templates(names: list[str] | None = None) -> list[str]:
         except TypeError:
             register_template(meta)
         done.append(meta.template_type if hasattr(meta, "template_type") else f"turbo_{name}")
+    return done
+
+
+# ---- ms-swift: keep what the models need across swift's own pre-forward step -----------------------------------------
+def merge_mrope_rows(inputs: dict[str, Any]) -> dict[str, Any]:
+    """swift delivers the text positions `[B, S]` and the three mRoPE rows `[3, B, S]` separately; the hybrid models
+    take one `[4, B, S]` tensor (text row first).  In place; other layouts pass through."""
+    tpos, pos = inputs.get("text_position_ids"), inputs.get("position_ids")
+    if tpos is not None and pos is not None and pos.dim() == 3 and pos.shape[0] == 3:
+        import torch
+
+        inputs["position_ids"] = torch.cat((tpos.reshape(1, *pos.shape[1:]), pos), dim=0)
+        inputs.pop("text_position_ids", None)
+    return inputs
+
+
+def keep_inputs_template(template_cls: type, keep: tuple[str, ...] = ("input_ids",)) -> type:
+    """Subclass of a swift template class whose `pre_forward_hook` puts back the keyword arguments swift drops when
+    it folds the vision features into `inputs_embeds` (the multi-token-prediction heads embed the shifted token ids
+    themselves), then merges the mRoPE rows.  Wrapping twice returns the class unchanged.
+    (models/qwen3_5/swift_template.py:33-52 in the reference.)"""
+    if getattr(template_cls, "_tt_keeps_inputs", False):
+        return template_cls
+
+    class KeepInputs(template_cls):  # type: ignore[misc, valid-type]
+        _tt_keeps_inputs = True
+
+        def pre_forward_hook(self, model, args, kwargs):
+            saved = {k: kwargs[k] for k in keep if k in kwargs}
+            args, kwargs = super().pre_forward_hook(model, args, kwargs)
+            for k, v in saved.items():
+                kwargs.setdefault(k, v)
+            return args, merge_mrope_rows(kwargs)
+
+    KeepInputs.__name__ = f"{template_cls.__name__}KeepInputs"
+    return KeepInputs
+
+
+def wrap_swift_native_templates(names: tuple[str, ...] = ("qwen3_5",)) -> list[str]:
+    """Re-register swift's own templates of the families the models of this package replace, with
+    `keep_inputs_template` around their class.  Names swift does not know are skipped."""
+    from copy import deepcopy
+
+    from swift.template.register import TEMPLATE_MAPPING, register_template
+
+    done = []
+    for name in names:
+        native = TEMPLATE_MAPPING.get(name)
+        if native is None or getattr(native.template_cls, "_tt_keeps_inputs", False):
+            continue
+        meta = deepcopy(native)
+        meta.template_cls = keep_inputs_template(native.template_cls)
+        register_template(meta, exist_ok=True)
+        done.append(name)
     return done

@@ -45,9 +45,10 @@ def register_models_to_swift() -> list[str]:
             except Exception:  # noqa: BLE001 - a template that cannot register must not stop the job
                 logger.warning_rank0("swift template of %s failed to register", name)
     try:
-        from ..chat_templates import register_swift_templates
+        from ..chat_templates import register_swift_templates, wrap_swift_native_templates
 
         register_swift_templates()
+        wrap_swift_native_templates()
     except Exception as e:  # noqa: BLE001 - another template API: the user's --template must exist already
         logger.warning_rank0("chat templates of the engine's model families were not registered: %s", e)
     logger.info_rank0("registered %d engine model types in swift", len(done))
