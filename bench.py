@@ -10,9 +10,17 @@ and synchronize on both sides, max over ranks); `e2e` repeats the measurement th
 per-step host-to-device copy of the batch from pinned memory and the device-to-host read of the loss inside the timed
 region.  Synthetic data (seeded random token ids, documents of 256..4096 tokens packed to 4096 per rank), random-init
 weights, bf16 compute with fp32 master weights and optimizer state, AdamW, global-norm clipping, aux loss 1e-3.
+After the W warm-up steps both arms keep warming up (each extra step timed on its own) until two consecutive steps
+differ by less than 3 % or 12 extra steps have run; `warmup_used` reports the total.
 
 Depth: the named model has 48 layers; its fp32 master + AdamW state (16 bytes per parameter) only fits when the
 experts are spread over 4 or more GPUs, so `layers = min(48, 12 * N)`; the depth used is reported in `config`.
+Because that changes the work per GPU between N = 1, 2 and 4, the line also carries `fixed_depth`: the same
+measurement at 12 layers for every N, which is the series to read scaling from.
+
+With 8 GPUs the line also carries `secondary`: the other named 8-GPU configurations (Qwen3-14B shape, Ulysses sp = 8,
+one 65536-token row per group; Qwen3-8B shape, FSDP over 8, 8192-token rows), each measured the same way in fresh
+processes that rank 0 starts after the headline run has released the GPUs (`--extras none|fixed|all` overrides).
 """
 from __future__ import annotations
 
@@ -37,7 +45,7 @@ def parse():
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--layers", type=int, default=0, help="0 = min(48, 12 * gpus)")
     p.add_argument("--seq-len", type=int, default=4096)
-    p.add_argument("--model", default="qwen3_moe_30b_a3b", choices=["qwen3_moe_30b_a3b", "qwen3_8b", "qwen3_14b", "tiny_moe"])
+    p.add_argument("--model", default="qwen3_moe_30b_a3b", choices=["qwen3_moe_30b_a3b", "qwen3_8b", "qwen3_14b", "tiny_moe", "tiny_dense"])
     p.add_argument("--sp", type=int, default=1, help="Ulysses sequence-parallel size (a sequence of --seq-len tokens per SP group)")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--fsdp-transport", default="auto", choices=["auto", "nccl", "p2p"],
@@ -46,6 +54,12 @@ def parse():
                    "this many MiB of bf16 parameters (-1: engine default, 0: one unit per layer)")
     p.add_argument("--ep-transport", default="auto", choices=["auto", "nccl", "p2p"],
                    help="expert-parallel token exchange: NVLink peer-memory kernels (p2p) or NCCL all-to-all")
+    p.add_argument("--extras", default="auto", choices=["auto", "none", "fixed", "all"],
+                   help="records attached to the headline line: fixed-depth (12-layer) run, secondary named configs "
+                        "(auto: fixed-depth from 2 GPUs on, secondaries at 8 GPUs)")
+    p.add_argument("--extras-budget-s", type=float, default=600.0, help="wall-clock budget of the whole call; an extra "
+                   "record is only started while enough of it is left")
+    p.add_argument("--child", action="store_true", help=argparse.SUPPRESS)   # a sub-measurement started by rank 0
     return p.parse_args()
 
 
@@ -63,6 +77,10 @@ def model_config(name: str, layers: int) -> dict:
         return dict(model_type="qwen3", vocab_size=151936, hidden_size=4096, intermediate_size=12288,
                     num_hidden_layers=layers, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
                     rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False)
+    if name == "tiny_dense":
+        return dict(model_type="qwen3", vocab_size=32000, hidden_size=512, intermediate_size=1024, num_hidden_layers=layers,
+                    num_attention_heads=8, num_key_value_heads=2, head_dim=128, rope_theta=1e6, rms_norm_eps=1e-6,
+                    tie_word_embeddings=False)
     return dict(model_type="qwen3_moe", vocab_size=32000, hidden_size=512, intermediate_size=1024,
                 num_hidden_layers=layers, num_attention_heads=8, num_key_value_heads=2, head_dim=128, num_experts=16,
                 num_experts_per_tok=4, moe_intermediate_size=256, norm_topk_prob=True)
@@ -133,7 +151,7 @@ def run_ours(args) -> dict:
     torch.cuda.set_device(local_rank)
     named_layers = {"qwen3_moe_30b_a3b": 48, "qwen3_8b": 36, "qwen3_14b": 40}.get(args.model, 4)
     layers = args.layers or min(named_layers, 12 * world)
-    is_moe = args.model not in ("qwen3_8b", "qwen3_14b")
+    is_moe = args.model not in ("qwen3_8b", "qwen3_14b", "tiny_dense")
     sp = max(args.sp, 1)
     cfg = EngineConfig.from_dict({
         "mixed_precision": "bf16",
@@ -150,7 +168,7 @@ def run_ours(args) -> dict:
     model = engine.build_model(None, load_weights=False, init_kwargs={"config": mc, "seed": 0})
     optim = engine.prepare_optimizer(model, OptimizerClassPlan(torch.optim.AdamW, lr=1e-5, weight_decay=0.01,
                                                                betas=(0.9, 0.95)))
-    n_batches = args.warmup + 2 * args.steps
+    n_batches = max(args.warmup, 1) + 2 * args.steps
     ds = SyntheticPackedDataset(n_batches * world, args.seq_len, mc["vocab_size"], min_doc=256, max_doc=args.seq_len,
                                 seed=1234)
     coll = PackedCollator(pin=True)
@@ -167,9 +185,11 @@ def run_ours(args) -> dict:
         torch.cuda.synchronize()
 
     model.train()
-    # ---- warm-up
+    # ---- warm-up: W steps, then until two consecutive steps agree within 3 % (at most EXTRA_WARMUP more)
     for i in range(args.warmup):
         train_step(engine, model, optim, [to_device(host[i])], check_finite=False)
+    warmup_used = args.warmup + stabilise(lambda j: train_step(engine, model, optim, [to_device(host[j % args.warmup])],
+                                                               check_finite=False), sync, world, dev)
     # ---- device-timed region: inputs staged on the device beforehand
     staged = [to_device(host[args.warmup + i]) for i in range(args.steps)]
     sampler = ClockSampler(local_rank)
@@ -214,6 +234,13 @@ def run_ours(args) -> dict:
                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4, "ms_per_step": float(t2.item()) / args.steps,
                "final_loss": losses[-1]}
     st = kernels.status()
+    # status words of every peer-memory workspace (expert-parallel, Ulysses, FSDP arenas): a timeout or a receive
+    # overflow anywhere in the run would make the number above meaningless
+    try:
+        engine.check_health()
+        peer_status = "ok"
+    except Exception as e:  # noqa: BLE001
+        peer_status = f"{type(e).__name__}: {e}"[:200]
     disp = [type(m.token_dispatcher).__name__ for m in model.modules() if hasattr(m, "token_dispatcher")]
     ep_transport = (disp[0] if disp else "none") if world > 1 else "local"
     out = {
@@ -232,7 +259,8 @@ def run_ours(args) -> dict:
                    "depth from 4 GPUs on", "tokens_per_s_scaled_to_named_layers": value * layers / float(named_layers),
                    "l2": "per-step working set (weights, optimizer state, activations: tens of GB) is far larger than the 126 MB L2"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "loss": float(last),
-        "kernel_status": list(st), "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30,
+        "kernel_status": list(st), "peer_status": peer_status, "warmup_used": warmup_used,
+        "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30,
     }
     if world > 1:
         dist.barrier()
@@ -241,7 +269,101 @@ def run_ours(args) -> dict:
     return out if rank == 0 else {}
 
 
+EXTRA_WARMUP = 12
+
+
+def stabilise(step_fn, sync, world, dev) -> int:
+    """Extra warm-up: runs single steps, each timed on the device (max over ranks), until two consecutive ones differ
+    by less than 3 % or EXTRA_WARMUP steps have run.  Returns how many ran."""
+    import torch
+    import torch.distributed as dist
+
+    prev, used = None, 0
+    while used < EXTRA_WARMUP:
+        sync()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        step_fn(used)
+        b.record()
+        sync()
+        t = torch.tensor([a.elapsed_time(b)], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        cur = float(t.item())
+        used += 1
+        if prev is not None and abs(cur - prev) <= 0.03 * max(cur, prev):
+            break
+        prev = cur
+    return used
+
+
+_LAUNCHER_ENV = ("RANK", "LOCAL_RANK", "WORLD_SIZE", "LOCAL_WORLD_SIZE", "GROUP_RANK", "ROLE_RANK", "ROLE_NAME",
+                 "ROLE_WORLD_SIZE", "GROUP_WORLD_SIZE", "MASTER_ADDR", "MASTER_PORT", "TORCHELASTIC_RESTART_COUNT",
+                 "TORCHELASTIC_MAX_RESTARTS", "TORCHELASTIC_RUN_ID", "TORCHELASTIC_USE_AGENT_STORE",
+                 "TORCHELASTIC_ERROR_FILE", "TORCH_NCCL_ASYNC_ERROR_HANDLING")
+
+
+def run_child(args, world: int, extra: list[str], timeout_s: float) -> dict:
+    """One more measurement in fresh processes (same arm, same launch form as this call); returns its JSON record."""
+    env = {k: v for k, v in os.environ.items() if k not in _LAUNCHER_ENV}
+    me = os.path.abspath(__file__)
+    base = [sys.executable]
+    if world > 1:
+        port = 29700 + (os.getpid() % 200)
+        base += ["-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+                 "--master-port", str(port)]
+    cmd = base + [me, "--child", "--extras", "none", "--impl", args.impl, "--gpus", str(world), "--steps", str(min(args.steps, 4)),
+                  "--warmup", str(max(args.warmup, 3))] + extra
+    try:
+        res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout_s)
+    except subprocess.TimeoutExpired:
+        return {"error": f"no result within {timeout_s:.0f} s"}
+    for line in reversed(res.stdout.strip().splitlines()):
+        if line.startswith("{"):
+            try:
+                return json.loads(line)
+            except ValueError:
+                continue
+    tail = (res.stderr or "").strip().splitlines()[-1:] or [""]
+    return {"error": f"exit {res.returncode}: {tail[0][:200]}"}
+
+
+def slim(rec: dict) -> dict:
+    """The fields of a sub-measurement that the headline line carries."""
+    keep = ("impl", "unavailable", "error", "value", "unit", "ms_per_step", "n_gpus", "steps", "warmup", "warmup_used", "e2e",
+            "clocks", "gpu_launches", "loss", "peak_mem_gb", "peer_status", "kernel_status", "dtype")
+    out = {k: rec[k] for k in keep if k in rec}
+    if "config" in rec:
+        out["config"] = {k: rec["config"][k] for k in ("model", "layers", "layers_named", "global_batch", "seq_len", "parallelism",
+                                                        "activation_checkpointing", "sp_transport", "ep_transport", "fsdp_transport")
+                         if k in rec["config"]}
+    return out
+
+
+def extras(args, out: dict, world: int, t_start: float) -> None:
+    """Attach `fixed_depth` and `secondary` to the headline record (rank 0, after the GPUs were released)."""
+    mode = args.extras
+    if mode == "none" or args.model != "qwen3_moe_30b_a3b" or args.sp != 1 or args.layers:
+        return
+    left = lambda: args.extras_budget_s - (time.time() - t_start)   # noqa: E731
+    # ---- the same model at 12 layers for every N: the like-for-like scaling series
+    if out.get("config", {}).get("layers") == 12:
+        out["fixed_depth"] = slim(out)
+    elif mode in ("auto", "fixed", "all") and left() > 150:
+        out["fixed_depth"] = slim(run_child(args, world, ["--layers", "12"], min(300.0, left() - 30)))
+    # ---- the other named configurations of the 8-GPU box
+    if mode == "all" or (mode == "auto" and world >= 8):
+        out["secondary"] = []
+        for extra in (["--model", "qwen3_14b", "--sp", str(world), "--seq-len", "65536", "--layers", "40"],
+                      ["--model", "qwen3_8b", "--seq-len", "8192", "--layers", "36"]):
+            if left() < 200:
+                out["secondary"].append({"config": {"model": extra[1]}, "error": "skipped: wall-clock budget of the call used up"})
+                continue
+            out["secondary"].append(slim(run_child(args, world, extra, min(420.0, left() - 30))))
+
+
 def main():
+    t_start = time.time()
     args = parse()
     # stdout carries the one JSON result line: the package's log lines go to stderr
     import logging
@@ -252,12 +374,31 @@ def main():
     for h in logging.getLogger("torchturbo_b200").handlers:
         if hasattr(h, "setStream"):
             h.setStream(sys.stderr)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         from baseline.run_reference import run_reference
 
         out = run_reference(args)
     else:
         out = run_ours(args)
+    if out and not args.child and "unavailable" not in out:
+        # the other ranks have returned and exit now; this rank drops what it holds on its GPU, then starts the
+        # additional measurements as fresh process groups
+        try:
+            import gc
+
+            import torch
+
+            if args.impl != "reference":
+                from torchturbo_b200.comm import ep_p2p, fsdp_p2p, rows_p2p, ulysses_p2p
+
+                for table in (ep_p2p._WORKSPACES, fsdp_p2p._ARENAS, ulysses_p2p._WORKSPACES, rows_p2p._WS):
+                    table.clear()
+            gc.collect()
+            torch.cuda.empty_cache()
+        except Exception:  # noqa: BLE001
+            pass
+        extras(args, out, world, t_start)
     if out:
         print(json.dumps(out), flush=True)
 

@@ -1,0 +1,108 @@
+"""Parity of this package's own modelling code and checkpoint format with Hugging Face `transformers`.
+
+For every family whose HF class ships with the installed `transformers`:
+  (a) a randomly initialised HF model is written with `save_pretrained`, loaded through `engine.build_model(path)`
+      (weight converter: per-projection HF tensors -> fused `qkv_proj` / `gate_up_proj` / `weight1` / `weight2`), and
+      must give the same logits and the same packed-batch loss in fp32;
+  (b) the engine's HF export (`save_model(..., hf_export)`) is loaded by `AutoModelForCausalLM.from_pretrained` and must
+      give the same logits again.
+The reference gets the first property for free by subclassing the HF classes (models/qwen3_moe/model.py:19) and tests
+its own modelling copies against them (tests/models/deepseek_v4/test_turbo_vs_base_precision.py)."""
+import os
+
+import pytest
+import torch
+
+from dist_utils import run_distributed
+
+transformers = pytest.importorskip("transformers")
+
+DENSE = dict(vocab_size=320, hidden_size=64, intermediate_size=160, num_hidden_layers=2, num_attention_heads=4,
+             num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False,
+             max_position_embeddings=512, attention_bias=False)
+MOE = dict(DENSE, moe_intermediate_size=48, num_experts=8, num_experts_per_tok=2, norm_topk_prob=True, decoder_sparse_step=1,
+           mlp_only_layers=[], router_aux_loss_coef=0.0, output_router_logits=False)
+
+
+def _hf(kind):
+    if kind == "qwen3":
+        from transformers import Qwen3Config, Qwen3ForCausalLM
+
+        return Qwen3Config(**DENSE), Qwen3ForCausalLM
+    from transformers import Qwen3MoeConfig, Qwen3MoeForCausalLM
+
+    return Qwen3MoeConfig(**MOE), Qwen3MoeForCausalLM
+
+
+def _engine():
+    from torchturbo_b200.engine import EngineConfig, TorchTurboEngine
+
+    return TorchTurboEngine(EngineConfig.from_dict({"mixed_precision": "fp32", "activation_checkpointing": {"enabled": False},
+                                                    "checkpoint": {"hf_export": "every"}}))
+
+
+def _hf_logits(model, ids, lens):
+    """Packed row through the HF model: one forward per document (position ids restart, no cross-document attention)."""
+    outs, s = [], 0
+    with torch.no_grad():
+        for n in lens:
+            outs.append(model(input_ids=ids[:, s:s + n]).logits.float())
+            s += n
+    return torch.cat(outs, dim=1)
+
+
+def _batch(vocab, lens, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    T = sum(lens)
+    ids = torch.randint(0, vocab, (1, T), generator=g)
+    pos = torch.cat([torch.arange(n) for n in lens])[None]
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    labels = ids.clone()
+    labels[0, cu[:-1].long()] = -100
+    return dict(input_ids=ids, position_ids=pos, labels=labels, cu_seq_lens_q=cu, cu_seq_lens_k=cu,
+                max_length_q=max(lens), max_length_k=max(lens))
+
+
+def _w_parity(rank, world, kind, root):
+    torch.manual_seed(0)
+    cfg, cls = _hf(kind)
+    cfg.torch_dtype = torch.float32
+    hf = cls(cfg).float().eval()
+    src = os.path.join(root, "hf_src")
+    hf.save_pretrained(src, safe_serialization=True)
+    lens = [23, 9, 16]
+    batch = _batch(cfg.vocab_size, lens)
+    ref_logits = _hf_logits(hf, batch["input_ids"], lens)
+    # ---- (a) HF checkpoint -> this engine
+    eng = _engine()
+    model = eng.build_model(src)
+    model.eval()
+    with torch.no_grad():
+        out = model(**{k: v for k, v in batch.items() if k != "labels"})
+    ours = out["logits"].float().reshape(1, -1, cfg.vocab_size)
+    err = (ours - ref_logits).abs().max().item()
+    assert err < 1e-4, f"{kind}: logits differ from transformers by {err}"
+    # packed loss: mean CE over the targets that stay inside their document
+    model.train()
+    loss = float(eng.compute_loss(model, dict(batch)))
+    tgt, lg = [], []
+    s = 0
+    for n in lens:
+        lg.append(ref_logits[0, s:s + n - 1])
+        tgt.append(batch["input_ids"][0, s + 1:s + n])
+        s += n
+    ref_loss = float(torch.nn.functional.cross_entropy(torch.cat(lg), torch.cat(tgt)))
+    assert abs(loss - ref_loss) < 1e-4, (kind, loss, ref_loss)
+    # ---- (b) this engine's HF export -> transformers
+    ckpt = os.path.join(root, "checkpoint-1")
+    eng.save_model(model, ckpt, final=True)
+    back = transformers.AutoModelForCausalLM.from_pretrained(os.path.join(ckpt, "huggingface"), torch_dtype=torch.float32).eval()
+    err = (_hf_logits(back, batch["input_ids"], lens) - ref_logits).abs().max().item()
+    assert err < 1e-4, f"{kind}: exported checkpoint differs from the source by {err}"
+    sd_a, sd_b = hf.state_dict(), back.state_dict()
+    assert set(sd_a) == set(sd_b), sorted(set(sd_a) ^ set(sd_b))[:8]
+
+
+@pytest.mark.parametrize("kind", ["qwen3", "qwen3_moe"])
+def test_logits_loss_and_export_match_transformers(tmp_path, kind):
+    run_distributed(_w_parity, 1, kind, str(tmp_path), timeout=400)

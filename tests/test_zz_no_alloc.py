@@ -31,23 +31,29 @@ def test_noalloc_entry_point_matches_regular_one():
     lib.ttb_noalloc_strerror.restype = C.c_char_p
     torch.manual_seed(0)
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
-    for T, H in [(300, 2048), (77, 4096)]:          # second call reuses the scratch the first one filled
+    # (rows, width, residual gradient given, (1 + w) variant): later calls reuse the scratch the earlier ones filled; the
+    # list covers the documented maximum width, the smallest width, fewer rows than scratch blocks and both options
+    for T, H, with_dres, one_plus_w in [(300, 2048, True, False), (77, 4096, True, False), (5, 8192, False, True),
+                                        (3, 8, False, False), (1000, 8192, True, True)]:
         x = torch.randn(T, H, device="cuda").bfloat16()
         dy = torch.randn(T, H, device="cuda").bfloat16()
-        dres = torch.randn(T, H, device="cuda").bfloat16()
+        dres = torch.randn(T, H, device="cuda").bfloat16() if with_dres else None
         w = torch.randn(H, device="cuda").bfloat16()
-        _, rstd, _ = K.rmsnorm_fwd(x, w, 1e-6)
-        dx_ref, dw_ref = K.rmsnorm_bwd(dy, x, w, rstd, dres=dres)
+        _, rstd, _ = K.rmsnorm_fwd(x, w, 1e-6, one_plus_w=one_plus_w)
+        dx_ref, dw_ref = K.rmsnorm_bwd(dy, x, w, rstd, dres=dres, one_plus_w=one_plus_w)
         dx = torch.empty_like(x)
         dw = torch.empty(H, dtype=torch.float32, device="cuda")
         before = torch.cuda.memory_allocated()
-        rc = fn(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dres.data_ptr(), dx.data_ptr(), dw.data_ptr(),
-                T, H, 0, stream)
+        rc = fn(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dres.data_ptr() if with_dres else None,
+                dx.data_ptr(), dw.data_ptr(), T, H, int(one_plus_w), stream)
         assert rc == 0, lib.ttb_noalloc_strerror(rc).decode()
         assert torch.cuda.memory_allocated() == before
         torch.cuda.synchronize()
         _close(dx, dx_ref)
         _close(dw, dw_ref)
+    # every error class has its own range and its own text
+    texts = {lib.ttb_noalloc_strerror(c) for c in (901, 100000 + 700, 110000 + 700, 200000 + 101)}
+    assert len(texts) == 4 and all(b"unknown" not in t for t in texts)
     # sizes beyond the built-in scratch are refused with a readable message, and nothing runs
     rc = fn(0, 0, 0, 0, 0, 0, 0, 4, 8192 + 8, 0, stream)
     assert rc == 901 and b"8192" in lib.ttb_noalloc_strerror(rc)

@@ -1,5 +1,22 @@
 """Expert-parallel token dispatch / combine over peer memory (NVLink), without NCCL and without host reads.
 
+Two forms share one workspace.  The FUSED form (`P2PTokenDispatcher.fused_experts`, default) puts the exchange inside
+the grouped GEMMs of the expert MLP:
+    prepare (one host call)     : counts exchange kernel (tables, send order), destination rows, receive padding cleared
+    fc1 GEMM + push prologue    : two extra warps per CTA copy this rank's routed rows (+ routing weight + return tag)
+                                  into the owners' expert-major buffers while the tensor cores run; the TMA producer
+                                  waits per expert for "rows landed" flags; SwiGLU x weight in the epilogue
+    fc2 GEMM + scatter epilogue : every output row is stored straight into the source rank's [T*k, H] return buffer;
+                                  the last CTA raises "rows returned" flags
+    k-sum kernel                : waits for the owners' flags, sums the k rows of a token (+ residual)
+Backward is the same pair around the transposed GEMMs: d(out) rows are pushed inside the d(act) GEMM, d(x) rows (and
+the routing-weight gradients) come back from the epilogue of the d(x) GEMM.  No kernel exists only to wait or to signal.
+Buffer reuse needs no extra handshake: a rank starts the push of its next exchange only after its k-sum has seen every
+owner's "returned" flag, which an owner raises at the end of the GEMM that follows its last read of the receive buffer;
+and an owner writes a source's return buffer only in tiles whose rows that source pushed after its previous k-sum.
+
+The UNFUSED form (`dispatch` / `combine`, `TORCHTURBO_EP_FUSED=0`) keeps exchange and GEMMs in separate kernels:
+
 Forward of one MoE layer on every rank (all stream-ordered, nothing waits on the host):
     counts exchange kernel      : my per-expert counts -> every peer; tables for my experts and my send offsets
     rank kernel                 : destination row of each of my (token, slot) entries on its owner
@@ -22,6 +39,7 @@ workspace status, which `check()` turns into an exception).
 """
 from __future__ import annotations
 
+import ctypes as C
 import os
 
 import torch
@@ -42,19 +60,69 @@ class EPWorkspace:
         rows = int(tokens * topk * capacity_factor)
         self.m_tiles_cap = (rows + K.SEG_ALIGN - 1) // K.SEG_ALIGN + self.El
         self.cap = self.m_tiles_cap * K.SEG_ALIGN
-        nbytes = 4 * self.W * self.E + 2 * self.cap * hidden * 2 + 2 * self.cap * 4 + 8 * 4 * self.W + 16 * 256
+        # rows of the return buffer of the fused form: this rank's own (token, expert) entries, with the same head
+        # room as the receive side so that later batches may be somewhat longer than the one that sized the workspace
+        self.entries = int(tokens * topk * max(capacity_factor, 1.0))
+        out_rows = max(self.cap, self.entries)             # y rows (unfused) and returned rows (fused) share one region
+        nbytes = (4 * self.W * self.E + self.cap * hidden * 2 + out_rows * hidden * 2 + 3 * self.cap * 4 + out_rows * 4
+                  + 4 * (4 * self.W + self.E) + 24 * 256)
         self.buf = SymmetricBuffer(nbytes, group)
         self.off_counts, self.counts_all = self.buf.carve(4 * self.W * self.E, torch.int32)
         self.off_recv, self.recv_rows = self.buf.carve(self.cap * hidden * 2, torch.bfloat16, (self.cap, hidden))
         self.off_recv_vals, self.recv_vals = self.buf.carve(self.cap * 4, torch.float32)
-        self.off_y, self.y_rows = self.buf.carve(self.cap * hidden * 2, torch.bfloat16, (self.cap, hidden))
-        self.off_y_vals, self.y_vals = self.buf.carve(self.cap * 4, torch.float32)
+        self.off_recv_tags, self.recv_tags = self.buf.carve(self.cap * 4, torch.int32)
+        self.off_y, out_region = self.buf.carve(out_rows * hidden * 2, torch.bfloat16, (out_rows, hidden))
+        self.y_rows, self.ret_rows = out_region[:self.cap], out_region[:self.entries]
+        self.off_y_vals, out_vals = self.buf.carve(out_rows * 4, torch.float32)
+        self.y_vals, self.ret_vals = out_vals[:self.cap], out_vals[:self.entries]
         self.ch_counts, self.ch_rows, self.ch_ready = self.buf.channel(), self.buf.channel(), self.buf.channel()
+        self.ch_push, self.ch_ret = self.buf.channel(self.E), self.buf.channel()
         dev = self.buf.local.device
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         self.done = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.sent = torch.zeros(self.E + 1, dtype=torch.int32, device=dev)   # rows sent per expert + chunk counter
         self.budget_ms = int(os.environ.get("TORCHTURBO_P2P_WAIT_MS", "5000"))
         self.ptrs = self.buf.peer_ptrs
+
+    # -- fused form -----------------------------------------------------------------------------------
+    def prepare(self, expert, counts=None, tables=None):
+        return K.ep_prepare(self.ptrs, off_counts=self.off_counts, off_flags_counts=self.ch_counts.offset, counts=counts,
+                            expert=expert, recv_rows=self.recv_rows, recv_vals=self.recv_vals, recv_tags=self.recv_tags,
+                            sent=self.sent, status=self.status, rank=self.rank, world=self.W, num_experts=self.E,
+                            m_tiles_cap=self.m_tiles_cap, epoch_counts=self.ch_counts.next() if tables is None else 0,
+                            budget_ms=self.budget_ms, tables=tables)
+
+    def _fuse(self) -> "K.EpFuseArgs":
+        a = K.EpFuseArgs()
+        a.peer_ptrs, a.W, a.rank, a.El = C.addressof(self.ptrs), self.W, self.rank, self.El
+        a.status, a.budget_ms = self.status.data_ptr(), self.budget_ms
+        return a
+
+    def push_args(self, src, order, expert, dest_row, val, counts, k) -> "K.EpFuseArgs":
+        """Push prologue: rows of `src` ([T, H]) -> the owners' receive buffers, in `order`."""
+        a = self._fuse()
+        a.push_on = 1
+        a.off_rows, a.off_vals, a.off_tags, a.off_flags = self.off_recv, self.off_recv_vals, self.off_recv_tags, self.ch_push.offset
+        a.src, a.lds = src.data_ptr(), src.stride(0)
+        a.order, a.expert, a.dest_row = order.data_ptr(), expert.data_ptr(), dest_row.data_ptr()
+        a.val = val.data_ptr() if val is not None else None
+        a.counts, a.sent = counts.data_ptr(), self.sent.data_ptr()
+        a.n_entries, a.k, a.H, a.epoch, a.cap_rows = expert.numel(), k, self.H, self.ch_push.next(), self.cap
+        return a
+
+    def scatter_args(self, row_val=None) -> "K.EpFuseArgs":
+        """Scatter epilogue: output rows -> the return buffer of the rank named by the row's tag."""
+        a = self._fuse()
+        a.scat_on = 1
+        a.off_ret, a.off_ret_vals, a.off_ret_flags = self.off_y, self.off_y_vals, self.ch_ret.offset
+        a.row_tag = self.recv_tags.data_ptr()
+        a.row_val = row_val.data_ptr() if row_val is not None else None
+        a.ret_epoch, a.done_counter = self.ch_ret.next(), self.done.data_ptr()
+        return a
+
+    def ksum(self, T, k, residual=None):
+        return K.ep_ksum(self.ptrs, self.off_y, self.ch_ret.offset, T, k, self.H, self.W, self.rank, self.ch_ret.epoch,
+                         self.budget_ms, self.status, residual=residual)
 
     # -- primitives ---------------------------------------------------------------------------------
     def exchange(self, counts):
@@ -170,6 +238,49 @@ class _Combine(torch.autograd.Function):
         return dy, None, None, None, None, None, None, None, (dout if has_res else None)
 
 
+class _FusedExperts(torch.autograd.Function):
+    """Expert MLP of one MoE layer with the token exchange inside its grouped GEMMs (module docstring, fused form)."""
+
+    @staticmethod
+    def forward(ctx, x, prob, idx32, counts, w1, w2, ws: EPWorkspace, residual):
+        T, k = idx32.shape
+        expert = idx32.reshape(-1)
+        probf = prob.reshape(-1)
+        seg_start, recv_counts, tile_group, dest_row, order = ws.prepare(expert, counts=counts)
+        pre = torch.empty(ws.cap, w1.shape[-1], dtype=torch.bfloat16, device=x.device)
+        act = K.gemm(ws.recv_rows, w1, b_mn=True, tile_group=tile_group, swiglu=True, row_scale=ws.recv_vals, preact=pre,
+                     ep=ws.push_args(x, order, expert, dest_row, probf, counts, k))
+        # the receive buffer is refilled by the next exchange: keep what backward needs
+        xp, rp = K.ep_save(ws.recv_rows, ws.recv_vals, seg_start, ws.El)
+        K.gemm(act, w2, b_mn=True, tile_group=tile_group, out=ws.ret_rows, ep=ws.scatter_args())
+        out = ws.ksum(T, k, residual=residual)
+        ctx.ws, ctx.dims = ws, (T, k, residual is not None)
+        ctx.save_for_backward(xp, rp, pre, w1, w2, tile_group, seg_start, recv_counts, expert, dest_row, order, counts)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        from ..ops.providers.b200 import _weight_grad
+
+        ws, (T, k, has_res) = ctx.ws, ctx.dims
+        xp, rp, pre, w1, w2, tile_group, seg_start, recv_counts, expert, dest_row, order, counts = ctx.saved_tensors
+        dout = dout.contiguous()
+        ws.prepare(expert, tables=(seg_start, recv_counts))
+        # d(act) = d(y) W2[e]^T with the d(out) rows pushed to the owners from inside the kernel (they land in recv_rows)
+        dact = K.gemm(ws.recv_rows, w2, tile_group=tile_group, ep=ws.push_args(dout, order, expert, dest_row, None, counts, k))
+        dpre, dprob_rows = K.swiglu_bwd(dact, pre, rp, want_dscale=True)
+        dw1 = dw2 = None
+        if ctx.needs_input_grad[5]:
+            dw2 = _weight_grad(w2, K.swiglu_fwd(pre, rp), ws.recv_rows, group_rows=seg_start)
+        if ctx.needs_input_grad[4]:
+            dw1 = _weight_grad(w1, xp, dpre, group_rows=seg_start)
+        # last reader of the received d(y) rows is done: d(x) rows and d(prob) go back to their sources from the epilogue
+        K.gemm(dpre, w1, tile_group=tile_group, out=ws.ret_rows, ep=ws.scatter_args(row_val=dprob_rows))
+        dx = ws.ksum(T, k)
+        dprob = ws.ret_vals[:T * k].clone().view(T, k)
+        return dx, dprob, None, None, dw1, dw2, None, (dout if has_res else None)
+
+
 class P2PTokenDispatcher:
     """Drop-in replacement of the all-to-all dispatcher of `MoELayer` for bf16 CUDA tensors on one NVLink domain."""
 
@@ -192,6 +303,27 @@ class P2PTokenDispatcher:
         return self._fallback
 
     accepts_counts = True
+
+    def fused_usable(self, x, w1, w2) -> bool:
+        """bf16 CUDA rows whose width fits the scatter epilogue (whole 32-column chunks)."""
+        return (os.environ.get("TORCHTURBO_EP_FUSED", "1") != "0" and x.is_cuda and x.dtype == torch.bfloat16
+                and w1.dtype == torch.bfloat16 and w2.dtype == torch.bfloat16 and x.shape[-1] % 32 == 0
+                and w1.shape[-1] % 16 == 0 and not self.config.moe_swiglu_limit)
+
+    def fused_experts(self, x, idx, prob, w1, w2, counts=None, residual=None):
+        """Dispatch + expert MLP + combine of one layer: `w1` [El, H, 2F], `w2` [El, F, H]; returns [T, H]."""
+        T, k = idx.shape
+        E = self.config.num_moe_experts
+        ws = get_workspace(self.ep_group, x.shape[-1], E, T, k, self.capacity_factor)
+        if T * k > ws.entries:
+            raise RuntimeError(f"expert-parallel workspace holds {ws.entries} (token, expert) entries per rank, this batch has "
+                               f"{T * k}: set TORCHTURBO_EP_MAX_TOKENS to the largest per-rank token count")
+        idx32 = idx if idx.dtype == torch.int32 and idx.is_contiguous() else idx.to(torch.int32).contiguous()
+        if counts is None or counts.dtype != torch.int32 or counts.numel() != E:
+            counts = torch.zeros(E, dtype=torch.int32, device=x.device)
+            counts.scatter_add_(0, idx32.reshape(-1).long(), torch.ones(idx32.numel(), dtype=torch.int32, device=x.device))
+        probf = prob if prob.dtype == torch.float32 and prob.is_contiguous() else prob.float().contiguous()
+        return _FusedExperts.apply(x.contiguous(), probf, idx32, counts, w1, w2, ws, residual)
 
     def dispatch(self, x, idx, prob, counts=None):
         """`counts` (int32 [E], the histogram of `idx`) is taken from the routing kernel when the caller has it."""

@@ -65,8 +65,9 @@ class SymmetricBuffer:
             view = view.view(*shape)
         return off, view
 
-    def channel(self) -> Channel:
-        off, view = self.carve(4 * self.world, torch.int32)
+    def channel(self, n: int | None = None) -> Channel:
+        """A block of `n` epoch flags (default: one per rank)."""
+        off, view = self.carve(4 * (n or self.world), torch.int32)
         return Channel(off, view)
 
     @staticmethod

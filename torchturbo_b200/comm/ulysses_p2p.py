@@ -33,29 +33,39 @@ D = 128
 
 
 class UlyssesWorkspace:
-    def __init__(self, group, tokens_local: int, n_q: int, n_kv: int, rep: int):
+    """Symmetric buffers for up to `cap_local` tokens per rank.  A call with `Tl` local tokens uses the first
+    `Tl * W` rows of every buffer (`rows()`), so one workspace serves every sequence length up to its capacity."""
+
+    NAMES = ("q", "k", "v", "o", "do", "dq", "dk", "dv")
+
+    def __init__(self, group, cap_local: int, n_q: int, n_kv: int, rep: int):
         self.group = group
         self.W, self.rank = dist.get_world_size(group), dist.get_rank(group)
-        self.Tl, self.T = tokens_local, tokens_local * self.W
+        self.cap_local = cap_local
+        Tc = cap_local * self.W
         self.n_q, self.n_kv, self.rep = n_q, n_kv, rep
         self.Hql, self.Hkl = n_q // self.W, n_kv * rep // self.W
-        qb, kb = self.T * self.Hql * D * 2, self.T * self.Hkl * D * 2
+        qb, kb = Tc * self.Hql * D * 2, Tc * self.Hkl * D * 2
         self.buf = SymmetricBuffer(4 * qb + 4 * kb + 16 * 256 + 8 * 4 * self.W, group)
         c = self.buf.carve
-        self.off_q, self.q = c(qb, torch.bfloat16, (self.T, self.Hql, D))
-        self.off_k, self.k = c(kb, torch.bfloat16, (self.T, self.Hkl, D))
-        self.off_v, self.v = c(kb, torch.bfloat16, (self.T, self.Hkl, D))
-        self.off_o, self.o = c(qb, torch.bfloat16, (self.T, self.Hql, D))
-        self.off_do, self.do = c(qb, torch.bfloat16, (self.T, self.Hql, D))
-        self.off_dq, self.dq = c(qb, torch.bfloat16, (self.T, self.Hql, D))
-        self.off_dk, self.dk = c(kb, torch.bfloat16, (self.T, self.Hkl, D))
-        self.off_dv, self.dv = c(kb, torch.bfloat16, (self.T, self.Hkl, D))
+        self.off_q, self._q = c(qb, torch.bfloat16, (Tc, self.Hql, D))
+        self.off_k, self._k = c(kb, torch.bfloat16, (Tc, self.Hkl, D))
+        self.off_v, self._v = c(kb, torch.bfloat16, (Tc, self.Hkl, D))
+        self.off_o, self._o = c(qb, torch.bfloat16, (Tc, self.Hql, D))
+        self.off_do, self._do = c(qb, torch.bfloat16, (Tc, self.Hql, D))
+        self.off_dq, self._dq = c(qb, torch.bfloat16, (Tc, self.Hql, D))
+        self.off_dk, self._dk = c(kb, torch.bfloat16, (Tc, self.Hkl, D))
+        self.off_dv, self._dv = c(kb, torch.bfloat16, (Tc, self.Hkl, D))
         self.ch_qkv, self.ch_out, self.ch_dout, self.ch_dqkv = (self.buf.channel() for _ in range(4))
         dev = self.buf.local.device
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         self.done = torch.zeros(1, dtype=torch.int32, device=dev)
         self.budget_ms = int(os.environ.get("TORCHTURBO_P2P_WAIT_MS", "5000"))
         self.ptrs = self.buf.peer_ptrs
+
+    def rows(self, name: str, Tl: int) -> torch.Tensor:
+        """The `[Tl * W, heads, D]` part of buffer `name` that a call with `Tl` local tokens reads and writes."""
+        return getattr(self, "_" + name)[:Tl * self.W]
 
     def wait(self, ch, epoch):
         K.flag_wait(self.ptrs, ch.offset, self.rank, self.W, epoch, self.budget_ms, self.status)
@@ -72,12 +82,17 @@ class UlyssesWorkspace:
 
 
 def get_workspace(group, tokens_local: int, n_q: int, n_kv: int, rep: int) -> UlyssesWorkspace:
-    """One workspace per (group, local tokens, head counts).  Sizes follow from arguments that are equal on every
-    rank of the group (the row is padded to a multiple of `sp` before it is sliced), so no agreement step is needed."""
-    key = (id(group), tokens_local, n_q, n_kv, rep)
+    """One workspace per (group, head counts), sized by a token capacity: the first request rounded up to 1024 tokens
+    (or `TORCHTURBO_ULYSSES_MAX_TOKENS`), doubled when a longer row arrives.  The local token count is equal on every
+    rank of the group (the row is padded to a multiple of `sp` before it is sliced), so all ranks create and grow the
+    workspace at the same call without an agreement step.  A workspace that was outgrown is dropped from the table;
+    autograd nodes that still hold it finish their backward on it."""
+    key = (id(group), n_q, n_kv, rep)
     ws = _WORKSPACES.get(key)
-    if ws is None:
-        ws = UlyssesWorkspace(group, tokens_local, n_q, n_kv, rep)
+    if ws is None or ws.cap_local < tokens_local:
+        preset = int(os.environ.get("TORCHTURBO_ULYSSES_MAX_TOKENS", "0"))
+        cap = max((tokens_local + 1023) // 1024 * 1024, preset, 2 * ws.cap_local if ws is not None else 0)
+        ws = UlyssesWorkspace(group, cap, n_q, n_kv, rep)
         _WORKSPACES[key] = ws
     return ws
 
@@ -113,7 +128,8 @@ class _QKVExchange(torch.autograd.Function):
         rstd = K.ulysses_qkv_scatter(ws.ptrs, ws.off_q, ws.off_k, ws.off_v, ws.ch_qkv.offset, qkv, n_q, n_kv, ws.rep, wq, wk,
                                      cos, sin, eps, ws.rank, ws.W, epoch, ws.done, use_norm)
         ws.wait(ws.ch_qkv, epoch)
-        q, k, v = ws.q.clone(), ws.k.clone(), ws.v.clone()
+        Tl = qkv.shape[0]
+        q, k, v = ws.rows("q", Tl).clone(), ws.rows("k", Tl).clone(), ws.rows("v", Tl).clone()
         ctx.save_for_backward(qkv, wq, wk, cos, sin, rstd)
         ctx.ws, ctx.dims = ws, (n_q, n_kv, use_norm)
         return q, k, v
@@ -122,11 +138,11 @@ class _QKVExchange(torch.autograd.Function):
     def backward(ctx, dq, dk, dv):
         qkv, wq, wk, cos, sin, rstd = ctx.saved_tensors
         ws, (n_q, n_kv, use_norm) = ctx.ws, ctx.dims
-        ws.dq.copy_(dq)
-        ws.dk.copy_(dk)
-        ws.dv.copy_(dv)
-        ws.ready(ws.ch_dqkv)
         Tl = qkv.shape[0]
+        ws.rows("dq", Tl).copy_(dq)
+        ws.rows("dk", Tl).copy_(dk)
+        ws.rows("dv", Tl).copy_(dv)
+        ws.ready(ws.ch_dqkv)
         dql = torch.empty(Tl, n_q, D, dtype=qkv.dtype, device=qkv.device)
         dkl = torch.empty(Tl, n_kv, D, dtype=qkv.dtype, device=qkv.device)
         dvl = torch.empty(Tl, n_kv, D, dtype=qkv.dtype, device=qkv.device)
@@ -143,11 +159,12 @@ class _QKVExchange(torch.autograd.Function):
 class _OutExchange(torch.autograd.Function):
     @staticmethod
     def forward(ctx, o_full, ws: UlyssesWorkspace):
-        ws.o.copy_(o_full)
+        Tl = o_full.shape[0] // ws.W
+        ws.rows("o", Tl).copy_(o_full)
         ws.ready(ws.ch_out)
-        out = torch.empty(ws.Tl, ws.n_q, D, dtype=o_full.dtype, device=o_full.device)
+        out = torch.empty(Tl, ws.n_q, D, dtype=o_full.dtype, device=o_full.device)
         K.ulysses_move(ws.ptrs, ws.off_o, 0, out, ws.n_q, 1, ws.rank, ws.W, 0, ws.done, ws.status, True)
-        ctx.ws = ws
+        ctx.ws, ctx.Tl = ws, Tl
         return out
 
     @staticmethod
@@ -157,7 +174,7 @@ class _OutExchange(torch.autograd.Function):
         K.ulysses_move(ws.ptrs, ws.off_do, ws.ch_dout.offset, dout.contiguous(), ws.n_q, 1, ws.rank, ws.W, epoch, ws.done,
                        ws.status, False)
         ws.wait(ws.ch_dout, epoch)
-        return ws.do.clone(), None
+        return ws.rows("do", ctx.Tl).clone(), None
 
 
 def qkv_exchange(qkv, n_q, n_kv, wq, wk, cos, sin, eps, group):

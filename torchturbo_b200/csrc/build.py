@@ -39,7 +39,7 @@ def sources() -> list[Path]:
 
 def _digest(paths: list[Path]) -> str:
     h = hashlib.sha256()
-    for p in sorted(paths) + sorted(CSRC.glob("*.cuh")):
+    for p in sorted(paths) + sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")):
         h.update(p.name.encode())
         h.update(p.read_bytes())
     h.update(" ".join(NVCC_FLAGS).encode())

@@ -17,44 +17,11 @@
 //
 // Together they replace counts all-gather + host read of split sizes + two all-to-all-v + chunk sort + unpermute of
 // the reference dispatcher (models/modules/moe/token_dispatcher.py:125-259).
-#include "common.cuh"
+#include "peer.cuh"
 
 namespace ttb {
 
-constexpr unsigned KID_COMM = 3;
-constexpr int MAX_RANKS = 16;
 constexpr int EP_ALIGN = 128;
-
-struct PeerTable {
-  unsigned long long base[MAX_RANKS];  // device-visible base address of every rank's symmetric buffer
-};
-
-__device__ __forceinline__ void st_release_sys(int* p, int v) {
-  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ int ld_acquire_sys(const int* p) {
-  int v;
-  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-
-// Wait until *flag >= epoch (epochs of one channel only grow).  Returns false after `budget_ns`.
-__device__ __forceinline__ bool wait_flag(const int* flag, int epoch, unsigned long long budget_ns, unsigned site,
-                                          unsigned peer, int* status) {
-  if (ld_acquire_sys(flag) >= epoch) return true;
-  // once any wait of this workspace has failed, later waits give up at once: the total stall stays within one budget
-  if (status && *reinterpret_cast<volatile int*>(status) != 0) return false;
-  const uint64_t t0 = globaltimer_ns();
-  while (ld_acquire_sys(flag) < epoch) {
-    if (globaltimer_ns() - t0 > budget_ns) {
-      set_status(KID_COMM, site, peer);
-      if (status) atomicExch(status, static_cast<int>((site << 8) | peer | 0x10000));
-      return false;
-    }
-    __nanosleep(64);
-  }
-  return true;
-}
 
 // ------------------------------------------------------------------------------------------------------------
 // counts exchange + layout tables.  One CTA.
@@ -72,6 +39,7 @@ struct EpExchangeParams {
   int* tile_group;     // [m_tiles_cap]
   int* dest_base;      // [E]
   int* status;         // [1] 0 ok, else error code (timeout or capacity overflow)
+  int* send_base;      // [E] optional: first position of every expert's rows in this rank's send order
 };
 
 __global__ void ep_exchange_kernel(const EpExchangeParams p) {
@@ -108,6 +76,8 @@ __global__ void ep_exchange_kernel(const EpExchangeParams p) {
       if (el < El) p.recv_counts[el] = 0;
     }
     for (int m = threadIdx.x; m < p.m_tiles_cap; m += blockDim.x) p.tile_group[m] = -1;
+    if (p.send_base)
+      for (int e = threadIdx.x; e < E; e += blockDim.x) p.send_base[e] = 0;
     return;
   }
   const int* mine = reinterpret_cast<const int*>(p.peers.base[p.rank] + p.off_counts);
@@ -133,6 +103,17 @@ __global__ void ep_exchange_kernel(const EpExchangeParams p) {
     int before = 0;
     for (int s = 0; s < p.rank; ++s) before += s_counts[s * E + e];
     p.dest_base[e] = s_seg[o * (El + 1) + el] + before;
+  }
+  // send order of the fused dispatch: local expert index major, owners rotated from rank + 1 (own rows last), so
+  // that all owners' first experts complete first and every owner receives from one source at a time
+  if (p.send_base && threadIdx.x == 0) {
+    int acc = 0;
+    for (int el = 0; el < El; ++el)
+      for (int j = 0; j < W; ++j) {
+        const int e = ((p.rank + 1 + j) % W) * El + el;
+        p.send_base[e] = acc;
+        acc += p.counts[e];
+      }
   }
   const int* my_seg = s_seg + p.rank * (El + 1);
   for (int el = threadIdx.x; el <= El; el += blockDim.x) {
@@ -293,7 +274,7 @@ TTB_EXPORT int ttb_ep_exchange(const unsigned long long* peer_ptrs, long long of
   if (sh > 48 * 1024) return 902;
   EpExchangeParams p{make_peers(peer_ptrs, W), off_counts, off_flags, counts, rank, W, E, epoch,
                      static_cast<unsigned long long>(budget_ms) * 1000000ull, m_tiles_cap, seg_start, recv_counts,
-                     tile_group, dest_base, status};
+                     tile_group, dest_base, status, nullptr};
   ep_exchange_kernel<<<1, 256, sh, STREAM(stream)>>>(p);
   LAUNCH_RET();
 }
@@ -827,4 +808,140 @@ TTB_EXPORT int ttb_ep_combine_all(const unsigned long long* peer_ptrs, long long
                     stream);
   if (r || vals_out == nullptr) return r;
   return ttb_ep_gather_vals(peer_ptrs, off_vals, expert, dest_row, vals_out, T * k, El, W, cap_rows, status, stream);
+}
+
+
+// ============================================================================================================
+// Expert-parallel exchange fused into the grouped GEMMs (gemm.cu: push prologue, scatter epilogue).  What is left
+// outside the GEMM kernels:
+//   ttb_ep_prepare : counts exchange + layout tables + send order (forward only), destination rows, padding rows of
+//                    the receive buffer zeroed with tag -1, progress counters cleared.  One host call.
+//   ttb_ep_save    : copy of the rows that landed (device-side row count) for the backward pass.
+//   ttb_ep_ksum    : waits (bounded) for every owner's "rows returned" flag, then out[t] = sum_j ret[t*k+j] (+ residual).
+// ============================================================================================================
+namespace ttb {
+
+__global__ void ep_save_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, const float* __restrict__ vsrc,
+                                    float* __restrict__ vdst, const int* __restrict__ seg_start, int El, int vec,
+                                    long long cap_rows) {
+  long long rows = seg_start[El];
+  if (rows > cap_rows) rows = cap_rows;
+  const long long total = rows * vec;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) dst[i] = src[i];
+  if (vsrc)
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < rows; i += stride) vdst[i] = vsrc[i];
+}
+
+struct EpKsumParams {
+  PeerTable peers;
+  long long off_ret, off_ret_flags;
+  const __nv_bfloat16* residual;
+  long long ldr;
+  __nv_bfloat16* out;
+  long long ldo;
+  int k, H, W, rank, epoch;
+  unsigned long long budget_ns;
+  int* status;
+};
+
+__global__ void ep_ksum_kernel(const EpKsumParams p) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (static_cast<int>(threadIdx.x) < p.W) {
+    const int* f = reinterpret_cast<const int*>(p.peers.base[p.rank] + p.off_ret_flags) + threadIdx.x;
+    if (!wait_flag(f, p.epoch, p.budget_ns, 10, threadIdx.x, p.status)) s_ok = 0;
+  }
+  __syncthreads();
+  const bool healthy = s_ok != 0;
+  const long long t = blockIdx.x;
+  const __nv_bfloat16* ret = reinterpret_cast<const __nv_bfloat16*>(p.peers.base[p.rank] + p.off_ret);
+  for (int c = threadIdx.x * 8; c < p.H; c += blockDim.x * 8) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (healthy) {
+      for (int j = 0; j < p.k; ++j) {
+        const uint4 u = __ldcg(reinterpret_cast<const uint4*>(ret + (t * p.k + j) * p.H + c));
+        float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), cc = unpack_bf16(u.z), d = unpack_bf16(u.w);
+        acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
+        acc[4] += cc.x; acc[5] += cc.y; acc[6] += d.x; acc[7] += d.y;
+      }
+    }
+    if (p.residual) {
+      const uint4 u = *reinterpret_cast<const uint4*>(p.residual + t * p.ldr + c);
+      float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), cc = unpack_bf16(u.z), d = unpack_bf16(u.w);
+      acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += cc.x; acc[5] += cc.y; acc[6] += d.x; acc[7] += d.y;
+    }
+    uint4 o4;
+    o4.x = pack_bf16(acc[0], acc[1]); o4.y = pack_bf16(acc[2], acc[3]);
+    o4.z = pack_bf16(acc[4], acc[5]); o4.w = pack_bf16(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(p.out + t * p.ldo + c) = o4;
+  }
+}
+
+}  // namespace ttb
+
+extern "C" int ttb_perm_rank_order(const int* idx, long long N, int E, const int* base, int* row_of, const int* order_base,
+                                   int* order, void* stream);
+extern "C" int ttb_perm_zero_pad_tags(void* dst, long long ldd, const int* counts, const int* seg_start, float* row_val,
+                                      int* row_tag, int* zero_ints, int n_zero, int E, int H, void* stream);
+
+struct EpPrepareArgs {
+  const unsigned long long* peer_ptrs;
+  long long off_counts, off_flags_counts;
+  const int* counts;        // [E] this rank's routing histogram
+  const int* expert;        // [N]
+  void* recv_rows_local;    // this rank's receive buffer: rows, scalars, tags
+  float* recv_vals_local;
+  int* recv_tags_local;
+  int* seg_start; int* recv_counts; int* tile_group; int* dest_base; int* dest_row; int* send_base; int* order;   // tables
+  int* sent;                // [E + 1] progress counters of the push warps (rows per expert, next chunk)
+  int* status;
+  long long N, budget_ms;
+  int rank, W, E, H, m_tiles_cap, epoch_counts, exchange;   // exchange = 0: the tables of the forward pass are given
+};
+
+TTB_EXPORT int ttb_ep_prepare(const EpPrepareArgs* a, void* stream) {
+  using namespace ttb;
+  if (a->W > MAX_RANKS || a->W < 1 || a->E % a->W) return 901;
+  const int El = a->E / a->W;
+  int r;
+  if (a->exchange) {
+    const size_t sh = static_cast<size_t>(a->W) * a->E * 4 + static_cast<size_t>(a->W) * (El + 1) * 4;
+    if (sh > 48 * 1024) return 902;
+    EpExchangeParams p{make_peers(a->peer_ptrs, a->W), a->off_counts, a->off_flags_counts, a->counts, a->rank, a->W, a->E,
+                       a->epoch_counts, static_cast<unsigned long long>(a->budget_ms) * 1000000ull, a->m_tiles_cap,
+                       a->seg_start, a->recv_counts, a->tile_group, a->dest_base, a->status, a->send_base};
+    ep_exchange_kernel<<<1, 256, sh, STREAM(stream)>>>(p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return 400 + (int)e;
+    r = ttb_perm_rank_order(a->expert, a->N, a->E, a->dest_base, a->dest_row, a->send_base, a->order, stream);
+    if (r) return r;
+  }
+  return ttb_perm_zero_pad_tags(a->recv_rows_local, a->H, a->recv_counts, a->seg_start, a->recv_vals_local,
+                                a->recv_tags_local, a->sent, a->E + 1, El, a->H, stream);
+}
+
+TTB_EXPORT int ttb_ep_save(const void* src, void* dst, const float* vsrc, float* vdst, const int* seg_start, int El, int H,
+                           long long cap_rows, int grid, void* stream) {
+  if (H % 8) return 901;
+  if (grid < 1) grid = 1;
+  ttb::ep_save_rows_kernel<<<grid, 256, 0, STREAM(stream)>>>((const uint4*)src, (uint4*)dst, vsrc, vdst, seg_start, El, H / 8,
+                                                           cap_rows);
+  LAUNCH_RET();
+}
+
+TTB_EXPORT int ttb_ep_ksum(const unsigned long long* peer_ptrs, long long off_ret, long long off_ret_flags, const void* residual,
+                           long long ldr, void* out, long long ldo, long long T, int k, int H, int W, int rank, int epoch,
+                           long long budget_ms, int* status, void* stream) {
+  using namespace ttb;
+  if (W > MAX_RANKS || W < 1 || H % 8 || ldo % 8 || (residual && ldr % 8)) return 901;
+  if (T == 0) return 0;
+  EpKsumParams p{make_peers(peer_ptrs, W), off_ret, off_ret_flags, (const __nv_bfloat16*)residual, ldr, (__nv_bfloat16*)out,
+                 ldo, k, H, W, rank, epoch, static_cast<unsigned long long>(budget_ms) * 1000000ull, status};
+  int threads = H / 8;
+  threads = threads > 256 ? 256 : ((threads + 31) / 32) * 32;
+  if (threads < 32) threads = 32;
+  ep_ksum_kernel<<<(unsigned)T, threads, 0, STREAM(stream)>>>(p);
+  LAUNCH_RET();
 }

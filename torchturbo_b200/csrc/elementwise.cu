@@ -1227,19 +1227,23 @@ TTB_EXPORT int ttb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void
   else
     rmsnorm_bwd_kernel<4><<<grid, threads, 0, STREAM(stream)>>>(DY, X, W, rstd, (const __nv_bfloat16*)dres_in,
                                                                (__nv_bfloat16*)dx, scratch, T, H, one_plus_w);
-  colsum_kernel<<<(H + 255) / 256, 256, 0, STREAM(stream)>>>(scratch, dw_out, grid, H);
   cudaError_t e = cudaGetLastError();
-  return e == cudaSuccess ? TTB_NOALLOC_OK : TTB_NOALLOC_ERR_LAUNCH + static_cast<int>(e);
+  if (e != cudaSuccess) return TTB_NOALLOC_ERR_LAUNCH_DX + static_cast<int>(e);
+  colsum_kernel<<<(H + 255) / 256, 256, 0, STREAM(stream)>>>(scratch, dw_out, grid, H);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? TTB_NOALLOC_OK : TTB_NOALLOC_ERR_LAUNCH_DW + static_cast<int>(e);
 }
 
 TTB_EXPORT const char* ttb_noalloc_strerror(int code) {
   if (code == TTB_NOALLOC_OK) return "ok";
   if (code == TTB_NOALLOC_ERR_SIZE)
     return "ttb_rmsnorm_bwd_noalloc: H must be a positive multiple of 8 and at most 8192 (TTB_NOALLOC_MAX_H), T >= 0";
-  if (code >= TTB_NOALLOC_ERR_SYMBOL && code < TTB_NOALLOC_ERR_SYMBOL + 1000 - 10)
+  if (code >= TTB_NOALLOC_ERR_SYMBOL && code < TTB_NOALLOC_ERR_SYMBOL + 10000)
     return "ttb_rmsnorm_bwd_noalloc: could not resolve the device address of the built-in scratch array "
-           "(cudaGetDevice / cudaGetSymbolAddress failed; code - 910 is the CUDA error)";
-  if (code >= TTB_NOALLOC_ERR_LAUNCH && code < TTB_NOALLOC_ERR_SIZE)
-    return "ttb_rmsnorm_bwd_noalloc: kernel launch failed (code - 400 is the CUDA error)";
+           "(cudaGetDevice / cudaGetSymbolAddress failed; code - 200000 is the CUDA error)";
+  if (code >= TTB_NOALLOC_ERR_LAUNCH_DW && code < TTB_NOALLOC_ERR_LAUNCH_DW + 10000)
+    return "ttb_rmsnorm_bwd_noalloc: launch of the weight-gradient column sum failed (code - 110000 is the CUDA error)";
+  if (code >= TTB_NOALLOC_ERR_LAUNCH_DX && code < TTB_NOALLOC_ERR_LAUNCH_DX + 10000)
+    return "ttb_rmsnorm_bwd_noalloc: launch of the dx / partial-sum kernel failed (code - 100000 is the CUDA error)";
   return "ttb_rmsnorm_bwd_noalloc: unknown error code";
 }

@@ -11,10 +11,25 @@
 // SwiGLU (gate and up column panels are loaded side by side into one 256-wide
 // accumulator; out = silu(g) * u * row_scale, pre-activations optionally kept).
 //
+//
+// Expert-parallel fusion (grouped-M only, both optional, see `EpFuse`):
+//   * push prologue: two extra warps per CTA copy this rank's routed token rows (plus routing weight and a
+//     return tag) straight into the owning ranks' expert-major receive buffers over NVLink while the tensor
+//     cores work; rows travel in (local expert, owner) order and every (source, expert) pair raises a flag on
+//     the owner when its last row has landed.  The TMA producer warp waits (bounded) for the flags of a
+//     tile's expert the first time the CTA meets it, so the math of the first experts overlaps the transfer
+//     of the later ones.  This is the token dispatch all-to-all of the reference
+//     (models/modules/moe/token_dispatcher.py:149-201) inside the fc1 GEMM.
+//   * scatter epilogue: every output row is stored straight into the source rank's [T*k, N] return buffer at
+//     the position its tag names (peer stores from the epilogue warps); the last CTA raises a "rows
+//     returned" flag on every peer.  This is the combine all-to-all (token_dispatcher.py:203-236) inside the
+//     fc2 / input-gradient GEMM.
+//
 // Replaces cuBLAS `F.linear`, `grouped_gemm.ops.gmm` and the torch.compile'd
 // SwiGLU of the reference (ops/providers/cuda/grouped_matmul.py:19-36,
 // ops/providers/cuda/swiglu.py:26-36, models/modules/moe/experts.py:181-254).
-#include "common.cuh"
+#include "peer.cuh"
+#include <cstring>
 
 namespace ttb {
 
@@ -24,7 +39,35 @@ constexpr unsigned KID_GEMM = 1;
 
 enum Epi : int { EPI_STORE = 0, EPI_SWIGLU = 1 };
 
+// Expert-parallel fusion parameters (device side).
+struct EpFuse {
+  PeerTable peers;
+  // push prologue
+  int push_on;
+  long long off_rows, off_vals, off_tags, off_flags;  // byte offsets inside every rank's symmetric buffer
+  const __nv_bfloat16* src;   // [T, lds] local token rows
+  long long lds;
+  const int* order;           // [n_entries] entry ids (token * k + slot) in send order
+  const int* expert;          // [n_entries] global expert of every entry
+  const int* dest_row;        // [n_entries] row on the owner
+  const float* val;           // [n_entries] scalar that travels with the row, or null
+  const int* counts;          // [E] rows this rank sends per global expert
+  int* sent;                  // [E + 1] rows sent per expert, then the next chunk to claim; all zero at launch
+  int n_entries, k, H, El, W, rank, epoch;
+  long long cap_rows;
+  unsigned long long budget_ns;
+  int* status;
+  // scatter epilogue
+  int scat_on;
+  long long off_ret, off_ret_vals, off_ret_flags;
+  const int* row_tag;         // [M] tags of this rank's received rows
+  const float* row_val;       // [M] scalar returned with the row, or null
+  int ret_epoch;
+  unsigned int* done_counter;
+};
+
 struct GemmParams {
+  EpFuse ep;
   int M, N, K;   // per-problem extents (N = output columns; for SwiGLU N = F)
   int m_tiles, n_tiles, groups_k;  // groups_k > 0 => grouped-K problem count
   void* C;
@@ -56,6 +99,9 @@ struct SmemLayout {
 
 constexpr int EPI_WARPS = 8;                       // two warps per TMEM lane quarter, each takes half of the columns
 constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
+constexpr int PUSH_WARPS = 2;                      // extra warps of a launch with the push prologue
+constexpr int GEMM_THREADS_PUSH = GEMM_THREADS + 32 * PUSH_WARPS;
+constexpr int PUSH_CHUNK = 8;                      // rows a push warp copies between two system-scope fences
 static_assert(EPI_WARPS == 8, "the staging area is sized for eight epilogue warps");
 
 // Epilogue staging.  tcgen05.ld hands every lane 32 consecutive columns of ITS row, so direct stores touch 32 rows per
@@ -71,7 +117,7 @@ __device__ __forceinline__ uint32_t epi_piece_addr64(uint32_t base, int row, int
 }
 
 template <int BN, bool A_MN, bool B_MN, int EPI>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_THREADS_PUSH, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
   using L = SmemLayout<BN, A_MN, B_MN>;
   constexpr int STAGES = L::STAGES;
@@ -85,9 +131,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   uint64_t* tempty = bars + 2 * STAGES + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
 
+  __shared__ uint32_t s_landed[32];   // push prologue: experts (up to 1024) whose rows are known to have landed
+  __shared__ int s_last_cta;
+
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
+  if (threadIdx.x < 32) s_landed[threadIdx.x] = 0u;
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
@@ -142,57 +192,94 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (elect_one()) {
-      tma_prefetch_desc(&tmA);
-      tma_prefetch_desc(&tmB);
-      int stage = 0;
-      uint32_t phase = 0;
+    int stage = 0;
+    uint32_t phase = 0;
+    // all k-blocks of one tile; run by one thread
+    auto load_tile = [&](int g, int mt, int nt, int bgroup) -> bool {
+      int k0, nkb;
+      krange(g, k0, nkb);
+      const int m0 = mt * BM;
+      const int n0 = nt * (EPI == EPI_SWIGLU ? BN / 2 : BN);
+      for (int kb = 0; kb < nkb; ++kb) {
+        if (!mbar_wait(&empty[stage], phase ^ 1, KID_GEMM, 1)) return false;
+        uint8_t* sa = smem + stage * L::STAGE_BYTES;
+        uint8_t* sb = sa + L::A_BYTES;
+        mbar_expect_tx(&full[stage], L::STAGE_BYTES);
+        const int kc = k0 + kb * BK;
+        if (!A_MN) {
+          tma_load_2d(sa, &tmA, &full[stage], kc, m0);
+        } else {
+          tma_load_2d(sa, &tmA, &full[stage], m0, kc);
+          tma_load_2d(sa + 8192, &tmA, &full[stage], m0 + 64, kc);
+        }
+        if (!B_MN) {
+          if (EPI == EPI_SWIGLU) {
+            tma_load_3d(sb, &tmB, &full[stage], kc, n0, bgroup);
+            tma_load_3d(sb + (BN / 2) * 128, &tmB, &full[stage], kc, p.F + n0, bgroup);
+          } else {
+            tma_load_3d(sb, &tmB, &full[stage], kc, n0, bgroup);
+          }
+        } else {
+          constexpr int PANELS = BN / 64;
+#pragma unroll
+          for (int q = 0; q < PANELS; ++q) {
+            int nc;
+            if (EPI == EPI_SWIGLU) {
+              nc = (q < PANELS / 2) ? (n0 + q * 64) : (p.F + n0 + (q - PANELS / 2) * 64);
+            } else {
+              nc = n0 + q * 64;
+            }
+            tma_load_3d(sb + q * 8192, &tmB, &full[stage], nc, kc, bgroup);
+          }
+        }
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+      return true;
+    };
+    if (!p.ep.push_on) {
+      if (elect_one()) {
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+        for (long long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+          int g, mt, nt;
+          decode(t, g, mt, nt);
+          int bgroup = 0;
+          if (p.tile_group) {
+            bgroup = p.tile_group[mt];
+            if (bgroup < 0) continue;
+          }
+          if (!load_tile(g, mt, nt, bgroup)) break;
+        }
+      }
+    } else {
+      // Push prologue active: the rows of A arrive from the peers while this kernel runs.  The whole warp walks the
+      // tile list; the first time the CTA meets an expert, lane s waits (bounded) for "source s has delivered its
+      // rows of this expert", then lane 0 issues the tile's loads.
+      if (lane == 0) {
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+      }
+      const int* my_flags = reinterpret_cast<const int*>(p.ep.peers.base[p.ep.rank] + p.ep.off_flags);
       bool ok = true;
       for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        int g, mt, nt, k0, nkb;
+        int g, mt, nt;
         decode(t, g, mt, nt);
-        int bgroup = 0;
-        if (p.tile_group) {
-          bgroup = p.tile_group[mt];
-          if (bgroup < 0) continue;
+        const int bgroup = p.tile_group[mt];
+        if (bgroup < 0) continue;
+        if (!((s_landed[bgroup >> 5] >> (bgroup & 31)) & 1u)) {
+          bool mine = true;
+          if (lane < p.ep.W)
+            mine = wait_flag(my_flags + bgroup * p.ep.W + lane, p.ep.epoch, p.ep.budget_ns, 9, lane, p.ep.status);
+          ok = __all_sync(0xffffffffu, mine);
+          if (!ok) break;
+          if (lane == 0) s_landed[bgroup >> 5] |= 1u << (bgroup & 31);
+          __syncwarp();
         }
-        krange(g, k0, nkb);
-        const int m0 = mt * BM;
-        const int n0 = nt * (EPI == EPI_SWIGLU ? BN / 2 : BN);
-        for (int kb = 0; kb < nkb; ++kb) {
-          if (!mbar_wait(&empty[stage], phase ^ 1, KID_GEMM, 1)) { ok = false; break; }
-          uint8_t* sa = smem + stage * L::STAGE_BYTES;
-          uint8_t* sb = sa + L::A_BYTES;
-          mbar_expect_tx(&full[stage], L::STAGE_BYTES);
-          const int kc = k0 + kb * BK;
-          if (!A_MN) {
-            tma_load_2d(sa, &tmA, &full[stage], kc, m0);
-          } else {
-            tma_load_2d(sa, &tmA, &full[stage], m0, kc);
-            tma_load_2d(sa + 8192, &tmA, &full[stage], m0 + 64, kc);
-          }
-          if (!B_MN) {
-            if (EPI == EPI_SWIGLU) {
-              tma_load_3d(sb, &tmB, &full[stage], kc, n0, bgroup);
-              tma_load_3d(sb + (BN / 2) * 128, &tmB, &full[stage], kc, p.F + n0, bgroup);
-            } else {
-              tma_load_3d(sb, &tmB, &full[stage], kc, n0, bgroup);
-            }
-          } else {
-            constexpr int PANELS = BN / 64;
-#pragma unroll
-            for (int q = 0; q < PANELS; ++q) {
-              int nc;
-              if (EPI == EPI_SWIGLU) {
-                nc = (q < PANELS / 2) ? (n0 + q * 64) : (p.F + n0 + (q - PANELS / 2) * 64);
-              } else {
-                nc = n0 + q * 64;
-              }
-              tma_load_3d(sb + q * 8192, &tmB, &full[stage], nc, kc, bgroup);
-            }
-          }
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        if (lane == 0) {
+          fence_proxy_async_all();
+          ok = load_tile(g, mt, nt, bgroup);
         }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       }
     }
   } else if (warp == 1) {
@@ -233,7 +320,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
     }
-  } else {
+  } else if (warp < 2 + EPI_WARPS) {
     // ------------------------------------------------------------ epilogue (warps 2..9)
     const int lane_group = warp & 3;  // TMEM lanes [32*lane_group, +32) are the ones this warp may touch
     const int col_half = (warp - 2) >> 2;  // which half of the tile's column chunks this warp stores
@@ -255,8 +342,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const int n0 = nt * BN;
         uint8_t* cbase = reinterpret_cast<uint8_t*>(p.C);
         const long long coff = static_cast<long long>(g) * p.c_group_stride + static_cast<long long>(row) * p.ldc;
-#pragma unroll 1
+        // bf16 output: first element of the four rows this lane stores in the row-major pass (null = skip the row).
+        // With the scatter epilogue a row goes to the rank it came from, at the entry its tag names.
+        __nv_bfloat16* rowptr[4] = {nullptr, nullptr, nullptr, nullptr};
+        if (!p.c_fp32) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int rr = mt * BM + lane_group * 32 + (lane >> 2) + 8 * j;
+            if (rr >= p.M) continue;
+            if (p.ep.scat_on) {
+              const int tag = __ldcg(p.ep.row_tag + rr);
+              if (tag >= 0)
+                rowptr[j] = reinterpret_cast<__nv_bfloat16*>(p.ep.peers.base[tag >> EP_TAG_SHIFT] + p.ep.off_ret) +
+                            static_cast<long long>(tag & EP_TAG_MASK) * p.ldc;
+            } else {
+              rowptr[j] = reinterpret_cast<__nv_bfloat16*>(cbase) + static_cast<long long>(g) * p.c_group_stride +
+                          static_cast<long long>(rr) * p.ldc;
+            }
+          }
+          if (p.ep.scat_on && p.ep.row_val && nt == 0 && col_half == 0 && row_ok) {
+            const int tag = __ldcg(p.ep.row_tag + row);
+            if (tag >= 0)
+              reinterpret_cast<float*>(p.ep.peers.base[tag >> EP_TAG_SHIFT] + p.ep.off_ret_vals)[tag & EP_TAG_MASK] =
+                  p.ep.row_val[row];
+          }
+        }
         constexpr int CH = BN / 32 / (EPI_WARPS / 4);
+#pragma unroll 1
         for (int c = col_half * CH; c < (col_half + 1) * CH; ++c) {
           const int col0 = n0 + c * 32;
           if (col0 >= p.N) break;  // uniform across the warp
@@ -300,14 +412,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 const int r = (lane >> 2) + 8 * j;
-                if (row_base + r >= p.M) continue;
+                if (rowptr[j] == nullptr) continue;
                 uint32_t w[8];
                 ld_shared_v4(epi_piece_addr(st, r, 2 * q), w[0], w[1], w[2], w[3]);
                 ld_shared_v4(epi_piece_addr(st, r, 2 * q + 1), w[4], w[5], w[6], w[7]);
                 float f[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(w[e]);
-                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(cbase) + gbase + static_cast<long long>(row_base + r) * p.ldc + col0 + 8 * q;
+                __nv_bfloat16* dst = rowptr[j] + col0 + 8 * q;
                 if (p.residual) {
                   const uint4 rr = *reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(row_base + r) * p.ldr + col0 + 8 * q);
                   const float2 a = unpack_bf16(rr.x), b = unpack_bf16(rr.y), c2 = unpack_bf16(rr.z), d = unpack_bf16(rr.w);
@@ -393,11 +505,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         // SwiGLU: accumulator columns [0,BN/2) = gate, [BN/2,BN) = up, for output columns n0..n0+BN/2.
         constexpr int HALF = BN / 2;
         const int n0 = nt * HALF;
-        const float scale = (p.row_scale && row_ok) ? p.row_scale[row] : 1.0f;
+        const float scale = (p.row_scale && row_ok) ? __ldcg(p.row_scale + row) : 1.0f;
         __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc;
         __nv_bfloat16* pre = p.preact ? p.preact + static_cast<long long>(row) * p.ld_preact : nullptr;
-#pragma unroll 1
         constexpr int CH = HALF / 32 / (EPI_WARPS / 4);
+#pragma unroll 1
         for (int c = col_half * CH; c < (col_half + 1) * CH; ++c) {
           const int col0 = n0 + c * 32;
           if (col0 >= p.N) break;
@@ -484,6 +596,81 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       if (lane == 0) mbar_arrive(&tempty[acc]);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
+    if (p.ep.scat_on) __threadfence_system();   // this thread's peer stores are ordered before the "returned" flag
+  } else if (p.ep.push_on) {
+    // ------------------------------------------------------------ push warps (warps 10..11)
+    // Entries are walked in send order (local expert major, owners rotated so that every owner receives from one
+    // source at a time).  A warp copies PUSH_CHUNK rows, fences at system scope, then counts the rows per expert:
+    // the warp whose count completes an expert raises this rank's flag for that expert on the owner.
+    const EpFuse& ep = p.ep;
+    const int E = ep.El * ep.W;
+    const int vec = ep.H / 8;
+    const bool healthy = *reinterpret_cast<volatile int*>(ep.status) == 0;
+    auto flag_of = [&](int e) -> int* {
+      const int o = e / ep.El;
+      return reinterpret_cast<int*>(ep.peers.base[o] + ep.off_flags) + (e - o * ep.El) * ep.W + ep.rank;
+    };
+    if (healthy) {
+      // Chunks are claimed from a counter (sent[E]) instead of being dealt out by CTA index: the owners' tiles wait for
+      // rows, so every row must go out even when some CTAs of this grid are not resident yet (another kernel holds
+      // their SM).  With a static split the rows of a waiting CTA would never leave while the resident CTAs spin.
+      int* next_chunk = ep.sent + E;
+      for (;;) {
+        long long chunk = 0;
+        if (lane == 0) chunk = atomicAdd(next_chunk, 1);
+        chunk = __shfl_sync(0xffffffffu, chunk, 0);
+        if (chunk == 0) {
+          // experts this rank sends nothing to: their owners must not wait for it
+          for (int e = lane; e < E; e += 32)
+            if (ep.counts[e] == 0) st_release_sys(flag_of(e), ep.epoch);
+        }
+        const long long c0 = chunk * PUSH_CHUNK;
+        if (c0 >= ep.n_entries) break;
+        const int cnt = static_cast<int>(ep.n_entries - c0 < PUSH_CHUNK ? ep.n_entries - c0 : PUSH_CHUNK);
+        int n_l = -1, e_l = -1, r_l = -1;
+        if (lane < cnt) {
+          n_l = ep.order[c0 + lane];
+          if (n_l >= 0 && n_l < ep.n_entries) {   // a broken order table must not become a wild read
+            e_l = ep.expert[n_l];
+            r_l = ep.dest_row[n_l];
+          }
+        }
+        for (int j = 0; j < cnt; ++j) {
+          const int n = __shfl_sync(0xffffffffu, n_l, j);
+          const int e = __shfl_sync(0xffffffffu, e_l, j);
+          const int r = __shfl_sync(0xffffffffu, r_l, j);
+          const int o = (e >= 0 && e < E) ? e / ep.El : -1;
+          if (o < 0 || r < 0 || r >= ep.cap_rows) {   // never write outside the owner's buffer
+            if (lane == 0) atomicExch(ep.status, 3);
+            continue;
+          }
+          const uint4* srow = reinterpret_cast<const uint4*>(ep.src + static_cast<long long>(n / ep.k) * ep.lds);
+          uint4* drow = reinterpret_cast<uint4*>(ep.peers.base[o] + ep.off_rows) + static_cast<long long>(r) * vec;
+          for (int c = lane; c < vec; c += 32 * 8) {
+            uint4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              if (c + 32 * u < vec) v[u] = srow[c + 32 * u];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              if (c + 32 * u < vec) drow[c + 32 * u] = v[u];
+          }
+          if (lane == 0) {
+            if (ep.val) reinterpret_cast<float*>(ep.peers.base[o] + ep.off_vals)[r] = ep.val[n];
+            reinterpret_cast<int*>(ep.peers.base[o] + ep.off_tags)[r] = (ep.rank << EP_TAG_SHIFT) | n;
+          }
+        }
+        __threadfence_system();
+        __syncwarp();
+        if (lane < cnt && e_l >= 0 && e_l < E) {
+          const int before = atomicAdd(ep.sent + e_l, 1);
+          if (before + 1 == ep.counts[e_l]) {
+            __threadfence_system();
+            st_release_sys(flag_of(e_l), ep.epoch);
+          }
+        }
+      }
+    }
   }
 
   tc_fence_before();
@@ -491,6 +678,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 2 * BN);
+  }
+  if (p.ep.scat_on) {
+    // the last CTA to get here tells every peer that this rank has returned all of its rows
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      s_last_cta = (atomicAdd(p.ep.done_counter, 1u) == gridDim.x - 1) ? 1 : 0;
+    }
+    __syncthreads();
+    if (s_last_cta) {
+      if (static_cast<int>(threadIdx.x) < p.ep.W) {
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<int*>(p.ep.peers.base[threadIdx.x] + p.ep.off_ret_flags) + p.ep.rank, p.ep.ret_epoch);
+      }
+      if (threadIdx.x == 0) *p.ep.done_counter = 0;
+    }
   }
 }
 
@@ -523,6 +725,35 @@ struct GemmArgs {
   void* preact;
   long long ld_preact;
   int num_sms;
+  const struct EpFuseArgs* ep;   // optional expert-parallel fusion (grouped-M launches only)
+};
+
+// Host description of the expert-parallel fusion of one launch (C ABI; see `EpFuse` for the meaning of the fields).
+struct EpFuseArgs {
+  const unsigned long long* peer_ptrs;   // [W] base address of every rank's symmetric buffer
+  int W, rank, El;
+  int* status;
+  long long budget_ms;
+  // push prologue
+  int push_on;
+  long long off_rows, off_vals, off_tags, off_flags;
+  const void* src;
+  long long lds;
+  const int* order;
+  const int* expert;
+  const int* dest_row;
+  const float* val;
+  const int* counts;
+  int* sent;
+  int n_entries, k, H, epoch;
+  long long cap_rows;
+  // scatter epilogue
+  int scat_on;
+  long long off_ret, off_ret_vals, off_ret_flags;
+  const int* row_tag;
+  const float* row_val;
+  int ret_epoch;
+  unsigned int* done_counter;
 };
 
 template <int BN, bool A_MN, bool B_MN, int EPI>
@@ -579,6 +810,23 @@ static int launch(const GemmArgs& a, cudaStream_t stream) {
     if (r) return 20000 + r;
   }
   GemmParams p;
+  memset(&p.ep, 0, sizeof(p.ep));
+  if (a.ep) {
+    const EpFuseArgs& e = *a.ep;
+    for (int i = 0; i < MAX_RANKS; ++i) p.ep.peers.base[i] = i < e.W ? e.peer_ptrs[i] : 0ull;
+    p.ep.W = e.W; p.ep.rank = e.rank; p.ep.El = e.El; p.ep.status = e.status;
+    p.ep.budget_ns = static_cast<unsigned long long>(e.budget_ms) * 1000000ull;
+    p.ep.push_on = e.push_on;
+    p.ep.off_rows = e.off_rows; p.ep.off_vals = e.off_vals; p.ep.off_tags = e.off_tags; p.ep.off_flags = e.off_flags;
+    p.ep.src = reinterpret_cast<const __nv_bfloat16*>(e.src); p.ep.lds = e.lds;
+    p.ep.order = e.order; p.ep.expert = e.expert; p.ep.dest_row = e.dest_row; p.ep.val = e.val;
+    p.ep.counts = e.counts; p.ep.sent = e.sent;
+    p.ep.n_entries = e.n_entries; p.ep.k = e.k; p.ep.H = e.H; p.ep.epoch = e.epoch; p.ep.cap_rows = e.cap_rows;
+    p.ep.scat_on = e.scat_on;
+    p.ep.off_ret = e.off_ret; p.ep.off_ret_vals = e.off_ret_vals; p.ep.off_ret_flags = e.off_ret_flags;
+    p.ep.row_tag = e.row_tag; p.ep.row_val = e.row_val; p.ep.ret_epoch = e.ret_epoch;
+    p.ep.done_counter = e.done_counter;
+  }
   p.M = a.M; p.N = a.N; p.K = a.K;
   constexpr int TN = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
   p.m_tiles = a.tile_group ? a.m_tiles_cap : (a.M + BM - 1) / BM;
@@ -600,7 +848,7 @@ static int launch(const GemmArgs& a, cudaStream_t stream) {
   long long total = static_cast<long long>(p.m_tiles) * p.n_tiles * (p.groups_k > 0 ? p.groups_k : 1);
   if (total <= 0) return 0;
   int grid = static_cast<int>(total < a.num_sms ? total : a.num_sms);
-  kfn<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(tmA, tmB, p);
+  kfn<<<grid, p.ep.push_on ? GEMM_THREADS_PUSH : GEMM_THREADS, L::TOTAL, stream>>>(tmA, tmB, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + static_cast<int>(e);
 }
@@ -620,6 +868,17 @@ TTB_EXPORT int ttb_gemm_bf16(const ttb::GemmArgs* args, void* stream_ptr) {
   if (reinterpret_cast<uintptr_t>(a.C) & 15) return 903;
   if (a.residual && ((a.ldr % 8) || (reinterpret_cast<uintptr_t>(a.residual) & 15))) return 904;
   if (a.epi == EPI_SWIGLU && ((a.F % 8) || a.c_fp32 || (a.preact && (a.ld_preact % 8)))) return 905;
+  if (a.ep) {
+    const EpFuseArgs& e = *a.ep;
+    if (!a.tile_group || a.groups_k > 0 || e.W < 1 || e.W > MAX_RANKS || e.El < 1 || e.El * e.W > 1024 || !e.status) return 906;
+    if (e.push_on && (a.a_mn || (e.H % 8) || (e.lds % 8) || !e.order || !e.expert || !e.dest_row || !e.counts || !e.sent ||
+                      e.n_entries < 0 || e.n_entries > EP_TAG_MASK || (e.off_rows % 16)))
+      return 907;
+    // the scatter epilogue lives in the bf16 row-major store path: whole 32-column chunks, no residual / accumulate
+    if (e.scat_on && (a.epi != EPI_STORE || a.c_fp32 || a.accumulate || a.residual || (a.N % 32) || !e.row_tag ||
+                      !e.done_counter || (e.off_ret % 16)))
+      return 908;
+  }
   const bool wide = (a.epi == EPI_SWIGLU) ? true : (a.N > 128);
 #define TTB_DISPATCH(AMN, BMN)                                                             \
   if (a.epi == EPI_SWIGLU) return launch<256, AMN, BMN, EPI_SWIGLU>(a, stream);            \

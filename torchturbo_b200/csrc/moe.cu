@@ -395,12 +395,16 @@ __global__ void perm_scan_kernel(const int* __restrict__ counts, int E, int* __r
 }
 
 __global__ void perm_rank_kernel(const int* __restrict__ idx, long long N, const int* __restrict__ seg_start,
-                                 int* __restrict__ row_of) {
+                                 int* __restrict__ row_of, const int* __restrict__ order_base, int* __restrict__ order) {
+  // `order` (optional): the inverse of a second packing of the same entries, order[order_base[e] + rank] = entry
   __shared__ int warp_tot[32];
-  __shared__ int base;
+  __shared__ int base, obase;
   const int e = blockIdx.x;
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  if (threadIdx.x == 0) base = seg_start[e];
+  if (threadIdx.x == 0) {
+    base = seg_start[e];
+    obase = order ? order_base[e] : 0;
+  }
   __syncthreads();
   for (long long i0 = 0; i0 < N; i0 += blockDim.x) {
     const long long i = i0 + threadIdx.x;
@@ -415,9 +419,15 @@ __global__ void perm_rank_kernel(const int* __restrict__ idx, long long N, const
       if (j < w) woff += v;
       tot += v;
     }
-    if (hit) row_of[i] = base + woff + pre;
+    if (hit) {
+      row_of[i] = base + woff + pre;
+      if (order) order[obase + woff + pre] = static_cast<int>(i);
+    }
     __syncthreads();
-    if (threadIdx.x == 0) base += tot;
+    if (threadIdx.x == 0) {
+      base += tot;
+      obase += tot;
+    }
     __syncthreads();
   }
 }
@@ -441,9 +451,11 @@ __global__ void perm_scatter_kernel(const __nv_bfloat16* __restrict__ src, long 
   }
 }
 
-// zero the pad rows [seg_start[e] + counts[e], seg_start[e+1]) of every expert
+// zero the pad rows [seg_start[e] + counts[e], seg_start[e+1]) of every expert (their scalars become 0, their return
+// tags -1); `zero_ints` (optional, `n_zero` entries) is cleared as well: the progress counters of the next exchange
 __global__ void perm_zero_pad_kernel(__nv_bfloat16* __restrict__ dst, long long ldd, const int* __restrict__ counts,
-                                     const int* __restrict__ seg_start, float* __restrict__ row_val_out, int H) {
+                                     const int* __restrict__ seg_start, float* __restrict__ row_val_out,
+                                     int* __restrict__ row_tag_out, int* __restrict__ zero_ints, int n_zero, int H) {
   const int e = blockIdx.x;
   const int r0 = seg_start[e] + counts[e], r1 = seg_start[e + 1];
   const uint4 z = make_uint4(0, 0, 0, 0);
@@ -452,8 +464,12 @@ __global__ void perm_zero_pad_kernel(__nv_bfloat16* __restrict__ dst, long long 
     const long long r = r0 + i / vec;
     reinterpret_cast<uint4*>(dst + r * ldd)[i % vec] = z;
   }
-  if (row_val_out)
-    for (int r = r0 + threadIdx.x; r < r1; r += blockDim.x) row_val_out[r] = 0.f;
+  for (int r = r0 + threadIdx.x; r < r1; r += blockDim.x) {
+    if (row_val_out) row_val_out[r] = 0.f;
+    if (row_tag_out) row_tag_out[r] = -1;
+  }
+  if (zero_ints)
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_zero; i += gridDim.x * blockDim.x) zero_ints[i] = 0;
 }
 
 // out[t, :] = sum_j w[t,j] * src[row_of[t*k + j], :] (+ residual[t, :]).  One block per token.
@@ -573,7 +589,7 @@ TTB_EXPORT int ttb_perm_index(const int* idx, long long N, int E, int* counts, i
   if (E > 1024) return 901;
   perm_count_kernel<<<E, 256, 0, STREAM(stream)>>>(idx, N, counts);
   perm_scan_kernel<<<1, 256, 0, STREAM(stream)>>>(counts, E, seg_start, tile_group, m_tiles_cap, status);
-  perm_rank_kernel<<<E, 256, 0, STREAM(stream)>>>(idx, N, seg_start, row_of);
+  perm_rank_kernel<<<E, 256, 0, STREAM(stream)>>>(idx, N, seg_start, row_of, nullptr, nullptr);
   LAUNCH_RET();
 }
 
@@ -581,7 +597,7 @@ TTB_EXPORT int ttb_perm_scatter(const void* src, long long lds, void* dst, long 
                                 const float* val, float* row_val_out, int* row_src_out, const int* counts,
                                 const int* seg_start, int E, long long N, int k, int H, void* stream) {
   if (H % 8 || lds % 8 || ldd % 8) return 901;
-  if (counts) perm_zero_pad_kernel<<<E, 256, 0, STREAM(stream)>>>((__nv_bfloat16*)dst, ldd, counts, seg_start, row_val_out, H);
+  if (counts) perm_zero_pad_kernel<<<E, 256, 0, STREAM(stream)>>>((__nv_bfloat16*)dst, ldd, counts, seg_start, row_val_out, nullptr, nullptr, 0, H);
   if (N > 0) {
     const long long blocks = (N + 7) / 8;
     perm_scatter_kernel<<<(unsigned)blocks, 256, 0, STREAM(stream)>>>((const __nv_bfloat16*)src, lds,
@@ -615,13 +631,29 @@ TTB_EXPORT int ttb_moe_seg_align() { return SEG_ALIGN; }
 // row_of[n] = base[idx[n]] + stable rank of n among the entries of its expert (base need not be a scan of counts)
 TTB_EXPORT int ttb_perm_rank(const int* idx, long long N, int E, const int* base, int* row_of, void* stream) {
   if (N == 0) return 0;
-  perm_rank_kernel<<<E, 256, 0, STREAM(stream)>>>(idx, N, base, row_of);
+  perm_rank_kernel<<<E, 256, 0, STREAM(stream)>>>(idx, N, base, row_of, nullptr, nullptr);
+  LAUNCH_RET();
+}
+
+// same, plus order[order_base[idx[n]] + rank] = n : the entries listed in a second (send) order
+TTB_EXPORT int ttb_perm_rank_order(const int* idx, long long N, int E, const int* base, int* row_of, const int* order_base,
+                                   int* order, void* stream) {
+  if (N == 0) return 0;
+  perm_rank_kernel<<<E, 256, 0, STREAM(stream)>>>(idx, N, base, row_of, order_base, order);
   LAUNCH_RET();
 }
 
 TTB_EXPORT int ttb_perm_zero_pad(void* dst, long long ldd, const int* counts, const int* seg_start, float* row_val,
                                  int E, int H, void* stream) {
   if (H % 8 || ldd % 8) return 901;
-  perm_zero_pad_kernel<<<E, 256, 0, STREAM(stream)>>>((__nv_bfloat16*)dst, ldd, counts, seg_start, row_val, H);
+  perm_zero_pad_kernel<<<E, 256, 0, STREAM(stream)>>>((__nv_bfloat16*)dst, ldd, counts, seg_start, row_val, nullptr, nullptr, 0, H);
+  LAUNCH_RET();
+}
+
+TTB_EXPORT int ttb_perm_zero_pad_tags(void* dst, long long ldd, const int* counts, const int* seg_start, float* row_val,
+                                      int* row_tag, int* zero_ints, int n_zero, int E, int H, void* stream) {
+  if (H % 8 || ldd % 8) return 901;
+  perm_zero_pad_kernel<<<E, 256, 0, STREAM(stream)>>>((__nv_bfloat16*)dst, ldd, counts, seg_start, row_val, row_tag, zero_ints,
+                                                     n_zero, H);
   LAUNCH_RET();
 }

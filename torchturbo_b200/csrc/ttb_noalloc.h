@@ -30,10 +30,13 @@ extern "C" {
 #define TTB_NOALLOC_MAX_H 8192
 #define TTB_NOALLOC_BLOCKS 64
 
+/* Return codes.  The three error classes use disjoint ranges (a CUDA error code is always below 10000), so a code
+ * names its class and, for the last three, the CUDA error: code - base. */
 #define TTB_NOALLOC_OK 0
-#define TTB_NOALLOC_ERR_SIZE 901     /* H not a multiple of 8, or H > TTB_NOALLOC_MAX_H, or T < 0 */
-#define TTB_NOALLOC_ERR_SYMBOL 910   /* cudaGetSymbolAddress / cudaGetDevice failed; add the CUDA error code */
-#define TTB_NOALLOC_ERR_LAUNCH 400   /* kernel launch failed; add the CUDA error code */
+#define TTB_NOALLOC_ERR_SIZE 901            /* H not a multiple of 8, or H > TTB_NOALLOC_MAX_H, or T < 0 */
+#define TTB_NOALLOC_ERR_LAUNCH_DX 100000    /* launch of the dx / partial-sum kernel failed; + CUDA error code */
+#define TTB_NOALLOC_ERR_LAUNCH_DW 110000    /* launch of the weight-gradient column sum failed; + CUDA error code */
+#define TTB_NOALLOC_ERR_SYMBOL 200000       /* cudaGetDevice / cudaGetSymbolAddress failed; + CUDA error code */
 
 /* dy, x, w, dres_in (may be NULL), dx: bf16 device pointers, row-major [T, H] ([H] for w); rstd: fp32 [T];
  * dw_out: fp32 [H].  `stream` is a cudaStream_t.  Returns TTB_NOALLOC_OK or one of the codes above. */

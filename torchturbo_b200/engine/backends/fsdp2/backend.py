@@ -654,6 +654,17 @@ class FSDP2Backend(BaseBackend):
                         p._tt_grad_scaled = True
 
     @torch.no_grad()
+    def _peer_status_flag(self) -> torch.Tensor | None:
+        """Device bool: any peer-memory workspace of this rank has a non-zero status word (None without workspaces)."""
+        if self.device.type != "cuda":
+            return None
+        from ...health import peer_workspaces
+
+        words = [ws.status.reshape(1) for ws in peer_workspaces(self) if isinstance(getattr(ws, "status", None), torch.Tensor)]
+        if not words:
+            return None
+        return (torch.cat(words) if len(words) > 1 else words[0]).ne(0).any()
+
     def clip_grad_norm_(self, model: nn.Module, max_norm: float, optimizer=None) -> torch.Tensor:
         """Global L2 norm over dense (world-sharded), expert (edp-sharded, unique per EP rank) and replicated /
         single-rank parameters; every gradient is then scaled by `min(1, max_norm / (norm + 1e-6))`.
@@ -715,6 +726,13 @@ class FSDP2Backend(BaseBackend):
                              sums["local"] + sumsq(sq["local"]))
         sharded = dense + moe
         if self.world_size > 1:
+            # A peer-memory kernel that timed out or overflowed its receive buffer on ANY rank poisons the norm: the
+            # status words ride on the all-reduce below (no extra collective, no host read), the coefficient becomes
+            # NaN on every rank, the fused AdamW kernel skips the update, and the loop's finite check of the norm raises
+            # in this very step instead of training on dropped rows until the next logging boundary.
+            bad = self._peer_status_flag()
+            if bad is not None:
+                sharded = torch.where(bad, torch.full_like(sharded, float("nan")), sharded)
             # FSDP shards and EP-local experts are disjoint across the world; replicated ones are not summed
             dist.all_reduce(sharded)
         total = (sharded + local).sqrt()

@@ -370,7 +370,9 @@ class TorchTurboEngine(RLMixin):
 
     def check_health(self) -> None:
         """Turn a timeout / overflow recorded by any rank's peer-memory kernels into an exception on every rank.
-        Runs at logging boundaries (one small device read per workspace), never inside a step."""
+        Runs at logging and checkpoint boundaries (one small device read per workspace).  Inside a step the same
+        status words poison the gradient norm on the device (`FSDP2Backend.clip_grad_norm_`), so the update of a
+        failed step is skipped without a host read."""
         if self.backend.world_size > 1 and self.runtime.turbo_device.value == "cuda":
             from .health import check_peer_status
 
@@ -409,9 +411,11 @@ class TorchTurboEngine(RLMixin):
     # checkpoint facade
     # ------------------------------------------------------------------------------------------
     def save_model(self, model: nn.Module, output_dir: str, *, final: bool = False, **kwargs: Any) -> None:
+        self.check_health()   # never persist weights trained on a failed peer-memory exchange
         self.checkpoint.save_model(model, output_dir, final=final, source_path=self._model_source, **kwargs)
 
     def save_optimizer_and_scheduler(self, model, optimizer, scheduler, output_dir: str) -> None:
+        self.check_health()
         self.checkpoint.save_optimizer_and_scheduler(model, optimizer, scheduler, output_dir)
 
     def load_optimizer_and_scheduler(self, model, optimizer, scheduler, checkpoint_dir: str) -> None:

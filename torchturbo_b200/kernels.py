@@ -42,6 +42,30 @@ class _GemmArgs(C.Structure):
         ("epi", C.c_int), ("F", C.c_int),
         ("row_scale", C.c_void_p), ("preact", C.c_void_p), ("ld_preact", C.c_longlong),
         ("num_sms", C.c_int),
+        ("ep", C.c_void_p),
+    ]
+
+
+class EpFuseArgs(C.Structure):
+    """Expert-parallel fusion of one grouped GEMM launch (`struct EpFuseArgs` of csrc/gemm.cu): the push prologue that
+    sends this rank's routed rows to their owners from inside the kernel, and / or the scatter epilogue that stores every
+    output row into the return buffer of the rank it came from."""
+
+    _fields_ = [
+        ("peer_ptrs", C.c_void_p), ("W", C.c_int), ("rank", C.c_int), ("El", C.c_int),
+        ("status", C.c_void_p), ("budget_ms", C.c_longlong),
+        ("push_on", C.c_int),
+        ("off_rows", C.c_longlong), ("off_vals", C.c_longlong), ("off_tags", C.c_longlong), ("off_flags", C.c_longlong),
+        ("src", C.c_void_p), ("lds", C.c_longlong),
+        ("order", C.c_void_p), ("expert", C.c_void_p), ("dest_row", C.c_void_p), ("val", C.c_void_p),
+        ("counts", C.c_void_p), ("sent", C.c_void_p),
+        ("n_entries", C.c_int), ("k", C.c_int), ("H", C.c_int), ("epoch", C.c_int),
+        ("cap_rows", C.c_longlong),
+        ("scat_on", C.c_int),
+        ("off_ret", C.c_longlong), ("off_ret_vals", C.c_longlong), ("off_ret_flags", C.c_longlong),
+        ("row_tag", C.c_void_p), ("row_val", C.c_void_p),
+        ("ret_epoch", C.c_int),
+        ("done_counter", C.c_void_p),
     ]
 
 
@@ -75,7 +99,7 @@ def lib():
 # kernels launched per C entry point (used to report how many of this library's kernels ran in a region)
 _LAUNCHES_PER_CALL = {"ttb_rmsnorm_bwd": 2, "ttb_layernorm_bwd": 2, "ttb_bias_act_bwd": 2, "ttb_causal_conv1d_bwd": 3,
                       "ttb_causal_conv1d_row_blocks": 0, "ttb_ep_dispatch_all": 5, "ttb_ep_dispatch_rows": 3,
-                      "ttb_ep_combine_all": 3, "ttb_ep_combine_vals": 4, "ttb_router_fwd": 2, "ttb_perm_index": 3, "ttb_perm_scatter": 2,
+                      "ttb_ep_combine_all": 3, "ttb_ep_combine_vals": 4, "ttb_ep_prepare": 3, "ttb_ep_prepare_bwd": 1, "ttb_router_fwd": 2, "ttb_perm_index": 3, "ttb_perm_scatter": 2,
                       "ttb_gemm_status": 0}
 LAUNCH_COUNT = 0
 
@@ -143,6 +167,7 @@ def gemm(
     swiglu: bool = False,
     row_scale: torch.Tensor | None = None,
     preact: torch.Tensor | None = None,
+    ep: "EpFuseArgs | None" = None,
 ) -> torch.Tensor:
     """tcgen05 GEMM ``C = op(A) @ op(B)`` on bf16 operands with fp32 accumulation.
 
@@ -215,6 +240,8 @@ def gemm(
         assert preact.dtype == torch.bfloat16
         args.preact, args.ld_preact = preact.data_ptr(), preact.stride(0)
     args.num_sms = num_sms(a.device.index)
+    if ep is not None:
+        args.ep = C.addressof(ep)
     _check(lib().ttb_gemm_bf16(C.byref(args), _stream()), "ttb_gemm_bf16")
     return out
 
@@ -728,6 +755,80 @@ def ep_combine_all(peer_ptrs, *, off_rows, off_vals, off_flags, expert, dest_row
                                     C.c_longlong(cap_rows), _p(status), _stream()),
            "ttb_ep_combine_vals" if want_vals else "ttb_ep_combine_all")
     return out, vals
+
+
+class _EpPrepareArgs(C.Structure):
+    _fields_ = [
+        ("peer_ptrs", C.c_void_p), ("off_counts", C.c_longlong), ("off_flags_counts", C.c_longlong),
+        ("counts", C.c_void_p), ("expert", C.c_void_p),
+        ("recv_rows_local", C.c_void_p), ("recv_vals_local", C.c_void_p), ("recv_tags_local", C.c_void_p),
+        ("seg_start", C.c_void_p), ("recv_counts", C.c_void_p), ("tile_group", C.c_void_p), ("dest_base", C.c_void_p),
+        ("dest_row", C.c_void_p), ("send_base", C.c_void_p), ("order", C.c_void_p),
+        ("sent", C.c_void_p), ("status", C.c_void_p),
+        ("N", C.c_longlong), ("budget_ms", C.c_longlong),
+        ("rank", C.c_int), ("W", C.c_int), ("E", C.c_int), ("H", C.c_int), ("m_tiles_cap", C.c_int),
+        ("epoch_counts", C.c_int), ("exchange", C.c_int),
+    ]
+
+
+def ep_prepare(peer_ptrs, *, off_counts, off_flags_counts, counts, expert, recv_rows, recv_vals, recv_tags, sent, status,
+               rank, world, num_experts, m_tiles_cap, epoch_counts, budget_ms, tables=None):
+    """Everything a fused expert-parallel GEMM needs before it starts, in one host call.  Forward (`tables=None`):
+    counts exchange with the peers, layout tables, destination row and send order of every entry, padding rows of the
+    receive buffer cleared; returns `(seg_start, recv_counts, tile_group, dest_row, order)`.  Backward (`tables =
+    (seg_start, recv_counts)` of the forward pass): only the receive buffer is prepared again."""
+    dev = expert.device
+    N = expert.numel()
+    El = num_experts // world
+    a = _EpPrepareArgs()
+    if tables is None:
+        # one int32 block: seg_start [El+1] | recv_counts [El] | tile_group [cap] | dest_base [E] | send_base [E]
+        meta = torch.empty(2 * El + 1 + m_tiles_cap + 2 * num_experts, dtype=torch.int32, device=dev)
+        seg_start, recv_counts = meta[:El + 1], meta[El + 1:2 * El + 1]
+        o = 2 * El + 1
+        tile_group = meta[o:o + m_tiles_cap]
+        dest_base, send_base = meta[o + m_tiles_cap:o + m_tiles_cap + num_experts], meta[o + m_tiles_cap + num_experts:]
+        rows = torch.empty(2, N, dtype=torch.int32, device=dev)
+        dest_row, order = rows[0], rows[1]
+        a.exchange, a.counts = 1, counts.data_ptr()
+        a.tile_group, a.dest_base, a.send_base = tile_group.data_ptr(), dest_base.data_ptr(), send_base.data_ptr()
+        a.dest_row, a.order = dest_row.data_ptr(), order.data_ptr()
+    else:
+        seg_start, recv_counts = tables
+        tile_group = dest_row = order = None
+        a.exchange = 0
+    a.peer_ptrs = C.addressof(peer_ptrs)
+    a.off_counts, a.off_flags_counts = off_counts, off_flags_counts
+    a.expert = expert.data_ptr()
+    a.recv_rows_local, a.recv_vals_local, a.recv_tags_local = recv_rows.data_ptr(), recv_vals.data_ptr(), recv_tags.data_ptr()
+    a.seg_start, a.recv_counts = seg_start.data_ptr(), recv_counts.data_ptr()
+    a.sent, a.status = sent.data_ptr(), status.data_ptr()
+    a.N, a.budget_ms = N, budget_ms
+    a.rank, a.W, a.E, a.H, a.m_tiles_cap = rank, world, num_experts, recv_rows.shape[1], m_tiles_cap
+    a.epoch_counts = epoch_counts
+    _check(lib().ttb_ep_prepare(C.byref(a), _stream()), "ttb_ep_prepare" if tables is None else "ttb_ep_prepare_bwd")
+    return seg_start, recv_counts, tile_group, dest_row, order
+
+
+def ep_save(recv_rows, recv_vals, seg_start, El):
+    """Copies the rows (and their scalars) that landed in the receive buffer; the row count is read on the device."""
+    cap, H = recv_rows.shape
+    rows = torch.empty_like(recv_rows)
+    vals = torch.empty_like(recv_vals) if recv_vals is not None else None
+    grid = 4 * num_sms(recv_rows.device.index)
+    _check(lib().ttb_ep_save(_p(recv_rows), _p(rows), _p(recv_vals), _p(vals), _p(seg_start), C.c_int(El), C.c_int(H),
+                             C.c_longlong(cap), C.c_int(grid), _stream()), "ttb_ep_save")
+    return rows, vals
+
+
+def ep_ksum(peer_ptrs, off_ret, off_ret_flags, T, k, H, world, rank, epoch, budget_ms, status, residual=None):
+    """Waits for every owner's "rows returned" flag, then sums the k returned rows of every token (+ residual)."""
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=status.device)
+    _check(lib().ttb_ep_ksum(peer_ptrs, C.c_longlong(off_ret), C.c_longlong(off_ret_flags), _p(residual),
+                             C.c_longlong(residual.stride(0) if residual is not None else 0), _p(out),
+                             C.c_longlong(out.stride(0)), C.c_longlong(T), C.c_int(k), C.c_int(H), C.c_int(world),
+                             C.c_int(rank), C.c_int(epoch), C.c_longlong(budget_ms), _p(status), _stream()), "ttb_ep_ksum")
+    return out
 
 
 def ep_scatter(peer_ptrs, off_rows, off_vals, off_flags, src, expert, dest_row, val, k, El, rank, world, epoch, cap_rows,

@@ -65,9 +65,14 @@ def train_step(engine, model, optimizer, micro_batches, *, max_grad_norm: float 
         engine.collect_metrics(model)
         d = loss.detach().float() * mult
         total = d if total is None else total + d
-    if check_finite:
-        assert_finite(total, "loss")
     gnorm = engine.clip_grad_norm_(model, max_grad_norm, optimizer)
+    if check_finite:
+        try:
+            # one host read for both; the norm is NaN on every rank when a peer-memory kernel of any rank failed
+            assert_finite(torch.stack([total.reshape(()), gnorm.detach().float().reshape(())]), "loss or gradient norm")
+        except FloatingPointError:
+            engine.check_health()     # names the failed exchange (timeout / receive overflow) when that is the cause
+            raise
     optimizer.step()
     optimizer.zero_grad(set_to_none=True)
     return total / ga, gnorm

@@ -476,6 +476,15 @@ class MoELayer(BaseMoELayer):
         if self.config.moe_apply_probs_on_input:
             xin = (x.float() * prob.view(-1, 1)).to(x.dtype)
             prob = torch.ones_like(prob)
+        fused = getattr(self.token_dispatcher, "fused_experts", None)
+        if fused is not None:
+            w1, w2 = self.experts.views()
+            if self.token_dispatcher.fused_usable(xin, w1, w2):
+                # exchange inside the grouped GEMMs (peer-memory push prologue / scatter epilogue)
+                out = fused(xin, idx, prob, w1, w2, counts=getattr(self.router, "last_counts", None)).to(x.dtype)
+                if self.shared_experts is not None:
+                    out = out + self.shared_experts(x)
+                return out.view(shape), logits
         if getattr(self.token_dispatcher, "accepts_counts", False):
             perm, tpe, state = self.token_dispatcher.dispatch(xin, idx, prob, counts=getattr(self.router, "last_counts", None))
         else:
