@@ -13,7 +13,7 @@ MOE = dict(model_type="qwen3_moe", num_hidden_layers=2, hidden_size=64, num_atte
            vocab_size=512)
 
 
-def _train(rank, world, mc, plan, steps, same_data, out_q=None, ac=False):
+def _train(rank, world, mc, plan, steps, same_data, out_q=None, ac=False, backend_config=None, different_data=False):
     from torchturbo_b200.data import PackedCollator, SyntheticPackedDataset
     from torchturbo_b200.engine import EngineConfig, TorchTurboEngine
     from torchturbo_b200.engine.optimizers import OptimizerClassPlan
@@ -21,7 +21,8 @@ def _train(rank, world, mc, plan, steps, same_data, out_q=None, ac=False):
 
     eng = TorchTurboEngine(EngineConfig.from_dict({"mixed_precision": "fp32", "parallel_plan": plan,
                                                    "moe": {"aux_loss_coeff": 1e-2},
-                                                   "activation_checkpointing": {"enabled": ac}}))
+                                                   "activation_checkpointing": {"enabled": ac},
+                                                   **({"backend_config": backend_config} if backend_config else {})}))
     model = eng.build_model(None, load_weights=False, init_kwargs={"config": dict(mc), "seed": 0})
     opt = eng.prepare_optimizer(model, OptimizerClassPlan(torch.optim.AdamW, lr=1e-2, weight_decay=0.0))
     ds = SyntheticPackedDataset(steps * world, 64, mc["vocab_size"], num_docs=3, seed=5)
@@ -55,6 +56,44 @@ def test_fsdp2_dense_world2_matches_single_process():
     run_distributed(_w_dense, 1)
     run_distributed(_w_dense, 2)
     a, b = torch.load("/tmp/tt_dense_world1.pt"), torch.load("/tmp/tt_dense_world2.pt")
+    assert torch.allclose(a, b, rtol=1e-4, atol=1e-5), (a, b)
+
+
+def _w_replicated(rank, world, kind, replicate):
+    """Different data per rank, two micro-batches per step: replicated decoder layers (flat gradient buffer, one
+    all-reduce per step) must train exactly like FSDP-sharded ones."""
+    import torch.distributed as dist
+
+    from torchturbo_b200.data import PackedCollator, SyntheticPackedDataset
+    from torchturbo_b200.engine import EngineConfig, TorchTurboEngine
+    from torchturbo_b200.engine.optimizers import OptimizerClassPlan
+    from torchturbo_b200.loops import train_step
+
+    mc = DENSE if kind == "dense" else MOE
+    eng = TorchTurboEngine(EngineConfig.from_dict({"mixed_precision": "fp32", "moe": {"aux_loss_coeff": 1e-2},
+                                                   "parallel_plan": {"sp_size": 1, "ep_size": world if kind == "moe" else 1},
+                                                   "activation_checkpointing": {"enabled": False},
+                                                   "backend_config": {"replicate_layers": replicate}}))
+    model = eng.build_model(None, load_weights=False, init_kwargs={"config": dict(mc), "seed": 0})
+    assert bool(eng.backend.replicated_units) == replicate
+    opt = eng.prepare_optimizer(model, OptimizerClassPlan(torch.optim.AdamW, lr=1e-2, weight_decay=0.0))
+    ds = SyntheticPackedDataset(32, 64, mc["vocab_size"], num_docs=3, seed=5)
+    out = []
+    for i in range(3):
+        mbs = [PackedCollator()([ds[(2 * i + j) * world + rank]]) for j in range(2)]
+        loss, gn = train_step(eng, model, opt, mbs)
+        t = torch.tensor([float(loss), float(gn)])
+        dist.all_reduce(t)
+        out.append(t / world)
+    if rank == 0:
+        torch.save(torch.stack(out), f"/tmp/tt_rep_{kind}_{int(replicate)}.pt")
+
+
+@pytest.mark.parametrize("kind", ["dense", "moe"])
+def test_replicated_layers_match_fsdp_sharded_layers(kind):
+    run_distributed(_w_replicated, 2, kind, False)
+    run_distributed(_w_replicated, 2, kind, True)
+    a, b = torch.load(f"/tmp/tt_rep_{kind}_0.pt"), torch.load(f"/tmp/tt_rep_{kind}_1.pt")
     assert torch.allclose(a, b, rtol=1e-4, atol=1e-5), (a, b)
 
 

@@ -18,7 +18,7 @@ from dist_utils import run_distributed
 transformers = pytest.importorskip("transformers")
 
 DENSE = dict(vocab_size=320, hidden_size=64, intermediate_size=160, num_hidden_layers=2, num_attention_heads=4,
-             num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False,
+             num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-5, rope_theta=50000.0, tie_word_embeddings=False,
              max_position_embeddings=512, attention_bias=False)
 MOE = dict(DENSE, moe_intermediate_size=48, num_experts=8, num_experts_per_tok=2, norm_topk_prob=True, decoder_sparse_step=1,
            mlp_only_layers=[], router_aux_loss_coef=0.0, output_router_logits=False)
@@ -66,7 +66,6 @@ def _batch(vocab, lens, seed=0):
 def _w_parity(rank, world, kind, root):
     torch.manual_seed(0)
     cfg, cls = _hf(kind)
-    cfg.torch_dtype = torch.float32
     hf = cls(cfg).float().eval()
     src = os.path.join(root, "hf_src")
     hf.save_pretrained(src, safe_serialization=True)
@@ -96,11 +95,16 @@ def _w_parity(rank, world, kind, root):
     # ---- (b) this engine's HF export -> transformers
     ckpt = os.path.join(root, "checkpoint-1")
     eng.save_model(model, ckpt, final=True)
-    back = transformers.AutoModelForCausalLM.from_pretrained(os.path.join(ckpt, "huggingface"), torch_dtype=torch.float32).eval()
-    err = (_hf_logits(back, batch["input_ids"], lens) - ref_logits).abs().max().item()
-    assert err < 1e-4, f"{kind}: exported checkpoint differs from the source by {err}"
+    back = transformers.AutoModelForCausalLM.from_pretrained(os.path.join(ckpt, "huggingface"), dtype=torch.float32).eval()
     sd_a, sd_b = hf.state_dict(), back.state_dict()
     assert set(sd_a) == set(sd_b), sorted(set(sd_a) ^ set(sd_b))[:8]
+    # the export is written in bf16 (the training compute dtype): every tensor must be the bf16 rounding of its source,
+    # in the source's own name and layout, so the logits equal those of the source model with bf16-rounded weights
+    for k in sd_a:
+        assert torch.equal(sd_b[k].float(), sd_a[k].bfloat16().float()), k
+    hf.load_state_dict({k: v.bfloat16().float() for k, v in sd_a.items()})
+    err = (_hf_logits(back, batch["input_ids"], lens) - _hf_logits(hf, batch["input_ids"], lens)).abs().max().item()
+    assert err < 1e-5, f"{kind}: exported checkpoint differs from the (bf16-rounded) source by {err}"
 
 
 @pytest.mark.parametrize("kind", ["qwen3", "qwen3_moe"])

@@ -11,20 +11,29 @@ from torchturbo_b200.adapters import msswift as sw
 from torchturbo_b200.adapters.msswift import session
 
 
-def test_raw_dataset_rows_are_validated_before_tokenisation():
+def test_raw_dataset_rows_are_audited_before_tokenisation():
+    from torchturbo_b200.adapters.msswift.data_check import audit_rows, classify_row
+
     assert sw.check_row({"messages": "hello"}) is None
     assert sw.check_row({"messages": "<image> a <image>", "images": ["a.png", {"path": "b.png"}]}) is None
-    assert "comma-joined" in sw.check_row({"messages": "<image>", "images": "a.png,b.png"})
-    assert "must be a list" in sw.check_row({"messages": "<image>", "images": "a.png"})
-    assert "without a path" in sw.check_row({"messages": "<image>", "images": [{"bytes": b"x"}]})
-    assert "tag count 1 != image count 2" in sw.check_row({"messages": "<image>", "images": ["a", "b"]})
+    assert classify_row({"messages": "<image>", "images": "a.png,b.png"})[0] == "joined_paths"
+    assert classify_row({"messages": "<image>", "images": ["a.png,b.png"]})[0] == "joined_paths"
+    assert classify_row({"messages": "<image>", "images": "a.png"})[0] == "not_a_list"
+    assert classify_row({"messages": "<image>", "images": [{"bytes": b"x"}]})[0] == "empty_reference"
+    assert classify_row({"messages": "<image>", "images": ["a", "b"]}) == ("placeholder_mismatch", "1 placeholder(s), 2 image(s)")
+    assert "different number" in sw.check_row({"messages": "<image>", "images": ["a", "b"]})
 
     class DS(list):
         column_names = ["messages", "images"]
 
-    sw.validate_raw_dataset(DS([{"messages": "<image>", "images": ["a"]}]))
-    with pytest.raises(ValueError, match="row 1: <image> tag count"):
-        sw.validate_raw_dataset(DS([{"messages": "<image>", "images": ["a"]}, {"messages": "x", "images": ["a"]}]), "train")
+    good = {"messages": "<image>", "images": ["a"]}
+    sw.validate_raw_dataset(DS([good]))
+    # every broken rule is reported with its count, not just the first offender
+    rows = DS([good, {"messages": "x", "images": ["a"]}, {"messages": "<image>", "images": "p,q"}, {"messages": "y", "images": ["b"]}])
+    rep = audit_rows(rows)
+    assert rep.rows == 4 and rep.by_rule["placeholder_mismatch"] == [1, 3] and rep.by_rule["joined_paths"] == [2]
+    with pytest.raises(ValueError, match=r"3 of 4 multimodal rows(.|\n)*2 row\(s\)(.|\n)*#1 (.|\n)*1 row\(s\)"):
+        sw.validate_raw_dataset(rows, "train")
     sw.validate_raw_dataset(iter([{"images": "bad,bad"}]))        # streaming datasets are not walked
     text_only = DS([{"messages": "x"}])
     text_only.column_names = ["messages"]

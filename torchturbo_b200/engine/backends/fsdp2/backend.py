@@ -38,22 +38,31 @@ from ..base import BaseBackend
 
 logger = get_logger(__name__)
 
-_RECOMPUTE = {"active": False}
+from ....utils.recompute import in_recompute, recompute_ctx as _recompute_ctx  # noqa: E402,F401  (re-exported)
 
 
-def in_recompute() -> bool:
-    """True while activation checkpointing replays a forward pass (statistics must not be counted twice)."""
-    return _RECOMPUTE["active"]
+def _reentrant_checkpoint(fn, args: tuple, kwargs: dict):
+    """`torch.utils.checkpoint` in reentrant mode around `fn(*args, **kwargs)` with the three things that mode does
+    not do by itself (engine/backends/fsdp2/backend.py:875-990 of the reference has the same glue):
+      * keyword arguments: the reentrant implementation only takes positional ones, so they are bound beforehand;
+      * recompute marking: the replay runs inside the checkpoint's backward with gradients enabled, the original pass
+        with gradients disabled; the replay is wrapped in the recompute context so that router statistics and
+        expert-bias token counts are not accumulated a second time;
+      * gradient anchor: when no tensor argument requires a gradient (frozen embeddings in front of the first layer,
+        LoRA), the reentrant implementation would skip the backward of the whole segment; a scalar that requires a
+        gradient rides along as an extra argument."""
+    from torch.utils.checkpoint import checkpoint
 
+    def body(_anchor, *a):
+        if torch.is_grad_enabled():          # the replay inside CheckpointFunction.backward
+            with _recompute_ctx():
+                return fn(*a, **kwargs)
+        return fn(*a, **kwargs)
 
-@contextlib.contextmanager
-def _recompute_ctx():
-    prev = _RECOMPUTE["active"]
-    _RECOMPUTE["active"] = True
-    try:
-        yield
-    finally:
-        _RECOMPUTE["active"] = prev
+    tensors = [a for a in args if isinstance(a, torch.Tensor)]
+    dev = tensors[0].device if tensors else None
+    anchor = torch.zeros((), device=dev, requires_grad=True) if not any(t.requires_grad for t in tensors) else None
+    return checkpoint(body, anchor, *args, use_reentrant=True)
 
 
 def confidence_entropy_sum(logits: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100):
@@ -94,6 +103,10 @@ class FSDP2Backend(BaseBackend):
         self.dp_rank, self.dp_size = self.rank, self.world_size
         self.gradient_scaling_factor = 1.0
         self.local_units: list[nn.Module] = []
+        self.replicated_units: list[nn.Module] = []      # decoder layers kept replicated (`replicate_layers`)
+        self._rep_flat: torch.Tensor | None = None       # flat fp32 gradient buffer of their parameters
+        self._rep_params: list[nn.Parameter] = []
+        self._rep_synced = False
         self.fsdp_units: list[nn.Module] = []
         self.expert_modules: list[nn.Module] = []
         self.no_shard_names: list[str] = []
@@ -240,7 +253,7 @@ class FSDP2Backend(BaseBackend):
                 if not torch.is_grad_enabled():
                     return __orig(*args, **kwargs)
                 if ac.use_reentrant:
-                    return checkpoint(__orig, *args, use_reentrant=True, **kwargs)
+                    return _reentrant_checkpoint(__orig, args, kwargs)
                 return checkpoint(__orig, *args, use_reentrant=False,
                                   context_fn=lambda: (contextlib.nullcontext(), _recompute_ctx()), **kwargs)
 
@@ -289,7 +302,7 @@ class FSDP2Backend(BaseBackend):
             skip = {id(q) for q in self.no_shard_params}
             for m in group:
                 for sub in m.modules():
-                    if sub is not m and getattr(sub, "_tt_unit", None) == "local":
+                    if sub is not m and getattr(sub, "_tt_unit", None) in ("local", "replicated"):
                         skip.update(id(q) for q in sub.parameters())
             ignored = {p for p in own if id(p) in skip}
             kw = self._fsdp_kwargs(mesh, is_expert=is_expert, reshard=reshard)
@@ -374,6 +387,21 @@ class FSDP2Backend(BaseBackend):
         self.fsdp_config.reshard_after_forward = not resident
         logger.info_rank0("reshard_after_forward resolved to %s", self.fsdp_config.reshard_after_forward)
 
+    def _resolve_replicate_layers(self, layers: list[nn.Module]) -> bool:
+        """`replicate_layers`: keep the decoder layers' world-sharded parameters replicated (see `FSDPConfig`)."""
+        mode = self.fsdp_config.replicate_layers
+        if self.world_mesh.size() <= 1 or not layers or self.fsdp_config.cpu_offload.enabled:
+            return False
+        if mode != "auto":
+            return bool(mode)
+        if not torch.cuda.is_available():
+            return False
+        n = sum(self._unit_param_bytes(m) // 2 for m in layers)
+        cap = torch.cuda.get_device_properties(torch.cuda.current_device()).total_memory
+        use = 18 * n <= self.fsdp_config.replicate_fraction * cap
+        logger.info_rank0("replicate_layers resolved to %s (%.2f B parameters in %d layers)", use, n / 1e9, len(layers))
+        return use
+
     def _collect_no_shard(self, model: nn.Module, compiled: dict[str, FSDPPlanSpec]) -> None:
         """`no_shard` entries may name modules or single parameters; their parameters stay replicated and
         get a world-average all-reduce on the gradient."""
@@ -404,12 +432,19 @@ class FSDP2Backend(BaseBackend):
             if tied and (mod is emb or mod is head):
                 continue  # tied input/output embeddings must live in one unit: the root
             self._make_unit(mod, spec)
-        # 2. every ModuleList child is a unit (small consecutive children share one)
-        for _, mod in list(model.named_modules()):
-            if isinstance(mod, nn.ModuleList):
-                children = [c for c in mod if any(True for _ in c.parameters()) and getattr(c, "_tt_unit", None) is None]
-                for group in self._group_layers(children):
-                    self._make_unit(group, None)
+        # 2. every ModuleList child is a unit (small consecutive children share one), or stays replicated
+        lists = [[c for c in mod if any(True for _ in c.parameters()) and getattr(c, "_tt_unit", None) is None]
+                 for _, mod in list(model.named_modules()) if isinstance(mod, nn.ModuleList)]
+        replicate = self._resolve_replicate_layers([c for children in lists for c in children])
+        for children in lists:
+            if replicate:
+                for c in children:
+                    if getattr(c, "_tt_unit", None) is None:
+                        c._tt_unit = "replicated"
+                        self.replicated_units.append(c)
+                continue
+            for group in self._group_layers(children):
+                self._make_unit(group, None)
         # 3. input embeddings, resident tail (final norm + output embedding), root
         if emb is not None and not tied:
             self._make_unit(emb, None)
@@ -559,6 +594,61 @@ class FSDP2Backend(BaseBackend):
                         if p.requires_grad:
                             p._master_init = master
         self._register_no_shard_grad_sync()
+        self._setup_replicated_grads()
+
+    # -- replicated decoder layers: one flat fp32 gradient buffer, one all-reduce per optimizer step ------------
+    def _setup_replicated_grads(self) -> None:
+        """Every trainable parameter of a replicated layer gets `main_grad`, a view into one flat fp32 buffer.  Weight
+        gradient GEMMs accumulate straight into it (no `.grad` tensor); gradients that autograd still delivers as
+        `.grad` are folded in before the buffer is averaged over the ranks (`_sync_replicated_grads`)."""
+        if not self.replicated_units or self._rep_flat is not None:
+            return
+        seen: set[int] = set()
+        params = []
+        for m in self.replicated_units:
+            nested = {id(q) for sub in m.modules() if sub is not m and getattr(sub, "_tt_unit", None) is not None
+                      for q in sub.parameters()}          # expert containers and other units inside the layer
+            for p in m.parameters():
+                if id(p) not in nested and id(p) not in seen and p.requires_grad:
+                    seen.add(id(p))
+                    params.append(p)
+        if not params:
+            return
+        sizes = [(p.numel() + 3) // 4 * 4 for p in params]          # 16-byte aligned slices
+        flat = torch.zeros(sum(sizes), dtype=torch.float32, device=params[0].device)
+        off = 0
+        for p, n in zip(params, sizes):
+            p.main_grad = flat[off:off + p.numel()].view(p.shape)
+            p.main_grad._tt_flat_owner = flat
+            off += n
+        self._rep_flat, self._rep_params = flat, params
+        logger.info_rank0("replicated layers: %d parameters, %.1f MB flat fp32 gradient buffer", len(params), flat.numel() * 4 / 2**20)
+
+    @torch.no_grad()
+    def _sync_replicated_grads(self) -> None:
+        """Fold stray `.grad` tensors into the flat buffer and average it over the world (once per optimizer step)."""
+        if self._rep_flat is None or self._rep_synced:
+            return
+        mains, grads = [], []
+        for p in self._rep_params:
+            if p.grad is not None:
+                mains.append(p.main_grad)
+                grads.append(p.grad if p.grad.dtype == torch.float32 else p.grad.float())
+                p.grad = None
+        if mains:
+            torch._foreach_add_(mains, grads)
+        if self.world_size > 1:
+            dist.all_reduce(self._rep_flat, op=dist.ReduceOp.SUM)
+            self._rep_flat.div_(self.world_size)
+        for p in self._rep_params:
+            if p.dtype == torch.float32:
+                p.grad = p.main_grad      # optimizers that only know `.grad` (fp32 runs) read the averaged view
+        self._rep_synced = True
+
+    def _after_optimizer_step(self, *_args, **_kwargs) -> None:
+        if self._rep_flat is not None:
+            self._rep_flat.zero_()
+            self._rep_synced = False
 
     def _register_no_shard_grad_sync(self) -> None:
         if self.world_size == 1:
@@ -636,6 +726,11 @@ class FSDP2Backend(BaseBackend):
                         st = o._init_state(p)
                         st["master"] = init
                         del p._master_init
+        if self._rep_flat is not None:
+            # replicated layers: gradients are averaged before the first optimizer touches them (normally already done
+            # by `clip_grad_norm_`), the flat buffer is cleared after the last one has stepped
+            opts[0].register_step_pre_hook(lambda *_a, **_k: self._sync_replicated_grads())
+            opts[-1].register_step_post_hook(self._after_optimizer_step)
         return opts[0] if len(opts) == 1 else OptimizersContainer(opts, names)
 
     # ------------------------------------------------------------------------------------------
@@ -683,6 +778,7 @@ class FSDP2Backend(BaseBackend):
             cache = self._clip_cache = {"key": ckey, "params": params, "fused": fused,
                                         "unfused": [p for p in params if id(p) not in fused]}
         params = cache["params"]
+        self._sync_replicated_grads()
         if self.ep_size > 1:
             # the fused optimizer of the expert parameters folds the 1/ep scaling into its gradient reads
             for o in opts:

@@ -256,7 +256,9 @@ class FSDP2CheckpointManager(BaseCheckpointManager):
     def save_native_model(self, model: nn.Module, path: str) -> None:
         import torch.distributed.checkpoint as dcp
 
-        dcp.save(self._model_state(model), checkpoint_id=path)
+        # nested under "model" like the reference's DCP layout (keys `model.<fqn>[::ep<r>]`,
+        # engine/backends/fsdp2/checkpoint/dcp.py:237-268 of the reference)
+        dcp.save({"model": self._model_state(model)}, checkpoint_id=path)
 
     def load_native_model(self, model: nn.Module, path: str) -> None:
         import torch.distributed.checkpoint as dcp
@@ -265,17 +267,22 @@ class FSDP2CheckpointManager(BaseCheckpointManager):
             raise RuntimeError(f"{path} is not a complete native checkpoint")
         state = self._model_state(model)
         self._check_ep_keys(path, state)
-        dcp.load(state, checkpoint_id=path)  # in-place into the model's tensors; extra saved keys are ignored
+        dcp.load({"model": state}, checkpoint_id=path)  # in-place into the model's tensors; extra saved keys are ignored
         if hasattr(model, "tie_weights"):
             model.tie_weights()
 
     def _check_ep_keys(self, path: str, state: dict[str, Any]) -> None:
         from torch.distributed.checkpoint import FileSystemReader
 
-        saved = set(FileSystemReader(path).read_metadata().state_dict_metadata.keys())
+        saved = {k[len("model."):] for k in FileSystemReader(path).read_metadata().state_dict_metadata.keys() if k.startswith("model.")}
+        saved_ep = sorted({k.rpartition("::ep")[2] for k in saved if "::ep" in k})
+        ep_size = self.backend.get_ep_info()["ep_size"]
+        if saved_ep and len(saved_ep) != ep_size:
+            # expert tensors are stored once per EP rank: another EP size cannot consume them
+            raise ValueError(f"native checkpoint was written with ep_size={len(saved_ep)} (expert entries ::ep{saved_ep[0]}..::ep"
+                             f"{saved_ep[-1]}), this run uses ep_size={ep_size}; export to Hugging Face format to change it")
         missing = [k for k in state if k not in saved]
         if missing:
-            saved_ep = sorted({k.rpartition("::ep")[2] for k in saved if "::ep" in k})
             hint = f" (checkpoint EP ranks: {saved_ep}; current suffix {self._ep_suffix() or 'none'})" if saved_ep or self._ep_suffix() else ""
             raise KeyError(f"native checkpoint lacks {len(missing)} required entries, e.g. {missing[:4]}{hint}")
 
@@ -339,14 +346,16 @@ class FSDP2CheckpointManager(BaseCheckpointManager):
         import torch.distributed.checkpoint as dcp
 
         tensors, groups = self._flatten_optimizer(model, optimizer)
-        dcp.save({"state": tensors, "param_groups": groups}, checkpoint_id=path)
+        # keys `optimizer.state.<optimizer>/<fqn>[::ep<r>]/<slot>` and `optimizer.param_groups.<optimizer>`: nested
+        # under "optimizer" like the reference's layout (dcp.py:370-388 there), one entry per state tensor
+        dcp.save({"optimizer": {"state": tensors, "param_groups": groups}}, checkpoint_id=path)
 
     def load_native_optimizer(self, model: nn.Module, optimizer, path: str) -> None:
         import torch.distributed.checkpoint as dcp
 
         tensors, groups = self._flatten_optimizer(model, optimizer)
         holder = {"state": tensors, "param_groups": groups}
-        dcp.load(holder, checkpoint_id=path)
+        dcp.load({"optimizer": holder}, checkpoint_id=path)
         from ...optimizers import OptimizersContainer
 
         opts = list(optimizer) if isinstance(optimizer, OptimizersContainer) else [optimizer]

@@ -119,5 +119,13 @@ class CheckpointCoordinator:
         collective_check(preflight, "optimizer checkpoint preflight")
         collective_check(lambda: self.manager.load_native_optimizer(model, optimizer, opt_dir), "optimizer load")
         sched_path = os.path.join(checkpoint_dir, SCHEDULER_FILE)
-        if scheduler is not None and os.path.isfile(sched_path):
-            scheduler.load_state_dict(load_scheduler(sched_path))
+        if scheduler is not None:
+            # a resume that restores the optimizer but silently restarts the learning-rate schedule trains with the
+            # wrong rate: a missing file is an error, as in the reference (engine/checkpoint/coordinator.py:197-250 there)
+            def load_sched():
+                if not os.path.isfile(sched_path):
+                    raise FileNotFoundError(f"{sched_path} is missing although {opt_dir} holds optimizer state; the checkpoint "
+                                            "is incomplete (pass scheduler=None to resume without a schedule)")
+                scheduler.load_state_dict(load_scheduler(sched_path))
+
+            collective_check(load_sched, "scheduler load")

@@ -114,7 +114,8 @@ def save_scheduler(path: str | os.PathLike, state: dict) -> None:
 
 def load_scheduler(path: str | os.PathLike) -> dict:
     try:
-        return torch.load(path, map_location="cpu", weights_only=False)
+        # scheduler state is numbers, lists and dicts: nothing in it needs unpickling of arbitrary objects
+        return torch.load(path, map_location="cpu", weights_only=True)
     except Exception as e:
         raise RuntimeError(f"{path} is unreadable (truncated save?): {e}") from e
 

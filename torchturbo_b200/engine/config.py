@@ -381,6 +381,13 @@ class FSDPConfig:
     # consecutive decoder layers share one FSDP unit until it gathers this many bf16 bytes; "auto" = 256 MiB on
     # CUDA meshes and no merging on CPU meshes; 0 = one unit per layer
     unit_min_bytes: Any = "auto"
+    # decoder layers whose world-sharded parameters are a small part of the device memory can stay REPLICATED instead
+    # (bf16 weights + fp32 master + moments on every rank, one gradient all-reduce of a flat buffer per optimizer
+    # step): no per-layer all-gather / reduce-scatter and none of their per-parameter host work.  True / False, or
+    # "auto": replicate on CUDA meshes when those parameters with their optimizer state (18 bytes each) take at most
+    # `replicate_fraction` of the device memory.  Embeddings, output head and expert containers keep their placements.
+    replicate_layers: Any = "auto"
+    replicate_fraction: float = 0.12
     # all-gather / reduce-scatter of FSDP units: "auto" (peer-memory NVLink kernels when every rank of the group
     # has its own GPU on one node, else NCCL), "p2p" (required), "nccl"
     transport: str = "auto"
@@ -413,6 +420,11 @@ class FSDPConfig:
             self.unit_min_bytes = (256 << 20) if torch.cuda.is_available() else 0
         self.unit_min_bytes = int(self.unit_min_bytes)
         self.resident_fraction = float(self.resident_fraction)
+        if not (isinstance(self.replicate_layers, str) and self.replicate_layers.lower() == "auto"):
+            self.replicate_layers = string_to_bool(self.replicate_layers)
+        else:
+            self.replicate_layers = "auto"
+        self.replicate_fraction = float(self.replicate_fraction)
         if str(self.transport).lower() not in ("auto", "p2p", "nccl"):
             raise ValueError("backend_config.transport must be auto, p2p or nccl")
         self.forward_prefetch_depth, self.backward_prefetch_depth = int(self.forward_prefetch_depth), int(self.backward_prefetch_depth)

@@ -151,5 +151,5 @@ class FusedAdamW(torch.optim.Optimizer):
         for group in self.param_groups:
             for p in group["params"]:
                 mg = getattr(p, "main_grad", None)
-                if mg is not None:
-                    mg.zero_()
+                if mg is not None and getattr(mg, "_tt_flat_owner", None) is None:
+                    mg.zero_()      # views of a flat buffer are cleared by its owner, once, after the step

@@ -20,12 +20,35 @@ class ModelConfig:
         merged = {}
         for klass in reversed(type(self).__mro__):
             merged.update(getattr(klass, "_defaults", {}) or {})
-        merged.update(kwargs)
+        merged.update(self._normalise_hf_keys(dict(kwargs)))
         merged.pop("model_type", None)
         for k, v in merged.items():
             setattr(self, k, v)
         if getattr(self, "head_dim", None) is None and hasattr(self, "hidden_size") and hasattr(self, "num_attention_heads"):
             self.head_dim = self.hidden_size // self.num_attention_heads
+
+    # `config.json` spellings of recent `transformers` releases -> the attribute names the modelling code reads
+    _hf_aliases = {"num_local_experts": "num_experts", "n_routed_experts": "num_experts"}
+
+    @classmethod
+    def _normalise_hf_keys(cls, d: dict[str, Any]) -> dict[str, Any]:
+        """transformers 5 stores the rotary settings as `rope_parameters: {rope_theta, rope_type, ...}` (4.x:
+        top-level `rope_theta` + `rope_scaling`) and writes some sizes under their attribute-map alias
+        (`num_local_experts` for `num_experts`).  Explicit canonical keys win over aliases."""
+        for alias, name in cls._hf_aliases.items():
+            if alias in d and name not in d:
+                d[name] = d[alias]
+        rp = d.get("rope_parameters")
+        if isinstance(rp, dict):
+            if "rope_theta" in rp and "rope_theta" not in d:
+                d["rope_theta"] = rp["rope_theta"]
+            if "rope_scaling" not in d and rp.get("rope_type", "default") not in (None, "default"):
+                d["rope_scaling"] = {k: v for k, v in rp.items() if k != "rope_theta"}
+            if "mrope_section" in rp and "mrope_section" not in d:
+                d["mrope_section"] = rp["mrope_section"]
+            if "partial_rotary_factor" in rp and "partial_rotary_factor" not in d:
+                d["partial_rotary_factor"] = rp["partial_rotary_factor"]
+        return d
 
     # -- io ---------------------------------------------------------------------------------------
     @classmethod

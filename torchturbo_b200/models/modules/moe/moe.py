@@ -30,6 +30,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ....ops import MoEPermutation, ops
+from ....utils.recompute import in_recompute
 from ..comm import all_gather_tensor, all_reduce_sum_autograd, all_to_all
 
 
@@ -170,6 +171,8 @@ class TopKRouter(nn.Module):
 
     # -- metrics protocol (consumed by MetricTracker) -------------------------------------------------
     def _record(self, name: str, value: torch.Tensor) -> None:
+        if in_recompute():      # the replay of a checkpointed layer reports nothing a second time
+            return
         self._metrics.setdefault(name, []).append(value.detach().float())
 
     def pop_metrics(self) -> dict[str, torch.Tensor]:
@@ -233,7 +236,7 @@ class TopKRouter(nn.Module):
             prob = MoEAuxLossAutoScaler.apply(prob, aux * runtime.aux_loss_scale)
             self._record("aux_loss", aux / cfg.moe_aux_loss_coeff)
             self._record("aux_loss_scaled", aux)
-        if self.expert_bias is not None and self.training and runtime.accumulate_tokens_per_expert:
+        if self.expert_bias is not None and self.training and runtime.accumulate_tokens_per_expert and not in_recompute():
             with torch.no_grad():
                 self.local_tokens_per_expert += stats["counts"].float()
         # histogram of `idx` over the experts, as the routing kernel produced it: dispatchers reuse it

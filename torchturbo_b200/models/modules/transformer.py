@@ -153,6 +153,26 @@ class CausalLMOutput(dict):
         self[k] = v
 
 
+def _register_output_pytree() -> None:
+    """FSDP2 finds the tensors of a module's output with `torch.utils._pytree` (to hook the start of backward on
+    them); a plain `dict` subclass would be an opaque leaf there, and a model whose only sharded unit is the root
+    would never run its gradient reduction."""
+    try:
+        from torch.utils import _pytree as pytree
+
+        pytree.register_pytree_node(
+            CausalLMOutput,
+            lambda d: (list(d.values()), list(d.keys())),
+            lambda values, keys: CausalLMOutput(zip(keys, values)),
+            serialized_type_name="torchturbo_b200.CausalLMOutput",
+        )
+    except Exception:  # noqa: BLE001 - already registered, or a torch build without the hook
+        pass
+
+
+_register_output_pytree()
+
+
 def init_weights(module: nn.Module, std: float) -> None:
     for m in module.modules():
         if isinstance(m, nn.Linear):
