@@ -6,7 +6,8 @@ Formats:
   fp8_block  : e4m3 weights with one fp32 `weight_scale_inv` per 128x128 block (DeepSeek / Bailing style)
   mxfp4      : e2m1 values packed two per byte with one ue8m0 scale per 32 values (`*_blocks`, `*_scales`)
   int4_group : symmetric int4 packed eight per int32 with per-group scales (`weight_packed`, `weight_scale`)
-Non-quantised tensors are copied unchanged; the index and every non-tensor file are carried over
+Non-quantised tensors are copied unchanged; the index and every non-tensor file are carried over.  Model-specific
+front ends with the reference's command lines: deepseekv4.py, deepseekv4_1.py, bailing.py, kimik26.py
 (scripts/dequant/{dequantize,converter,deepseekv4,bailing,kimik26}.py of the reference)."""
 from __future__ import annotations
 
@@ -70,35 +71,23 @@ def convert_state(tensors: dict[str, torch.Tensor], fmt: str) -> dict[str, torch
     return out
 
 
+PROFILE_OF = {"fp8_block": "bailing", "mxfp4": "mxfp4_blocks", "int4_group": "kimi_k26"}
+
+
 def main(argv=None):
-    from safetensors import safe_open
-    from safetensors.torch import save_file
+    """Generic front end: picks the profile by format name.  Scales are looked up through the checkpoint index, so a
+    scale tensor stored in another shard file than its weight is found (`convert.convert_checkpoint`)."""
+    import sys
+
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from convert import convert_checkpoint
 
     p = argparse.ArgumentParser()
     p.add_argument("--input", required=True)
     p.add_argument("--output", required=True)
-    p.add_argument("--format", required=True, choices=["fp8_block", "mxfp4", "int4_group"])
+    p.add_argument("--format", required=True, choices=sorted(PROFILE_OF))
     a = p.parse_args(argv)
-    os.makedirs(a.output, exist_ok=True)
-    weight_map = {}
-    for fn in sorted(os.listdir(a.input)):
-        src = os.path.join(a.input, fn)
-        if fn.endswith(".safetensors"):
-            with safe_open(src, framework="pt") as f:
-                tensors = {k: f.get_tensor(k) for k in f.keys()}
-            conv = convert_state(tensors, a.format)
-            save_file({k: v.contiguous() for k, v in conv.items()}, os.path.join(a.output, fn), metadata={"format": "pt"})
-            weight_map.update({k: fn for k in conv})
-        elif fn != "model.safetensors.index.json" and os.path.isfile(src):
-            shutil.copy2(src, os.path.join(a.output, fn))
-    cfg_path = os.path.join(a.output, "config.json")
-    if os.path.exists(cfg_path):
-        cfg = json.load(open(cfg_path))
-        cfg.pop("quantization_config", None)
-        cfg["torch_dtype"] = "bfloat16"
-        json.dump(cfg, open(cfg_path, "w"), indent=2)
-    json.dump({"metadata": {"format": "pt"}, "weight_map": weight_map},
-              open(os.path.join(a.output, "model.safetensors.index.json"), "w"), indent=2)
+    return convert_checkpoint(a.input, a.output, PROFILE_OF[a.format])
 
 
 if __name__ == "__main__":

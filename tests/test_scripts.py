@@ -15,6 +15,7 @@ ROOT = Path(__file__).resolve().parents[1]
 def _load(rel: str, name: str):
     spec = importlib.util.spec_from_file_location(name, ROOT / rel)
     mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod            # dataclasses resolve annotations through sys.modules
     spec.loader.exec_module(mod)
     return mod
 
@@ -81,6 +82,87 @@ def test_dequantize_cli_rewrites_shards_index_and_config(tmp_path):
     assert (dst / "tokenizer.json").exists()
     with pytest.raises(ValueError, match="unknown format"):
         dq.convert_state({"a": torch.zeros(1)}, "nf4")
+
+
+def _pack_e2m1(codes):
+    """uint8 codes [R, C] (0..15) -> packed bytes [R, C/2], low nibble = even column."""
+    return (codes[:, 0::2] | (codes[:, 1::2] << 4)).to(torch.uint8)
+
+
+def test_model_dequant_profiles_decode_their_formats():
+    fm = _load("scripts/dequant/formats.py", "tt_formats")
+    torch.manual_seed(0)
+    # fp8 with fp32 128x128 block scales (DeepSeek V4 dense weights, Bailing)
+    w = torch.randn(200, 300).to(torch.float8_e4m3fn)
+    s = torch.rand(2, 3) + 0.5
+    want = (w.float() * s.repeat_interleave(128, 0)[:200].repeat_interleave(128, 1)[:, :300]).bfloat16()
+    for prof in ("deepseek_v4", "bailing"):
+        assert torch.equal(fm.PROFILES[prof].decode({"weight": w, "scale": s}, {}), want)
+    # packed mxfp4 with one fp32 scale per row and 32 columns (DeepSeek V4 experts)
+    codes = torch.randint(0, 16, (4, 64), dtype=torch.uint8)
+    s = torch.rand(4, 2) + 0.5
+    want = (fm.E2M1[codes.long()] * s.repeat_interleave(32, 1)).bfloat16()
+    assert torch.equal(fm.PROFILES["deepseek_v4"].decode({"weight": _pack_e2m1(codes), "scale": s}, {}), want)
+    # DeepSeek V4.1: ue8m0 scales; fp4 per row / 32 columns, fp8 per row / 32 columns or square blocks
+    e = torch.randint(120, 134, (4, 2), dtype=torch.uint8)
+    want = (fm.E2M1[codes.long()] * torch.exp2(e.float() - 127).repeat_interleave(32, 1)).bfloat16()
+    assert torch.equal(fm.PROFILES["deepseek_v4_1"].decode({"weight": _pack_e2m1(codes), "scale": e}, {}), want)
+    w = torch.randn(64, 96).to(torch.float8_e4m3fn)
+    for shape, (rb, cb) in (((64, 3), (1, 32)), ((2, 3), (32, 32)), ((1, 1), (128, 128))):
+        e = torch.randint(120, 134, shape, dtype=torch.uint8)
+        full = torch.exp2(e.float() - 127).repeat_interleave(cb, 1)
+        full = (full.repeat_interleave(rb, 0) if rb > 1 else full)[:64, :96]
+        assert torch.equal(fm.PROFILES["deepseek_v4_1"].decode({"weight": w, "scale": e}, {}), (w.float() * full).bfloat16())
+    with pytest.raises(ValueError, match="fits none"):
+        fm.PROFILES["deepseek_v4_1"].decode({"weight": w, "scale": torch.zeros(5, 5, dtype=torch.uint8)}, {})
+    # Kimi: eight offset-binary nibbles per int32, group scales
+    vals = torch.randint(-8, 8, (3, 64))
+    words = torch.zeros(3, 8, dtype=torch.int64)
+    for i in range(8):
+        words |= ((vals[:, i::8] + 8) & 0xF) << (4 * i)
+    packed = words.to(torch.int32) if int(words.max()) < 2 ** 31 else (words - (words >= 2 ** 31) * 2 ** 32).to(torch.int32)
+    s = torch.rand(3, 2) + 0.5
+    got = fm.PROFILES["kimi_k26"].decode({"packed": packed, "scale": s, "shape": torch.tensor([3, 64])}, {"group_size": 32})
+    assert torch.equal(got, (vals.float() * s.repeat_interleave(32, 1)).bfloat16())
+
+
+def test_dequant_converter_finds_scales_in_other_shards_and_rejects_half_described_tensors(tmp_path):
+    from safetensors import safe_open
+    from safetensors.torch import save_file
+
+    cv = _load("scripts/dequant/convert.py", "tt_convert")
+    src, dst = tmp_path / "q", tmp_path / "bf16"
+    src.mkdir()
+    wa, wb = torch.randn(128, 128).to(torch.float8_e4m3fn), torch.randn(128, 256).to(torch.float8_e4m3fn)
+    sa, sb = torch.tensor([[3.0]]), torch.tensor([[0.25, 4.0]])
+    # shards cut by size: the scale of `a` sits in shard 2, the scale of `b` in shard 1
+    save_file({"l.a.weight": wa, "l.b.weight_scale_inv": sb, "l.norm.weight": torch.ones(8, dtype=torch.bfloat16)}, str(src / "m-1.safetensors"))
+    save_file({"l.b.weight": wb, "l.a.weight_scale_inv": sa, "l.a.bias": torch.zeros(4)}, str(src / "m-2.safetensors"))
+    wmap = {"l.a.weight": "m-1.safetensors", "l.b.weight_scale_inv": "m-1.safetensors", "l.norm.weight": "m-1.safetensors",
+            "l.b.weight": "m-2.safetensors", "l.a.weight_scale_inv": "m-2.safetensors", "l.a.bias": "m-2.safetensors"}
+    (src / "model.safetensors.index.json").write_text(json.dumps({"weight_map": wmap}))
+    (src / "config.json").write_text(json.dumps({"quantization_config": {"x": 1}, "text_config": {"quantization_config": {}}}))
+    bl = _load("scripts/dequant/bailing.py", "tt_bailing")
+    summary = bl.main(["--input-fp8-hf-path", str(src), "--output-hf-path", str(dst)])
+    assert (summary.tensors, summary.dequantised, summary.cross_shard, summary.shards) == (4, 2, 2, 2)
+    idx = json.loads((dst / "model.safetensors.index.json").read_text())["weight_map"]
+    assert idx == {"l.a.bias": "m-2.safetensors", "l.a.weight": "m-1.safetensors", "l.b.weight": "m-2.safetensors",
+                   "l.norm.weight": "m-1.safetensors"}
+    with safe_open(str(dst / "m-1.safetensors"), framework="pt") as f:
+        assert torch.equal(f.get_tensor("l.a.weight"), (wa.float() * 3.0).bfloat16())
+    with safe_open(str(dst / "m-2.safetensors"), framework="pt") as f:
+        got = f.get_tensor("l.b.weight")
+    assert torch.equal(got[:, :128], (wb.float()[:, :128] * 0.25).bfloat16()) and torch.equal(got[:, 128:], (wb.float()[:, 128:] * 4.0).bfloat16())
+    cfg = json.loads((dst / "config.json").read_text())
+    assert "quantization_config" not in cfg and "quantization_config" not in cfg["text_config"] and cfg["torch_dtype"] == "bfloat16"
+    # planning errors: a packed tensor without its scale, an orphan scale, output inside input
+    kimi = cv.PROFILES["kimi_k26"]
+    with pytest.raises(ValueError, match="lacks its scale"):
+        cv.plan({"x.weight_packed": "a", "x.weight_shape": "a"}, kimi)
+    with pytest.raises(ValueError, match="without a quantised weight"):
+        cv.plan({"y.weight_scale_inv": "a", "z.weight": "a"}, cv.PROFILES["bailing"])
+    with pytest.raises(ValueError, match="must not be"):
+        cv.convert_checkpoint(str(src), str(src / "out"), "bailing")
 
 
 def test_dataset_converters(tmp_path):

@@ -255,7 +255,8 @@ class _FusedExperts(torch.autograd.Function):
         K.gemm(act, w2, b_mn=True, tile_group=tile_group, out=ws.ret_rows, ep=ws.scatter_args())
         out = ws.ksum(T, k, residual=residual)
         ctx.ws, ctx.dims = ws, (T, k, residual is not None)
-        ctx.save_for_backward(xp, rp, pre, w1, w2, tile_group, seg_start, recv_counts, expert, dest_row, order, counts)
+        # `act` is kept as well: recomputing it in backward costs a pass over `pre`, keeping it costs cap x F bf16
+        ctx.save_for_backward(xp, rp, pre, act, w1, w2, tile_group, seg_start, recv_counts, expert, dest_row, order, counts)
         return out
 
     @staticmethod
@@ -263,15 +264,16 @@ class _FusedExperts(torch.autograd.Function):
         from ..ops.providers.b200 import _weight_grad
 
         ws, (T, k, has_res) = ctx.ws, ctx.dims
-        xp, rp, pre, w1, w2, tile_group, seg_start, recv_counts, expert, dest_row, order, counts = ctx.saved_tensors
+        xp, rp, pre, act, w1, w2, tile_group, seg_start, recv_counts, expert, dest_row, order, counts = ctx.saved_tensors
         dout = dout.contiguous()
         ws.prepare(expert, tables=(seg_start, recv_counts))
         # d(act) = d(y) W2[e]^T with the d(out) rows pushed to the owners from inside the kernel (they land in recv_rows)
         dact = K.gemm(ws.recv_rows, w2, tile_group=tile_group, ep=ws.push_args(dout, order, expert, dest_row, None, counts, k))
-        dpre, dprob_rows = K.swiglu_bwd(dact, pre, rp, want_dscale=True)
+        # rows past the last expert segment were never computed: the element-wise pass stops at the device-side count
+        dpre, dprob_rows = K.swiglu_bwd(dact, pre, rp, want_dscale=True, nrows=seg_start[ws.El:])
         dw1 = dw2 = None
         if ctx.needs_input_grad[5]:
-            dw2 = _weight_grad(w2, K.swiglu_fwd(pre, rp), ws.recv_rows, group_rows=seg_start)
+            dw2 = _weight_grad(w2, act, ws.recv_rows, group_rows=seg_start)
         if ctx.needs_input_grad[4]:
             dw1 = _weight_grad(w1, xp, dpre, group_rows=seg_start)
         # last reader of the received d(y) rows is done: d(x) rows and d(prob) go back to their sources from the epilogue

@@ -646,12 +646,15 @@ __global__ void qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, con
 // ============================================================================
 // SwiGLU (standalone).  x: [R, 2F] = [gate | up]; y: [R, F]; optional row_scale [R].
 // ============================================================================
+// `nrows` (optional, device): rows at or beyond *nrows are skipped (padded buffers whose fill is only known on the device)
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_bfloat16* __restrict__ y,
-                                  long long ldy, const float* __restrict__ row_scale, long long R, int F) {
+                                  long long ldy, const float* __restrict__ row_scale, long long R, int F,
+                                  const int* __restrict__ nrows) {
   const long long idx = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
   const long long total = R * F;
   if (idx >= total) return;
   const long long r = idx / F;
+  if (nrows && r >= *nrows) return;
   const int c = static_cast<int>(idx - r * F);
   const float sc = row_scale ? row_scale[r] : 1.f;
   uint4 g = *reinterpret_cast<const uint4*>(x + r * ldx + c);
@@ -671,9 +674,10 @@ __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ x, long long
 __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dy, long long lddy,
                                   const __nv_bfloat16* __restrict__ x, long long ldx,
                                   const float* __restrict__ row_scale, __nv_bfloat16* __restrict__ dx, long long lddx,
-                                  float* __restrict__ dscale, int F) {
+                                  float* __restrict__ dscale, int F, const int* __restrict__ nrows) {
   __shared__ float red[32];
   const long long r = blockIdx.x;
+  if (nrows && r >= *nrows) return;
   const float sc = row_scale ? row_scale[r] : 1.f;
   float ds = 0.f;
   for (int c = threadIdx.x * 8; c < F; c += blockDim.x * 8) {
@@ -1115,24 +1119,24 @@ TTB_EXPORT int ttb_qknorm_rope_bwd(const void* dq, const void* dk, const void* q
 }
 
 TTB_EXPORT int ttb_swiglu_fwd(const void* x, long long ldx, void* y, long long ldy, const float* row_scale, long long R,
-                              int F, void* stream) {
+                              int F, const int* nrows, void* stream) {
   if (F % 8 || ldx % 8 || ldy % 8) return 901;
   const long long n = R * F / 8;
   if (n == 0) return 0;
   swiglu_fwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, STREAM(stream)>>>((const __nv_bfloat16*)x, ldx,
-                                                                            (__nv_bfloat16*)y, ldy, row_scale, R, F);
+                                                                            (__nv_bfloat16*)y, ldy, row_scale, R, F, nrows);
   LAUNCH_RET();
 }
 
 TTB_EXPORT int ttb_swiglu_bwd(const void* dy, long long lddy, const void* x, long long ldx, const float* row_scale,
-                              void* dx, long long lddx, float* dscale, long long R, int F, void* stream) {
+                              void* dx, long long lddx, float* dscale, long long R, int F, const int* nrows, void* stream) {
   if (F % 8 || ldx % 8 || lddy % 8 || lddx % 8) return 901;
   if (R == 0) return 0;
   int threads = F / 8;
   threads = threads > 256 ? 256 : ((threads + 31) / 32) * 32;
   swiglu_bwd_kernel<<<(unsigned)R, threads, 0, STREAM(stream)>>>((const __nv_bfloat16*)dy, lddy,
                                                                 (const __nv_bfloat16*)x, ldx, row_scale,
-                                                                (__nv_bfloat16*)dx, lddx, dscale, F);
+                                                                (__nv_bfloat16*)dx, lddx, dscale, F, nrows);
   LAUNCH_RET();
 }
 

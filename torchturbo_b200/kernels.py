@@ -401,22 +401,24 @@ def qknorm_rope_bwd(dq, dk, qkv, n_q, n_kv, head_dim, wq, wk, cos, sin, rstd, dq
 # --------------------------------------------------------------------------------------
 # SwiGLU
 # --------------------------------------------------------------------------------------
-def swiglu_fwd(x, row_scale=None):
+def swiglu_fwd(x, row_scale=None, nrows=None):
+    """`nrows` (int32 device scalar, optional): only the first `nrows[0]` rows are computed (padded buffers)."""
     R, F2 = x.shape
     F = F2 // 2
     y = torch.empty(R, F, dtype=x.dtype, device=x.device)
     _check(lib().ttb_swiglu_fwd(_p(x), C.c_longlong(x.stride(0)), _p(y), C.c_longlong(y.stride(0)), _p(row_scale),
-                                C.c_longlong(R), C.c_int(F), _stream()), "ttb_swiglu_fwd")
+                                C.c_longlong(R), C.c_int(F), _p(nrows), _stream()), "ttb_swiglu_fwd")
     return y
 
 
-def swiglu_bwd(dy, x, row_scale=None, want_dscale=False):
+def swiglu_bwd(dy, x, row_scale=None, want_dscale=False, nrows=None):
+    """`nrows` (int32 device scalar, optional): rows from `nrows[0]` on are left untouched (padded buffers)."""
     R, F2 = x.shape
     F = F2 // 2
     dx = torch.empty_like(x)
     dscale = torch.empty(R, dtype=torch.float32, device=x.device) if want_dscale else None
     _check(lib().ttb_swiglu_bwd(_p(dy), C.c_longlong(dy.stride(0)), _p(x), C.c_longlong(x.stride(0)), _p(row_scale),
-                                _p(dx), C.c_longlong(dx.stride(0)), _p(dscale), C.c_longlong(R), C.c_int(F),
+                                _p(dx), C.c_longlong(dx.stride(0)), _p(dscale), C.c_longlong(R), C.c_int(F), _p(nrows),
                                 _stream()), "ttb_swiglu_bwd")
     return dx, dscale
 
