@@ -83,6 +83,37 @@ def test_save_resume_and_hf_roundtrip(tmp_path, world, ep):
     run_distributed(_w_roundtrip, world, ep, str(tmp_path))
 
 
+def _w_split_load(rank, world, root):
+    """HF load on 2 ranks: every shared tensor is read by exactly one rank and broadcast (also with a budget so small
+    that every broadcast is its own window), experts are read by their owners only; the result equals the source."""
+    import torch.distributed as dist
+
+    eng, model, opt = _build(2)
+    ckpt = os.path.join(root, "checkpoint-1")
+    eng.save_model(model, ckpt, final=True)
+    ref = {n: _full(p).detach().clone() for n, p in model.named_parameters()}
+    for budget in ("0", "1"):
+        if budget == "1":
+            os.environ["TORCHTURBO_LOAD_BROADCAST_BYTES"] = "1"
+        eng2, model2, _ = _build(2, seed=31)
+        eng2.checkpoint.load_pretrained(model2, os.path.join(ckpt, "huggingface"))
+        st = eng2.checkpoint.manager.last_load_stats
+        t = torch.tensor([st["read_here"], st["received"], st["direct"]])
+        both = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(both, t)
+        shared = int(both[0][0] + both[0][1])
+        assert all(int(b[0] + b[1]) == shared for b in both)                 # same shared tensors on every rank
+        assert sum(int(b[0]) for b in both) == shared                        # each one read exactly once
+        assert all(int(b[2]) > 0 for b in both)                              # experts: direct reads by their owner
+        for n, p in model2.named_parameters():
+            assert torch.allclose(_full(p).float(), ref[n].float(), atol=1e-2, rtol=1e-2), n   # export is bf16
+    os.environ.pop("TORCHTURBO_LOAD_BROADCAST_BYTES", None)
+
+
+def test_hf_load_splits_reads_across_ranks(tmp_path):
+    run_distributed(_w_split_load, 2, str(tmp_path))
+
+
 def _w_ep_mismatch(rank, world, root):
     eng, model, opt = _build(2)
     ckpt = os.path.join(root, "checkpoint-1")

@@ -82,26 +82,76 @@ class FSDP2CheckpointManager(BaseCheckpointManager):
 
     @torch.no_grad()
     def load_hf(self, model: nn.Module, path: str) -> None:
+        """Hugging Face safetensors -> this rank's shards.
+
+        With more than one rank the work is split instead of repeated: every tensor that all ranks need (everything but
+        expert-parallel tensors) has ONE reader rank, chosen by the shard file its first source lives in, so each file
+        is opened and decoded by one rank; the reader assembles the engine tensor (fused projections, dtype cast) on
+        its device and broadcasts it, and every rank cuts its own shard out of what it receives.  Broadcasts are
+        asynchronous and issued in windows of at most `TORCHTURBO_LOAD_BROADCAST_BYTES` (default 5 GiB) in flight, the
+        same bound the reference uses (engine/backends/fsdp2/checkpoint/weight_loader.py:68-72,232-592 there).
+        Expert-parallel tensors differ per rank, so each rank reads only the experts it owns."""
         conv = model.get_weight_converter(self.backend.get_parallel_context(), path)
-        reader = _SafetensorsReader(path, conv.checkpoint_info.tensor_files)
+        files = conv.checkpoint_info.tensor_files
+        reader = _SafetensorsReader(path, files)
+        world, rank = _world(), _rank()
+        eids = self.backend.expert_param_ids if self.backend.get_ep_info()["ep_size"] > 1 else set()
+        budget = int(os.environ.get("TORCHTURBO_LOAD_BROADCAST_BYTES", 5 * 1024 ** 3))
+        file_rank = {fn: i % world for i, fn in enumerate(sorted(set(files.values())))}
         missing: list[str] = []
+        window: list[tuple[Any, torch.Tensor, torch.Tensor, str]] = []   # (work handle, buffer, target, name)
+        in_flight = 0
+        stats = {"read_here": 0, "received": 0, "direct": 0}
+
+        def drain():
+            nonlocal in_flight
+            for work, buf, target, name in window:
+                if work is not None:
+                    work.wait()
+                self._assign(target, buf, name)
+            window.clear()
+            in_flight = 0
+
         for name, t, dup in self._named_state(model):
             if dup:
                 continue
             recipe = conv.load_recipe(name)
             if recipe is None:
                 continue  # tied alias omitted by the checkpoint
-            try:
-                full = recipe.assemble([reader.get(s) for s in recipe.sources])
-            except KeyError as e:
-                missing.append(f"{name} <- {e}")
+            absent = [s_ for s_ in recipe.sources if s_ not in files]
+            if absent:      # decided from the index alone, so every rank skips the same tensors
+                missing.append(f"{name} <- {absent[0]!r}")
                 continue
-            self._assign(t, full, name)
+            if world == 1 or id(t) in eids:
+                self._assign(t, recipe.assemble([reader.get(s_) for s_ in recipe.sources]), name)
+                stats["direct"] += 1
+                continue
+            owner = file_rank[files[recipe.sources[0]]]
+            local = t._local_tensor if _is_dtensor(t) else t
+            nbytes = t.numel() * local.element_size()
+            if in_flight and in_flight + nbytes > budget:
+                drain()
+            if rank == owner:
+                full = recipe.assemble([reader.get(s_) for s_ in recipe.sources])
+                if tuple(full.shape) != tuple(t.shape):
+                    raise ValueError(f"{name}: checkpoint shape {tuple(full.shape)} != parameter shape {tuple(t.shape)}")
+                buf = full.to(device=local.device, dtype=local.dtype).contiguous()
+                stats["read_here"] += 1
+            else:
+                buf = torch.empty(tuple(t.shape), dtype=local.dtype, device=local.device)
+                stats["received"] += 1
+            work = dist.broadcast(buf, src=owner, async_op=True)
+            window.append((work, buf, t, name))
+            in_flight += nbytes
+        drain()
         reader.close()
+        logger.info_rank0("HF load: rank 0 read %d tensor(s) itself, received %d, %d expert / single-rank read(s)",
+                          stats["read_here"], stats["received"], stats["direct"])
         if missing:
             raise KeyError(f"checkpoint {path} lacks tensors for: {missing[:8]}{'...' if len(missing) > 8 else ''}")
         if hasattr(model, "tie_weights"):
             model.tie_weights()
+        self.last_load_stats = stats
 
     def _assign(self, target: torch.Tensor, full: torch.Tensor, name: str) -> None:
         if _is_dtensor(target):
