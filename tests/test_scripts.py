@@ -210,3 +210,30 @@ def test_launchers_split_engine_flags_from_framework_arguments(monkeypatch):
         src = (ROOT / "scripts" / "runs" / script).read_text()
         compile(src, script, "exec")                                   # launchers at least parse
     assert "adapter.main(stage, rest)" in (ROOT / "scripts" / "runs" / "run_swift.py").read_text()
+
+
+def test_every_run_recipe_parses_against_the_engine_schema():
+    """Every `scripts/runs/<model>/*.yaml` must load through the same path `--tt_config` uses (unknown keys are
+    rejected there), every launcher must be valid bash and name a recipe that exists."""
+    import subprocess
+
+    from torchturbo_b200.engine.config import EngineConfig, load_config_file
+
+    runs = ROOT / "scripts" / "runs"
+    recipes = sorted(runs.glob("*/*.yaml"))
+    assert len(recipes) >= 14
+    for y in recipes:
+        cfg = EngineConfig.from_dict(load_config_file(str(y)))
+        assert cfg.parallel_plan.ep_size in (1, 8) and cfg.parallel_plan.sp_size in (1, 2, 8), y
+    launchers = sorted(runs.glob("*/*.sh")) + [runs / "common.sh"]
+    assert len(launchers) >= 25
+    for sh in launchers:
+        assert subprocess.run(["bash", "-n", str(sh)]).returncode == 0, sh
+        text = sh.read_text()
+        for tok in text.split():
+            if tok.endswith(".yaml}") and "/" in tok:
+                name = tok.split("/")[-1].rstrip("}")
+                assert (sh.parent / name).exists() or (runs / "qwen3" / name).exists(), (sh, name)
+    for j in ("moe_30b_a3b", "dense_14b", "dense_8b"):
+        shape = json.loads((runs / "qwen3" / f"{j}.json").read_text())
+        assert shape["vocab_size"] == 151936 and shape["model_type"] in ("qwen3", "qwen3_moe")
