@@ -45,7 +45,7 @@ def parse():
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--layers", type=int, default=0, help="0 = min(48, 12 * gpus)")
     p.add_argument("--seq-len", type=int, default=4096)
-    p.add_argument("--model", default="qwen3_moe_30b_a3b", choices=["qwen3_moe_30b_a3b", "qwen3_8b", "qwen3_14b", "tiny_moe", "tiny_dense"])
+    p.add_argument("--model", default="qwen3_moe_30b_a3b", choices=["qwen3_moe_30b_a3b", "qwen3_8b", "qwen3_14b", "qwen3_vl_8b", "tiny_moe", "tiny_dense"])
     p.add_argument("--sp", type=int, default=1, help="Ulysses sequence-parallel size (a sequence of --seq-len tokens per SP group)")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--fsdp-transport", default="auto", choices=["auto", "nccl", "p2p"],
@@ -77,6 +77,12 @@ def model_config(name: str, layers: int) -> dict:
         return dict(model_type="qwen3", vocab_size=151936, hidden_size=4096, intermediate_size=12288,
                     num_hidden_layers=layers, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
                     rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False)
+    if name == "qwen3_vl_8b":
+        # 27-layer ViT (width 1152, 16 heads, MLP 4304, patch 14, 2x2 merge) in front of the Qwen3-8B decoder
+        text = model_config("qwen3_8b", layers)
+        text.pop("model_type")
+        return dict(model_type="qwen3_vl", text_config=text, vision_config=dict(depth=27, hidden_size=1152, num_heads=16,
+                    intermediate_size=4304, patch_size=14, temporal_patch_size=2, spatial_merge_size=2), vocab_size=151936)
     if name == "tiny_dense":
         return dict(model_type="qwen3", vocab_size=32000, hidden_size=512, intermediate_size=1024, num_hidden_layers=layers,
                     num_attention_heads=8, num_key_value_heads=2, head_dim=128, rope_theta=1e6, rms_norm_eps=1e-6,
@@ -149,15 +155,18 @@ def run_ours(args) -> dict:
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
-    named_layers = {"qwen3_moe_30b_a3b": 48, "qwen3_8b": 36, "qwen3_14b": 40}.get(args.model, 4)
+    named_layers = {"qwen3_moe_30b_a3b": 48, "qwen3_8b": 36, "qwen3_14b": 40, "qwen3_vl_8b": 36}.get(args.model, 4)
     layers = args.layers or min(named_layers, 12 * world)
-    is_moe = args.model not in ("qwen3_8b", "qwen3_14b", "tiny_dense")
+    is_vlm = args.model == "qwen3_vl_8b"
+    is_moe = args.model not in ("qwen3_8b", "qwen3_14b", "tiny_dense", "qwen3_vl_8b")
     sp = max(args.sp, 1)
     cfg = EngineConfig.from_dict({
         "mixed_precision": "bf16",
         "parallel_plan": {"sp_size": sp, "ep_size": world if is_moe else 1},
         "moe": {"aux_loss_coeff": 1e-3},
         "activation_checkpointing": {"enabled": not is_moe},
+        **({"parallel_plan": {"sp_size": sp, "ep_size": 1, "plan": {"model.visual": {"vision_balance": {"mode": "patch_sq"}}}}}
+           if is_vlm else {}),
         "backend_config": dict({"transport": args.fsdp_transport},
                                **({"unit_min_bytes": args.fsdp_unit_mb << 20} if args.fsdp_unit_mb >= 0 else {})),
     })
@@ -169,10 +178,27 @@ def run_ours(args) -> dict:
     optim = engine.prepare_optimizer(model, OptimizerClassPlan(torch.optim.AdamW, lr=1e-5, weight_decay=0.01,
                                                                betas=(0.9, 0.95)))
     n_batches = max(args.warmup, 1) + 2 * args.steps
-    ds = SyntheticPackedDataset(n_batches * world, args.seq_len, mc["vocab_size"], min_doc=256, max_doc=args.seq_len,
-                                seed=1234)
-    coll = PackedCollator(pin=True)
-    host = [coll([ds[(rank // sp) * n_batches + i]]) for i in range(n_batches)]   # an SP group shares its row
+    if is_vlm:
+        # one sample per rank: `seq_len` text tokens plus 0..8 images of 224..1344 pixels a side (placeholders inserted);
+        # the images of all ranks are pooled and spread by squared patch count before the vision tower runs
+        from torchturbo_b200.data import SyntheticVLMDataset
+
+        ds = SyntheticVLMDataset(n_batches * world, args.seq_len, mc["vocab_size"], image_token_id=151655,
+                                 vision_start_token_id=151652, seed=1234)
+        host = [{k: (v.pin_memory() if isinstance(v, torch.Tensor) and not k.startswith("cu_seq") else v)
+                 for k, v in ds[(rank // sp) * n_batches + i].items()} for i in range(n_batches)]
+    else:
+        ds = SyntheticPackedDataset(n_batches * world, args.seq_len, mc["vocab_size"], min_doc=256, max_doc=args.seq_len,
+                                    seed=1234)
+        coll = PackedCollator(pin=True)
+        host = [coll([ds[(rank // sp) * n_batches + i]]) for i in range(n_batches)]   # an SP group shares its row
+
+    def tokens_in(batches) -> float:
+        """Tokens of the given steps summed over the data-parallel groups (rows differ in length with images)."""
+        n = torch.tensor([float(sum(int(b["input_ids"].numel()) for b in batches))], device=torch.device("cuda", local_rank))
+        if world > 1:
+            dist.all_reduce(n)
+        return float(n.item()) / sp
     dev = torch.device("cuda", local_rank)
 
     def to_device(b):
@@ -211,7 +237,8 @@ def run_ours(args) -> dict:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_dev = float(t.item())
     tokens_per_step = args.seq_len * (world // sp)
-    value = tokens_per_step * args.steps / (ms_dev / 1e3)
+    timed_tokens = tokens_in(host[args.warmup:args.warmup + args.steps]) if is_vlm else tokens_per_step * args.steps
+    value = timed_tokens / (ms_dev / 1e3)
     # ---- end-to-end region: public API, H2D of every batch from pinned memory, D2H of every loss
     e2e = None
     if not args.no_e2e:
@@ -230,7 +257,9 @@ def run_ours(args) -> dict:
         t2 = torch.tensor([f0.elapsed_time(f1)], device=dev)
         if world > 1:
             dist.all_reduce(t2, op=dist.ReduceOp.MAX)
-        e2e = {"value": tokens_per_step * args.steps / (float(t2.item()) / 1e3), "unit": "tokens/s",
+        e2e_tokens = (tokens_in(host[args.warmup + args.steps:args.warmup + 2 * args.steps]) if is_vlm
+                      else tokens_per_step * args.steps)
+        e2e = {"value": e2e_tokens / (float(t2.item()) / 1e3), "unit": "tokens/s",
                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4, "ms_per_step": float(t2.item()) / args.steps,
                "final_loss": losses[-1]}
     st = kernels.status()
@@ -355,7 +384,8 @@ def extras(args, out: dict, world: int, t_start: float) -> None:
     if mode == "all" or (mode == "auto" and world >= 8):
         out["secondary"] = []
         for extra in (["--model", "qwen3_14b", "--sp", str(world), "--seq-len", "65536", "--layers", "40"],
-                      ["--model", "qwen3_8b", "--seq-len", "8192", "--layers", "36"]):
+                      ["--model", "qwen3_8b", "--seq-len", "8192", "--layers", "36"],
+                      ["--model", "qwen3_vl_8b", "--sp", "2", "--seq-len", "4096", "--layers", "36"]):
             if left() < 200:
                 out["secondary"].append({"config": {"model": extra[1]}, "error": "skipped: wall-clock budget of the call used up"})
                 continue

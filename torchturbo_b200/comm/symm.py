@@ -15,6 +15,7 @@ from __future__ import annotations
 import importlib
 
 import ctypes as C
+import os
 
 import torch
 import torch.distributed as dist
@@ -51,6 +52,11 @@ class SymmetricBuffer:
         ptrs = list(self.handle.buffer_ptrs)
         assert len(ptrs) == self.world and ptrs[self.rank] == self.local.data_ptr()
         self.peer_ptrs = (C.c_ulonglong * self.world)(*ptrs)
+        # NVSwitch multicast address of the same buffer (0 when the fabric or the driver has no multicast support):
+        # `multimem.*` instructions on it reduce in the switch / store to every rank at once
+        self.multicast_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        if os.environ.get("TORCHTURBO_MULTIMEM", "1") == "0" or os.environ.get("NCCL_NVLS_ENABLE", "1") == "0":
+            self.multicast_ptr = 0        # multicast deliberately off (failure-detection runs keep every library off it)
         self.nbytes = nbytes
         self._cursor = 0
         dist.barrier(self.group)

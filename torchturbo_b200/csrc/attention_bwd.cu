@@ -11,8 +11,10 @@
 //     dV  += P^T  dO_i           [kv, d]     (K-major  x MN-major)
 //     dK  += dS^T Q_i            [kv, d]     (K-major  x MN-major)
 //     dQ^T = K_j^T dS^T          [d, q]      (MN-major x MN-major)  -> fp32 atomic add into dQ
-// Warp roles: 0 TMA producer, 1 MMA issuer, 2-5 softmax/dS, 6-9 dQ read-out.  Waits are bounded; on timeout the
-// roles drain to the final barrier, TMEM is freed and the status word records where the wait gave up.
+// Warp roles: 0 TMA producer, 1 MMA issuer, 2-5 softmax/dS, 6-9 dQ read-out.  P^T / dS^T (shared memory) and dQ^T
+// (TMEM) are double-buffered: the softmax warps of query tile i+1 run while the tensor cores still consume the
+// P^T / dS^T of tile i, and the dQ read-out of tile i overlaps the dQ^T MMAs of tile i+1.  Waits are bounded; on
+// timeout the roles drain to the final barrier, TMEM is freed and the status word records where the wait gave up.
 //
 // Replaces flash-attn 2's backward used through the reference attention interface
 // (models/modules/attention/interface.py:114-158).
@@ -45,9 +47,9 @@ struct BwdSmem {
   static constexpr int V = K + 32768;               // 32 KB
   static constexpr int Q0 = V + 32768;              // 2 x 16 KB
   static constexpr int DO0 = Q0 + 2 * 16384;        // 2 x 16 KB
-  static constexpr int PT = DO0 + 2 * 16384;        // 16 KB  P^T  [128 kv][64 q]
-  static constexpr int DST = PT + 16384;            // 16 KB  dS^T [128 kv][64 q]
-  static constexpr int LSE = DST + 16384;           // float [2][64]
+  static constexpr int PT = DO0 + 2 * 16384;        // 2 x 16 KB  P^T  [128 kv][64 q]
+  static constexpr int DST = PT + 2 * 16384;        // 2 x 16 KB  dS^T [128 kv][64 q]
+  static constexpr int LSE = DST + 2 * 16384;       // float [2][64]
   static constexpr int DELTA = LSE + 2 * 64 * 4;    // float [2][64]
   static constexpr int BARS = DELTA + 2 * 64 * 4;
   static constexpr int TOTAL = BARS + 256 + 1024;
@@ -83,12 +85,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* qdo_empty = bars + 3;   // [2]
   uint64_t* st_full = bars + 5;
   uint64_t* st_empty = bars + 6;
-  uint64_t* pds_full = bars + 7;
-  uint64_t* pds_empty = bars + 8;
-  uint64_t* dq_full = bars + 9;
-  uint64_t* dq_empty = bars + 10;
-  uint64_t* acc_full = bars + 11;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* pds_full = bars + 7;    // [2]
+  uint64_t* pds_empty = bars + 9;   // [2]
+  uint64_t* dq_full = bars + 11;    // [2]
+  uint64_t* dq_empty = bars + 13;   // [2]
+  uint64_t* acc_full = bars + 15;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   float* s_lse = reinterpret_cast<float*>(smem + BwdSmem::LSE);
   float* s_delta = reinterpret_cast<float*>(smem + BwdSmem::DELTA);
 
@@ -108,8 +110,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     mbar_init(kv_full, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
     mbar_init(st_full, 1); mbar_init(st_empty, 4);
-    mbar_init(pds_full, 4); mbar_init(pds_empty, 1);
-    mbar_init(dq_full, 1); mbar_init(dq_empty, 4);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&pds_full[i], 4); mbar_init(&pds_empty[i], 1);
+      mbar_init(&dq_full[i], 1); mbar_init(&dq_empty[i], 4);
+    }
     mbar_init(acc_full, 1);
     mbar_fence_init();
   }
@@ -123,7 +127,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tm_ST = tmem_base;          // 64 cols
   const uint32_t tm_DPT = tmem_base + 64;    // 64 cols
-  const uint32_t tm_DQT = tmem_base + 128;   // 64 cols
+  const uint32_t tm_DQT = tmem_base + 128;   // 2 x 64 cols
   const uint32_t tm_DV = tmem_base + 256;    // 128 cols
   const uint32_t tm_DK = tmem_base + 384;    // 128 cols
 
@@ -191,31 +195,33 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           if (!issue_scores(it + 1)) { ok = false; break; }
         }
         const int st = it & 1;
-        if (!mbar_wait(pds_full, it & 1, KID_ATTN_BWD, 5)) { ok = false; break; }
-        if (!mbar_wait(dq_empty, (it & 1) ^ 1, KID_ATTN_BWD, 6)) { ok = false; break; }
+        const uint32_t ph2 = (it >> 1) & 1;
+        if (!mbar_wait(&pds_full[st], ph2, KID_ATTN_BWD, 5)) { ok = false; break; }
+        if (!mbar_wait(&dq_empty[st], ph2 ^ 1, KID_ATTN_BWD, 6)) { ok = false; break; }
         tc_fence_after();
+        const uint32_t sPTb = sPT + st * 16384, sDSTb = sDST + st * 16384;
         const uint32_t sQ = smem_u32(smem + BwdSmem::Q0 + st * 16384);
         const uint32_t sDO = smem_u32(smem + BwdSmem::DO0 + st * 16384);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {  // reduction over q = 64
           // A: P^T / dS^T K-major single panel; B: dO / Q as [q rows][d] MN-major, d panels 8 KB apart
-          umma_ss(tm_DV, make_smem_desc(sPT + kk * 32, 16, 1024), make_smem_desc(sDO + kk * 2048, 8192, 1024), id_acc,
+          umma_ss(tm_DV, make_smem_desc(sPTb + kk * 32, 16, 1024), make_smem_desc(sDO + kk * 2048, 8192, 1024), id_acc,
                   (it | kk) != 0);
         }
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
-          umma_ss(tm_DK, make_smem_desc(sDST + kk * 32, 16, 1024), make_smem_desc(sQ + kk * 2048, 8192, 1024), id_acc,
+          umma_ss(tm_DK, make_smem_desc(sDSTb + kk * 32, 16, 1024), make_smem_desc(sQ + kk * 2048, 8192, 1024), id_acc,
                   (it | kk) != 0);
         }
         umma_commit(&qdo_empty[st]);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {  // reduction over kv = 128
           // A: K^T from the K tile ([kv rows][d], MN-major, d panels 16 KB apart); B: dS^T ([kv rows][q]) MN-major
-          umma_ss(tm_DQT, make_smem_desc(sK + kk * 2048, 16384, 1024), make_smem_desc(sDST + kk * 2048, 8192, 1024),
+          umma_ss(tm_DQT + st * 64, make_smem_desc(sK + kk * 2048, 16384, 1024), make_smem_desc(sDSTb + kk * 2048, 8192, 1024),
                   id_dq, kk != 0);
         }
-        umma_commit(dq_full);
-        umma_commit(pds_empty);
+        umma_commit(&dq_full[st]);
+        umma_commit(&pds_empty[st]);
       }
       if (ok) umma_commit(acc_full);
     }
@@ -227,8 +233,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const bool kv_ok = kv < de;
     const float c = p.scale * 1.4426950408889634f;
     const int tid = threadIdx.x - 64;  // 0..127 inside this group
-    uint8_t* sPT = smem + BwdSmem::PT;
-    uint8_t* sDST = smem + BwdSmem::DST;
     bool ok = true;
     // lse / delta of the 64 query rows of an iteration are staged one iteration ahead (double-buffered)
     auto stage = [&](int it) {
@@ -257,10 +261,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const float* lse = s_lse + (it & 1) * 64;
       const float* dl = s_delta + (it & 1) * 64;
       const bool need_mask = (q0 + BW_Q > de) || (kv0 + BW_KV > de) || (p.causal && kv0 + BW_KV - 1 > q0);
-      // previous P^T / dS^T must have been consumed
-      if (it > 0) {
-        if (!mbar_wait(pds_empty, (it - 1) & 1, KID_ATTN_BWD, 8)) { ok = false; break; }
-      }
+      // the tile that used this P^T / dS^T buffer two iterations ago must have been consumed (a fresh barrier passes)
+      if (!mbar_wait(&pds_empty[it & 1], ((it >> 1) & 1) ^ 1, KID_ATTN_BWD, 8)) { ok = false; break; }
+      uint8_t* sPT = smem + BwdSmem::PT + (it & 1) * 16384;
+      uint8_t* sDST = smem + BwdSmem::DST + (it & 1) * 16384;
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) {
         uint32_t wp[4], wd[4];
@@ -288,7 +292,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(pds_full);
+      if (lane == 0) mbar_arrive(&pds_full[it & 1]);
       if (it + 1 < n_it) stage(it + 1);
       asm volatile("bar.sync 1, 128;" ::: "memory");
     }
@@ -343,13 +347,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     bool ok = true;
     for (int it = 0; it < n_it && ok; ++it) {
       const int h = hq, q0 = it_q0(it);
-      if (!mbar_wait(dq_full, it & 1, KID_ATTN_BWD, 10)) { ok = false; break; }
+      if (!mbar_wait(&dq_full[it & 1], (it >> 1) & 1, KID_ATTN_BWD, 10)) { ok = false; break; }
       tc_fence_after();
       float v[64];
-      tmem_ld64(tm_DQT + (static_cast<uint32_t>(lg * 32) << 16), v);
+      tmem_ld64(tm_DQT + (it & 1) * 64 + (static_cast<uint32_t>(lg * 32) << 16), v);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(dq_empty);
+      if (lane == 0) mbar_arrive(&dq_empty[it & 1]);
       float* base = p.dq_acc + (static_cast<long long>(q0) * p.Hq + h) * BW_D + d;
       const int nq = min(BW_Q, de - q0);
 #pragma unroll

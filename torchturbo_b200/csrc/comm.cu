@@ -945,3 +945,45 @@ TTB_EXPORT int ttb_ep_ksum(const unsigned long long* peer_ptrs, long long off_re
   ep_ksum_kernel<<<(unsigned)T, threads, 0, STREAM(stream)>>>(p);
   LAUNCH_RET();
 }
+
+
+// ============================================================================================================
+// In-switch all-reduce of one symmetric fp32 buffer (NVLS multimem): rank r owns slice r of the buffer; it loads the
+// SUM of that slice over all ranks with one `multimem.ld_reduce` per 16 bytes (the NVSwitch adds the W copies on the
+// way), scales it and writes the result to every rank's buffer with one `multimem.st` (the switch replicates it).
+// Per GPU that is 1/W of the buffer in and 1/W out instead of the 2 (W-1)/W of a ring.  `mc` is the multicast
+// address of the buffer (same offset on every rank).  The caller brackets the kernel with the epoch-flag barrier
+// (every rank has finished writing its gradients / every rank has finished storing its slice).
+// Used for the flat gradient buffer of replicated decoder layers; the NCCL all-reduce it replaces is the one the
+// reference issues per replicated parameter (engine/backends/fsdp2/backend.py:415-436 there).
+// ============================================================================================================
+namespace ttb {
+__global__ void __launch_bounds__(512) multimem_allreduce_f32_kernel(float* mc, long long first4, long long last4, float scale) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = first4 + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < last4; i += stride) {
+    float* addr = mc + 4 * i;
+    float a, b, c, d;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(a), "=f"(b), "=f"(c), "=f"(d)
+                 : "l"(addr)
+                 : "memory");
+    a *= scale; b *= scale; c *= scale; d *= scale;
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+                 : "memory");
+  }
+}
+}  // namespace ttb
+
+// `n` floats (multiple of 4) at multicast address `mc`; this rank reduces and broadcasts slice `rank` of `W`.
+TTB_EXPORT int ttb_multimem_allreduce_f32(void* mc, long long n, int rank, int W, float scale, int grid, void* stream) {
+  if (mc == nullptr || (reinterpret_cast<unsigned long long>(mc) & 15) || n < 0 || (n & 3) || W < 1 || rank < 0 || rank >= W)
+    return 901;
+  const long long n4 = n / 4;
+  const long long per = (n4 + W - 1) / W;
+  const long long first = per * rank < n4 ? per * rank : n4;
+  const long long last = first + per < n4 ? first + per : n4;
+  if (grid < 1) grid = 1;
+  if (last > first)
+    ttb::multimem_allreduce_f32_kernel<<<grid, 512, 0, STREAM(stream)>>>(reinterpret_cast<float*>(mc), first, last, scale);
+  LAUNCH_RET();
+}

@@ -18,6 +18,7 @@ use `torch.distributed.fsdp.fully_shard` with bf16 parameters, fp32 reduction an
 from __future__ import annotations
 
 import contextlib
+import os
 import functools
 from typing import Any
 
@@ -75,6 +76,19 @@ def confidence_entropy_sum(logits: torch.Tensor, labels: torch.Tensor, ignore_in
     ent = -(lp.exp() * lp).sum(-1)
     return (ent * correct.to(ent.dtype)).sum(), n
 
+
+
+class _FlatGradExchange:
+    """Health view of the symmetric flat gradient buffer (status word of its flag waits), so that the engine's peer
+    status checks cover it like the other peer-memory workspaces."""
+
+    def __init__(self, parts: dict, rank: int):
+        self.status, self.rank = parts["status"], rank
+
+    def check(self) -> None:
+        code = int(self.status.item())
+        if code:
+            raise RuntimeError(f"gradient all-reduce of the replicated layers timed out on rank {self.rank} (code {code:#x})")
 
 
 class _HostInput:
@@ -615,7 +629,7 @@ class FSDP2Backend(BaseBackend):
         if not params:
             return
         sizes = [(p.numel() + 3) // 4 * 4 for p in params]          # 16-byte aligned slices
-        flat = torch.zeros(sum(sizes), dtype=torch.float32, device=params[0].device)
+        flat = self._alloc_replicated_flat(sum(sizes), params[0].device)
         off = 0
         for p, n in zip(params, sizes):
             p.main_grad = flat[off:off + p.numel()].view(p.shape)
@@ -623,6 +637,44 @@ class FSDP2Backend(BaseBackend):
             off += n
         self._rep_flat, self._rep_params = flat, params
         logger.info_rank0("replicated layers: %d parameters, %.1f MB flat fp32 gradient buffer", len(params), flat.numel() * 4 / 2**20)
+
+    def _alloc_replicated_flat(self, numel: int, device: torch.device) -> torch.Tensor:
+        """The flat gradient buffer lives in symmetric memory when the world is one NVLink domain: weight-gradient GEMMs
+        accumulate straight into peer-visible memory and the all-reduce is the in-switch multimem kernel (no copy-in)."""
+        self._rep_symm = None
+        if device.type == "cuda" and self.world_size > 1:
+            try:
+                from ....comm.symm import SymmetricBuffer
+
+                if SymmetricBuffer.usable(dist.group.WORLD) and os.environ.get("TORCHTURBO_REPLICATED_ALLREDUCE", "auto") != "nccl":
+                    buf = SymmetricBuffer(numel * 4 + 2 * 4 * self.world_size + 4096, dist.group.WORLD)
+                    if buf.multicast_ptr:
+                        off, flat = buf.carve(numel * 4, torch.float32)
+                        self._rep_symm = {"buf": buf, "off": off, "before": buf.channel(), "after": buf.channel(),
+                                          "status": torch.zeros(1, dtype=torch.int32, device=device)}
+                        self.peer_arenas = list(getattr(self, "peer_arenas", [])) + [_FlatGradExchange(self._rep_symm, self.rank)]
+                        logger.info_rank0("replicated layers: gradient all-reduce in the NVSwitch (multimem), %.1f MB", numel * 4 / 2**20)
+                        return flat
+            except Exception as e:  # noqa: BLE001 - no symmetric memory on this system: NCCL all-reduce
+                logger.info_rank0("replicated layers: symmetric gradient buffer unavailable (%s), NCCL all-reduce", e)
+        return torch.zeros(numel, dtype=torch.float32, device=device)
+
+    def _allreduce_replicated_flat(self) -> None:
+        sy = self._rep_symm
+        if sy is None:
+            dist.all_reduce(self._rep_flat, op=dist.ReduceOp.SUM)
+            self._rep_flat.div_(self.world_size)
+            return
+        from .... import kernels as K
+
+        buf, W, r = sy["buf"], self.world_size, self.rank
+        budget = int(os.environ.get("TORCHTURBO_P2P_WAIT_MS", "5000"))
+        for ch, run in ((sy["before"], True), (sy["after"], False)):
+            epoch = ch.next()
+            K.flag_signal(buf.peer_ptrs, ch.offset, r, W, epoch)        # mine is written / my slice is stored
+            K.flag_wait(buf.peer_ptrs, ch.offset, r, W, epoch, budget, sy["status"])
+            if run:
+                K.multimem_allreduce_f32(buf.multicast_ptr + sy["off"], self._rep_flat.numel(), r, W, 1.0 / W)
 
     @torch.no_grad()
     def _sync_replicated_grads(self) -> None:
@@ -638,8 +690,7 @@ class FSDP2Backend(BaseBackend):
         if mains:
             torch._foreach_add_(mains, grads)
         if self.world_size > 1:
-            dist.all_reduce(self._rep_flat, op=dist.ReduceOp.SUM)
-            self._rep_flat.div_(self.world_size)
+            self._allreduce_replicated_flat()
         for p in self._rep_params:
             if p.dtype == torch.float32:
                 p.grad = p.main_grad      # optimizers that only know `.grad` (fp32 runs) read the averaged view

@@ -938,6 +938,13 @@ def ulysses_move(peer_ptrs, off_buf, off_flags, local, heads, rep, rank, world, 
     return local
 
 
+def multimem_allreduce_f32(mc_ptr: int, n: int, rank: int, world: int, scale: float = 1.0, grid: int = 128):
+    """In-switch all-reduce (sum, then `scale`) of `n` fp32 values at multicast address `mc_ptr`; this rank handles slice
+    `rank`.  The caller synchronises the ranks before (all inputs written) and after (all slices stored)."""
+    _check(lib().ttb_multimem_allreduce_f32(C.c_void_p(mc_ptr), C.c_longlong(n), C.c_int(rank), C.c_int(world), C.c_float(scale),
+                                            C.c_int(grid), _stream()), "ttb_multimem_allreduce_f32")
+
+
 def peer_collective(peer_ptrs, off_data, off_ready, off_consumed, units, rank, world, epoch, budget_ms, done_counter,
                     status, *, kind: int, out: torch.Tensor | None = None, scale: float = 1.0, grid: int = 64):
     """Pull all-gather (kind 0) or pull reduce-scatter of fp32 (kind 1) / bf16 (kind 2) pieces over a slot of the
