@@ -290,20 +290,44 @@ class DistributedMuon(torch.optim.Optimizer):
                     self.state[e.param]["master"] = init if init is not None else lp.detach().float().clone()
                 m = self._momentum(e, group)
                 self._apply(e, self._orthogonalise(e, m.view(e.full_rows, e.cols)), group)
-            for bucket in self.buckets:
-                self._step_bucket(bucket, group)
+            self._run_buckets(group)
         except Exception:
             self._failed = True
             raise
         return loss
 
-    def _step_bucket(self, bucket: list[_Entry], group) -> None:
+    def _run_buckets(self, group) -> None:
+        """Two-slot software pipeline over the buckets: while the owners run Newton-Schulz on bucket i-1, the shards
+        of bucket i are already travelling (asynchronous all-to-all on the communication stream / gloo thread), and
+        the updates of bucket i-2 are applied once they have come back.  At most two buckets hold exchange buffers at
+        any time.  `TORCHTURBO_MUON_PIPELINE=0` runs the three phases of every bucket back to back instead (same
+        arithmetic, used as the reference in tests).  The reference's counterpart is `_run_async`
+        (engine/backends/fsdp2/optimizers/muon.py:2286 there)."""
+        import os
+
+        live = [b for b in self.buckets if any(e.param.grad is not None for e in b)]
+        if os.environ.get("TORCHTURBO_MUON_PIPELINE", "1") == "0":
+            for b in live:
+                ctx = self._bucket_gather(b, group, async_op=False)
+                self._bucket_compute(ctx, async_op=False)
+                self._bucket_finish(ctx, group)
+            return
+        n = len(live)
+        ctxs: list[dict | None] = [None] * n
+        for i in range(n + 2):
+            if i < n:
+                ctxs[i] = self._bucket_gather(live[i], group, async_op=True)
+            if 1 <= i <= n:
+                self._bucket_compute(ctxs[i - 1], async_op=True)
+            if i >= 2:
+                self._bucket_finish(ctxs[i - 2], group)
+                ctxs[i - 2] = None
+
+    def _bucket_gather(self, bucket: list[_Entry], group, *, async_op: bool) -> dict:
+        """Phase 1: momentum update of this rank's shards, packed by owner, sent with one all-to-all."""
         W, r = self.world, self.rank
         live = [e for e in bucket if e.param.grad is not None]
-        if not live:
-            return
         moms = {id(e): self._momentum(e, group).to(torch.bfloat16) for e in live}
-        # ---- gather shards at owners
         send_chunks, send_splits = [], [0] * W
         for o in range(W):
             for e in live:
@@ -313,37 +337,54 @@ class DistributedMuon(torch.optim.Optimizer):
                     send_chunks.append(chunk)
                     send_splits[o] += chunk.numel()
         recv_splits = [0] * W
-        for s in range(W):
+        for s_ in range(W):
             for e in live:
                 if e.owner == r:
-                    lo, hi = e.row_ranges[s]
-                    recv_splits[s] += (hi - lo) * e.cols
+                    lo, hi = e.row_ranges[s_]
+                    recv_splits[s_] += (hi - lo) * e.cols
         dev = _local(live[0].param).device
         send = torch.cat(send_chunks) if send_chunks else torch.empty(0, dtype=torch.bfloat16, device=dev)
         recv = torch.empty(sum(recv_splits), dtype=torch.bfloat16, device=dev)
-        dist.all_to_all_single(recv, send, recv_splits, send_splits, group=self.group)
-        # ---- owners: reassemble, orthogonalise, split back
+        work = dist.all_to_all_single(recv, send, recv_splits, send_splits, group=self.group, async_op=async_op)
+        return {"live": live, "send": send, "recv": recv, "send_splits": send_splits, "recv_splits": recv_splits, "work": work,
+                "dev": dev}
+
+    def _bucket_compute(self, ctx: dict, *, async_op: bool) -> None:
+        """Phase 2 (owners): reassemble the complete matrices, orthogonalise, send the rows back."""
+        W, r = self.world, self.rank
+        if ctx["work"] is not None:
+            ctx["work"].wait()
+        live, recv, dev = ctx["live"], ctx["recv"], ctx["dev"]
         mine = [e for e in live if e.owner == r]
         fulls = {id(e): torch.empty(e.full_rows, e.cols, dtype=torch.bfloat16, device=dev) for e in mine}
         off = 0
-        for s in range(W):
+        for s_ in range(W):
             for e in mine:
-                lo, hi = e.row_ranges[s]
+                lo, hi = e.row_ranges[s_]
                 n = (hi - lo) * e.cols
                 fulls[id(e)][lo:hi].copy_(recv[off:off + n].view(hi - lo, e.cols))
                 off += n
         outs = {id(e): self._orthogonalise(e, fulls[id(e)]) for e in mine}
         back_chunks = []
-        for s in range(W):
+        for s_ in range(W):
             for e in mine:
-                lo, hi = e.row_ranges[s]
+                lo, hi = e.row_ranges[s_]
                 back_chunks.append(outs[id(e)][lo:hi].reshape(-1))
         back = torch.cat(back_chunks) if back_chunks else torch.empty(0, dtype=torch.bfloat16, device=dev)
-        ret = torch.empty(sum(send_splits), dtype=torch.bfloat16, device=dev)
-        dist.all_to_all_single(ret, back, send_splits, recv_splits, group=self.group)
-        off = 0
+        ret = torch.empty(sum(ctx["send_splits"]), dtype=torch.bfloat16, device=dev)
+        ctx["back"], ctx["ret"] = back, ret
+        ctx["work"] = dist.all_to_all_single(ret, back, ctx["send_splits"], ctx["recv_splits"], group=self.group,
+                                             async_op=async_op)
+        ctx["send"] = ctx["recv"] = None
+
+    def _bucket_finish(self, ctx: dict, group) -> None:
+        """Phase 3: the orthogonalised rows of this rank's shards are back; apply them."""
+        W, r = self.world, self.rank
+        if ctx["work"] is not None:
+            ctx["work"].wait()
+        ret, off = ctx["ret"], 0
         for o in range(W):
-            for e in live:
+            for e in ctx["live"]:
                 if e.owner == o:
                     lo, hi = e.row_ranges[r]
                     n = (hi - lo) * e.cols
