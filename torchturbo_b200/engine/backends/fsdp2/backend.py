@@ -948,6 +948,9 @@ class FSDP2Backend(BaseBackend):
         use_chunk = self.config.loss_chunk.enabled or self.runtime.turbo_device.value == "cuda" or self.world_size > 1
         head = model.get_lm_head() if hasattr(model, "get_lm_head") else None
         use_chunk = use_chunk and head is not None
+        if self.config.dspark.enabled and getattr(model, "dspark", None) is not None:
+            # block-draft heads (DeepSeek-V4 DSpark): trained from the same row; they need the unshifted labels
+            inputs["dspark_labels"], inputs["dspark_config"] = labels, self.config.dspark
         out = model(**inputs, skip_lm_head=use_chunk)
         n_streams = 1 + (len(out.get("mtp_hidden_states") or ()) if self.config.mtp.enabled else 0)
         scales = [1.0] + [self.config.mtp.loss_scaling_factor] * (n_streams - 1)
@@ -964,6 +967,8 @@ class FSDP2Backend(BaseBackend):
             total = all_reduce_sum_autograd(total, self.sp_group)
             for k in comps:
                 dist.all_reduce(comps[k], group=self.sp_group)
+        if out.get("dspark_loss") is not None:
+            total = total + self.config.dspark.loss_scaling_factor * out["dspark_loss"]
         out["loss"] = total
         out["main_loss"] = comps.get("main")
         for k, v in comps.items():

@@ -53,6 +53,9 @@ class DeepseekV4Config(ModelConfig):
         index_topk=512, hc_mult=4, hc_sinkhorn_iters=20, hc_eps=1e-6, swiglu_limit=0.0, num_hash_layers=0,
         num_mtp_layers=0, rms_norm_eps=1e-6, tie_word_embeddings=False, initializer_range=0.02, pad_token_id=0,
         torch_dtype="bfloat16", first_k_dense_replace=0, router_dtype="fp32", dsa_indexer_loss_coeff=0.0,
+        # DSpark block-draft heads (0 = none): block length, draft stages, rank of the transition head, the target layers
+        # whose states feed the draft context (default: the last one), the token id that fills the undrafted positions
+        dspark_block_size=0, dspark_num_layers=1, dspark_markov_rank=64, dspark_target_layer_ids=None, dspark_mask_token_id=None,
     )
 
     def __init__(self, **kw):
@@ -65,6 +68,11 @@ class DeepseekV4Config(ModelConfig):
         self.compress_ratios = list(self.compress_ratios)
         self.num_experts = self.n_routed_experts
         self.num_nextn_predict_layers = self.num_mtp_layers
+        if not self.dspark_target_layer_ids:
+            self.dspark_target_layer_ids = [self.num_hidden_layers - 1]
+        self.dspark_target_layer_ids = [int(i) for i in self.dspark_target_layer_ids]
+        if self.dspark_mask_token_id is None:
+            self.dspark_mask_token_id = int(self.pad_token_id or 0)
 
 
 # --------------------------------------------------------------------------------------------------
@@ -451,16 +459,22 @@ class DeepseekV4Model(nn.Module):
         return emb.unsqueeze(1).expand(-1, self.config.hc_mult, -1).contiguous()
 
     def forward(self, input_ids=None, position_ids=None, inputs_embeds=None, cu_seq_lens_q=None, max_length_q=None,
-                global_position_ids=None, return_context=False, **_):
+                global_position_ids=None, return_context=False, collect_layers=None, **_):
         if inputs_embeds is None:
             inputs_embeds = self.embed_tokens(input_ids)
         e = inputs_embeds.reshape(-1, inputs_embeds.shape[-1])
         ctx = self.context(e.shape[0], global_position_ids if global_position_ids is not None else position_ids,
                            cu_seq_lens_q, max_length_q, input_ids, e.device)
         h = self.expand(e)
-        for layer in self.layers:
+        keep = set(collect_layers or ())
+        kept: dict[int, torch.Tensor] = {}
+        for i, layer in enumerate(self.layers):
             h = layer(h, ctx)
+            if i in keep:
+                kept[i] = h.float().mean(1).to(h.dtype)      # the hyper-connection copies of a layer, averaged
         out = self.norm(self.hc_head(h)).unsqueeze(0)
+        if collect_layers is not None:
+            ctx.extras["layer_states"] = kept
         return (out, ctx, h) if return_context else out
 
 
@@ -492,6 +506,11 @@ class DeepseekV4ForCausalLMBase(nn.Module):
         self.lm_head = LMHead(config.hidden_size, config.vocab_size, bias=False, dtype=dtype)
         n = int(config.num_mtp_layers or 0)
         self.mtp = nn.ModuleList([DeepseekV4NextN(config, config.num_hidden_layers + i, dtype) for i in range(n)]) if n else None
+        self.dspark = None
+        if int(getattr(config, "dspark_block_size", 0) or 0) > 0:
+            from .dspark import DSparkDraft
+
+            self.dspark = DSparkDraft(config, dtype)
         if not any(p.is_meta for p in self.parameters()):
             init_hybrid_weights(self, config.initializer_range)
             self.init_family_parameters()
@@ -520,11 +539,21 @@ class DeepseekV4ForCausalLMBase(nn.Module):
 
     def forward(self, input_ids=None, position_ids=None, inputs_embeds=None, cu_seq_lens_q=None, cu_seq_lens_k=None,
                 max_length_q=None, max_length_k=None, skip_lm_head=False, global_input_ids=None,
-                global_position_ids=None, **kw):
+                global_position_ids=None, dspark_labels=None, dspark_config=None, **kw):
+        draft = (self.dspark is not None and self.training and dspark_labels is not None and dspark_config is not None
+                 and self.model.sp_size == 1 and input_ids is not None)
         hidden, ctx, _ = self.model(input_ids=input_ids, position_ids=position_ids, inputs_embeds=inputs_embeds,
                                     cu_seq_lens_q=cu_seq_lens_q, max_length_q=max_length_q,
-                                    global_position_ids=global_position_ids, return_context=True)
+                                    global_position_ids=global_position_ids, return_context=True,
+                                    collect_layers=self.config.dspark_target_layer_ids if draft else None)
         out = CausalLMOutput(hidden_states=hidden)
+        if draft:
+            states = ctx.extras["layer_states"]
+            out["dspark_loss"] = self.dspark(
+                embed=self.model.embed_tokens, lm_head=self.lm_head, expand=self.model.expand,
+                target_hiddens=[states[i] for i in self.config.dspark_target_layer_ids], final_hidden=hidden[0],
+                input_ids=input_ids, labels=dspark_labels, positions=ctx.extras["positions_full"], cu_seqlens=ctx.cu_seqlens,
+                train_cfg=dspark_config)
         ids = global_input_ids if global_input_ids is not None else input_ids
         if self.mtp is not None and self.training and ids is not None:
             m = self.model
