@@ -147,8 +147,8 @@ def run(args, ref_dir: str) -> dict:
     for i in range(args.warmup):
         step(to_device(host[i]))
     # same rule as the other arm: keep warming up until two consecutive steps agree within 3 % (bounded)
-    warmup_used = args.warmup + (stabilise(lambda j: step(to_device(host[j % max(args.warmup, 1)])), sync, world, dev)
-                                 if use_cuda else 0)
+    warmup_used = args.warmup + (stabilise(lambda j: step(to_device(host[j % max(args.warmup, 1)])), sync, world, dev,
+                                           4 if getattr(args, "child", False) else 12) if use_cuda else 0)
     staged = [to_device(host[args.warmup + i]) for i in range(args.steps)]
     sampler = ClockSampler(local_rank)
     sync()

@@ -215,7 +215,8 @@ def run_ours(args) -> dict:
     for i in range(args.warmup):
         train_step(engine, model, optim, [to_device(host[i])], check_finite=False)
     warmup_used = args.warmup + stabilise(lambda j: train_step(engine, model, optim, [to_device(host[j % args.warmup])],
-                                                               check_finite=False), sync, world, dev)
+                                                               check_finite=False), sync, world, dev,
+                                          4 if args.child else EXTRA_WARMUP)
     # ---- device-timed region: inputs staged on the device beforehand
     staged = [to_device(host[args.warmup + i]) for i in range(args.steps)]
     sampler = ClockSampler(local_rank)
@@ -301,14 +302,14 @@ def run_ours(args) -> dict:
 EXTRA_WARMUP = 12
 
 
-def stabilise(step_fn, sync, world, dev) -> int:
+def stabilise(step_fn, sync, world, dev, limit: int = EXTRA_WARMUP) -> int:
     """Extra warm-up: runs single steps, each timed on the device (max over ranks), until two consecutive ones differ
-    by less than 3 % or EXTRA_WARMUP steps have run.  Returns how many ran."""
+    by less than 3 % or `limit` steps have run.  Returns how many ran."""
     import torch
     import torch.distributed as dist
 
     prev, used = None, 0
-    while used < EXTRA_WARMUP:
+    while used < limit:
         sync()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()

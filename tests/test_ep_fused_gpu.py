@@ -135,6 +135,81 @@ def _run(world, skew):
             raise
 
 
+def _worker_overflow(rank, world, init_file, err_dir, _skew):
+    """Adversarial routing: every token of every rank picks experts of rank 0, with a receive capacity of 1.0 x the
+    balanced share.  Rows that do not fit are not written (never outside the buffer); the step must not train on the
+    rest: the workspace status poisons the gradient norm on the device, the optimizer update is skipped and the
+    step's own finite check raises on every rank, naming the overflow."""
+    try:
+        import datetime
+
+        import torch.distributed as dist
+
+        os.environ.update({"NCCL_NVLS_ENABLE": "0", "LOCAL_RANK": str(rank), "RANK": str(rank), "WORLD_SIZE": str(world),
+                           "TORCHTURBO_EP_CAPACITY_FACTOR": "1.0", "TORCHTURBO_P2P_WAIT_MS": "20000"})
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", init_method=f"file://{init_file}", rank=rank, world_size=world,
+                                timeout=datetime.timedelta(seconds=120), device_id=torch.device("cuda", rank))
+        from torchturbo_b200.data import PackedCollator, SyntheticPackedDataset
+        from torchturbo_b200.engine import EngineConfig, TorchTurboEngine
+        from torchturbo_b200.engine.optimizers import OptimizerClassPlan
+        from torchturbo_b200.loops import train_step
+        from torchturbo_b200.models.modules.moe import MoELayer
+
+        eng = TorchTurboEngine(EngineConfig.from_dict({"mixed_precision": "bf16", "parallel_plan": {"sp_size": 1, "ep_size": world},
+                                                       "activation_checkpointing": {"enabled": False}}))
+        mc = dict(model_type="qwen3_moe", vocab_size=4096, hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+                  num_attention_heads=8, num_key_value_heads=2, head_dim=128, num_experts=16, num_experts_per_tok=4,
+                  moe_intermediate_size=256, norm_topk_prob=True)
+        model = eng.build_model(None, load_weights=False, init_kwargs={"config": mc})
+        opt = eng.prepare_optimizer(model, OptimizerClassPlan(torch.optim.AdamW, lr=1e-3))
+        ds = SyntheticPackedDataset(8, 1024, mc["vocab_size"], min_doc=128, max_doc=700, seed=0)
+
+        def batch(i):
+            b = PackedCollator()([ds[rank * 4 + i]])
+            return {k: (v.cuda() if isinstance(v, torch.Tensor) and not k.startswith("cu_seq") else v) for k, v in b.items()}
+
+        loss, _ = train_step(eng, model, opt, [batch(0)])          # balanced routing: fine
+        assert torch.isfinite(loss)
+        before = [p.detach().clone() for p in model.parameters()]
+        for m in model.modules():
+            if isinstance(m, MoELayer):
+                orig = m.router.forward
+
+                def skewed(x, input_ids=None, runtime=None, _orig=orig, _router=m.router):
+                    idx, prob, logits = _orig(x, input_ids, runtime)
+                    _router.last_counts = None          # the kernel's histogram belongs to the routing it replaced
+                    return torch.arange(idx.shape[1], device=idx.device, dtype=idx.dtype).expand_as(idx).contiguous(), prob, logits
+
+                m.router.forward = skewed
+        with pytest.raises(RuntimeError, match="capacity"):
+            train_step(eng, model, opt, [batch(1)])
+        for p, q in zip(model.parameters(), before):
+            pl, ql = (p._local_tensor if hasattr(p, "_local_tensor") else p), (q._local_tensor if hasattr(q, "_local_tensor") else q)
+            assert torch.equal(pl, ql), "the optimizer stepped on a batch with dropped rows"
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception:
+        with open(os.path.join(err_dir, f"rank{rank}.err"), "w") as f:
+            f.write(traceback.format_exc())
+        raise
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_receive_overflow_raises_in_the_same_step_and_skips_the_update():
+    import torch.multiprocessing as mp
+
+    with tempfile.TemporaryDirectory() as d:
+        try:
+            mp.start_processes(_worker_overflow, args=(2, os.path.join(d, "rdzv"), d, False), nprocs=2, join=True,
+                               start_method="spawn")
+        except Exception:
+            errs = sorted(f for f in os.listdir(d) if f.endswith(".err"))
+            if errs:
+                raise AssertionError(open(os.path.join(d, errs[0])).read())
+            raise
+
+
 def test_fused_exchange_single_rank_matches_oracle():
     """World 1: the push warps write into this GPU's own receive buffer and the scatter epilogue into its own return
     buffer, so the whole fused path (flags included) runs on one GPU."""
