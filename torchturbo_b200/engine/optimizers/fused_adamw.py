@@ -33,6 +33,11 @@ class FusedAdamW(torch.optim.Optimizer):
         # the backend uses it for the 1/ep scaling of expert gradients instead of a pass of its own over them
         self.grad_prescale: float = 1.0
         self._plans: dict[int, tuple[tuple, Any]] = {}
+        # the clip coefficient of the last CUDA step, copied to pinned host memory without blocking: a step the kernel
+        # skipped (non-finite coefficient) is taken back out of the step counters at the start of the next `step()`
+        self._clip_host: torch.Tensor | None = None
+        self._clip_event = None
+        self._clip_pending: list[dict] | None = None
 
     # -- clipping ------------------------------------------------------------------------------------
     def set_clip_coef(self, coef: torch.Tensor | None) -> None:
@@ -51,6 +56,39 @@ class FusedAdamW(torch.optim.Optimizer):
                 st["master"] = _local(p).detach().float().clone()
         return st
 
+    def load_state_dict(self, state_dict):
+        """State tensors are replaced: the cached pointer tables of the multi-tensor kernels are rebuilt."""
+        self._plans.clear()
+        self._clip_pending = None
+        return super().load_state_dict(state_dict)
+
+    def add_param_group(self, param_group):
+        if hasattr(self, "_plans"):
+            self._plans.clear()
+        return super().add_param_group(param_group)
+
+    def _settle_skipped_step(self) -> None:
+        """torch's fused AdamW does not advance `step` when `found_inf` is set; the kernel here skips the same way
+        on a non-finite clip coefficient, which the host learns one step later (no synchronisation inside a step)."""
+        pending, self._clip_pending = self._clip_pending, None
+        if pending is None:
+            return
+        self._clip_event.synchronize()
+        v = float(self._clip_host[0])
+        if v != v or v in (float("inf"), float("-inf")):
+            for st in pending:
+                st["step"] -= 1
+
+    def _note_clip(self, clip: torch.Tensor | None, states: list[dict]) -> None:
+        if clip is None or not clip.is_cuda:
+            return
+        if self._clip_host is None:
+            self._clip_host = torch.empty(1, dtype=torch.float32, pin_memory=True)
+            self._clip_event = torch.cuda.Event()
+        self._clip_host.copy_(clip.detach().reshape(1).float(), non_blocking=True)
+        self._clip_event.record()
+        self._clip_pending = (self._clip_pending or []) + states
+
     def grad_of(self, p: torch.Tensor) -> torch.Tensor | None:
         g = getattr(p, "main_grad", None)
         return g if g is not None else p.grad
@@ -60,6 +98,7 @@ class FusedAdamW(torch.optim.Optimizer):
         loss = closure() if closure is not None else None
         clip, self._clip_coef = self._clip_coef, None
         prescale, self.grad_prescale = self.grad_prescale, 1.0
+        self._settle_skipped_step()
         for gi, group in enumerate(self.param_groups):
             ps = [p for p in group["params"] if self.grad_of(p) is not None]
             if not ps:
@@ -72,6 +111,7 @@ class FusedAdamW(torch.optim.Optimizer):
             lp0 = _local(ps[0])
             if lp0.is_cuda and K.available():
                 self._step_cuda(gi, group, ps, states, step, clip, prescale)
+                self._note_clip(clip, states)
             else:
                 self._step_torch(group, ps, states, step, clip, prescale)
         return loss
@@ -94,7 +134,7 @@ class FusedAdamW(torch.optim.Optimizer):
         return total
 
     def _plan_for(self, gi, ps, states):
-        key = tuple(id(p) for p in ps)
+        key = tuple(id(p) for p in ps) + tuple(_local(st["exp_avg"]).data_ptr() for st in states)
         cached = self._plans.get(gi)
         if cached is None or cached[0] != key:
             masters, shadows = [], []
@@ -132,6 +172,8 @@ class FusedAdamW(torch.optim.Optimizer):
         bc1, bc2 = 1 - b1 ** step, 1 - b2 ** step
         coef = (float(clip) if clip is not None else 1.0) * prescale
         if coef != coef or coef in (float("inf"), float("-inf")):
+            for st in states:
+                st["step"] -= 1        # a skipped update does not advance the bias correction
             return
         for p, st in zip(ps, states):
             lp = _local(p)
