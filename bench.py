@@ -292,8 +292,10 @@ def run_ours(args) -> dict:
         "kernel_status": list(st), "peer_status": peer_status, "warmup_used": warmup_used,
         "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30,
     }
-    if world > 1:
-        dist.barrier()
+    # every rank lets go of its peer-mapped buffers before any of them leaves (rank 0 carries on with other work)
+    del optim
+    engine.close(model)
+    del model
     if dist.is_initialized():
         dist.destroy_process_group()
     return out if rank == 0 else {}

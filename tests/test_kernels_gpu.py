@@ -267,6 +267,28 @@ def test_fused_adamw_gradient_prescale(K):
 
 
 @pytest.mark.parametrize("score_fn", ["softmax_post", "softmax_pre", "sigmoid"])
+def test_router_rows_without_a_finite_logit_select_valid_experts(K, score_fn):
+    """A row of NaN (or -inf) logits, e.g. after an upstream exchange gave up, must still select expert ids inside
+    [0, E): the ids index histograms and routing tables in later kernels.  The weights of such a row may be NaN."""
+    torch.manual_seed(1)
+    T, E, k = 64, 128, 8
+    logits = torch.randn(T, E, device="cuda")
+    logits[3] = float("nan")
+    logits[7, ::2] = float("nan")
+    logits[11] = float("-inf")
+    bias = torch.randn(E, device="cuda")
+    out = K.router_fwd(logits, k, score_fn, expert_bias=bias, want_stats=True)
+    idx = out["topk_idx"].long()
+    assert int(idx.min()) >= 0 and int(idx.max()) < E
+    assert int(out["counts"].sum()) == T * k and int(out["aux_counts"].sum()) == T * k
+    for t in range(T):
+        assert idx[t].unique().numel() == k          # k distinct experts per token
+    good = torch.ones(T, dtype=torch.bool, device="cuda")
+    good[[3, 7, 11]] = False
+    assert torch.isfinite(out["topk_prob"][good]).all()
+
+
+@pytest.mark.parametrize("score_fn", ["softmax_post", "softmax_pre", "sigmoid"])
 def test_router(K, score_fn):
     torch.manual_seed(0)
     T, E, k = 333, 128, 8

@@ -64,8 +64,9 @@ def main(argv=None) -> None:
         torch.cuda.synchronize()
     if rank == 0:
         print(prof.key_averages().table(sort_by=args.sort, row_limit=args.rows, max_name_column_width=70))
+    del opt
+    eng.close(model)
     if world > 1:
-        torch.distributed.barrier()
         torch.distributed.destroy_process_group()
 
 

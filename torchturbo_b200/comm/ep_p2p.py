@@ -117,7 +117,7 @@ class EPWorkspace:
         a.off_ret, a.off_ret_vals, a.off_ret_flags = self.off_y, self.off_y_vals, self.ch_ret.offset
         a.row_tag = self.recv_tags.data_ptr()
         a.row_val = row_val.data_ptr() if row_val is not None else None
-        a.ret_epoch, a.done_counter = self.ch_ret.next(), self.done.data_ptr()
+        a.ret_epoch, a.done_counter, a.ret_rows = self.ch_ret.next(), self.done.data_ptr(), self.entries
         return a
 
     def ksum(self, T, k, residual=None):
@@ -169,7 +169,8 @@ class EPWorkspace:
         code = int(self.status.item())
         if code:
             what = "receive capacity exceeded (raise capacity_factor)" if code == 2 else \
-                "row index outside the receive buffer" if code == 3 else f"peer wait timed out (code {code:#x})"
+                "a row was addressed beyond its owner's receive buffer and was not sent (receive capacity exceeded on " \
+                "the owner, raise capacity_factor)" if code == 3 else f"peer wait timed out (code {code:#x})"
             raise RuntimeError(f"expert-parallel exchange failed on rank {self.rank}: {what}")
 
 

@@ -67,9 +67,10 @@ __global__ void ep_exchange_kernel(const EpExchangeParams p) {
     if (!wait_flag(f, p.epoch, p.budget_ns, 1, threadIdx.x, p.status)) s_ok = 0;
   }
   __syncthreads();
-  if (!s_ok) {
-    // a peer never answered: leave tables that make every later kernel of this layer a no-op (no rows, no tiles,
-    // destination rows outside the buffer, which the scatter kernel skips) instead of uninitialised indices
+  // a peer never answered, or (below) some owner's receive buffer is too small for this batch: leave tables that make
+  // every later kernel of this layer a no-op (no rows, no tiles, destination rows outside the buffer, which the
+  // senders skip) instead of uninitialised indices or rows past the end of a buffer
+  auto no_op_tables = [&]() {
     for (int e = threadIdx.x; e < E; e += blockDim.x) p.dest_base[e] = -(1 << 30);
     for (int el = threadIdx.x; el <= El; el += blockDim.x) {
       p.seg_start[el] = 0;
@@ -78,6 +79,9 @@ __global__ void ep_exchange_kernel(const EpExchangeParams p) {
     for (int m = threadIdx.x; m < p.m_tiles_cap; m += blockDim.x) p.tile_group[m] = -1;
     if (p.send_base)
       for (int e = threadIdx.x; e < E; e += blockDim.x) p.send_base[e] = 0;
+  };
+  if (!s_ok) {
+    no_op_tables();
     return;
   }
   const int* mine = reinterpret_cast<const int*>(p.peers.base[p.rank] + p.off_counts);
@@ -94,9 +98,16 @@ __global__ void ep_exchange_kernel(const EpExchangeParams p) {
       acc += ((tot + EP_ALIGN - 1) / EP_ALIGN) * EP_ALIGN;
     }
     s_seg[o * (El + 1) + El] = acc;
-    if (o == p.rank && acc > p.m_tiles_cap * EP_ALIGN) atomicExch(p.status, 2);  // receive capacity exceeded
+    // receive capacity exceeded on owner `o` (every rank sees the whole matrix, so all of them drop this layer's
+    // exchange together; the status makes the step fail before the optimizer runs)
+    if (acc > p.m_tiles_cap * EP_ALIGN) s_ok = 0;
   }
   __syncthreads();
+  if (!s_ok) {
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, 2);
+    no_op_tables();
+    return;
+  }
   // 4. tables
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     const int o = e / El, el = e - o * El;

@@ -86,14 +86,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t phase) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false (and records kernel/site) when the budget runs out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t phase, unsigned kernel_id, unsigned site) {
+// Bounded wait.  Returns false (and records kernel/site) when the budget runs out.  `budget_ns` is longer than the
+// default where the barrier's producer may itself be waiting for another GPU (rows pushed by peers).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t phase, unsigned kernel_id, unsigned site,
+                                          uint64_t budget_ns = kWaitBudgetNs) {
   if (mbar_try_wait(bar, phase)) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, phase)) {
     if ((++spins & 0xff) == 0) {
-      if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+      if (globaltimer_ns() - t0 > budget_ns) {
         set_status(kernel_id, site, blockIdx.x);
         return false;
       }

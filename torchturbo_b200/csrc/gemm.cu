@@ -64,6 +64,7 @@ struct EpFuse {
   const float* row_val;       // [M] scalar returned with the row, or null
   int ret_epoch;
   unsigned int* done_counter;
+  int ret_rows;               // rows of every rank's return buffer (tags at or past it are refused)
 };
 
 struct GemmParams {
@@ -136,6 +137,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // With the push prologue the producer may spend up to the exchange budget waiting for a peer's rows; the warps
+  // downstream of it (MMA issuer, epilogue) must outwait it, or they give up on tiles whose rows arrive later.
+  const uint64_t consumer_budget = p.ep.push_on ? p.ep.budget_ns + kWaitBudgetNs : kWaitBudgetNs;
 
   if (threadIdx.x < 32) s_landed[threadIdx.x] = 0u;
   if (threadIdx.x == 0) {
@@ -300,7 +304,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < nkb; ++kb) {
-          if (!mbar_wait(&full[stage], phase, KID_GEMM, 3)) { ok = false; break; }
+          if (!mbar_wait(&full[stage], phase, KID_GEMM, 3, consumer_budget)) {
+            if (p.ep.status) atomicCAS(p.ep.status, 0, 0x10000 | (11 << 8));
+            ok = false;
+            break;
+          }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * L::STAGE_BYTES);
           const uint32_t sb = sa + L::A_BYTES;
@@ -332,7 +340,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       decode(t, g, mt, nt);
       if (p.tile_group && p.tile_group[mt] < 0) continue;
       krange(g, k0, nkb);
-      if (!mbar_wait(&tfull[acc], acc_phase, KID_GEMM, 4)) { ok = false; break; }
+      if (!mbar_wait(&tfull[acc], acc_phase, KID_GEMM, 4, consumer_budget)) { ok = false; break; }
       tc_fence_after();
       const int row = mt * BM + lane_group * 32 + lane;
       const bool row_ok = row < p.M;
@@ -352,9 +360,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             if (rr >= p.M) continue;
             if (p.ep.scat_on) {
               const int tag = __ldcg(p.ep.row_tag + rr);
-              if (tag >= 0)
-                rowptr[j] = reinterpret_cast<__nv_bfloat16*>(p.ep.peers.base[tag >> EP_TAG_SHIFT] + p.ep.off_ret) +
-                            static_cast<long long>(tag & EP_TAG_MASK) * p.ldc;
+              if (tag >= 0) {
+                // a tag that names no rank or no entry (rows that never landed) must not become an address
+                if ((tag >> EP_TAG_SHIFT) < p.ep.W && (tag & EP_TAG_MASK) < p.ep.ret_rows)
+                  rowptr[j] = reinterpret_cast<__nv_bfloat16*>(p.ep.peers.base[tag >> EP_TAG_SHIFT] + p.ep.off_ret) +
+                              static_cast<long long>(tag & EP_TAG_MASK) * p.ldc;
+                else
+                  atomicCAS(p.ep.status, 0, 3);
+              }
             } else {
               rowptr[j] = reinterpret_cast<__nv_bfloat16*>(cbase) + static_cast<long long>(g) * p.c_group_stride +
                           static_cast<long long>(rr) * p.ldc;
@@ -362,7 +375,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
           if (p.ep.scat_on && p.ep.row_val && nt == 0 && col_half == 0 && row_ok) {
             const int tag = __ldcg(p.ep.row_tag + row);
-            if (tag >= 0)
+            if (tag >= 0 && (tag >> EP_TAG_SHIFT) < p.ep.W && (tag & EP_TAG_MASK) < p.ep.ret_rows)
               reinterpret_cast<float*>(p.ep.peers.base[tag >> EP_TAG_SHIFT] + p.ep.off_ret_vals)[tag & EP_TAG_MASK] =
                   p.ep.row_val[row];
           }
@@ -754,6 +767,7 @@ struct EpFuseArgs {
   const float* row_val;
   int ret_epoch;
   unsigned int* done_counter;
+  int ret_rows;
 };
 
 template <int BN, bool A_MN, bool B_MN, int EPI>
@@ -826,6 +840,7 @@ static int launch(const GemmArgs& a, cudaStream_t stream) {
     p.ep.off_ret = e.off_ret; p.ep.off_ret_vals = e.off_ret_vals; p.ep.off_ret_flags = e.off_ret_flags;
     p.ep.row_tag = e.row_tag; p.ep.row_val = e.row_val; p.ep.ret_epoch = e.ret_epoch;
     p.ep.done_counter = e.done_counter;
+    p.ep.ret_rows = e.ret_rows;
   }
   p.M = a.M; p.N = a.N; p.K = a.K;
   constexpr int TN = (EPI == EPI_SWIGLU) ? BN / 2 : BN;

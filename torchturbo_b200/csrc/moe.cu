@@ -50,6 +50,7 @@ __device__ __forceinline__ void warp_topk(const float (&sel)[MAX_E_PER_LANE], in
         int e = j * 32 + lane;
         if (e < E && !((taken >> j) & 1u)) {
           float v = sel[j];
+          if (!(v == v)) v = -INFINITY;   // NaN never wins a comparison: rank it last instead of selecting nothing
           if (v > bv || (v == bv && e < bi)) { bv = v; bi = e; }
         }
       }
@@ -118,7 +119,9 @@ __global__ void router_fwd_kernel(const RouterParams p) {
       float base = (p.score_fn == SOFTMAX_POST) ? lg[j] : sc[j];
       if (lg[j] == -INFINITY) base = -INFINITY;
       else if (p.expert_bias) base += p.expert_bias[e];
-      sel[j] = base;
+      // NaN compares false with everything: the selection below would find no candidate and return an index far
+      // outside [0, E).  As -inf a NaN row selects the lowest expert ids; its weights stay NaN and reach the loss.
+      sel[j] = (base == base) ? base : -INFINITY;
     }
     int idx[MAX_K];
     warp_topk(sel, epl, p.E, p.k, lane, idx);
@@ -152,9 +155,10 @@ __global__ void router_fwd_kernel(const RouterParams p) {
     }
     for (int r = 0; r < p.k; ++r) {
       if (lane == r) {
-        p.topk_idx[t * p.k + r] = idx[r];
+        const int e_sel = idx[r] < p.E ? idx[r] : p.E - 1;   // k > number of selectable experts: stay in range
+        p.topk_idx[t * p.k + r] = e_sel;
         p.topk_prob[t * p.k + r] = w;
-        if (p.counts) atomicAdd(&p.counts[idx[r]], 1);
+        if (p.counts) atomicAdd(&p.counts[e_sel], 1);
       }
     }
     // aux statistics: bias-free top-k over normalised scores, padding excluded
@@ -173,7 +177,7 @@ __global__ void router_fwd_kernel(const RouterParams p) {
           for (int r = 0; r < MAX_K; ++r) aidx[r] = idx[r];
         }
         for (int r = 0; r < p.k; ++r)
-          if (lane == r) atomicAdd(&p.aux_counts[aidx[r]], 1);
+          if (lane == r) atomicAdd(&p.aux_counts[aidx[r] < p.E ? aidx[r] : p.E - 1], 1);
       }
       if (p.score_partial) {
 #pragma unroll

@@ -378,6 +378,34 @@ class TorchTurboEngine(RLMixin):
 
             check_peer_status(what="peer-memory exchange since the last report")
 
+    def close(self, model: nn.Module | None = None) -> None:
+        """Orderly release of every peer-mapped (symmetric / multicast-bound) buffer this process holds: the flat
+        gradient buffer of replicated layers, the FSDP arenas and the exchange workspaces.  Collective: every rank
+        drops its buffers, drains its GPU and then meets the others at a barrier, so that no rank exits (or goes on to
+        other work) while its memory is still bound into an NVLink multicast object that the others have mapped.
+        The engine must not run another step afterwards."""
+        import gc
+
+        be = self.backend
+        if model is not None:
+            for p in model.parameters():
+                if getattr(p, "main_grad", None) is not None and getattr(p.main_grad, "_tt_flat_owner", None) is not None:
+                    p.main_grad = None
+                    p.grad = None
+        for name, empty in (("_rep_flat", None), ("_rep_symm", None), ("_rep_params", []), ("peer_arenas", [])):
+            if hasattr(be, name):
+                setattr(be, name, empty)
+        if self.runtime.turbo_device.value == "cuda":
+            from ..comm import ep_p2p, fsdp_p2p, rows_p2p, ulysses_p2p
+
+            for table in (ep_p2p._WORKSPACES, fsdp_p2p._ARENAS, ulysses_p2p._WORKSPACES, rows_p2p._WS):
+                table.clear()
+            gc.collect()
+            torch.cuda.synchronize()
+            torch.cuda.empty_cache()
+        if dist.is_available() and dist.is_initialized() and be.world_size > 1:
+            dist.barrier()
+
     def _get_mfu_estimator(self, model: nn.Module | None = None):
         if self._mfu is None and self.config.mfu.enabled and model is not None:
             recipe = model.get_flops_class()(model.config)

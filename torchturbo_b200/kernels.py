@@ -66,6 +66,7 @@ class EpFuseArgs(C.Structure):
         ("row_tag", C.c_void_p), ("row_val", C.c_void_p),
         ("ret_epoch", C.c_int),
         ("done_counter", C.c_void_p),
+        ("ret_rows", C.c_int),
     ]
 
 
@@ -475,11 +476,19 @@ class MultiTensorPlan:
         self.partial = torch.empty(max(self.n_chunks, 1), dtype=torch.float32, device=self.device)
 
     def refresh_grads(self, grads):
+        # the pinned table is read by the previous refresh's asynchronous copy until that copy has run on the device:
+        # a host that is a whole step ahead waits here instead of overwriting pointers still to be copied
+        ev = getattr(self, "_copy_event", None)
+        if ev is not None:
+            ev.synchronize()
         for i, g in enumerate(grads):
             assert g.is_contiguous() and g.numel() == self.host_meta[i, 5]
             self.host_meta[i, 1] = g.data_ptr()
             self.host_meta[i, 6] = int(g.dtype == torch.bfloat16)
         self.meta.copy_(self.host_meta, non_blocking=True)
+        if self.device.type == "cuda":
+            self._copy_event = torch.cuda.Event()
+            self._copy_event.record()
 
 
 def grad_sqnorm_partials(plan: MultiTensorPlan, prescale: float = 1.0) -> torch.Tensor:

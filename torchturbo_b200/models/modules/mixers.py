@@ -212,7 +212,9 @@ class MLAttention(nn.Module):
         self.q_lora, self.kv_lora = getattr(config, "q_lora_rank", None), config.kv_lora_rank
         self.d_nope, self.d_rope, self.d_v = config.qk_nope_head_dim, config.qk_rope_head_dim, config.v_head_dim
         self.d_qk = self.d_nope + self.d_rope
-        eps = config.rms_norm_eps
+        # the latent norms keep the norm class's default epsilon in every published MLA implementation, whatever
+        # `rms_norm_eps` says (transformers: deepseek_v3/modeling_deepseek_v3.py `DeepseekV3RMSNorm(config.q_lora_rank)`)
+        eps = getattr(config, "mla_latent_norm_eps", 1e-6)
         bias = getattr(config, "attention_bias", False) or getattr(config, "use_qkv_bias", False)
         if self.q_lora:
             self.q_a_proj = nn.Linear(H, self.q_lora, bias=bias, dtype=dtype)

@@ -182,8 +182,16 @@ class BaseWeightConverter:
 
 
 class FusedExpertWeightConverter(BaseWeightConverter):
-    """For checkpoints whose experts are 3-D fused tensors: `experts.gate_up_proj [E, H, 2F]` and
-    `experts.down_proj [E, F, H]`.  A rank loads only its expert slice (`narrow` on dim 0)."""
+    """For checkpoints whose experts are 3-D fused tensors in the Hugging Face layout: `experts.gate_up_proj
+    [E, 2F, H]` and `experts.down_proj [E, H, F]` (nn.Linear orientation per expert; the engine keeps `[E*H, 2F]` and
+    `[E*F, H]`, so each expert is transposed on the way in and out).  A rank loads only its expert slice (`narrow` on
+    dim 0).  Tensors whose fused key is absent from the checkpoint (the prediction-depth layers of Qwen3.5 ship per
+    expert; `transformers` writes per-expert files for the whole model) use the per-expert rules of the base class,
+    in both directions (models/weight_converter.py:477-560 of the reference)."""
+
+    def _fused_in_checkpoint(self, key: str) -> bool:
+        infos = self.checkpoint_info.tensor_infos if self.checkpoint_info else None
+        return infos is None or key in infos
 
     def load_recipe(self, name: str):
         m = re.match(r"(.*)\.experts\.weight([12])$", name)
@@ -191,8 +199,15 @@ class FusedExpertWeightConverter(BaseWeightConverter):
             return super().load_recipe(name)
         pre, which = m.groups()
         src = f"{pre}.experts.gate_up_proj" if which == "1" else f"{pre}.experts.down_proj"
+        if not self._fused_in_checkpoint(src):
+            return super().load_recipe(name)
         lo, n = self.ep_rank * self.num_local_experts, self.num_local_experts
-        return LoadRecipe([src], lambda ts: ts[0].narrow(0, lo, n).reshape(-1, ts[0].shape[-1]))
+
+        def asm(ts):
+            w = ts[0].narrow(0, lo, n).transpose(1, 2)          # [n, H, 2F] / [n, F, H]
+            return w.reshape(-1, w.shape[-1])
+
+        return LoadRecipe([src], asm)
 
     def to_hf_tensors(self, name, tensor, expert_offset=None):
         m = re.match(r"(.*)\.experts\.weight([12])$", name)
@@ -201,6 +216,9 @@ class FusedExpertWeightConverter(BaseWeightConverter):
         pre, which = m.groups()
         rows = self.config.hidden_size if which == "1" else self.config.moe_intermediate_size
         key = f"{pre}.experts.gate_up_proj" if which == "1" else f"{pre}.experts.down_proj"
+        if not self._fused_in_checkpoint(key):
+            return super().to_hf_tensors(name, tensor, expert_offset)
         off = self.ep_rank * self.num_local_experts if expert_offset is None else expert_offset
         # a virtual per-EP-rank key; the saver concatenates the `__ep<N>` pieces in rank order
-        return {f"{key}__ep{off // max(self.num_local_experts, 1)}": tensor.view(-1, rows, tensor.shape[-1])}
+        return {f"{key}__ep{off // max(self.num_local_experts, 1)}":
+                tensor.view(-1, rows, tensor.shape[-1]).transpose(1, 2).contiguous()}
