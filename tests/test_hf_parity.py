@@ -24,14 +24,36 @@ MOE = dict(DENSE, moe_intermediate_size=48, num_experts=8, num_experts_per_tok=2
            mlp_only_layers=[], router_aux_loss_coef=0.0, output_router_logits=False)
 
 
+LINEAR = dict(linear_conv_kernel_dim=4, linear_key_head_dim=16, linear_value_head_dim=16, linear_num_key_heads=2,
+              linear_num_value_heads=4, full_attention_interval=2)
+MLA = dict(vocab_size=320, hidden_size=64, intermediate_size=160, moe_intermediate_size=48, num_hidden_layers=3,
+           num_attention_heads=4, num_key_value_heads=4, n_routed_experts=8, n_shared_experts=1, num_experts_per_tok=2,
+           first_k_dense_replace=1, q_lora_rank=32, kv_lora_rank=24, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
+           n_group=2, topk_group=1, max_position_embeddings=512, rms_norm_eps=1e-5, tie_word_embeddings=False)
+
+
 def _hf(kind):
+    """(config, class) of the `transformers` model.  Attention runs in its eager form: the sparse-attention family
+    builds its causal mask only there (with sdpa and no padding the mask is left to the kernel, and the indexer's
+    selection then replaces it)."""
+    from transformers.models.auto.configuration_auto import CONFIG_MAPPING
+
     if kind == "qwen3":
-        from transformers import Qwen3Config, Qwen3ForCausalLM
-
-        return Qwen3Config(**DENSE), Qwen3ForCausalLM
-    from transformers import Qwen3MoeConfig, Qwen3MoeForCausalLM
-
-    return Qwen3MoeConfig(**MOE), Qwen3MoeForCausalLM
+        cfg, cls = CONFIG_MAPPING["qwen3"](**DENSE), transformers.Qwen3ForCausalLM
+    elif kind == "qwen3_moe":
+        cfg, cls = CONFIG_MAPPING["qwen3_moe"](**MOE), transformers.Qwen3MoeForCausalLM
+    elif kind == "qwen3_5_moe_text":
+        base = {k: v for k, v in DENSE.items() if k not in ("rope_theta", "attention_bias")}
+        cfg = CONFIG_MAPPING[kind](**dict(base, num_hidden_layers=4), **LINEAR, moe_intermediate_size=48,
+                                   shared_expert_intermediate_size=48, num_experts=8, num_experts_per_tok=2)
+        cls = transformers.Qwen3_5MoeForCausalLM
+    elif kind == "glm_moe_dsa":
+        cfg = CONFIG_MAPPING[kind](**MLA, index_n_heads=2, index_head_dim=16, index_topk=8)
+        cls = transformers.GlmMoeDsaForCausalLM
+    else:
+        raise KeyError(kind)
+    cfg._attn_implementation = "eager"
+    return cfg, cls
 
 
 def _engine():
@@ -67,6 +89,10 @@ def _w_parity(rank, world, kind, root):
     torch.manual_seed(0)
     cfg, cls = _hf(kind)
     hf = cls(cfg).float().eval()
+    with torch.no_grad():        # norm weights and biases away from their constant initial values
+        for p in hf.parameters():
+            if p.ndim == 1:
+                p.add_(torch.randn_like(p) * 0.1)
     src = os.path.join(root, "hf_src")
     hf.save_pretrained(src, safe_serialization=True)
     lens = [23, 9, 16]
@@ -95,7 +121,8 @@ def _w_parity(rank, world, kind, root):
     # ---- (b) this engine's HF export -> transformers
     ckpt = os.path.join(root, "checkpoint-1")
     eng.save_model(model, ckpt, final=True)
-    back = transformers.AutoModelForCausalLM.from_pretrained(os.path.join(ckpt, "huggingface"), dtype=torch.float32).eval()
+    back = transformers.AutoModelForCausalLM.from_pretrained(os.path.join(ckpt, "huggingface"), dtype=torch.float32,
+                                                                attn_implementation="eager").eval()
     sd_a, sd_b = hf.state_dict(), back.state_dict()
     assert set(sd_a) == set(sd_b), sorted(set(sd_a) ^ set(sd_b))[:8]
     # the export is written in bf16 (the training compute dtype): every tensor must be the bf16 rounding of its source,
@@ -107,6 +134,68 @@ def _w_parity(rank, world, kind, root):
     assert err < 1e-5, f"{kind}: exported checkpoint differs from the (bf16-rounded) source by {err}"
 
 
-@pytest.mark.parametrize("kind", ["qwen3", "qwen3_moe"])
+@pytest.mark.parametrize("kind", ["qwen3", "qwen3_moe", "qwen3_5_moe_text", "glm_moe_dsa"])
 def test_logits_loss_and_export_match_transformers(tmp_path, kind):
     run_distributed(_w_parity, 1, kind, str(tmp_path), timeout=400)
+
+
+def _fuse_expert_files(src):
+    """Rewrite the per-expert tensors of a checkpoint as the fused 3-D tensors that published Qwen3.5-MoE checkpoints
+    carry: `experts.gate_up_proj [E, 2F, H]`, `experts.down_proj [E, H, F]`."""
+    import re
+
+    from safetensors.torch import load_file, save_file
+
+    path = os.path.join(src, "model.safetensors")
+    sd = {k: v.clone() for k, v in load_file(path).items()}     # the file is rewritten below: no memory-mapped views
+    groups = {}
+    for k in list(sd):
+        m = re.match(r"(.*\.experts)\.(\d+)\.(gate_proj|up_proj|down_proj)\.weight$", k)
+        if m:
+            groups.setdefault(m.group(1), {}).setdefault(m.group(3), {})[int(m.group(2))] = sd.pop(k)
+    for pre, g in groups.items():
+        n = len(g["gate_proj"])
+        sd[f"{pre}.gate_up_proj"] = torch.stack([torch.cat([g["gate_proj"][e], g["up_proj"][e]], 0) for e in range(n)])
+        sd[f"{pre}.down_proj"] = torch.stack([g["down_proj"][e] for e in range(n)])
+    save_file(sd, path, metadata={"format": "pt"})
+    return sd
+
+
+def _w_fused_layout(rank, world, root):
+    torch.manual_seed(0)
+    cfg, cls = _hf("qwen3_5_moe_text")
+    hf = cls(cfg).float().eval()
+    src = os.path.join(root, "hf_src")
+    hf.save_pretrained(src, safe_serialization=True)
+    fused = _fuse_expert_files(src)
+    assert any(k.endswith("experts.gate_up_proj") for k in fused)
+    lens = [19, 14]
+    batch = _batch(cfg.vocab_size, lens)
+    ref_logits = _hf_logits(hf, batch["input_ids"], lens)
+    eng = _engine()
+    model = eng.build_model(src)
+    model.eval()
+    with torch.no_grad():
+        out = model(**{k: v for k, v in batch.items() if k != "labels"})
+    err = (out["logits"].float().reshape(1, -1, cfg.vocab_size) - ref_logits).abs().max().item()
+    assert err < 1e-4, f"fused expert layout: logits differ from transformers by {err}"
+    ckpt = os.path.join(root, "checkpoint-1")
+    eng.save_model(model, ckpt, final=True)
+    from safetensors import safe_open
+
+    got = {}
+    hf_dir = os.path.join(ckpt, "huggingface")
+    for f in sorted(os.listdir(hf_dir)):
+        if f.endswith(".safetensors"):
+            with safe_open(os.path.join(hf_dir, f), "pt") as sf:
+                for k in sf.keys():
+                    got[k] = sf.get_tensor(k)
+    assert set(got) == set(fused), sorted(set(got) ^ set(fused))[:8]
+    for k, v in fused.items():
+        assert got[k].shape == v.shape and torch.equal(got[k].float(), v.bfloat16().float()), k
+
+
+def test_fused_expert_checkpoint_layout_round_trip(tmp_path):
+    """Checkpoints with 3-D fused expert tensors load into the engine's `[E*H, 2F]` / `[E*F, H]` parameters (each
+    expert transposed) and are exported in the same fused layout and names."""
+    run_distributed(_w_fused_layout, 1, str(tmp_path), timeout=400)

@@ -185,7 +185,11 @@ class FSDP2CheckpointManager(BaseCheckpointManager):
         from safetensors.torch import save_file
 
         ctx = self.backend.get_parallel_context()
-        conv = model.get_weight_converter(ctx, None)
+        # with the source checkpoint at hand the export mirrors its expert format (fused 3-D tensors or per expert)
+        has_src = bool(source_path) and os.path.isdir(source_path) and (
+            os.path.exists(os.path.join(source_path, HF_INDEX)) or
+            any(f.endswith(".safetensors") for f in os.listdir(source_path)))
+        conv = model.get_weight_converter(ctx, source_path if has_src else None)
         rank, world = _rank(), _world()
         ep_size, ep_rank = ctx["ep"]["ep_size"], ctx["ep"]["ep_rank"]
         if rank == 0:
@@ -193,21 +197,34 @@ class FSDP2CheckpointManager(BaseCheckpointManager):
         if world > 1:
             dist.barrier()
         lora = getattr(model, "merged_lora_delta", None)
-        shard_idx, cur, cur_bytes = 0, {}, 0
         weight_map: dict[str, str] = {}
 
-        def flush():
-            nonlocal shard_idx, cur, cur_bytes
-            if not cur:
-                return
-            fn = f"model-rank{rank:05d}-{shard_idx:05d}.safetensors"
-            save_file({k: v.contiguous() for k, v in cur.items()}, os.path.join(path, fn), metadata={"format": "pt"})
-            with open(os.path.join(path, fn), "rb") as f:
-                os.fsync(f.fileno())
-            for k in cur:
-                weight_map[k] = fn
-            shard_idx, cur, cur_bytes = shard_idx + 1, {}, 0
+        class _Shards:
+            """Accumulates tensors and writes a file whenever the next one would pass the shard size."""
 
+            def __init__(self, stem: str):
+                self.stem, self.idx, self.cur, self.bytes = stem, 0, {}, 0
+
+            def add(self, key: str, t: torch.Tensor) -> None:
+                n = t.numel() * t.element_size()
+                if self.cur and self.bytes + n > MAX_SHARD_BYTES:
+                    self.flush()
+                self.cur[key] = t
+                self.bytes += n
+
+            def flush(self) -> None:
+                if not self.cur:
+                    return
+                fn = f"{self.stem}-{self.idx:05d}.safetensors"
+                save_file({k: v.contiguous() for k, v in self.cur.items()}, os.path.join(path, fn), metadata={"format": "pt"})
+                with open(os.path.join(path, fn), "rb") as f:
+                    os.fsync(f.fileno())
+                for k in self.cur:
+                    weight_map[k] = fn
+                self.idx, self.cur, self.bytes = self.idx + 1, {}, 0
+
+        # per-EP-rank pieces of fused expert tensors go to files of their own: rank 0 joins them and removes the files
+        shards, pieces = _Shards(f"model-rank{rank:05d}"), _Shards(f"ep-pieces-rank{rank:05d}")
         owner_rr = 0
         for name, t, dup in self._named_state(model):
             if dup:
@@ -229,12 +246,9 @@ class FSDP2CheckpointManager(BaseCheckpointManager):
                 full = full.float() + lora[name].to(full.device).float()
             for hf_name, ht in conv.to_hf_tensors(name, full.detach()).items():
                 ht = ht.to(dtype if ht.dtype.is_floating_point else ht.dtype).cpu()
-                nbytes = ht.numel() * ht.element_size()
-                if cur and cur_bytes + nbytes > MAX_SHARD_BYTES:
-                    flush()
-                cur[hf_name] = ht
-                cur_bytes += nbytes
-        flush()
+                (pieces if "__ep" in hf_name else shards).add(hf_name, ht)
+        shards.flush()
+        pieces.flush()
         maps: list[dict] = [weight_map]
         if world > 1:
             maps = [None] * world
@@ -258,8 +272,8 @@ class FSDP2CheckpointManager(BaseCheckpointManager):
             dist.barrier()
 
     def _merge_virtual_ep_keys(self, path: str, weight_map: dict[str, str]) -> dict[str, str]:
-        """Fused-expert checkpoints write one `<name>__ep<r>` piece per EP rank; concatenate them (rank order)
-        into the real tensor."""
+        """Fused-expert checkpoints write one `<name>__ep<r>` piece per EP rank; concatenate them (rank order) into
+        the real tensors, written in size-bounded files one tensor at a time, and remove the piece files."""
         from safetensors import safe_open
         from safetensors.torch import save_file
 
@@ -271,17 +285,32 @@ class FSDP2CheckpointManager(BaseCheckpointManager):
         if not groups:
             return weight_map
         out = {k: v for k, v in weight_map.items() if "__ep" not in k}
-        merged_tensors = {}
-        for base, parts in groups.items():
-            pieces = []
+        cur, cur_bytes, idx = {}, 0, 0
+
+        def flush():
+            nonlocal cur, cur_bytes, idx
+            if not cur:
+                return
+            fn = f"model-fused-experts-{idx:05d}.safetensors"
+            save_file(cur, os.path.join(path, fn), metadata={"format": "pt"})
+            for base in cur:
+                out[base] = fn
+            cur, cur_bytes, idx = {}, 0, idx + 1
+
+        for base, parts in sorted(groups.items()):
+            pcs = []
             for _, k in sorted(parts):
                 with safe_open(os.path.join(path, weight_map[k]), framework="pt", device="cpu") as f:
-                    pieces.append(f.get_tensor(k))
-            merged_tensors[base] = torch.cat(pieces, dim=0)
-        fn = "model-fused-experts.safetensors"
-        save_file(merged_tensors, os.path.join(path, fn), metadata={"format": "pt"})
-        for base in merged_tensors:
-            out[base] = fn
+                    pcs.append(f.get_tensor(k))
+            t = torch.cat(pcs, dim=0)
+            n = t.numel() * t.element_size()
+            if cur and cur_bytes + n > MAX_SHARD_BYTES:
+                flush()
+            cur[base] = t
+            cur_bytes += n
+        flush()
+        for fn in {weight_map[k] for parts in groups.values() for _, k in parts}:
+            os.remove(os.path.join(path, fn))
         return out
 
     # ------------------------------------------------------------------------------------------
