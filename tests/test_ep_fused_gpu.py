@@ -137,9 +137,9 @@ def _run(world, skew):
 
 def _worker_overflow(rank, world, init_file, err_dir, _skew):
     """Adversarial routing: every token of every rank picks experts of rank 0, with a receive capacity of 1.0 x the
-    balanced share.  Rows that do not fit are not written (never outside the buffer); the step must not train on the
-    rest: the workspace status poisons the gradient norm on the device, the optimizer update is skipped and the
-    step's own finite check raises on every rank, naming the overflow."""
+    balanced share.  The layer's exchange is dropped as a whole (no row is written anywhere), the workspace status
+    poisons the gradient norm on the device, the optimizer update is skipped and the step's own finite check raises
+    `EPCapacityExceeded` on every rank; with retries allowed the buffers are doubled and the step is repeated."""
     try:
         import datetime
 
@@ -182,11 +182,31 @@ def _worker_overflow(rank, world, init_file, err_dir, _skew):
                     return torch.arange(idx.shape[1], device=idx.device, dtype=idx.dtype).expand_as(idx).contiguous(), prob, logits
 
                 m.router.forward = skewed
-        with pytest.raises(RuntimeError, match="capacity"):
-            train_step(eng, model, opt, [batch(1)])
-        for p, q in zip(model.parameters(), before):
-            pl, ql = (p._local_tensor if hasattr(p, "_local_tensor") else p), (q._local_tensor if hasattr(q, "_local_tensor") else q)
-            assert torch.equal(pl, ql), "the optimizer stepped on a batch with dropped rows"
+        from torchturbo_b200.comm.ep_p2p import _WORKSPACES, EPCapacityExceeded
+
+        def params():
+            return [(p._local_tensor if hasattr(p, "_local_tensor") else p).detach().clone() for p in model.parameters()]
+
+        # (1) no retry allowed: the step raises on every rank, names the overflow, and no weight has changed
+        with pytest.raises(EPCapacityExceeded, match="capacity"):
+            train_step(eng, model, opt, [batch(1)], ep_overflow_retries=0)
+        for p, q in zip(params(), before):
+            ql = q._local_tensor if hasattr(q, "_local_tensor") else q
+            assert torch.equal(p, ql), "the optimizer stepped on a batch whose rows were not exchanged"
+        # (2) default: buffers are doubled (capacity 1.0 -> 2.0 covers "everything to one of two ranks") and the step is
+        #     repeated; it must now train, on a clean status
+        eng.recover_from_ep_overflow(opt)
+        cf0 = [ws.capacity_factor for ws in _WORKSPACES.values()]
+        os.environ["TORCHTURBO_EP_CAPACITY_FACTOR"] = "1.0"
+        for key in list(_WORKSPACES):      # back to the small buffers so that the step itself has to grow them
+            ws = _WORKSPACES.pop(key)
+            _WORKSPACES[key] = type(ws)(ws.group, ws.H, ws.E, ws.tokens, ws.topk, 1.0)
+            del ws
+        loss, gnorm = train_step(eng, model, opt, [batch(1)])
+        assert torch.isfinite(loss) and torch.isfinite(gnorm)
+        assert all(ws.capacity_factor == 2.0 for ws in _WORKSPACES.values()), (cf0, [ws.capacity_factor for ws in _WORKSPACES.values()])
+        assert any(not torch.equal(p, (q._local_tensor if hasattr(q, "_local_tensor") else q)) for p, q in zip(params(), before))
+        eng.check_health()
         dist.barrier()
         dist.destroy_process_group()
     except Exception:
@@ -196,7 +216,7 @@ def _worker_overflow(rank, world, init_file, err_dir, _skew):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_receive_overflow_raises_in_the_same_step_and_skips_the_update():
+def test_receive_overflow_is_caught_in_the_same_step_then_recovered_by_growing_the_buffers():
     import torch.multiprocessing as mp
 
     with tempfile.TemporaryDirectory() as d:

@@ -47,7 +47,8 @@ def main(argv=None) -> None:
         b = PackedCollator()([ds[i]])
         batches.append({k: (v.cuda() if isinstance(v, torch.Tensor) and not k.startswith("cu_seq") else v) for k, v in b.items()})
     for i in range(3):
-        train_step(eng, model, opt, [batches[i]], check_finite=False)
+        # warm-up reads the loss on the host: a step whose expert exchange overflows is repeated with larger buffers
+        train_step(eng, model, opt, [batches[i]], check_finite=True)
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     for i in range(3):
@@ -62,6 +63,7 @@ def main(argv=None) -> None:
     with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
         train_step(eng, model, opt, [batches[0]], check_finite=False)
         torch.cuda.synchronize()
+    eng.check_health()
     if rank == 0:
         print(prof.key_averages().table(sort_by=args.sort, row_limit=args.rows, max_name_column_width=70))
     del opt

@@ -52,8 +52,18 @@ from .symm import SymmetricBuffer
 _WORKSPACES: dict[tuple, "EPWorkspace"] = {}
 
 
+class EPCapacityExceeded(RuntimeError):
+    """Some rank's experts were routed more rows than its receive buffer holds.  No row was sent for that layer and
+    the optimizer update of the step is skipped (the status poisons the gradient norm); `grow_workspaces()` followed
+    by a repeat of the step makes the exchange dropless again."""
+
+
+CAPACITY_MARK = "receive capacity exceeded"
+
+
 class EPWorkspace:
     def __init__(self, group, hidden: int, num_experts: int, tokens: int, topk: int, capacity_factor: float):
+        self.tokens, self.topk, self.capacity_factor = tokens, topk, float(capacity_factor)
         self.group = group
         self.W, self.rank = dist.get_world_size(group), dist.get_rank(group)
         self.E, self.El, self.H = num_experts, num_experts // self.W, hidden
@@ -168,10 +178,34 @@ class EPWorkspace:
     def check(self) -> None:
         code = int(self.status.item())
         if code:
+            if code in (2, 3):
+                raise EPCapacityExceeded(
+                    f"expert-parallel exchange on rank {self.rank}: {CAPACITY_MARK} (capacity factor "
+                    f"{self.capacity_factor:g}: an owner was routed more than {self.cap} rows"
+                    + (", seen here as rows addressed beyond that owner's buffer" if code == 3 else "") + ")")
             what = "receive capacity exceeded (raise capacity_factor)" if code == 2 else \
                 "a row was addressed beyond its owner's receive buffer and was not sent (receive capacity exceeded on " \
                 "the owner, raise capacity_factor)" if code == 3 else f"peer wait timed out (code {code:#x})"
             raise RuntimeError(f"expert-parallel exchange failed on rank {self.rank}: {what}")
+
+
+def grow_workspaces(factor: float = 2.0) -> list[float]:
+    """Replace every workspace by one with `factor` x the receive capacity, up to the worst case (every row of every
+    rank routed to one owner).  Collective: all ranks call it at the same point (they all see the overflow status).
+    Returns the new capacity factors."""
+    out = []
+    for key, ws in list(_WORKSPACES.items()):
+        cf = min(ws.capacity_factor * factor, float(ws.W))
+        if cf <= ws.capacity_factor:
+            raise EPCapacityExceeded(f"expert-parallel receive buffer is already sized for the worst case ({cf:g} x the "
+                                     "balanced share) and still overflowed: the batch is longer than the one that sized it "
+                                     "(set TORCHTURBO_EP_MAX_TOKENS)")
+        group, H, E, tokens, topk = ws.group, ws.H, ws.E, ws.tokens, ws.topk
+        del _WORKSPACES[key]
+        del ws
+        _WORKSPACES[key] = EPWorkspace(group, H, E, tokens, topk, cf)
+        out.append(cf)
+    return out
 
 
 def get_workspace(group, hidden, num_experts, tokens, topk, capacity_factor=2.0) -> EPWorkspace:

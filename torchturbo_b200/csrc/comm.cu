@@ -61,10 +61,12 @@ __global__ void ep_exchange_kernel(const EpExchangeParams p) {
     int* f = reinterpret_cast<int*>(p.peers.base[threadIdx.x] + p.off_flags) + p.rank;
     st_release_sys(f, p.epoch);
   }
-  // 2. wait for every peer's counts
+  // 2. wait for every peer's counts (a workspace that has already failed does not wait: its peers have their answer
+  //    above, and this layer's exchange is dropped like the rest of the step)
   if (threadIdx.x < W) {
     const int* f = reinterpret_cast<const int*>(p.peers.base[p.rank] + p.off_flags) + threadIdx.x;
-    if (!wait_flag(f, p.epoch, p.budget_ns, 1, threadIdx.x, p.status)) s_ok = 0;
+    if (*reinterpret_cast<volatile int*>(p.status) != 0 || !wait_flag(f, p.epoch, p.budget_ns, 1, threadIdx.x, p.status))
+      s_ok = 0;
   }
   __syncthreads();
   // a peer never answered, or (below) some owner's receive buffer is too small for this batch: leave tables that make

@@ -134,6 +134,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   __shared__ uint32_t s_landed[32];   // push prologue: experts (up to 1024) whose rows are known to have landed
   __shared__ int s_last_cta;
+  __shared__ int s_dead;              // the exchange this launch belongs to has already failed: no tile is computed
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -143,6 +144,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   if (threadIdx.x < 32) s_landed[threadIdx.x] = 0u;
   if (threadIdx.x == 0) {
+    // rows of a failed exchange never arrive: without this every CTA would sit out the full wait budget per launch
+    s_dead = (p.ep.status != nullptr && *reinterpret_cast<volatile int*>(p.ep.status) != 0) ? 1 : 0;
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
@@ -164,7 +167,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   const int groups = p.groups_k > 0 ? p.groups_k : 1;
   const long long tiles_per_group = static_cast<long long>(p.m_tiles) * p.n_tiles;
-  const long long total_tiles = tiles_per_group * groups;
+  const long long total_tiles = s_dead ? 0 : tiles_per_group * groups;
 
   // Decode tile -> (g, m_tile, n_tile).  Tiles are walked in bands of RASTER_M m-tiles: inside a band m runs
   // fastest, then n, so the ~148 tiles in flight cover a near-square RASTER_M x (148 / RASTER_M) block of C.  Per wave

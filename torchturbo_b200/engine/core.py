@@ -378,6 +378,29 @@ class TorchTurboEngine(RLMixin):
 
             check_peer_status(what="peer-memory exchange since the last report")
 
+    def recover_from_ep_overflow(self, optimizer=None) -> list[float]:
+        """Collective recovery after `EPCapacityExceeded`: drop the gradients of the failed step, give the expert-parallel
+        workspaces twice the receive capacity and clear the status words.  The caller then repeats the step (its
+        optimizer update was skipped on every rank, so the weights are those from before the step)."""
+        from ..comm.ep_p2p import grow_workspaces
+        from .health import reset_peer_status
+
+        be = self.backend
+        if optimizer is not None:
+            for o in getattr(optimizer, "optimizers", [optimizer]):
+                if hasattr(o, "set_clip_coef"):
+                    o.set_clip_coef(None)
+                    o.grad_prescale = 1.0
+                o.zero_grad(set_to_none=True)
+        if hasattr(be, "_after_optimizer_step"):
+            be._after_optimizer_step()       # flat gradient buffer of replicated layers
+        torch.cuda.synchronize()
+        grown = grow_workspaces(2.0)
+        reset_peer_status(be)
+        logger.warning_rank0("expert-parallel receive capacity exceeded: buffers grown to %s x the balanced share, step repeated",
+                             ", ".join(f"{c:g}" for c in grown))
+        return grown
+
     def close(self, model: nn.Module | None = None) -> None:
         """Orderly release of every peer-mapped (symmetric / multicast-bound) buffer this process holds: the flat
         gradient buffer of replicated layers, the FSDP arenas and the exchange workspaces.  Collective: every rank

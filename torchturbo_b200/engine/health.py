@@ -125,11 +125,34 @@ def peer_workspaces(backend: Any = None) -> list[Any]:
 def check_peer_status(workspaces: Iterable[Any] | None = None, *, what: str = "peer-memory exchange") -> None:
     """Raise on every rank if any rank's peer-memory kernels recorded a timeout / overflow since the last check."""
 
+    from ..comm.ep_p2p import CAPACITY_MARK, EPCapacityExceeded
+
     def local():
         for ws in (peer_workspaces() if workspaces is None else workspaces):
             ws.check()
 
-    collective_check(local, what)
+    try:
+        collective_check(local, what)
+    except RemoteRankError as e:
+        # the same class on every rank: the caller's recovery (grow the buffers, repeat the step) is collective
+        if CAPACITY_MARK in str(e):
+            raise EPCapacityExceeded(str(e)) from None
+        raise
 
 
-__all__ = ["Heartbeat", "RankFailure", "RemoteRankError", "check_peer_status", "peer_workspaces"]
+def reset_peer_status(backend: Any = None) -> None:
+    """Clear every status word (workspaces, arenas and the per-unit words of the kernels) after a handled failure."""
+    import torch
+
+    from .. import kernels as K
+
+    for ws in peer_workspaces(backend):
+        st = getattr(ws, "status", None)
+        if isinstance(st, torch.Tensor):
+            st.zero_()
+    if K.available():
+        K.status(reset=True)
+        K.comm_status(reset=True)
+
+
+__all__ = ["Heartbeat", "RankFailure", "RemoteRankError", "check_peer_status", "peer_workspaces", "reset_peer_status"]

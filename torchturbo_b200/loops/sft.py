@@ -54,24 +54,43 @@ def _loss_multiplier(engine, num_items_in_batch) -> float:
 
 
 def train_step(engine, model, optimizer, micro_batches, *, max_grad_norm: float = 1.0, num_items_in_batch=None,
-               check_finite: bool = True):
-    """One optimizer step over a list of micro-batches.  Returns (mean loss tensor, grad norm tensor)."""
+               check_finite: bool = True, ep_overflow_retries: int = 4):
+    """One optimizer step over a list of micro-batches.  Returns (mean loss tensor, grad norm tensor).
+
+    With `check_finite` the loss and the gradient norm are read on the host before the update; a step whose
+    expert-parallel exchange overflowed a receive buffer is repeated with larger buffers (up to `ep_overflow_retries`
+    times; each repeat doubles the capacity).  Without it nothing is read: a failed step skips its update on the device
+    and the failure surfaces at the next `engine.check_health()` (logging / checkpoint boundaries)."""
+    from ..comm.ep_p2p import EPCapacityExceeded
+
     ga = len(micro_batches)
-    total = None
     mult = _loss_multiplier(engine, num_items_in_batch)
-    for mb in micro_batches:
-        loss = engine.compute_loss(model, mb, num_items_in_batch=num_items_in_batch, gradient_accumulation_steps=ga)
-        (loss * (mult / ga)).backward()
-        engine.collect_metrics(model)
-        d = loss.detach().float() * mult
-        total = d if total is None else total + d
-    gnorm = engine.clip_grad_norm_(model, max_grad_norm, optimizer)
-    if check_finite:
+    for attempt in range(1 + max(int(ep_overflow_retries), 0)):
+        total = None
+        for mb in micro_batches:
+            loss = engine.compute_loss(model, mb, num_items_in_batch=num_items_in_batch, gradient_accumulation_steps=ga)
+            (loss * (mult / ga)).backward()
+            engine.collect_metrics(model)
+            d = loss.detach().float() * mult
+            total = d if total is None else total + d
+        gnorm = engine.clip_grad_norm_(model, max_grad_norm, optimizer)
+        if not check_finite:
+            break
         try:
             # one host read for both; the norm is NaN on every rank when a peer-memory kernel of any rank failed
             assert_finite(torch.stack([total.reshape(()), gnorm.detach().float().reshape(())]), "loss or gradient norm")
+            break
         except FloatingPointError:
-            engine.check_health()     # names the failed exchange (timeout / receive overflow) when that is the cause
+            try:
+                engine.check_health()     # names the failed exchange (timeout / receive overflow) when that is the cause
+            except EPCapacityExceeded:
+                # dropless routing without a worst-case buffer: no row of the overflowing layer was sent and no weight
+                # has changed, so the receive buffers are doubled (on every rank, collectively) and the step is run again
+                if attempt >= ep_overflow_retries:
+                    raise
+                del loss, total, gnorm, d
+                engine.recover_from_ep_overflow(optimizer)
+                continue
             raise
     optimizer.step()
     optimizer.zero_grad(set_to_none=True)
