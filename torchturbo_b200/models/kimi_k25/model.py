@@ -1,11 +1,12 @@
 """`kimi_k25`: Kimi-K2.5, a DeepSeek-V3 language model (MLA + sigmoid group-limited MoE with shared experts) behind
-a ViT tower whose merged patch features replace the media placeholder tokens.
+the MoonViT tower (`vision.py`) whose merged, projected patch features replace the media placeholder tokens.
 
-Module tree as in models/kimi_k25/modeling_kimi_k25.py:901-925 of the reference: `vision_tower`, `mm_projector`
-(folded into the tower's merger here) and `language_model` (`.model`, `.lm_head`).  Plan
-(models/kimi_k25/parallel_plan.py:60-133): experts on the expert-data-parallel mesh, MoE blocks rebuilt EP-aware,
-decoder layers and tower blocks checkpointed, the tower world-sharded with vision balancing; Ulysses attention is
-bound per attention instance.  Muon recipe with MLA QK-clip as for the other MLA families."""
+Module tree and parameter names as in models/kimi_k25/modeling_kimi_k25.py:901-925 of the reference: `vision_tower`
+(MoonViT), `mm_projector` (patch-merger MLP) and `language_model` (`.model`, `.lm_head`), so a published checkpoint
+loads tower, projector and decoder by name.  Plan (models/kimi_k25/parallel_plan.py:60-133): experts on the
+expert-data-parallel mesh, MoE blocks rebuilt EP-aware, decoder layers and tower blocks checkpointed, the tower
+world-sharded with vision balancing; Ulysses attention is bound per attention instance.  Muon recipe with MLA QK-clip
+as for the other MLA families."""
 from __future__ import annotations
 
 from typing import Any
@@ -19,10 +20,9 @@ from ..base import TurboVLMModel
 from ..config import ModelConfig
 from ..modules.deepseek import DeepseekV3Config, DeepseekV3ForCausalLMBase, DeepseekWeightConverter, deepseek_plan
 from ..modules.transformer import CausalLMOutput
-from ..modules.vision import GridVisionBalanceIO
-from ..qwen3_5.modeling import as_dtype, init_hybrid_weights
-from ..qwen3_vl.modeling import Qwen3VLVisionConfig, VisionTower
+from ..qwen3_5.modeling import as_dtype
 from ..registry import register_model
+from .vision import MoonViT, MoonViTConfig, PatchMergerMLP, TemporalPoolVisionBalanceIO, init_moonvit
 
 
 class KimiK25Config(ModelConfig):
@@ -35,16 +35,8 @@ class KimiK25Config(ModelConfig):
         self.text_config = text_config if isinstance(text_config, ModelConfig) else DeepseekV3Config(**(text_config or {}))
         if not isinstance(vision_config, ModelConfig):
             vc = dict(vision_config or {})
-            # MoonViT key names -> the tower's
-            for src, dst in (("vt_num_hidden_layers", "depth"), ("vt_hidden_size", "hidden_size"),
-                             ("vt_num_attention_heads", "num_heads"), ("vt_intermediate_size", "intermediate_size")):
-                if src in vc:
-                    vc.setdefault(dst, vc.pop(src))
-            if "merge_kernel_size" in vc:
-                vc.setdefault("spatial_merge_size", int(tuple(vc.pop("merge_kernel_size"))[0]))
-            vc.setdefault("temporal_patch_size", 1)
-            vc.setdefault("out_hidden_size", self.text_config.hidden_size)
-            vision_config = Qwen3VLVisionConfig(**{k: v for k, v in vc.items() if not k.startswith("_")})
+            vc.setdefault("text_hidden_size", self.text_config.hidden_size)
+            vision_config = MoonViTConfig(**vc)
         self.vision_config = vision_config
         for k in ("hidden_size", "vocab_size", "num_hidden_layers", "num_attention_heads", "n_routed_experts",
                   "moe_intermediate_size", "num_experts"):
@@ -66,10 +58,12 @@ class KimiK25ForConditionalGenerationBase(nn.Module):
         super().__init__()
         self.config = config
         dtype = as_dtype(config.dtype)
-        self.vision_tower = VisionTower(config.vision_config, dtype)
+        vc = config.vision_config
+        self.vision_tower = MoonViT(vc, dtype)
+        self.mm_projector = PatchMergerMLP(vc, dtype) if vc.mm_projector_type == "patchmerger" else nn.Identity()
         self.language_model = DeepseekV3ForCausalLMBase(config.text_config)
         if not any(p.is_meta for p in self.vision_tower.parameters()):
-            init_hybrid_weights(self.vision_tower, config.initializer_range)
+            init_moonvit(self.vision_tower, self.mm_projector, config.initializer_range)
 
     @property
     def lm_head(self):
@@ -86,8 +80,9 @@ class KimiK25ForConditionalGenerationBase(nn.Module):
         emb = self.language_model.model.embed_tokens(input_ids)
         if pixel_values is None:
             v_in, grid = self.vision_tower.dummy_inputs(emb.device, emb.dtype)
-            return emb + 0.0 * self.vision_tower(v_in, grid_thw=grid).sum()
-        feats = self.vision_tower(pixel_values, grid_thw=grid_thw)
+            return emb + 0.0 * self.mm_projector(self.vision_tower(v_in, grid_thw=grid)).sum()
+        # patches arrive as [L, 3, p, p]; the tower (and the balancer in front of it) works on flat rows
+        feats = self.mm_projector(self.vision_tower(pixel_values.reshape(pixel_values.shape[0], -1), grid_thw=grid_thw))
         mask = input_ids == self.config.media_placeholder_token_id
         n = int(mask.sum())
         if n == 0:
@@ -109,9 +104,10 @@ class KimiK25ForConditionalGenerationBase(nn.Module):
 def get_parallel_plan():
     plan = deepseek_plan("language_model.model")
     plan.plan.update({
-        "vision_tower.blocks.*": FSDPPlanSpec(activation_checkpoint=True),
+        "vision_tower.encoder.blocks.*": FSDPPlanSpec(activation_checkpoint=True),
         "vision_tower": FSDPPlanSpec(standalone_world_shard=True, vision_balance=VisionBalanceSpec(
-            mode=VisionBalanceMode.PATCH_SQ, io=GridVisionBalanceIO(2))),
+            mode=VisionBalanceMode.PATCH_SQ, io=TemporalPoolVisionBalanceIO(2))),
+        "mm_projector": FSDPPlanSpec(standalone_world_shard=True),
         "language_model.model.embed_tokens": FSDPPlanSpec(standalone_world_shard=True),
         "language_model.lm_head": FSDPPlanSpec(standalone_world_shard=True),
     })
@@ -122,6 +118,8 @@ def get_parallel_plan():
 class TurboKimiK25ForConditionalGeneration(TurboVLMModel, KimiK25ForConditionalGenerationBase):
     config_class = KimiK25Config
     multimodal_input_keys = ("pixel_values", "grid_thws", "image_grid_thw")
+    vision_tower_module_names = ("vision_tower",)
+    multi_modal_projector_module_names = ("mm_projector",)
 
     @classmethod
     def get_default_parallel_plan(cls, **kwargs):
