@@ -199,3 +199,96 @@ def test_fused_expert_checkpoint_layout_round_trip(tmp_path):
     """Checkpoints with 3-D fused expert tensors load into the engine's `[E*H, 2F]` / `[E*F, H]` parameters (each
     expert transposed) and are exported in the same fused layout and names."""
     run_distributed(_w_fused_layout, 1, str(tmp_path), timeout=400)
+
+
+# ---- vision-language families: tower, placeholder fusion, multimodal rotary positions, DeepStack --------------------
+VIS = dict(depth=2, hidden_size=32, num_heads=4, intermediate_size=48, patch_size=2, temporal_patch_size=2, in_channels=3,
+           spatial_merge_size=2, out_hidden_size=64, num_position_embeddings=16)
+IMG, VSTART = 300, 301
+
+
+def _hf_vlm(kind):
+    from transformers.models.auto.configuration_auto import CONFIG_MAPPING
+
+    text = {k: v for k, v in DENSE.items() if k not in ("rope_theta", "attention_bias", "tie_word_embeddings")}
+    text["num_hidden_layers"] = 4
+    if kind == "qwen3_5":
+        text.update(LINEAR, rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.5,
+                                             "mrope_section": [2, 1, 1], "mrope_interleaved": True})
+        vis, cls = dict(VIS), transformers.Qwen3_5ForConditionalGeneration
+    else:
+        text.update(rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "mrope_section": [4, 2, 2],
+                                     "mrope_interleaved": True})
+        vis, cls = dict(VIS, deepstack_visual_indexes=[0, 1]), transformers.Qwen3VLForConditionalGeneration
+    cfg = CONFIG_MAPPING[kind](text_config=text, vision_config=vis, image_token_id=IMG, video_token_id=302,
+                               vision_start_token_id=VSTART, tie_word_embeddings=False)
+    cfg._attn_implementation = "eager"
+    return cfg, cls
+
+
+def _published_key(k: str) -> str:
+    """`save_pretrained` of the installed transformers applies its load-time renaming in reverse once too often for
+    these classes (`model.language_model.language_model.*`, `model.language_model.visual.*`); published checkpoints
+    have `model.language_model.*` and `model.visual.*`."""
+    import re
+
+    k = re.sub(r"^model\.(language_model\.)+visual\.", "model.visual.", k)
+    return k if k.startswith("model.visual.") else re.sub(r"^model\.(language_model\.)+", "model.language_model.", k)
+
+
+def _w_vlm(rank, world, kind, root):
+    from safetensors import safe_open
+    from safetensors.torch import load_file, save_file
+
+    torch.manual_seed(0)
+    cfg, cls = _hf_vlm(kind)
+    hf = cls(cfg).float().eval()
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.ndim == 1:
+                p.add_(torch.randn_like(p) * 0.1)
+    src = os.path.join(root, "hf_src")
+    hf.save_pretrained(src, safe_serialization=True)
+    fp = os.path.join(src, "model.safetensors")
+    published = {_published_key(k): v.clone() for k, v in load_file(fp).items()}
+    save_file(published, fp, metadata={"format": "pt"})
+    grid = torch.tensor([[1, 4, 4], [1, 2, 6]])                      # two images: 16 and 12 patches -> 4 and 3 rows
+    pixels = torch.randn(int(grid.prod(-1).sum()), 3 * 2 * 2 * 2)
+    T = 40
+    ids = torch.randint(0, 290, (1, T))
+    ids[0, 3], ids[0, 20] = VSTART, VSTART
+    ids[0, 4:8], ids[0, 21:24] = IMG, IMG
+    mm = (ids == IMG).int()
+    with torch.no_grad():
+        ref = hf(input_ids=ids, pixel_values=pixels, image_grid_thw=grid, mm_token_type_ids=mm).logits.float()
+        pos = hf.model.get_rope_index(ids, mm_token_type_ids=mm, image_grid_thw=grid)[0]          # [3, 1, T]
+        tower_ref = hf.model.visual(pixels, grid_thw=grid).pooler_output
+    eng = _engine()
+    model = eng.build_model(src)
+    model.eval()
+    cu = torch.tensor([0, T], dtype=torch.int32)
+    with torch.no_grad():
+        tower = model.model.visual(pixels, grid_thw=grid)
+        out = model(input_ids=ids, position_ids=pos, pixel_values=pixels, image_grid_thw=grid, cu_seq_lens_q=cu,
+                    cu_seq_lens_k=cu, max_length_q=T, max_length_k=T)
+    assert (tower - tower_ref).abs().max().item() < 1e-5, f"{kind}: vision tower differs from transformers"
+    err = (out["logits"].float().reshape(1, T, -1) - ref).abs().max().item()
+    assert err < 1e-4, f"{kind}: logits with images differ from transformers by {err}"
+    # export: same names, same (bf16-rounded) tensors as the published layout of the source
+    ckpt = os.path.join(root, "checkpoint-1")
+    eng.save_model(model, ckpt, final=True)
+    got = {}
+    hf_dir = os.path.join(ckpt, "huggingface")
+    for f in sorted(os.listdir(hf_dir)):
+        if f.endswith(".safetensors"):
+            with safe_open(os.path.join(hf_dir, f), "pt") as sf:
+                for k in sf.keys():
+                    got[k] = sf.get_tensor(k)
+    assert set(got) == set(published), sorted(set(got) ^ set(published))[:8]
+    for k, v in published.items():
+        assert got[k].shape == v.shape and torch.equal(got[k].float(), v.bfloat16().float()), k
+
+
+@pytest.mark.parametrize("kind", ["qwen3_5", "qwen3_vl"])
+def test_vision_language_logits_and_export_match_transformers(tmp_path, kind):
+    run_distributed(_w_vlm, 1, kind, str(tmp_path), timeout=400)

@@ -20,7 +20,7 @@ from ...parallel import FSDPPlanSpec, VisionBalanceMode, VisionBalanceSpec
 from ..bailing_hybrid.model import BailingWeightConverter, get_parallel_plan as text_plan
 from ..bailing_hybrid.modeling import BailingModel, BailingMoeV3Config
 from ..base import TurboVLMModel
-from ..config import ModelConfig
+from ..config import ModelConfig, NestedDtype
 from ..modules.hybrid import run_nextn_layers
 from ..modules.transformer import CausalLMOutput
 from ..modules.vision import GridVisionBalanceIO
@@ -30,7 +30,7 @@ from ..qwen3_vl.modeling import Qwen3VLVisionConfig, VisionTower
 from ..registry import register_model
 
 
-class BailingMoeV3VLConfig(ModelConfig):
+class BailingMoeV3VLConfig(NestedDtype, ModelConfig):
     model_type = "bailing_moe_v3_vl"
     _defaults = dict(image_patch_token=157157, video_patch_token=157175, tie_word_embeddings=False, initializer_range=0.02)
 
@@ -39,22 +39,18 @@ class BailingMoeV3VLConfig(ModelConfig):
         self.text_config = text_config if isinstance(text_config, ModelConfig) else BailingMoeV3Config(**(text_config or {}))
         if not isinstance(vision_config, ModelConfig):
             vc = dict(vision_config or {})
-            vc.setdefault("out_hidden_size", vc.get("hidden_size", 1152))       # the projector maps to the LLM width
-            vision_config = Qwen3VLVisionConfig(**vc)
+            vc.setdefault("out_hidden_size", 3584)
+            # DeepStack features of this tower are cut off before the projector (modeling_bailing_moe_v3_vl.py:2514-2520
+            # of the reference keeps the first `vision_out_dim` columns), so their mergers are not built
+            vc["deepstack_visual_indexes"] = ()
+            vision_config = Qwen3VLVisionConfig(**{k: v for k, v in vc.items() if not k.startswith("_")})
         self.vision_config = vision_config
+        self._adopt_dtype()
         for k in ("hidden_size", "vocab_size", "num_hidden_layers", "num_attention_heads", "num_experts",
                   "moe_intermediate_size", "head_dim"):
             setattr(self, k, getattr(self.text_config, k))
         self.image_token_id = self.image_patch_token
 
-    @property
-    def dtype(self):
-        return getattr(self.text_config, "dtype", None) or getattr(self.text_config, "torch_dtype", None)
-
-    @dtype.setter
-    def dtype(self, v):
-        self.text_config.torch_dtype = v
-        self.text_config.dtype = v
 
 
 class BailingVLModel(BailingModel):
@@ -76,7 +72,10 @@ class BailingMoeV3VLForConditionalGenerationBase(nn.Module):
         dtype = as_dtype(config.dtype)
         tc, vc = config.text_config, config.vision_config
         self.model = BailingVLModel(config, dtype)
-        self.linear_proj = nn.Linear(vc.out_hidden_size, tc.hidden_size, bias=True, dtype=dtype)
+        # `disable_merger_proj`: the tower hands over the joined 2x2 patch rows and this projector does all the mapping
+        vin = vc.hidden_size * vc.spatial_merge_size ** 2 if getattr(vc, "disable_merger_proj", False) else vc.out_hidden_size
+        self.linear_proj = nn.Sequential(nn.Linear(vin, tc.hidden_size, bias=True, dtype=dtype), nn.GELU(),
+                                         nn.Linear(tc.hidden_size, tc.hidden_size, bias=True, dtype=dtype))
         self.lm_head = LMHead(tc.hidden_size, tc.vocab_size, bias=False, dtype=dtype)
         n = int(getattr(tc, "num_nextn_predict_layers", 0) or 0)
         self.mtp = nn.ModuleList([self.model.make_nextn_layer(tc.num_hidden_layers + i, dtype) for i in range(n)]) if n else None
@@ -92,7 +91,8 @@ class BailingMoeV3VLForConditionalGenerationBase(nn.Module):
         return {"lm_head.weight": "model.embed_tokens.weight"} if getattr(self.config, "tie_word_embeddings", False) else {}
 
     def project(self, feats):
-        return ops.linear(feats, self.linear_proj.weight) + self.linear_proj.bias
+        a, b = self.linear_proj[0], self.linear_proj[2]
+        return ops.bias_act(ops.linear(ops.bias_act(ops.linear(feats, a.weight), a.bias, "gelu"), b.weight), b.bias)
 
     def fuse_media(self, input_ids, pixel_values, grid):
         emb = self.model.embed_tokens(input_ids)

@@ -34,20 +34,20 @@ class ModelConfig:
     def _normalise_hf_keys(cls, d: dict[str, Any]) -> dict[str, Any]:
         """transformers 5 stores the rotary settings as `rope_parameters: {rope_theta, rope_type, ...}` (4.x:
         top-level `rope_theta` + `rope_scaling`) and writes some sizes under their attribute-map alias
-        (`num_local_experts` for `num_experts`).  Explicit canonical keys win over aliases."""
+        (`num_local_experts` for `num_experts`).  Explicit canonical keys win over aliases; rotary settings inside
+        `rope_parameters` win over top-level keys of the same name."""
         for alias, name in cls._hf_aliases.items():
             if alias in d and name not in d:
                 d[name] = d[alias]
         rp = d.get("rope_parameters")
         if isinstance(rp, dict):
-            if "rope_theta" in rp and "rope_theta" not in d:
-                d["rope_theta"] = rp["rope_theta"]
+            # where `rope_parameters` exists it is what transformers 5 reads; a top-level key of the same name is a
+            # leftover default written next to it (`partial_rotary_factor` of the Qwen3.5 text config)
+            for k in ("rope_theta", "mrope_section", "mrope_interleaved", "partial_rotary_factor"):
+                if k in rp:
+                    d[k] = rp[k]
             if "rope_scaling" not in d and rp.get("rope_type", "default") not in (None, "default"):
                 d["rope_scaling"] = {k: v for k, v in rp.items() if k != "rope_theta"}
-            if "mrope_section" in rp and "mrope_section" not in d:
-                d["mrope_section"] = rp["mrope_section"]
-            if "partial_rotary_factor" in rp and "partial_rotary_factor" not in d:
-                d["partial_rotary_factor"] = rp["partial_rotary_factor"]
         return d
 
     # -- io ---------------------------------------------------------------------------------------
@@ -79,6 +79,35 @@ class ModelConfig:
 
     def __repr__(self) -> str:
         return f"{type(self).__name__}({self.to_dict()})"
+
+
+class NestedDtype:
+    """`dtype` of a composite (text + vision) config lives in its text config.  A `dtype` key at the top level of
+    `config.json` reaches the setter before the text config exists: it is kept and applied by `_adopt_dtype()`, which
+    the subclass calls once `text_config` is built (a dtype stated in the text config itself wins)."""
+
+    @property
+    def dtype(self):
+        tc = self.__dict__.get("text_config")
+        if tc is None:
+            return self.__dict__.get("_dtype_pending")
+        return getattr(tc, "dtype", None) or getattr(tc, "torch_dtype", None)
+
+    @dtype.setter
+    def dtype(self, v):
+        tc = self.__dict__.get("text_config")
+        if tc is None:
+            self.__dict__["_dtype_pending"] = v
+            return
+        tc.torch_dtype = v
+        tc.dtype = v
+
+    torch_dtype = dtype
+
+    def _adopt_dtype(self) -> None:
+        v = self.__dict__.pop("_dtype_pending", None)
+        if v is not None and self.dtype is None:
+            self.dtype = v
 
 
 def load_config(path_or_dict) -> ModelConfig:

@@ -17,7 +17,7 @@ import torch.nn as nn
 from ...engine.metrics.flops import VLMFlops
 from ...parallel import FSDPPlanSpec, VisionBalanceMode, VisionBalanceSpec
 from ..base import TurboVLMModel
-from ..config import ModelConfig
+from ..config import ModelConfig, NestedDtype
 from ..modules.deepseek import DeepseekV3Config, DeepseekV3ForCausalLMBase, DeepseekWeightConverter, deepseek_plan
 from ..modules.transformer import CausalLMOutput
 from ..qwen3_5.modeling import as_dtype
@@ -25,7 +25,7 @@ from ..registry import register_model
 from .vision import MoonViT, MoonViTConfig, PatchMergerMLP, TemporalPoolVisionBalanceIO, init_moonvit
 
 
-class KimiK25Config(ModelConfig):
+class KimiK25Config(NestedDtype, ModelConfig):
     model_type = "kimi_k25"
     _defaults = dict(media_placeholder_token_id=163605, pad_token_id=0, ignore_index=-100, tie_word_embeddings=False,
                      initializer_range=0.02)
@@ -38,19 +38,12 @@ class KimiK25Config(ModelConfig):
             vc.setdefault("text_hidden_size", self.text_config.hidden_size)
             vision_config = MoonViTConfig(**vc)
         self.vision_config = vision_config
+        self._adopt_dtype()
         for k in ("hidden_size", "vocab_size", "num_hidden_layers", "num_attention_heads", "n_routed_experts",
                   "moe_intermediate_size", "num_experts"):
             setattr(self, k, getattr(self.text_config, k))
         self.image_token_id = self.media_placeholder_token_id
 
-    @property
-    def dtype(self):
-        return getattr(self.text_config, "dtype", None) or getattr(self.text_config, "torch_dtype", None)
-
-    @dtype.setter
-    def dtype(self, v):
-        self.text_config.torch_dtype = v
-        self.text_config.dtype = v
 
 
 class KimiK25ForConditionalGenerationBase(nn.Module):

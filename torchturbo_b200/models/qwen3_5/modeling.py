@@ -13,7 +13,7 @@ from typing import Any
 import torch
 import torch.nn as nn
 
-from ..config import ModelConfig
+from ..config import ModelConfig, NestedDtype
 from ..modules.hybrid import HybridDecoderLayer, HybridModel, MultiTokenPredictor
 from ..modules.mixers import GatedDeltaNet, KimiDeltaAttention
 from ..modules.transformer import CausalLMOutput, DenseMLP, init_weights
@@ -38,7 +38,7 @@ class Qwen3_5TextConfig(ModelConfig):
         for k_src, k_dst in (("rope_theta", "rope_theta"), ("partial_rotary_factor", "partial_rotary_factor"),
                              ("mrope_section", "mrope_section"), ("mrope_interleaved", "mrope_interleaved")):
             if k_src in rp:
-                kw.setdefault(k_dst, rp[k_src])
+                kw[k_dst] = rp[k_src]          # what transformers reads; a top-level key next to it is a leftover default
         super().__init__(**kw)
         if not self.layer_types:
             n = self.full_attention_interval
@@ -46,7 +46,7 @@ class Qwen3_5TextConfig(ModelConfig):
                                 for i in range(self.num_hidden_layers)]
 
 
-class Qwen3_5Config(ModelConfig):
+class Qwen3_5Config(NestedDtype, ModelConfig):
     model_type = "qwen3_5"
     text_config_class = Qwen3_5TextConfig
     _defaults = dict(image_token_id=248056, video_token_id=248057, vision_start_token_id=248053, tie_word_embeddings=False,
@@ -61,18 +61,11 @@ class Qwen3_5Config(ModelConfig):
             vc.setdefault("out_hidden_size", self.text_config.hidden_size)
             vision_config = Qwen3VLVisionConfig(**vc)
         self.vision_config = vision_config
+        self._adopt_dtype()
         for k in self._mirrored + tuple(getattr(self, "_mirrored_extra", ())):
             if hasattr(self.text_config, k):
                 setattr(self, k, getattr(self.text_config, k))
 
-    @property
-    def dtype(self):
-        return getattr(self.text_config, "dtype", None) or getattr(self.text_config, "torch_dtype", None)
-
-    @dtype.setter
-    def dtype(self, v):
-        self.text_config.torch_dtype = v
-        self.text_config.dtype = v
 
 
 class Qwen3_5TextModel(HybridModel):

@@ -52,7 +52,8 @@ class TurboQwen3VLForConditionalGeneration(TurboVLMModel, Qwen3VLForConditionalG
         from ..modules.attention.ulysses import SequenceParallelInputSlicingSpec
 
         lm = self.model.language_model
-        return SequenceParallelInputSlicingSpec(lm, type(lm).forward)
+        return SequenceParallelInputSlicingSpec(lm, type(lm).forward, sliced_inputs=(
+            ("inputs_embeds", 1), ("position_ids", -1), ("deepstack_embeds", 2)))
 
     def on_materialized(self) -> None:
         self.model.language_model.rotary_emb.reset(self.lm_head.weight.device)
