@@ -292,3 +292,65 @@ def _w_vlm(rank, world, kind, root):
 @pytest.mark.parametrize("kind", ["qwen3_5", "qwen3_vl"])
 def test_vision_language_logits_and_export_match_transformers(tmp_path, kind):
     run_distributed(_w_vlm, 1, kind, str(tmp_path), timeout=400)
+
+
+def _w_kimi(rank, world, root):
+    """`kimi_k25` on a checkpoint laid out like the published one (`language_model.*`, `vision_tower.*`,
+    `mm_projector.*`): the decoder must equal `transformers.DeepseekV3ForCausalLM` on text, and a row with media must
+    run through MoonViT and the projector."""
+    import json
+
+    from safetensors.torch import load_file, save_file
+    from transformers.models.auto.configuration_auto import CONFIG_MAPPING
+
+    from torchturbo_b200.models.kimi_k25.vision import MoonViT, MoonViTConfig, PatchMergerMLP, init_moonvit
+
+    torch.manual_seed(0)
+    cfg = CONFIG_MAPPING["deepseek_v3"](**MLA)
+    cfg._attn_implementation = "eager"
+    hf = transformers.DeepseekV3ForCausalLM(cfg).float().eval()
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.ndim == 1:
+                p.add_(torch.randn_like(p) * 0.1)
+    lm_dir, src = os.path.join(root, "lm"), os.path.join(root, "kimi")
+    hf.save_pretrained(lm_dir, safe_serialization=True)
+    sd = {"language_model." + k: v.clone() for k, v in load_file(os.path.join(lm_dir, "model.safetensors")).items()}
+    vcfg = dict(patch_size=14, init_pos_emb_height=6, init_pos_emb_width=6, init_pos_emb_time=4, vt_num_attention_heads=4,
+                vt_num_hidden_layers=2, vt_hidden_size=64, vt_intermediate_size=96, merge_kernel_size=[2, 2],
+                text_hidden_size=MLA["hidden_size"])
+    vc = MoonViTConfig(**vcfg)
+    tower, proj = MoonViT(vc, torch.float32), PatchMergerMLP(vc, torch.float32)
+    init_moonvit(tower, proj, 0.05)
+    sd.update({"vision_tower." + k: v.clone() for k, v in tower.state_dict().items()})
+    sd.update({"mm_projector." + k: v.clone() for k, v in proj.state_dict().items()})
+    os.makedirs(src)
+    save_file(sd, os.path.join(src, "model.safetensors"), metadata={"format": "pt"})
+    with open(os.path.join(lm_dir, "config.json")) as f:
+        text_cfg = json.load(f)
+    with open(os.path.join(src, "config.json"), "w") as f:
+        json.dump({"model_type": "kimi_k25", "text_config": text_cfg, "vision_config": vcfg, "media_placeholder_token_id": 300}, f)
+    T = 24
+    ids = torch.randint(0, 290, (1, T))
+    with torch.no_grad():
+        ref = hf(input_ids=ids).logits.float()
+    eng = _engine()
+    model = eng.build_model(src)
+    model.eval()
+    for k, v in tower.state_dict().items():
+        assert torch.equal(model.vision_tower.state_dict()[k], v), k          # the tower was loaded by name
+    cu = torch.tensor([0, T], dtype=torch.int32)
+    kw = dict(position_ids=torch.arange(T)[None], cu_seq_lens_q=cu, cu_seq_lens_k=cu, max_length_q=T, max_length_k=T)
+    with torch.no_grad():
+        out = model(input_ids=ids, **kw)["logits"].float().reshape(1, T, -1)
+    err = (out - ref).abs().max().item()
+    assert err < 1e-4, f"kimi_k25 decoder differs from transformers.DeepseekV3ForCausalLM by {err}"
+    # one 4x4-patch image -> 4 media tokens
+    ids[0, 5:9] = 300
+    with torch.no_grad():
+        with_img = model(input_ids=ids, pixel_values=torch.randn(16, 3, 14, 14), grid_thws=torch.tensor([[1, 4, 4]]), **kw)["logits"]
+    assert torch.isfinite(with_img).all() and (with_img.float().reshape(1, T, -1)[0, 9:] - out[0, 9:]).abs().max() > 1e-4
+
+
+def test_kimi_k25_decoder_matches_transformers_and_tower_loads_by_name(tmp_path):
+    run_distributed(_w_kimi, 1, str(tmp_path), timeout=400)
