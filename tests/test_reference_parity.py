@@ -1,0 +1,117 @@
+"""This package's own modelling code against the reference's modelling classes, on identical weights (fp32, CPU).
+
+For the families that have no `transformers` class (`bailing_hybrid`, `llada2_moe`, `deepseek_v4`) the reference ships
+its own modelling files; when the reference is installed offline next to the benchmark baseline
+(`baseline/_ref`, not part of the repository) a tiny random model of its class is written as a checkpoint with its own
+tensor names, loaded through `engine.build_model`, and must give the same logits; the engine's Hugging Face export must
+then carry exactly the reference's tensor names and (bf16-rounded) values.  Skipped where the install is absent or its
+modelling code does not import with the installed `transformers`."""
+import importlib
+import json
+import os
+import sys
+
+import pytest
+import torch
+
+from dist_utils import run_distributed
+
+ROOT = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline")
+
+CASES = {
+    "bailing_hybrid": ("configuration_bailing_moe_v3", "BailingMoeV3Config", "modeling_bailing_moe_v3", "BailingMoeV3ForCausalLM", dict(
+        vocab_size=320, hidden_size=64, intermediate_size=160, num_hidden_layers=5, num_attention_heads=4, num_key_value_heads=4,
+        num_experts=8, num_shared_experts=1, num_experts_per_tok=2, n_group=2, topk_group=1, moe_intermediate_size=48,
+        moe_shared_expert_intermediate_size=48, first_k_dense_replace=1, head_dim=16, layer_group_size=5, kv_lora_rank=24,
+        q_lora_rank=32, qk_rope_head_dim=8, v_head_dim=16, qk_nope_head_dim=16, max_position_embeddings=512, pad_token_id=0,
+        eos_token_id=1, rms_norm_eps=1e-5), 2e-3),     # chunked (here) vs step-by-step (there) delta rule in fp32
+    "llada2_moe": ("configuration_llada2_moe", "LLaDA2MoeConfig", "modeling_llada2_moe", "LLaDA2MoeModelLM", dict(
+        vocab_size=320, hidden_size=64, intermediate_size=160, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
+        num_experts=8, num_shared_experts=1, num_experts_per_tok=2, n_group=2, topk_group=1, moe_intermediate_size=48,
+        first_k_dense_replace=1, head_dim=16, max_position_embeddings=512, pad_token_id=0, rms_norm_eps=1e-5, use_bias=False,
+        embedding_dropout=0.0, attention_dropout=0.0, output_dropout=0.0), 1e-4),
+    "deepseek_v4": ("configuration_deepseek_v4", "DeepseekV4Config", "modeling_deepseek_v4", "DeepseekV4ForCausalLM", dict(
+        vocab_size=320, hidden_size=64, intermediate_size=96, moe_intermediate_size=48, num_hidden_layers=4, num_attention_heads=4,
+        num_key_value_heads=1, n_routed_experts=8, n_shared_experts=1, num_experts_per_tok=2, q_lora_rank=32, kv_lora_rank=24,
+        qk_rope_head_dim=8, qk_nope_head_dim=24, v_head_dim=32, head_dim=32, o_groups=2, o_lora_rank=16, sliding_window=8,
+        compress_ratios=[1, 4, 1, 4], index_n_heads=2, index_head_dim=16, index_topk=4, hc_mult=2, hc_sinkhorn_iters=4,
+        num_hash_layers=1, max_position_embeddings=512, original_max_position_embeddings=256, rope_factor=1.0), 1e-4),
+}
+
+
+def _reference(kind):
+    if not os.path.isdir(os.path.join(ROOT, "_ref", "torchturbo")):
+        return None
+    sys.path[:0] = [os.path.join(ROOT, "_ref"), os.path.join(ROOT, "shims")]
+    try:
+        cmod, cname, mmod, mname, kw, tol = CASES[kind]
+        C = importlib.import_module(f"torchturbo.models.{kind}.{cmod}")
+        M = importlib.import_module(f"torchturbo.models.{kind}.{mmod}")
+        return getattr(C, cname), getattr(M, mname), kw, tol
+    except Exception:  # noqa: BLE001 - written for another transformers release
+        return None
+    finally:
+        del sys.path[:2]
+
+
+def _w_case(rank, world, kind, root):
+    from safetensors import safe_open
+    from safetensors.torch import save_file
+
+    from torchturbo_b200.engine import EngineConfig, TorchTurboEngine
+
+    cfg_cls, model_cls, kw, tol = _reference(kind)
+    torch.manual_seed(0)
+    cfg = cfg_cls(**kw)
+    cfg._attn_implementation = "eager"
+    ref = model_cls(cfg).float().eval()
+    with torch.no_grad():
+        for n, p in ref.named_parameters():
+            if not torch.isfinite(p).all() or p.abs().max() > 1e3:       # parameters the reference leaves uninitialised
+                p.copy_(torch.zeros_like(p) if "A_log" in n else torch.randn_like(p).clamp(-1, 1) * 0.1)
+            elif p.ndim == 1 and "A_log" not in n and "dt_bias" not in n:
+                p.add_(torch.randn_like(p) * 0.05)
+    src = os.path.join(root, "src")
+    os.makedirs(src)
+    sd = {k: v.detach().clone().contiguous() for k, v in ref.state_dict().items()}
+    save_file(sd, os.path.join(src, "model.safetensors"), metadata={"format": "pt"})
+    cd = cfg.to_dict()
+    cd.pop("torch_dtype", None)
+    cd.pop("dtype", None)
+    with open(os.path.join(src, "config.json"), "w") as f:
+        json.dump(cd, f, default=str)
+    T = 32
+    ids = torch.randint(0, cfg.vocab_size - 10, (1, T))
+    with torch.no_grad():
+        want = ref(input_ids=ids).logits.float()
+    eng = TorchTurboEngine(EngineConfig.from_dict({"mixed_precision": "fp32", "activation_checkpointing": {"enabled": False},
+                                                   "checkpoint": {"hf_export": "every"}}))
+    model = eng.build_model(src)
+    model.eval()
+    cu = torch.tensor([0, T], dtype=torch.int32)
+    with torch.no_grad():
+        got = model(input_ids=ids, position_ids=torch.arange(T)[None], cu_seq_lens_q=cu, cu_seq_lens_k=cu, max_length_q=T,
+                    max_length_k=T)["logits"].float().reshape(1, T, -1)
+    err = (got - want).abs().max().item()
+    assert err < tol * max(1.0, want.abs().max().item()), f"{kind}: logits differ from the reference's class by {err}"
+    ckpt = os.path.join(root, "checkpoint-1")
+    eng.save_model(model, ckpt, final=True)
+    out = {}
+    hf_dir = os.path.join(ckpt, "huggingface")
+    for fn in sorted(os.listdir(hf_dir)):
+        if fn.endswith(".safetensors"):
+            with safe_open(os.path.join(hf_dir, fn), "pt") as sf:
+                for k in sf.keys():
+                    out[k] = sf.get_tensor(k)
+    tied = {k for k in sd if k not in out and k.endswith(("lm_head.weight", "head.weight"))}
+    assert set(out) == set(sd) - tied, sorted(set(out) ^ (set(sd) - tied))[:8]
+    for k, v in out.items():
+        want_v = sd[k].bfloat16().float() if sd[k].is_floating_point() else sd[k]
+        assert v.shape == sd[k].shape and torch.equal(v.float() if v.is_floating_point() else v, want_v), k
+
+
+@pytest.mark.parametrize("kind", sorted(CASES))
+def test_logits_and_exported_names_match_the_reference_class(tmp_path, kind):
+    if _reference(kind) is None:
+        pytest.skip("reference package (or a transformers release its modelling code imports with) not installed")
+    run_distributed(_w_case, 1, kind, str(tmp_path), timeout=600)

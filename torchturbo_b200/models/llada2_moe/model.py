@@ -97,7 +97,9 @@ class BlockDiffusionAttention(nn.Module):
         if allow is not None:
             out = ops.masked_attention(q, k, v, allow, scale=self.scale)
         else:
-            out = ops.attention(q, k, v.contiguous(), ctx.cu_seqlens, ctx.max_seqlen, causal=True, scale=self.scale)
+            # a diffusion LM has no causal default: without a block mask every token of a packed segment sees the whole
+            # segment (`is_causal = False` in models/llada2_moe/modeling_llada2_moe.py:466 of the reference)
+            out = ops.attention(q, k, v.contiguous(), ctx.cu_seqlens, ctx.max_seqlen, causal=False, scale=self.scale)
         if sp > 1:
             out = gather_heads_scatter_seq(out.contiguous(), ctx.sp_group, sp)
         y = ops.linear(out.reshape(T, self.n_q * D), self.dense.weight)
