@@ -25,6 +25,21 @@ CASES = {
         moe_shared_expert_intermediate_size=48, first_k_dense_replace=1, head_dim=16, layer_group_size=5, kv_lora_rank=24,
         q_lora_rank=32, qk_rope_head_dim=8, v_head_dim=16, qk_nope_head_dim=16, max_position_embeddings=512, pad_token_id=0,
         eos_token_id=1, rms_norm_eps=1e-5), 2e-3),     # chunked (here) vs step-by-step (there) delta rule in fp32
+    # The language model of the VL family runs the reference's pure-torch delta-rule fallback on CPU, which normalises
+    # q and k with `F.normalize` (eps 1e-12 on the norm); this package and the kernels the reference uses on
+    # accelerators add 1e-6 under the square root, which shows on the tiny activations of a random 64-wide model.
+    "bailing_moe_v3_vl": ("configuration_bailing_moe_v3_vl", "BailingMoeV3VLConfig", "modeling_bailing_moe_v3_vl",
+                          "BailingMoeV3VLForConditionalGeneration", dict(
+        text_config=dict(
+            vocab_size=320, hidden_size=64, intermediate_size=160, num_hidden_layers=5, num_attention_heads=4, num_key_value_heads=4,
+            num_experts=8, num_shared_experts=1, num_experts_per_tok=2, n_group=2, topk_group=1, moe_intermediate_size=48,
+            moe_shared_expert_intermediate_size=48, first_k_dense_replace=1, head_dim=16, layer_group_size=5, kv_lora_rank=24,
+            q_lora_rank=32, qk_rope_head_dim=8, v_head_dim=16, qk_nope_head_dim=16, max_position_embeddings=512, pad_token_id=0,
+            eos_token_id=1, rms_norm_eps=1e-5),
+        vision_config=dict(depth=2, hidden_size=32, num_heads=4, intermediate_size=48, patch_size=2, temporal_patch_size=2,
+                           in_channels=3, spatial_merge_size=2, out_hidden_size=64, num_position_embeddings=16,
+                           deepstack_visual_indexes=[], disable_merger_proj=True),
+        image_token_id=300, video_token_id=302, vision_start_token_id=301, vision_end_token_id=303, mrope_section=[2, 1, 1]), 1e-2),
     "llada2_moe": ("configuration_llada2_moe", "LLaDA2MoeConfig", "modeling_llada2_moe", "LLaDA2MoeModelLM", dict(
         vocab_size=320, hidden_size=64, intermediate_size=160, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
         num_experts=8, num_shared_experts=1, num_experts_per_tok=2, n_group=2, topk_group=1, moe_intermediate_size=48,
@@ -81,7 +96,8 @@ def _w_case(rank, world, kind, root):
     with open(os.path.join(src, "config.json"), "w") as f:
         json.dump(cd, f, default=str)
     T = 32
-    ids = torch.randint(0, cfg.vocab_size - 10, (1, T))
+    vocab = getattr(cfg, "vocab_size", None) or cfg.text_config.vocab_size
+    ids = torch.randint(0, vocab - 30, (1, T))
     with torch.no_grad():
         want = ref(input_ids=ids).logits.float()
     eng = TorchTurboEngine(EngineConfig.from_dict({"mixed_precision": "fp32", "activation_checkpointing": {"enabled": False},
