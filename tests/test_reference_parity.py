@@ -131,3 +131,61 @@ def test_logits_and_exported_names_match_the_reference_class(tmp_path, kind):
     if _reference(kind) is None:
         pytest.skip("reference package (or a transformers release its modelling code imports with) not installed")
     run_distributed(_w_case, 1, kind, str(tmp_path), timeout=600)
+
+
+def _w_v4_depths(rank, world, root):
+    from safetensors.torch import save_file
+
+    from torchturbo_b200.engine import EngineConfig, TorchTurboEngine
+
+    sys.path[:0] = [os.path.join(ROOT, "_ref"), os.path.join(ROOT, "shims")]
+    C = importlib.import_module("torchturbo.models.deepseek_v4.configuration_deepseek_v4")
+    M = importlib.import_module("torchturbo.models.deepseek_v4.modeling_deepseek_v4")
+    P = importlib.import_module("torchturbo.models.deepseek_v4.mtp")
+    torch.manual_seed(0)
+    kw = dict(CASES["deepseek_v4"][4], num_hidden_layers=3, compress_ratios=[1, 4, 1, 1, 1], num_hash_layers=0,
+              num_nextn_predict_layers=2)
+    cfg = C.DeepseekV4Config(**kw)
+    cfg._attn_implementation = "eager"
+    ref = M.DeepseekV4ForCausalLM(cfg).float().eval()
+    ref.mtp = P.DeepseekV4MultiTokenPredictor(cfg).float().eval()
+    with torch.no_grad():
+        for p in ref.parameters():
+            if not torch.isfinite(p).all() or p.abs().max() > 1e3:
+                p.copy_(torch.randn_like(p).clamp(-1, 1) * 0.1)
+            elif p.ndim == 1:
+                p.add_(torch.randn_like(p) * 0.05)
+    T = 32
+    ids, pos = torch.randint(1, 300, (1, T)), torch.arange(T)[None]
+    streams = []
+    hook = ref.layers[-1].register_forward_hook(lambda m, a, o: streams.append(o[0]))
+    with torch.no_grad():
+        main = ref(input_ids=ids, position_ids=pos).logits.float()
+        hook.remove()
+        want = P.DeepseekV4MTPForwarder()._mtp_logits(ref, streams[0], ids, None, pos, None)
+    src = os.path.join(root, "src")
+    os.makedirs(src)
+    save_file({k: v.detach().clone().contiguous() for k, v in ref.state_dict().items()}, os.path.join(src, "model.safetensors"),
+              metadata={"format": "pt"})
+    cd = cfg.to_dict()
+    cd.pop("torch_dtype", None)
+    cd.pop("dtype", None)
+    with open(os.path.join(src, "config.json"), "w") as f:
+        json.dump(cd, f, default=str)
+    eng = TorchTurboEngine(EngineConfig.from_dict({"mixed_precision": "fp32", "activation_checkpointing": {"enabled": False}}))
+    model = eng.build_model(src)
+    model.train()                                     # prediction depths run in training mode only
+    cu = torch.tensor([0, T], dtype=torch.int32)
+    with torch.no_grad():
+        out = model(input_ids=ids, position_ids=pos, cu_seq_lens_q=cu, cu_seq_lens_k=cu, max_length_q=T, max_length_k=T)
+    assert (out["logits"].float().reshape(1, T, -1) - main).abs().max().item() < 1e-4
+    assert len(out["mtp_logits"]) == len(want) == 2
+    for i, (a, b) in enumerate(zip(out["mtp_logits"], want)):
+        err = (a.float().reshape(1, T, -1) - b.float()).abs().max().item()
+        assert err < 1e-4, f"prediction depth {i} differs from the reference by {err}"
+
+
+def test_deepseek_v4_prediction_depths_match_the_reference_forwarder(tmp_path):
+    if _reference("deepseek_v4") is None:
+        pytest.skip("reference package not installed")
+    run_distributed(_w_v4_depths, 1, str(tmp_path), timeout=600)

@@ -61,6 +61,12 @@ class DeepseekV4Config(ModelConfig):
     def __init__(self, **kw):
         if "window_size" in kw:
             kw.setdefault("sliding_window", kw.pop("window_size"))
+        # checkpoints state the number of prediction depths as `num_nextn_predict_layers`
+        # (models/deepseek_v4/configuration_deepseek_v4.py:179 of the reference); `num_mtp_layers` is this package's name
+        if kw.get("num_nextn_predict_layers") and not kw.get("num_mtp_layers"):
+            kw["num_mtp_layers"] = kw["num_nextn_predict_layers"]
+        if "dspark_noise_token_id" in kw and kw.get("dspark_mask_token_id") is None:
+            kw["dspark_mask_token_id"] = kw["dspark_noise_token_id"]
         super().__init__(**kw)
         self.head_dim = self.qk_nope_head_dim + self.qk_rope_head_dim
         if not self.compress_ratios:
@@ -479,7 +485,12 @@ class DeepseekV4Model(nn.Module):
 
 
 class DeepseekV4NextN(nn.Module):
-    """Prediction depth: `[enorm(emb(ids << 1)) | hnorm(h)] -> eh_proj -> block (own hyper-connections) -> head mix`."""
+    """Prediction depth (models/deepseek_v4/mtp.py:32-102 of the reference): every hyper-connection copy of the
+    incoming stream `[T, hc, H]` (the last decoder layer's output, or the previous depth's) is normalised and
+    projected, the projected embedding of the tokens shifted one step further is added to all copies, the result runs
+    through a decoder layer of its own, and the depth's own head mix and norm give the hidden state for the shared
+    head.  `eh_proj [H, 2H]` holds the checkpoint's `e_proj` (columns 0..H) and `h_proj` (columns H..2H).
+    Returns (stream for the next depth, hidden state for the head)."""
 
     def __init__(self, config: Any, layer_idx: int, dtype=None):
         super().__init__()
@@ -490,9 +501,13 @@ class DeepseekV4NextN(nn.Module):
         self.hc_head = HyperHead(h, config.hc_mult, config.hc_eps, eps)
         self.norm = RMSNorm(h, eps, dtype)
 
-    def forward(self, emb, hidden, ctx, expand):
-        x = ops.linear(torch.cat((self.enorm(emb), self.hnorm(hidden)), -1), self.eh_proj.weight)
-        return self.norm(self.hc_head(self.block(expand(x), ctx)))
+    def forward(self, emb, stream, ctx):
+        T, hc, H = stream.shape
+        w = self.eh_proj.weight
+        x = ops.linear(self.hnorm(stream.reshape(T * hc, H)), w[:, H:].contiguous()).view(T, hc, H)
+        x = x + ops.linear(self.enorm(emb), w[:, :H].contiguous()).unsqueeze(1)
+        y = self.block(x, ctx)
+        return y, self.norm(self.hc_head(y))
 
 
 class DeepseekV4ForCausalLMBase(nn.Module):
@@ -542,7 +557,7 @@ class DeepseekV4ForCausalLMBase(nn.Module):
                 global_position_ids=None, dspark_labels=None, dspark_config=None, **kw):
         draft = (self.dspark is not None and self.training and dspark_labels is not None and dspark_config is not None
                  and self.model.sp_size == 1 and input_ids is not None)
-        hidden, ctx, _ = self.model(input_ids=input_ids, position_ids=position_ids, inputs_embeds=inputs_embeds,
+        hidden, ctx, stream = self.model(input_ids=input_ids, position_ids=position_ids, inputs_embeds=inputs_embeds,
                                     cu_seq_lens_q=cu_seq_lens_q, max_length_q=max_length_q,
                                     global_position_ids=global_position_ids, return_context=True,
                                     collect_layers=self.config.dspark_target_layer_ids if draft else None)
@@ -558,14 +573,14 @@ class DeepseekV4ForCausalLMBase(nn.Module):
         if self.mtp is not None and self.training and ids is not None:
             m = self.model
             Tl = hidden.shape[1]
-            cur, outs, roll = hidden[0], [], ids
+            cur, outs, roll = stream, [], ids
             for layer in self.mtp:
                 roll = roll_left_in_sequences(roll, ctx.cu_seqlens, getattr(self.config, "pad_token_id", 0) or 0)
                 emb = m.embed_tokens(roll).reshape(-1, cur.shape[-1])
                 if m.sp_size > 1 and emb.shape[0] != Tl:
                     emb = emb[m.sp_rank * Tl:(m.sp_rank + 1) * Tl]
-                cur = layer(emb, cur, ctx, m.expand)
-                outs.append(cur.unsqueeze(0))
+                cur, head_in = layer(emb, cur, ctx)
+                outs.append(head_in.unsqueeze(0))
             out["mtp_hidden_states"] = outs
         if not skip_lm_head:
             out["logits"] = self.lm_head(hidden)
