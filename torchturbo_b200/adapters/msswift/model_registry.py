@@ -49,6 +49,9 @@ def register_models_to_swift() -> list[str]:
 
         register_swift_templates()
         wrap_swift_native_templates()
+        from .mm_templates import register_swift_mm_templates
+
+        register_swift_mm_templates()
     except Exception as e:  # noqa: BLE001 - another template API: the user's --template must exist already
         logger.warning_rank0("chat templates of the engine's model families were not registered: %s", e)
     logger.info_rank0("registered %d engine model types in swift", len(done))
