@@ -777,12 +777,38 @@ class FSDP2Backend(BaseBackend):
                         st = o._init_state(p)
                         st["master"] = init
                         del p._master_init
+        self._enable_update_overlap(model, [o for o in opts if isinstance(o, FusedAdamW)])
         if self._rep_flat is not None:
             # replicated layers: gradients are averaged before the first optimizer touches them (normally already done
             # by `clip_grad_norm_`), the flat buffer is cleared after the last one has stepped
             opts[0].register_step_pre_hook(lambda *_a, **_k: self._sync_replicated_grads())
             opts[-1].register_step_post_hook(self._after_optimizer_step)
         return opts[0] if len(opts) == 1 else OptimizersContainer(opts, names)
+
+    def _enable_update_overlap(self, model: nn.Module, fused: list) -> None:
+        """Let the AdamW update of the decoder layers run on a side stream under the next forward pass: one bucket per
+        layer of every `layers` ModuleList, and a forward pre-hook per layer that waits for its own bucket only
+        (`FusedAdamW.enable_overlap`).  `TORCHTURBO_ADAMW_OVERLAP=0` keeps the whole update on the compute stream."""
+        if not fused or self.device.type != "cuda" or os.environ.get("TORCHTURBO_ADAMW_OVERLAP", "1") == "0":
+            return
+        layers = [m for name, mod in model.named_modules() if isinstance(mod, nn.ModuleList) and name.split(".")[-1] == "layers"
+                  for m in mod]
+        if not layers:
+            return
+        buckets = [[p for p in layer.parameters() if p.requires_grad and not hasattr(p, "_local_tensor")] for layer in layers]
+        for o in fused:
+            o.enable_overlap(buckets)
+
+        def make_hook(i):
+            def hook(_module, _args):
+                for o in fused:
+                    o.wait_bucket(i)
+            return hook
+
+        for i, layer in enumerate(layers):
+            layer.register_forward_pre_hook(make_hook(i))
+        logger.info_rank0("AdamW update of %d decoder layers overlaps the next forward pass (side stream, one event per layer)",
+                          len(layers))
 
     # ------------------------------------------------------------------------------------------
     # gradient clipping

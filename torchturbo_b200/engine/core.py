@@ -370,9 +370,15 @@ class TorchTurboEngine(RLMixin):
 
     def check_health(self) -> None:
         """Turn a timeout / overflow recorded by any rank's peer-memory kernels into an exception on every rank.
+        Also orders the current stream after optimizer updates still running on their side stream, so that whatever
+        follows (a checkpoint, an export) reads finished weights.
         Runs at logging and checkpoint boundaries (one small device read per workspace).  Inside a step the same
         status words poison the gradient norm on the device (`FSDP2Backend.clip_grad_norm_`), so the update of a
         failed step is skipped without a host read."""
+        if self.runtime.turbo_device.value == "cuda":
+            from .optimizers.fused_adamw import join_update_streams
+
+            join_update_streams()
         if self.backend.world_size > 1 and self.runtime.turbo_device.value == "cuda":
             from .health import check_peer_status
 

@@ -9,9 +9,18 @@ The gradient-clipping coefficient is a device scalar applied inside the update k
 "scale all gradients" pass and no host synchronisation); a non-finite norm skips the update.
 On CPU (tests, oracle) the same arithmetic runs in PyTorch.  Math follows torch's fused AdamW, which the
 reference calls on the shards (engine/backends/fsdp2/optimizers/adamw.py:226-251).
+
+Overlap with the next step (`enable_overlap`).  The update is bandwidth-bound (28 B per parameter) and the forward pass
+that follows it is tensor-core-bound, so the two share a GPU well.  Parameters handed over in buckets (one per decoder
+layer, in forward order) are updated on a side stream, bucket after bucket, each followed by an event; the forward
+pre-hook of layer i makes the compute stream wait for event i only, so layer i of the next step starts as soon as its
+own weights are new while the update of the later layers is still running.  Only parameters whose gradient is a plain
+`.grad` tensor take part (its memory is kept for the side stream with `record_stream`); `synchronize()` joins the
+streams for anything that reads the weights outside a forward pass (checkpoints, evaluation of raw tensors).
 """
 from __future__ import annotations
 
+import weakref
 from typing import Any
 
 import torch
@@ -23,6 +32,16 @@ def _local(t: torch.Tensor) -> torch.Tensor:
     return t._local_tensor if hasattr(t, "_local_tensor") else t
 
 
+_OVERLAPPING: "weakref.WeakSet[FusedAdamW]" = weakref.WeakSet()
+
+
+def join_update_streams() -> None:
+    """Order the current stream after every side-stream update in flight (call before reading weights outside a
+    forward pass: checkpoints, exports, weight statistics)."""
+    for opt in list(_OVERLAPPING):
+        opt.synchronize()
+
+
 class FusedAdamW(torch.optim.Optimizer):
     def __init__(self, params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01,
                  **_ignored: Any):
@@ -32,12 +51,17 @@ class FusedAdamW(torch.optim.Optimizer):
         # constant folded into every gradient read by `grad_sq_sum()` and by the next `step()` (then reset to 1):
         # the backend uses it for the 1/ep scaling of expert gradients instead of a pass of its own over them
         self.grad_prescale: float = 1.0
-        self._plans: dict[int, tuple[tuple, Any]] = {}
+        self._plans: dict[Any, tuple[tuple, Any]] = {}
         # the clip coefficient of the last CUDA step, copied to pinned host memory without blocking: a step the kernel
         # skipped (non-finite coefficient) is taken back out of the step counters at the start of the next `step()`
         self._clip_host: torch.Tensor | None = None
         self._clip_event = None
         self._clip_pending: list[dict] | None = None
+        # overlap of the update with the next forward pass
+        self._buckets: list[list[torch.Tensor]] = []
+        self._bucket_of: dict[int, int] = {}
+        self._bucket_events: list[Any] = []
+        self._side_stream = None
 
     # -- clipping ------------------------------------------------------------------------------------
     def set_clip_coef(self, coef: torch.Tensor | None) -> None:
@@ -56,8 +80,15 @@ class FusedAdamW(torch.optim.Optimizer):
                 st["master"] = _local(p).detach().float().clone()
         return st
 
+    def state_dict(self):
+        if self._bucket_events and torch.cuda.is_available():
+            self.synchronize()
+        return super().state_dict()
+
     def load_state_dict(self, state_dict):
         """State tensors are replaced: the cached pointer tables of the multi-tensor kernels are rebuilt."""
+        if self._bucket_events and torch.cuda.is_available():
+            self.synchronize()
         self._plans.clear()
         self._clip_pending = None
         return super().load_state_dict(state_dict)
@@ -66,6 +97,32 @@ class FusedAdamW(torch.optim.Optimizer):
         if hasattr(self, "_plans"):
             self._plans.clear()
         return super().add_param_group(param_group)
+
+    # -- overlap ---------------------------------------------------------------------------------------
+    def enable_overlap(self, buckets: list[list[torch.Tensor]]) -> None:
+        """`buckets[i]`: parameters of this optimizer that the forward pass first reads in its i-th stage (a decoder
+        layer).  They are updated on a side stream in this order; `wait_bucket(i)` orders the caller's stream after
+        bucket i.  Parameters outside every bucket are updated on the caller's stream as before."""
+        mine = {id(p) for g in self.param_groups for p in g["params"]}
+        self._buckets = [[p for p in b if id(p) in mine] for b in buckets]
+        self._bucket_of = {id(p): i for i, b in enumerate(self._buckets) for p in b}
+        self._bucket_events = [None] * len(self._buckets)
+        self._plans.clear()
+        _OVERLAPPING.add(self)
+
+    def wait_bucket(self, i: int) -> None:
+        ev = self._bucket_events[i] if i < len(self._bucket_events) else None
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+
+    def synchronize(self) -> None:
+        """Order the current stream after every update in flight on the side stream."""
+        for i in range(len(self._bucket_events)):
+            self.wait_bucket(i)
+
+    def _overlappable(self, p: torch.Tensor) -> bool:
+        return (id(p) in self._bucket_of and getattr(p, "main_grad", None) is None and p.grad is not None
+                and _local(p).is_cuda)
 
     def _settle_skipped_step(self) -> None:
         """torch's fused AdamW does not advance `step` when `found_inf` is set; the kernel here skips the same way
@@ -107,14 +164,42 @@ class FusedAdamW(torch.optim.Optimizer):
             for st in states:
                 st["step"] += 1
             step = int(states[0]["step"].item())
-            b1, b2 = group["betas"]
             lp0 = _local(ps[0])
             if lp0.is_cuda and K.available():
-                self._step_cuda(gi, group, ps, states, step, clip, prescale)
+                side = [(p, st) for p, st in zip(ps, states) if self._overlappable(p)] if self._buckets else []
+                if side:
+                    taken = {id(p) for p, _ in side}
+                    rest = [(p, st) for p, st in zip(ps, states) if id(p) not in taken]
+                    if rest:
+                        self._step_cuda(("rest", gi), group, [p for p, _ in rest], [st for _, st in rest], step, clip, prescale)
+                    self._step_side(gi, group, side, step, clip, prescale)
+                else:
+                    self._step_cuda(gi, group, ps, states, step, clip, prescale)
                 self._note_clip(clip, states)
             else:
                 self._step_torch(group, ps, states, step, clip, prescale)
         return loss
+
+    def _step_side(self, gi, group, side, step, clip, prescale) -> None:
+        """Bucket after bucket on the side stream, an event after each."""
+        if self._side_stream is None:
+            self._side_stream = torch.cuda.Stream()
+        S, main = self._side_stream, torch.cuda.current_stream()
+        S.wait_stream(main)                       # gradients and the clip coefficient are products of the caller's stream
+        by_bucket: dict[int, list] = {}
+        for p, st in side:
+            by_bucket.setdefault(self._bucket_of[id(p)], []).append((p, st))
+        if clip is not None:
+            clip.record_stream(S)
+        with torch.cuda.stream(S):
+            for b in sorted(by_bucket):
+                ps = [p for p, _ in by_bucket[b]]
+                for p in ps:
+                    _local(p.grad).record_stream(S)      # `zero_grad(set_to_none)` frees it on the caller's stream
+                self._step_cuda((gi, b), group, ps, [st for _, st in by_bucket[b]], step, clip, prescale)
+                ev = torch.cuda.Event()
+                ev.record(S)
+                self._bucket_events[b] = ev
 
     @torch.no_grad()
     def grad_sq_sum(self) -> torch.Tensor | None:
