@@ -64,7 +64,7 @@ def _worker(rank, world, init_file, err_dir, skew):
         sl = slice(rank * El, (rank + 1) * El)
         disp = P2PTokenDispatcher(cfg, dist.group.WORLD, El)
         nccl = MoEAlltoAllTokenDispatcher(cfg, dist.group.WORLD, El) if world > 1 else None
-        steps = [(300 + 57 * rank, False), (1900 - 301 * rank, True), (64 + rank, False), (1000, True)]
+        steps = [(300 + 57 * rank, False), (1900 - 230 * rank, True), (64 + rank, False), (1000, True)]
         for step, (T, with_res) in enumerate(steps):
             torch.manual_seed(100 + 10 * step + rank)
             x = (torch.randn(T, H, device="cuda") * 0.5).bfloat16()
