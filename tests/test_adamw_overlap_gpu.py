@@ -15,7 +15,7 @@ def _train(overlap: bool, steps: int = 5):
     from torchturbo_b200.engine.optimizers.fused_adamw import FusedAdamW
     from torchturbo_b200.loops import train_step
 
-    os.environ["TORCHTURBO_ADAMW_OVERLAP"] = "1" if overlap else "0"
+    os.environ["TORCHTURBO_ADAMW_OVERLAP"] = "1" if overlap else "0"       # opt-in: off by default
     eng = TorchTurboEngine(EngineConfig.from_dict({"mixed_precision": "bf16", "activation_checkpointing": {"enabled": False}}))
     mc = dict(model_type="qwen3_moe", vocab_size=4096, hidden_size=512, intermediate_size=1024, num_hidden_layers=4,
               num_attention_heads=8, num_key_value_heads=2, head_dim=128, num_experts=8, num_experts_per_tok=2,

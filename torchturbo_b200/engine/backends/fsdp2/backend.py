@@ -788,8 +788,10 @@ class FSDP2Backend(BaseBackend):
     def _enable_update_overlap(self, model: nn.Module, fused: list) -> None:
         """Let the AdamW update of the decoder layers run on a side stream under the next forward pass: one bucket per
         layer of every `layers` ModuleList, and a forward pre-hook per layer that waits for its own bucket only
-        (`FusedAdamW.enable_overlap`).  `TORCHTURBO_ADAMW_OVERLAP=0` keeps the whole update on the compute stream."""
-        if not fused or self.device.type != "cuda" or os.environ.get("TORCHTURBO_ADAMW_OVERLAP", "1") == "0":
+        (`FusedAdamW.enable_overlap`).  Off unless `TORCHTURBO_ADAMW_OVERLAP=1`: the persistent GEMMs of the forward pass
+        hold every SM's registers and shared memory, so the bandwidth-bound update only gets the gaps between kernels
+        (measured: 84.7 against 85.9 ms per step at 1 GPU, 12 layers)."""
+        if not fused or self.device.type != "cuda" or os.environ.get("TORCHTURBO_ADAMW_OVERLAP", "0") != "1":
             return
         layers = [m for name, mod in model.named_modules() if isinstance(mod, nn.ModuleList) and name.split(".")[-1] == "layers"
                   for m in mod]
