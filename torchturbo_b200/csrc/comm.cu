@@ -971,18 +971,33 @@ TTB_EXPORT int ttb_ep_ksum(const unsigned long long* peer_ptrs, long long off_re
 // reference issues per replicated parameter (engine/backends/fsdp2/backend.py:415-436 there).
 // ============================================================================================================
 namespace ttb {
+__device__ __forceinline__ void mm_ld_reduce_v4(const float* addr, float& a, float& b, float& c, float& d) {
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(a), "=f"(b), "=f"(c), "=f"(d)
+               : "l"(addr)
+               : "memory");
+}
+__device__ __forceinline__ void mm_st_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+
+// Four independent 16-byte reductions in flight per thread: one `multimem.ld_reduce` is a round trip to the switch.
 __global__ void __launch_bounds__(512) multimem_allreduce_f32_kernel(float* mc, long long first4, long long last4, float scale) {
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  for (long long i = first4 + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < last4; i += stride) {
-    float* addr = mc + 4 * i;
+  long long i = first4 + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < last4; i += 4 * stride) {
+    float v[4][4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) mm_ld_reduce_v4(mc + 4 * (i + u * stride), v[u][0], v[u][1], v[u][2], v[u][3]);
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      mm_st_v4(mc + 4 * (i + u * stride), v[u][0] * scale, v[u][1] * scale, v[u][2] * scale, v[u][3] * scale);
+  }
+  for (; i < last4; i += stride) {
     float a, b, c, d;
-    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
-                 : "=f"(a), "=f"(b), "=f"(c), "=f"(d)
-                 : "l"(addr)
-                 : "memory");
-    a *= scale; b *= scale; c *= scale; d *= scale;
-    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
-                 : "memory");
+    mm_ld_reduce_v4(mc + 4 * i, a, b, c, d);
+    mm_st_v4(mc + 4 * i, a * scale, b * scale, c * scale, d * scale);
   }
 }
 }  // namespace ttb

@@ -947,7 +947,7 @@ def ulysses_move(peer_ptrs, off_buf, off_flags, local, heads, rep, rank, world, 
     return local
 
 
-def multimem_allreduce_f32(mc_ptr: int, n: int, rank: int, world: int, scale: float = 1.0, grid: int = 128):
+def multimem_allreduce_f32(mc_ptr: int, n: int, rank: int, world: int, scale: float = 1.0, grid: int = 296):
     """In-switch all-reduce (sum, then `scale`) of `n` fp32 values at multicast address `mc_ptr`; this rank handles slice
     `rank`.  The caller synchronises the ranks before (all inputs written) and after (all slices stored)."""
     _check(lib().ttb_multimem_allreduce_f32(C.c_void_p(mc_ptr), C.c_longlong(n), C.c_int(rank), C.c_int(world), C.c_float(scale),
