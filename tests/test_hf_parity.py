@@ -212,10 +212,14 @@ def _hf_vlm(kind):
 
     text = {k: v for k, v in DENSE.items() if k not in ("rope_theta", "attention_bias", "tie_word_embeddings")}
     text["num_hidden_layers"] = 4
-    if kind == "qwen3_5":
+    if kind in ("qwen3_5", "qwen3_5_moe"):
         text.update(LINEAR, rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.5,
                                              "mrope_section": [2, 1, 1], "mrope_interleaved": True})
-        vis, cls = dict(VIS), transformers.Qwen3_5ForConditionalGeneration
+        if kind == "qwen3_5_moe":
+            text.pop("intermediate_size")
+            text.update(moe_intermediate_size=48, shared_expert_intermediate_size=48, num_experts=8, num_experts_per_tok=2)
+        vis = dict(VIS)
+        cls = transformers.Qwen3_5ForConditionalGeneration if kind == "qwen3_5" else transformers.Qwen3_5MoeForConditionalGeneration
     else:
         text.update(rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "mrope_section": [4, 2, 2],
                                      "mrope_interleaved": True})
@@ -289,7 +293,7 @@ def _w_vlm(rank, world, kind, root):
         assert got[k].shape == v.shape and torch.equal(got[k].float(), v.bfloat16().float()), k
 
 
-@pytest.mark.parametrize("kind", ["qwen3_5", "qwen3_vl"])
+@pytest.mark.parametrize("kind", ["qwen3_5", "qwen3_5_moe", "qwen3_vl"])
 def test_vision_language_logits_and_export_match_transformers(tmp_path, kind):
     run_distributed(_w_vlm, 1, kind, str(tmp_path), timeout=400)
 
