@@ -189,3 +189,79 @@ def test_deepseek_v4_prediction_depths_match_the_reference_forwarder(tmp_path):
     if _reference("deepseek_v4") is None:
         pytest.skip("reference package not installed")
     run_distributed(_w_v4_depths, 1, str(tmp_path), timeout=600)
+
+
+def _w_q35_text_depth(rank, world, root):
+    from safetensors import safe_open
+    from safetensors.torch import save_file
+
+    from torchturbo_b200.engine import EngineConfig, TorchTurboEngine
+
+    sys.path[:0] = [os.path.join(ROOT, "_ref"), os.path.join(ROOT, "shims")]
+    C = importlib.import_module("torchturbo.models.qwen3_5_moe_text.configuration_qwen3_5_moe_text")
+    M = importlib.import_module("torchturbo.models.qwen3_5_moe_text.modeling_qwen3_5_moe_text")
+    torch.manual_seed(0)
+    # full attention in every layer: the reference's gated-delta layers need a GPU (their CPU path is a Triton call)
+    cfg = C.Qwen3_5MoeTextConfig(
+        vocab_size=320, hidden_size=64, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+        rms_norm_eps=1e-5, max_position_embeddings=512, linear_conv_kernel_dim=4, linear_key_head_dim=16, linear_value_head_dim=16,
+        linear_num_key_heads=2, linear_num_value_heads=4, full_attention_interval=1, moe_intermediate_size=48,
+        shared_expert_intermediate_size=48, num_experts=8, num_experts_per_tok=2, mtp_num_hidden_layers=1, pad_token_id=0,
+        tie_word_embeddings=False)
+    cfg._attn_implementation = "eager"
+    ref = M.Qwen3_5MoeTextForCausalLM(cfg).float()
+    with torch.no_grad():
+        for p in ref.parameters():
+            if not torch.isfinite(p).all() or p.abs().max() > 1e3:
+                p.copy_(torch.randn_like(p).clamp(-1, 1) * 0.1)
+            elif p.ndim == 1:
+                p.add_(torch.randn_like(p) * 0.05)
+    T = 24
+    ids = torch.randint(1, 300, (1, T))
+    ref.train()                                      # the prediction depth runs in training mode only
+    with torch.no_grad():                            # eager attention of the reference is causal only through its mask
+        want = ref(input_ids=ids, attention_mask=torch.full((1, 1, T, T), float("-inf")).triu(1))
+    assert want.mtp_logits is not None and len(want.mtp_logits) == 1
+    src = os.path.join(root, "src")
+    os.makedirs(src)
+    sd = {k: v.detach().clone().contiguous() for k, v in ref.state_dict().items()}
+    assert "model.layers.0.mlp.experts.gate_up_proj" in sd and "mtp.fc.weight" in sd       # text-only names: no language_model level
+    save_file(sd, os.path.join(src, "model.safetensors"), metadata={"format": "pt"})
+    cd = cfg.to_dict()
+    cd.pop("torch_dtype", None)
+    cd.pop("dtype", None)
+    with open(os.path.join(src, "config.json"), "w") as f:
+        json.dump(cd, f, default=str)
+    eng = TorchTurboEngine(EngineConfig.from_dict({"mixed_precision": "fp32", "activation_checkpointing": {"enabled": False},
+                                                   "checkpoint": {"hf_export": "every"}}))
+    model = eng.build_model(src)
+    model.train()
+    cu = torch.tensor([0, T], dtype=torch.int32)
+    with torch.no_grad():
+        out = model(input_ids=ids, position_ids=torch.arange(T)[None], cu_seq_lens_q=cu, cu_seq_lens_k=cu, max_length_q=T,
+                    max_length_k=T)
+    assert (out["logits"].float().reshape(1, T, -1) - want.logits.float()).abs().max().item() < 1e-4
+    err = (out["mtp_logits"][0].float().reshape(1, T, -1) - want.mtp_logits[0].float()).abs().max().item()
+    assert err < 1e-4, f"prediction depth differs from the reference by {err}"
+    ckpt = os.path.join(root, "checkpoint-1")
+    eng.save_model(model, ckpt, final=True)
+    names = set()
+    hf_dir = os.path.join(ckpt, "huggingface")
+    for fn in sorted(os.listdir(hf_dir)):
+        if fn.endswith(".safetensors"):
+            with safe_open(os.path.join(hf_dir, fn), "pt") as sf:
+                names |= set(sf.keys())
+    assert names == set(sd), sorted(names ^ set(sd))[:8]
+
+
+def test_qwen3_5_moe_text_prediction_depth_and_text_only_names_match_the_reference_class(tmp_path):
+    if _reference("deepseek_v4") is None:
+        pytest.skip("reference package not installed")
+    try:
+        sys.path[:0] = [os.path.join(ROOT, "_ref"), os.path.join(ROOT, "shims")]
+        importlib.import_module("torchturbo.models.qwen3_5_moe_text.modeling_qwen3_5_moe_text")
+    except Exception:  # noqa: BLE001 - written for another transformers release
+        pytest.skip("the reference's qwen3_5_moe_text does not import with this transformers release")
+    finally:
+        del sys.path[:2]
+    run_distributed(_w_q35_text_depth, 1, str(tmp_path), timeout=600)
