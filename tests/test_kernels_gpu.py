@@ -359,6 +359,36 @@ def test_attention_fwd(K, causal):
 
 
 @pytest.mark.parametrize("causal", [True, False])
+def test_attention_fwd_rescales_in_place_when_a_later_block_raises_the_maximum(K, causal):
+    """Keys whose logits grow by far more than 2^8 from one 128-row block to the next (the accumulator in tensor memory is
+    rescaled in place) and keys that grow slowly (the running maximum is left stale); output and lse against fp32."""
+    from torchturbo_b200.ops.providers.native import attention_ref
+
+    torch.manual_seed(3)
+    T, Hq, Hk, D = 900, 4, 2, 128
+    cu = torch.tensor([0, 520, 900], dtype=torch.int32)
+    q, k, v = (torch.randn(T, Hq if i == 0 else Hk, D, device="cuda") for i in range(3))
+    ramp = torch.ones(T, device="cuda")
+    ramp[128:256] = 1.5          # a modest rise: no rescale
+    ramp[256:384] = 9.0          # far beyond the threshold
+    ramp[384:520] = 0.2
+    ramp[520 + 300:] = 7.0
+    q, k, v = q.bfloat16(), (k * ramp[:, None, None]).bfloat16(), v.bfloat16()
+    tiles = K.build_q_tiles(cu).cuda()
+    out, lse, ml = K.attn_fwd(q, k, v, tiles, scale=D ** -0.5, causal=causal, want_max_logit=True)
+    torch.cuda.synchronize()
+    assert K.attn_status() == (0, 0)
+    ref, ref_ml = attention_ref(q, k, v, cu, causal=causal, scale=D ** -0.5, want_max_logits=True)
+    _close(out, ref, atol=3e-2)
+    _close(ml, ref_ml, rtol=1e-2, atol=1e-2)
+    for a, b, hq in ((0, 520, 1), (520, 900, 2)):
+        sc = (q[a:b, hq].float() @ k[a:b, hq // 2].float().t()) * D ** -0.5
+        if causal:
+            sc = sc.masked_fill(~torch.ones(b - a, b - a, dtype=torch.bool, device="cuda").tril(), float("-inf"))
+        _close(lse[hq, a:b], torch.logsumexp(sc, -1), rtol=1e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("causal", [True, False])
 def test_attention_bwd(K, causal):
     from torchturbo_b200.ops.providers.native import attention_ref
 

@@ -36,4 +36,22 @@ def bench_attention():
             row["flash_attn2_error"] = str(e)[:80]
         rows.append(row)
         print(json.dumps(row), flush=True)
+        # backward: the whole call (row dot products, the tcgen05 kernel, fp32 -> bf16 casts of dQ / dK / dV)
+        out, lse, _ = K.attn_fwd(q, k, v, tiles, scale=D ** -0.5, causal=True)
+        dout = torch.randn_like(out)
+        kv_tiles = K.build_kv_tiles(cu).cuda()
+        tb, _ = time_fn(lambda: K.attn_bwd(dout, q, k, v, out, lse, kv_tiles, scale=D ** -0.5, causal=True))
+        rowb = dict(op="attn_bwd_causal", T=T, Hq=Hq, Hk=Hk, docs=docs, ms=tb, tflops=2.5 * fl / tb / 1e9,
+                    frac_of_peak=2.5 * fl / tb / 1e9 / pk["tflops"], peak_src=pk["src"])
+        try:
+            from flash_attn import flash_attn_varlen_func
+
+            qg, kg, vg = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
+            o2 = flash_attn_varlen_func(qg, kg, vg, cud, cud, mx, mx, causal=True)
+            t3, _ = time_fn(lambda: torch.autograd.grad(o2, (qg, kg, vg), dout, retain_graph=True))
+            rowb["flash_attn2_ms"] = t3
+        except Exception as e:  # noqa: BLE001
+            rowb["flash_attn2_error"] = str(e)[:80]
+        rows.append(rowb)
+        print(json.dumps(rowb), flush=True)
     return rows

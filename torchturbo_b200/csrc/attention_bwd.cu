@@ -11,10 +11,13 @@
 //     dV  += P^T  dO_i           [kv, d]     (K-major  x MN-major)
 //     dK  += dS^T Q_i            [kv, d]     (K-major  x MN-major)
 //     dQ^T = K_j^T dS^T          [d, q]      (MN-major x MN-major)  -> fp32 atomic add into dQ
-// Warp roles: 0 TMA producer, 1 MMA issuer, 2-5 softmax/dS, 6-9 dQ read-out.  P^T / dS^T (shared memory) and dQ^T
-// (TMEM) are double-buffered: the softmax warps of query tile i+1 run while the tensor cores still consume the
-// P^T / dS^T of tile i, and the dQ read-out of tile i overlaps the dQ^T MMAs of tile i+1.  Waits are bounded; on
-// timeout the roles drain to the final barrier, TMEM is freed and the status word records where the wait gave up.
+// Warp roles: 0 TMA producer, 1 MMA issuer, 2-9 softmax/dS, 10-13 dQ read-out.  The softmax of a tile is the longest
+// dependent chain of an iteration (TMEM read, 64 exponentials per kv row, two bf16 tiles to shared memory), so two
+// warpgroups share it: warps 2-5 take query columns 0-31 of every kv row, warps 6-9 columns 32-63 (a warp may read
+// the TMEM lanes 32 (warp % 4) .. +31 at any column).  P^T / dS^T (shared memory) and dQ^T (TMEM) are double-buffered:
+// the softmax warps of query tile i+1 run while the tensor cores still consume the P^T / dS^T of tile i, and the dQ
+// read-out of tile i overlaps the dQ^T MMAs of tile i+1.  Waits are bounded; on timeout the roles drain to the final
+// barrier, TMEM is freed and the status word records where the wait gave up.
 //
 // Replaces flash-attn 2's backward used through the reference attention interface
 // (models/modules/attention/interface.py:114-158).
@@ -61,6 +64,19 @@ __device__ __forceinline__ float bw_exp2(float x) {
   return y;
 }
 
+// Warp-collective: 32 consecutive fp32 columns of two accumulators, both loads in flight before the one wait.
+__device__ __forceinline__ void tmem_ld32x2(uint32_t ta, uint32_t tb, float (&a)[32], float (&b)[32]) {
+  uint32_t va[32], vb[32];
+  tmem_ld_32x32b_x32(ta, va);
+  tmem_ld_32x32b_x32(tb, vb);
+  tmem_ld_wait();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    a[i] = __uint_as_float(va[i]);
+    b[i] = __uint_as_float(vb[i]);
+  }
+}
+
 // Warp-collective: 64 consecutive fp32 columns of this thread's TMEM lane.
 __device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&out)[64]) {
 #pragma unroll
@@ -73,7 +89,7 @@ __device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&out)[64]) {
   }
 }
 
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(448, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                 const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                 const AttnBwdParams p) {
@@ -91,6 +107,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* dq_empty = bars + 13;   // [2]
   uint64_t* acc_full = bars + 15;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile int* s_dead = reinterpret_cast<volatile int*>(bars + 17);   // a softmax warp's wait gave up
   float* s_lse = reinterpret_cast<float*>(smem + BwdSmem::LSE);
   float* s_delta = reinterpret_cast<float*>(smem + BwdSmem::DELTA);
 
@@ -109,12 +126,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
-    mbar_init(st_full, 1); mbar_init(st_empty, 4);
+    mbar_init(st_full, 1); mbar_init(st_empty, 8);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&pds_full[i], 4); mbar_init(&pds_empty[i], 1);
+      mbar_init(&pds_full[i], 8); mbar_init(&pds_empty[i], 1);
       mbar_init(&dq_full[i], 1); mbar_init(&dq_empty[i], 4);
     }
     mbar_init(acc_full, 1);
+    *s_dead = 0;
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -225,84 +243,103 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       if (ok) umma_commit(acc_full);
     }
-  } else if (warp < 6) {
-    // ---------------------------------------------------------------- softmax / dS (thread = kv row)
+  } else if (warp < 10) {
+    // ---------------------------------------------------------------- softmax / dS (thread = kv row, 32 query columns)
     const int lg = warp & 3;
+    const int half = (warp - 2) >> 2;          // 0: query columns 0-31, 1: columns 32-63
     const int row = lg * 32 + lane;
     const int kv = kv0 + row;
     const bool kv_ok = kv < de;
     const float c = p.scale * 1.4426950408889634f;
-    const int tid = threadIdx.x - 64;  // 0..127 inside this group
+    const int tid = threadIdx.x - 64;  // 0..255 inside the two groups
     bool ok = true;
-    // lse / delta of the 64 query rows of an iteration are staged one iteration ahead (double-buffered)
-    auto stage = [&](int it) {
+    // lse / delta of the 64 query rows of an iteration are staged one iteration ahead (double-buffered); the global
+    // load is issued at the top of the iteration before and stored at its end
+    auto fetch = [&](int it) -> float {
       const int q0s = it_q0(it);
       if (tid < 64) {
         const int q = q0s + tid;
-        s_lse[(it & 1) * 64 + tid] = (q < de) ? p.lse[static_cast<long long>(hq) * p.T + q] * 1.4426950408889634f : INFINITY;
-      } else {
-        const int q = q0s + tid - 64;
-        s_delta[(it & 1) * 64 + tid - 64] = (q < de) ? p.delta[static_cast<long long>(hq) * p.T + q] : 0.f;
+        return (q < de) ? p.lse[static_cast<long long>(hq) * p.T + q] * 1.4426950408889634f : INFINITY;
       }
+      if (tid < 128) {
+        const int q = q0s + tid - 64;
+        return (q < de) ? p.delta[static_cast<long long>(hq) * p.T + q] : 0.f;
+      }
+      return 0.f;
     };
-    if (n_it > 0) stage(0);
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    for (int it = 0; it < n_it && ok; ++it) {
+    auto put = [&](int it, float v) {
+      if (tid < 64) s_lse[(it & 1) * 64 + tid] = v;
+      else if (tid < 128) s_delta[(it & 1) * 64 + tid - 64] = v;
+    };
+    if (n_it > 0) put(0, fetch(0));
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    // one iteration; false when a wait gave up (the caller still joins the group barrier, so no warp is left in it)
+    auto body = [&](int it) -> bool {
       const int q0 = it_q0(it);
-      if (!mbar_wait(st_full, it & 1, KID_ATTN_BWD, 7)) { ok = false; break; }
+      const float staged = (it + 1 < n_it) ? fetch(it + 1) : 0.f;
+      if (!mbar_wait(st_full, it & 1, KID_ATTN_BWD, 7)) return false;
       tc_fence_after();
-      float s[64], dp[64];
-      const uint32_t lane_off = static_cast<uint32_t>(lg * 32) << 16;
-      tmem_ld64(tm_ST + lane_off, s);
-      tmem_ld64(tm_DPT + lane_off, dp);
+      float s[32], dp[32];
+      const uint32_t lane_off = (static_cast<uint32_t>(lg * 32) << 16) + half * 32;
+      tmem_ld32x2(tm_ST + lane_off, tm_DPT + lane_off, s, dp);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(st_empty);
-      const float* lse = s_lse + (it & 1) * 64;
-      const float* dl = s_delta + (it & 1) * 64;
-      const bool need_mask = (q0 + BW_Q > de) || (kv0 + BW_KV > de) || (p.causal && kv0 + BW_KV - 1 > q0);
+      const float* lse = s_lse + (it & 1) * 64 + half * 32;
+      const float* dl = s_delta + (it & 1) * 64 + half * 32;
+      const int qh = q0 + half * 32;
+      const bool need_mask = (q0 + BW_Q > de) || (kv0 + BW_KV > de) || (p.causal && kv0 + BW_KV - 1 > qh);
       // the tile that used this P^T / dS^T buffer two iterations ago must have been consumed (a fresh barrier passes)
-      if (!mbar_wait(&pds_empty[it & 1], ((it >> 1) & 1) ^ 1, KID_ATTN_BWD, 8)) { ok = false; break; }
+      if (!mbar_wait(&pds_empty[it & 1], ((it >> 1) & 1) ^ 1, KID_ATTN_BWD, 8)) return false;
       uint8_t* sPT = smem + BwdSmem::PT + (it & 1) * 16384;
       uint8_t* sDST = smem + BwdSmem::DST + (it & 1) * 16384;
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
+      for (int ch = 0; ch < 4; ++ch) {
         uint32_t wp[4], wd[4];
+        const float4 l0 = *reinterpret_cast<const float4*>(lse + ch * 8), l1 = *reinterpret_cast<const float4*>(lse + ch * 8 + 4);
+        const float4 d0 = *reinterpret_cast<const float4*>(dl + ch * 8), d1 = *reinterpret_cast<const float4*>(dl + ch * 8 + 4);
+        const float lv[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+        const float dlv[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
 #pragma unroll
         for (int qq = 0; qq < 4; ++qq) {
           float pv[2], dv[2];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int col = ch * 8 + qq * 2 + e;
-            float pr = bw_exp2(s[col] * c - lse[col]);
+            float pr = bw_exp2(fmaf(s[col], c, -lv[qq * 2 + e]));
             if (need_mask) {
-              const int q = q0 + col;
+              const int q = qh + col;
               const bool vis = kv_ok && q < de && (!p.causal || kv <= q);
               pr = vis ? pr : 0.f;
             }
             pv[e] = pr;
-            dv[e] = pr * (dp[col] - dl[col]) * p.scale;
+            dv[e] = pr * (dp[col] - dlv[qq * 2 + e]) * p.scale;
           }
           wp[qq] = pack_bf16(pv[0], pv[1]);
           wd[qq] = pack_bf16(dv[0], dv[1]);
         }
-        const int off = row * 128 + ((ch ^ (row & 7)) * 16);
+        const int off = row * 128 + (((half * 4 + ch) ^ (row & 7)) * 16);
         *reinterpret_cast<uint4*>(sPT + off) = make_uint4(wp[0], wp[1], wp[2], wp[3]);
         *reinterpret_cast<uint4*>(sDST + off) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
       }
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&pds_full[it & 1]);
-      if (it + 1 < n_it) stage(it + 1);
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (it + 1 < n_it) put(it + 1, staged);
+      return true;
+    };
+    for (int it = 0; it < n_it; ++it) {
+      if (!body(it)) { *s_dead = 1; ok = false; }
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (*s_dead) { ok = false; break; }
     }
     // ---- epilogue: dK / dV of this tile
     if (ok && n_it > 0) ok = mbar_wait(acc_full, 0, KID_ATTN_BWD, 9);
     if (ok) {
       tc_fence_after();
       const uint32_t lane_off = static_cast<uint32_t>(lg * 32) << 16;
-#pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
+      {
+        const int which = half;                  // columns 0-31 group: dV, the other group: dK
         const long long off = (static_cast<long long>(kv) * p.Hk + hk) * BW_D;
         __nv_bfloat16* dst = (which == 0 ? p.dv : p.dk) + off;
         float* acc = (which == 0 ? p.dv_acc : p.dk_acc) + off;
@@ -342,7 +379,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else {
     // ---------------------------------------------------------------- dQ read-out (thread = head-dim index d)
-    const int lg = warp & 3;
+    const int lg = warp & 3;                    // warps 10-13: TMEM lane groups 2, 3, 0, 1
     const int d = lg * 32 + lane;
     bool ok = true;
     for (int it = 0; it < n_it && ok; ++it) {
@@ -434,7 +471,7 @@ TTB_EXPORT int ttb_attn_bwd(const void* q, const void* k, long long ldk, const v
   if (Hq != Hk && (dk_acc == nullptr || dv_acc == nullptr)) return 903;
   AttnBwdParams p{kv_tiles, lse, delta, dq_acc, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, dk_acc, dv_acc, Hq, Hk, T, scale, causal};
   dim3 grid(n_tiles, Hq);
-  attn_bwd_kernel<<<grid, 320, BwdSmem::TOTAL, stream>>>(tq, tdo, tk, tv, p);
+  attn_bwd_kernel<<<grid, 448, BwdSmem::TOTAL, stream>>>(tq, tdo, tk, tv, p);
   const long long n = T * Hq * D;
   attn_bwd_cast_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, stream>>>(dq_acc, (__nv_bfloat16*)dq, n);
   if (Hq != Hk) {

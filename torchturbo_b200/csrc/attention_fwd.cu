@@ -3,11 +3,17 @@
 // One CTA handles one 128-row query tile of one document for one query head.  Warp roles:
 //   warp 0      TMA producer   : Q once, then K_j / V_j tiles (2 stages each)
 //   warp 1      MMA issuer     : S_j = Q K_j^T  (tcgen05, fp32 in TMEM, 2 buffers)
-//                                O_j = P_j V_j  (V consumed MN-major straight from its [kv, d] tile, 2 buffers)
-//   warps 2-5   softmax        : one thread per query row: mask, running max, exp2, row sum,
-//                                P_j -> shared memory (bf16, 128B-swizzled K-major A operand)
-//   warps 6-9   accumulate     : one thread per query row keeps the 128 output values in registers,
-//                                O = O * alpha_j + O_j (O_j read from TMEM), final 1/l scaling and store
+//                                O  += P_j V_j  (V consumed MN-major straight from its [kv, d] tile; O stays in TMEM)
+//   warps 2-9   softmax        : thread = query row; warps 2-5 take kv columns 0-63 of the block, warps 6-9 columns
+//                                64-127 (a warp may read the TMEM lanes 32 (warp % 4) .. +31 at any column), so the
+//                                dependent chain per block is half as long.  The halves exchange their row maxima
+//                                through shared memory, write P_j (bf16, 128B-swizzled K-major A operand) and keep
+//                                partial row sums.
+// The output accumulator is never copied out between blocks.  The running maximum of a row is raised only when the
+// new block exceeds it by more than 2^8 in the exponent (probabilities then stay below 256, exact in fp32 sums and
+// harmless in bf16); only then the row's accumulator is rescaled in place (tcgen05.ld / multiply / tcgen05.st by the
+// softmax warps, each half its 64 output columns) before the block's P.V is issued.  The normalisation by the row
+// sum at the end uses the same maximum, so the result does not depend on when the maximum was raised.
 // Every wait is bounded (mbar_wait): on timeout the role stops, all roles meet at the final barrier,
 // TMEM is released and the status word records kernel/site.
 //
@@ -23,6 +29,7 @@ constexpr int AT_BM = 128;   // query rows per CTA
 constexpr int AT_BN = 128;   // kv rows per block
 constexpr int AT_D = 128;    // head dim
 constexpr int TILE_BYTES = 128 * 128 * 2;  // one [128 x 128] bf16 tile = two 16 KB swizzle panels
+constexpr float AT_LAZY = 8.f;             // raise the running maximum only beyond this many powers of two
 
 struct AttnFwdParams {
   const int* q_tiles;   // [n_tiles, 3]: first query row, document start, document end (token indices)
@@ -41,9 +48,9 @@ struct AttnSmem {
   static constexpr int K0 = Q + TILE_BYTES;
   static constexpr int V0 = K0 + 2 * TILE_BYTES;
   static constexpr int P = V0 + 2 * TILE_BYTES;
-  static constexpr int ALPHA = P + TILE_BYTES;            // float [4][128]
-  static constexpr int ROWSUM = ALPHA + 4 * 128 * 4;      // float [128]
-  static constexpr int BARS = ROWSUM + 128 * 4;
+  static constexpr int ROWMAX = P + TILE_BYTES;           // float [2 parities][2 halves][128]
+  static constexpr int ROWSUM = ROWMAX + 4 * 128 * 4;     // float [2 halves][128]
+  static constexpr int BARS = ROWSUM + 2 * 128 * 4;
   static constexpr int TOTAL = BARS + 256 + 1024;
 };
 
@@ -73,11 +80,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* s_full = bars + 9;    // [2]
   uint64_t* s_empty = bars + 11;  // [2]
   uint64_t* p_full = bars + 13;
-  uint64_t* p_empty = bars + 14;
-  uint64_t* o_full = bars + 15;   // [2]
-  uint64_t* o_empty = bars + 17;  // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
-  float* s_alpha = reinterpret_cast<float*>(smem + AttnSmem::ALPHA);
+  uint64_t* p_empty = bars + 14;  // P_j V_j retired: P may be rewritten, O holds blocks 0..j
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  volatile int* s_dead = reinterpret_cast<volatile int*>(bars + 16);   // a softmax warp's wait gave up
+  float* s_rowmax = reinterpret_cast<float*>(smem + AttnSmem::ROWMAX);
   float* s_rowsum = reinterpret_cast<float*>(smem + AttnSmem::ROWSUM);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -94,11 +100,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
-      mbar_init(&o_full[i], 1); mbar_init(&o_empty[i], 4);
+      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 8);
     }
-    mbar_init(p_full, 4);
+    mbar_init(p_full, 8);
     mbar_init(p_empty, 1);
+    *s_dead = 0;
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -110,7 +116,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tm_S = tmem_base;        // 2 x 128 columns
-  const uint32_t tm_O = tmem_base + 256;  // 2 x 128 columns
+  const uint32_t tm_O = tmem_base + 256;  // 128 columns
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -167,8 +173,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         if (!mbar_wait(&v_full[st], ph, KID_ATTN_FWD, 6)) { ok = false; break; }
+        // P_j written and, where a row maximum was raised, O rescaled in place
         if (!mbar_wait(p_full, j & 1, KID_ATTN_FWD, 7)) { ok = false; break; }
-        if (!mbar_wait(&o_empty[st], ph ^ 1, KID_ATTN_FWD, 8)) { ok = false; break; }
         tc_fence_after();
         const uint32_t sV = smem_u32(smem + AttnSmem::V0 + st * TILE_BYTES);
 #pragma unroll
@@ -176,139 +182,160 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           // A = P: K-major, k-step of 16 kv columns = 32 bytes inside a panel, second panel after 64 columns
           const uint32_t offp = (kk >> 2) * 16384 + (kk & 3) * 32;
           // B = V: MN-major [kv rows][d], k-step of 16 kv rows = 2048 bytes, d panels 16 KB apart
-          umma_ss(tm_O + st * 128, make_smem_desc(sP + offp, 16, 1024), make_smem_desc(sV + kk * 2048, 16384, 1024),
-                  idesc_o, kk != 0);
+          umma_ss(tm_O, make_smem_desc(sP + offp, 16, 1024), make_smem_desc(sV + kk * 2048, 16384, 1024), idesc_o,
+                  (j | kk) != 0);
         }
-        umma_commit(&o_full[st]);
         umma_commit(&v_empty[st]);
         umma_commit(p_empty);
       }
     }
-  } else if (warp < 6) {
-    // ---------------------------------------------------------------- softmax (thread = query row)
+  } else {
+    // ---------------------------------------------------------------- softmax (thread = query row, 64 kv columns)
     const int lg = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int row = lg * 32 + lane;
     const int qrow = q0 + row;
     const bool row_ok = qrow < de;
     const float c = p.scale * 1.4426950408889634f;
+    const uint32_t lane_off = static_cast<uint32_t>(lg * 32) << 16;
     float m_run = -INFINITY, l_run = 0.f, mx_logit = -INFINITY;
-    uint8_t* sP = smem + AttnSmem::P;
+    uint8_t* sP = smem + AttnSmem::P + half * 16384;    // this half's 64 columns are one swizzle panel
     bool ok = true;
-    for (int j = 0; j < nblk && ok; ++j) {
+    // one kv block; false when a wait gave up
+    auto block = [&](int j, float (&s)[64], float& m_half) -> bool {
       const int st = j & 1;
       const uint32_t ph = (j >> 1) & 1;
-      if (!mbar_wait(&s_full[st], ph, KID_ATTN_FWD, 9)) { ok = false; break; }
+      if (!mbar_wait(&s_full[st], ph, KID_ATTN_FWD, 9)) return false;
       tc_fence_after();
-      const int kv0 = ds + j * AT_BN;
-      const bool need_mask = (kv0 + AT_BN > de) || (p.causal && kv0 + AT_BN - 1 > q0);
-      float s[128];
-      const uint32_t t_row = tm_S + st * 128 + (static_cast<uint32_t>(lg * 32) << 16);
-#pragma unroll
-      for (int cb = 0; cb < 4; ++cb) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(t_row + cb * 32, v);
+      const int kv0 = ds + j * AT_BN + half * 64;
+      const uint32_t t_row = tm_S + st * 128 + half * 64 + lane_off;
+      {
+        uint32_t va[32], vb[32];
+        tmem_ld_32x32b_x32(t_row, va);
+        tmem_ld_32x32b_x32(t_row + 32, vb);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) s[cb * 32 + i] = __uint_as_float(v[i]);
+        for (int i = 0; i < 32; ++i) {
+          s[i] = __uint_as_float(va[i]);
+          s[32 + i] = __uint_as_float(vb[i]);
+        }
       }
       // S buffer can be refilled as soon as every warp has its copy
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[st]);
-      float m_blk = -INFINITY;
+      const bool need_mask = (kv0 + 64 > de) || (p.causal && kv0 + 63 > q0);
+      m_half = -INFINITY;
       if (need_mask) {
         const int lim = p.causal ? min(de - 1, qrow) : de - 1;  // last visible kv index
 #pragma unroll
-        for (int i = 0; i < 128; ++i) {
+        for (int i = 0; i < 64; ++i) {
           const bool vis = row_ok && (kv0 + i <= lim);
           s[i] = vis ? s[i] : -INFINITY;
-          m_blk = fmaxf(m_blk, s[i]);
+          m_half = fmaxf(m_half, s[i]);
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < 128; ++i) m_blk = fmaxf(m_blk, s[i]);
+        for (int i = 0; i < 64; ++i) m_half = fmaxf(m_half, s[i]);
       }
+      s_rowmax[((j & 1) * 2 + half) * 128 + row] = m_half;
+      return true;
+    };
+    for (int j = 0; j < nblk; ++j) {
+      float s[64];
+      float m_half = -INFINITY;
+      // a wait that gave up is published before the group barrier, so that all eight warps leave the loop together
+      if (!ok || !block(j, s, m_half)) { *s_dead = 1; ok = false; }
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (*s_dead) { ok = false; break; }
+      const float m_blk = fmaxf(m_half, s_rowmax[((j & 1) * 2 + (half ^ 1)) * 128 + row]);
       mx_logit = fmaxf(mx_logit, m_blk);
-      const float m_new = fmaxf(m_run, m_blk);
-      const float alpha = (m_run == -INFINITY) ? 0.f : fast_exp2((m_run - m_new) * c);
-      const float mc = (m_new == -INFINITY) ? 0.f : m_new * c;
-      float l_blk = 0.f;
-      // P may only be overwritten once the previous P.V has retired
-      if (j > 0) {
-        if (!mbar_wait(p_empty, (j - 1) & 1, KID_ATTN_FWD, 10)) { ok = false; break; }
+      // raise the running maximum only when the block exceeds it by more than AT_LAZY powers of two
+      float alpha = 1.f;
+      if (m_blk > m_run && (m_run == -INFINITY || (m_blk - m_run) * c > AT_LAZY)) {
+        alpha = (m_run == -INFINITY) ? 0.f : fast_exp2((m_run - m_blk) * c);
+        m_run = m_blk;
       }
-      s_alpha[(j & 3) * 128 + row] = alpha;
+      const float mc = (m_run == -INFINITY) ? 0.f : m_run * c;
+      // P may only be overwritten, and O only be touched, once the previous P.V has retired
+      if (j > 0) {
+        if (!mbar_wait(p_empty, (j - 1) & 1, KID_ATTN_FWD, 10)) { ok = false; continue; }
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {
+          tc_fence_after();
 #pragma unroll
-      for (int ch = 0; ch < 16; ++ch) {  // 16 chunks of 8 columns (16 bytes of bf16)
+          for (int cb = 0; cb < 2; ++cb) {
+            uint32_t v[32];
+            const uint32_t t_o = tm_O + half * 64 + cb * 32 + lane_off;
+            tmem_ld_32x32b_x32(t_o, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tmem_st_32x32b_x32(t_o, v);
+          }
+          tmem_st_wait();
+          tc_fence_before();
+        }
+      }
+      float l_blk = 0.f;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {  // 8 chunks of 8 columns (16 bytes of bf16)
         uint32_t w[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          const float e0 = fast_exp2(s[ch * 8 + 2 * q] * c - mc);
-          const float e1 = fast_exp2(s[ch * 8 + 2 * q + 1] * c - mc);
+          const float e0 = fast_exp2(fmaf(s[ch * 8 + 2 * q], c, -mc));
+          const float e1 = fast_exp2(fmaf(s[ch * 8 + 2 * q + 1], c, -mc));
           w[q] = pack_bf16(e0, e1);
           // accumulate what the tensor core will actually see (bf16-rounded probabilities)
           float2 r = unpack_bf16(w[q]);
           l_blk += r.x + r.y;
         }
-        const int panel = ch >> 3, cc = ch & 7;
-        uint8_t* dst = sP + panel * 16384 + row * 128 + ((cc ^ (row & 7)) * 16);
+        uint8_t* dst = sP + row * 128 + ((ch ^ (row & 7)) * 16);
         *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
       }
       l_run = l_run * alpha + l_blk;
-      m_run = m_new;
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
     }
-    s_rowsum[row] = l_run;
-    if (ok && row_ok) {
-      if (p.lse) p.lse[static_cast<long long>(h) * p.T + qrow] = (l_run > 0.f) ? m_run * p.scale + logf(l_run) : -INFINITY;
+    // ---- epilogue: both halves' row sums, then each half normalises and stores its 64 output columns
+    s_rowsum[half * 128 + row] = l_run;
+    if (ok && nblk > 0) ok = mbar_wait(p_empty, (nblk - 1) & 1, KID_ATTN_FWD, 11);
+    if (!ok) *s_dead = 1;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (*s_dead) ok = false;
+    const float l = s_rowsum[row] + s_rowsum[128 + row];
+    if (ok && row_ok && half == 0) {
+      if (p.lse) p.lse[static_cast<long long>(h) * p.T + qrow] = (l > 0.f) ? m_run * p.scale + logf(l) : -INFINITY;
     }
-    if (p.max_logit) {
+    if (p.max_logit && half == 0) {
       float wm = warp_max(row_ok ? mx_logit * p.scale : -INFINITY);
       if (lane == 0 && wm > -INFINITY) atomic_max_float(&p.max_logit[h], wm);
     }
-    // hand the row sums to the accumulate warps: named barrier over the 256 threads of warps 2..9
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-  } else {
-    // ---------------------------------------------------------------- accumulate (thread = query row)
-    const int lg = warp & 3;
-    const int row = lg * 32 + lane;
-    const int qrow = q0 + row;
-    float o[128];
-#pragma unroll
-    for (int i = 0; i < 128; ++i) o[i] = 0.f;
-    bool ok = true;
-    for (int j = 0; j < nblk && ok; ++j) {
-      const int st = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      if (!mbar_wait(&o_full[st], ph, KID_ATTN_FWD, 11)) { ok = false; break; }
+    if (ok) {
       tc_fence_after();
-      const float alpha = s_alpha[(j & 3) * 128 + row];
-      const uint32_t t_row = tm_O + st * 128 + (static_cast<uint32_t>(lg * 32) << 16);
-#pragma unroll
-      for (int cb = 0; cb < 4; ++cb) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(t_row + cb * 32, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[cb * 32 + i] = o[cb * 32 + i] * alpha + __uint_as_float(v[i]);
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&o_empty[st]);
-    }
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    if (ok && qrow < de) {
-      const float l = s_rowsum[row];
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* dst = p.out + (static_cast<long long>(qrow) * p.Hq + h) * AT_D;
+      __nv_bfloat16* dst = p.out + (static_cast<long long>(qrow) * p.Hq + h) * AT_D + half * 64;
 #pragma unroll
-      for (int i = 0; i < 128; i += 8) {
-        uint4 w;
-        w.x = pack_bf16(o[i] * inv, o[i + 1] * inv); w.y = pack_bf16(o[i + 2] * inv, o[i + 3] * inv);
-        w.z = pack_bf16(o[i + 4] * inv, o[i + 5] * inv); w.w = pack_bf16(o[i + 6] * inv, o[i + 7] * inv);
-        *reinterpret_cast<uint4*>(dst + i) = w;
+      for (int cb = 0; cb < 2; ++cb) {
+        uint32_t v[32];
+        if (nblk > 0) {
+          tmem_ld_32x32b_x32(tm_O + half * 64 + cb * 32 + lane_off, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0u;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 w;
+            w.x = pack_bf16(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
+            w.y = pack_bf16(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
+            w.z = pack_bf16(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
+            w.w = pack_bf16(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + cb * 32 + i) = w;
+          }
+        }
       }
     }
   }

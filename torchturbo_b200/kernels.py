@@ -642,6 +642,7 @@ def build_q_tiles(cu_seqlens, block: int = 128) -> torch.Tensor:
         # emit them first to shorten the tail of the launch
         for q0 in range(a + ((b - a - 1) // block) * block, a - 1, -block) if b > a else ():
             rows.append((q0, a, b))
+    rows.sort(key=lambda r: -(r[0] - r[1]))          # across documents too: the tiles with the most KV blocks first
     return torch.tensor(rows, dtype=torch.int32).reshape(-1, 3)
 
 
