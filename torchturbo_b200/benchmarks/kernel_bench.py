@@ -1,6 +1,6 @@
 """Device-timed microbenchmarks of the sm_100a kernels with roofline fractions.
 
-    python -m torchturbo_b200.benchmarks.kernel_bench [gemm] [grouped] [elementwise] [attention]
+    python -m torchturbo_b200.benchmarks.kernel_bench [gemm] [grouped] [elementwise] [attention] [delta]
 
 Timing rules: 3+ warm-up launches, CUDA events on the launching stream, an L2 flush (write of a
 256 MiB buffer) between timed launches, best and median of the timed launches reported.  The
@@ -239,6 +239,41 @@ def profile_case(name: str) -> None:
     print(json.dumps({"profile_case": name, "launches": 3}))
 
 
+def bench_delta_rule():
+    """Gated delta rule, forward + backward of one layer: the chunk-parallel formulation with the `delta_state` kernel
+    against the torch loop over chunks; the kernel alone for the recurrence time."""
+    from ..ops.providers.b200_linear_attention import chunk_delta_rule_batched
+    from ..ops.providers.native_linear_attention import chunk_delta_rule
+
+    rows = []
+    for T, H, vec in [(4096, 32, False), (4096, 8, True)]:
+        D = 128
+        q, k, v = (torch.randn(1, T, H, D, device="cuda").bfloat16().requires_grad_(True) for _ in range(3))
+        g = (-torch.rand(1, T, H, *([D] if vec else []), device="cuda") * 0.3).requires_grad_(True)
+        beta = torch.rand(1, T, H, device="cuda").requires_grad_(True)
+        cu = [0, T]
+
+        def run(fn):
+            o, _ = fn(q, k, v, g, beta, cu_seqlens=cu, use_qk_l2norm=True)
+            o.float().sum().backward()
+
+        t_new, _ = time_fn(lambda: run(chunk_delta_rule_batched), iters=5, warmup=2)
+        row = dict(op="delta_rule_fwd_bwd", T=T, H=H, vector_gate=vec, ms=t_new)
+        if not vec:
+            t_old, _ = time_fn(lambda: run(lambda *a, **kw: chunk_delta_rule(*a, **kw)), iters=2, warmup=1)
+            row["torch_chunk_loop_ms"] = t_old
+        NC = T // 64
+        a = torch.randn(H, NC, 64, D, device="cuda").bfloat16() * 0.05
+        u = torch.randn(H, NC, 64, D, device="cuda")
+        dec = torch.rand(H, NC, device="cuda")
+        seq = torch.tensor([[0, NC]], dtype=torch.int32, device="cuda")
+        t_k, _ = time_fn(lambda: K.delta_state_scan(a, a, u, dec, None, None, seq, reverse=False, s1=-1.0, s2=1.0))
+        row["state_kernel_ms"] = t_k
+        rows.append(row)
+        print(json.dumps(row), flush=True)
+    return rows
+
+
 def main(argv):
     for a in argv:
         if a.startswith("profile:"):
@@ -256,6 +291,8 @@ def main(argv):
         from .attention_bench import bench_attention
 
         out["attention"] = bench_attention()
+    if "delta" in which:
+        out["delta"] = bench_delta_rule()
     return out
 
 

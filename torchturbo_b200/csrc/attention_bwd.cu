@@ -259,11 +259,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int q0s = it_q0(it);
       if (tid < 64) {
         const int q = q0s + tid;
-        return (q < de) ? p.lse[static_cast<long long>(hq) * p.T + q] * 1.4426950408889634f : INFINITY;
+        return (q < de) ? -p.lse[static_cast<long long>(hq) * p.T + q] * 1.4426950408889634f : -INFINITY;
       }
       if (tid < 128) {
         const int q = q0s + tid - 64;
-        return (q < de) ? p.delta[static_cast<long long>(hq) * p.T + q] : 0.f;
+        return (q < de) ? -p.delta[static_cast<long long>(hq) * p.T + q] * p.scale : 0.f;
       }
       return 0.f;
     };
@@ -293,30 +293,30 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (!mbar_wait(&pds_empty[it & 1], ((it >> 1) & 1) ^ 1, KID_ATTN_BWD, 8)) return false;
       uint8_t* sPT = smem + BwdSmem::PT + (it & 1) * 16384;
       uint8_t* sDST = smem + BwdSmem::DST + (it & 1) * 16384;
+      // two columns per instruction; the staged row statistics are -lse log2(e) and -Delta scale
+      const uint64_t cc = f2_pack(c, c), sc2 = f2_pack(p.scale, p.scale);
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
         uint32_t wp[4], wd[4];
-        const float4 l0 = *reinterpret_cast<const float4*>(lse + ch * 8), l1 = *reinterpret_cast<const float4*>(lse + ch * 8 + 4);
-        const float4 d0 = *reinterpret_cast<const float4*>(dl + ch * 8), d1 = *reinterpret_cast<const float4*>(dl + ch * 8 + 4);
-        const float lv[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
-        const float dlv[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+        const ulonglong2 l01 = *reinterpret_cast<const ulonglong2*>(lse + ch * 8), l23 = *reinterpret_cast<const ulonglong2*>(lse + ch * 8 + 4);
+        const ulonglong2 d01 = *reinterpret_cast<const ulonglong2*>(dl + ch * 8), d23 = *reinterpret_cast<const ulonglong2*>(dl + ch * 8 + 4);
+        const uint64_t lv[4] = {l01.x, l01.y, l23.x, l23.y};
+        const uint64_t dlv[4] = {d01.x, d01.y, d23.x, d23.y};
 #pragma unroll
         for (int qq = 0; qq < 4; ++qq) {
-          float pv[2], dv[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int col = ch * 8 + qq * 2 + e;
-            float pr = bw_exp2(fmaf(s[col], c, -lv[qq * 2 + e]));
-            if (need_mask) {
-              const int q = qh + col;
-              const bool vis = kv_ok && q < de && (!p.causal || kv <= q);
-              pr = vis ? pr : 0.f;
-            }
-            pv[e] = pr;
-            dv[e] = pr * (dp[col] - dlv[qq * 2 + e]) * p.scale;
+          const int col = ch * 8 + qq * 2;
+          float a0, a1;
+          f2_unpack(f2_fma(f2_pack(s[col], s[col + 1]), cc, lv[qq]), a0, a1);
+          float p0 = bw_exp2(a0), p1 = bw_exp2(a1);
+          if (need_mask) {
+            const int q = qh + col;
+            p0 = (kv_ok && q < de && (!p.causal || kv <= q)) ? p0 : 0.f;
+            p1 = (kv_ok && q + 1 < de && (!p.causal || kv <= q + 1)) ? p1 : 0.f;
           }
-          wp[qq] = pack_bf16(pv[0], pv[1]);
-          wd[qq] = pack_bf16(dv[0], dv[1]);
+          float d0, d1;
+          f2_unpack(f2_mul(f2_pack(p0, p1), f2_fma(f2_pack(dp[col], dp[col + 1]), sc2, dlv[qq])), d0, d1);
+          wp[qq] = pack_bf16(p0, p1);
+          wd[qq] = pack_bf16(d0, d1);
         }
         const int off = row * 128 + (((half * 4 + ch) ^ (row & 7)) * 16);
         *reinterpret_cast<uint4*>(sPT + off) = make_uint4(wp[0], wp[1], wp[2], wp[3]);

@@ -236,7 +236,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) m_half = fmaxf(m_half, s[i]);
+        for (int i = 0; i < 64; i += 2) m_half = fmax3(m_half, s[i], s[i + 1]);
       }
       s_rowmax[((j & 1) * 2 + half) * 128 + row] = m_half;
       return true;
@@ -276,22 +276,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           tc_fence_before();
         }
       }
-      float l_blk = 0.f;
+      // two columns per instruction: exponent argument, row-sum accumulation (of the unrounded probabilities)
+      const uint64_t cc = f2_pack(c, c), nmc = f2_pack(-mc, -mc);
+      uint64_t l2 = f2_pack(0.f, 0.f);
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) {  // 8 chunks of 8 columns (16 bytes of bf16)
         uint32_t w[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          const float e0 = fast_exp2(fmaf(s[ch * 8 + 2 * q], c, -mc));
-          const float e1 = fast_exp2(fmaf(s[ch * 8 + 2 * q + 1], c, -mc));
+          float a0, a1;
+          f2_unpack(f2_fma(f2_pack(s[ch * 8 + 2 * q], s[ch * 8 + 2 * q + 1]), cc, nmc), a0, a1);
+          const float e0 = fast_exp2(a0), e1 = fast_exp2(a1);
           w[q] = pack_bf16(e0, e1);
-          // accumulate what the tensor core will actually see (bf16-rounded probabilities)
-          float2 r = unpack_bf16(w[q]);
-          l_blk += r.x + r.y;
+          l2 = f2_add(l2, f2_pack(e0, e1));
         }
         uint8_t* dst = sP + row * 128 + ((ch ^ (row & 7)) * 16);
         *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
       }
+      float l_lo, l_hi;
+      f2_unpack(l2, l_lo, l_hi);
+      const float l_blk = l_lo + l_hi;
       l_run = l_run * alpha + l_blk;
       fence_proxy_async_smem();
       __syncwarp();

@@ -662,6 +662,32 @@ def attn_fwd(q, k, v, q_tiles_dev, *, scale: float, causal: bool = True, want_ls
     return out, lse, ml
 
 
+def delta_state_scan(a_tiles, b_tiles, u, decay, init, add, seq_chunks_dev, *, reverse: bool, s1: float, s2: float):
+    """Chunk-state recurrence of the delta rule (csrc/delta_state.cu).  `a_tiles`, `b_tiles`: bf16 [H, NC, 64, 128];
+    `u`: fp32 [H, NC, 64, 128]; `decay`: fp32 [H, NC] or [H, NC, 128]; `init`: fp32 [H, nseq, 128, 128] or None;
+    `add`: fp32 [H, NC + nseq, 128, 128] (required when `reverse`); `seq_chunks_dev`: int32 [nseq, 2].
+    Returns (x fp32 [H, NC, 64, 128], states fp32 [H, NC + nseq, 128, 128])."""
+    H, NC, Cc, D = u.shape
+    nseq = seq_chunks_dev.shape[0]
+    assert Cc == 64 and D == 128 and a_tiles.shape == u.shape and b_tiles.shape == u.shape
+    assert a_tiles.dtype == torch.bfloat16 and b_tiles.dtype == torch.bfloat16 and u.dtype == torch.float32
+    assert a_tiles.is_contiguous() and b_tiles.is_contiguous() and u.is_contiguous() and decay.is_contiguous()
+    assert decay.dtype == torch.float32 and decay.shape[:2] == (H, NC) and decay.dim() in (2, 3)
+    if init is not None:
+        init = init.contiguous()
+        assert init.shape == (H, nseq, 128, 128) and init.dtype == torch.float32
+    if add is not None:
+        add = add.contiguous()
+        assert add.shape == (H, NC + nseq, 128, 128) and add.dtype == torch.float32
+    x = torch.empty_like(u)
+    states = torch.empty(H, NC + nseq, 128, 128, dtype=torch.float32, device=u.device)
+    _check(lib().ttb_delta_state_scan(_p(a_tiles), _p(b_tiles), _p(u), _p(x), _p(decay), C.c_int(int(decay.dim() == 3)),
+                                      _p(init), _p(add), _p(states), _p(seq_chunks_dev), C.c_int(nseq), C.c_int(H),
+                                      C.c_int(NC), C.c_int(int(reverse)), C.c_float(s1), C.c_float(s2), _stream()),
+           "ttb_delta_state_scan")
+    return x, states
+
+
 # --------------------------------------------------------------------------------------
 # Expert-parallel exchange over peer memory (see csrc/comm.cu)
 # --------------------------------------------------------------------------------------

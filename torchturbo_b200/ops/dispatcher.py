@@ -22,7 +22,7 @@ logger = get_logger(__name__)
 
 _PROVIDER_MODULES = ("torchturbo_b200.ops.providers.native", "torchturbo_b200.ops.providers.native_linear_attention",
                      "torchturbo_b200.ops.providers.native_sparse_attention",
-                     "torchturbo_b200.ops.providers.b200")
+                     "torchturbo_b200.ops.providers.b200", "torchturbo_b200.ops.providers.b200_linear_attention")
 
 
 def load_providers() -> None:
