@@ -3,11 +3,14 @@
 // One CTA handles one 128-row query tile of one document for one query head.  Warp roles:
 //   warp 0      TMA producer   : Q once, then K_j / V_j tiles (2 stages each)
 //   warp 1      MMA issuer     : S_j = Q K_j^T  (tcgen05, fp32 in TMEM, 2 buffers)
-//                                O  += P_j V_j  (V consumed MN-major straight from its [kv, d] tile; O stays in TMEM)
+//                                O  += P_j V_j  (P read from TMEM, V MN-major straight from its [kv, d] tile; O stays
+//                                               in TMEM)
 //   warps 2-9   softmax        : thread = query row; warps 2-5 take kv columns 0-63 of the block, warps 6-9 columns
 //                                64-127 (a warp may read the TMEM lanes 32 (warp % 4) .. +31 at any column), so the
 //                                dependent chain per block is half as long.  The halves exchange their row maxima
-//                                through shared memory, write P_j (bf16, 128B-swizzled K-major A operand) and keep
+//                                through shared memory, write P_j as packed bf16 pairs into TMEM (two buffers: the
+//                                A operand of P.V comes from tensor memory, which spares the shared-memory
+//                                bandwidth that the K / V operands and the TMA writes already use up) and keep
 //                                partial row sums.
 // The output accumulator is never copied out between blocks.  The running maximum of a row is raised only when the
 // new block exceeds it by more than 2^8 in the exponent (probabilities then stay below 256, exact in fp32 sums and
@@ -47,8 +50,7 @@ struct AttnSmem {
   static constexpr int Q = 0;
   static constexpr int K0 = Q + TILE_BYTES;
   static constexpr int V0 = K0 + 2 * TILE_BYTES;
-  static constexpr int P = V0 + 2 * TILE_BYTES;
-  static constexpr int ROWMAX = P + TILE_BYTES;           // float [2 parities][2 halves][128]
+  static constexpr int ROWMAX = V0 + 2 * TILE_BYTES;      // float [2 parities][2 halves][128]
   static constexpr int ROWSUM = ROWMAX + 4 * 128 * 4;     // float [2 halves][128]
   static constexpr int BARS = ROWSUM + 2 * 128 * 4;
   static constexpr int TOTAL = BARS + 256 + 1024;
@@ -80,9 +82,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* s_full = bars + 9;    // [2]
   uint64_t* s_empty = bars + 11;  // [2]
   uint64_t* p_full = bars + 13;
-  uint64_t* p_empty = bars + 14;  // P_j V_j retired: P may be rewritten, O holds blocks 0..j
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
-  volatile int* s_dead = reinterpret_cast<volatile int*>(bars + 16);   // a softmax warp's wait gave up
+  uint64_t* p_empty = bars + 14;  // [2] P_j V_j retired: that P buffer may be rewritten, O holds blocks 0..j
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile int* s_dead = reinterpret_cast<volatile int*>(bars + 17);   // a softmax warp's wait gave up
   float* s_rowmax = reinterpret_cast<float*>(smem + AttnSmem::ROWMAX);
   float* s_rowsum = reinterpret_cast<float*>(smem + AttnSmem::ROWSUM);
 
@@ -103,7 +105,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 8);
     }
     mbar_init(p_full, 8);
-    mbar_init(p_empty, 1);
+    mbar_init(&p_empty[0], 1);
+    mbar_init(&p_empty[1], 1);
     *s_dead = 0;
     mbar_fence_init();
   }
@@ -117,6 +120,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tm_S = tmem_base;        // 2 x 128 columns
   const uint32_t tm_O = tmem_base + 256;  // 128 columns
+  const uint32_t tm_P = tmem_base + 384;  // 2 x 64 columns: bf16 pairs, column = kv index / 2
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -146,7 +150,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);  // Q (K-major) x K (K-major)
       constexpr uint32_t idesc_o = make_idesc_bf16(128, 128, false, true);   // P (K-major) x V (MN-major)
       const uint32_t sQ = smem_u32(smem + AttnSmem::Q);
-      const uint32_t sP = smem_u32(smem + AttnSmem::P);
       bool ok = mbar_wait(q_full, 0, KID_ATTN_FWD, 3);
       auto issue_s = [&](int j) -> bool {
         const int st = j & 1;
@@ -179,14 +182,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint32_t sV = smem_u32(smem + AttnSmem::V0 + st * TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          // A = P: K-major, k-step of 16 kv columns = 32 bytes inside a panel, second panel after 64 columns
-          const uint32_t offp = (kk >> 2) * 16384 + (kk & 3) * 32;
+          // A = P from TMEM: a k-step of 16 kv columns is 8 packed columns
           // B = V: MN-major [kv rows][d], k-step of 16 kv rows = 2048 bytes, d panels 16 KB apart
-          umma_ss(tm_O, make_smem_desc(sP + offp, 16, 1024), make_smem_desc(sV + kk * 2048, 16384, 1024), idesc_o,
-                  (j | kk) != 0);
+          umma_ts(tm_O, tm_P + st * 64 + kk * 8, make_smem_desc(sV + kk * 2048, 16384, 1024), idesc_o, (j | kk) != 0);
         }
         umma_commit(&v_empty[st]);
-        umma_commit(p_empty);
+        umma_commit(&p_empty[st]);
       }
     }
   } else {
@@ -199,7 +200,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const float c = p.scale * 1.4426950408889634f;
     const uint32_t lane_off = static_cast<uint32_t>(lg * 32) << 16;
     float m_run = -INFINITY, l_run = 0.f, mx_logit = -INFINITY;
-    uint8_t* sP = smem + AttnSmem::P + half * 16384;    // this half's 64 columns are one swizzle panel
     bool ok = true;
     // one kv block; false when a wait gave up
     auto block = [&](int j, float (&s)[64], float& m_half) -> bool {
@@ -257,53 +257,53 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         m_run = m_blk;
       }
       const float mc = (m_run == -INFINITY) ? 0.f : m_run * c;
-      // P may only be overwritten, and O only be touched, once the previous P.V has retired
-      if (j > 0) {
-        if (!mbar_wait(p_empty, (j - 1) & 1, KID_ATTN_FWD, 10)) { ok = false; continue; }
-        if (__any_sync(0xffffffffu, alpha != 1.f)) {
-          tc_fence_after();
+      // O may only be touched once the previous P.V has retired (rare: only when a row maximum was raised)
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        if (!mbar_wait(&p_empty[(j - 1) & 1], ((j - 1) >> 1) & 1, KID_ATTN_FWD, 10)) { ok = false; continue; }
+        tc_fence_after();
 #pragma unroll
-          for (int cb = 0; cb < 2; ++cb) {
-            uint32_t v[32];
-            const uint32_t t_o = tm_O + half * 64 + cb * 32 + lane_off;
-            tmem_ld_32x32b_x32(t_o, v);
-            tmem_ld_wait();
+        for (int cb = 0; cb < 2; ++cb) {
+          uint32_t v[32];
+          const uint32_t t_o = tm_O + half * 64 + cb * 32 + lane_off;
+          tmem_ld_32x32b_x32(t_o, v);
+          tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-            tmem_st_32x32b_x32(t_o, v);
-          }
-          tmem_st_wait();
-          tc_fence_before();
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+          tmem_st_32x32b_x32(t_o, v);
         }
+        tmem_st_wait();
+        tc_fence_before();
+      }
+      // this P buffer was read by the P.V of two blocks ago
+      if (j > 1) {
+        if (!mbar_wait(&p_empty[j & 1], ((j >> 1) & 1) ^ 1, KID_ATTN_FWD, 12)) { ok = false; continue; }
+        tc_fence_after();
       }
       // two columns per instruction: exponent argument, row-sum accumulation (of the unrounded probabilities)
       const uint64_t cc = f2_pack(c, c), nmc = f2_pack(-mc, -mc);
       uint64_t l2 = f2_pack(0.f, 0.f);
+      uint32_t w[32];
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {  // 8 chunks of 8 columns (16 bytes of bf16)
-        uint32_t w[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          float a0, a1;
-          f2_unpack(f2_fma(f2_pack(s[ch * 8 + 2 * q], s[ch * 8 + 2 * q + 1]), cc, nmc), a0, a1);
-          const float e0 = fast_exp2(a0), e1 = fast_exp2(a1);
-          w[q] = pack_bf16(e0, e1);
-          l2 = f2_add(l2, f2_pack(e0, e1));
-        }
-        uint8_t* dst = sP + row * 128 + ((ch ^ (row & 7)) * 16);
-        *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+      for (int i = 0; i < 32; ++i) {
+        float a0, a1;
+        f2_unpack(f2_fma(f2_pack(s[2 * i], s[2 * i + 1]), cc, nmc), a0, a1);
+        const float e0 = fast_exp2(a0), e1 = fast_exp2(a1);
+        w[i] = pack_bf16(e0, e1);
+        l2 = f2_add(l2, f2_pack(e0, e1));
       }
+      tmem_st_32x32b_x32(tm_P + (j & 1) * 64 + half * 32 + lane_off, w);
+      tmem_st_wait();
       float l_lo, l_hi;
       f2_unpack(l2, l_lo, l_hi);
       const float l_blk = l_lo + l_hi;
       l_run = l_run * alpha + l_blk;
-      fence_proxy_async_smem();
+      tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
     }
     // ---- epilogue: both halves' row sums, then each half normalises and stores its 64 output columns
     s_rowsum[half * 128 + row] = l_run;
-    if (ok && nblk > 0) ok = mbar_wait(p_empty, (nblk - 1) & 1, KID_ATTN_FWD, 11);
+    if (ok && nblk > 0) ok = mbar_wait(&p_empty[(nblk - 1) & 1], ((nblk - 1) >> 1) & 1, KID_ATTN_FWD, 11);
     if (!ok) *s_dead = 1;
     asm volatile("bar.sync 1, 256;" ::: "memory");
     if (*s_dead) ok = false;
