@@ -93,3 +93,47 @@ def test_delta_state_kernel_matches_the_oracle_forward_and_backward(vec):
     for name, a, b in zip(("dq", "dk", "dv", "dg", "dbeta"), leaves, ref_leaves):
         close(a.grad, b.grad, name)
     close(init.grad, init_c.grad, "dinit")
+
+
+def test_chunk_aligned_rows_take_the_view_path_and_a_padded_tail_is_one_more_sequence():
+    T, H, Kd, V = 256, 2, 16, 16
+    q, k, v, g, beta = _inputs(T, H, Kd, V, False, seed=4)
+    qn, kn = l2norm(q), l2norm(k)
+    for cu in ([0, 128, 256], [0, 100, 200]):             # whole chunks (a view) / ragged with rows behind the last boundary
+        want, _ = delta_rule_recurrent(qn, kn, v, g, beta, cu_seqlens=cu)
+        got, _ = chunk_delta_rule_batched(q, k, v, g, beta, cu_seqlens=cu, use_qk_l2norm=True)
+        assert torch.allclose(got, want, atol=2e-4, rtol=1e-3), cu
+
+
+@pytest.mark.gpu
+def test_gated_delta_net_mixer_on_cuda_runs_the_state_kernel_and_matches_the_cpu_module():
+    """The Qwen3.5 mixer through the operator dispatcher: on CUDA `ops.gated_delta_rule` resolves to the provider with
+    the `delta_state` kernel; output and parameter gradients against the same module on the CPU in fp32."""
+    from types import SimpleNamespace
+
+    from torchturbo_b200 import kernels as K
+    from torchturbo_b200.models.modules.mixers import GatedDeltaNet, MixerContext
+    from torchturbo_b200.ops import OpDispatcher, OpPolicy
+
+    assert type(OpDispatcher(OpPolicy.AUTO).resolve("gated_delta_rule")).__name__ == "B200GatedDeltaRule"
+    cfg = SimpleNamespace(hidden_size=256, linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=128,
+                          linear_value_head_dim=128, linear_conv_kernel_dim=4, rms_norm_eps=1e-6, hidden_act="silu")
+    torch.manual_seed(0)
+    ref = GatedDeltaNet(cfg, 0).float()
+    dev = GatedDeltaNet(cfg, 0).float()
+    dev.load_state_dict(ref.state_dict())
+    dev = dev.cuda()
+    T = 200
+    x = torch.randn(T, 256) * 0.5
+    cu = torch.tensor([0, 70, 200], dtype=torch.int32)
+    ctx_c = ctx_g = MixerContext(cos=None, sin=None, cu_seqlens=cu, max_seqlen=130)
+    want = ref(x, ctx_c)
+    want.square().sum().backward()
+    before = K.launch_count()
+    got = dev(x.cuda(), ctx_g)
+    got.square().sum().backward()
+    torch.cuda.synchronize()
+    assert K.launch_count() > before and K.status() == (0, 0)
+    assert (got.cpu() - want).abs().max() <= 2e-2 * max(1.0, want.abs().max())
+    for (n, a), b in zip(dev.named_parameters(), ref.parameters()):
+        assert (a.grad.cpu() - b.grad).abs().max() <= 3e-2 * max(1.0, b.grad.abs().max()), n

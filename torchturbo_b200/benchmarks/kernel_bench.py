@@ -141,7 +141,7 @@ def bench_elementwise():
 def profile_case(name: str) -> None:
     """One small, self-ending case per kernel for a profiler capture: inputs larger than L2 (126 MB) but well under
     a GB on the device, one warm-up launch and two more.  `python -m torchturbo_b200.benchmarks.kernel_bench
-    profile:<gemm|grouped|grouped_dw|attn_fwd|attn_bwd|adamw|rmsnorm>`."""
+    profile:<gemm|grouped|grouped_dw|attn_fwd|attn_bwd|delta_state|adamw|rmsnorm>`."""
     dev = "cuda"
     g = torch.Generator(device=dev).manual_seed(0)
 
@@ -177,6 +177,14 @@ def profile_case(name: str) -> None:
             o = FlashAttnFn.apply(q, k, v, cu, 5192, True, D ** -0.5, False)
             if name == "attn_bwd":
                 o.backward(do)
+    elif name == "delta_state":
+        # recurrence over 64 chunks (4096 tokens) of 32 heads: 134 MB of states written, 67 MB of U read and X written
+        H, NC = 32, 64
+        a, b = rnd(H, NC, 64, 128), rnd(H, NC, 64, 128)
+        u = torch.randn(H, NC, 64, 128, device=dev, generator=g)
+        dec = torch.rand(H, NC, device=dev, generator=g)
+        seq = torch.tensor([[0, NC]], dtype=torch.int32, device=dev)
+        fn = lambda: K.delta_state_scan(a, b, u, dec, None, None, seq, reverse=False, s1=-1.0, s2=1.0)   # noqa: E731
     elif name == "adamw":
         n = 64 << 20                                                   # 64 Mi params: 256 MB each of p32, m, v, grad
         p16 = torch.zeros(n, device=dev, dtype=torch.bfloat16)

@@ -1,7 +1,7 @@
 // Variable-length (packed) flash attention forward for sm_100a, head_dim 128, GQA, causal or full.
 //
 // One CTA handles one 128-row query tile of one document for one query head.  Warp roles:
-//   warp 0      TMA producer   : Q once, then K_j / V_j tiles (2 stages each)
+//   warp 0      TMA producer   : Q once, then K_j (3 stages) / V_j (2 stages) tiles
 //   warp 1      MMA issuer     : S_j = Q K_j^T  (tcgen05, fp32 in TMEM, 2 buffers)
 //                                O  += P_j V_j  (P read from TMEM, V MN-major straight from its [kv, d] tile; O stays
 //                                               in TMEM)
@@ -49,7 +49,7 @@ struct AttnSmem {
   // tiles (each 32 KB, 1024-byte aligned)
   static constexpr int Q = 0;
   static constexpr int K0 = Q + TILE_BYTES;
-  static constexpr int V0 = K0 + 2 * TILE_BYTES;
+  static constexpr int V0 = K0 + 3 * TILE_BYTES;           // K: three stages (a TMA round trip is longer than one block)
   static constexpr int ROWMAX = V0 + 2 * TILE_BYTES;      // float [2 parities][2 halves][128]
   static constexpr int ROWSUM = ROWMAX + 4 * 128 * 4;     // float [2 halves][128]
   static constexpr int BARS = ROWSUM + 2 * 128 * 4;
@@ -75,16 +75,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AttnSmem::BARS);
   uint64_t* q_full = bars + 0;
-  uint64_t* k_full = bars + 1;    // [2]
-  uint64_t* k_empty = bars + 3;   // [2]
-  uint64_t* v_full = bars + 5;    // [2]
-  uint64_t* v_empty = bars + 7;   // [2]
-  uint64_t* s_full = bars + 9;    // [2]
-  uint64_t* s_empty = bars + 11;  // [2]
-  uint64_t* p_full = bars + 13;
-  uint64_t* p_empty = bars + 14;  // [2] P_j V_j retired: that P buffer may be rewritten, O holds blocks 0..j
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
-  volatile int* s_dead = reinterpret_cast<volatile int*>(bars + 17);   // a softmax warp's wait gave up
+  uint64_t* k_full = bars + 1;    // [3]
+  uint64_t* k_empty = bars + 4;   // [3]
+  uint64_t* v_full = bars + 7;    // [2]
+  uint64_t* v_empty = bars + 9;   // [2]
+  uint64_t* s_full = bars + 11;   // [2]
+  uint64_t* s_empty = bars + 13;  // [2]
+  uint64_t* p_full = bars + 15;
+  uint64_t* p_empty = bars + 16;  // [2] P_j V_j retired: that P buffer may be rewritten, O holds blocks 0..j
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+  volatile int* s_dead = reinterpret_cast<volatile int*>(bars + 19);   // a softmax warp's wait gave up
   float* s_rowmax = reinterpret_cast<float*>(smem + AttnSmem::ROWMAX);
   float* s_rowsum = reinterpret_cast<float*>(smem + AttnSmem::ROWSUM);
 
@@ -99,8 +99,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
+    for (int i = 0; i < 3; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 8);
     }
@@ -130,14 +130,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tma_load_2d(smem + AttnSmem::Q, &tmQ, q_full, h * AT_D, q0);
       tma_load_2d(smem + AttnSmem::Q + 16384, &tmQ, q_full, h * AT_D + 64, q0);
       bool ok = true;
+      auto load_k = [&](int j) -> bool {
+        const int ks = j % 3;
+        if (!mbar_wait(&k_empty[ks], ((j / 3) & 1) ^ 1, KID_ATTN_FWD, 1)) return false;
+        const int kv0 = ds + j * AT_BN;
+        mbar_expect_tx(&k_full[ks], TILE_BYTES);
+        tma_load_2d(smem + AttnSmem::K0 + ks * TILE_BYTES, &tmK, &k_full[ks], hk * AT_D, kv0);
+        tma_load_2d(smem + AttnSmem::K0 + ks * TILE_BYTES + 16384, &tmK, &k_full[ks], hk * AT_D + 64, kv0);
+        return true;
+      };
+      // K runs one block ahead of V, so that a wait for a V buffer never holds back the next K request
+      if (nblk > 0) ok = load_k(0);
       for (int j = 0; j < nblk && ok; ++j) {
+        if (j + 1 < nblk && !load_k(j + 1)) { ok = false; break; }
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         const int kv0 = ds + j * AT_BN;
-        if (!mbar_wait(&k_empty[st], ph ^ 1, KID_ATTN_FWD, 1)) { ok = false; break; }
-        mbar_expect_tx(&k_full[st], TILE_BYTES);
-        tma_load_2d(smem + AttnSmem::K0 + st * TILE_BYTES, &tmK, &k_full[st], hk * AT_D, kv0);
-        tma_load_2d(smem + AttnSmem::K0 + st * TILE_BYTES + 16384, &tmK, &k_full[st], hk * AT_D + 64, kv0);
         if (!mbar_wait(&v_empty[st], ph ^ 1, KID_ATTN_FWD, 2)) { ok = false; break; }
         mbar_expect_tx(&v_full[st], TILE_BYTES);
         tma_load_2d(smem + AttnSmem::V0 + st * TILE_BYTES, &tmV, &v_full[st], hk * AT_D, kv0);
@@ -154,10 +162,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       auto issue_s = [&](int j) -> bool {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&k_full[st], ph, KID_ATTN_FWD, 4)) return false;
+        const int ks = j % 3;
+        if (!mbar_wait(&k_full[ks], (j / 3) & 1, KID_ATTN_FWD, 4)) return false;
         if (!mbar_wait(&s_empty[st], ph ^ 1, KID_ATTN_FWD, 5)) return false;
         tc_fence_after();
-        const uint32_t sK = smem_u32(smem + AttnSmem::K0 + st * TILE_BYTES);
+        const uint32_t sK = smem_u32(smem + AttnSmem::K0 + ks * TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
@@ -165,7 +174,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                   kk != 0);
         }
         umma_commit(&s_full[st]);
-        umma_commit(&k_empty[st]);
+        umma_commit(&k_empty[ks]);
         return true;
       };
       if (ok && nblk > 0) ok = issue_s(0);

@@ -172,11 +172,11 @@ delta_state_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       const float* src = p.reverse ? (p.add ? state_ptr(p.add, slot0) : nullptr)
                                    : (p.init ? p.init + ((static_cast<long long>(h) * p.nseq + seq) * DS_D) * DS_D + v : nullptr);
       float* dst = const_cast<float*>(state_ptr(p.states, slot0));
+      // all loads before the first store: the compiler may not move a load above a store that could alias it
 #pragma unroll
-      for (int k = 0; k < DS_D; ++k) {
-        S[k] = src ? src[k * DS_D] : 0.f;
-        dst[k * DS_D] = S[k];
-      }
+      for (int k = 0; k < DS_D; ++k) S[k] = src ? src[k * DS_D] : 0.f;
+#pragma unroll
+      for (int k = 0; k < DS_D; ++k) dst[k * DS_D] = S[k];
     }
     if (n > 0) publish();
     bool ok = true;
@@ -231,6 +231,11 @@ delta_state_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       float* dst = const_cast<float*>(state_ptr(p.states, slot));
 #pragma unroll
       for (int cb = 0; cb < 4; ++cb) {
+        // the 32 added values are fetched together, ahead of the stores of this block (a load may not pass a store
+        // that could alias it, and one exposed memory round trip per value would dominate the chunk)
+        float av[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) av[j] = addp ? addp[(cb * 32 + j) * DS_D] : 0.f;
         uint32_t r[32];
         tmem_ld_32x32b_x32(tm2 + cb * 32 + lane_off, r);
         tmem_ld_wait();
@@ -238,11 +243,10 @@ delta_state_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         for (int j = 0; j < 32; ++j) {
           const int k = cb * 32 + j;
           const float d = p.vec ? s_dec[k] : dsc;
-          float s = fmaf(d, S[k], __uint_as_float(r[j]));
-          if (addp) s += addp[k * DS_D];
-          S[k] = s;
-          dst[k * DS_D] = s;
+          S[k] = fmaf(d, S[k], __uint_as_float(r[j])) + av[j];
         }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) dst[(cb * 32 + j) * DS_D] = S[cb * 32 + j];
       }
       tc_fence_before();
       if (i + 1 < n) publish();

@@ -134,13 +134,22 @@ def chunk_delta_rule_batched(q, k, v, g, beta, scale=None, initial_state=None, o
         raise ValueError("packed delta rule expects a single row")
     segs = [(0, a, b) for a, b in _bounds(cu_seqlens, T)] if cu_seqlens is not None else [(r * T, 0, T) for r in range(B)]
     vec = gf.dim() == 4
-    gather, inv, seq_chunks, NC = _layout(segs, B * T, C, dev)
+    # sequences that are whole chunks and tile the rows need no gather: the chunk layout is a view of the packed rows
+    aligned = all((b - a) % C == 0 for _, a, b in segs) and sum(b - a for _, a, b in segs) == B * T
+    if aligned:
+        seq_chunks, NC = [], 0
+        for _, a, b in segs:
+            seq_chunks.append((NC, (b - a) // C))
+            NC += (b - a) // C
+        gather = inv = None
+    else:
+        gather, inv, seq_chunks, NC = _layout(segs, B * T, C, dev)
 
     def to_chunks(x):                                   # [B, T, H, ...] -> [H, NC, C, ...]
         flat = x.reshape(B * T, *x.shape[2:])
-        flat = torch.cat((flat, flat.new_zeros(1, *flat.shape[1:])), 0)
-        y = flat.index_select(0, gather).reshape(NC, C, *flat.shape[1:])
-        return y.movedim(2, 0)
+        if not aligned:
+            flat = torch.cat((flat, flat.new_zeros(1, *flat.shape[1:])), 0).index_select(0, gather)
+        return flat.reshape(NC, C, *flat.shape[1:]).movedim(2, 0)
 
     qc, kc, vc = to_chunks(qf) * scale, to_chunks(kf), to_chunks(vf)            # [H, NC, C, K|V]
     bc = to_chunks(bf.unsqueeze(-1)).squeeze(-1)                                # [H, NC, C]
@@ -184,9 +193,14 @@ def chunk_delta_rule_batched(q, k, v, g, beta, scale=None, initial_state=None, o
     start = torch.tensor([c + s for s, (c0, n) in enumerate(seq_chunks) for c in range(c0, c0 + n)], device=dev)
     S_c = states.index_select(1, start)
     o = q_in @ S_c + qk.masked_fill(~lowd, 0.0) @ v_new                          # [H, NC, C, V]
-    o = o.movedim(0, 2).reshape(NC * C, H, V).index_select(0, inv.clamp_min(0)).reshape(B, T, H, V)
-    if bool((inv < 0).any()):                                                   # rows past the last boundary
-        o = o * (inv >= 0).reshape(B, T, 1, 1)
+    o = o.movedim(0, 2).reshape(NC * C, H, V)
+    if aligned:
+        o = o.reshape(B, T, H, V)
+    else:
+        covered = sum(b - a for _, a, b in segs) == B * T
+        o = o.index_select(0, inv.clamp_min(0)).reshape(B, T, H, V)
+        if not covered:                                                         # rows past the last boundary read as zero
+            o = o * (inv >= 0).reshape(B, T, 1, 1)
     final = None
     if output_final_state:
         last = torch.tensor([c0 + n + s for s, (c0, n) in enumerate(seq_chunks)], device=dev)
