@@ -10,7 +10,8 @@
 //     P^T  = exp2(S^T c - lse_q),  dS^T = P^T (dP^T - Delta_q) scale        (one thread per kv row, bf16 -> smem)
 //     dV  += P^T  dO_i           [kv, d]     (K-major  x MN-major)
 //     dK  += dS^T Q_i            [kv, d]     (K-major  x MN-major)
-//     dQ^T = K_j^T dS^T          [d, q]      (MN-major x MN-major)  -> fp32 atomic add into dQ
+//     dQ^T = K_j^T dS^T          [d, q]      (MN-major x MN-major)  -> transposed through shared memory and added
+//                                            into the fp32 dQ buffer by one TMA reduction per tile (the L2 does the adds)
 // Warp roles: 0 TMA producer, 1 MMA issuer, 2-9 softmax/dS, 10-13 dQ read-out.  The softmax of a tile is the longest
 // dependent chain of an iteration (TMEM read, 64 exponentials per kv row, two bf16 tiles to shared memory), so two
 // warpgroups share it: warps 2-5 take query columns 0-31 of every kv row, warps 6-9 columns 32-63 (a warp may read
@@ -52,7 +53,8 @@ struct BwdSmem {
   static constexpr int DO0 = Q0 + 2 * 16384;        // 2 x 16 KB
   static constexpr int PT = DO0 + 2 * 16384;        // 2 x 16 KB  P^T  [128 kv][64 q]
   static constexpr int DST = PT + 2 * 16384;        // 2 x 16 KB  dS^T [128 kv][64 q]
-  static constexpr int LSE = DST + 2 * 16384;       // float [2][64]
+  static constexpr int DQS = DST + 2 * 16384;       // 32 KB  dQ tile [64 q][128 d] fp32, source of the TMA reduction
+  static constexpr int LSE = DQS + 32768;           // float [2][64]
   static constexpr int DELTA = LSE + 2 * 64 * 4;    // float [2][64]
   static constexpr int BARS = DELTA + 2 * 64 * 4;
   static constexpr int TOTAL = BARS + 256 + 1024;
@@ -92,7 +94,7 @@ __device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&out)[64]) {
 __global__ void __launch_bounds__(448, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                 const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                const AttnBwdParams p) {
+                const __grid_constant__ CUtensorMap tmDQ, const AttnBwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BwdSmem::BARS);
@@ -108,6 +110,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* acc_full = bars + 15;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* s_dead = reinterpret_cast<volatile int*>(bars + 17);   // a softmax warp's wait gave up
+  volatile int* s_dead_dq = reinterpret_cast<volatile int*>(bars + 18);  // a dQ warp's wait gave up
   float* s_lse = reinterpret_cast<float*>(smem + BwdSmem::LSE);
   float* s_delta = reinterpret_cast<float*>(smem + BwdSmem::DELTA);
 
@@ -133,6 +136,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     mbar_init(acc_full, 1);
     *s_dead = 0;
+    *s_dead_dq = 0;
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -381,23 +385,38 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // ---------------------------------------------------------------- dQ read-out (thread = head-dim index d)
     const int lg = warp & 3;                    // warps 10-13: TMEM lane groups 2, 3, 0, 1
     const int d = lg * 32 + lane;
-    bool ok = true;
-    for (int it = 0; it < n_it && ok; ++it) {
-      const int h = hq, q0 = it_q0(it);
-      if (!mbar_wait(&dq_full[it & 1], (it >> 1) & 1, KID_ATTN_BWD, 10)) { ok = false; break; }
-      tc_fence_after();
+    const int tid_dq = threadIdx.x - 320;       // 0..127
+    float* sdq = reinterpret_cast<float*>(smem + BwdSmem::DQS);
+    bool alive = true;
+    if (tid_dq == 0) tma_prefetch_desc(&tmDQ);
+    for (int it = 0; it < n_it; ++it) {
+      const int q0 = it_q0(it);
       float v[64];
-      tmem_ld64(tm_DQT + (it & 1) * 64 + (static_cast<uint32_t>(lg * 32) << 16), v);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&dq_empty[it & 1]);
-      float* base = p.dq_acc + (static_cast<long long>(q0) * p.Hq + h) * BW_D + d;
-      const int nq = min(BW_Q, de - q0);
+      if (alive && !mbar_wait(&dq_full[it & 1], (it >> 1) & 1, KID_ATTN_BWD, 10)) { alive = false; *s_dead_dq = 1; }
+      if (alive) {
+        tc_fence_after();
+        tmem_ld64(tm_DQT + (it & 1) * 64 + (static_cast<uint32_t>(lg * 32) << 16), v);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&dq_empty[it & 1]);
+      }
+      // the reduction of the previous tile has finished reading the staging tile
+      if (it > 0 && tid_dq == 0) bulk_wait_read_all();
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (*s_dead_dq) break;
+      // transpose: this thread's d column of the [64 q][128 d] tile (a warp writes 128 contiguous bytes per row).
+      // Query rows past the end of the document carry exact zeros (their P and dS were masked), so the full tile
+      // is added; rows past the end of the tensor are clipped by the copy engine.
 #pragma unroll
-      for (int col = 0; col < BW_Q; ++col) {
-        if (col < nq) atomicAdd(base + static_cast<long long>(col) * p.Hq * BW_D, v[col]);
+      for (int col = 0; col < BW_Q; ++col) sdq[col * BW_D + d] = v[col];
+      fence_proxy_async_smem();
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (tid_dq == 0) {
+        tma_reduce_add_2d(&tmDQ, sdq, hq * BW_D, q0);
+        bulk_commit_group();
       }
     }
+    if (tid_dq == 0) bulk_wait_all();
   }
 
   tc_fence_before();
@@ -463,6 +482,13 @@ TTB_EXPORT int ttb_attn_bwd(const void* q, const void* k, long long ldk, const v
   if (bw_map(&tdo, dout, T, (long long)Hq * D, Hq * D, 64)) return 102;
   if (bw_map(&tk, k, T, ldk, Hk * D, 128)) return 103;
   if (bw_map(&tv, v, T, ldv, Hk * D, 128)) return 104;
+  CUtensorMap tdq;
+  {
+    uint64_t dims[2] = {static_cast<uint64_t>(Hq) * D, static_cast<uint64_t>(T)};
+    uint64_t str[1] = {static_cast<uint64_t>(Hq) * D * 4};
+    uint32_t box[2] = {static_cast<uint32_t>(D), 64};
+    if (make_tmap_f32_linear(&tdq, dq_acc, 2, dims, str, box)) return 105;
+  }
   static bool smem_done[16] = {};
   {
     const cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(attn_bwd_kernel), BwdSmem::TOTAL, smem_done);
@@ -471,7 +497,7 @@ TTB_EXPORT int ttb_attn_bwd(const void* q, const void* k, long long ldk, const v
   if (Hq != Hk && (dk_acc == nullptr || dv_acc == nullptr)) return 903;
   AttnBwdParams p{kv_tiles, lse, delta, dq_acc, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, dk_acc, dv_acc, Hq, Hk, T, scale, causal};
   dim3 grid(n_tiles, Hq);
-  attn_bwd_kernel<<<grid, 448, BwdSmem::TOTAL, stream>>>(tq, tdo, tk, tv, p);
+  attn_bwd_kernel<<<grid, 448, BwdSmem::TOTAL, stream>>>(tq, tdo, tk, tv, tdq, p);
   const long long n = T * Hq * D;
   attn_bwd_cast_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, stream>>>(dq_acc, (__nv_bfloat16*)dq, n);
   if (Hq != Hk) {

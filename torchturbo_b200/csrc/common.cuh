@@ -123,6 +123,20 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+// Tile in shared memory added element-wise into a tile of a global tensor (fp32 add done by the L2), tracked by the
+// thread's bulk async-group.  The x coordinate times the element size must be a multiple of 16 B and no coordinate
+// may be negative.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+               :
+               : "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the committed groups of this thread have finished reading their shared-memory sources
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// the committed groups of this thread have completed
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
@@ -342,8 +356,24 @@ inline cudaError_t ensure_dynamic_smem(const void* fn, int bytes, bool (&done)[1
   return cudaSuccess;
 }
 
+inline int make_tmap_typed(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                           const uint64_t* strides_bytes /* rank-1 entries */, const uint32_t* box,
+                           CUtensorMapDataType dtype, CUtensorMapSwizzle swizzle);
+
 inline int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
                           const uint64_t* strides_bytes /* rank-1 entries */, const uint32_t* box) {
+  return make_tmap_typed(out, base, rank, dims, strides_bytes, box, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+// fp32 tiles without swizzle (rows of the box contiguous in shared memory): TMA stores and reductions
+inline int make_tmap_f32_linear(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                                const uint64_t* strides_bytes, const uint32_t* box) {
+  return make_tmap_typed(out, base, rank, dims, strides_bytes, box, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
+inline int make_tmap_typed(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                           const uint64_t* strides_bytes /* rank-1 entries */, const uint32_t* box,
+                           CUtensorMapDataType dtype, CUtensorMapSwizzle swizzle) {
   auto fn = get_encode_fn();
   if (!fn) return -1;
   cuuint64_t gdim[3];
@@ -355,16 +385,16 @@ inline int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const ui
     bdim[i] = box[i];
   }
   for (int i = 0; i + 1 < rank; ++i) gstr[i] = strides_bytes[i];
-  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), gdim, gstr, bdim, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+  CUresult r = fn(out, dtype, rank, const_cast<void*>(base), gdim, gstr, bdim, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r == CUDA_ERROR_INVALID_CONTEXT || r == CUDA_ERROR_NOT_INITIALIZED) {
     // The encode call is a driver API and needs a context current on this thread.  A worker thread of the framework
     // (the autograd thread of device 0, which never has to switch devices) can arrive here before any runtime call
     // has bound the primary context to it: bind it (cudaFree(0) is the no-op that does) and encode again.
     (void)cudaFree(nullptr);
-    r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), gdim, gstr, bdim, estr,
-           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+    r = fn(out, dtype, rank, const_cast<void*>(base), gdim, gstr, bdim, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   }
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
