@@ -117,8 +117,43 @@ def _layout(segs, T_total: int, C: int, device):
     return gather.to(device), inv.to(device), seq_chunks, c
 
 
+def _channel_decay_products(kb, qc, kc, G, head_slab: int = 8, sub: int = 16):
+    """`sum_k x[i, k] kc[j, k] exp(G[i, k] - G[j, k])` on `i >= j` (zero above the diagonal) for `x` in (kb, qc), with
+    per-channel cumulative log decays `G [H, NC, C, K]` (non-increasing along C).
+
+    The chunk is cut into sub-chunks of `sub` rows.  Between different sub-chunks the decay factorises around the first
+    row `r` of the later one, `exp(G_i - G_r) exp(G_r - G_j)`, with both exponents non-positive, so those blocks are
+    plain matrix products; only the `sub x sub` diagonal blocks materialise pairwise decays (`[.., sub, sub, K]`, a
+    sixteenth of the `[.., C, C, K]` tensor per block row), a few heads at a time."""
+    H, NC, C, Kd = G.shape
+    nsb = C // sub
+    x = torch.stack((kb, qc))                                              # [2, H, NC, C, K]
+    rows = []
+    tril = torch.ones(sub, sub, dtype=torch.bool, device=G.device).tril()
+    for a in range(nsb):
+        ra = slice(a * sub, (a + 1) * sub)
+        Ga = G[:, :, ra]                                                    # [H, NC, sub, K]
+        parts = []
+        if a > 0:
+            ref = Ga[:, :, :1]                                              # first row of this sub-chunk
+            left = x[:, :, :, ra] * (Ga - ref).exp()
+            right = kc[:, :, : a * sub] * (ref - G[:, :, : a * sub]).exp()
+            parts.append(left @ right.transpose(-1, -2))                    # [2, H, NC, sub, a * sub]
+        diag = []
+        for h0 in range(0, H, head_slab):
+            sl = slice(h0, h0 + head_slab)
+            Dm = (Ga[sl, :, :, None, :] - Ga[sl, :, None, :, :]).masked_fill(~tril[None, None, :, :, None], -float("inf")).exp()
+            diag.append(torch.einsum("xhnik,hnijk,hnjk->xhnij", x[:, sl, :, ra], Dm, kc[sl, :, ra]))
+        parts.append(torch.cat(diag, 1))
+        if a + 1 < nsb:
+            parts.append(x.new_zeros(2, H, NC, sub, C - (a + 1) * sub))
+        rows.append(torch.cat(parts, -1))
+    out = torch.cat(rows, -2)                                               # [2, H, NC, C, C]
+    return out[0], out[1]
+
+
 def chunk_delta_rule_batched(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False, cu_seqlens=None,
-                             use_qk_l2norm=False, head_slab: int = 4):
+                             use_qk_l2norm=False, head_slab: int = 8):
     """q, k: [B, T, H, K]; v: [B, T, H, V]; g: [B, T, H] (scalar log decay) or [B, T, H, K]; beta: [B, T, H].
     Returns (o [B, T, H, V] in v's dtype, final state [N, H, K, V] fp32 or None)."""
     B, T, H, Kd = q.shape
@@ -159,14 +194,7 @@ def chunk_delta_rule_batched(q, k, v, g, beta, scale=None, initial_state=None, o
     lowd = torch.ones(C, C, dtype=torch.bool, device=dev).tril()
     kb = kc * bc[..., None]
     if vec:
-        # pairwise per-channel decays are materialised for a few heads at a time ([h, NC, C, C, K] fp32)
-        kk_parts, qk_parts = [], []
-        for h0 in range(0, H, head_slab):
-            sl = slice(h0, h0 + head_slab)
-            Dm = (G[sl, :, :, None, :] - G[sl, :, None, :, :]).masked_fill(~lowd[None, None, :, :, None], -float("inf")).exp()
-            kk_parts.append(torch.einsum("hnik,hnijk,hnjk->hnij", kb[sl], Dm, kc[sl]))
-            qk_parts.append(torch.einsum("hnik,hnijk,hnjk->hnij", qc[sl], Dm, kc[sl]))
-        kk, qk = torch.cat(kk_parts, 0), torch.cat(qk_parts, 0)
+        kk, qk = _channel_decay_products(kb, qc, kc, G, head_slab)
         eG = G.exp()
         k_in, q_in = kb * eG, qc * eG
         k_out = kc * (G[:, :, -1:, :] - G).exp()
