@@ -411,6 +411,70 @@ def test_attention_bwd(K, causal):
     assert float(dk[650:].abs().max()) == 0.0 and float(dq[650:].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("causal", [True, False])
+def test_latent_attention_widths_forward_and_backward(K, causal):
+    """Query / key heads 192 wide with 128-wide values (multi-head latent attention): forward, dK / dV from the
+    kv-major kernel and dQ from the query-major pass, against the fp32 formulation."""
+    from torchturbo_b200.ops.providers.native import attention_ref
+
+    torch.manual_seed(4)
+    T, H, Dqk, Dv = 700, 4, 192, 128
+    cu = torch.tensor([0, 200, 201, 520, 650], dtype=torch.int32)
+    q, k, v = _rand(T, H, Dqk), _rand(T, H, Dqk), _rand(T, H, Dv)
+    tiles, kv_tiles = K.build_q_tiles(cu).cuda(), K.build_kv_tiles(cu).cuda()
+    scale = Dqk ** -0.5
+    out, lse, ml = K.attn_fwd(q, k, v, tiles, scale=scale, causal=causal, want_max_logit=True)
+    assert out.shape == (T, H, Dv)
+    dout = _rand(T, H, Dv)
+    dq, dk, dv = K.attn_bwd(dout, q, k, v, out, lse, kv_tiles, scale=scale, causal=causal, q_tiles_dev=tiles)
+    torch.cuda.synchronize()
+    assert K.attn_status() == (0, 0)
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    ref, ref_ml = attention_ref(qf, kf, vf, cu, causal=causal, scale=scale, want_max_logits=True)
+    ref.backward(dout.float())
+    _close(out, ref, atol=2e-2)
+    _close(ml, ref_ml, rtol=1e-2, atol=1e-2)
+    _close(dq, qf.grad, atol=3e-2)
+    _close(dk, kf.grad, atol=3e-2)
+    _close(dv, vf.grad, atol=3e-2)
+    assert float(out[650:].abs().max()) == 0.0 and float(dq[650:].abs().max()) == 0.0 and float(dk[650:].abs().max()) == 0.0
+
+
+def test_deterministic_attention_backward_is_bit_reproducible_and_matches_the_default(K):
+    from torchturbo_b200.ops.providers.native import attention_ref
+
+    torch.manual_seed(5)
+    T, Hq, Hk, D = 900, 4, 4, 128
+    cu = torch.tensor([0, 300, 900], dtype=torch.int32)
+    q, k, v = _rand(T, Hq, D), _rand(T, Hk, D), _rand(T, Hk, D)
+    tiles, kv_tiles = K.build_q_tiles(cu).cuda(), K.build_kv_tiles(cu).cuda()
+    out, lse, _ = K.attn_fwd(q, k, v, tiles, scale=D ** -0.5, causal=True)
+    dout = _rand(T, Hq, D)
+    runs = [K.attn_bwd(dout, q, k, v, out, lse, kv_tiles, scale=D ** -0.5, causal=True, q_tiles_dev=tiles, deterministic=True)
+            for _ in range(3)]
+    fast = K.attn_bwd(dout, q, k, v, out, lse, kv_tiles, scale=D ** -0.5, causal=True)
+    torch.cuda.synchronize()
+    assert K.attn_status() == (0, 0)
+    for r in runs[1:]:
+        assert all(torch.equal(a, b) for a, b in zip(r, runs[0]))
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    attention_ref(qf, kf, vf, cu, causal=True, scale=D ** -0.5).backward(dout.float())
+    for got, fast_g, want in zip(runs[0], fast, (qf.grad, kf.grad, vf.grad)):
+        _close(got, want, atol=3e-2)
+        _close(got, fast_g.float(), atol=3e-2)
+    # grouped-query heads through the operator with the global switch on
+    from torchturbo_b200.ops.providers import b200_attention as BA
+
+    q2, k2, v2 = (_rand(T, h, D).requires_grad_(True) for h in (8, 2, 2))
+    torch.use_deterministic_algorithms(True)
+    try:
+        BA.B200Attention()(q2, k2, v2, cu, 600, causal=True, scale=D ** -0.5).backward(_rand(T, 8, D))
+    finally:
+        torch.use_deterministic_algorithms(False)
+    torch.cuda.synchronize()
+    assert K.attn_status() == (0, 0) and bool(torch.isfinite(q2.grad).all())
+
+
 def test_narrow_heads_run_on_the_tcgen05_kernel_with_zero_padding(K):
     """ViT-style attention (head width 72, full attention, no GQA) through the operator: zero-padded to 128 columns on
     the library's own kernel, forward and backward against the fp32 formulation."""

@@ -21,6 +21,7 @@ def main(argv=None) -> None:
     ap.add_argument("--seq-len", type=int, default=4096)
     ap.add_argument("--rows", type=int, default=40)
     ap.add_argument("--sort", default="cuda_time_total", help="profiler sort key, e.g. self_cpu_time_total")
+    ap.add_argument("--cprofile", type=int, default=0, help="also print the N host functions with the most own time (cProfile over 3 steps)")
     args = ap.parse_args(argv)
     sys.path.insert(0, str(Path(__file__).resolve().parents[2]))
     from bench import model_config  # the benchmark's model table (repository root)
@@ -58,6 +59,21 @@ def main(argv=None) -> None:
     t2 = time.perf_counter()
     if rank == 0:
         print(f"cpu issue time per step {(t1 - t0) / 3 * 1e3:.1f} ms, total per step {(t2 - t0) / 3 * 1e3:.1f} ms")
+    if args.cprofile:
+        import cProfile
+        import io
+        import pstats
+
+        pr = cProfile.Profile()
+        pr.enable()
+        for i in range(3):
+            train_step(eng, model, opt, [batches[3 + i]], check_finite=False)
+        pr.disable()
+        torch.cuda.synchronize()
+        if rank == 0:
+            buf = io.StringIO()
+            pstats.Stats(pr, stream=buf).sort_stats("tottime").print_stats(args.cprofile)
+            print(buf.getvalue())
     from torch.profiler import ProfilerActivity, profile
 
     with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:

@@ -1,4 +1,8 @@
-// Variable-length flash attention backward for sm_100a (head_dim 128, GQA, causal or full).
+// Variable-length flash attention backward for sm_100a (GQA, causal or full; value heads 128 wide, query / key heads
+// 128 wide, or 192 for multi-head latent attention).  The kernel is built in two forms: with the dQ^T product and its
+// reduction (128-wide heads, the default), and without it, where dQ comes from the query-major pass in
+// attention_bwd_dq.cu (192-wide heads, whose accumulators do not fit tensor memory together, and the bit-reproducible
+// mode of 128-wide heads).
 //
 // One CTA owns one 128-row KV tile of one document for one *query* head; K_j and V_j stay resident in shared memory
 // and dK_j / dV_j accumulate in TMEM over every 64-row query tile that can see the KV tile.  With grouped-query
@@ -46,15 +50,18 @@ struct AttnBwdParams {
   int causal;
 };
 
+template <int DQK, bool WITH_DQ>
 struct BwdSmem {
-  static constexpr int K = 0;                       // 32 KB
-  static constexpr int V = K + 32768;               // 32 KB
-  static constexpr int Q0 = V + 32768;              // 2 x 16 KB
-  static constexpr int DO0 = Q0 + 2 * 16384;        // 2 x 16 KB
+  static constexpr int K_BYTES = 128 * DQK * 2;     // K tile: DQK / 64 panels of 16 KB
+  static constexpr int Q_BYTES = 64 * DQK * 2;      // Q tile: DQK / 64 panels of 8 KB
+  static constexpr int K = 0;
+  static constexpr int V = K + K_BYTES;             // 32 KB
+  static constexpr int Q0 = V + 32768;              // 2 x Q_BYTES
+  static constexpr int DO0 = Q0 + 2 * Q_BYTES;      // 2 x 16 KB
   static constexpr int PT = DO0 + 2 * 16384;        // 2 x 16 KB  P^T  [128 kv][64 q]
   static constexpr int DST = PT + 2 * 16384;        // 2 x 16 KB  dS^T [128 kv][64 q]
   static constexpr int DQS = DST + 2 * 16384;       // 32 KB  dQ tile [64 q][128 d] fp32, source of the TMA reduction
-  static constexpr int LSE = DQS + 32768;           // float [2][64]
+  static constexpr int LSE = DQS + (WITH_DQ ? 32768 : 0);   // float [2][64]
   static constexpr int DELTA = LSE + 2 * 64 * 4;    // float [2][64]
   static constexpr int BARS = DELTA + 2 * 64 * 4;
   static constexpr int TOTAL = BARS + 256 + 1024;
@@ -91,10 +98,14 @@ __device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&out)[64]) {
   }
 }
 
+template <int DQK, bool WITH_DQ>
 __global__ void __launch_bounds__(448, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                 const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                 const __grid_constant__ CUtensorMap tmDQ, const AttnBwdParams p) {
+  static_assert(DQK == 128 || !WITH_DQ, "the fused dQ path exists for 128-wide heads only");
+  using BwdSmem = ttb::BwdSmem<DQK, WITH_DQ>;
+  constexpr int NP = DQK / 64, Q_BYTES = BwdSmem::Q_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BwdSmem::BARS);
@@ -149,9 +160,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tm_ST = tmem_base;          // 64 cols
   const uint32_t tm_DPT = tmem_base + 64;    // 64 cols
-  const uint32_t tm_DQT = tmem_base + 128;   // 2 x 64 cols
-  const uint32_t tm_DV = tmem_base + 256;    // 128 cols
-  const uint32_t tm_DK = tmem_base + 384;    // 128 cols
+  const uint32_t tm_DQT = tmem_base + 128;   // 2 x 64 cols (form with dQ)
+  const uint32_t tm_DV = tmem_base + (WITH_DQ ? 256 : 128);    // 128 cols
+  const uint32_t tm_DK = tmem_base + (WITH_DQ ? 384 : 256);    // DQK cols
 
   auto it_head = [&](int) { return hq; };
   auto it_q0 = [&](int it) { return q_first + it * BW_Q; };
@@ -160,9 +171,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // ---------------------------------------------------------------- TMA producer
     if (elect_one()) {
       tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmDO); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
-      mbar_expect_tx(kv_full, 65536);
-      tma_load_2d(smem + BwdSmem::K, &tmK, kv_full, hk * BW_D, kv0);
-      tma_load_2d(smem + BwdSmem::K + 16384, &tmK, kv_full, hk * BW_D + 64, kv0);
+      mbar_expect_tx(kv_full, BwdSmem::K_BYTES + 32768);
+#pragma unroll
+      for (int pn = 0; pn < NP; ++pn) tma_load_2d(smem + BwdSmem::K + pn * 16384, &tmK, kv_full, hk * DQK + pn * 64, kv0);
       tma_load_2d(smem + BwdSmem::V, &tmV, kv_full, hk * BW_D, kv0);
       tma_load_2d(smem + BwdSmem::V + 16384, &tmV, kv_full, hk * BW_D + 64, kv0);
       for (int it = 0; it < n_it; ++it) {
@@ -170,11 +181,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint32_t ph = (it >> 1) & 1;
         if (!mbar_wait(&qdo_empty[st], ph ^ 1, KID_ATTN_BWD, 1)) break;
         const int h = it_head(it), q0 = it_q0(it);
-        mbar_expect_tx(&qdo_full[st], 32768);
-        uint8_t* sq = smem + BwdSmem::Q0 + st * 16384;
+        mbar_expect_tx(&qdo_full[st], Q_BYTES + 16384);
+        uint8_t* sq = smem + BwdSmem::Q0 + st * Q_BYTES;
         uint8_t* sd = smem + BwdSmem::DO0 + st * 16384;
-        tma_load_2d(sq, &tmQ, &qdo_full[st], h * BW_D, q0);
-        tma_load_2d(sq + 8192, &tmQ, &qdo_full[st], h * BW_D + 64, q0);
+#pragma unroll
+        for (int pn = 0; pn < NP; ++pn) tma_load_2d(sq + pn * 8192, &tmQ, &qdo_full[st], h * DQK + pn * 64, q0);
         tma_load_2d(sd, &tmDO, &qdo_full[st], h * BW_D, q0);
         tma_load_2d(sd + 8192, &tmDO, &qdo_full[st], h * BW_D + 64, q0);
       }
@@ -184,6 +195,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (elect_one()) {
       constexpr uint32_t id_s = make_idesc_bf16(128, 64, false, false);
       constexpr uint32_t id_acc = make_idesc_bf16(128, 128, false, true);
+      constexpr uint32_t id_dk = make_idesc_bf16(128, DQK, false, true);
       constexpr uint32_t id_dq = make_idesc_bf16(128, 64, true, true);
       const uint32_t sK = smem_u32(smem + BwdSmem::K), sV = smem_u32(smem + BwdSmem::V);
       const uint32_t sPT = smem_u32(smem + BwdSmem::PT), sDST = smem_u32(smem + BwdSmem::DST);
@@ -194,10 +206,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!mbar_wait(&qdo_full[st], ph, KID_ATTN_BWD, 3)) return false;
         if (!mbar_wait(st_empty, (it & 1) ^ 1, KID_ATTN_BWD, 4)) return false;
         tc_fence_after();
-        const uint32_t sQ = smem_u32(smem + BwdSmem::Q0 + st * 16384);
+        const uint32_t sQ = smem_u32(smem + BwdSmem::Q0 + st * Q_BYTES);
         const uint32_t sDO = smem_u32(smem + BwdSmem::DO0 + st * 16384);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {  // reduction over d = 128
+        for (int kk = 0; kk < DQK / 16; ++kk) {  // reduction over the query / key head width
           const uint32_t offa = (kk >> 2) * 16384 + (kk & 3) * 32;   // K / V tiles: [128 rows][64 d] panels
           const uint32_t offb = (kk >> 2) * 8192 + (kk & 3) * 32;    // Q / dO tiles: [64 rows][64 d] panels
           umma_ss(tm_ST, make_smem_desc(sK + offa, 16, 1024), make_smem_desc(sQ + offb, 16, 1024), id_s, kk != 0);
@@ -219,10 +231,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const int st = it & 1;
         const uint32_t ph2 = (it >> 1) & 1;
         if (!mbar_wait(&pds_full[st], ph2, KID_ATTN_BWD, 5)) { ok = false; break; }
-        if (!mbar_wait(&dq_empty[st], ph2 ^ 1, KID_ATTN_BWD, 6)) { ok = false; break; }
+        if (WITH_DQ) {
+          if (!mbar_wait(&dq_empty[st], ph2 ^ 1, KID_ATTN_BWD, 6)) { ok = false; break; }
+        }
         tc_fence_after();
         const uint32_t sPTb = sPT + st * 16384, sDSTb = sDST + st * 16384;
-        const uint32_t sQ = smem_u32(smem + BwdSmem::Q0 + st * 16384);
+        const uint32_t sQ = smem_u32(smem + BwdSmem::Q0 + st * Q_BYTES);
         const uint32_t sDO = smem_u32(smem + BwdSmem::DO0 + st * 16384);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {  // reduction over q = 64
@@ -232,17 +246,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
-          umma_ss(tm_DK, make_smem_desc(sDSTb + kk * 32, 16, 1024), make_smem_desc(sQ + kk * 2048, 8192, 1024), id_acc,
+          umma_ss(tm_DK, make_smem_desc(sDSTb + kk * 32, 16, 1024), make_smem_desc(sQ + kk * 2048, 8192, 1024), id_dk,
                   (it | kk) != 0);
         }
         umma_commit(&qdo_empty[st]);
+        if (WITH_DQ) {
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {  // reduction over kv = 128
-          // A: K^T from the K tile ([kv rows][d], MN-major, d panels 16 KB apart); B: dS^T ([kv rows][q]) MN-major
-          umma_ss(tm_DQT + st * 64, make_smem_desc(sK + kk * 2048, 16384, 1024), make_smem_desc(sDSTb + kk * 2048, 8192, 1024),
-                  id_dq, kk != 0);
+          for (int kk = 0; kk < 8; ++kk) {  // reduction over kv = 128
+            // A: K^T from the K tile ([kv rows][d], MN-major, d panels 16 KB apart); B: dS^T ([kv rows][q]) MN-major
+            umma_ss(tm_DQT + st * 64, make_smem_desc(sK + kk * 2048, 16384, 1024),
+                    make_smem_desc(sDSTb + kk * 2048, 8192, 1024), id_dq, kk != 0);
+          }
+          umma_commit(&dq_full[st]);
         }
-        umma_commit(&dq_full[st]);
         umma_commit(&pds_empty[st]);
       }
       if (ok) umma_commit(acc_full);
@@ -344,12 +360,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t lane_off = static_cast<uint32_t>(lg * 32) << 16;
       {
         const int which = half;                  // columns 0-31 group: dV, the other group: dK
-        const long long off = (static_cast<long long>(kv) * p.Hk + hk) * BW_D;
+        const int width = which == 0 ? BW_D : DQK;
+        const long long off = (static_cast<long long>(kv) * p.Hk + hk) * width;
         __nv_bfloat16* dst = (which == 0 ? p.dv : p.dk) + off;
         float* acc = (which == 0 ? p.dv_acc : p.dk_acc) + off;
         const uint32_t tm = (which == 0 ? tm_DV : tm_DK) + lane_off;
 #pragma unroll 1
-        for (int cb = 0; cb < 4; ++cb) {
+        for (int cb = 0; cb < width / 32; ++cb) {
           uint32_t v[32];
           if (n_it > 0) {
             tmem_ld_32x32b_x32(tm + cb * 32, v);
@@ -381,7 +398,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       }
     }
-  } else {
+  } else if (WITH_DQ) {
     // ---------------------------------------------------------------- dQ read-out (thread = head-dim index d)
     const int lg = warp & 3;                    // warps 10-13: TMEM lane groups 2, 3, 0, 1
     const int d = lg * 32 + lane;
@@ -464,13 +481,29 @@ static int bw_map(CUtensorMap* m, const void* base, long long rows, long long ro
 
 using namespace ttb;
 
-// q, dout, out: [T, Hq*128] contiguous rows; k: [T, Hk*128] (ldk); v: [T, Hk*128] (ldv, may be strided).
-// dq_acc fp32 [T*Hq*128] zero-initialised scratch; delta fp32 [Hq*T] scratch.
+template <int DQK, bool WITH_DQ>
+static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const CUtensorMap& tk, const CUtensorMap& tv,
+                           const CUtensorMap& tdq, const AttnBwdParams& p, int n_tiles, cudaStream_t stream) {
+  static bool smem_done[16] = {};
+  using Smem = ttb::BwdSmem<DQK, WITH_DQ>;
+  const cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(attn_bwd_kernel<DQK, WITH_DQ>), Smem::TOTAL, smem_done);
+  if (e != cudaSuccess) return 300 + static_cast<int>(e);
+  dim3 grid(n_tiles, p.Hq);
+  attn_bwd_kernel<DQK, WITH_DQ><<<grid, WITH_DQ ? 448 : 320, Smem::TOTAL, stream>>>(tq, tdo, tk, tv, tdq, p);
+  return 0;
+}
+
+// q: [T, Hq*D] contiguous rows; dout, out: [T, Hq*128] contiguous rows; k: [T, Hk*D] (ldk); v: [T, Hk*128] (ldv, may be
+// strided); D = 128 or 192.  delta fp32 [Hq*T] scratch (left filled with rowsum(dO * O) for the query-major dQ pass).
+// with_dq != 0 (D = 128 only): dQ too, reduced into dq_acc (fp32 [T*Hq*128], zero-initialised) and cast to dq;
+// with_dq == 0: dK and dV only (dq_acc and dq unused).  dk: [T, Hk, D], dv: [T, Hk, 128]; with Hq > Hk the fp32
+// accumulators dk_acc / dv_acc (zero-initialised, same shapes) are required.
 TTB_EXPORT int ttb_attn_bwd(const void* q, const void* k, long long ldk, const void* v, long long ldv, const void* out,
                             const void* dout, const float* lse, float* delta, float* dq_acc, float* dk_acc,
                             float* dv_acc, void* dq, void* dk, void* dv, const int* kv_tiles, int n_tiles, long long T, int Hq, int Hk, int D, float scale,
-                            int causal, void* stream_ptr) {
-  if (D != 128 || Hq % Hk) return 901;
+                            int causal, int with_dq, void* stream_ptr) {
+  if ((D != 128 && D != 192) || Hq % Hk) return 901;
+  if (with_dq && D != 128) return 904;
   if ((ldk % 8) || (ldv % 8)) return 902;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_ptr);
   if (T == 0 || n_tiles == 0) return 0;
@@ -479,31 +512,31 @@ TTB_EXPORT int ttb_attn_bwd(const void* q, const void* k, long long ldk, const v
                                                                         (const __nv_bfloat16*)out, delta, T, Hq);
   CUtensorMap tq, tdo, tk, tv;
   if (bw_map(&tq, q, T, (long long)Hq * D, Hq * D, 64)) return 101;
-  if (bw_map(&tdo, dout, T, (long long)Hq * D, Hq * D, 64)) return 102;
+  if (bw_map(&tdo, dout, T, (long long)Hq * BW_D, Hq * BW_D, 64)) return 102;
   if (bw_map(&tk, k, T, ldk, Hk * D, 128)) return 103;
-  if (bw_map(&tv, v, T, ldv, Hk * D, 128)) return 104;
-  CUtensorMap tdq;
-  {
+  if (bw_map(&tv, v, T, ldv, Hk * BW_D, 128)) return 104;
+  CUtensorMap tdq = tq;   // placeholder in the form without dQ
+  if (with_dq) {
+    if (dq_acc == nullptr || dq == nullptr) return 905;
     uint64_t dims[2] = {static_cast<uint64_t>(Hq) * D, static_cast<uint64_t>(T)};
     uint64_t str[1] = {static_cast<uint64_t>(Hq) * D * 4};
     uint32_t box[2] = {static_cast<uint32_t>(D), 64};
     if (make_tmap_f32_linear(&tdq, dq_acc, 2, dims, str, box)) return 105;
   }
-  static bool smem_done[16] = {};
-  {
-    const cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(attn_bwd_kernel), BwdSmem::TOTAL, smem_done);
-    if (e != cudaSuccess) return 300 + static_cast<int>(e);
-  }
   if (Hq != Hk && (dk_acc == nullptr || dv_acc == nullptr)) return 903;
   AttnBwdParams p{kv_tiles, lse, delta, dq_acc, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, dk_acc, dv_acc, Hq, Hk, T, scale, causal};
-  dim3 grid(n_tiles, Hq);
-  attn_bwd_kernel<<<grid, 448, BwdSmem::TOTAL, stream>>>(tq, tdo, tk, tv, tdq, p);
-  const long long n = T * Hq * D;
-  attn_bwd_cast_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, stream>>>(dq_acc, (__nv_bfloat16*)dq, n);
+  const int rc = with_dq ? launch_attn_bwd<128, true>(tq, tdo, tk, tv, tdq, p, n_tiles, stream)
+                         : (D == 128 ? launch_attn_bwd<128, false>(tq, tdo, tk, tv, tdq, p, n_tiles, stream)
+                                     : launch_attn_bwd<192, false>(tq, tdo, tk, tv, tdq, p, n_tiles, stream));
+  if (rc) return rc;
+  if (with_dq) {
+    const long long n = T * Hq * D;
+    attn_bwd_cast_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, stream>>>(dq_acc, (__nv_bfloat16*)dq, n);
+  }
   if (Hq != Hk) {
-    const long long nk = T * Hk * D;
+    const long long nk = T * Hk * D, nv = T * Hk * BW_D;
     attn_bwd_cast_kernel<<<(unsigned)((nk / 8 + 255) / 256), 256, 0, stream>>>(dk_acc, (__nv_bfloat16*)dk, nk);
-    attn_bwd_cast_kernel<<<(unsigned)((nk / 8 + 255) / 256), 256, 0, stream>>>(dv_acc, (__nv_bfloat16*)dv, nk);
+    attn_bwd_cast_kernel<<<(unsigned)((nv / 8 + 255) / 256), 256, 0, stream>>>(dv_acc, (__nv_bfloat16*)dv, nv);
   }
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;

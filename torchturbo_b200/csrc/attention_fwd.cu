@@ -1,4 +1,5 @@
-// Variable-length (packed) flash attention forward for sm_100a, head_dim 128, GQA, causal or full.
+// Variable-length (packed) flash attention forward for sm_100a, GQA, causal or full; value heads 128 wide, query / key
+// heads 128 wide or 192 (multi-head latent attention: 128 without position + 64 rotary).
 //
 // One CTA handles one 128-row query tile of one document for one query head.  Warp roles:
 //   warp 0      TMA producer   : Q once, then K_j (3 stages) / V_j (2 stages) tiles
@@ -45,11 +46,14 @@ struct AttnFwdParams {
   int causal;
 };
 
+template <int DQK>
 struct AttnSmem {
-  // tiles (each 32 KB, 1024-byte aligned)
+  // tiles of 128 rows in 64-column swizzle panels of 16 KB, 1024-byte aligned
+  static constexpr int QK_BYTES = 128 * DQK * 2;          // one Q or K tile
+  static constexpr int KS = DQK == 128 ? 3 : 2;           // K stages
   static constexpr int Q = 0;
-  static constexpr int K0 = Q + TILE_BYTES;
-  static constexpr int V0 = K0 + 3 * TILE_BYTES;           // K: three stages (a TMA round trip is longer than one block)
+  static constexpr int K0 = Q + QK_BYTES;
+  static constexpr int V0 = K0 + KS * QK_BYTES;
   static constexpr int ROWMAX = V0 + 2 * TILE_BYTES;      // float [2 parities][2 halves][128]
   static constexpr int ROWSUM = ROWMAX + 4 * 128 * 4;     // float [2 halves][128]
   static constexpr int BARS = ROWSUM + 2 * 128 * 4;
@@ -68,9 +72,12 @@ __device__ __forceinline__ void atomic_max_float(float* addr, float v) {
   else atomicMin(reinterpret_cast<unsigned int*>(addr), __float_as_uint(v));
 }
 
+template <int DQK>
 __global__ void __launch_bounds__(320, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const AttnFwdParams p) {
+  using AttnSmem = ttb::AttnSmem<DQK>;
+  constexpr int KS = AttnSmem::KS, QK_BYTES = AttnSmem::QK_BYTES, NP = DQK / 64;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AttnSmem::BARS);
@@ -126,17 +133,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // ---------------------------------------------------------------- TMA producer
     if (elect_one()) {
       tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
-      mbar_expect_tx(q_full, TILE_BYTES);
-      tma_load_2d(smem + AttnSmem::Q, &tmQ, q_full, h * AT_D, q0);
-      tma_load_2d(smem + AttnSmem::Q + 16384, &tmQ, q_full, h * AT_D + 64, q0);
+      mbar_expect_tx(q_full, QK_BYTES);
+#pragma unroll
+      for (int pn = 0; pn < NP; ++pn) tma_load_2d(smem + AttnSmem::Q + pn * 16384, &tmQ, q_full, h * DQK + pn * 64, q0);
       bool ok = true;
       auto load_k = [&](int j) -> bool {
-        const int ks = j % 3;
-        if (!mbar_wait(&k_empty[ks], ((j / 3) & 1) ^ 1, KID_ATTN_FWD, 1)) return false;
+        const int ks = j % KS;
+        if (!mbar_wait(&k_empty[ks], ((j / KS) & 1) ^ 1, KID_ATTN_FWD, 1)) return false;
         const int kv0 = ds + j * AT_BN;
-        mbar_expect_tx(&k_full[ks], TILE_BYTES);
-        tma_load_2d(smem + AttnSmem::K0 + ks * TILE_BYTES, &tmK, &k_full[ks], hk * AT_D, kv0);
-        tma_load_2d(smem + AttnSmem::K0 + ks * TILE_BYTES + 16384, &tmK, &k_full[ks], hk * AT_D + 64, kv0);
+        mbar_expect_tx(&k_full[ks], QK_BYTES);
+#pragma unroll
+        for (int pn = 0; pn < NP; ++pn)
+          tma_load_2d(smem + AttnSmem::K0 + ks * QK_BYTES + pn * 16384, &tmK, &k_full[ks], hk * DQK + pn * 64, kv0);
         return true;
       };
       // K runs one block ahead of V, so that a wait for a V buffer never holds back the next K request
@@ -162,13 +170,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       auto issue_s = [&](int j) -> bool {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        const int ks = j % 3;
-        if (!mbar_wait(&k_full[ks], (j / 3) & 1, KID_ATTN_FWD, 4)) return false;
+        const int ks = j % KS;
+        if (!mbar_wait(&k_full[ks], (j / KS) & 1, KID_ATTN_FWD, 4)) return false;
         if (!mbar_wait(&s_empty[st], ph ^ 1, KID_ATTN_FWD, 5)) return false;
         tc_fence_after();
-        const uint32_t sK = smem_u32(smem + AttnSmem::K0 + ks * TILE_BYTES);
+        const uint32_t sK = smem_u32(smem + AttnSmem::K0 + ks * QK_BYTES);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
+        for (int kk = 0; kk < DQK / 16; ++kk) {
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
           umma_ss(tm_S + st * 128, make_smem_desc(sQ + off, 16, 1024), make_smem_desc(sK + off, 16, 1024), idesc_s,
                   kk != 0);
@@ -361,6 +369,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
+template <int DQK>
+static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnFwdParams& p, int n_tiles,
+                           cudaStream_t stream) {
+  static bool smem_done[16] = {};
+  const cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(attn_fwd_kernel<DQK>), AttnSmem<DQK>::TOTAL, smem_done);
+  if (e != cudaSuccess) return 300 + static_cast<int>(e);
+  dim3 grid(n_tiles, p.Hq);
+  attn_fwd_kernel<DQK><<<grid, 320, AttnSmem<DQK>::TOTAL, stream>>>(tq, tk, tv, p);
+  return 0;
+}
+
 static int make_rows_map(CUtensorMap* m, const void* base, long long rows, long long row_stride_elems, int cols) {
   uint64_t dims[2] = {static_cast<uint64_t>(cols), static_cast<uint64_t>(rows)};
   uint64_t str[1] = {static_cast<uint64_t>(row_stride_elems) * 2};
@@ -372,26 +391,22 @@ static int make_rows_map(CUtensorMap* m, const void* base, long long rows, long 
 
 using namespace ttb;
 
-// q: [T, Hq*128] (row stride ldq), k: [T, Hk*128] (ldk), v: [T, Hk*128] (ldv; may be a strided view)
+// q: [T, Hq*D] (row stride ldq), k: [T, Hk*D] (ldk), v: [T, Hk*128] (ldv; may be a strided view); D = 128 or 192
 TTB_EXPORT int ttb_attn_fwd(const void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv,
                             void* out, float* lse, float* max_logit, const int* q_tiles, int n_tiles, long long T,
                             int Hq, int Hk, int D, float scale, int causal, void* stream) {
-  if (D != 128 || Hq % Hk) return 901;
+  if ((D != 128 && D != 192) || Hq % Hk) return 901;
   if ((ldq % 8) || (ldk % 8) || (ldv % 8)) return 902;
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) return 903;
   if (n_tiles == 0) return 0;
   CUtensorMap tq, tk, tv;
   if (make_rows_map(&tq, q, T, ldq, Hq * D)) return 101;
   if (make_rows_map(&tk, k, T, ldk, Hk * D)) return 102;
-  if (make_rows_map(&tv, v, T, ldv, Hk * D)) return 103;
-  static bool smem_done[16] = {};
-  {
-    const cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(attn_fwd_kernel), AttnSmem::TOTAL, smem_done);
-    if (e != cudaSuccess) return 300 + static_cast<int>(e);
-  }
+  if (make_rows_map(&tv, v, T, ldv, Hk * AT_D)) return 103;
   AttnFwdParams p{q_tiles, (__nv_bfloat16*)out, lse, max_logit, Hq, Hk, T, scale, causal};
-  dim3 grid(n_tiles, Hq);
-  attn_fwd_kernel<<<grid, 320, AttnSmem::TOTAL, reinterpret_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);
+  const int rc = D == 128 ? launch_attn_fwd<128>(tq, tk, tv, p, n_tiles, reinterpret_cast<cudaStream_t>(stream))
+                          : launch_attn_fwd<192>(tq, tk, tv, p, n_tiles, reinterpret_cast<cudaStream_t>(stream));
+  if (rc) return rc;
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }

@@ -648,11 +648,14 @@ def build_q_tiles(cu_seqlens, block: int = 128) -> torch.Tensor:
 
 def attn_fwd(q, k, v, q_tiles_dev, *, scale: float, causal: bool = True, want_lse: bool = True,
              want_max_logit: bool = False):
-    """q: [T, Hq, 128]; k, v: [T, Hk, 128] (v may be a row-strided view).  Returns (out, lse [Hq, T], max_logit [Hq])."""
+    """q: [T, Hq, D]; k: [T, Hk, D] with D = 128 or 192 (multi-head latent attention); v: [T, Hk, 128] (may be a
+    row-strided view).  Returns (out [T, Hq, 128], lse [Hq, T], max_logit [Hq])."""
     T, Hq, D = q.shape
     Hk = k.shape[1]
-    assert q.stride(2) == 1 and q.stride(1) == D and k.stride(1) == D and v.stride(1) == D and v.stride(2) == 1
-    out = torch.zeros_like(q)  # rows past the last sequence boundary are never written by the kernel and must read as zero
+    assert D in (128, 192) and k.shape[2] == D and v.shape[2] == 128
+    assert q.stride(2) == 1 and q.stride(1) == D and k.stride(1) == D and k.stride(2) == 1 and v.stride(1) == 128 and v.stride(2) == 1
+    # rows past the last sequence boundary are never written by the kernel and must read as zero
+    out = torch.zeros(T, Hq, 128, dtype=q.dtype, device=q.device)
     lse = torch.full((Hq, T), float("-inf"), dtype=torch.float32, device=q.device) if want_lse else None
     ml = torch.full((Hq,), float("-inf"), dtype=torch.float32, device=q.device) if want_max_logit else None
     _check(lib().ttb_attn_fwd(_p(q), C.c_longlong(q.stride(0)), _p(k), C.c_longlong(k.stride(0)), _p(v),
@@ -909,32 +912,45 @@ def ep_gather_vals(peer_ptrs, off_vals, expert, dest_row, El, world, cap_rows, s
     return out
 
 
-def attn_bwd(dout, q, k, v, out, lse, kv_tiles_dev, *, scale: float, causal: bool = True):
-    """Gradients of `attn_fwd`.  Returns (dq [T,Hq,128], dk [T,Hk,128], dv [T,Hk,128]) in bf16; dQ is accumulated in
-    an fp32 scratch buffer with atomic adds (the order of the adds is not deterministic)."""
+def attn_bwd(dout, q, k, v, out, lse, kv_tiles_dev, *, scale: float, causal: bool = True, q_tiles_dev=None,
+             deterministic: bool = False):
+    """Gradients of `attn_fwd`.  Returns (dq [T,Hq,D], dk [T,Hk,D], dv [T,Hk,128]) in bf16.
+
+    128-wide heads by default: one kernel; dQ tiles are added into an fp32 scratch buffer by TMA reductions (the order
+    of the adds is not fixed).  With `deterministic=True`, and always for 192-wide query / key heads, that kernel
+    computes dK / dV only and dQ comes from the query-major pass (`q_tiles_dev` required), which writes every dQ tile
+    once; with grouped-query attention the dK / dV sums over the query heads of a group still use atomics."""
     T, Hq, D = q.shape
     Hk = k.shape[1]
     assert dout.is_contiguous() and out.is_contiguous() and q.is_contiguous()
-    assert k.stride(1) == D and v.stride(1) == D and v.stride(2) == 1
+    assert k.stride(1) == D and k.stride(2) == 1 and v.stride(1) == 128 and v.stride(2) == 1
+    split = deterministic or D != 128
+    if split and q_tiles_dev is None:
+        raise ValueError("the query-major dQ pass needs the query tile table")
     delta = torch.empty(Hq * T, dtype=torch.float32, device=q.device)
-    dq_acc = torch.zeros(T, Hq, D, dtype=torch.float32, device=q.device)
-    dq = torch.empty_like(q)
+    dq_acc = None if split else torch.zeros(T, Hq, D, dtype=torch.float32, device=q.device)
+    dq = torch.zeros_like(q) if split else torch.empty_like(q)
     if Hq != Hk:   # query heads of a group add into fp32 accumulators, converted at the end
-        kv_acc = torch.zeros(2, T, Hk, D, dtype=torch.float32, device=q.device)
-        dk_acc, dv_acc = kv_acc[0], kv_acc[1]
+        dk_acc = torch.zeros(T, Hk, D, dtype=torch.float32, device=q.device)
+        dv_acc = torch.zeros(T, Hk, 128, dtype=torch.float32, device=q.device)
         dk = torch.empty(T, Hk, D, dtype=q.dtype, device=q.device)
-        dv = torch.empty(T, Hk, D, dtype=q.dtype, device=q.device)
+        dv = torch.empty(T, Hk, 128, dtype=q.dtype, device=q.device)
     else:
         dk_acc = dv_acc = None
         dk = torch.zeros(T, Hk, D, dtype=q.dtype, device=q.device)
-        dv = torch.zeros(T, Hk, D, dtype=q.dtype, device=q.device)
+        dv = torch.zeros(T, Hk, 128, dtype=q.dtype, device=q.device)
     global LAUNCH_COUNT
     _check(lib().ttb_attn_bwd(_p(q), _p(k), C.c_longlong(k.stride(0)), _p(v), C.c_longlong(v.stride(0)), _p(out),
                               _p(dout), _p(lse), _p(delta), _p(dq_acc), _p(dk_acc), _p(dv_acc), _p(dq), _p(dk), _p(dv),
                               _p(kv_tiles_dev),
                               C.c_int(kv_tiles_dev.shape[0]), C.c_longlong(T), C.c_int(Hq), C.c_int(Hk), C.c_int(D),
-                              C.c_float(scale), C.c_int(int(causal)), _stream()), "ttb_attn_bwd")
-    LAUNCH_COUNT += 2 if Hq == Hk else 4
+                              C.c_float(scale), C.c_int(int(causal)), C.c_int(0 if split else 1), _stream()), "ttb_attn_bwd")
+    LAUNCH_COUNT += (1 if split else 2) + (0 if Hq == Hk else 2)
+    if split:
+        _check(lib().ttb_attn_bwd_dq(_p(q), _p(k), C.c_longlong(k.stride(0)), _p(v), C.c_longlong(v.stride(0)), _p(dout),
+                                     _p(lse), _p(delta), _p(dq), _p(q_tiles_dev), C.c_int(q_tiles_dev.shape[0]),
+                                     C.c_longlong(T), C.c_int(Hq), C.c_int(Hk), C.c_int(D), C.c_float(scale),
+                                     C.c_int(int(causal)), _stream()), "ttb_attn_bwd_dq")
     return dq, dk, dv
 
 

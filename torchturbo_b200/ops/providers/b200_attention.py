@@ -43,8 +43,9 @@ class FlashAttnFn(torch.autograd.Function):
         q, k, v, out, lse = ctx.saved_tensors
         cu_seqlens, max_seqlen, causal, scale, n = ctx.meta
         if os.environ.get("TORCHTURBO_ATTN_BWD", "tcgen05") == "tcgen05":
-            tiles = _tiles_for(cu_seqlens, q.device)[3]
-            dq, dk, dv = K.attn_bwd(dout.contiguous(), q, k, v, out, lse, tiles, scale=scale, causal=causal)
+            cached = _tiles_for(cu_seqlens, q.device)
+            dq, dk, dv = K.attn_bwd(dout.contiguous(), q, k, v, out, lse, cached[3], scale=scale, causal=causal,
+                                    q_tiles_dev=cached[0], deterministic=torch.are_deterministic_algorithms_enabled())
             return dq, dk, dv, None, None, None, None, None
         # library backward on this kernel's out / lse (selected with TORCHTURBO_ATTN_BWD=flash_attn2; used as a baseline)
         from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
@@ -69,8 +70,9 @@ def _LIB_FALLBACK(q, k, v, cu_seqlens, max_seqlen, *, causal, scale):
 
 
 def _usable(q, k, v):
-    return _ok(q, k, v) and q.shape[-1] == 128 and v.shape[-1] == 128 and q.dim() == 3 and q.shape[1] % k.shape[1] == 0 and v.stride(2) == 1 \
-        and v.stride(1) == 128
+    """128-wide heads, or multi-head latent attention (query / key 192 wide, value 128 wide)."""
+    return _ok(q, k, v) and q.shape[-1] in (128, 192) and k.shape[-1] == q.shape[-1] and v.shape[-1] == 128 and q.dim() == 3 \
+        and q.shape[1] % k.shape[1] == 0 and v.stride(2) == 1 and v.stride(1) == 128
 
 
 def _paddable(q, k, v):
@@ -100,7 +102,7 @@ class B200Attention(_B200Op):
         if not _usable(q, k, v):
             if _paddable(q, k, v):
                 return _padded_call(q, k, v, cu, max_seqlen, causal, scale, False)
-            # wider heads (MLA 192 / 128): the library kernel
+            # other head widths: the library kernel
             return _LIB_FALLBACK(q, k, v, cu_seqlens, max_seqlen, causal=causal, scale=scale)
         scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
         return FlashAttnFn.apply(q.contiguous(), k.contiguous(), v, cu.cpu() if cu.is_cuda else cu, max_seqlen, causal,
