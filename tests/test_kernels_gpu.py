@@ -870,3 +870,49 @@ def test_fused_aux_loss_matches_the_torch_chain(K):
     assert torch.allclose(score.grad, s2.grad, rtol=1e-5, atol=1e-10)
     z, _ = _FusedAuxLoss.apply(score.detach(), torch.zeros_like(cnt), k, float(E * coeff), coeff)
     assert float(z) == 0.0
+
+
+def test_latent_attention_mixer_runs_on_the_tcgen05_kernels(K):
+    """The multi-head latent attention mixer (192-wide query / key heads, 128-wide values) in bf16 on CUDA against the
+    same module in fp32 on the CPU; the attention goes to this library's kernels, not to the flash-attn fallback."""
+    from types import SimpleNamespace
+
+    from torchturbo_b200.models.modules.mixers import MixerContext, MLAttention
+    from torchturbo_b200.ops.providers import b200_attention as BA
+
+    cfg = SimpleNamespace(hidden_size=256, num_attention_heads=4, q_lora_rank=64, kv_lora_rank=64, qk_nope_head_dim=128,
+                          qk_rope_head_dim=64, v_head_dim=128, rms_norm_eps=1e-6, rope_interleave=True)
+    torch.manual_seed(0)
+    ref = MLAttention(cfg, 0).float()
+    with torch.no_grad():
+        for p in ref.parameters():
+            p.copy_(p.bfloat16().float())
+    dev = MLAttention(cfg, 0).float()
+    dev.load_state_dict(ref.state_dict())
+    dev = dev.cuda().bfloat16()
+    T = 300
+    x = (torch.randn(T, 256) * 0.5).bfloat16()
+    cu = torch.tensor([0, 130, 300], dtype=torch.int32)
+    pos = torch.cat((torch.arange(130), torch.arange(170))).float()
+    ang = pos[:, None] * (10000.0 ** (-torch.arange(32).float() / 32))[None]
+    ctx_c = MixerContext(cos=ang.cos(), sin=ang.sin(), cu_seqlens=cu, max_seqlen=170)
+    ctx_g = MixerContext(cos=ang.cos().cuda(), sin=ang.sin().cuda(), cu_seqlens=cu, max_seqlen=170)
+    xc = x.float().requires_grad_(True)
+    want = ref(xc, ctx_c)
+    g = torch.randn_like(want)
+    want.backward(g)
+    fallback = []
+    orig = BA._LIB_FALLBACK
+    BA._LIB_FALLBACK = lambda *a, **kw: fallback.append(1) or orig(*a, **kw)
+    try:
+        xg = x.cuda().requires_grad_(True)
+        got = dev(xg, ctx_g)
+        got.backward(g.cuda().bfloat16())
+    finally:
+        BA._LIB_FALLBACK = orig
+    torch.cuda.synchronize()
+    assert not fallback and K.attn_status() == (0, 0)
+    _close(got.cpu(), want, atol=3e-2)
+    _close(xg.grad.cpu(), xc.grad, atol=5e-2)
+    for (n, a), b in zip(dev.named_parameters(), ref.parameters()):
+        assert (a.grad.float().cpu() - b.grad).abs().max() <= 5e-2 * max(1.0, float(b.grad.abs().max())), n
