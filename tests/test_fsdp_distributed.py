@@ -182,3 +182,41 @@ def test_merged_units_with_expert_units_sharded_over_edp():
     a = torch.load("/tmp/tt_merged_0_1_1_ep2_w4.pt")
     b = torch.load("/tmp/tt_merged_50000_1_1_ep2_w4.pt")
     assert torch.allclose(a, b, rtol=1e-5, atol=1e-6), (a, b)
+
+
+VLM = dict(model_type="qwen3_vl", vocab_size=512,
+           text_config=dict(num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                            intermediate_size=128, vocab_size=512, tie_word_embeddings=False),
+           vision_config=dict(depth=2, hidden_size=32, num_heads=4, intermediate_size=48, patch_size=2, temporal_patch_size=2,
+                              spatial_merge_size=2, out_hidden_size=64, num_position_embeddings=16, deepstack_visual_indexes=[0]),
+           image_token_id=500, vision_start_token_id=501)
+
+
+def _w_vlm(rank, world, sp):
+    """The vision-language family with its default plan (tower as one standalone unit, blocks listed for activation
+    checkpointing, squared-patch-count balancing) on two ranks, with and without sequence parallelism."""
+    from torchturbo_b200.data import SyntheticVLMDataset
+    from torchturbo_b200.engine import EngineConfig, TorchTurboEngine
+    from torchturbo_b200.engine.optimizers import OptimizerClassPlan
+    from torchturbo_b200.loops import train_step
+
+    eng = TorchTurboEngine(EngineConfig.from_dict({
+        "mixed_precision": "fp32", "activation_checkpointing": {"enabled": True},
+        "parallel_plan": {"sp_size": sp, "ep_size": 1, "plan": {"model.visual": {"vision_balance": {"mode": "patch_sq"}}}}}))
+    model = eng.build_model(None, load_weights=False, init_kwargs={"config": copy.deepcopy(VLM), "seed": 0})
+    tower = [p for n, p in model.named_parameters() if n.startswith("model.visual.")]
+    assert tower and all(hasattr(p, "_local_tensor") for p in tower), "the tower is one world-sharded unit"
+    opt = eng.prepare_optimizer(model, OptimizerClassPlan(torch.optim.AdamW, lr=1e-3))
+    ds = SyntheticVLMDataset(4, 64, 512, image_token_id=500, vision_start_token_id=501, min_images=1, max_images=2, min_side=8,
+                             max_side=16, patch=2, merge=2, seed=3)
+    losses = []
+    for i in range(2):
+        loss, gn = train_step(eng, model, opt, [ds[(rank // sp) * 2 + i]])
+        losses.append(float(loss))
+        assert torch.isfinite(torch.as_tensor(gn))
+    assert all(l == l for l in losses)
+
+
+@pytest.mark.parametrize("sp", [1, 2])
+def test_vision_language_family_trains_with_its_default_plan_on_two_ranks(sp):
+    run_distributed(_w_vlm, 2, sp)

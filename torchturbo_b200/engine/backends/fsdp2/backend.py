@@ -447,7 +447,11 @@ class FSDP2Backend(BaseBackend):
                 continue  # tied input/output embeddings must live in one unit: the root
             self._make_unit(mod, spec)
         # 2. every ModuleList child is a unit (small consecutive children share one), or stays replicated
-        lists = [[c for c in mod if any(True for _ in c.parameters()) and getattr(c, "_tt_unit", None) is None]
+        #    (not inside an explicit unit: a tower that is one standalone unit already owns its blocks' parameters)
+        owned = {id(sub) for fqn, _ in explicit for sub in model.get_submodule(fqn).modules()
+                 if getattr(model.get_submodule(fqn), "_tt_unit", None) is not None}
+        lists = [[c for c in mod if any(True for _ in c.parameters()) and getattr(c, "_tt_unit", None) is None
+                  and id(c) not in owned]
                  for _, mod in list(model.named_modules()) if isinstance(mod, nn.ModuleList)]
         replicate = self._resolve_replicate_layers([c for children in lists for c in children])
         for children in lists:

@@ -75,10 +75,23 @@ class GridVisionBalanceIO(BaseVisionBalanceIO):
         return args, kw
 
     def read_outputs(self, tower, output):
+        """A tower called with `return_deepstack=True` returns `(features, [per-level features, ...])`, all with one row
+        per merged patch: they travel as one stream, concatenated along the feature axis (one exchange, not one per
+        level)."""
+        if isinstance(output, tuple):
+            feats, deep = output
+            return {self.stream: torch.cat([feats, *deep], dim=-1) if len(deep) else feats}
         return {self.stream: output}
 
     def write_outputs(self, tower, output, streams):
-        return streams[self.stream]
+        x = streams[self.stream]
+        if isinstance(output, tuple):
+            feats, deep = output
+            if not len(deep):
+                return x, []
+            parts = x.split([feats.shape[-1]] + [d.shape[-1] for d in deep], dim=-1)
+            return parts[0].contiguous(), [p.contiguous() for p in parts[1:]]
+        return x
 
     def make_dummy(self, tower, like):
         m = self.merge
