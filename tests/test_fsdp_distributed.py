@@ -207,7 +207,8 @@ def _w_vlm(rank, world, sp):
     tower = [p for n, p in model.named_parameters() if n.startswith("model.visual.")]
     assert tower and all(hasattr(p, "_local_tensor") for p in tower), "the tower is one world-sharded unit"
     opt = eng.prepare_optimizer(model, OptimizerClassPlan(torch.optim.AdamW, lr=1e-3))
-    ds = SyntheticVLMDataset(4, 64, 512, image_token_id=500, vision_start_token_id=501, min_images=1, max_images=2, min_side=8,
+    # seed 3: the first row of rank 1 (sp=1) carries no image, so a rank without media and the sparse-pool path are covered
+    ds = SyntheticVLMDataset(4, 64, 512, image_token_id=500, vision_start_token_id=501, min_images=0, max_images=2, min_side=8,
                              max_side=16, patch=2, merge=2, seed=3)
     losses = []
     for i in range(2):

@@ -71,7 +71,7 @@ class KimiK25ForConditionalGenerationBase(nn.Module):
 
     def fuse_media(self, input_ids, pixel_values, grid_thw):
         emb = self.language_model.model.embed_tokens(input_ids)
-        if pixel_values is None:
+        if pixel_values is None or pixel_values.shape[0] == 0:        # no media in this rank's row
             v_in, grid = self.vision_tower.dummy_inputs(emb.device, emb.dtype)
             return emb + 0.0 * self.mm_projector(self.vision_tower(v_in, grid_thw=grid)).sum()
         # patches arrive as [L, 3, p, p]; the tower (and the balancer in front of it) works on flat rows

@@ -231,6 +231,11 @@ class VisionBalanceState:
         if not torch.is_grad_enabled() or self.world == 1:
             return None
         batch = self.io.read_inputs(module, args, kwargs)
+        # one element type on every rank: a rank without media feeds a dummy image that it builds itself, and the data
+        # loader's type need not be the tower's (the patch embedding casts to the parameter type anyway)
+        want = next((p.dtype for p in module.parameters()), batch.pixels.dtype)
+        if batch.pixels.is_floating_point() and batch.pixels.dtype != want:
+            batch = VisionBatch(batch.pixels.to(want), batch.grid_thw, batch.output_lengths)
         names = tuple(batch.output_lengths.keys())
         meta = self._gather_metadata(batch, names)
         pool = MediaPool.from_metadata(meta, names, self.mode)

@@ -138,7 +138,7 @@ class Qwen3_5ForConditionalGenerationBase(nn.Module):
         if not self.with_vision:
             return emb
         visual = self.model.visual
-        if pixel_values is None:
+        if pixel_values is None or pixel_values.shape[0] == 0:        # no media in this rank's row
             v_in, grid = visual.dummy_inputs(emb.device, emb.dtype)
             return emb + 0.0 * visual(v_in, grid_thw=grid).sum()
         feats = visual(pixel_values, grid_thw=image_grid_thw)

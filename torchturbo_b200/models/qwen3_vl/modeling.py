@@ -80,7 +80,7 @@ class _PatchEmbed(nn.Module):
 
     def forward(self, pixels: torch.Tensor) -> torch.Tensor:
         w = self.proj.weight
-        return ops.bias_act(ops.linear(pixels.reshape(pixels.shape[0], -1).to(w.dtype), w.reshape(w.shape[0], -1)), self.proj.bias)
+        return ops.bias_act(ops.linear(pixels.reshape(pixels.shape[0], w[0].numel()).to(w.dtype), w.reshape(w.shape[0], -1)), self.proj.bias)
 
 
 class _VisionAttention(nn.Module):
@@ -217,8 +217,10 @@ class VisionTower(nn.Module):
         return (out, deep) if return_deepstack else out
 
     def dummy_inputs(self, device, dtype):
-        m = self.config.spatial_merge_size
-        pin = self.patch_embed.proj.weight[0].numel()
+        # sizes from the configuration: reading the (sharded) projection weight here would start a collective of its own
+        c = self.config
+        m = c.spatial_merge_size
+        pin = c.in_channels * c.temporal_patch_size * c.patch_size ** 2
         return torch.zeros(m * m, pin, device=device, dtype=dtype), torch.tensor([[1, m, m]], device=device)
 
 
@@ -306,18 +308,27 @@ class Qwen3VLForConditionalGenerationBase(nn.Module):
         emb = self.model.language_model.embed_tokens(input_ids)
         visual = self.model.visual
         n_deep = len(visual.deepstack_visual_indexes)
-        if pixel_values is None:
+        def no_media(feats, deep):
+            """The tower ran on the dummy image.  Its outputs enter the graph where real features would, each DeepStack
+            level at its own decoder layer, multiplied by zero: a rank without media then meets the tower's gradient
+            at the same point of the backward pass as the ranks with media, so the FSDP collectives of all ranks
+            stay in one order."""
+            e = emb + 0.0 * feats.sum()
+            if not n_deep:
+                return e, None
+            dense = torch.stack([emb.new_zeros(emb.shape[-2:]) + 0.0 * d.sum() for d in deep])
+            return e, dense.unsqueeze(1) if emb.dim() == 3 else dense
+
+        if pixel_values is None or pixel_values.shape[0] == 0:        # no media in this rank's row
             v_in, grid = visual.dummy_inputs(emb.device, emb.dtype)
-            feats, deep = visual(v_in, grid_thw=grid, return_deepstack=True)
-            keep = feats.sum() + sum(d.sum() for d in deep)      # keeps the tower in the graph (FSDP hooks, balanced backward)
-            return emb + 0.0 * keep, None
+            return no_media(*visual(v_in, grid_thw=grid, return_deepstack=True))
         feats, deep = visual(pixel_values, grid_thw=image_grid_thw, return_deepstack=True)
         mask = (input_ids == self.config.image_token_id) | (input_ids == getattr(self.config, "video_token_id", -1))
         n = int(mask.sum())
         if n != feats.shape[0]:
             # dummy media on media-less batches produce features that no placeholder consumes
             if n == 0:
-                return emb + 0.0 * (feats.sum() + sum(d.sum() for d in deep)), None
+                return no_media(feats, deep)
             raise ValueError(f"{n} image placeholder tokens but {feats.shape[0]} image features")
         out = emb.masked_scatter(mask.unsqueeze(-1), feats.to(emb.dtype))
         if not n_deep:

@@ -308,7 +308,7 @@ class Qwen4ExpForConditionalGenerationBase(nn.Module):
     def fuse_media(self, input_ids, pixel_values, grid):
         emb = self.model.language_model.embed_tokens(input_ids)
         visual = self.model.visual
-        if pixel_values is None:
+        if pixel_values is None or pixel_values.shape[0] == 0:        # no media in this rank's row
             v_in, g = visual.dummy_inputs(emb.device, emb.dtype)
             return emb + 0.0 * visual(v_in, grid_thw=g).sum()
         feats = visual(pixel_values, grid_thw=grid)
