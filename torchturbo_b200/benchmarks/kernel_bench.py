@@ -141,7 +141,7 @@ def bench_elementwise():
 def profile_case(name: str) -> None:
     """One small, self-ending case per kernel for a profiler capture: inputs larger than L2 (126 MB) but well under
     a GB on the device, one warm-up launch and two more.  `python -m torchturbo_b200.benchmarks.kernel_bench
-    profile:<gemm|grouped|grouped_dw|attn_fwd|attn_bwd|delta_state|adamw|rmsnorm>`."""
+    profile:<gemm|grouped|grouped_dw|attn_fwd|attn_bwd|attn_mla|delta_state|adamw|rmsnorm>`."""
     dev = "cuda"
     g = torch.Generator(device=dev).manual_seed(0)
 
@@ -177,6 +177,17 @@ def profile_case(name: str) -> None:
             o = FlashAttnFn.apply(q, k, v, cu, 5192, True, D ** -0.5, False)
             if name == "attn_bwd":
                 o.backward(do)
+    elif name == "attn_mla":
+        # multi-head latent attention widths: forward, kv-major backward (dK / dV) and the query-major dQ pass
+        from ..ops.providers.b200_attention import FlashAttnFn
+
+        T, H = 8192, 16
+        q, k, v = rnd(T, H, 192).requires_grad_(True), rnd(T, H, 192).requires_grad_(True), rnd(T, H, 128).requires_grad_(True)
+        cu = torch.tensor([0, 3000, T], dtype=torch.int32)
+        do = rnd(T, H, 128)
+
+        def fn():
+            FlashAttnFn.apply(q, k, v, cu, 5192, True, 192 ** -0.5, False).backward(do)
     elif name == "delta_state":
         # recurrence over 64 chunks (4096 tokens) of 32 heads: 134 MB of states written, 67 MB of U read and X written
         H, NC = 32, 64
