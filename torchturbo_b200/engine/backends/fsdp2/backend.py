@@ -17,6 +17,8 @@ use `torch.distributed.fsdp.fully_shard` with bf16 parameters, fp32 reduction an
 """
 from __future__ import annotations
 
+import math
+
 import contextlib
 import os
 import functools
@@ -599,9 +601,76 @@ class FSDP2Backend(BaseBackend):
                 if b.dtype.is_floating_point and "inv_freq" not in name:
                     b.zero_()
 
+    def _init_adapters(self, model: nn.Module) -> None:
+        """LoRA / DoRA adapters of a materialised model start as a no-op: A is uniform in +-1/sqrt(fan_in) (drawn at its
+        global shape from a generator seeded by its name, then cut to this rank's shard, like the base parameters), B is
+        zero, a DoRA magnitude is the row norm of the weight it scales.  Runs after the base weights are in place, for
+        loaded and for freshly initialised models alike (the base initialiser knows nothing about adapters)."""
+        if not getattr(model, "peft_config", None):
+            return
+        import zlib
+
+        from ...peft.lora import LoRALinear, is_adapter_param
+
+        seed = int(getattr(self, "_init_seed", 0))
+        with torch.no_grad():
+            for name, p in model.named_parameters():
+                if not is_adapter_param(name):
+                    continue
+                lp = p._local_tensor if hasattr(p, "_local_tensor") else p
+                parts = name.split(".")
+                if "lora_B" in parts:
+                    lp.zero_()
+                    continue
+                if "lora_magnitude_vector" in parts:
+                    lp.fill_(1.0)
+                    continue
+                gen = torch.Generator(device=lp.device)
+                gen.manual_seed(seed * 1000003 + zlib.crc32(name.encode()))
+                shape = list(p.shape)
+                is_expert = p.dim() == 3 and self.ep_size > 1          # grouped factors hold the local experts only
+                if is_expert:
+                    shape[0] *= self.ep_size
+                bound = 1.0 / math.sqrt(shape[-1])
+                full = torch.empty(shape, dtype=torch.float32, device=lp.device).uniform_(-bound, bound, generator=gen)
+                if is_expert:
+                    full = full[self.ep_rank * p.shape[0]:(self.ep_rank + 1) * p.shape[0]]
+                if hasattr(p, "_local_tensor"):
+                    from torch.distributed.tensor import Shard
+
+                    for mesh_dim, pl in enumerate(p.placements):
+                        if isinstance(pl, Shard):
+                            n, r = p.device_mesh.size(mesh_dim), p.device_mesh.get_local_rank(mesh_dim)
+                            chunks = torch.chunk(full, n, dim=pl.dim)
+                            full = chunks[r] if r < len(chunks) else full.narrow(pl.dim, 0, 0)
+                    lp.zero_()
+                    lp[tuple(slice(0, s_) for s_ in full.shape)].copy_(full)
+                else:
+                    lp.copy_(full)
+            for m in model.modules():
+                if isinstance(m, LoRALinear) and m.lora_magnitude_vector is not None:
+                    mag = m.lora_magnitude_vector[m.cfg.adapter_name].weight
+                    norms = m.delta_free_weight().float().norm(dim=1)          # gathers a sharded weight: all ranks take part
+                    if hasattr(mag, "_local_tensor"):
+                        from torch.distributed.tensor import distribute_tensor
+
+                        mag._local_tensor.copy_(distribute_tensor(norms.to(mag.dtype), mag.device_mesh, mag.placements)._local_tensor)
+                    else:
+                        mag.copy_(norms.to(mag.dtype))
+
+    def reshard_all(self, model: nn.Module) -> None:
+        """Every FSDP unit of `model` back to its sharded parameters.  A unit that is kept gathered after a forward
+        (the resident tail, every unit after a forward without gradients) shows plain, unsharded tensors under the names
+        of its parameters; state dictionaries must be built from the sharded ones."""
+        for m in model.modules():
+            if getattr(m, "_tt_unit", None) == "fsdp" and hasattr(m, "reshard"):
+                m.reshard()
+
     def finalize_model_load(self, model: nn.Module) -> None:
-        """After weights are in place: single-rank units switch to bf16 parameters (their fp32 values become
-        the optimizer's master copy), replicated parameters get their gradient all-reduce hook."""
+        """After weights are in place: adapters get their initial values, single-rank units switch to bf16 parameters
+        (their fp32 values become the optimizer's master copy), replicated parameters get their gradient all-reduce
+        hook."""
+        self._init_adapters(model)
         if self.config.mixed_precision is MixedPrecisionPolicy.BF16:
             owner = self._unit_owned_params(model)
             with torch.no_grad():

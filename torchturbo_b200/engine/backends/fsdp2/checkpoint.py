@@ -25,6 +25,7 @@ import torch.nn as nn
 
 from ....logging import get_logger
 from ...checkpoint.layout import DCP_COMMIT, HF_INDEX, dcp_status, fsync_dir, save_json
+from ...peft.lora import is_adapter_param, lora_merge_functions, strip_peft_name
 from ..base import BaseCheckpointManager
 
 logger = get_logger(__name__)
@@ -112,9 +113,16 @@ class FSDP2CheckpointManager(BaseCheckpointManager):
             window.clear()
             in_flight = 0
 
+        peft = bool(getattr(model, "peft_config", None))
         for name, t, dup in self._named_state(model):
             if dup:
                 continue
+            if peft:
+                # adapters keep their initial values (the base checkpoint has none); wrapped base parameters are read
+                # under the names of the unwrapped model
+                if is_adapter_param(name):
+                    continue
+                name = strip_peft_name(name)
             recipe = conv.load_recipe(name)
             if recipe is None:
                 continue  # tied alias omitted by the checkpoint
@@ -184,6 +192,7 @@ class FSDP2CheckpointManager(BaseCheckpointManager):
     def save_hf(self, model: nn.Module, path: str, *, source_path: str | None = None, dtype=torch.bfloat16) -> None:
         from safetensors.torch import save_file
 
+        self.backend.reshard_all(model)
         ctx = self.backend.get_parallel_context()
         # with the source checkpoint at hand the export mirrors its expert format (fused 3-D tensors or per expert)
         has_src = bool(source_path) and os.path.isdir(source_path) and (
@@ -226,9 +235,18 @@ class FSDP2CheckpointManager(BaseCheckpointManager):
         # per-EP-rank pieces of fused expert tensors go to files of their own: rank 0 joins them and removes the files
         shards, pieces = _Shards(f"model-rank{rank:05d}"), _Shards(f"ep-pieces-rank{rank:05d}")
         owner_rr = 0
+        peft = bool(getattr(model, "peft_config", None))
+        merges = lora_merge_functions(model) if peft else {}
         for name, t, dup in self._named_state(model):
             if dup:
                 continue
+            merge = merges.get(name)
+            if peft:
+                # the export is a plain checkpoint of the base architecture: adapters are merged into the weights they
+                # wrap and not written themselves (engine/backends/fsdp2/checkpoint/weight_saver.py:391-409 of the reference)
+                if is_adapter_param(name):
+                    continue
+                name = strip_peft_name(name)
             is_expert = conv.is_expert_param(name)
             full = t.full_tensor() if _is_dtensor(t) else t
             master = getattr(t, "_tt_master", None)
@@ -240,9 +258,11 @@ class FSDP2CheckpointManager(BaseCheckpointManager):
             else:
                 writer = (rank == owner_rr % world)
                 owner_rr += 1
+            if merge is not None:
+                full = merge(full.detach())         # gathers the adapter factors: every rank takes part
             if not writer:
                 continue
-            if lora is not None and name in lora:
+            if merge is None and lora is not None and name in lora:
                 full = full.float() + lora[name].to(full.device).float()
             for hf_name, ht in conv.to_hf_tensors(name, full.detach()).items():
                 ht = ht.to(dtype if ht.dtype.is_floating_point else ht.dtype).cpu()
@@ -337,6 +357,7 @@ class FSDP2CheckpointManager(BaseCheckpointManager):
 
         # nested under "model" like the reference's DCP layout (keys `model.<fqn>[::ep<r>]`,
         # engine/backends/fsdp2/checkpoint/dcp.py:237-268 of the reference)
+        self.backend.reshard_all(model)
         dcp.save({"model": self._model_state(model)}, checkpoint_id=path)
 
     def load_native_model(self, model: nn.Module, path: str) -> None:
@@ -344,6 +365,7 @@ class FSDP2CheckpointManager(BaseCheckpointManager):
 
         if dcp_status(path) != "complete":
             raise RuntimeError(f"{path} is not a complete native checkpoint")
+        self.backend.reshard_all(model)
         state = self._model_state(model)
         self._check_ep_keys(path, state)
         dcp.load({"model": state}, checkpoint_id=path)  # in-place into the model's tensors; extra saved keys are ignored
@@ -367,6 +389,7 @@ class FSDP2CheckpointManager(BaseCheckpointManager):
 
     # -- optimizer -------------------------------------------------------------------------------------
     def _flatten_optimizer(self, model: nn.Module, optimizer) -> tuple[dict[str, torch.Tensor], dict[str, Any]]:
+        self.backend.reshard_all(model)
         from ...optimizers import OptimizersContainer
 
         names = {id(p): n for n, p in model.named_parameters()}

@@ -232,6 +232,47 @@ def apply_peft(model: nn.Module, peft_config) -> nn.Module:
     return model
 
 
+_ADAPTER_SEGMENTS = ("lora_A", "lora_B", "lora_magnitude_vector", "lora1", "lora2")
+
+
+def strip_peft_name(name: str) -> str:
+    """Parameter FQN of a wrapped model -> the name the base model uses (`x.base_layer.weight` -> `x.weight`)."""
+    return name.replace(".base_layer.", ".")
+
+
+def is_adapter_param(name: str) -> bool:
+    parts = name.split(".")
+    return any(seg in parts for seg in _ADAPTER_SEGMENTS)
+
+
+def _full(t: torch.Tensor) -> torch.Tensor:
+    return t.full_tensor() if hasattr(t, "full_tensor") else t
+
+
+def lora_merge_functions(model: nn.Module) -> dict[str, Any]:
+    """{FQN of a wrapped base parameter: fn(full base tensor) -> merged tensor} for export.  The functions gather the
+    adapter factors (`full_tensor()` on sharded ones), so every rank has to call them in the same order."""
+    out: dict[str, Any] = {}
+    for n, m in model.named_modules():
+        if isinstance(m, LoRALinear):
+            def merge(w, m=m):
+                name = m.cfg.adapter_name
+                a, b = _full(m.lora_A[name].weight).float(), _full(m.lora_B[name].weight).float()
+                eff = w.float() + (b.to(w.device) @ a.to(w.device)) * m.cfg.scaling
+                if m.lora_magnitude_vector is not None:
+                    mag = _full(m.lora_magnitude_vector[name].weight).float().to(w.device)
+                    eff = eff * (mag.view(-1, 1) / eff.norm(dim=1, keepdim=True).clamp_min(1e-12))
+                return eff
+            out[f"{n}.base_layer.weight"] = merge
+        elif isinstance(m, GroupedMLPLoRA):
+            for key, lo in (("weight1", m.lora1), ("weight2", m.lora2)):
+                def merge(w, lo=lo):
+                    a, b = _full(lo.lora_A).float().to(w.device), _full(lo.lora_B).float().to(w.device)
+                    return w.float() + torch.bmm(a, b).view(-1, lo.cols) * lo.cfg.scaling
+                out[f"{n}.base_layer.{key}"] = merge
+    return out
+
+
 def build_lora_delta_map(model: nn.Module) -> dict[str, torch.Tensor]:
     """{base parameter FQN (without wrapper segments): merged delta} for export-time merging."""
     out: dict[str, torch.Tensor] = {}
