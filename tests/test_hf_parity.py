@@ -48,7 +48,9 @@ def _hf(kind):
                                    shared_expert_intermediate_size=48, num_experts=8, num_experts_per_tok=2)
         cls = transformers.Qwen3_5MoeForCausalLM
     elif kind == "glm_moe_dsa":
-        cfg = CONFIG_MAPPING[kind](**MLA, index_n_heads=2, index_head_dim=16, index_topk=8)
+        # eight index heads: with two, a quarter of all index scores are exactly zero after the ReLU, and among tied keys
+        # `torch.topk` (transformers) and this package's stable order (the same under any slicing of the queries) may differ
+        cfg = CONFIG_MAPPING[kind](**MLA, index_n_heads=8, index_head_dim=16, index_topk=8)
         cls = transformers.GlmMoeDsaForCausalLM
     else:
         raise KeyError(kind)

@@ -598,8 +598,13 @@ class FSDP2Backend(BaseBackend):
                     lp.copy_(full)
                 del full
             for name, b in model.named_buffers():
-                if b.dtype.is_floating_point and "inv_freq" not in name:
-                    b.zero_()
+                if "inv_freq" in name:
+                    continue
+                b.zero_()                      # integer tables too: uninitialised storage must never be used as an index
+            for m in model.modules():          # buffers with content of their own (seeded routing tables, ...)
+                hook = getattr(m, "reset_buffers_after_materialize", None)
+                if callable(hook):
+                    hook()
 
     def _init_adapters(self, model: nn.Module) -> None:
         """LoRA / DoRA adapters of a materialised model start as a no-op: A is uniform in +-1/sqrt(fan_in) (drawn at its

@@ -372,13 +372,26 @@ class DeepseekV4MoE(MoELayer):
 
     def __init__(self, config: MoELayerConfig, hash_layer: bool = False, **kw):
         super().__init__(config, **kw)
+        self.hash_layer = hash_layer
         if hash_layer:
-            g = torch.Generator().manual_seed(1234)
+            del self.router.tid2eid                                     # plain attribute placeholder -> buffer
+            self.router.register_buffer("tid2eid", self._hash_table(config), persistent=True)
+
+    @staticmethod
+    def _hash_table(config: MoELayerConfig) -> torch.Tensor:
+        """Seeded token-id -> expert table for models built without a checkpoint (a checkpoint brings its own)."""
+        g = torch.Generator(device="cpu").manual_seed(1234)
+        with torch.device("cpu"):
             table = torch.stack([torch.randperm(config.num_moe_experts, generator=g)[: config.moe_router_topk]
                                  for _ in range(config.vocab_size)]) if config.vocab_size <= 4096 else \
                 torch.randint(0, config.num_moe_experts, (config.vocab_size, config.moe_router_topk), generator=g)
-            del self.router.tid2eid                                     # plain attribute placeholder -> buffer
-            self.router.register_buffer("tid2eid", table.to(torch.int32), persistent=True)
+        return table.to(torch.int32)
+
+    def reset_buffers_after_materialize(self) -> None:
+        """A model constructed on the meta device gets its table here, once the buffer has real storage."""
+        if self.hash_layer:
+            with torch.no_grad():
+                self.router.tid2eid.copy_(self._hash_table(self.config).to(self.router.tid2eid.device))
 
     def forward(self, hidden_states, input_ids=None):
         return super().forward(hidden_states, input_ids)[0]

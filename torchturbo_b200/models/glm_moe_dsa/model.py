@@ -84,14 +84,18 @@ class DsaIndexer(nn.Module):
 
 
 class DsaAttention(MLAttention):
-    """MLA whose softmax runs over the indexer's selection.  Layers hand the selection on through
-    `ctx.extras["dsa_topk"]`."""
+    """MLA whose softmax runs over the indexer's selection.  A layer with an indexer files its selection under its own
+    layer index in `ctx.extras["dsa_topk"]`; a shared layer reads the entry of the nearest earlier layer with an
+    indexer.  Keyed by layer, the entries are still the right ones when activation checkpointing replays a layer in
+    the backward pass, long after later layers have filed theirs."""
 
     def __init__(self, config: Any, layer_idx: int, dtype=None):
         super().__init__(config, layer_idx, dtype)
         kinds = config.indexer_types
         self.shared = (kinds[layer_idx] if layer_idx < len(kinds) else "full") == "shared"
         self.indexer = None if self.shared else DsaIndexer(config, dtype)
+        self.source_layer = layer_idx if not self.shared else next(
+            (i for i in range(min(layer_idx, len(kinds)) - 1, -1, -1) if kinds[i] != "shared"), None)
 
     def forward(self, x, ctx: MixerContext):
         T = x.shape[0]
@@ -109,8 +113,8 @@ class DsaAttention(MLAttention):
                 full = sel.new_empty(ctx.sp_size * T, sel.shape[1])
                 dist.all_gather_into_tensor(full, sel.contiguous(), group=ctx.sp_group)
                 sel = full
-            ctx.extras["dsa_topk"] = sel
-        sel = ctx.extras.get("dsa_topk")
+            ctx.extras.setdefault("dsa_topk", {})[self.layer_idx] = sel
+        sel = ctx.extras.get("dsa_topk", {}).get(self.source_layer)
         if sel is None:
             raise ValueError("a shared sparse-attention layer needs the selection of an earlier full layer")
         q = q.view(T, self.n_heads, self.d_qk)

@@ -48,7 +48,10 @@ def lightning_indexer_ref(q, k, weights, topk, cu_seqlens=None, scale=None, q_of
             pos_k = torch.arange(a, e, device=q.device)[None, :]
             sc = sc.masked_fill(pos_k > pos_q, -float("inf"))
             kk = min(topk, e - a)
-            val, idx = sc.topk(kk, dim=-1)
+            # a stable sort, not `topk`: ReLU makes exact ties common, and which of two tied keys `topk` returns depends on
+            # the shape of the score block, i.e. on how the queries were sliced (sequence parallelism, chunking)
+            val, idx = sc.sort(dim=-1, descending=True, stable=True)
+            val, idx = val[:, :kk], idx[:, :kk]
             idx = (idx + a).to(torch.int32).masked_fill(~torch.isfinite(val), -1)
             out[s - q_offset:e - q_offset, :kk] = idx
     return out
