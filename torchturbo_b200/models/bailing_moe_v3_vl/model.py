@@ -65,6 +65,16 @@ class BailingVLModel(BailingModel):
                                     cu_seq_lens_q=cu_seq_lens_q, max_length_q=max_length_q, return_context=True)
 
 
+class _Projector(nn.Sequential):
+    """`Linear - GELU - Linear` under the checkpoint's names (`linear_proj.0`, `linear_proj.2`), evaluated with the fused
+    bias + activation operator.  It is called as a module, never read parameter by parameter from outside: as an FSDP
+    unit of its own its weights are only gathered inside its forward."""
+
+    def forward(self, feats):
+        a, b = self[0], self[2]
+        return ops.bias_act(ops.linear(ops.bias_act(ops.linear(feats, a.weight), a.bias, "gelu"), b.weight), b.bias)
+
+
 class BailingMoeV3VLForConditionalGenerationBase(nn.Module):
     def __init__(self, config: Any):
         super().__init__()
@@ -74,8 +84,8 @@ class BailingMoeV3VLForConditionalGenerationBase(nn.Module):
         self.model = BailingVLModel(config, dtype)
         # `disable_merger_proj`: the tower hands over the joined 2x2 patch rows and this projector does all the mapping
         vin = vc.hidden_size * vc.spatial_merge_size ** 2 if getattr(vc, "disable_merger_proj", False) else vc.out_hidden_size
-        self.linear_proj = nn.Sequential(nn.Linear(vin, tc.hidden_size, bias=True, dtype=dtype), nn.GELU(),
-                                         nn.Linear(tc.hidden_size, tc.hidden_size, bias=True, dtype=dtype))
+        self.linear_proj = _Projector(nn.Linear(vin, tc.hidden_size, bias=True, dtype=dtype), nn.GELU(),
+                                      nn.Linear(tc.hidden_size, tc.hidden_size, bias=True, dtype=dtype))
         self.lm_head = LMHead(tc.hidden_size, tc.vocab_size, bias=False, dtype=dtype)
         n = int(getattr(tc, "num_nextn_predict_layers", 0) or 0)
         self.mtp = nn.ModuleList([self.model.make_nextn_layer(tc.num_hidden_layers + i, dtype) for i in range(n)]) if n else None
@@ -91,8 +101,7 @@ class BailingMoeV3VLForConditionalGenerationBase(nn.Module):
         return {"lm_head.weight": "model.embed_tokens.weight"} if getattr(self.config, "tie_word_embeddings", False) else {}
 
     def project(self, feats):
-        a, b = self.linear_proj[0], self.linear_proj[2]
-        return ops.bias_act(ops.linear(ops.bias_act(ops.linear(feats, a.weight), a.bias, "gelu"), b.weight), b.bias)
+        return self.linear_proj(feats)
 
     def fuse_media(self, input_ids, pixel_values, grid):
         emb = self.model.embed_tokens(input_ids)
