@@ -119,3 +119,47 @@ def test_expert_parallel_lora_exports_one_merged_checkpoint(tmp_path):
 
 def test_fsdp_sharded_dora_exports_one_merged_checkpoint(tmp_path):
     run_distributed(_w_finetune, 2, str(tmp_path), 1, dict(PEFT, use_dora=True, target_parameters=[]), DENSE, timeout=600)
+
+
+def _w_resume(rank, world, root):
+    from torchturbo_b200.data import PackedCollator, SyntheticPackedDataset
+    from torchturbo_b200.engine import EngineConfig, TorchTurboEngine
+    from torchturbo_b200.engine.optimizers import OptimizerClassPlan
+    from torchturbo_b200.loops import train_step
+
+    def engine():
+        return TorchTurboEngine(EngineConfig.from_dict({"mixed_precision": "fp32", "parallel_plan": {"sp_size": 1, "ep_size": 2},
+                                                        "activation_checkpointing": {"enabled": False},
+                                                        "checkpoint": {"hf_export": "every"}}))
+
+    eng = engine()
+    base = eng.build_model(None, load_weights=False, init_kwargs={"config": dict(MOE), "seed": 0})
+    eng.save_model(base, os.path.join(root, "base", "checkpoint-0"), final=True)
+    src = os.path.join(root, "base", "checkpoint-0", "huggingface")
+    b = PackedCollator()([SyntheticPackedDataset(2, 64, 512, num_docs=3, seed=5)[0]])
+    eng = engine()
+    model = eng.build_model(src, peft_config=dict(PEFT))
+    opt = eng.prepare_optimizer(model, OptimizerClassPlan(torch.optim.AdamW, lr=1e-2))
+    for _ in range(3):
+        train_step(eng, model, opt, [b])
+    ck = os.path.join(root, "tuned", "checkpoint-3")
+    eng.save_model(model, ck, final=False)
+    eng.save_optimizer_and_scheduler(model, opt, None, ck)
+    model.eval()
+    want = _logits(model, b)
+    model.train()
+    step4 = train_step(eng, model, opt, [b])
+    eng2 = engine()
+    again = eng2.build_model(src, peft_config=dict(PEFT))
+    opt2 = eng2.prepare_optimizer(again, OptimizerClassPlan(torch.optim.AdamW, lr=1e-2))
+    eng2.load_from_checkpoint(again, ck)
+    eng2.load_optimizer_and_scheduler(again, opt2, None, ck)
+    again.eval()
+    assert torch.equal(_logits(again, b), want), "adapters and wrapped base weights come back from the sharded checkpoint"
+    again.train()
+    step4b = train_step(eng2, again, opt2, [b])
+    assert float(step4[0]) == float(step4b[0]) and abs(float(step4[1]) - float(step4b[1])) < 1e-6     # AdamW moments too
+
+
+def test_adapter_training_resumes_exactly_from_a_sharded_checkpoint(tmp_path):
+    run_distributed(_w_resume, 2, str(tmp_path), timeout=600)
