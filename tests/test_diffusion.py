@@ -75,3 +75,40 @@ def test_diffusion_loss_single_and_sp(tmp_path):
     run_distributed(_loss_worker, 2, 2, 0.0, str(tmp_path), "c")
     for r in range(2):
         assert abs(torch.load(tmp_path / f"c_r{r}.pt")[0] - l1) < 1e-4      # SP=2 reproduces the SP=1 mean
+
+
+def test_block_diffusion_sampling_fills_blocks_in_order_and_stops_at_eos():
+    """`generate`: every new block starts masked and ends committed, earlier blocks are frozen context, greedy sampling is
+    repeatable, the result is cut at the first end-of-sequence token and never longer than asked."""
+    from torchturbo_b200.models.llada2_moe.generate import generate
+    from torchturbo_b200.models.registry import get_model
+
+    cls = get_model("llada2_moe")
+    torch.manual_seed(0)
+    model = cls(cls.config_class(**{k: v for k, v in LLADA.items() if k != "model_type"}, torch_dtype="float32")).eval()
+    prompt = torch.randint(2, 128, (11,))
+    seen = []
+    orig = model.forward
+
+    def spy(*a, **kw):
+        seen.append(kw["input_ids"][0].clone())
+        return orig(*a, **kw)
+
+    model.forward = spy
+    out = generate(model, prompt, max_new_tokens=20, block_size=8, steps=4)
+    model.forward = orig
+    assert out.shape == (31,) and torch.equal(out[:11], prompt) and not bool((out == 1).any())      # no mask token left
+    # three blocks of 8 (the last one cut to 4): the first call of a block sees it fully masked behind frozen context
+    firsts = [s for s in seen if bool((s[-8:] == 1).all())]
+    assert [int(s.numel()) for s in firsts] == [19, 27, 35]
+    assert torch.equal(firsts[1][:19], out[:19]) and torch.equal(firsts[2][:27], out[:27])
+    # inside a block the number of masked positions only goes down, by the per-step quota (8 -> 6 -> 4 -> 2 -> 0)
+    first_block = [int((s[11:19] == 1).sum()) for s in seen if s.numel() == 19]
+    assert first_block == [8, 6, 4, 2]
+    assert torch.equal(generate(model, prompt, max_new_tokens=20, block_size=8, steps=4), out)       # greedy is repeatable
+    eos = int(out[14])
+    cut = generate(model, prompt, max_new_tokens=20, block_size=8, steps=4, eos_id=eos)
+    assert cut.numel() <= 19 and int(cut[-1]) == eos and int((cut[11:] == eos).sum()) == 1
+    torch.manual_seed(1)
+    sampled = generate(model, prompt, max_new_tokens=8, block_size=8, steps=2, temperature=1.0)
+    assert sampled.shape == (19,) and not bool((sampled == 1).any())
