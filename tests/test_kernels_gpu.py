@@ -462,17 +462,29 @@ def test_deterministic_attention_backward_is_bit_reproducible_and_matches_the_de
     for got, fast_g, want in zip(runs[0], fast, (qf.grad, kf.grad, vf.grad)):
         _close(got, want, atol=3e-2)
         _close(got, fast_g.float(), atol=3e-2)
-    # grouped-query heads through the operator with the global switch on
+    # grouped-query heads (one CTA per kv head walks its four query heads): bit-reproducible too, through the operator
+    # with the global switch on
     from torchturbo_b200.ops.providers import b200_attention as BA
 
-    q2, k2, v2 = (_rand(T, h, D).requires_grad_(True) for h in (8, 2, 2))
+    q2, k2, v2 = _rand(T, 8, D), _rand(T, 2, D), _rand(T, 2, D)
+    g2 = _rand(T, 8, D)
+    grads = []
     torch.use_deterministic_algorithms(True)
     try:
-        BA.B200Attention()(q2, k2, v2, cu, 600, causal=True, scale=D ** -0.5).backward(_rand(T, 8, D))
+        for _ in range(3):
+            leaves = [t.clone().requires_grad_(True) for t in (q2, k2, v2)]
+            BA.B200Attention()(*leaves, cu, 600, causal=True, scale=D ** -0.5).backward(g2)
+            grads.append([t.grad for t in leaves])
     finally:
         torch.use_deterministic_algorithms(False)
     torch.cuda.synchronize()
-    assert K.attn_status() == (0, 0) and bool(torch.isfinite(q2.grad).all())
+    assert K.attn_status() == (0, 0)
+    for r in grads[1:]:
+        assert all(torch.equal(a, b) for a, b in zip(r, grads[0]))
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q2, k2, v2))
+    attention_ref(qf, kf, vf, cu, causal=True, scale=D ** -0.5).backward(g2.float())
+    for got, want in zip(grads[0], (qf.grad, kf.grad, vf.grad)):
+        _close(got, want, atol=3e-2)
 
 
 def test_narrow_heads_run_on_the_tcgen05_kernel_with_zero_padding(K):

@@ -48,6 +48,7 @@ struct AttnBwdParams {
   long long T;
   float scale;
   int causal;
+  int group_loop;   // 1: one CTA per kv head loops over the query heads of its group (no atomics on dK / dV)
 };
 
 template <int DQK, bool WITH_DQ>
@@ -126,16 +127,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   float* s_delta = reinterpret_cast<float*>(smem + BwdSmem::DELTA);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = blockIdx.x, hq = blockIdx.y;
+  const int tile = blockIdx.x;
   const int G = p.Hq / p.Hk;
-  const int hk = hq / G;
+  // default: one CTA per query head (parallel, dK / dV of a group summed with atomics); group loop: one CTA per kv head
+  // walks the query heads of its group one after the other and owns dK / dV alone
+  const int hk = p.group_loop ? static_cast<int>(blockIdx.y) : static_cast<int>(blockIdx.y) / G;
+  const int hq = p.group_loop ? hk * G : static_cast<int>(blockIdx.y);
   const int kv0 = p.kv_tiles[tile * 3 + 0];
   const int ds = p.kv_tiles[tile * 3 + 1];
   const int de = p.kv_tiles[tile * 3 + 2];
   // query tiles (64 rows, aligned to the document start) that can see this kv tile
   const int q_first = p.causal ? ds + ((kv0 - ds) / BW_Q) * BW_Q : ds;
   const int n_qt = (de - q_first + BW_Q - 1) / BW_Q;
-  const int n_it = n_qt;
+  const int n_it = p.group_loop ? n_qt * G : n_qt;
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
@@ -164,8 +168,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t tm_DV = tmem_base + (WITH_DQ ? 256 : 128);    // 128 cols
   const uint32_t tm_DK = tmem_base + (WITH_DQ ? 384 : 256);    // DQK cols
 
-  auto it_head = [&](int) { return hq; };
-  auto it_q0 = [&](int it) { return q_first + it * BW_Q; };
+  auto it_head = [&](int it) { return p.group_loop ? hq + it / n_qt : hq; };
+  auto it_q0 = [&](int it) { return q_first + (p.group_loop ? it % n_qt : it) * BW_Q; };
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -279,11 +283,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int q0s = it_q0(it);
       if (tid < 64) {
         const int q = q0s + tid;
-        return (q < de) ? -p.lse[static_cast<long long>(hq) * p.T + q] * 1.4426950408889634f : -INFINITY;
+        return (q < de) ? -p.lse[static_cast<long long>(it_head(it)) * p.T + q] * 1.4426950408889634f : -INFINITY;
       }
       if (tid < 128) {
         const int q = q0s + tid - 64;
-        return (q < de) ? -p.delta[static_cast<long long>(hq) * p.T + q] * p.scale : 0.f;
+        return (q < de) ? -p.delta[static_cast<long long>(it_head(it)) * p.T + q] * p.scale : 0.f;
       }
       return 0.f;
     };
@@ -376,7 +380,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             for (int i = 0; i < 32; ++i) v[i] = 0u;
           }
           if (kv_ok) {
-            if (G == 1) {
+            if (G == 1 || p.group_loop) {
 #pragma unroll
               for (int i = 0; i < 32; i += 8) {
                 uint4 w;
@@ -488,7 +492,7 @@ static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const 
   using Smem = ttb::BwdSmem<DQK, WITH_DQ>;
   const cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(attn_bwd_kernel<DQK, WITH_DQ>), Smem::TOTAL, smem_done);
   if (e != cudaSuccess) return 300 + static_cast<int>(e);
-  dim3 grid(n_tiles, p.Hq);
+  dim3 grid(n_tiles, p.group_loop ? p.Hk : p.Hq);
   attn_bwd_kernel<DQK, WITH_DQ><<<grid, WITH_DQ ? 448 : 320, Smem::TOTAL, stream>>>(tq, tdo, tk, tv, tdq, p);
   return 0;
 }
@@ -496,13 +500,16 @@ static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const 
 // q: [T, Hq*D] contiguous rows; dout, out: [T, Hq*128] contiguous rows; k: [T, Hk*D] (ldk); v: [T, Hk*128] (ldv, may be
 // strided); D = 128 or 192.  delta fp32 [Hq*T] scratch (left filled with rowsum(dO * O) for the query-major dQ pass).
 // with_dq != 0 (D = 128 only): dQ too, reduced into dq_acc (fp32 [T*Hq*128], zero-initialised) and cast to dq;
-// with_dq == 0: dK and dV only (dq_acc and dq unused).  dk: [T, Hk, D], dv: [T, Hk, 128]; with Hq > Hk the fp32
+// with_dq == 0: dK and dV only (dq_acc and dq unused); with_dq == 2: the same with one CTA per kv head looping over the
+// query heads of its group, so that dK / dV are written once and without atomics (no accumulators needed).  dk: [T, Hk, D], dv: [T, Hk, 128]; with Hq > Hk the fp32
 // accumulators dk_acc / dv_acc (zero-initialised, same shapes) are required.
 TTB_EXPORT int ttb_attn_bwd(const void* q, const void* k, long long ldk, const void* v, long long ldv, const void* out,
                             const void* dout, const float* lse, float* delta, float* dq_acc, float* dk_acc,
                             float* dv_acc, void* dq, void* dk, void* dv, const int* kv_tiles, int n_tiles, long long T, int Hq, int Hk, int D, float scale,
                             int causal, int with_dq, void* stream_ptr) {
   if ((D != 128 && D != 192) || Hq % Hk) return 901;
+  const int group_loop = with_dq == 2;
+  if (group_loop) with_dq = 0;
   if (with_dq && D != 128) return 904;
   if ((ldk % 8) || (ldv % 8)) return 902;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_ptr);
@@ -523,8 +530,8 @@ TTB_EXPORT int ttb_attn_bwd(const void* q, const void* k, long long ldk, const v
     uint32_t box[2] = {static_cast<uint32_t>(D), 64};
     if (make_tmap_f32_linear(&tdq, dq_acc, 2, dims, str, box)) return 105;
   }
-  if (Hq != Hk && (dk_acc == nullptr || dv_acc == nullptr)) return 903;
-  AttnBwdParams p{kv_tiles, lse, delta, dq_acc, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, dk_acc, dv_acc, Hq, Hk, T, scale, causal};
+  if (Hq != Hk && !group_loop && (dk_acc == nullptr || dv_acc == nullptr)) return 903;
+  AttnBwdParams p{kv_tiles, lse, delta, dq_acc, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, dk_acc, dv_acc, Hq, Hk, T, scale, causal, group_loop};
   const int rc = with_dq ? launch_attn_bwd<128, true>(tq, tdo, tk, tv, tdq, p, n_tiles, stream)
                          : (D == 128 ? launch_attn_bwd<128, false>(tq, tdo, tk, tv, tdq, p, n_tiles, stream)
                                      : launch_attn_bwd<192, false>(tq, tdo, tk, tv, tdq, p, n_tiles, stream));
@@ -533,7 +540,7 @@ TTB_EXPORT int ttb_attn_bwd(const void* q, const void* k, long long ldk, const v
     const long long n = T * Hq * D;
     attn_bwd_cast_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, stream>>>(dq_acc, (__nv_bfloat16*)dq, n);
   }
-  if (Hq != Hk) {
+  if (Hq != Hk && !group_loop) {
     const long long nk = T * Hk * D, nv = T * Hk * BW_D;
     attn_bwd_cast_kernel<<<(unsigned)((nk / 8 + 255) / 256), 256, 0, stream>>>(dk_acc, (__nv_bfloat16*)dk, nk);
     attn_bwd_cast_kernel<<<(unsigned)((nv / 8 + 255) / 256), 256, 0, stream>>>(dv_acc, (__nv_bfloat16*)dv, nv);

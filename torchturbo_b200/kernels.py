@@ -916,10 +916,12 @@ def attn_bwd(dout, q, k, v, out, lse, kv_tiles_dev, *, scale: float, causal: boo
              deterministic: bool = False):
     """Gradients of `attn_fwd`.  Returns (dq [T,Hq,D], dk [T,Hk,D], dv [T,Hk,128]) in bf16.
 
-    128-wide heads by default: one kernel; dQ tiles are added into an fp32 scratch buffer by TMA reductions (the order
-    of the adds is not fixed).  With `deterministic=True`, and always for 192-wide query / key heads, that kernel
-    computes dK / dV only and dQ comes from the query-major pass (`q_tiles_dev` required), which writes every dQ tile
-    once; with grouped-query attention the dK / dV sums over the query heads of a group still use atomics."""
+    128-wide heads by default: one kernel; dQ tiles are added into an fp32 scratch buffer by TMA reductions and, with
+    grouped-query attention, the dK / dV of a group's query heads are summed with atomics (the order of the adds is not
+    fixed).  For 192-wide query / key heads that kernel computes dK / dV only and dQ comes from the query-major pass
+    (`q_tiles_dev` required), which writes every dQ tile once.  `deterministic=True` uses that split for every width
+    and lets one CTA per kv head walk the query heads of its group, so nothing is reduced with atomics and the result
+    is bit-reproducible."""
     T, Hq, D = q.shape
     Hk = k.shape[1]
     assert dout.is_contiguous() and out.is_contiguous() and q.is_contiguous()
@@ -930,7 +932,7 @@ def attn_bwd(dout, q, k, v, out, lse, kv_tiles_dev, *, scale: float, causal: boo
     delta = torch.empty(Hq * T, dtype=torch.float32, device=q.device)
     dq_acc = None if split else torch.zeros(T, Hq, D, dtype=torch.float32, device=q.device)
     dq = torch.zeros_like(q) if split else torch.empty_like(q)
-    if Hq != Hk:   # query heads of a group add into fp32 accumulators, converted at the end
+    if Hq != Hk and not deterministic:   # query heads of a group add into fp32 accumulators, converted at the end
         dk_acc = torch.zeros(T, Hk, D, dtype=torch.float32, device=q.device)
         dv_acc = torch.zeros(T, Hk, 128, dtype=torch.float32, device=q.device)
         dk = torch.empty(T, Hk, D, dtype=q.dtype, device=q.device)
@@ -944,8 +946,9 @@ def attn_bwd(dout, q, k, v, out, lse, kv_tiles_dev, *, scale: float, causal: boo
                               _p(dout), _p(lse), _p(delta), _p(dq_acc), _p(dk_acc), _p(dv_acc), _p(dq), _p(dk), _p(dv),
                               _p(kv_tiles_dev),
                               C.c_int(kv_tiles_dev.shape[0]), C.c_longlong(T), C.c_int(Hq), C.c_int(Hk), C.c_int(D),
-                              C.c_float(scale), C.c_int(int(causal)), C.c_int(0 if split else 1), _stream()), "ttb_attn_bwd")
-    LAUNCH_COUNT += (1 if split else 2) + (0 if Hq == Hk else 2)
+                              C.c_float(scale), C.c_int(int(causal)), C.c_int((2 if deterministic else 0) if split else 1), _stream()),
+           "ttb_attn_bwd")
+    LAUNCH_COUNT += (1 if split else 2) + (0 if (Hq == Hk or deterministic) else 2)
     if split:
         _check(lib().ttb_attn_bwd_dq(_p(q), _p(k), C.c_longlong(k.stride(0)), _p(v), C.c_longlong(v.stride(0)), _p(dout),
                                      _p(lse), _p(delta), _p(dq), _p(q_tiles_dev), C.c_int(q_tiles_dev.shape[0]),
