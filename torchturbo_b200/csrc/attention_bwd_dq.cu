@@ -74,7 +74,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = blockIdx.x, h = blockIdx.y;
+  const int tile = blockIdx.y, h = blockIdx.x;     // heads vary fastest: the longest tiles of all heads start first
   const int hk = h / (p.Hq / p.Hk);
   const int q0 = p.q_tiles[tile * 3 + 0];
   const int ds = p.q_tiles[tile * 3 + 1];
@@ -289,7 +289,7 @@ static int launch_attn_dq(const CUtensorMap& tq, const CUtensorMap& tdo, const C
   static bool smem_done[16] = {};
   const cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(attn_bwd_dq_kernel<DQK>), DqSmem<DQK>::TOTAL, smem_done);
   if (e != cudaSuccess) return 300 + static_cast<int>(e);
-  dim3 grid(n_tiles, p.Hq);
+  dim3 grid(p.Hq, n_tiles);
   attn_bwd_dq_kernel<DQK><<<grid, 320, DqSmem<DQK>::TOTAL, stream>>>(tq, tdo, tk, tv, p);
   return 0;
 }

@@ -96,7 +96,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   float* s_rowsum = reinterpret_cast<float*>(smem + AttnSmem::ROWSUM);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = blockIdx.x, h = blockIdx.y;
+  // heads vary fastest in launch order: the tile table lists the tiles with the most KV blocks first, so every head's
+  // longest tiles start before any short one, and neighbouring CTAs (the query heads of a group) read the same K / V
+  const int tile = blockIdx.y, h = blockIdx.x;
   const int hk = h / (p.Hq / p.Hk);
   const int q0 = p.q_tiles[tile * 3 + 0];
   const int ds = p.q_tiles[tile * 3 + 1];
@@ -375,7 +377,7 @@ static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const C
   static bool smem_done[16] = {};
   const cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(attn_fwd_kernel<DQK>), AttnSmem<DQK>::TOTAL, smem_done);
   if (e != cudaSuccess) return 300 + static_cast<int>(e);
-  dim3 grid(n_tiles, p.Hq);
+  dim3 grid(p.Hq, n_tiles);
   attn_fwd_kernel<DQK><<<grid, 320, AttnSmem<DQK>::TOTAL, stream>>>(tq, tk, tv, p);
   return 0;
 }
