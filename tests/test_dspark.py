@@ -103,3 +103,32 @@ def test_engine_trains_the_draft_heads_with_the_main_model():
             assert {"dspark/ce", "dspark/l1", "dspark/confidence", "dspark/accept_rate", "dspark/anchors"} <= set(metrics)
             assert 0.0 <= float(metrics["dspark/accept_rate"]) <= 1.0
     assert losses[True] > losses[False]          # the draft objective is added to the language-model loss
+
+
+def test_sequence_parallel_run_says_that_the_draft_heads_are_left_out():
+    import pytest
+
+    m = _model()
+    m.model.sp_size = 2                      # as `set_sequence_parallel` leaves it on a rank of a two-way group
+    seen = {}
+
+    class Stop(Exception):
+        pass
+
+    def trunk(**kw):
+        seen.update(kw)
+        raise Stop
+
+    m.model.forward = trunk                  # the check comes before the trunk runs; no process group is needed
+    ids = torch.randint(0, 90, (1, 12))
+    kw = dict(input_ids=ids, cu_seq_lens_q=torch.tensor([0, 24], dtype=torch.int32), max_length_q=24,
+              dspark_labels=ids.clone(), dspark_config=types.SimpleNamespace(num_anchors=1), skip_lm_head=True)
+    with pytest.warns(RuntimeWarning, match="DSpark draft heads are not trained under sequence parallelism"):
+        with pytest.raises(Stop):
+            m(**kw)
+    assert seen["collect_layers"] is None    # the trunk is not asked for the draft branch's layer states
+    import warnings as w
+    with w.catch_warnings():
+        w.simplefilter("error")              # said once per model, not every step
+        with pytest.raises(Stop):
+            m(**kw)

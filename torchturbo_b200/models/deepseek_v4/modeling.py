@@ -23,6 +23,7 @@ document is not compressed).
 from __future__ import annotations
 
 import math
+import warnings
 from typing import Any
 
 import torch
@@ -569,7 +570,15 @@ class DeepseekV4ForCausalLMBase(nn.Module):
                 max_length_q=None, max_length_k=None, skip_lm_head=False, global_input_ids=None,
                 global_position_ids=None, dspark_labels=None, dspark_config=None, **kw):
         draft = (self.dspark is not None and self.training and dspark_labels is not None and dspark_config is not None
-                 and self.model.sp_size == 1 and input_ids is not None)
+                 and input_ids is not None)
+        if draft and self.model.sp_size > 1:
+            # the draft branch needs a halo of context states from the neighbouring sequence shards, which is not built:
+            # say so once instead of training the main model only without notice
+            if not getattr(self, "_warned_dspark_sp", False):
+                self._warned_dspark_sp = True
+                warnings.warn("DSpark draft heads are not trained under sequence parallelism (sp_size "
+                              f"{self.model.sp_size}): the draft loss is left out of this run", RuntimeWarning, stacklevel=2)
+            draft = False
         hidden, ctx, stream = self.model(input_ids=input_ids, position_ids=position_ids, inputs_embeds=inputs_embeds,
                                     cu_seq_lens_q=cu_seq_lens_q, max_length_q=max_length_q,
                                     global_position_ids=global_position_ids, return_context=True,
